@@ -1,0 +1,243 @@
+"""Headline benchmark: Wan2.2 TI2V-5B-shaped DiT flow-matching training, tokens/s per box.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the unmodified reference installed in baseline/_ref
+
+Config (BASELINE config 2): 30 blocks, dim 3072, 24 heads, FFN 14336, 48 latent channels, patch
+1x2x2; one sample of latent [1,48,31,44,80] (27,280 tokens), text embedding [1,512,4096], bf16,
+logit-normal sigmas with shift 5; Ulysses SP = N over the N GPUs (the one sample is split, so
+scaling is strong), gradients summed over the SP group, AdamW update inside the timed region.
+Synthetic data, random-init weights.
+
+Two timed regions, each of exactly K steps bracketed by barrier + synchronize and timed with
+CUDA events (max over ranks): (1) device-resident inputs -> ``value``; (2) end to end through
+``WanStage0p5Trainer.train_step`` with the host->device copy of the step's inputs from pinned
+memory and a device->host read of the loss every step -> ``e2e``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+BASELINE_TOKENS_PER_S = None  # the reference publishes no tokens/s figure
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="ti2v_5b", choices=["ti2v_5b", "small"])
+    ap.add_argument("--frames", type=int, default=31)
+    ap.add_argument("--height", type=int, default=44)
+    ap.add_argument("--width", type=int, default=80)
+    ap.add_argument("--checkpointing", default="auto", choices=["auto", "none", "full"])
+    ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_config(args):
+    from solarwm_b200.models.wan import WanConfig, wan_preset
+
+    if args.model == "small":
+        return WanConfig(model_type="ti2v", in_dim=48, out_dim=48, dim=512, ffn_dim=2048, num_heads=8,
+                         num_layers=4, text_dim=4096, text_len=512)
+    return wan_preset("ti2v_5b")
+
+
+def make_batch(cfg, args, pinned=True):
+    import torch
+
+    g = torch.Generator().manual_seed(1234)
+    lat = torch.randn(1, args.frames, cfg.in_dim, args.height, args.width, generator=g).to(torch.bfloat16)
+    txt = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(torch.bfloat16)
+    if pinned:
+        lat, txt = lat.pin_memory(), txt.pin_memory()
+    return {"latents": lat, "text": txt}
+
+
+def timed_region(steps, fn, dist, torch):
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = torch.tensor([start.elapsed_time(stop)], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def run_ours(args):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dist = None
+    sp = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+        from solarwm_b200.parallel.ulysses import UlyssesCollective
+
+        sp = UlyssesCollective(None)
+
+    from solarwm_b200 import ops
+    from solarwm_b200.backends.wan22.stage0p5 import Stage0p5Options, WanStage0p5Trainer
+
+    if args.attention:
+        ops.set_backend(args.attention)
+    cfg = model_config(args)
+    ckpt = args.checkpointing
+    if ckpt == "auto":
+        ckpt = "full" if (args.model == "ti2v_5b" and world < 4) else "none"
+    opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
+                           max_grad_norm=1.0, seed=0)
+    trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp)
+    with torch.no_grad():  # a zero head would zero every upstream gradient; keep the step representative
+        trainer.model.get_parameter("head.head.weight").normal_(0, 0.02)
+    batch = make_batch(cfg, args)
+    dev_batch = {k: v.to(f"cuda:{local}") for k, v in batch.items()}
+    tokens = args.frames * (args.height // 2) * (args.width // 2)
+    h2d = sum(v.numel() * v.element_size() for v in batch.values())
+
+    def step_device():
+        trainer.train_step(dev_batch)
+
+    losses = []
+
+    def step_e2e():
+        loss = trainer.train_step(batch)
+        losses.append(float(loss.item()))  # device -> host read of the step's result
+
+    for _ in range(args.warmup):
+        step_e2e()
+    ops.check_status(f"cuda:{local}")
+    sampler = ClockSampler(local)
+    sampler.start()
+    ops.reset_counters()
+    ms = timed_region(args.steps, step_device, dist, torch)
+    launches = ops.total_launches()
+    counters = dict(ops.COUNTERS)
+    ms_e2e = timed_region(args.steps, step_e2e, dist, torch)
+    clocks = sampler.stop()
+    ops.check_status(f"cuda:{local}")
+    peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
+    if rank == 0:
+        value = tokens * args.steps / (ms / 1e3)
+        e2e = tokens * args.steps / (ms_e2e / 1e3)
+        out = {
+            "metric": "DiT train tokens/s/box (Wan2.2 TI2V-5B-shaped flow-matching step)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None if BASELINE_TOKENS_PER_S is None else value / BASELINE_TOKENS_PER_S,
+            "dtype": "bf16", "data": "synthetic latents/text of the named shapes, random-init weights",
+            "impl": "ours",
+            "config": {"model": "wan22_ti2v_5b-shaped" if args.model == "ti2v_5b" else "small-debug",
+                       "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}",
+                       "latent": [1, cfg.in_dim, args.frames, args.height, args.width],
+                       "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt,
+                       "attention_backend": ops.get_backend(), "optimizer": "AdamW fp32 master (in timed region)",
+                       "l2": "no flush: per-step working set (>=10 GB of weights) exceeds the 126 MB L2",
+                       "peak_allocated_gib": round(peak_gib, 2)},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "launch_counters": counters,
+            "final_loss": losses[-1] if losses else None,
+        }
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        sys.path.insert(0, str(ROOT / "baseline"))
+        try:
+            import reference_arm
+        except Exception as exc:  # noqa: BLE001
+            print(json.dumps({"impl": "reference", "unavailable": f"reference arm import failed: {exc!r}"[:300]}))
+            return 0
+        return reference_arm.run(args)
+    run_ours(args)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

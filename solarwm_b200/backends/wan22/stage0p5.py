@@ -1,0 +1,122 @@
+"""Wan Stage0.5: bidirectional flow-matching training step.
+
+One call of ``train_step`` does what the reference's ``Wan5BStage0p5Runtime.train_microbatch`` +
+``prepare_optimizer_step`` + ``optimizer_step`` do (solar/backends/wan22/runtime/stage0p5.py:148-383):
+copy the batch from pinned host memory, sample per-video timesteps, broadcast the sampled
+tensors inside the SP group, build ``x_t`` / velocity target with the fused scheduler kernel,
+run the DiT forward and backward, sum gradients over the SP group, clip by global norm and
+apply the sharded fused AdamW (+EMA) update.
+
+TI2V semantics: frame 0 is a clean image condition (timestep 0, excluded from the loss) unless
+the sample's image condition is dropped.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ... import ops
+from ...engine.flow import FlowMatchScheduler, first_frame_loss_mask, logit_normal_sigmas
+from ...engine.optim import FlatAdamW
+from ...models.wan import WanConfig, WanDiT
+
+
+@dataclass
+class Stage0p5Options:
+    lr: float = 1e-4
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    max_grad_norm: Optional[float] = 1.0
+    timestep_shift: float = 5.0
+    sigma_sampling: str = "logit_normal"      # or "uniform_index" (reference randint over the 1000-grid)
+    ti2v_first_frame_clean: bool = True
+    image_dropout: float = 0.0
+    grad_accum: int = 1
+    ema_decay: Optional[float] = None
+    checkpointing: str = "none"
+    seed: int = 0
+
+
+class WanStage0p5Trainer:
+    def __init__(self, cfg: WanConfig, device, opts: Stage0p5Options = Stage0p5Options(), sp=None,
+                 dtype=torch.bfloat16, model: Optional[WanDiT] = None):
+        self.cfg, self.opts, self.device = cfg, opts, torch.device(device)
+        self.sp = sp
+        self.sp_size = 1 if sp is None else sp.size
+        self.model = model or WanDiT(cfg, device=device, dtype=dtype, seed=opts.seed)
+        if sp is not None:
+            self.model.sp = sp
+        self.model.checkpointing = opts.checkpointing
+        self.model.ensure_grads()
+        self.optimizer = FlatAdamW(self.model.units(), lr=opts.lr, betas=opts.betas, eps=opts.eps,
+                                   weight_decay=opts.weight_decay, ema_decay=opts.ema_decay)
+        self.scheduler = FlowMatchScheduler(shift=opts.timestep_shift)
+        self.gen = torch.Generator(device=self.device).manual_seed(opts.seed * 100003)
+        self.global_step = 0
+        self.last_grad_norm = None
+
+    # ------------------------------------------------------------------------------------
+    def sample_timesteps(self, B: int) -> torch.Tensor:
+        """One timestep per video on the 1000-step grid (values in [0, 1000])."""
+        if self.opts.sigma_sampling == "uniform_index":
+            idx = torch.randint(0, self.scheduler.num_train_timesteps, (B,), generator=self.gen, device=self.device)
+            return self.scheduler.timesteps.to(self.device)[idx]
+        s = logit_normal_sigmas(B, self.opts.timestep_shift, generator=self.gen, device=self.device)
+        return s * self.scheduler.num_train_timesteps
+
+    def microbatch(self, latents: torch.Tensor, text: torch.Tensor, y: Optional[torch.Tensor] = None):
+        """latents [B, F, C, H, W] (frame-major, as stored by the data plane); text [B, T, text_dim]."""
+        o = self.opts
+        B, F = latents.shape[:2]
+        t_video = self.sample_timesteps(B)
+        noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32).to(latents.dtype)
+        dropped = torch.rand(B, generator=self.gen, device=self.device) < o.image_dropout
+        if self.sp is not None and self.sp.size > 1:
+            d8 = dropped.to(torch.uint8)
+            self.sp.broadcast_(t_video, noise, d8)
+            dropped = d8.bool()
+        t = t_video.view(B, 1).expand(B, F).clone()
+        if o.ti2v_first_frame_clean and self.cfg.model_type == "ti2v":
+            t[:, 0] = torch.where(dropped, t[:, 0], torch.zeros_like(t[:, 0]))
+            mask = first_frame_loss_mask(B, F, dropped).to(self.device)
+        else:
+            mask = torch.ones((B, F), dtype=torch.bool, device=self.device)
+        sigma = (t / self.scheduler.num_train_timesteps).float().reshape(B * F)
+        x_t, target = ops.add_noise(latents.reshape(B * F, *latents.shape[2:]),
+                                    noise.reshape(B * F, *latents.shape[2:]), sigma)
+        x_in = x_t.view(B, F, *latents.shape[2:]).permute(0, 2, 1, 3, 4)
+        y_in = None if y is None else y.permute(0, 2, 1, 3, 4)
+        pred = self.model(x_in, t, text, y=y_in)                       # [B, C, F, H, W]
+        pred = pred.permute(0, 2, 1, 3, 4).reshape(B * F, *pred.shape[1:2], *pred.shape[3:]).contiguous()
+        weight = self.scheduler.training_weight(t_video).view(B, 1).expand(B, F).reshape(B * F)
+        loss = ops.weighted_masked_mse(pred, target[:, :pred.shape[1]], weight.float(),
+                                       mask.reshape(B * F).float())
+        (loss / (o.grad_accum * self.sp_size)).backward()
+        return loss.detach()
+
+    def optimizer_step(self) -> torch.Tensor:
+        self.model.finalize_grads()
+        opt = self.optimizer
+        if self.sp is not None and self.sp.size > 1:
+            self.sp.sum_gradients_([g for u in self.model.units() for g in (u.grad, u.grad_v)])
+        norm = opt.local_grad_sumsq().sqrt()
+        opt.set_clip(norm, self.opts.max_grad_norm)
+        opt.step()
+        self.model.zero_grads()
+        self.global_step += 1
+        self.last_grad_norm = norm
+        return norm
+
+    def train_step(self, batch: dict) -> torch.Tensor:
+        """batch: pinned host (or device) tensors ``latents`` [B,F,C,H,W], ``text`` [B,T,text_dim], optional ``y``."""
+        dev = self.device
+        lat = batch["latents"].to(dev, non_blocking=True)
+        txt = batch["text"].to(dev, non_blocking=True)
+        y = batch.get("y")
+        y = None if y is None else y.to(dev, non_blocking=True)
+        loss = self.microbatch(lat, txt, y)
+        self.optimizer_step()
+        return loss

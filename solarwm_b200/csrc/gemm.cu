@@ -1,0 +1,363 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma
+// with fp32 accumulators in TMEM -> tcgen05.ld epilogue -> TMA store.
+//
+//   C[M,N] (+)= op(A)[M,K] * op(B)[K,N]   (+ bias[N]) (-> GELU-tanh)
+//
+// Three operand layouts cover a linear layer's forward, data gradient and weight
+// gradient without any transposed copy in global memory:
+//   NT : A [M,K] row-major (K-major),  B [N,K] row-major (K-major)   y  = x  W^T
+//   NN : A [M,K] row-major (K-major),  B [K,N] row-major (MN-major)  dx = dy W
+//   TN : A [K,M] row-major (MN-major), B [K,N] row-major (MN-major)  dW = dy^T x
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 allocates TMEM and issues the MMAs
+// (one elected thread), warps 2..5 drain TMEM (each warp owns the 32 TMEM lanes its
+// rank-in-warpgroup may touch) and store through shared memory with TMA.  Two 256-column
+// accumulators double-buffer the epilogue against the next tile's main loop.
+//
+// Replaces the cuBLAS calls behind every nn.Linear of the reference models
+// (reference: solar/backends/wan22/runtime/modeling/model.py:112-147, 230-233).
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace solar {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;              // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;              // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KiB
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_BUF_BYTES = 32 * 128;           // one warp, 32 rows x 128 B
+constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;  // 32 KiB
+constexpr int SMEM_MAIN = STAGES * STAGE_BYTES + EPI_BYTES;
+constexpr int SMEM_TOTAL = SMEM_MAIN + 256 + 1024;  // barriers + alignment slack
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct GemmParams {
+  int M, N, K;
+  int tiles_m, tiles_n;
+  const __nv_bfloat16* bias;  // [N] or null
+  int act;                    // 0 none, 1 gelu-tanh
+  int accumulate;             // 1: C += result (TMA reduce-add)
+  int* status;                // device status word (0 = ok)
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // Groups of 8 M-tiles sweep N together so that the CTAs running at the same time share
+  // A and B tiles in L2.
+  constexpr int G = 8;
+  const int per_group = G * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * G;
+  const int rows = min(G, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + SMEM_MAIN);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], EPI_WARPS * 32);
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, ST_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (64 * BK * 2), &tmA, &full_bar[stage], m0 + c * 64, k0);
+          } else {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * BK * 2), &tmB, &full_bar[stage], n0 + c * 64, k0);
+          } else {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_word, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word, ST_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t adesc = A_MN ? umma_desc_mnmajor(sa + kk * 2048, 64 * BK * 2)
+                                        : umma_desc_kmajor(sa + kk * 32);
+            const uint64_t bdesc = B_MN ? umma_desc_mnmajor(sb + kk * 2048, 64 * BK * 2)
+                                        : umma_desc_kmajor(sb + kk * 32);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint8_t* my_buf = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
+    constexpr int CHUNK = OUT_F32 ? 32 : 64;  // columns per 128-byte staged row
+    int local = 0;
+    int buf = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const bool rows_live = (m0 + q * 32) < p.M;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+        const int ncol = n0 + c0;
+        if (ncol >= p.N) break;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* dst = my_buf + buf * EPI_BUF_BYTES + lane * 128;
+        if (OUT_F32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = __uint_as_float(r[g * 4 + e]);
+            if (p.bias != nullptr && ncol + g * 4 < p.N) {
+              const uint2 bb = *reinterpret_cast<const uint2*>(p.bias + ncol + g * 4);
+              const float2 b01 = unpack_bf16x2(bb.x), b23 = unpack_bf16x2(bb.y);
+              v[0] += b01.x; v[1] += b01.y; v[2] += b23.x; v[3] += b23.y;
+            }
+            if (p.act == 1) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) v[e] = gelu_tanh(v[e]);
+            }
+            uint4 o = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]),
+                                 __float_as_uint(v[2]), __float_as_uint(v[3]));
+            *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
+          }
+        } else {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c0, r0);
+          tmem_ld_32x32(t_row + c0 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              v[e] = __uint_as_float(g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e]);
+            if (p.bias != nullptr && ncol + g * 8 < p.N) {
+              const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + ncol + g * 8);
+              const float2 b0 = unpack_bf16x2(bb.x), b1 = unpack_bf16x2(bb.y),
+                           b2 = unpack_bf16x2(bb.z), b3 = unpack_bf16x2(bb.w);
+              v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y;
+              v[4] += b2.x; v[5] += b2.y; v[6] += b3.x; v[7] += b3.y;
+            }
+            if (p.act == 1) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+            }
+            uint4 o = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                 pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+            *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && rows_live) {
+          const void* src = my_buf + buf * EPI_BUF_BYTES;
+          if (p.accumulate) {
+            asm volatile(
+                "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::
+                    "l"(reinterpret_cast<uint64_t>(&tmC)),
+                "r"(smem_u32(src)), "r"(ncol), "r"(m0 + q * 32)
+                : "memory");
+          } else {
+            tma_store_2d(&tmC, src, ncol, m0 + q * 32);
+          }
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty_bar[acc]);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_word != 0) bounded_drain_pause();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicExch(p.status, *abort_word);
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
+                       const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+    configured = true;
+  }
+  int grid = p.tiles_m * p.tiles_n;
+  int cap = max_ctas > 0 ? max_ctas : sm_count();
+  if (grid > cap) grid = cap;
+  kern<<<grid, GEMM_THREADS, SMEM_TOTAL, stream>>>(tA, tB, tC, p);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace solar
+
+using namespace solar;
+
+// layout: 0 = NT, 1 = NN, 2 = TN (see the header comment).  lda/ldb/ldc are leading
+// dimensions in elements of the row-major arrays as they sit in memory.
+// out_f32: C is fp32 instead of bf16.  accumulate: C += (atomic-free TMA reduce-add).
+// status: optional device int that receives a non-zero code if a bounded wait gave up.
+extern "C" int solar_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N,
+                               int K, long long lda, long long ldb, long long ldc, int layout,
+                               int act, int out_f32, int accumulate, int* status, int max_ctas,
+                               void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: empty problem%s");
+  if (N % 8 != 0) return fail("gemm: N must be a multiple of 8%s");
+  if (layout < 0 || layout > 2) return fail("gemm: bad layout%s");
+  CUtensorMap tA, tB, tC;
+  int rc;
+  const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (layout == 2) {  // A stored [K, M]
+    rc = make_tmap_2d(&tA, A, bf, 2, K, M, lda, BK, 64);
+  } else {            // A stored [M, K]
+    rc = make_tmap_2d(&tA, A, bf, 2, M, K, lda, BM, BK);
+  }
+  if (rc) return rc;
+  if (layout == 0) {  // B stored [N, K]
+    rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, BN, BK);
+  } else {            // B stored [K, N]
+    rc = make_tmap_2d(&tB, B, bf, 2, K, N, ldb, BK, 64);
+  }
+  if (rc) return rc;
+  if (out_f32) {
+    rc = make_tmap_2d(&tC, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32);
+  } else {
+    rc = make_tmap_2d(&tC, C, bf, 2, M, N, ldc, 32, 64);
+  }
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.act = act;
+  p.accumulate = accumulate;
+  p.status = status;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (layout * 2 + (out_f32 ? 1 : 0)) {
+    case 0: return launch_gemm<0, 0, 0>(tA, tB, tC, p, max_ctas, st);
+    case 1: return launch_gemm<0, 0, 1>(tA, tB, tC, p, max_ctas, st);
+    case 2: return launch_gemm<0, 1, 0>(tA, tB, tC, p, max_ctas, st);
+    case 3: return launch_gemm<0, 1, 1>(tA, tB, tC, p, max_ctas, st);
+    case 4: return launch_gemm<1, 1, 0>(tA, tB, tC, p, max_ctas, st);
+    default: return launch_gemm<1, 1, 1>(tA, tB, tC, p, max_ctas, st);
+  }
+}
+
+extern "C" const char* solar_last_error() { return last_error_buf(); }

@@ -1,0 +1,101 @@
+// Host-side helpers shared by the launchers: error reporting through a thread-local
+// message (the C entry points return 0 on success and a negative code otherwise),
+// TMA tensor-map encoding through the driver entry point, SM count cache.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace solar {
+
+inline char* last_error_buf() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+inline int fail(const char* fmt, const char* a = "", long long b = 0, long long c = 0) {
+  snprintf(last_error_buf(), 512, fmt, a, b, c);
+  return -1;
+}
+
+#define SOLAR_CUDA_OK(expr)                                                         \
+  do {                                                                              \
+    cudaError_t _e = (expr);                                                        \
+    if (_e != cudaSuccess) {                                                        \
+      snprintf(::solar::last_error_buf(), 512, "%s failed: %s (%s:%d)", #expr,      \
+               cudaGetErrorString(_e), __FILE__, __LINE__);                         \
+      return -2;                                                                    \
+    }                                                                               \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Row-major 2-D tensor [rows, cols] with leading dimension `ld` (elements); the box is
+// [box_rows, box_cols] and is stored in shared memory with the 128-byte swizzle, so
+// box_cols * elt_bytes must equal 128.
+inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elt_bytes,
+                        uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                        uint32_t box_cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail("cuTensorMapEncodeTiled entry point not available%s");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail("TMA base not 16-byte aligned%s");
+  if ((ld * elt_bytes) % 16 != 0) return fail("TMA row stride not a multiple of 16 bytes%s");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elt_bytes)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed (code %s%lld)", "", (long long)r);
+  return 0;
+}
+
+// 3-D tensor [d2, d1, d0] (d0 innermost) with byte strides s1 (for d1) and s2 (for d2).
+inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elt_bytes,
+                        uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes, uint64_t s2_bytes,
+                        uint32_t b0, uint32_t b1, uint32_t b2) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail("cuTensorMapEncodeTiled entry point not available%s");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail("TMA base not 16-byte aligned%s");
+  if (s1_bytes % 16 != 0 || s2_bytes % 16 != 0) return fail("TMA stride not a multiple of 16 bytes%s");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  (void)elt_bytes;
+  CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled(3d) failed (code %s%lld)", "", (long long)r);
+  return 0;
+}
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace solar

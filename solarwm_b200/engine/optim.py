@@ -1,0 +1,116 @@
+"""Sharded fp32-master AdamW over flat parameter units, one fused kernel launch per buffer.
+
+State per unit (only the slice this rank owns when sharded): fp32 master copy of the bf16
+matrices, fp32 first/second moments, optional fp32 EMA shadow.  ``step`` applies decoupled weight
+decay, the Adam update, refreshes the bf16 live parameters and the EMA in a single pass over
+memory (``csrc/pointwise.cu: adamw_kernel``); the gradient scale (clip coefficient) and a
+skip flag are read from device memory, so clipping needs no host round trip.
+
+Reference behaviour: ``FP32MasterAdamW`` (solar/training/optim.py:18-226) loops over parameters
+with ~8 element-wise kernels each, ``ShardedEMA.update`` (solar/training/ema.py:71-81) adds a
+``mul_/add_`` pair per parameter; both are folded into the one kernel here.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+
+from .. import ops
+
+
+def shard_bounds(numel: int, rank: int, world: int):
+    per = numel // world
+    assert per * world == numel, "flat units must be padded to a multiple of the shard count"
+    return rank * per, (rank + 1) * per
+
+
+class FlatAdamW:
+    def __init__(self, units: Iterable, *, lr: float = 1e-4, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, shard_rank: int = 0, shard_world: int = 1,
+                 ema_decay: Optional[float] = None):
+        self.units = list(units)
+        self.lr, self.betas, self.eps, self.weight_decay = float(lr), tuple(betas), float(eps), float(weight_decay)
+        self.shard_rank, self.shard_world = int(shard_rank), int(shard_world)
+        self.ema_decay = ema_decay
+        self.step_count = 0
+        self.state = []
+        for u in self.units:
+            entry = {}
+            for key, buf in (("m", u.flat), ("v", u.flat_v)):
+                a, b = shard_bounds(buf.numel(), self.shard_rank, self.shard_world)
+                live = buf[a:b]
+                needs_master = live.dtype != torch.float32
+                entry[key] = {
+                    "range": (a, b),
+                    "master": live.float().clone() if needs_master else None,
+                    "exp_avg": torch.zeros(b - a, dtype=torch.float32, device=live.device),
+                    "exp_avg_sq": torch.zeros(b - a, dtype=torch.float32, device=live.device),
+                    "ema": live.float().clone() if ema_decay is not None else None,
+                }
+            self.state.append(entry)
+        dev = self.units[0].device
+        self._norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._scale = torch.ones(1, dtype=torch.float32, device=dev)
+        self._skip = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    # gradients ---------------------------------------------------------------------------
+    def _grad_shards(self):
+        for u, st in zip(self.units, self.state):
+            for key, g in (("m", u.grad), ("v", u.grad_v)):
+                a, b = st[key]["range"]
+                yield g[a:b]
+
+    def local_grad_sumsq(self) -> torch.Tensor:
+        """Sum of squares of this rank's gradient shards (device scalar, no host sync)."""
+        first = True
+        for g in self._grad_shards():
+            ops.sumsq(g, out=self._norm_sq, accumulate=not first)
+            first = False
+        return self._norm_sq
+
+    def set_clip(self, total_norm: torch.Tensor, max_norm: Optional[float]) -> None:
+        """clip coefficient min(1, max_norm / (norm + 1e-6)); a non-finite norm raises the skip flag."""
+        finite = torch.isfinite(total_norm)
+        self._skip.copy_((~finite).to(torch.int32).view(1))
+        if max_norm is None:
+            self._scale.fill_(1.0)
+        else:
+            self._scale.copy_(torch.clamp(max_norm / (total_norm + 1e-6), max=1.0).view(1))
+
+    # update ------------------------------------------------------------------------------
+    def step(self) -> None:
+        self.step_count += 1
+        b1, b2 = self.betas
+        for u, st in zip(self.units, self.state):
+            for key, buf, g in (("m", u.flat, u.grad), ("v", u.flat_v, u.grad_v)):
+                s = st[key]
+                a, b = s["range"]
+                live = buf[a:b]
+                master = s["master"] if s["master"] is not None else live
+                ops.adamw_(master, s["exp_avg"], s["exp_avg_sq"], g[a:b],
+                           live=live if s["master"] is not None else None, ema=s["ema"], lr=self.lr,
+                           beta1=b1, beta2=b2, eps=self.eps, wd=self.weight_decay, step=self.step_count,
+                           grad_scale=self._scale, skip=self._skip,
+                           ema_decay=0.0 if self.ema_decay is None else self.ema_decay)
+
+    # state -------------------------------------------------------------------------------
+    def state_dict(self):
+        out = {"step": self.step_count, "lr": self.lr, "betas": self.betas, "eps": self.eps,
+               "weight_decay": self.weight_decay, "shard": (self.shard_rank, self.shard_world), "units": []}
+        for st in self.state:
+            out["units"].append({k: {n: (t if not torch.is_tensor(t) else t.detach().cpu())
+                                     for n, t in s.items()} for k, s in st.items()})
+        return out
+
+    def load_state_dict(self, state) -> None:
+        if tuple(state["shard"]) != (self.shard_rank, self.shard_world):
+            raise ValueError("optimizer shard layout differs from the checkpoint")
+        self.step_count = int(state["step"])
+        for st, saved in zip(self.state, state["units"]):
+            for k in ("m", "v"):
+                for n in ("master", "exp_avg", "exp_avg_sq", "ema"):
+                    if st[k][n] is not None and saved[k][n] is not None:
+                        if st[k][n].dtype != saved[k][n].dtype:
+                            raise ValueError("optimizer state dtype mismatch (casting is refused)")
+                        st[k][n].copy_(saved[k][n])

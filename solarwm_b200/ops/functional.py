@@ -1,0 +1,651 @@
+"""Autograd-aware front ends of the native sm_100a kernels.
+
+Every op takes 2-D ``[rows, features]`` bf16 activations.  On CUDA tensors the native kernel
+is launched (and a launch counter is bumped); on CPU tensors the PyTorch statement from
+``ops.reference`` runs, which is what the gloo/CPU tests exercise.  There is no silent
+fallback on CUDA: if the native library cannot be loaded the call raises.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib, reference
+from ._lib import c_float, c_int, c_ll, check, count, ptr, stream_handle
+
+NT, NN, TN = 0, 1, 2
+
+_status: dict[int, torch.Tensor] = {}
+_scratch: dict[int, torch.Tensor] = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits set when a wait gave up."""
+    idx = torch.device(device).index or 0
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[idx]
+
+
+def check_status(device="cuda") -> None:
+    """Synchronising check of the bounded-wait status word (0 = every wait completed)."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise _lib.NativeError(f"a device-side bounded wait gave up (code {code})")
+
+
+def _scratch_f32(device, n=2048) -> torch.Tensor:
+    idx = torch.device(device).index or 0
+    if idx not in _scratch or _scratch[idx].numel() < n:
+        _scratch[idx] = torch.empty(n, dtype=torch.float32, device=device)
+    return _scratch[idx]
+
+
+def _rowmajor(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        raise ValueError(f"expected a 2-D tensor, got {tuple(t.shape)}")
+    if t.stride(1) != 1 or (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+# --------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------
+def gemm(a, b, layout=NT, *, bias=None, act=None, out=None, out_dtype=None, accumulate=False,
+         max_ctas=0):
+    """C = op(A) op(B) with bf16 operands and fp32 accumulation.
+
+    layout NT: a [M,K], b [N,K];  NN: a [M,K], b [K,N];  TN: a [K,M], b [K,N].
+    """
+    if not a.is_cuda:
+        af, bf = a.float(), b.float()
+        c = af @ bf.t() if layout == NT else (af @ bf if layout == NN else af.t() @ bf)
+        if bias is not None:
+            c = c + bias.float()
+        if act == "gelu":
+            c = torch.nn.functional.gelu(c, approximate="tanh")
+        dt = out_dtype or (out.dtype if out is not None else a.dtype)
+        if out is not None:
+            if accumulate:
+                out.add_(c.to(out.dtype))
+            else:
+                out.copy_(c.to(out.dtype))
+            return out
+        return c.to(dt)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm operands must be bf16"
+    a = _rowmajor(a)
+    b = _rowmajor(b)
+    if layout == NT:
+        M, K = a.shape
+        N, K2 = b.shape
+    elif layout == NN:
+        M, K = a.shape
+        K2, N = b.shape
+    else:
+        K, M = a.shape
+        K2, N = b.shape
+    if K != K2:
+        raise ValueError(f"gemm inner dimensions differ: {K} vs {K2}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
+        accumulate = False
+    else:
+        if out.shape != (M, N) or out.stride(1) != 1:
+            raise ValueError("gemm: bad output tensor")
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.is_contiguous()
+    lib = _lib.load()
+    rc = lib.solar_gemm_bf16(
+        ptr(a), ptr(b), ptr(out), ptr(bias), c_int(M), c_int(N), c_int(K),
+        c_ll(a.stride(0)), c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(layout),
+        c_int(1 if act == "gelu" else 0), c_int(1 if out.dtype == torch.float32 else 0),
+        c_int(1 if accumulate else 0), ptr(status_word(a.device)), c_int(max_ctas), stream_handle())
+    check(rc, "solar_gemm_bf16")
+    count("gemm")
+    return out
+
+
+def colsum(a, splits=None):
+    """Column sums of a 2-D bf16 tensor -> fp32 [D] (deterministic two-stage reduction)."""
+    if not a.is_cuda:
+        return a.float().sum(0)
+    a = _rowmajor(a)
+    R, D = a.shape
+    splits = splits or max(1, min(64, 600 // max(1, (D + 63) // 64)))
+    part = torch.empty((splits, 1, D), dtype=torch.float32, device=a.device)
+    lib = _lib.load()
+    rc = lib.solar_colreduce(ptr(a), c_ll(a.stride(0)), ptr(None), c_ll(0), ptr(None), ptr(None), ptr(None),
+                             ptr(None), c_ll(0), c_int(0), ptr(part), ptr(None), c_ll(R), c_int(R),
+                             c_int(1), c_int(splits), c_int(D), c_int(3), c_int(0), c_int(1), stream_handle())
+    check(rc, "solar_colreduce")
+    count("colreduce")
+    return part.sum(0).view(D)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = b is not None
+        return gemm(x, w, NT, bias=b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = _rowmajor(dy)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, w, NN)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy, x, TN, out_dtype=w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = colsum(dy)
+        return dx, dw, db
+
+
+def linear(x, w, b=None, act=None):
+    """y = x w^T (+ b) (-> GELU-tanh when act == 'gelu', inference only)."""
+    if not x.is_cuda:
+        return reference.linear(x, w, b, act)
+    if act is not None:
+        if torch.is_grad_enabled() and (x.requires_grad or w.requires_grad):
+            raise RuntimeError("fused activation epilogue is forward-only; use gelu() when training")
+        return gemm(x, w, NT, bias=b, act=act)
+    if hasattr(w, "main_grad"):
+        return _LinearMainGradFn.apply(x, w, b)
+    return _LinearFn.apply(x, w, b)
+
+
+class _LinearMainGradFn(torch.autograd.Function):
+    """Linear whose parameter gradients are written straight into flat ``main_grad`` buffers."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        ctx.save_for_backward(x)
+        ctx.w, ctx.b = w, b
+        return gemm(x, w, NT, bias=b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        w, b = ctx.w, ctx.b
+        dy = _rowmajor(dy)
+        dx = gemm(dy, w, NN) if ctx.needs_input_grad[0] else None
+        if w.requires_grad:
+            gemm(dy, x, TN, out=w.main_grad, accumulate=_grad_is_live(w))
+            _mark_grad_live(w)
+        if b is not None and b.requires_grad:
+            accumulate_main_grad(b, colsum(dy))
+        return dx, None, None
+
+
+def _grad_is_live(p) -> bool:
+    """Has ``main_grad`` of this parameter been written since the last ``zero_grads``?  A fused
+    view over several parameters carries them in ``_anchors`` and shares their state."""
+    anchors = getattr(p, "_anchors", None) or (p,)
+    return bool(getattr(anchors[0], "grad_live", False))
+
+
+def _mark_grad_live(p) -> None:
+    for a in getattr(p, "_anchors", None) or (p,):
+        a.grad_live = True
+
+
+def accumulate_main_grad(p, g) -> None:
+    """Add (or first-write) a gradient into a parameter's flat ``main_grad`` view."""
+    if _grad_is_live(p):
+        p.main_grad.add_(g.to(p.main_grad.dtype).view_as(p.main_grad))
+    else:
+        p.main_grad.copy_(g.view_as(p.main_grad))
+    _mark_grad_live(p)
+
+
+# --------------------------------------------------------------------------------------
+# norm + adaLN modulation
+# --------------------------------------------------------------------------------------
+def _mod_args(shift, scale):
+    if scale is None:
+        return ptr(None), ptr(None), c_ll(0)
+    assert shift.dtype == torch.float32 and scale.dtype == torch.float32
+    assert shift.stride(-1) == 1 and scale.stride(-1) == 1 and shift.stride(0) == scale.stride(0)
+    return ptr(shift), ptr(scale), c_ll(scale.stride(0))
+
+
+def _splits_for(D, groups):
+    blocks = ((D + 63) // 64) * max(groups, 1)
+    return max(1, min(32, 600 // blocks))
+
+
+class _NormModFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shift, scale, w, b, mode, eps, rpg, goff, table):
+        x = _rowmajor(x)
+        R, D = x.shape
+        y = torch.empty((R, D), dtype=x.dtype, device=x.device)
+        stats = torch.empty((R, 2), dtype=torch.float32, device=x.device)
+        sh, sc, ms = _mod_args(shift, scale)
+        lib = _lib.load()
+        rc = lib.solar_norm_modulate_fwd(ptr(x), c_ll(x.stride(0)), ptr(y), c_ll(D), ptr(stats), ptr(w),
+                                         ptr(b), sh, sc, ms, ptr(table), c_int(rpg), c_int(goff),
+                                         c_ll(R), c_int(D), c_float(eps), c_int(mode), stream_handle())
+        check(rc, "solar_norm_modulate_fwd")
+        count("norm_modulate_fwd")
+        ctx.save_for_backward(x, stats, scale, w, b, table)
+        ctx.cfg = (mode, rpg, goff, None if scale is None else scale.shape[0])
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, stats, scale, w, b, table = ctx.saved_tensors
+        mode, rpg, goff, G = ctx.cfg
+        dy = _rowmajor(dy)
+        R, D = x.shape
+        lib = _lib.load()
+        dx = dshift = dscale = dw = db = None
+        _, sc, ms = _mod_args(scale, scale)
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            rc = lib.solar_norm_modulate_bwd(ptr(dy), c_ll(dy.stride(0)), ptr(x), c_ll(x.stride(0)), ptr(dx),
+                                             c_ll(dx.stride(0)), ptr(stats), ptr(w), sc, ms, ptr(table),
+                                             c_int(rpg), c_int(goff), c_ll(R), c_int(D), c_int(mode),
+                                             c_int(0), stream_handle())
+            check(rc, "solar_norm_modulate_bwd")
+            count("norm_modulate_bwd")
+        if scale is not None and (ctx.needs_input_grad[1] or ctx.needs_input_grad[2]):
+            if table is not None:
+                raise RuntimeError("modulation gradients with an explicit group table are not supported")
+            gl = (R + rpg - 1) // rpg
+            splits = _splits_for(D, gl)
+            o0 = torch.empty((splits, gl, D), dtype=torch.float32, device=x.device)
+            o1 = torch.empty_like(o0)
+            rc = lib.solar_colreduce(ptr(dy), c_ll(dy.stride(0)), ptr(x), c_ll(x.stride(0)), ptr(stats), ptr(w),
+                                     ptr(b), ptr(None), c_ll(0), c_int(0), ptr(o0), ptr(o1), c_ll(R),
+                                     c_int(rpg), c_int(gl), c_int(splits), c_int(D), c_int(0), c_int(mode),
+                                     c_int(1), stream_handle())
+            check(rc, "solar_colreduce")
+            count("colreduce")
+            dscale = torch.zeros((G, D), dtype=torch.float32, device=x.device)
+            dshift = torch.zeros_like(dscale)
+            dscale[goff:goff + gl] = o0.sum(0)
+            dshift[goff:goff + gl] = o1.sum(0)
+        if mode >= 1 and w is not None and ctx.needs_input_grad[3]:
+            splits = _splits_for(D, 1)
+            o0 = torch.empty((splits, 1, D), dtype=torch.float32, device=x.device)
+            o1 = torch.empty_like(o0)
+            rc = lib.solar_colreduce(ptr(dy), c_ll(dy.stride(0)), ptr(x), c_ll(x.stride(0)), ptr(stats),
+                                     ptr(None), ptr(None), sc, ms, c_int(goff), ptr(o0), ptr(o1), c_ll(R),
+                                     c_int(R), c_int(1), c_int(splits), c_int(D),
+                                     c_int(1), c_int(mode), c_int(rpg), stream_handle())
+            check(rc, "solar_colreduce")
+            count("colreduce")
+            dw = o0.sum(0).view(D)
+            if mode == 2:
+                db = o1.sum(0).view(D)
+        return dx, dshift, dscale, dw, db, None, None, None, None, None
+
+
+def norm_modulate(x, shift=None, scale=None, *, mode=0, w=None, b=None, eps=1e-6, rows_per_group=1,
+                  group_offset=0, table=None):
+    """y = norm(x) [*w + b] * (1 + scale[g]) + shift[g];  shift/scale are fp32 ``[G, D]`` views."""
+    if not x.is_cuda:
+        return reference.norm_modulate(x, shift, scale, mode=mode, w=w, b=b, eps=eps,
+                                       rows_per_group=rows_per_group, group_offset=group_offset, table=table)
+    if mode >= 1 and scale is not None and w is not None and w.requires_grad and torch.is_grad_enabled():
+        # dw with modulation needs the per-row scale; colreduce kind 1 handles contiguous groups only.
+        if table is not None:
+            raise RuntimeError("trainable norm weight with a group table is not supported")
+    return _NormModFn.apply(x, shift, scale, w, b, int(mode), float(eps), int(rows_per_group),
+                            int(group_offset), table)
+
+
+class _GatedResidualFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, res, y, gate, rpg, goff, table):
+        res = _rowmajor(res)
+        y = _rowmajor(y)
+        R, D = res.shape
+        out = torch.empty((R, D), dtype=res.dtype, device=res.device)
+        lib = _lib.load()
+        gs = c_ll(0 if gate is None else gate.stride(0))
+        rc = lib.solar_gated_residual(ptr(res), c_ll(res.stride(0)), ptr(y), c_ll(y.stride(0)), ptr(out),
+                                      c_ll(D), ptr(gate), gs, ptr(table), c_int(rpg), c_int(goff), c_ll(R),
+                                      c_int(D), c_int(0), stream_handle())
+        check(rc, "solar_gated_residual")
+        count("gated_residual")
+        need_y = gate is not None and gate.requires_grad
+        ctx.save_for_backward(y if need_y else None, gate, table)
+        ctx.cfg = (rpg, goff)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, gate, table = ctx.saved_tensors
+        rpg, goff = ctx.cfg
+        dout = _rowmajor(dout)
+        R, D = dout.shape
+        lib = _lib.load()
+        dy = dgate = None
+        if ctx.needs_input_grad[1]:
+            if gate is None:
+                dy = dout
+            else:
+                dy = torch.empty_like(dout)
+                rc = lib.solar_gated_residual(ptr(None), c_ll(0), ptr(dout), c_ll(dout.stride(0)), ptr(dy),
+                                              c_ll(D), ptr(gate), c_ll(gate.stride(0)), ptr(table), c_int(rpg),
+                                              c_int(goff), c_ll(R), c_int(D), c_int(1), stream_handle())
+                check(rc, "solar_gated_residual")
+                count("gated_residual_bwd")
+        if gate is not None and ctx.needs_input_grad[2]:
+            if table is not None:
+                raise RuntimeError("gate gradients with an explicit group table are not supported")
+            gl = (R + rpg - 1) // rpg
+            splits = _splits_for(D, gl)
+            o0 = torch.empty((splits, gl, D), dtype=torch.float32, device=dout.device)
+            rc = lib.solar_colreduce(ptr(dout), c_ll(dout.stride(0)), ptr(y), c_ll(y.stride(0)), ptr(None),
+                                     ptr(None), ptr(None), ptr(None), c_ll(0), c_int(0), ptr(o0), ptr(None),
+                                     c_ll(R), c_int(rpg), c_int(gl), c_int(splits), c_int(D), c_int(2),
+                                     c_int(0), c_int(1), stream_handle())
+            check(rc, "solar_colreduce")
+            count("colreduce")
+            dgate = torch.zeros((gate.shape[0], D), dtype=torch.float32, device=dout.device)
+            dgate[goff:goff + gl] = o0.sum(0)
+        return dout if ctx.needs_input_grad[0] else None, dy, dgate, None, None, None
+
+
+def gated_residual(res, y, gate=None, *, rows_per_group=1, group_offset=0, table=None):
+    """out = res + gate[g] * y  (gate fp32 ``[G, D]`` view, or None for a plain residual add)."""
+    if not res.is_cuda:
+        return reference.gated_residual(res, y, gate, rows_per_group=rows_per_group,
+                                        group_offset=group_offset, table=table)
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(-1) == 1
+    return _GatedResidualFn.apply(res, y, gate, int(rows_per_group), int(group_offset), table)
+
+
+# --------------------------------------------------------------------------------------
+# full-width RMSNorm + RoPE
+# --------------------------------------------------------------------------------------
+class _RmsRopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, rope, eps, no_norm):
+        x = _rowmajor(x)
+        R, D = x.shape
+        y = torch.empty((R, D), dtype=x.dtype, device=x.device)
+        rstd = torch.empty((R,), dtype=torch.float32, device=x.device)
+        half = 0 if rope is None else rope.shape[1]
+        lib = _lib.load()
+        rc = lib.solar_rmsnorm_rope_fwd(ptr(x), c_ll(x.stride(0)), ptr(y), c_ll(D), ptr(w), ptr(rope),
+                                        c_int(half), ptr(rstd), c_ll(R), c_int(D), c_float(eps),
+                                        c_int(1 if no_norm else 0), stream_handle())
+        check(rc, "solar_rmsnorm_rope_fwd")
+        count("rmsnorm_rope_fwd")
+        ctx.save_for_backward(x, w, rope, rstd)
+        ctx.no_norm = no_norm
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rope, rstd = ctx.saved_tensors
+        dy = _rowmajor(dy)
+        R, D = x.shape
+        half = 0 if rope is None else rope.shape[1]
+        need_dw = (not ctx.no_norm) and w is not None and ctx.needs_input_grad[1]
+        splits = _splits_for(D, 1)
+        part = torch.empty((splits, D), dtype=torch.float32, device=x.device) if need_dw else None
+        dx = torch.empty_like(x)
+        lib = _lib.load()
+        rc = lib.solar_rmsnorm_rope_bwd(ptr(dy), c_ll(dy.stride(0)), ptr(x), c_ll(x.stride(0)), ptr(dx),
+                                        c_ll(dx.stride(0)), ptr(w), ptr(rope), c_int(half), ptr(rstd),
+                                        ptr(part), c_int(splits), c_ll(R), c_int(D),
+                                        c_int(1 if ctx.no_norm else 0), stream_handle())
+        check(rc, "solar_rmsnorm_rope_bwd")
+        count("rmsnorm_rope_bwd")
+        dw = part.sum(0) if need_dw else None
+        return dx, dw, None, None, None
+
+
+def rmsnorm_rope(x, w, rope, *, eps=1e-6, no_norm=False):
+    """Full-width RMSNorm * w then per-head interleaved RoPE; rope fp32 ``[R, hd/2, 2]`` or None."""
+    if not x.is_cuda:
+        return reference.rmsnorm_rope(x, w, rope, eps=eps, no_norm=no_norm)
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.is_contiguous() and rope.shape[0] == x.shape[0]
+    if w is not None:
+        assert w.dtype == torch.float32
+    return _RmsRopeFn.apply(x, w, rope, float(eps), bool(no_norm))
+
+
+# --------------------------------------------------------------------------------------
+# activations
+# --------------------------------------------------------------------------------------
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        lib = _lib.load()
+        check(lib.solar_gelu(ptr(x), ptr(None), ptr(y), ptr(None), c_ll(x.numel()), c_int(0), stream_handle()),
+              "solar_gelu")
+        count("gelu_fwd")
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        lib = _lib.load()
+        check(lib.solar_gelu(ptr(x), ptr(dy), ptr(dx), ptr(None), c_ll(x.numel()), c_int(1), stream_handle()),
+              "solar_gelu")
+        count("gelu_bwd")
+        return dx
+
+
+def gelu(x):
+    if not x.is_cuda:
+        return reference.gelu_tanh(x)
+    return _GeluFn.apply(x)
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        gu = gu.contiguous()
+        M, N2 = gu.shape
+        y = torch.empty((M, N2 // 2), dtype=gu.dtype, device=gu.device)
+        lib = _lib.load()
+        check(lib.solar_swiglu(ptr(gu), ptr(None), ptr(y), c_ll(M), c_int(N2 // 2), c_int(0), stream_handle()),
+              "solar_swiglu")
+        count("swiglu_fwd")
+        ctx.save_for_backward(gu)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        M, N2 = gu.shape
+        dgu = torch.empty_like(gu)
+        lib = _lib.load()
+        check(lib.solar_swiglu(ptr(gu), ptr(dy), ptr(dgu), c_ll(M), c_int(N2 // 2), c_int(1), stream_handle()),
+              "solar_swiglu")
+        count("swiglu_bwd")
+        return dgu
+
+
+def swiglu(gu):
+    """[M, 2N] (gate | up) -> up * silu(gate)."""
+    if not gu.is_cuda:
+        return reference.swiglu(gu)
+    return _SwigluFn.apply(gu)
+
+
+# --------------------------------------------------------------------------------------
+# optimizer / reductions / scheduler math / loss
+# --------------------------------------------------------------------------------------
+def adamw_(master, m, v, grad, *, live=None, ema=None, lr, beta1, beta2, eps, wd, step,
+           grad_scale: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None,
+           ema_decay: float = 0.0):
+    """In-place fused AdamW over flat fp32 shards; refreshes the bf16 live copy and EMA shadow."""
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    if not master.is_cuda:
+        gs = 1.0 if grad_scale is None else float(grad_scale)
+        if skip is not None and int(skip) != 0:
+            return
+        reference.adamw_step(master, m, v, grad, lr=lr, beta1=beta1, beta2=beta2, eps=eps, wd=wd,
+                             step=step, grad_scale=gs)
+        if live is not None:
+            live.copy_(master.to(live.dtype))
+        if ema is not None:
+            ema.mul_(ema_decay).add_(master, alpha=1.0 - ema_decay)
+        return
+    n = master.numel()
+    assert n % 4 == 0 and grad.numel() == n
+    lib = _lib.load()
+    rc = lib.solar_adamw(ptr(master), ptr(m), ptr(v), ptr(live), ptr(ema), ptr(grad),
+                         c_int(1 if grad.dtype == torch.float32 else 0), ptr(grad_scale), ptr(skip), c_ll(n),
+                         c_float(lr), c_float(beta1), c_float(beta2), c_float(eps), c_float(wd),
+                         c_float(bc1), c_float(bc2), c_float(ema_decay), stream_handle())
+    check(rc, "solar_adamw")
+    count("adamw")
+
+
+def sumsq(x, out=None, accumulate=False):
+    """Sum of squares of a flat bf16/fp32 tensor into a 1-element fp32 tensor."""
+    if not x.is_cuda:
+        s = x.float().pow(2).sum().view(1)
+        if out is None:
+            return s
+        out.copy_(out + s if accumulate else s)
+        return out
+    x = x.contiguous().view(-1)
+    assert x.numel() % 8 == 0
+    if out is None:
+        out = torch.zeros(1, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    rc = lib.solar_sumsq(ptr(x), c_int(1 if x.dtype == torch.float32 else 0), c_ll(x.numel()),
+                         ptr(_scratch_f32(x.device)), ptr(out), c_int(1 if accumulate else 0), stream_handle())
+    check(rc, "solar_sumsq")
+    count("sumsq", 2)
+    return out
+
+
+def flow_op(a, b, sigma, sigma2, op, group_size, want_second=False):
+    out0 = torch.empty_like(a)
+    out1 = torch.empty_like(a) if want_second else None
+    lib = _lib.load()
+    rc = lib.solar_flow(ptr(a), ptr(b), ptr(sigma), ptr(sigma2), ptr(out0), ptr(out1), c_ll(a.numel()),
+                        c_ll(group_size), c_int(op), stream_handle())
+    check(rc, "solar_flow")
+    count("flow")
+    return out0, out1
+
+
+def add_noise(x0, noise, sigma):
+    """x_t = (1-s) x0 + s n and velocity target n - x0; sigma fp32 [G], x0 [G, ...]."""
+    G = sigma.numel()
+    if not x0.is_cuda:
+        shape = (G,) + (1,) * (x0.dim() - 1)
+        s = sigma.float().view(shape)
+        return ((1 - s) * x0.float() + s * noise.float()).to(x0.dtype), (noise.float() - x0.float()).to(x0.dtype)
+    x0 = x0.contiguous()
+    noise = noise.contiguous()
+    return flow_op(x0, noise, sigma.contiguous(), None, 0, x0.numel() // G, want_second=True)
+
+
+def flow_to_x0(x_t, v, sigma):
+    G = sigma.numel()
+    if not x_t.is_cuda:
+        s = sigma.float().view((G,) + (1,) * (x_t.dim() - 1))
+        return (x_t.float() - s * v.float()).to(x_t.dtype)
+    return flow_op(x_t.contiguous(), v.contiguous(), sigma.contiguous(), None, 1, x_t.numel() // G)[0]
+
+
+def euler_step(x_t, v, sigma, sigma_next):
+    G = sigma.numel()
+    if not x_t.is_cuda:
+        d = (sigma_next.float() - sigma.float()).view((G,) + (1,) * (x_t.dim() - 1))
+        return (x_t.float() + d * v.float()).to(x_t.dtype)
+    return flow_op(x_t.contiguous(), v.contiguous(), sigma.contiguous(), sigma_next.contiguous(), 2,
+                   x_t.numel() // G)[0]
+
+
+class _MseFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pred, target, weight, mask, denom):
+        pred = pred.contiguous()
+        target = target.contiguous()
+        G = pred.shape[0]
+        loss = torch.empty(1, dtype=torch.float32, device=pred.device)
+        lib = _lib.load()
+        rc = lib.solar_mse(ptr(pred), ptr(target), ptr(weight), ptr(mask), c_ll(pred.numel()),
+                           c_ll(pred.numel() // G), c_float(1.0 / denom), ptr(_scratch_f32(pred.device)),
+                           ptr(loss), ptr(None), ptr(None), stream_handle())
+        check(rc, "solar_mse")
+        count("mse_fwd", 2)
+        ctx.save_for_backward(pred, target, weight, mask)
+        ctx.denom = denom
+        return loss.view(())
+
+    @staticmethod
+    def backward(ctx, gloss):
+        pred, target, weight, mask = ctx.saved_tensors
+        G = pred.shape[0]
+        dpred = torch.empty_like(pred)
+        gl = gloss.reshape(1).float().contiguous()
+        lib = _lib.load()
+        rc = lib.solar_mse(ptr(pred), ptr(target), ptr(weight), ptr(mask), c_ll(pred.numel()),
+                           c_ll(pred.numel() // G), c_float(1.0 / ctx.denom), ptr(_scratch_f32(pred.device)),
+                           ptr(None), ptr(dpred), ptr(gl), stream_handle())
+        check(rc, "solar_mse")
+        count("mse_bwd")
+        return dpred, None, None, None, None
+
+
+def weighted_masked_mse(pred, target, weight=None, mask=None, denom=None):
+    """sum_g w[g] m[g] |pred_g - target_g|^2 / denom with pred/target ``[G, ...]`` bf16.
+    ``denom`` defaults to (number of unmasked groups) x (elements per group)."""
+    if not pred.is_cuda:
+        return reference.weighted_masked_mse(pred, target, weight, mask)
+    G = pred.shape[0]
+    if denom is None:
+        sel = float(G) if mask is None else max(float(mask.sum().item()), 1.0)
+        denom = sel * (pred.numel() // G)
+    weight = None if weight is None else weight.float().contiguous()
+    mask = None if mask is None else mask.float().contiguous()
+    return _MseFn.apply(pred, target, weight, mask, float(denom))
+
+
+def rgb8(frame_chw, mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225)):
+    """bf16 ``[3, H, W]`` -> uint8 ``[H, W, 3]`` on the tensor's device; raises on a NaN pixel."""
+    import ctypes
+
+    assert frame_chw.dtype == torch.bfloat16 and frame_chw.dim() == 3 and frame_chw.shape[0] == 3
+    H, W = frame_chw.shape[1:]
+    m3 = (ctypes.c_float * 3)(*mean)
+    s3 = (ctypes.c_float * 3)(*std)
+    lib = _lib.load()
+    if frame_chw.is_cuda:
+        out = torch.empty((H, W, 3), dtype=torch.uint8, device=frame_chw.device)
+        flag = torch.zeros(1, dtype=torch.int32, device=frame_chw.device)
+        rc = lib.solar_rgb8(ptr(frame_chw), ptr(out), c_int(H), c_int(W), c_ll(frame_chw.stride(0)),
+                            c_ll(frame_chw.stride(1)), c_ll(frame_chw.stride(2)), m3, s3, ptr(flag),
+                            stream_handle())
+        check(rc, "solar_rgb8")
+        count("rgb8")
+        return out, flag
+    out = torch.empty((H, W, 3), dtype=torch.uint8)
+    lib.solar_host_rgb8_bf16.restype = ctypes.c_int
+    ok = lib.solar_host_rgb8_bf16(ptr(frame_chw), ctypes.c_size_t(H), ctypes.c_size_t(W),
+                                  ctypes.c_size_t(frame_chw.stride(0)), ctypes.c_size_t(frame_chw.stride(1)),
+                                  ctypes.c_size_t(frame_chw.stride(2)), m3, s3, ptr(out))
+    if not ok:
+        raise FloatingPointError("nonfinite RGB pixel")
+    return out, None
