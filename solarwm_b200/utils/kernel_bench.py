@@ -1,0 +1,200 @@
+"""Per-kernel timing with CUDA events (warm-up, L2 flush between iterations, synchronised on both
+sides) and roofline fractions against the measured peaks of the box.
+
+    python -m solarwm_b200.utils.kernel_bench gemm --m 27280 --n 3072 --k 3072 --layout nt
+    python -m solarwm_b200.utils.kernel_bench attention --seq 27280 --heads 24 --head-dim 128 [--backward]
+    python -m solarwm_b200.utils.kernel_bench rowops --rows 27280 --dim 3072
+    python -m solarwm_b200.utils.kernel_bench suite            # the Wan-5B block shapes
+
+Each line of output is one JSON object: the op, its shape, milliseconds (median of the timed
+iterations), achieved TFLOP/s or GB/s, the fraction of the measured peak, and the same numbers
+for the library kernel (cuBLAS / SDPA) that the hand-written kernel replaces.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+
+import torch
+
+from .. import ops
+
+_PEAKS = None
+
+
+def peaks():
+    """Measured copy bandwidth / bf16 GEMM throughput of this pool (fallback: earlier measurement)."""
+    global _PEAKS
+    if _PEAKS is None:
+        p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+        if p.exists():
+            d = json.loads(p.read_text())
+            _PEAKS = {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+        else:
+            _PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+    return _PEAKS
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_fn(fn, iters=10, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def bench_gemm(M, N, K, layout="nt", out_f32=False, iters=10):
+    lay = {"nt": ops.NT, "nn": ops.NN, "tn": ops.TN}[layout]
+    dev = "cuda"
+    if lay == ops.NT:
+        a, b = torch.randn(M, K, device=dev).bfloat16(), torch.randn(N, K, device=dev).bfloat16()
+        lib = lambda: torch.matmul(a, b.t())
+    elif lay == ops.NN:
+        a, b = torch.randn(M, K, device=dev).bfloat16(), torch.randn(K, N, device=dev).bfloat16()
+        lib = lambda: torch.matmul(a, b)
+    else:
+        a, b = torch.randn(K, M, device=dev).bfloat16(), torch.randn(K, N, device=dev).bfloat16()
+        lib = lambda: torch.matmul(a.t(), b)
+    out = torch.empty(M, N, device=dev, dtype=torch.float32 if out_f32 else torch.bfloat16)
+    ms = time_fn(lambda: ops.gemm(a, b, lay, out=out), iters)
+    ms_lib = time_fn(lib, iters)
+    fl = 2.0 * M * N * K
+    pk = peaks()
+    return {"op": "gemm", "layout": layout, "M": M, "N": N, "K": K, "out": "f32" if out_f32 else "bf16",
+            "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+            "frac_of_peak": round(fl / ms / 1e9 / pk["bf16_tflops"], 3), "peak_src": pk["src"],
+            "cublas_ms": round(ms_lib, 4), "cublas_tflops": round(fl / ms_lib / 1e9, 1),
+            "speedup_vs_cublas": round(ms_lib / ms, 3)}
+
+
+def bench_attention(S, H, D, Sk=None, backward=False, iters=5):
+    dev = "cuda"
+    Sk = Sk or S
+    q = torch.randn(1, S, H, D, device=dev).bfloat16().requires_grad_(backward)
+    k = torch.randn(1, Sk, H, D, device=dev).bfloat16().requires_grad_(backward)
+    v = torch.randn(1, Sk, H, D, device=dev).bfloat16().requires_grad_(backward)
+    fl = 4.0 * S * Sk * H * D
+    res = {"op": "attention", "S": S, "Sk": Sk, "H": H, "D": D, "backward": backward}
+    for name in ("native", "library"):
+        try:
+            if backward:
+                o = ops.attention(q, k, v, backend=name)
+                g = torch.randn_like(o)
+
+                def run():
+                    q.grad = k.grad = v.grad = None
+                    o.backward(g, retain_graph=True)
+
+                ms = time_fn(run, iters)
+                f = fl * 2.5
+            else:
+                with torch.no_grad():
+                    ms = time_fn(lambda: ops.attention(q, k, v, backend=name), iters)
+                f = fl
+            res[f"{name}_ms"] = round(ms, 4)
+            res[f"{name}_tflops"] = round(f / ms / 1e9, 1)
+            if name == "native":
+                res["frac_of_peak"] = round(f / ms / 1e9 / peaks()["bf16_tflops"], 3)
+        except Exception as exc:  # noqa: BLE001
+            res[f"{name}_error"] = repr(exc)[:200]
+    res["peak_src"] = peaks()["src"]
+    return res
+
+
+def bench_rowops(R, D, iters=10):
+    dev = "cuda"
+    x = torch.randn(R, D, device=dev).bfloat16()
+    y = torch.randn(R, D, device=dev).bfloat16()
+    G = max(R // 880, 1)
+    mod = torch.randn(G + 1, 6, D, device=dev)
+    rpg = (R + G - 1) // G
+    pk = peaks()
+    out = []
+
+    def add(name, fn, bytes_moved):
+        ms = time_fn(fn, iters)
+        gbs = bytes_moved / ms / 1e6
+        out.append({"op": name, "rows": R, "D": D, "ms": round(ms, 4), "gbs": round(gbs, 1),
+                    "frac_of_peak": round(gbs / pk["hbm_gbs"], 3), "peak_src": pk["src"]})
+
+    with torch.no_grad():
+        add("norm_modulate_fwd", lambda: ops.norm_modulate(x, mod[:, 0], mod[:, 1], rows_per_group=rpg), 2 * R * D * 2)
+        add("gated_residual", lambda: ops.gated_residual(x, y, mod[:, 2], rows_per_group=rpg), 3 * R * D * 2)
+        w = torch.ones(D, device=dev)
+        add("rmsnorm_rope_fwd(no rope)", lambda: ops.rmsnorm_rope(x, w, None), 2 * R * D * 2)
+        add("gelu_fwd", lambda: ops.gelu(x), 2 * R * D * 2)
+    return out
+
+
+def wan5b_suite(seq=27280):
+    d, f = 3072, 14336
+    rows = []
+    for (M, N, K, lay) in [(seq, 3 * d, d, "nt"), (seq, d, d, "nt"), (seq, f, d, "nt"), (seq, d, f, "nt"),
+                           (seq, d, 3 * d, "nn"), (seq, d, f, "nn"), (seq, f, d, "nn"),
+                           (3 * d, d, seq, "tn"), (f, d, seq, "tn"), (d, f, seq, "tn")]:
+        rows.append(bench_gemm(M, N, K, lay, out_f32=(lay == "tn")))
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=4096)
+    g.add_argument("--n", type=int, default=4096)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--layout", default="nt")
+    g.add_argument("--f32", action="store_true")
+    g.add_argument("--iters", type=int, default=10)
+    a = sub.add_parser("attention")
+    a.add_argument("--seq", type=int, default=8192)
+    a.add_argument("--kv", type=int, default=None)
+    a.add_argument("--heads", type=int, default=24)
+    a.add_argument("--head-dim", type=int, default=128)
+    a.add_argument("--backward", action="store_true")
+    a.add_argument("--iters", type=int, default=5)
+    r = sub.add_parser("rowops")
+    r.add_argument("--rows", type=int, default=27280)
+    r.add_argument("--dim", type=int, default=3072)
+    s = sub.add_parser("suite")
+    s.add_argument("--seq", type=int, default=27280)
+    args = ap.parse_args()
+    if args.cmd == "gemm":
+        print(json.dumps(bench_gemm(args.m, args.n, args.k, args.layout, args.f32, args.iters)))
+    elif args.cmd == "attention":
+        print(json.dumps(bench_attention(args.seq, args.heads, args.head_dim, args.kv, args.backward, args.iters)))
+    elif args.cmd == "rowops":
+        for row in bench_rowops(args.rows, args.dim):
+            print(json.dumps(row))
+    else:
+        for row in wan5b_suite(args.seq):
+            print(json.dumps(row))
+        for row in bench_rowops(args.seq, 3072):
+            print(json.dumps(row))
+    ops.check_status()
+
+
+if __name__ == "__main__":
+    main()
