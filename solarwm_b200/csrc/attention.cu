@@ -1,0 +1,394 @@
+// Flash attention forward for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+//
+//   O[b, i, h, :] = softmax_j(scale * Q[b,i,h,:] . K[b,j,h,:]) V[b,j,h,:]      (bidirectional)
+//
+// One CTA owns 256 consecutive queries of one (batch, head): two 128-row Q tiles that
+// ping-pong so the tensor pipe works on one tile while the softmax warps work on the other.
+//
+//   warp 0        TMA producer: Q tiles once, then a 2-deep ring of K tiles and a 2-deep ring of
+//                 V tiles (128 keys x head_dim each, 128-byte swizzle, no cluster qualifiers)
+//   warp 1        allocates TMEM and issues every tcgen05.mma:
+//                   S_t = Q_t K_j^T   (both operands from shared memory, K-major)
+//                   O_t += P_t V_j    (P from TMEM as bf16, V from shared memory, MN-major)
+//   warps 4..7    softmax for Q tile 0 (one thread per query row, TMEM lane = row)
+//   warps 8..11   softmax for Q tile 1
+//
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overwrites the
+// first 64 columns of S_t as packed bf16 pairs.  The running maximum is only raised (and O
+// rescaled in TMEM by the softmax warps) when it would grow by more than 2^8, so the rescale is
+// rare; the final O / l division makes the result exact either way.
+//
+// Every wait is bounded (sm100.cuh); on a timeout the CTA drains, frees TMEM, reports a status.
+//
+// Replaces flash_attn_varlen_func / SDPA on the reference's attention path
+// (solar/backends/wan22/runtime/modeling/attention.py:34-188).
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace solar {
+
+constexpr int ATT_THREADS = 384;
+constexpr int QT = 128;    // rows per Q tile
+constexpr int KT = 128;    // keys per KV tile
+constexpr int KV_STAGES = 2;
+
+struct AttnParams {
+  int Sq, Sk, H, B;
+  float scale_log2;   // scale * log2(e)
+  float scale;
+  float* lse;         // [B, H, Sq] natural-log sum-exp of the scaled scores (may be null)
+  int* status;
+};
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+template <int HD>
+struct AttnSmem {
+  static constexpr int CHUNKS = HD / 64;                 // 64-element (128-byte) column chunks
+  static constexpr int TILE_BYTES = 128 * HD * 2;        // one Q / K / V tile
+  static constexpr int CHUNK_BYTES = 128 * 128;          // 128 rows x 128 bytes
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = 2 * TILE_BYTES;
+  static constexpr int V_OFF = K_OFF + KV_STAGES * TILE_BYTES;
+  static constexpr int BAR_OFF = V_OFF + KV_STAGES * TILE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                const AttnParams p) {
+  using L = AttnSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* k_full = bars + 1;             // KV_STAGES
+  uint64_t* k_empty = k_full + KV_STAGES;
+  uint64_t* v_full = k_empty + KV_STAGES;
+  uint64_t* v_empty = v_full + KV_STAGES;
+  uint64_t* s_ready = v_empty + KV_STAGES; // 2
+  uint64_t* p_ready = s_ready + 2;         // 2
+  uint64_t* o_done = p_ready + 2;          // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * (2 * QT);
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int n_kv = (p.Sk + KT - 1) / KT;
+  // the second Q tile may be entirely past the end of the sequence
+  const bool tile1_live = (q0 + QT) < p.Sq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_ready[t], 1);
+      mbar_init(&p_ready[t], 128);
+      mbar_init(&o_done[t], 1);
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t TS[2] = {tmem_base + 0, tmem_base + 128};
+  const uint32_t TO[2] = {tmem_base + 256, tmem_base + 384};
+
+  if (warp == 0) {
+    // -------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * L::TILE_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int c = 0; c < L::CHUNKS; ++c)
+          tma_load_4d(smem + L::Q_OFF + t * L::TILE_BYTES + c * L::CHUNK_BYTES, &tmQ, q_full, c * 64, head,
+                      q0 + t * QT, batch);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_word, ST_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&k_full[s], L::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < L::CHUNKS; ++c)
+          tma_load_4d(smem + L::K_OFF + s * L::TILE_BYTES + c * L::CHUNK_BYTES, &tmK, &k_full[s], c * 64, head,
+                      j * KT, batch);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_word, ST_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&v_full[s], L::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < L::CHUNKS; ++c)
+          tma_load_4d(smem + L::V_OFF + s * L::TILE_BYTES + c * L::CHUNK_BYTES, &tmV, &v_full[s], c * 64, head,
+                      j * KT, batch);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, KT, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, HD, 0, 1);
+      const uint32_t q_smem = smem_u32(smem + L::Q_OFF);
+      const uint32_t k_smem = smem_u32(smem + L::K_OFF);
+      const uint32_t v_smem = smem_u32(smem + L::V_OFF);
+      auto issue_qk = [&](int t, int s) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * L::CHUNK_BYTES + (kk % 4) * 32;
+          umma_ss(TS[t], umma_desc_kmajor(q_smem + t * L::TILE_BYTES + off),
+                  umma_desc_kmajor(k_smem + s * L::TILE_BYTES + off), idesc_qk, kk != 0);
+        }
+        umma_commit(&s_ready[t]);
+      };
+      auto issue_pv = [&](int t, int s, int j) {
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+          umma_ts(TO[t], TS[t] + kk * 8,
+                  umma_desc_mnmajor(v_smem + s * L::TILE_BYTES + kk * 2048, L::CHUNK_BYTES), idesc_pv,
+                  (j | kk) != 0);
+        }
+        umma_commit(&o_done[t]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_word, ST_TIMEOUT_FULL);
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_word, ST_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0);
+        if (tile1_live) issue_qk(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        const int sn = (j + 1) % KV_STAGES;
+        const uint32_t phn = ((j + 1) / KV_STAGES) & 1;
+        const bool more = (j + 1) < n_kv;
+        if (!mbar_wait(&v_full[s], ph, abort_word, ST_TIMEOUT_FULL)) break;
+        // ---- tile 0
+        if (!mbar_wait(&p_ready[0], j & 1, abort_word, ST_TIMEOUT_OTHER)) break;
+        tc_fence_after();
+        issue_pv(0, s, j);
+        if (more) {
+          if (!mbar_wait(&k_full[sn], phn, abort_word, ST_TIMEOUT_FULL)) break;
+          tc_fence_after();
+          issue_qk(0, sn);
+        }
+        // ---- tile 1
+        if (tile1_live) {
+          if (!mbar_wait(&p_ready[1], j & 1, abort_word, ST_TIMEOUT_OTHER)) break;
+          tc_fence_after();
+          issue_pv(1, s, j);
+        }
+        umma_commit(&v_empty[s]);
+        if (more) {
+          if (tile1_live) issue_qk(1, sn);
+          umma_commit(&k_empty[sn]);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // -------------------------------------------------------------- softmax (2 x 4 warps)
+    const int t = (warp - 4) >> 2;              // Q tile of this warpgroup
+    const int quarter = warp & 3;               // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;        // row inside the Q tile
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = TS[t] + lane_off, tO = TO[t] + lane_off;
+    const bool live = (t == 0) || tile1_live;
+    float m_used = -INFINITY, l = 0.f;
+    const float c = p.scale_log2;
+    bool ok = live;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      if (!mbar_wait(&s_ready[t], j & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int kv_valid = p.Sk - j * KT;       // >= 128 except on the last tile
+      // pass 1: row maximum of the raw scores
+      float mx = -INFINITY;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + cc * 32, r);
+        tmem_ld_wait();
+        if (kv_valid < KT) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (cc * 32 + e < kv_valid) mx = fmaxf(mx, __uint_as_float(r[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
+        }
+      }
+      if (j == 0) {
+        m_used = mx;
+      } else {
+        const float m_new = fmaxf(m_used, mx);
+        const bool need = (m_new - m_used) * c > 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          // O_t of the previous KV tile must have landed before it is rescaled in place
+          if (!mbar_wait(&o_done[t], (j - 1) & 1, abort_word, ST_TIMEOUT_OTHER)) { ok = false; break; }
+          tc_fence_after();
+          const float f = need ? exp2_fast((m_used - m_new) * c) : 1.0f;
+          if (need) m_used = m_new;
+          l *= f;
+#pragma unroll
+          for (int cc = 0; cc < HD / 32; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * f);
+            tmem_st_32x32(tO + cc * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: P = exp2(s * c - m * c), packed to bf16 over the first 64 columns of S_t
+      const float neg_mc = -m_used * c;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + cc * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float a = exp2_fast(fmaf(__uint_as_float(r[2 * e]), c, neg_mc));
+          float b = exp2_fast(fmaf(__uint_as_float(r[2 * e + 1]), c, neg_mc));
+          if (kv_valid < KT) {
+            if (cc * 32 + 2 * e >= kv_valid) a = 0.f;
+            if (cc * 32 + 2 * e + 1 >= kv_valid) b = 0.f;
+          }
+          l += a + b;
+          pk[e] = pack_bf16x2(a, b);
+        }
+        tmem_st_32x16(tS + cc * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_ready[t]);
+    }
+    // ---- epilogue: O / l -> bf16 -> shared memory (the tile's Q buffer) -> TMA store
+    if (ok) ok = mbar_wait(&o_done[t], (n_kv - 1) & 1, abort_word, ST_TIMEOUT_OTHER);
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = 1.0f / l;
+      uint8_t* obuf = smem + L::Q_OFF + t * L::TILE_BYTES;
+#pragma unroll
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(tO + cc * 32, r);
+        tmem_ld_wait();
+        uint8_t* dst = obuf + (cc / 2) * L::CHUNK_BYTES + row * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]) * inv_l, __uint_as_float(r[g * 8 + 1]) * inv_l);
+          o.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * inv_l, __uint_as_float(r[g * 8 + 3]) * inv_l);
+          o.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * inv_l, __uint_as_float(r[g * 8 + 5]) * inv_l);
+          o.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * inv_l, __uint_as_float(r[g * 8 + 7]) * inv_l);
+          const int piece = (cc & 1) * 4 + g;  // 16-byte piece inside the 128-byte row
+          *reinterpret_cast<uint4*>(dst + ((piece ^ (row & 7)) << 4)) = o;
+        }
+      }
+      const int qrow = q0 + t * QT + row;
+      if (p.lse != nullptr && qrow < p.Sq)
+        p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq + qrow] = m_used * p.scale + __logf(l);
+      fence_proxy_async_smem();
+      named_bar_sync(1 + t, 128);
+      if (quarter == 0 && lane == 0) {
+#pragma unroll
+        for (int ch = 0; ch < L::CHUNKS; ++ch)
+          tma_store_4d(&tmO, obuf + ch * L::CHUNK_BYTES, ch * 64, head, q0 + t * QT, batch);
+        tma_store_commit();
+        tma_store_wait_all<0>();
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_word != 0) bounded_drain_pause();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicExch(p.status, *abort_word);
+}
+
+template <int HD>
+static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const CUtensorMap& to, const AttnParams& p, cudaStream_t st) {
+  auto kern = attn_fwd_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::TOTAL));
+    configured = true;
+  }
+  dim3 grid((p.Sq + 2 * QT - 1) / (2 * QT), p.H, p.B);
+  kern<<<grid, ATT_THREADS, AttnSmem<HD>::TOTAL, st>>>(tq, tk, tv, to, p);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+static int make_bshd_map(CUtensorMap* m, const void* ptr, int B, int S, int H, int D, long long stride_s,
+                         long long stride_b) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)stride_s * 2, (uint64_t)stride_b * 2};
+  const uint32_t box[4] = {64, 1, 128, 1};
+  return make_tmap_4d(m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dims, strides, box);
+}
+
+}  // namespace solar
+
+using namespace solar;
+
+// q [B,Sq,H,D], k/v [B,Sk,H,D], o [B,Sq,H,D] bf16 with unit stride on D, stride D on H and the
+// given element strides on the sequence and batch axes (so q/k/v may be slices of a fused QKV
+// buffer).  lse [B,H,Sq] fp32 or null.
+extern "C" int solar_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B,
+                              int Sq, int Sk, int H, int D, long long q_ss, long long q_sb,
+                              long long k_ss, long long k_sb, long long v_ss, long long v_sb,
+                              long long o_ss, long long o_sb, float scale, int* status, void* stream) {
+  if (D != 64 && D != 128) return fail("attention: head_dim must be 64 or 128%s");
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0) return fail("attention: empty problem%s");
+  CUtensorMap tq, tk, tv, to;
+  int rc;
+  if ((rc = make_bshd_map(&tq, q, B, Sq, H, D, q_ss, q_sb))) return rc;
+  if ((rc = make_bshd_map(&tk, k, B, Sk, H, D, k_ss, k_sb))) return rc;
+  if ((rc = make_bshd_map(&tv, v, B, Sk, H, D, v_ss, v_sb))) return rc;
+  if ((rc = make_bshd_map(&to, o, B, Sq, H, D, o_ss, o_sb))) return rc;
+  AttnParams p;
+  p.Sq = Sq; p.Sk = Sk; p.H = H; p.B = B;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse;
+  p.status = status;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 128) return launch_attn_fwd<128>(tq, tk, tv, to, p, st);
+  return launch_attn_fwd<64>(tq, tk, tv, to, p, st);
+}

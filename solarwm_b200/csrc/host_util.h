@@ -87,6 +87,25 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   return 0;
 }
 
+// 4-D tensor (d0 innermost) with byte strides for d1..d3; 128-byte swizzle.
+inline int make_tmap_4d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, const uint64_t dims[4],
+                        const uint64_t strides_bytes[3], const uint32_t box[4]) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail("cuTensorMapEncodeTiled entry point not available%s");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail("TMA base not 16-byte aligned%s");
+  for (int i = 0; i < 3; ++i)
+    if (strides_bytes[i] % 16 != 0) return fail("TMA stride not a multiple of 16 bytes%s");
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t s[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t e[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, dt, 4, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled(4d) failed (code %s%lld)", "", (long long)r);
+  return 0;
+}
+
 inline int sm_count() {
   static int n = 0;
   if (n == 0) {

@@ -1,0 +1,72 @@
+"""tcgen05 flash attention against an fp32 softmax(QK^T)V of the same bf16 inputs."""
+import math
+
+import pytest
+import torch
+
+from solarwm_b200 import ops
+from solarwm_b200.ops import reference as R
+from solarwm_b200.ops.attention_native import attn_fwd
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(B, S, H, D, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(B, S, H, D, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,H,D", [(1, 256, 256, 2, 128), (1, 128, 128, 1, 128), (2, 384, 512, 3, 128),
+                                          (1, 300, 200, 2, 128), (1, 1000, 1111, 2, 128), (1, 640, 512, 4, 64),
+                                          (2, 250, 77, 2, 64), (1, 2000, 3000, 1, 128)])
+def test_attention_forward(B, Sq, Sk, H, D):
+    q, k, v = _mk(B, Sq, H, D, 1), _mk(B, Sk, H, D, 2), _mk(B, Sk, H, D, 3)
+    scale = 1.0 / math.sqrt(D)
+    o, lse = attn_fwd(q, k, v, scale)
+    ops.check_status()
+    ref = R.attention(q.float(), k.float(), v.float(), scale=scale)
+    err = (o.float() - ref).abs().max().item()
+    rel = ((o.float() - ref).norm() / ref.norm()).item()
+    assert rel < 1e-2 and err < 5e-2, (rel, err)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    lse_ref = torch.logsumexp(s, dim=-1)
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+
+
+def test_attention_large_scores_trigger_rescale():
+    """Scores that grow along the key axis force the running-maximum rescale path."""
+    B, S, H, D = 1, 1024, 1, 128
+    q = _mk(B, S, H, D, 5, 2.0)
+    k = _mk(B, S, H, D, 6, 2.0)
+    ramp = torch.linspace(0.2, 3.0, S, device="cuda").view(1, S, 1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    v = _mk(B, S, H, D, 7)
+    scale = 1.0 / math.sqrt(D)
+    o, _ = attn_fwd(q, k, v, scale)
+    ops.check_status()
+    ref = R.attention(q.float(), k.float(), v.float(), scale=scale)
+    assert ((o.float() - ref).norm() / ref.norm()).item() < 1.5e-2
+
+
+def test_attention_strided_views_of_fused_qkv():
+    B, S, H, D = 1, 512, 2, 128
+    qkv = _mk(B, S, 3 * H, D, 9).view(B, S, 3, H, D)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    scale = 1.0 / math.sqrt(D)
+    o, _ = attn_fwd(q, k, v, scale)
+    ops.check_status()
+    ref = R.attention(q.float(), k.float(), v.float(), scale=scale)
+    assert ((o.float() - ref).norm() / ref.norm()).item() < 1e-2
+
+
+def test_attention_autograd_path():
+    B, S, H, D = 1, 256, 2, 128
+    q, k, v = (_mk(B, S, H, D, s).requires_grad_(True) for s in (11, 12, 13))
+    o = ops.attention(q, k, v, backend="native")
+    g = torch.randn_like(o)
+    o.backward(g)
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o2 = R.attention(q2, k2, v2)
+    o2.backward(g.float())
+    for a, b in ((q.grad, q2.grad), (k.grad, k2.grad), (v.grad, v2.grad)):
+        assert ((a.float() - b).norm() / b.norm()).item() < 2e-2
