@@ -148,7 +148,7 @@ def run(args) -> int:
                                 timestep.flatten(0, 1)).unflatten(0, (B, F)).to(clean.dtype)
         noisy[~dropped, 0] = clean[~dropped, 0]
         t_tokens = expand_timesteps_to_tokens(timestep, frame_tokens)
-        pred = diffusion(noisy, prompt, {}, t_tokens, sequence_length=F * frame_tokens)
+        pred = diffusion(noisy, prompt, None, t_tokens, sequence_length=F * frame_tokens)
         target = sched.training_target(clean, noise, timestep)
         weight = sched.training_weight(timestep).view(B, F, 1, 1, 1)
         mask = first_frame_loss_mask(B, F, dropped)
