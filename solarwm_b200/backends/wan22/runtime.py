@@ -1,0 +1,226 @@
+"""``TrainingRuntime`` implementation for the Wan Stage0.5 flow-matching route and the
+``run_training`` entry the backend calls (reference: Wan5BStage0p5Runtime and
+run_stage0p5_training, solar/backends/wan22/runtime/stage0p5.py:105-587)."""
+from __future__ import annotations
+
+import hashlib
+from typing import Any, Iterator, Mapping
+
+import torch
+
+from ...config.routes import validate_route
+from ...engine.schedule import WarmupCosine
+from ...engine.train_engine import (BatchIdentity, GradientStatus, JsonlEventSink, MicrobatchResult, StepPolicy,
+                                    TrainingEngine)
+from ...errors import BackendContractError
+from ...parallel import dist_init
+from ...runtime import distributed as rdist
+from ...runtime.output_layout import events_path, output_root
+from ...runtime.randomness import model_init_seed, objective_seed
+from ...runtime.safe_state import capture_rank_state
+from . import checkpoint as ckpt
+from .contracts import PROFILES, architecture, latent_frames
+from .stage0p5 import Stage0p5Options, WanStage0p5Trainer
+
+
+def synthetic_batches(config, arch, device) -> Iterator[dict]:
+    data, family = config["data"], config["model"]["family"]
+    prof = PROFILES[family]
+    frames = latent_frames(int(data["pixel_frames"]), prof.vae_stride[0])
+    h = int(data.get("latent_height", 16))
+    w = int(data.get("latent_width", 16))
+    micro = int(config["train"].get("micro_batch_size", 1))
+    g = torch.Generator().manual_seed(int(data.get("seed", 0)))
+    step = 0
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    ch = arch.out_dim
+    while True:
+        lat = torch.randn(micro, frames, ch, h, w, generator=g).to(dtype)
+        txt = torch.randn(micro, arch.text_len, arch.text_dim, generator=g).to(dtype)
+        batch = {"latents": lat, "text": txt, "sample_ids": [f"synthetic-{step}-{i}" for i in range(micro)],
+                 "start_frames": [0] * micro}
+        if arch.in_dim > ch:
+            batch["y"] = torch.randn(micro, frames, arch.in_dim - ch, h, w, generator=g).to(dtype)
+        if device.type == "cuda":
+            batch = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in batch.items()}
+        step += 1
+        yield batch
+
+
+class WanStage0p5Runtime:
+    """Adapts ``WanStage0p5Trainer`` to the engine's 11-hook protocol."""
+
+    def __init__(self, config: Mapping[str, Any]):
+        self.config = config
+        self.route = validate_route(config)
+        dist_cfg = config.get("distributed", {}) or {}
+        self.ctx = dist_init.initialize(int(dist_cfg.get("sequence_parallel_size", 1)),
+                                        device=str(config.get("runtime", {}).get("device", "auto")))
+        topo = self.ctx.topology
+        self.arch = architecture(config)
+        train = config["train"]
+        opt = train.get("optimizer", {}) or {}
+        ema = train.get("ema", {}) or {}
+        seed = int(config["data"].get("seed", 0))
+        opts = Stage0p5Options(
+            lr=float(opt.get("lr", 1e-4)), betas=tuple(opt.get("betas", (0.9, 0.999))), eps=float(opt.get("eps", 1e-8)),
+            weight_decay=float(opt.get("weight_decay", 0.01)), max_grad_norm=float(opt.get("grad_clip", 1.0)),
+            timestep_shift=float(config["model"].get("timestep_shift", 5.0)),
+            sigma_sampling=str(train.get("sigma_sampling", "uniform_index")),
+            image_dropout=float(train.get("i2v_image_condition_dropout", 0.0)),
+            grad_accum=int(train.get("grad_accum", train.get("gradient_accumulation_steps", 1))),
+            ema_decay=float(ema["decay"]) if ema.get("enabled") else None,
+            checkpointing="full" if (train.get("fsdp", {}) or {}).get("activation_checkpointing") else "none",
+            seed=seed)
+        dtype = torch.bfloat16 if self.ctx.device.type == "cuda" else torch.float32
+        from ...models.wan import WanDiT
+
+        model = WanDiT(self.arch, device=self.ctx.device, dtype=dtype,
+                       seed=model_init_seed(self.route.family, seed))
+        if bool(config["model"].get("nonzero_head_init", False)):
+            with torch.no_grad():
+                model.get_parameter("head.head.weight").normal_(0, 0.02)
+        self.trainer = WanStage0p5Trainer(self.arch, self.ctx.device, opts, sp=self.ctx.sp, dtype=dtype, model=model)
+        self.trainer.gen.manual_seed(objective_seed(seed, topo.dp_rank))
+        self.scheduler = WarmupCosine(self.trainer.optimizer, warmup_steps=int(train.get("warmup_steps", 0)),
+                                      total_steps=int(train["max_steps"]),
+                                      min_lr_ratio=float(opt.get("min_lr_ratio", 0.1)))
+        self.batches = synthetic_batches(config, self.arch, self.ctx.device)
+        self.batches_consumed = 0
+        self._step = 0
+        self.checkpoint_id = "init:random"
+        self.contract = ckpt.build_contract(config, self.route, topo.sp_size)
+        self._resume()
+
+    # -- checkpoint wiring ---------------------------------------------------------------
+    def _resume(self) -> None:
+        c = self.config.get("checkpoint", {}) or {}
+        mode = str(c.get("mode", "none"))
+        if mode == "none" or not c.get("resume_from"):
+            return
+        verified, payload = ckpt.load_checkpoint(
+            c["resume_from"], model=self.trainer.model, optimizer=self.trainer.optimizer, scheduler=self.scheduler,
+            mode=mode, expected=self.contract, weight_source=str(c.get("weight_source", "live")),
+            map_location=self.ctx.device)
+        self.checkpoint_id = verified.manifest_digest
+        if mode == "full_resume":
+            self._step = int(payload["global_step"])
+            self.trainer.global_step = self._step
+            # exact resume: this rank's objective RNG stream and reader cursor
+            states = payload.get("rank_runtime_state") or []
+            rank = self.ctx.topology.raw_rank
+            if rank < len(states) and states[rank] is not None:
+                mine = states[rank]
+                self.trainer.gen.set_state(mine["objective_gen"].cpu())
+                for _ in range(int(mine["batches_consumed"])):
+                    next(self.batches)
+                self.batches_consumed = int(mine["batches_consumed"])
+
+    # -- TrainingRuntime -----------------------------------------------------------------
+    @property
+    def global_step(self) -> int:
+        return self._step
+
+    def zero_grad(self) -> None:
+        self.trainer.model.zero_grads()
+
+    def train_microbatch(self, micro_index: int, grad_accum: int) -> MicrobatchResult:
+        batch = next(self.batches)
+        self.batches_consumed += 1
+        dev = self.ctx.device
+        seed_digest = hashlib.blake2s(self.trainer.gen.get_state().cpu().numpy().tobytes()).hexdigest()
+        loss = self.trainer.microbatch(batch["latents"].to(dev, non_blocking=True),
+                                       batch["text"].to(dev, non_blocking=True),
+                                       None if "y" not in batch else batch["y"].to(dev, non_blocking=True))
+        value = float(loss.item())
+        if value != value or value in (float("inf"), float("-inf")):
+            raise BackendContractError(f"non-finite Wan Stage0.5 loss: {value}")
+        plan = repr((batch["sample_ids"], batch["start_frames"]))
+        ident = BatchIdentity(tuple(batch["sample_ids"]), tuple(batch["start_frames"]),
+                              tuple(int(seed_digest[:15], 16) + i for i in range(len(batch["sample_ids"]))),
+                              self.checkpoint_id, hashlib.blake2s(plan.encode()).hexdigest())
+        return MicrobatchResult(ident, {"flow_matching": value})
+
+    def assert_sp_peer_identity(self, identity: BatchIdentity) -> None:
+        rdist.gather_and_assert_sp_identity(
+            {"sample_ids": identity.sample_ids, "start_frames": identity.start_frames,
+             "noise_seeds": identity.noise_seeds, "plan_fingerprint": identity.plan_fingerprint},
+            sp_size=self.ctx.topology.sp_size, group=self.ctx.sp_group)
+
+    def prepare_optimizer_step(self) -> GradientStatus:
+        tr = self.trainer
+        tr.model.finalize_grads()
+        if tr.sp is not None and tr.sp.size > 1:
+            tr.sp.sum_gradients_([g for u in tr.model.units() for g in (u.grad, u.grad_v)])
+        norm = tr.optimizer.local_grad_sumsq().sqrt()
+        tr.optimizer.set_clip(norm, tr.opts.max_grad_norm)
+        value = float(norm.item())
+        tr.last_grad_norm = norm
+        return GradientStatus(finite=value == value and value not in (float("inf"), float("-inf")), norm=value)
+
+    def optimizer_step(self) -> None:
+        self.trainer.optimizer.step()
+
+    def scheduler_step(self) -> None:
+        self.scheduler.step()
+
+    def ema_update(self, step: int) -> None:
+        return None  # the EMA shadow is refreshed inside the fused AdamW kernel
+
+    def set_global_step(self, step: int) -> None:
+        self._step = int(step)
+        self.trainer.global_step = int(step)
+
+    def save_checkpoint(self, step: int) -> str:
+        import torch.distributed as dist
+
+        topo = self.ctx.topology
+        state = capture_rank_state(self.ctx.device)
+        state = {k: (v if not torch.is_tensor(v) else v.cpu()) for k, v in state.items()}
+        state["objective_gen"] = self.trainer.gen.get_state().cpu()
+        state["batches_consumed"] = int(self.batches_consumed)
+        states = [state]
+        if topo.raw_world_size > 1:
+            states = [None] * topo.raw_world_size
+            dist.all_gather_object(states, state)
+        ema_state = None
+        if self.trainer.optimizer.ema_decay is not None:
+            from ...engine.ema import FlatEMAView
+
+            ema_state = FlatEMAView(self.trainer.model, self.trainer.optimizer).state_dict()
+
+        def agree(ident):
+            return rdist.collective_rank_zero_call(lambda: ident, dist=dist if topo.raw_world_size > 1 else None,
+                                                   label="checkpoint commit")
+
+        ident = ckpt.save_checkpoint(output_root(self.config), step, model=self.trainer.model,
+                                     optimizer=self.trainer.optimizer, scheduler=self.scheduler,
+                                     contract=self.contract, config=self.config, ema_state=ema_state,
+                                     ema_num_updates=self.trainer.optimizer.step_count, rank_states=states,
+                                     is_main=topo.is_main, barrier=agree)
+        self.checkpoint_id = ident
+        return ident
+
+    def validate(self, step: int) -> Mapping[str, Any]:
+        from .inference import run_inline_validation
+
+        return run_inline_validation(self, step)
+
+    def close(self) -> None:
+        dist_init.shutdown(self.ctx)
+
+
+def run_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
+    runtime = WanStage0p5Runtime(config)
+    try:
+        train, rt = config["train"], config.get("runtime", {})
+        max_steps = int(rt.get("max_steps_override") or train["max_steps"])
+        policy = StepPolicy(max_steps=max_steps,
+                            grad_accum=int(train.get("grad_accum", train.get("gradient_accumulation_steps", 1))),
+                            save_every=int(rt.get("save_every", 0)), validate_every=int(rt.get("validate_every", 0)))
+        sink = JsonlEventSink(events_path(output_root(config), runtime.ctx.topology.raw_rank))
+        final = TrainingEngine(runtime, policy, event_sink=sink).run()
+        return {"final_step": final, "checkpoint_id": runtime.checkpoint_id,
+                "native_launches": __import__("solarwm_b200.ops", fromlist=["x"]).total_launches()}
+    finally:
+        runtime.close()

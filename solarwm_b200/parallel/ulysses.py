@@ -67,9 +67,14 @@ class _AllGatherSeq(torch.autograd.Function):
         ctx.group, ctx.sizes = group, sizes
         rank = dist.get_rank(group)
         ctx.rank = rank
-        outs = [x.new_empty((n,) + tuple(x.shape[1:])) for n in sizes]
-        dist.all_gather(outs, x.contiguous(), group=group)
-        return torch.cat(outs, 0)
+        # shards may be uneven: pad to the largest, gather equal blocks, drop the padding
+        biggest = max(sizes)
+        x = x.contiguous()
+        if x.shape[0] < biggest:
+            x = torch.cat([x, x.new_zeros((biggest - x.shape[0],) + tuple(x.shape[1:]))], 0)
+        outs = [torch.empty_like(x) for _ in sizes]
+        dist.all_gather(outs, x, group=group)
+        return torch.cat([o[:n] for o, n in zip(outs, sizes)], 0)
 
     @staticmethod
     def backward(ctx, g):

@@ -1,0 +1,71 @@
+import json
+
+import pytest
+
+from solarwm_b200.checkpoint import (CheckpointContract, CheckpointTransaction, assert_resume_compatible,
+                                     verify_checkpoint)
+from solarwm_b200.errors import CheckpointError
+
+
+def _contract(**kw):
+    base = dict(family="wan22_ti2v_5b", stage="stage0p5", causal_mode="bidirectional", objective="flow_matching",
+                objective_variant="", camera_translation_transform="linear", parameterization="full", sp_size=2,
+                data_generation="g1")
+    base.update(kw)
+    return CheckpointContract(**base)
+
+
+def test_transaction_commit_verify_and_layout(tmp_path):
+    target = tmp_path / "checkpoint_model_000010"
+    with CheckpointTransaction(target) as tx:
+        assert tx.path.name.startswith(".checkpoint_model_000010.") and tx.path.name.endswith(".partial")
+        (tx.path / "model.pt").write_bytes(b"x" * 100)
+        (tx.path / "critic.pt").write_bytes(b"y" * 10)
+        done = tx.commit(step=10, contract=_contract(), required_components=["model.pt", "critic.pt"], metadata={"a": 1})
+    assert target.is_dir() and not tx.path.exists()
+    manifest = json.loads((target / "checkpoint-manifest.json").read_text())
+    assert manifest["schema"] == "solarwm.checkpoint.v2" and manifest["step"] == 10
+    assert manifest["files"] == [{"path": "critic.pt", "size": 10}, {"path": "model.pt", "size": 100}]
+    assert json.loads((target / "COMPLETE.json").read_text())["manifest_digest"] == done.manifest_digest
+    v = verify_checkpoint(target)
+    assert v.step == 10 and v.contract == _contract() and v.metadata == {"a": 1}
+
+
+def test_missing_component_leaves_partial_and_no_target(tmp_path):
+    target = tmp_path / "ck"
+    with pytest.raises(CheckpointError):
+        with CheckpointTransaction(target) as tx:
+            (tx.path / "model.pt").write_bytes(b"x")
+            tx.commit(step=1, contract=_contract(), required_components=["model.pt", "optimizer.pt"], metadata={})
+    assert not target.exists() and tx.path.exists()
+
+
+def test_tamper_detection_and_existing_target(tmp_path):
+    target = tmp_path / "ck"
+    with CheckpointTransaction(target) as tx:
+        (tx.path / "model.pt").write_bytes(b"x" * 8)
+        tx.commit(step=3, contract=_contract(), required_components=["model.pt"], metadata={})
+    (target / "model.pt").write_bytes(b"x" * 9)
+    with pytest.raises(CheckpointError, match="size differs"):
+        verify_checkpoint(target)
+    (target / "model.pt").write_bytes(b"x" * 8)
+    m = target / "checkpoint-manifest.json"
+    m.write_bytes(m.read_bytes().replace(b'"step":3', b'"step":4'))
+    with pytest.raises(CheckpointError):
+        verify_checkpoint(target)
+    with pytest.raises(CheckpointError, match="already exists"):
+        with CheckpointTransaction(target):
+            pass
+    (tmp_path / "nocomplete").mkdir()
+    with pytest.raises(CheckpointError, match="not complete"):
+        verify_checkpoint(tmp_path / "nocomplete")
+
+
+def test_resume_contract_and_validation():
+    assert_resume_compatible(_contract(), _contract())
+    with pytest.raises(CheckpointError, match="sp_size"):
+        assert_resume_compatible(_contract(), _contract(sp_size=4))
+    with pytest.raises(CheckpointError):
+        _contract(family="")
+    with pytest.raises(CheckpointError):
+        _contract(sp_size=0)

@@ -1,0 +1,50 @@
+import json
+import os
+from pathlib import Path
+
+import pytest
+
+from solarwm_b200.cli import main
+
+CONFIG = str(Path(__file__).resolve().parent.parent / "configs" / "wan22_ti2v_5b" / "tiny_stage0p5_cpu.yaml")
+
+
+def _events(root):
+    return [json.loads(l) for l in (Path(root) / "events" / "rank-00000.jsonl").read_text().splitlines()]
+
+
+def test_train_resume_is_exact_and_infer_publishes(tmp_path, monkeypatch):
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "a"))
+    assert main(["train", "--config", CONFIG, "--set", "runtime.device=cpu"]) == 0
+    a = tmp_path / "a"
+    for name in ("resolved-config.json", "launch-manifest.json", "run-result.json"):
+        assert (a / name).is_file()
+    assert json.loads((a / "run-result.json").read_text())["schema"] == "solarwm.run-result.v1"
+    assert json.loads((a / "launch-manifest.json").read_text())["schema"] == "solarwm.launch.v2"
+    assert (a / "checkpoint_model_000002" / "model.pt").is_file() and (a / "checkpoint_model_000004" / "COMPLETE.json").is_file()
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "b"))
+    assert main(["train", "--config", CONFIG, "--set", "runtime.device=cpu", "--set", "checkpoint.mode=full_resume",
+                 "--set", f"checkpoint.resume_from={a / 'checkpoint_model_000002'}", "--set", "runtime.save_every=0"]) == 0
+    first = {e["step"]: (e["losses"], e["gradient_norm"]) for e in _events(a) if e["event"] == "optimizer_step"}
+    second = {e["step"]: (e["losses"], e["gradient_norm"]) for e in _events(tmp_path / "b") if e["event"] == "optimizer_step"}
+    assert sorted(second) == [3, 4] and all(second[s] == first[s] for s in second)
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "c"))
+    assert main(["infer", "--config", CONFIG, "--set", "action=infer", "--set", "runtime.device=cpu",
+                 "--set", f"checkpoint.resume_from={a / 'checkpoint_model_000004'}", "--set", "inference.cases=2",
+                 "--set", "inference.steps=2"]) == 0
+    out = tmp_path / "c" / "generate"
+    assert (out / "COMPLETE.json").is_file() and (out / "slot-000001" / "latents.pt").is_file()
+
+
+def test_cli_errors_exit_2_and_helpers(tmp_path, monkeypatch, capsys):
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path))
+    assert main(["infer", "--config", CONFIG]) == 2                       # action mismatch
+    assert main(["train", "--config", CONFIG, "--set", "train.stage=stage9"]) == 2
+    assert main(["train", "--config", CONFIG, "--set", "distributed.sequence_parallel_size=3"]) == 2
+    assert main(["train", "--config", str(tmp_path / "missing.yaml")]) == 2
+    assert main(["config", "routes"]) == 0
+    assert "minimax_h3:stage2:self_gradient_forcing:flow_matching" in capsys.readouterr().out
+    assert main(["config", "resolve", "--config", CONFIG, "--output", str(tmp_path / "r.json")]) == 0
+    assert json.loads((tmp_path / "r.json").read_text())["schema"] == "solarwm.run.v1"
+    assert main(["environment", "probe"]) == 0
+    assert "native_library" in capsys.readouterr().out

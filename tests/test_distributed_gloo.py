@@ -1,0 +1,105 @@
+"""Real two-process gloo runs on CPU: fail-together error propagation, the data-readiness side
+channel with a failing and a slow reader, and BASELINE config 1 -- the tiny Wan-style DiT trained
+with Ulysses SP=2 matches the single-process oracle in loss and in every parameter gradient."""
+import os
+import time
+from datetime import timedelta
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _init(rank, world, path):
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world,
+                            timeout=timedelta(seconds=60))
+
+
+def _failure_worker(rank, world, path, out):
+    from solarwm_b200.errors import BackendContractError
+    from solarwm_b200.runtime import distributed as rdist
+
+    _init(rank, world, path)
+    result = {}
+    try:
+        rdist.collective_call(lambda: (_ for _ in ()).throw(ValueError("shard 7 missing")) if rank == 1 else 1,
+                              dist=dist, label="preflight")
+    except BackendContractError as exc:
+        result["collective"] = str(exc)
+    state = torch.get_rng_state().clone()
+    ready = rdist.DataReadiness(enabled=True, timeout=timedelta(seconds=30))
+
+    def slow_then_fail():
+        if rank == 0:
+            time.sleep(1.0)            # a slow reader only delays its peers
+            return "batch"
+        raise OSError("bucket read failed")
+
+    try:
+        ready.read(slow_then_fail)
+    except BackendContractError as exc:
+        result["readiness"] = str(exc)
+    result["rng_unchanged"] = bool(torch.equal(state, torch.get_rng_state()))
+    result["ok_read"] = ready.read(lambda: rank)
+    torch.save(result, f"{out}.{rank}")
+    dist.destroy_process_group()
+
+
+def test_errors_and_data_readiness_fail_together(tmp_path):
+    out = str(tmp_path / "res")
+    mp.spawn(_failure_worker, args=(2, str(tmp_path / "rdv"), out), nprocs=2, join=True)
+    r0, r1 = (torch.load(f"{out}.{r}", weights_only=True) for r in range(2))
+    assert r0["collective"] == r1["collective"] == "preflight failed collectively: rank 1: ValueError: shard 7 missing"
+    assert r0["readiness"] == r1["readiness"] and "rank 1: OSError: bucket read failed" in r0["readiness"]
+    assert r0["rng_unchanged"] and r1["rng_unchanged"] and (r0["ok_read"], r1["ok_read"]) == (0, 1)
+
+
+def _make_trainer(sp=None):
+    from solarwm_b200.backends.wan22.stage0p5 import Stage0p5Options, WanStage0p5Trainer
+    from solarwm_b200.models.wan import wan_preset
+
+    tr = WanStage0p5Trainer(wan_preset("tiny"), "cpu", Stage0p5Options(lr=1e-3, seed=0, sigma_sampling="uniform_index"),
+                            sp=sp, dtype=torch.float32)
+    with torch.no_grad():
+        tr.model.get_parameter("head.head.weight").normal_(0, 0.02, generator=torch.Generator().manual_seed(5))
+    return tr
+
+
+def _batch():
+    g = torch.Generator().manual_seed(0)
+    return torch.randn(1, 5, 16, 16, 16, generator=g), torch.randn(1, 32, 256, generator=g)
+
+
+def _sp_worker(rank, world, path, out):
+    from solarwm_b200.parallel.ulysses import UlyssesCollective
+
+    _init(rank, world, path)
+    tr = _make_trainer(UlyssesCollective(None))
+    lat, txt = _batch()
+    loss = tr.microbatch(lat, txt)
+    tr.model.finalize_grads()
+    tr.sp.sum_gradients_([g for u in tr.model.units() for g in (u.grad, u.grad_v)])
+    grads = {n: p.main_grad.clone() for n, p in tr.model.named_parameters()}
+    torch.save({"loss": loss, "grads": grads}, f"{out}.{rank}")
+    dist.destroy_process_group()
+
+
+def test_tiny_wan_sp2_matches_single_process_oracle(tmp_path):
+    tr = _make_trainer()
+    lat, txt = _batch()
+    loss = tr.microbatch(lat, txt)
+    tr.model.finalize_grads()
+    want = {n: p.main_grad.clone() for n, p in tr.model.named_parameters()}
+    out = str(tmp_path / "sp")
+    mp.spawn(_sp_worker, args=(2, str(tmp_path / "rdv"), out), nprocs=2, join=True)
+    got = [torch.load(f"{out}.{r}", weights_only=True) for r in range(2)]
+    for r in got:
+        assert abs(float(r["loss"]) - float(loss)) < 1e-5 * max(1.0, abs(float(loss)))
+    worst = 0.0
+    for name, ref in want.items():
+        for r in got:
+            err = (r["grads"][name] - ref).norm().item() / max(ref.norm().item(), 1e-8)
+            worst = max(worst, err)
+            assert err < 2e-4, (name, err)
+    assert torch.equal(got[0]["grads"]["blocks.0.ffn.0.weight"], got[1]["grads"]["blocks.0.ffn.0.weight"])

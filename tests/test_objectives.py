@@ -1,0 +1,78 @@
+import numpy as np
+import pytest
+import torch
+
+from solarwm_b200 import ops
+from solarwm_b200.engine import anyflow as af
+from solarwm_b200.engine import sgf
+from solarwm_b200.engine.flow import (FlowMatchScheduler, first_frame_loss_mask, rectified_interpolate_array,
+                                      velocity_target_array, weighted_masked_mse_array)
+from solarwm_b200.engine.schedule import warmup_cosine_factor
+
+
+def test_flow_scheduler_matches_closed_form_and_numpy_twins():
+    s = FlowMatchScheduler(shift=5.0)
+    lin = torch.linspace(1, 0, 1001)[:-1]
+    assert torch.allclose(s.sigmas, 5 * lin / (1 + 4 * lin))
+    assert abs(s.linear_timesteps_weights.mean().item() - 1.0) < 1e-5 and s.linear_timesteps_weights.min() == 0
+    t = s.timesteps[[0, 400, 999]]
+    x0, n = torch.randn(3, 4, 8), torch.randn(3, 4, 8)
+    xt, target = s.add_noise(x0, n, t)
+    assert np.allclose(xt.numpy(), rectified_interpolate_array(x0, n, s.sigma_of(t)), atol=1e-6)
+    assert np.allclose(target.numpy(), velocity_target_array(x0, n), atol=1e-6)
+    mask = first_frame_loss_mask(1, 3, torch.tensor([False]))[0]
+    w = torch.tensor([0.5, 1.0, 2.0])
+    got = ops.weighted_masked_mse(xt, target, w, mask.float())
+    want = weighted_masked_mse_array(xt, target, mask.numpy()[:, None, None], w.numpy()[:, None, None])
+    assert abs(got.item() - want) < 1e-5
+    assert torch.allclose(ops.flow_to_x0(xt, target, s.sigma_of(t)), x0, atol=1e-5)
+
+
+def test_warmup_cosine():
+    f = lambda i: warmup_cosine_factor(i, warmup_steps=10, total_steps=110, min_lr_ratio=0.1)
+    assert f(0) == 0.1 and f(9) == 1.0 and abs(f(60) - 0.55) < 1e-9 and abs(f(110) - 0.1) < 1e-9
+
+
+def test_anyflow_time_pairs_types_and_windows():
+    g = torch.Generator().manual_seed(0)
+    pairs = [af.sample_time_pairs(4, dp_rank=r, dp_world=2, generator=torch.Generator().manual_seed(r)) for r in range(2)]
+    kinds = torch.cat([p.sample_type for p in pairs]).tolist()
+    assert kinds == [0, 0, 0, 0, 1, 1, 2, 2]
+    p = pairs[1]
+    assert torch.equal(p.r[p.is_consistency], torch.zeros(2))
+    fm = p.sample_type == af.FLOW_MAP
+    assert bool(((p.r[fm] > 0) & (p.r[fm] < p.t[fm])).all())
+    assert torch.equal(pairs[0].r, pairs[0].t)
+    tp, tm = af.difference_window(torch.tensor([998.0, 3.0, 500.0]), torch.tensor([0.0, 1.0, 499.0]))
+    assert tp.tolist() == [1000.0, 8.0, 505.0] and tm.tolist() == [993.0, 1.0, 499.0]
+    u_plus, u_minus = torch.full((3, 2), 4.0), torch.full((3, 2), 1.0)
+    d = af.central_difference(u_plus, u_minus, tp, tm)
+    assert torch.allclose(d[:, 0], torch.tensor([3 / 7, 3 / 7, 3 / 6]))
+    w = af.gaussian_timestep_weights(torch.tensor([500.0, 0.0]), shift=5.0)
+    assert w[0] > w[1]
+    with pytest.raises(ValueError):
+        af.sample_time_pairs(2, diffusion_ratio=0.8, consistency_ratio=0.5)
+
+
+def test_anyflow_adaptive_rescale():
+    loss = torch.tensor([2.0, 4.0, 8.0, 1.0])
+    is_diff = torch.tensor([True, True, False, False])
+    out = af.adaptive_rescale(loss, is_diff)
+    assert torch.allclose(out[:2], loss[:2]) and torch.allclose(out[2:], torch.tensor([3.0, 3.0]), atol=1e-3)
+    assert torch.equal(af.adaptive_rescale(loss, torch.zeros(4, dtype=torch.bool)), loss)
+    gathered = af.adaptive_rescale(loss, is_diff, gather_fn=lambda x: [x, x * 0 + (10.0 if x.dtype != torch.bool else 1)])
+    assert gathered.shape == loss.shape
+
+
+def test_sgf_gradient_masks_before_reducing():
+    assert [sgf.should_update_student(s, 5) for s in (0, 4, 5, 10)] == [False, False, True, True]
+    fake, real, out = torch.randn(2, 3, 4), torch.randn(2, 3, 4), torch.randn(2, 3, 4, requires_grad=True)
+    real[:, 0] = float("nan")
+    mask = torch.tensor([False, True, True]).view(1, 3, 1)
+    g = sgf.sgf_kl_gradient(fake_x0=fake, real_x0=real, student_output=out.detach(), mask=mask)
+    assert torch.isfinite(g).all() and g[:, 0].abs().sum() == 0
+    norm = (out.detach() - real)[:, 1:].abs().mean(dim=(1, 2), keepdim=True)
+    assert torch.allclose(g[:, 1:], (fake - real)[:, 1:] / norm, atol=1e-5)
+    loss = sgf.sgf_student_loss(out, g, mask=mask)
+    loss.backward()
+    assert torch.allclose(out.grad[:, 1:], g[:, 1:] / (2 * 2 * 4), atol=1e-6) and out.grad[:, 0].abs().sum() == 0

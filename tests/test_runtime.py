@@ -1,0 +1,157 @@
+import os
+import random
+import threading
+
+import numpy as np
+import pytest
+
+from solarwm_b200.errors import BackendContractError, CheckpointError, ConfigurationError
+from solarwm_b200.runtime import create_only, distributed as rdist, output_layout, provenance, randomness, safe_state
+from solarwm_b200.runtime.topology import Topology
+
+
+def test_topology_rank_algebra():
+    t = Topology(16, 11, 8, 3, 4)
+    assert (t.dp_rank, t.sp_rank, t.dp_size, t.node_rank, t.num_nodes) == (2, 3, 4, 1, 2)
+    assert t.sp_group_ranks() == (8, 9, 10, 11) and t.dp_group_ranks() == (3, 7, 11, 15)
+    env = {"WORLD_SIZE": "8", "RANK": "5", "LOCAL_WORLD_SIZE": "8", "LOCAL_RANK": "5"}
+    assert Topology.from_environ(2, env).dp_rank == 2
+    with pytest.raises(ConfigurationError):
+        Topology(8, 0, 8, 0, 3)
+    with pytest.raises(ConfigurationError):
+        Topology.from_environ(1, {})
+
+
+class FakeDist:
+    """Stands in for torch.distributed: every rank's record is supplied up front."""
+
+    def __init__(self, rank, world, records=None, broadcast_value=None):
+        self.rank, self.world, self.records, self.broadcast_value = rank, world, records, broadcast_value
+        self.ran_broadcast = False
+
+    def is_initialized(self):
+        return True
+
+    def get_rank(self):
+        return self.rank
+
+    def get_world_size(self):
+        return self.world
+
+    def all_gather_object(self, out, local):
+        for i in range(self.world):
+            out[i] = local if i == self.rank else self.records[i]
+
+    def broadcast_object_list(self, box, src=0):
+        self.ran_broadcast = True
+        if self.rank != src:
+            box[0] = self.broadcast_value
+
+
+def test_collective_error_is_rank_sorted_text_on_every_rank():
+    records = {0: (0, ""), 1: (1, "ValueError: bad shard"), 2: (2, ""), 3: (3, "OSError: disk")}
+    messages = []
+    for rank in range(4):
+        d = FakeDist(rank, 4, records)
+        with pytest.raises(BackendContractError) as e:
+            rdist.propagate_collective_error(records[rank][1], dist=d, label="phase")
+        messages.append(str(e.value))
+    assert len(set(messages)) == 1
+    assert messages[0] == "phase failed collectively: rank 1: ValueError: bad shard | rank 3: OSError: disk"
+
+
+def test_collective_call_chains_local_exception_and_rank_zero_call():
+    d = FakeDist(1, 2, {0: (0, "")})
+    with pytest.raises(BackendContractError) as e:
+        rdist.collective_call(lambda: (_ for _ in ()).throw(KeyError("k")), dist=d, label="load")
+    assert isinstance(e.value.__cause__, KeyError) and "rank 1: KeyError" in str(e.value)
+    ran = []
+    d1 = FakeDist(1, 2, {0: (0, "")}, broadcast_value="from-zero")
+    assert rdist.collective_rank_zero_call(lambda: ran.append(1) or "mine", dist=d1, label="x") == "from-zero"
+    assert ran == [] and d1.ran_broadcast
+    d0 = FakeDist(0, 2, {1: (1, "")})
+    assert rdist.collective_rank_zero_call(lambda: "zero", dist=d0, label="x") == "zero"
+    assert rdist.collective_call(lambda: 5, dist=None, label="single") == 5
+
+
+def test_malformed_exchange_and_fingerprints():
+    with pytest.raises(BackendContractError, match="malformed"):
+        rdist.propagate_collective_error("", dist=FakeDist(0, 2, {1: "oops"}), label="p")
+    with pytest.raises(BackendContractError, match="every raw rank"):
+        rdist.propagate_collective_error("", dist=FakeDist(0, 2, {1: (0, "")}), label="p")
+    a = rdist.identity_fingerprint({"s": ["a"], "n": [1]})
+    assert rdist.assert_peer_fingerprints([a, a]) == a
+    with pytest.raises(BackendContractError):
+        rdist.assert_peer_fingerprints([a, rdist.identity_fingerprint({"s": ["b"], "n": [1]})])
+    assert rdist.gather_and_assert_sp_identity({"x": 1}, sp_size=1) == rdist.identity_fingerprint({"x": 1})
+
+
+def test_create_only_publish_race_winner_is_never_replaced(tmp_path):
+    results = []
+
+    def publisher(i):
+        staging = tmp_path / f".stage{i}"
+        staging.mkdir()
+        (staging / "who").write_text(str(i))
+        try:
+            create_only.publish_directory_no_replace(staging, tmp_path / "public")
+            results.append(("won", i))
+        except FileExistsError:
+            results.append(("lost", i))
+
+    threads = [threading.Thread(target=publisher, args=(i,)) for i in range(6)]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    winners = [i for s, i in results if s == "won"]
+    assert len(winners) == 1 and (tmp_path / "public" / "who").read_text() == str(winners[0])
+    create_only.write_file_create_only(tmp_path / "f.bin", b"one")
+    with pytest.raises(FileExistsError):
+        create_only.write_file_create_only(tmp_path / "f.bin", b"two")
+    assert (tmp_path / "f.bin").read_bytes() == b"one"
+    create_only.link_file_create_only(tmp_path / "f.bin", tmp_path / "g.bin")
+    with pytest.raises(FileExistsError):
+        create_only.link_file_create_only(tmp_path / "f.bin", tmp_path / "g.bin")
+    src = tmp_path / "a"
+    src.write_text("a")
+    (tmp_path / "b").write_text("b")
+    with pytest.raises(FileExistsError):
+        create_only.rename_noreplace(src, tmp_path / "b")
+
+
+def test_rng_state_round_trip_is_plain_data():
+    random.seed(7)
+    np.random.seed(7)
+    enc_p, enc_n = safe_state.encode_python_rng(), safe_state.encode_numpy_rng()
+
+    def plain(v):
+        if isinstance(v, dict):
+            return all(isinstance(k, str) and plain(x) for k, x in v.items())
+        if isinstance(v, list):
+            return all(plain(x) for x in v)
+        return v is None or isinstance(v, (int, float, str))
+
+    assert plain(enc_p) and plain(enc_n)
+    want = (random.random(), np.random.rand())
+    random.random(), np.random.rand()
+    safe_state.restore_python_rng(enc_p)
+    safe_state.restore_numpy_rng(enc_n)
+    assert (random.random(), np.random.rand()) == want
+    with pytest.raises(CheckpointError):
+        safe_state.decode_python_rng({"schema": "other"})
+
+
+def test_seed_domains_layout_and_secrets():
+    assert randomness.objective_seed(3, 0) == 300009 and randomness.objective_seed(3, 2) == 300009 + 2048
+    assert randomness.model_init_seed("minimax_h3", 1) != randomness.model_init_seed("ltx25_video", 1)
+    assert randomness.stable_validation_seed("a", 1) == randomness.stable_validation_seed("a", 1)
+    assert output_layout.checkpoint_model_dir("/o", 12).name == "checkpoint_model_000012"
+    assert output_layout.public_validation_dir("/o", 5, "ema").as_posix() == "/o/validation/step_000005_ema"
+    assert output_layout.events_path("/o", 3).name == "rank-00003.jsonl"
+    assert output_layout.inference_layout({"inference": {"length_policy": "camera"}}) == "dataset_triplet_v1"
+    with pytest.raises(ConfigurationError):
+        output_layout.public_validation_dir("/o", 1, "../x")
+    provenance.reject_inline_secrets({"data": {"token_file": "/secrets/t"}})
+    with pytest.raises(ConfigurationError):
+        provenance.reject_inline_secrets({"data": {"api_key": "abc123"}})
+    with pytest.raises(ConfigurationError):
+        provenance.reject_inline_secrets({"x": ["ghp_" + "a" * 36]})
