@@ -1,0 +1,452 @@
+// Flash attention backward for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+//
+// One kernel template, launched twice:
+//
+//   MODE_DKV  CTA owns 128 keys (TMEM lane = key).  Stationary tiles K, V; streams 64-query tiles
+//             (Q_i, dO_i).   S^T = K Q_i^T,  dP^T = V dO_i^T,
+//             P^T = exp2(S^T c - L2[q]),  dS^T = P^T (dP^T - delta[q]) scale,
+//             dV += P^T dO_i,  dK += dS^T Q_i.
+//   MODE_DQ   CTA owns 128 queries (TMEM lane = query).  Stationary tiles Q, dO; streams 64-key
+//             tiles (K_j, V_j).   S = Q K_j^T,  dP = dO V_j^T,  dS as above (L2, delta per lane),
+//             dQ += dS K_j.
+//
+// L2 = log2(e) * logsumexp(scale * scores) and delta = rowsum(O * dO) come from the preprocess
+// kernel and are padded to a multiple of 128 rows (L2 = +large, delta = 0 in the padding), which
+// together with TMA zero-fill removes every boundary mask from the main loops.
+//
+// Roles: warp 0 TMA producer (stationary tiles once, then a 3-deep ring of streamed tile pairs),
+// warp 1 TMEM allocation + every tcgen05.mma, warps 4..7 / 8..11 two compute warpgroups that
+// alternate over streamed tiles (thread = TMEM lane).  The streamed tile in shared memory feeds
+// two different MMAs through two descriptors: K-major as the B operand of the score GEMMs and
+// MN-major as the B operand of the accumulate GEMMs.  P^T / dS are written back to TMEM as packed
+// bf16 over the first half of the S / dP columns and consumed as the A operand from TMEM.
+//
+// TMEM columns: buf0 {S [0,64) dP [64,128)}  buf1 {S [128,192) dP [192,256)}  acc0 [256,384)
+// acc1 [384,512).  Every wait is bounded (sm100.cuh).
+//
+// Replaces the flash_attn / cuDNN SDPA backward used by the reference
+// (solar/backends/wan22/runtime/modeling/attention.py:98-135, solar/backends/minimax_h3/fast_attention.py:103).
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace solar {
+
+constexpr int BW_THREADS = 384;
+constexpr int ST_ROWS = 128;   // stationary tile rows
+constexpr int SR_ROWS = 64;    // streamed tile rows
+constexpr int BW_STAGES = 3;
+
+struct AttnBwdParams {
+  int S_stat, S_stream, H, B;
+  int S_pad;             // padded length of the L2 / delta rows (multiple of 128)
+  float scale, scale_log2;
+  const float* L2;       // [B, H, S_pad]
+  const float* delta;    // [B, H, S_pad]
+  int* status;
+};
+
+template <int HD>
+struct BwdSmem {
+  static constexpr int CHUNKS = HD / 64;
+  static constexpr int STAT_CHUNK = ST_ROWS * 128;          // 16 KiB
+  static constexpr int STAT_TILE = STAT_CHUNK * CHUNKS;
+  static constexpr int STRM_CHUNK = SR_ROWS * 128;          // 8 KiB
+  static constexpr int STRM_TILE = STRM_CHUNK * CHUNKS;
+  static constexpr int STAT_OFF = 0;                        // stat0 | stat1
+  static constexpr int STRM_OFF = 2 * STAT_TILE;            // BW_STAGES x (stream0 | stream1)
+  static constexpr int BAR_OFF = STRM_OFF + BW_STAGES * 2 * STRM_TILE;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__device__ __forceinline__ void bw_tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2,
+                                                int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+// fp32 accumulator rows (this thread's TMEM lane) -> bf16 -> 128-byte-swizzled staging chunk(s).
+template <int NCOLS>
+__device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint8_t* region, int chunk_bytes, int row) {
+#pragma unroll
+  for (int cc = 0; cc < NCOLS / 32; ++cc) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_acc + cc * 32, r);
+    tmem_ld_wait();
+    uint8_t* dst = region + (cc / 2) * chunk_bytes + row * 128;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint4 o;
+      o.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+      o.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+      o.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+      o.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+      const int piece = (cc & 1) * 4 + g;
+      *reinterpret_cast<uint4*>(dst + ((piece ^ (row & 7)) << 4)) = o;
+    }
+  }
+}
+
+// MODE 0 = dK/dV, MODE 1 = dQ.
+template <int HD, int MODE>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_constant__ CUtensorMap tmStat1,
+                const __grid_constant__ CUtensorMap tmStrm0, const __grid_constant__ CUtensorMap tmStrm1,
+                const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
+                const AttnBwdParams p) {
+  using L = BwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* stat_full = bars;                        // 1
+  uint64_t* strm_full = bars + 1;                    // BW_STAGES
+  uint64_t* strm_empty = strm_full + BW_STAGES;      // BW_STAGES
+  uint64_t* s_ready = strm_empty + BW_STAGES;        // 2
+  uint64_t* p_ready = s_ready + 2;                   // 2
+  uint64_t* acc_done = p_ready + 2;                  // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * ST_ROWS;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int n_tiles = (p.S_stream + SR_ROWS - 1) / SR_ROWS;
+
+  if (threadIdx.x == 0) {
+    mbar_init(stat_full, 1);
+    for (int s = 0; s < BW_STAGES; ++s) {
+      mbar_init(&strm_full[s], 1);
+      mbar_init(&strm_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_ready[b], 1);
+      mbar_init(&p_ready[b], 128);
+    }
+    mbar_init(acc_done, 1);
+    *abort_word = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmStat0);
+    tma_prefetch_desc(&tmStat1);
+    tma_prefetch_desc(&tmStrm0);
+    tma_prefetch_desc(&tmStrm1);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // -------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(stat_full, 2 * L::STAT_TILE);
+#pragma unroll
+      for (int c = 0; c < L::CHUNKS; ++c) {
+        tma_load_4d(smem + L::STAT_OFF + c * L::STAT_CHUNK, &tmStat0, stat_full, c * 64, head, row0, batch);
+        tma_load_4d(smem + L::STAT_OFF + L::STAT_TILE + c * L::STAT_CHUNK, &tmStat1, stat_full, c * 64, head,
+                    row0, batch);
+      }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % BW_STAGES;
+        const uint32_t ph = (j / BW_STAGES) & 1;
+        if (!mbar_wait(&strm_empty[s], ph ^ 1, abort_word, ST_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&strm_full[s], 2 * L::STRM_TILE);
+        uint8_t* base = smem + L::STRM_OFF + s * 2 * L::STRM_TILE;
+#pragma unroll
+        for (int c = 0; c < L::CHUNKS; ++c) {
+          tma_load_4d(base + c * L::STRM_CHUNK, &tmStrm0, &strm_full[s], c * 64, head, j * SR_ROWS, batch);
+          tma_load_4d(base + L::STRM_TILE + c * L::STRM_CHUNK, &tmStrm1, &strm_full[s], c * 64, head,
+                      j * SR_ROWS, batch);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_score = umma_idesc_bf16(128, SR_ROWS, 0, 0);   // [128 x 64], K = HD
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);          // [128 x HD], K = 64, B MN-major
+      const uint32_t stat0 = smem_u32(smem + L::STAT_OFF);
+      const uint32_t stat1 = stat0 + L::STAT_TILE;
+      const uint32_t strm = smem_u32(smem + L::STRM_OFF);
+      auto score = [&](int b, int s) {
+        const uint32_t s0 = strm + s * 2 * L::STRM_TILE, s1 = s0 + L::STRM_TILE;
+        const uint32_t tS = tmem_base + b * 128, tD = tS + 64;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t oa = (kk / 4) * L::STAT_CHUNK + (kk % 4) * 32;
+          const uint32_t ob = (kk / 4) * L::STRM_CHUNK + (kk % 4) * 32;
+          umma_ss(tS, umma_desc_kmajor(stat0 + oa), umma_desc_kmajor(s0 + ob), idesc_score, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t oa = (kk / 4) * L::STAT_CHUNK + (kk % 4) * 32;
+          const uint32_t ob = (kk / 4) * L::STRM_CHUNK + (kk % 4) * 32;
+          umma_ss(tD, umma_desc_kmajor(stat1 + oa), umma_desc_kmajor(s1 + ob), idesc_score, kk != 0);
+        }
+        umma_commit(&s_ready[b]);
+      };
+      auto accumulate = [&](int t) -> bool {
+        const int b = t & 1, s = t % BW_STAGES;
+        if (!mbar_wait(&p_ready[b], (t >> 1) & 1, abort_word, ST_TIMEOUT_OTHER)) return false;
+        tc_fence_after();
+        const uint32_t s0 = strm + s * 2 * L::STRM_TILE, s1 = s0 + L::STRM_TILE;
+        const uint32_t tP = tmem_base + b * 128, tdS = tP + 64;
+        if (MODE == 0) {
+#pragma unroll
+          for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dV += P^T dO_i
+            umma_ts(tmem_base + 256, tP + kk * 8, umma_desc_mnmajor(s1 + kk * 2048, L::STRM_CHUNK), idesc_acc,
+                    (t | kk) != 0);
+#pragma unroll
+          for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dK += dS^T Q_i
+            umma_ts(tmem_base + 384, tdS + kk * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
+                    (t | kk) != 0);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dQ += dS K_j
+            umma_ts(tmem_base + 256, tdS + kk * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
+                    (t | kk) != 0);
+        }
+        umma_commit(&strm_empty[s]);
+        return true;
+      };
+      bool ok = mbar_wait(stat_full, 0, abort_word, ST_TIMEOUT_FULL);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % BW_STAGES;
+        const uint32_t ph = (j / BW_STAGES) & 1;
+        if (!mbar_wait(&strm_full[s], ph, abort_word, ST_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        score(j & 1, s);
+        if (j >= 1) ok = accumulate(j - 1);
+      }
+      if (ok) ok = accumulate(n_tiles - 1);
+      if (ok) umma_commit(acc_done);
+    }
+  } else if (warp >= 4) {
+    // -------------------------------------------------------------- compute warpgroups
+    const int wg = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_off + wg * 128, tD = tS + 64;
+    const long long vec_base = (static_cast<long long>(batch) * p.H + head) * p.S_pad;
+    const float c = p.scale_log2, sc = p.scale;
+    float my_L2 = 0.f, my_delta = 0.f;
+    if (MODE == 1) {
+      my_L2 = p.L2[vec_base + row0 + row];
+      my_delta = p.delta[vec_base + row0 + row];
+    }
+    bool ok = true;
+    for (int j = wg; j < n_tiles && ok; j += 2) {
+      if (!mbar_wait(&s_ready[wg], (j >> 1) & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32], d[32];
+        tmem_ld_32x32(tS + half * 32, s);
+        tmem_ld_32x32(tD + half * 32, d);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+        const float4* l4 = nullptr;
+        const float4* d4 = nullptr;
+        if (MODE == 0) {
+          l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + j * SR_ROWS + half * 32);
+          d4 = reinterpret_cast<const float4*>(p.delta + vec_base + j * SR_ROWS + half * 32);
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          float L[4], Dl[4];
+          if (MODE == 0) {
+            const float4 a = __ldg(l4 + g), b = __ldg(d4 + g);
+            L[0] = a.x; L[1] = a.y; L[2] = a.z; L[3] = a.w;
+            Dl[0] = b.x; Dl[1] = b.y; Dl[2] = b.z; Dl[3] = b.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { L[e] = my_L2; Dl[e] = my_delta; }
+          }
+          float pv[4], dv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            pv[e] = exp2_fast(fmaf(__uint_as_float(s[g * 4 + e]), c, -L[e]));
+            dv[e] = pv[e] * (__uint_as_float(d[g * 4 + e]) - Dl[e]) * sc;
+          }
+          pk[g * 2] = pack_bf16x2(pv[0], pv[1]);
+          pk[g * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+          dk[g * 2] = pack_bf16x2(dv[0], dv[1]);
+          dk[g * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
+        }
+        if (MODE == 0) tmem_st_32x16(tS + half * 16, pk);
+        tmem_st_32x16(tD + half * 16, dk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_ready[wg]);
+    }
+    // ---- epilogue: accumulators -> bf16 -> shared memory (stationary buffers) -> TMA store
+    if (ok) ok = mbar_wait(acc_done, 0, abort_word, ST_TIMEOUT_OTHER);
+    if (ok) {
+      tc_fence_after();
+      if (MODE == 0) {
+        // warpgroup 0 drains dV (acc0), warpgroup 1 drains dK (acc1)
+        uint8_t* region = smem + L::STAT_OFF + wg * L::STAT_TILE;
+        acc_to_smem<HD>(tmem_base + lane_off + 256 + wg * 128, region, L::STAT_CHUNK, row);
+        fence_proxy_async_smem();
+        named_bar_sync(1 + wg, 128);
+        if (quarter == 0 && lane == 0) {
+          const CUtensorMap* out = wg == 0 ? &tmOut0 : &tmOut1;
+#pragma unroll
+          for (int ch = 0; ch < L::CHUNKS; ++ch)
+            bw_tma_store_4d(out, region + ch * L::STAT_CHUNK, ch * 64, head, row0, batch);
+          tma_store_commit();
+          tma_store_wait_all<0>();
+        }
+      } else {
+        // dQ (acc0): each warpgroup drains one 64-column chunk
+        if (wg < L::CHUNKS) {
+          uint8_t* region = smem + L::STAT_OFF + wg * L::STAT_CHUNK;
+          acc_to_smem<64>(tmem_base + lane_off + 256 + wg * 64, region, L::STAT_CHUNK, row);
+          fence_proxy_async_smem();
+          named_bar_sync(1 + wg, 128);
+          if (quarter == 0 && lane == 0) {
+            bw_tma_store_4d(&tmOut0, region, wg * 64, head, row0, batch);
+            tma_store_commit();
+            tma_store_wait_all<0>();
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_word != 0) bounded_drain_pause();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicExch(p.status, *abort_word);
+}
+
+// L2[i] = log2(e) * lse[i], delta[i] = sum_d O[i,d] dO[i,d]; rows >= S get (+1e30, 0).
+// One warp per row; grid covers B*H*S_pad rows.
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, const float* lse,
+                                     float* L2, float* delta, int B, int S, int H, int D, int S_pad,
+                                     long long o_ss, long long o_sb, long long do_ss, long long do_sb) {
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * H * S_pad;
+  if (gw >= total) return;
+  const int i = static_cast<int>(gw % S_pad);
+  const long long bh = gw / S_pad;
+  const int h = static_cast<int>(bh % H);
+  const int b = static_cast<int>(bh / H);
+  if (i >= S) {
+    if (lane == 0) { L2[gw] = 1e30f; delta[gw] = 0.f; }
+    return;
+  }
+  const __nv_bfloat16* po = o + b * o_sb + i * o_ss + static_cast<long long>(h) * D;
+  const __nv_bfloat16* pd = dout + b * do_sb + i * do_ss + static_cast<long long>(h) * D;
+  float acc = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + d));
+    const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + d));
+    acc += a.x * g.x + a.y * g.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    delta[gw] = acc;
+    L2[gw] = lse[(static_cast<long long>(b) * H + h) * S + i] * 1.4426950408889634f;
+  }
+}
+
+static int bshd_map(CUtensorMap* m, const void* ptr, int B, int S, int H, int D, long long ss, long long sb,
+                    int box_rows) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)ss * 2, (uint64_t)sb * 2};
+  const uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return make_tmap_4d(m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dims, strides, box);
+}
+
+template <int HD, int MODE>
+static int launch_bwd(const CUtensorMap* maps, const AttnBwdParams& p, cudaStream_t st) {
+  auto kern = attn_bwd_kernel<HD, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<HD>::TOTAL));
+    configured = true;
+  }
+  dim3 grid((p.S_stat + ST_ROWS - 1) / ST_ROWS, p.H, p.B);
+  kern<<<grid, BW_THREADS, BwdSmem<HD>::TOTAL, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace solar
+
+using namespace solar;
+
+// All tensors are [B, S, H, D] bf16 with unit stride on D and stride D on H; *_ss / *_sb are the
+// element strides of the sequence and batch axes.  lse [B,H,Sq] fp32 (natural log, from the
+// forward kernel).  scratch: 2 * B*H*Sq_pad fp32 of caller-provided memory, Sq_pad = Sq rounded
+// up to 128.  Writes dq [B,Sq,H,D], dk and dv [B,Sk,H,D] (contiguous).
+extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                              const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq,
+                              int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
+                              long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
+                              long long do_ss, long long do_sb, float scale, int* status, void* stream) {
+  if (D != 64 && D != 128) return fail("attention backward: head_dim must be 64 or 128%s");
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0) return fail("attention backward: empty problem%s");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int Sq_pad = (Sq + 127) / 128 * 128;
+  float* L2 = scratch;
+  float* delta = scratch + static_cast<long long>(B) * H * Sq_pad;
+  {
+    const long long warps = static_cast<long long>(B) * H * Sq_pad;
+    const int block = 256;
+    const long long blocks = (warps * 32 + block - 1) / block;
+    attn_bwd_prep_kernel<<<(unsigned)blocks, block, 0, st>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, L2, delta, B, Sq, H, D, Sq_pad, o_ss, o_sb,
+        do_ss, do_sb);
+    SOLAR_CUDA_OK(cudaGetLastError());
+  }
+  AttnBwdParams p;
+  p.H = H; p.B = B; p.S_pad = Sq_pad;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.L2 = L2; p.delta = delta; p.status = status;
+  const long long c_ss = static_cast<long long>(H) * D;   // contiguous outputs
+  int rc;
+  {
+    // dK / dV: stationary K, V (128-row boxes); streamed Q, dO (64-row boxes)
+    CUtensorMap m[6];
+    if ((rc = bshd_map(&m[0], k, B, Sk, H, D, k_ss, k_sb, ST_ROWS))) return rc;
+    if ((rc = bshd_map(&m[1], v, B, Sk, H, D, v_ss, v_sb, ST_ROWS))) return rc;
+    if ((rc = bshd_map(&m[2], q, B, Sq, H, D, q_ss, q_sb, SR_ROWS))) return rc;
+    if ((rc = bshd_map(&m[3], dout, B, Sq, H, D, do_ss, do_sb, SR_ROWS))) return rc;
+    if ((rc = bshd_map(&m[4], dv, B, Sk, H, D, c_ss, c_ss * Sk, ST_ROWS))) return rc;
+    if ((rc = bshd_map(&m[5], dk, B, Sk, H, D, c_ss, c_ss * Sk, ST_ROWS))) return rc;
+    p.S_stat = Sk; p.S_stream = Sq;
+    rc = D == 128 ? launch_bwd<128, 0>(m, p, st) : launch_bwd<64, 0>(m, p, st);
+    if (rc) return rc;
+  }
+  {
+    // dQ: stationary Q, dO; streamed K, V
+    CUtensorMap m[6];
+    if ((rc = bshd_map(&m[0], q, B, Sq, H, D, q_ss, q_sb, ST_ROWS))) return rc;
+    if ((rc = bshd_map(&m[1], dout, B, Sq, H, D, do_ss, do_sb, ST_ROWS))) return rc;
+    if ((rc = bshd_map(&m[2], k, B, Sk, H, D, k_ss, k_sb, SR_ROWS))) return rc;
+    if ((rc = bshd_map(&m[3], v, B, Sk, H, D, v_ss, v_sb, SR_ROWS))) return rc;
+    if ((rc = bshd_map(&m[4], dq, B, Sq, H, D, c_ss, c_ss * Sq, ST_ROWS))) return rc;
+    m[5] = m[4];
+    p.S_stat = Sq; p.S_stream = Sk;
+    rc = D == 128 ? launch_bwd<128, 1>(m, p, st) : launch_bwd<64, 1>(m, p, st);
+    if (rc) return rc;
+  }
+  return 0;
+}

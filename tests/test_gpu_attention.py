@@ -59,6 +59,23 @@ def test_attention_strided_views_of_fused_qkv():
     assert ((o.float() - ref).norm() / ref.norm()).item() < 1e-2
 
 
+@pytest.mark.parametrize("B,Sq,Sk,H,D", [(1, 256, 256, 2, 128), (1, 128, 64, 1, 128), (2, 300, 520, 2, 128),
+                                          (1, 1000, 777, 2, 128), (1, 384, 512, 3, 64), (1, 2100, 2100, 1, 128)])
+def test_attention_backward(B, Sq, Sk, H, D):
+    q, k, v = (_mk(B, n, H, D, s).requires_grad_(True) for n, s in ((Sq, 21), (Sk, 22), (Sk, 23)))
+    ops.reset_counters()
+    o = ops.attention(q, k, v, backend="native")
+    g = _mk(B, Sq, H, D, 24)
+    o.backward(g)
+    ops.check_status()
+    assert ops.COUNTERS.get("attn_bwd", 0) == 3 and "library_sdpa_bwd" not in ops.COUNTERS
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    R.attention(q2, k2, v2).backward(g.float())
+    for name, a, b in (("dq", q.grad, q2.grad), ("dk", k.grad, k2.grad), ("dv", v.grad, v2.grad)):
+        rel = ((a.float() - b).norm() / b.norm()).item()
+        assert rel < 2e-2, (name, rel)
+
+
 def test_attention_autograd_path():
     B, S, H, D = 1, 256, 2, 128
     q, k, v = (_mk(B, S, H, D, s).requires_grad_(True) for s in (11, 12, 13))
