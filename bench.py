@@ -42,7 +42,7 @@ def parse_args():
     ap.add_argument("--frames", type=int, default=31)
     ap.add_argument("--height", type=int, default=44)
     ap.add_argument("--width", type=int, default=80)
-    ap.add_argument("--checkpointing", default="auto", choices=["auto", "none", "full"])
+    ap.add_argument("--checkpointing", default="auto", choices=["auto", "none", "full", "selective"])
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
     return ap.parse_args()
 
@@ -164,7 +164,7 @@ def run_ours(args):
     cfg = model_config(args)
     ckpt = args.checkpointing
     if ckpt == "auto":
-        ckpt = "full" if (args.model == "ti2v_5b" and world < 4) else "none"
+        ckpt = "selective" if (args.model == "ti2v_5b" and world < 4) else "none"
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
                            max_grad_norm=1.0, seed=0)
     trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp)

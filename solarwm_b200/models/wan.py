@@ -207,7 +207,7 @@ class WanBlock(nn.Module):
             return F_._LinearMainGradFn.apply(x, w, b)
         return F_.gemm(x, w, F_.NT, bias=b)
 
-    def forward(self, x, e0, rope, context, *, B, L, frame_tokens, group_offset=0, sp=None):
+    def forward(self, x, e0, rope, context, *, B, L, frame_tokens, group_offset=0, sp=None, memo=None):
         """x [B*L_local, dim]; e0 fp32 [G, 6, dim] (G = B * frames); context [B*T, dim]."""
         cfg = self.cfg
         D, H, hd = cfg.dim, cfg.num_heads, cfg.head_dim
@@ -224,7 +224,7 @@ class WanBlock(nn.Module):
         Ll = x.shape[0] // B
         q, k, v = (t.reshape(B, Ll, H, hd) for t in (q, k, v))
         q, k, v = sp.scatter_heads(q, k, v)
-        o = ops.attention(q, k, v)
+        o = ops.attention(q, k, v, memo=None if memo is None else (memo, "self"))
         o = sp.gather_heads(o).reshape(B * Ll, D)
         y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
         x = F_.gated_residual(x, y, mod[:, 2], **gk)
@@ -241,7 +241,8 @@ class WanBlock(nn.Module):
         kc = F_.rmsnorm_rope(kvc[:, :D], self._p("cross_attn.norm_k.weight").float(), None, eps=cfg.eps)
         vc = kvc[:, D:]
         T = context.shape[0] // B
-        oc = ops.attention(qc.reshape(B, Ll, H, hd), kc.reshape(B, T, H, hd), vc.reshape(B, T, H, hd))
+        oc = ops.attention(qc.reshape(B, Ll, H, hd), kc.reshape(B, T, H, hd), vc.reshape(B, T, H, hd),
+                           memo=None if memo is None else (memo, "cross"))
         yc = self._linear(oc.reshape(B * Ll, D), "cross_attn.o.weight", "cross_attn.o.bias")
         x = F_.gated_residual(x, yc, None)
 
@@ -286,7 +287,7 @@ class WanDiT(nn.Module):
             _register(self, name, self.stem.parameter(name))
         self.blocks = nn.ModuleList([WanBlock(cfg, device, dtype, shard_pad) for _ in range(cfg.num_layers)])
         self.sp = _NoSP()
-        self.checkpointing = "none"  # "none" | "full"
+        self.checkpointing = "none"  # "none" | "full" | "selective"
         self._rope_cache: dict = {}
         if seed is not None:
             self.init_weights(seed)
@@ -401,10 +402,15 @@ class WanDiT(nn.Module):
         return F_.linear(c, P["text_embedding.2.weight"], P["text_embedding.2.bias"])
 
     def _run_block(self, block, x, e0, rope, ctx, kw):
-        if self.checkpointing == "full" and torch.is_grad_enabled():
+        """``checkpointing``: "none" keeps every activation; "full" recomputes the whole block in
+        backward; "selective" recomputes the block except its two attention calls, whose outputs are
+        carried across the recompute (the reference's saved-attention policy,
+        solar/backends/minimax_h3/fsdp.py:146-165)."""
+        if self.checkpointing in ("full", "selective") and torch.is_grad_enabled():
             from torch.utils.checkpoint import checkpoint
 
-            return checkpoint(lambda a, b, c: block(a, b, rope, c, **kw), x, e0, ctx, use_reentrant=False)
+            memo = {"__store__": True} if (self.checkpointing == "selective" and x.is_cuda) else None
+            return checkpoint(lambda a, b, c: block(a, b, rope, c, memo=memo, **kw), x, e0, ctx, use_reentrant=False)
         return block(x, e0, rope, ctx, **kw)
 
     def forward(self, x, t, context, y=None, r=None):

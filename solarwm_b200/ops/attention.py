@@ -45,10 +45,19 @@ def native_supported(q, k) -> bool:
 
 class _AttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale):
+    def forward(ctx, q, k, v, scale, memo):
         from .attention_native import attn_fwd
 
-        o, lse = attn_fwd(q, k, v, scale)
+        # ``memo`` = (dict, key): under activation checkpointing the first forward stores the
+        # attention output and log-sum-exp there and the recompute pass takes them back instead
+        # of running the kernel a second time (attention is the one op too costly to recompute).
+        cached = None if memo is None else memo[0].pop(memo[1], None)
+        if cached is not None:
+            o, lse = cached
+        else:
+            o, lse = attn_fwd(q, k, v, scale)
+            if memo is not None and memo[0].get("__store__", False):
+                memo[0][memo[1]] = (o, lse)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.scale = scale
         return o
@@ -59,11 +68,12 @@ class _AttnFn(torch.autograd.Function):
 
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = attn_bwd(q, k, v, o, lse, do.contiguous(), ctx.scale)
-        return dq, dk, dv, None
+        return dq, dk, dv, None, None
 
 
-def attention(q, k, v, *, scale=None, backend=None):
-    """Bidirectional softmax attention; q ``[B, Sq, H, D]``, k/v ``[B, Sk, H, D]`` -> ``[B, Sq, H, D]``."""
+def attention(q, k, v, *, scale=None, backend=None, memo=None):
+    """Bidirectional softmax attention; q ``[B, Sq, H, D]``, k/v ``[B, Sk, H, D]`` -> ``[B, Sq, H, D]``.
+    ``memo`` is an optional ``(dict, key)`` slot used to carry the output across a checkpoint recompute."""
     d = q.shape[-1]
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(d)
     if not q.is_cuda:
@@ -72,6 +82,6 @@ def attention(q, k, v, *, scale=None, backend=None):
     if backend == "native":
         if not native_supported(q, k):
             raise _lib.NativeError(f"native attention does not support head_dim={d}")
-        return _AttnFn.apply(q, k, v, scale)
+        return _AttnFn.apply(q, k, v, scale, memo)
     count("library_sdpa")
     return _library_attention(q, k, v, scale)
