@@ -22,6 +22,7 @@
 //
 // Replaces flash_attn_varlen_func / SDPA on the reference's attention path
 // (solar/backends/wan22/runtime/modeling/attention.py:34-188).
+#include "comm.cuh"
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -64,7 +65,7 @@ template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
-                const AttnParams p) {
+                const AttnParams p, const __grid_constant__ RowScatter rs) {
   using L = AttnSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -303,6 +304,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32(tO + cc * 32, r);
         tmem_ld_wait();
         uint8_t* dst = obuf + (cc / 2) * L::CHUNK_BYTES + row * 128;
+        // Ulysses gather of the attention output: the row also goes straight to the rank that owns
+        // this token, into the column block of this rank's heads (peer stores over NVLink).
+        uint4* remote = nullptr;
+        if (rs.active() && (q0 + t * QT + row) < p.Sq)
+          remote = reinterpret_cast<uint4*>(rs.addr(q0 + t * QT + row, head * HD + cc * 32, 2));
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 o;
@@ -312,6 +318,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           o.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * inv_l, __uint_as_float(r[g * 8 + 7]) * inv_l);
           const int piece = (cc & 1) * 4 + g;  // 16-byte piece inside the 128-byte row
           *reinterpret_cast<uint4*>(dst + ((piece ^ (row & 7)) << 4)) = o;
+          if (remote != nullptr) remote[g] = o;
         }
       }
       const int qrow = q0 + t * QT + row;
@@ -338,11 +345,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicExch(p.status, *abort_word);
+  if (rs.active()) cta_done_signal_peers(rs.flags);
 }
 
 template <int HD>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                           const CUtensorMap& to, const AttnParams& p, cudaStream_t st) {
+                           const CUtensorMap& to, const AttnParams& p, cudaStream_t st, const RowScatter& rs) {
   auto kern = attn_fwd_kernel<HD>;
   static bool configured = false;
   if (!configured) {
@@ -350,7 +358,7 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
     configured = true;
   }
   dim3 grid((p.Sq + 2 * QT - 1) / (2 * QT), p.H, p.B);
-  kern<<<grid, ATT_THREADS, AttnSmem<HD>::TOTAL, st>>>(tq, tk, tv, to, p);
+  kern<<<grid, ATT_THREADS, AttnSmem<HD>::TOTAL, st>>>(tq, tk, tv, to, p, rs);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -370,10 +378,10 @@ using namespace solar;
 // q [B,Sq,H,D], k/v [B,Sk,H,D], o [B,Sq,H,D] bf16 with unit stride on D, stride D on H and the
 // given element strides on the sequence and batch axes (so q/k/v may be slices of a fused QKV
 // buffer).  lse [B,H,Sq] fp32 or null.
-extern "C" int solar_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B,
-                              int Sq, int Sk, int H, int D, long long q_ss, long long q_sb,
-                              long long k_ss, long long k_sb, long long v_ss, long long v_sb,
-                              long long o_ss, long long o_sb, float scale, int* status, void* stream) {
+static int attn_fwd_entry(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                          int H, int D, long long q_ss, long long q_sb, long long k_ss, long long k_sb,
+                          long long v_ss, long long v_sb, long long o_ss, long long o_sb, float scale, int* status,
+                          void* stream, const RowScatter& rs) {
   if (D != 64 && D != 128) return fail("attention: head_dim must be 64 or 128%s");
   if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0) return fail("attention: empty problem%s");
   CUtensorMap tq, tk, tv, to;
@@ -389,6 +397,43 @@ extern "C" int solar_attn_fwd(const void* q, const void* k, const void* v, void*
   p.lse = lse;
   p.status = status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 128) return launch_attn_fwd<128>(tq, tk, tv, to, p, st);
-  return launch_attn_fwd<64>(tq, tk, tv, to, p, st);
+  if (D == 128) return launch_attn_fwd<128>(tq, tk, tv, to, p, st, rs);
+  return launch_attn_fwd<64>(tq, tk, tv, to, p, st, rs);
+}
+
+extern "C" int solar_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B,
+                              int Sq, int Sk, int H, int D, long long q_ss, long long q_sb,
+                              long long k_ss, long long k_sb, long long v_ss, long long v_sb,
+                              long long o_ss, long long o_sb, float scale, int* status, void* stream) {
+  RowScatter none;
+  memset(&none, 0, sizeof(none));
+  return attn_fwd_entry(q, k, v, o, lse, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss, v_sb, o_ss, o_sb, scale,
+                        status, stream, none);
+}
+
+// Attention over this rank's heads and the whole sequence whose output rows are, in addition to
+// the local copy in `o`, stored into the token owner's buffer (Ulysses output exchange fused into
+// the epilogue): row i goes to the rank r with row_start[r] <= i < row_start[r+1], at local row
+// i - row_start[r], columns col_offset + head*D .. of a [*, dst_ld] matrix.  B must be 1.
+extern "C" int solar_attn_fwd_scatter(const void* q, const void* k, const void* v, void* o, float* lse, int Sq,
+                                      int Sk, int H, int D, long long q_ss, long long k_ss, long long v_ss,
+                                      long long o_ss, float scale, int* status, void* stream,
+                                      void* const* dst_bases, void* const* flag_ptrs, unsigned* counter,
+                                      int n_ranks, long long dst_ld, const int* row_start, int col_offset) {
+  if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("attention scatter: rank count out of range%s");
+  RowScatter rs;
+  memset(&rs, 0, sizeof(rs));
+  rs.dst.n = n_ranks;
+  rs.flags.n = n_ranks;
+  for (int i = 0; i < n_ranks; ++i) {
+    rs.dst.base[i] = dst_bases[i];
+    rs.flags.flag[i] = static_cast<unsigned*>(flag_ptrs[i]);
+    rs.row_start[i] = row_start[i];
+  }
+  rs.row_start[n_ranks] = row_start[n_ranks];
+  rs.flags.local_counter = counter;
+  rs.ld = dst_ld;
+  rs.col_offset = col_offset;
+  return attn_fwd_entry(q, k, v, o, lse, 1, Sq, Sk, H, D, q_ss, q_ss * Sq, k_ss, k_ss * Sk, v_ss, v_ss * Sk, o_ss,
+                        o_ss * Sq, scale, status, stream, rs);
 }

@@ -1,0 +1,146 @@
+// Peer-memory communication runtime for one node of NVLink-connected GPUs (one process per GPU).
+//
+// Host side: device buffers that every rank of the group can address.  Each rank allocates the
+// same layout ("symmetric"), exports a CUDA IPC handle, the handles are exchanged by the Python
+// layer over the existing process group, and every rank maps its peers' buffers.  Kernels then
+// receive the table of peer base pointers and read/write peers' memory directly over NVLink with
+// ordinary global loads/stores (or TMA without cluster qualifiers).
+//
+// Device side: monotonically increasing 32-bit flags in symmetric memory.
+//   producer:  all CTAs of a kernel write their tiles, fence at system scope and bump a local
+//              counter; the last CTA adds 1 to the flag word in EVERY rank's memory (release).
+//   consumer:  solar_comm_wait enqueues a one-thread kernel that polls the local flag (acquire)
+//              until it reaches the expected count, with a wall-clock bound: on timeout it writes a
+//              status code and returns, so no stream can hang on a missing peer.
+//
+// The reference moves the same data with NCCL all_to_all_single / all_gather / all_reduce plus
+// packing copies (solar/backends/wan22/runtime/sequence_parallel.py:335-622).
+#include "comm.cuh"
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace solar {
+
+__global__ void comm_wait_kernel(const unsigned* flag, unsigned expected, int* status, unsigned long long limit_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    // counters only grow; compare with wrap-around in mind
+    if (static_cast<int>(v - expected) >= 0) return;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      if (status) atomicExch(status, ST_TIMEOUT_PEER);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
+__global__ void comm_signal_kernel(PeerFlags flags) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) signal_all_peers(flags);
+}
+
+// Plain peer copy used by tests and by the all-gather of small vectors: every rank pushes
+// `bytes` from src to offset `dst_off` of each peer's buffer, then signals.
+__global__ void comm_push_kernel(const uint4* src, PeerTable dst, long long dst_off_bytes, long long n16,
+                                 PeerFlags flags) {
+  for (int r = 0; r < dst.n; ++r) {
+    uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst.base[r]) + dst_off_bytes);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n16;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+      out[i] = src[i];
+  }
+  cta_done_signal_peers(flags);
+}
+
+}  // namespace solar
+
+using namespace solar;
+
+extern "C" int solar_comm_alloc(long long bytes, void** out) {
+  void* p = nullptr;
+  SOLAR_CUDA_OK(cudaMalloc(&p, static_cast<size_t>(bytes)));
+  SOLAR_CUDA_OK(cudaMemset(p, 0, static_cast<size_t>(bytes)));
+  SOLAR_CUDA_OK(cudaDeviceSynchronize());
+  *out = p;
+  return 0;
+}
+
+extern "C" int solar_comm_free(void* p) {
+  SOLAR_CUDA_OK(cudaFree(p));
+  return 0;
+}
+
+extern "C" int solar_comm_ipc_handle(void* p, unsigned char* out64) {
+  cudaIpcMemHandle_t h;
+  SOLAR_CUDA_OK(cudaIpcGetMemHandle(&h, p));
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(out64, &h, 64);
+  return 0;
+}
+
+extern "C" int solar_comm_ipc_open(const unsigned char* in64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, in64, 64);
+  void* p = nullptr;
+  SOLAR_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *out = p;
+  return 0;
+}
+
+extern "C" int solar_comm_ipc_close(void* p) {
+  SOLAR_CUDA_OK(cudaIpcCloseMemHandle(p));
+  return 0;
+}
+
+// Same-process peers (tests that drive two GPUs from one process): enable direct access.
+extern "C" int solar_comm_enable_peer(int peer_device) {
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    return 0;
+  }
+  SOLAR_CUDA_OK(e);
+  return 0;
+}
+
+extern "C" int solar_comm_wait(const void* flag, unsigned expected, int* status, double limit_seconds, void* stream) {
+  const unsigned long long ns = static_cast<unsigned long long>(limit_seconds * 1e9);
+  comm_wait_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned*>(flag), expected,
+                                                                       status, ns);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+static PeerFlags make_flags(void* const* flag_ptrs, int n, unsigned* counter) {
+  PeerFlags f;
+  f.n = n;
+  for (int i = 0; i < kMaxPeers; ++i) f.flag[i] = i < n ? static_cast<unsigned*>(flag_ptrs[i]) : nullptr;
+  f.local_counter = counter;
+  return f;
+}
+
+extern "C" int solar_comm_signal(void* const* flag_ptrs, int n, void* stream) {
+  if (n < 1 || n > kMaxPeers) return fail("comm: peer count out of range%s");
+  comm_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_flags(flag_ptrs, n, nullptr));
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// counter: a zero-initialised local u32 the kernel uses to find its last CTA (it resets it).
+extern "C" int solar_comm_push(const void* src, void* const* dst_bases, int n, long long dst_off_bytes,
+                               long long bytes, void* const* flag_ptrs, unsigned* counter, void* stream) {
+  if (n < 1 || n > kMaxPeers) return fail("comm: peer count out of range%s");
+  if (bytes % 16 != 0 || dst_off_bytes % 16 != 0) return fail("comm: push size and offset must be multiples of 16%s");
+  PeerTable t;
+  t.n = n;
+  for (int i = 0; i < kMaxPeers; ++i) t.base[i] = i < n ? dst_bases[i] : nullptr;
+  const long long n16 = bytes / 16;
+  int grid = static_cast<int>((n16 + 255) / 256);
+  if (grid > 4 * sm_count()) grid = 4 * sm_count();
+  if (grid < 1) grid = 1;
+  comm_push_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), t, dst_off_bytes, n16, make_flags(flag_ptrs, n, counter));
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -16,6 +16,7 @@
 //
 // Replaces the cuBLAS calls behind every nn.Linear of the reference models
 // (reference: solar/backends/wan22/runtime/modeling/model.py:112-147, 230-233).
+#include "comm.cuh"
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -61,7 +62,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int A_MN, int B_MN, int OUT_F32>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p,
+                 const __grid_constant__ ColScatter sc) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -254,6 +256,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
           }
         }
+        if (!OUT_F32 && sc.active() && ncol >= sc.first_col) {
+          // Ulysses scatter: this 64-column chunk belongs to one head, hence to one rank.  The
+          // thread owns one output row; it copies its 128 staged bytes straight into the owning
+          // rank's receive buffer over NVLink (the staging pass above already applied the epilogue).
+          __syncwarp();
+          const int grow = m0 + q * 32 + lane;
+          if (grow < p.M) {
+            uint4* out = reinterpret_cast<uint4*>(sc.addr(grow, ncol, 2));
+#pragma unroll
+            for (int g = 0; g < 8; ++g) out[g] = *reinterpret_cast<const uint4*>(dst + ((g ^ (lane & 7)) << 4));
+          }
+          __syncwarp();
+          if (lane == 0) tma_store_commit();   // empty group: keeps the two-deep staging count aligned
+          buf ^= 1;
+          continue;
+        }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && rows_live) {
@@ -286,11 +304,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicExch(p.status, *abort_word);
+  if (sc.active()) cta_done_signal_peers(sc.flags);
 }
 
 template <int A_MN, int B_MN, int OUT_F32>
 static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
-                       const GemmParams& p, int max_ctas, cudaStream_t stream) {
+                       const GemmParams& p, int max_ctas, cudaStream_t stream, const ColScatter& sc) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT_F32>;
   static bool configured = false;
   if (!configured) {
@@ -300,7 +319,7 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   int grid = p.tiles_m * p.tiles_n;
   int cap = max_ctas > 0 ? max_ctas : sm_count();
   if (grid > cap) grid = cap;
-  kern<<<grid, GEMM_THREADS, SMEM_TOTAL, stream>>>(tA, tB, tC, p);
+  kern<<<grid, GEMM_THREADS, SMEM_TOTAL, stream>>>(tA, tB, tC, p, sc);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -313,10 +332,9 @@ using namespace solar;
 // dimensions in elements of the row-major arrays as they sit in memory.
 // out_f32: C is fp32 instead of bf16.  accumulate: C += (atomic-free TMA reduce-add).
 // status: optional device int that receives a non-zero code if a bounded wait gave up.
-extern "C" int solar_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N,
-                               int K, long long lda, long long ldb, long long ldc, int layout,
-                               int act, int out_f32, int accumulate, int* status, int max_ctas,
-                               void* stream) {
+static int gemm_entry(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                      long long ldb, long long ldc, int layout, int act, int out_f32, int accumulate, int* status,
+                      int max_ctas, void* stream, const ColScatter& sc) {
   if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: empty problem%s");
   if (N % 8 != 0) return fail("gemm: N must be a multiple of 8%s");
   if (layout < 0 || layout > 2) return fail("gemm: bad layout%s");
@@ -351,13 +369,56 @@ extern "C" int solar_gemm_bf16(const void* A, const void* B, void* C, const void
   p.status = status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (layout * 2 + (out_f32 ? 1 : 0)) {
-    case 0: return launch_gemm<0, 0, 0>(tA, tB, tC, p, max_ctas, st);
-    case 1: return launch_gemm<0, 0, 1>(tA, tB, tC, p, max_ctas, st);
-    case 2: return launch_gemm<0, 1, 0>(tA, tB, tC, p, max_ctas, st);
-    case 3: return launch_gemm<0, 1, 1>(tA, tB, tC, p, max_ctas, st);
-    case 4: return launch_gemm<1, 1, 0>(tA, tB, tC, p, max_ctas, st);
-    default: return launch_gemm<1, 1, 1>(tA, tB, tC, p, max_ctas, st);
+    case 0: return launch_gemm<0, 0, 0>(tA, tB, tC, p, max_ctas, st, sc);
+    case 1: return launch_gemm<0, 0, 1>(tA, tB, tC, p, max_ctas, st, sc);
+    case 2: return launch_gemm<0, 1, 0>(tA, tB, tC, p, max_ctas, st, sc);
+    case 3: return launch_gemm<0, 1, 1>(tA, tB, tC, p, max_ctas, st, sc);
+    case 4: return launch_gemm<1, 1, 0>(tA, tB, tC, p, max_ctas, st, sc);
+    default: return launch_gemm<1, 1, 1>(tA, tB, tC, p, max_ctas, st, sc);
   }
+}
+
+extern "C" int solar_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N,
+                               int K, long long lda, long long ldb, long long ldc, int layout,
+                               int act, int out_f32, int accumulate, int* status, int max_ctas,
+                               void* stream) {
+  ColScatter none;
+  memset(&none, 0, sizeof(none));
+  return gemm_entry(A, B, C, bias, M, N, K, lda, ldb, ldc, layout, act, out_f32, accumulate, status, max_ctas,
+                    stream, none);
+}
+
+// GEMM whose output columns >= first_col leave through the Ulysses column scatter: every
+// 64-column chunk is written by the epilogue warps straight into the owning rank's receive
+// buffer (peer stores over NVLink), columns below first_col go to C as usual, and the last CTA
+// bumps the flag word on every rank.  dst_bases / flag_ptrs: n_ranks pointers each; counter: a
+// zeroed local u32.  Destination row stride dst_ld (elements); this rank's rows start at
+// row_offset in every destination.
+extern "C" int solar_gemm_bf16_scatter(const void* A, const void* B, void* C, const void* bias, int M, int N,
+                                       int K, long long lda, long long ldb, long long ldc, int layout, int act,
+                                       int* status, int max_ctas, void* stream, void* const* dst_bases,
+                                       void* const* flag_ptrs, unsigned* counter, int n_ranks, long long dst_ld,
+                                       int group_cols, int cols_per_dest, int row_offset, int first_col,
+                                       int col_base) {
+  if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("gemm scatter: rank count out of range%s");
+  if (cols_per_dest % 64 != 0 || group_cols % cols_per_dest != 0 || first_col % 64 != 0)
+    return fail("gemm scatter: column blocks must be multiples of 64%s");
+  ColScatter sc;
+  memset(&sc, 0, sizeof(sc));
+  sc.dst.n = n_ranks;
+  sc.flags.n = n_ranks;
+  for (int i = 0; i < n_ranks; ++i) {
+    sc.dst.base[i] = dst_bases[i];
+    sc.flags.flag[i] = static_cast<unsigned*>(flag_ptrs[i]);
+  }
+  sc.flags.local_counter = counter;
+  sc.ld = dst_ld;
+  sc.group_cols = group_cols;
+  sc.cols_per_dest = cols_per_dest;
+  sc.row_offset = row_offset;
+  sc.first_col = first_col;
+  sc.col_base = col_base;
+  return gemm_entry(A, B, C, bias, M, N, K, lda, ldb, ldc, layout, act, 0, 0, status, max_ctas, stream, sc);
 }
 
 extern "C" const char* solar_last_error() { return last_error_buf(); }

@@ -15,6 +15,7 @@
 // (solar/backends/wan22/runtime/modeling/causal_model.py:1636-1707), its Triton
 // rmsnorm_modulate / gated_residual kernels (solar/backends/minimax_h3/fused_ops.py:39-206)
 // and the fp64 complex rope_apply loop (solar/backends/wan22/runtime/modeling/model.py:38-66).
+#include "comm.cuh"
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -339,7 +340,8 @@ struct RmsRopeParams {
   int no_norm;                       // 1: rotation only
 };
 
-__global__ void __launch_bounds__(ROW_THREADS) rmsnorm_rope_fwd_kernel(RmsRopeParams p) {
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_rope_fwd_kernel(RmsRopeParams p, const __grid_constant__ ColScatter sc) {
   __shared__ float red[4];
   const long long row = blockIdx.x;
   const int nvec = p.D >> 3;
@@ -384,9 +386,13 @@ __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_rope_fwd_kernel(RmsRopePa
           o[2 * e + 1] = a * cs.y + b * cs.x;
         }
       }
-      store8(p.y + row * p.ldy + vi * 8, o);
+      if (sc.active())   // heads -> ranks: straight into the owning rank's receive buffer
+        store8(static_cast<__nv_bfloat16*>(sc.addr(row, vi * 8, 2)), o);
+      else
+        store8(p.y + row * p.ldy + vi * 8, o);
     }
   }
+  if (sc.active()) cta_done_signal_peers(sc.flags);
 }
 
 // Backward: dy is the gradient of the rotated output; writes dx (may alias dy).
@@ -580,7 +586,41 @@ extern "C" int solar_rmsnorm_rope_fwd(const void* x, long long ldx, void* y, lon
   if (rows <= 0) return 0;
   RmsRopeParams p{(const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)y, ldy, w, (const float2*)rope, half_hd,
                   rstd, D, eps, no_norm};
-  rmsnorm_rope_fwd_kernel<<<(unsigned)rows, ROW_THREADS, 0, (cudaStream_t)stream>>>(p);
+  ColScatter none;
+  memset(&none, 0, sizeof(none));
+  rmsnorm_rope_fwd_kernel<<<(unsigned)rows, ROW_THREADS, 0, (cudaStream_t)stream>>>(p, none);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Same operator with the Ulysses column scatter as its output stage: every 16-byte piece of the
+// normalised, rotated row is stored into the receive buffer of the rank that owns its head, and the
+// last CTA bumps the flag word on every rank.  `rstd` is still written locally for the backward.
+extern "C" int solar_rmsnorm_rope_scatter(const void* x, long long ldx, const float* w, const void* rope,
+                                          int half_hd, float* rstd, long long rows, int D, float eps,
+                                          int no_norm, void* stream, void* const* dst_bases,
+                                          void* const* flag_ptrs, unsigned* counter, int n_ranks,
+                                          long long dst_ld, int cols_per_dest, int row_offset, int col_base) {
+  if (check_D(D)) return -1;
+  if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("rmsnorm_rope scatter: rank count out of range%s");
+  if (cols_per_dest % 8 != 0 || D % cols_per_dest != 0) return fail("rmsnorm_rope scatter: bad column blocks%s");
+  if (rows <= 0) return fail("rmsnorm_rope scatter: every rank must launch at least one row%s");
+  RmsRopeParams p{(const __nv_bfloat16*)x, ldx, nullptr, 0, w, (const float2*)rope, half_hd, rstd, D, eps, no_norm};
+  ColScatter sc;
+  memset(&sc, 0, sizeof(sc));
+  sc.dst.n = n_ranks;
+  sc.flags.n = n_ranks;
+  for (int i = 0; i < n_ranks; ++i) {
+    sc.dst.base[i] = dst_bases[i];
+    sc.flags.flag[i] = static_cast<unsigned*>(flag_ptrs[i]);
+  }
+  sc.flags.local_counter = counter;
+  sc.ld = dst_ld;
+  sc.group_cols = D;
+  sc.cols_per_dest = cols_per_dest;
+  sc.row_offset = row_offset;
+  sc.col_base = col_base;
+  rmsnorm_rope_fwd_kernel<<<(unsigned)rows, ROW_THREADS, 0, (cudaStream_t)stream>>>(p, sc);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }
