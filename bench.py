@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--width", type=int, default=80)
     ap.add_argument("--checkpointing", default="auto", choices=["auto", "none", "full", "selective"])
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
+    ap.add_argument("--sp-transport", default="fused", choices=["fused", "nccl"],
+                    help="Ulysses exchange: fused into the kernels over NVLink peer memory, or NCCL all-to-all")
     return ap.parse_args()
 
 
@@ -152,9 +154,16 @@ def run_ours(args):
 
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
-        from solarwm_b200.parallel.ulysses import UlyssesCollective
+        if args.sp_transport == "fused":
+            from solarwm_b200.parallel.fused_ulysses import FusedUlysses
 
-        sp = UlyssesCollective(None)
+            mc = model_config(args)
+            sp = FusedUlysses(None, max_tokens=args.frames * (args.height // 2) * (args.width // 2), dim=mc.dim,
+                              num_heads=mc.num_heads)
+        else:
+            from solarwm_b200.parallel.ulysses import UlyssesCollective
+
+            sp = UlyssesCollective(None)
 
     from solarwm_b200 import ops
     from solarwm_b200.backends.wan22.stage0p5 import Stage0p5Options, WanStage0p5Trainer
@@ -208,7 +217,7 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic latents/text of the named shapes, random-init weights",
             "impl": "ours",
             "config": {"model": "wan22_ti2v_5b-shaped" if args.model == "ti2v_5b" else "small-debug",
-                       "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}",
+                       "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
                        "latent": [1, cfg.in_dim, args.frames, args.height, args.width],
                        "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt,
                        "attention_backend": ops.get_backend(), "optimizer": "AdamW fp32 master (in timed region)",
@@ -222,6 +231,8 @@ def run_ours(args):
         }
         print(json.dumps(out))
     if dist is not None:
+        if hasattr(sp, "close"):
+            sp.close()
         dist.destroy_process_group()
 
 

@@ -184,18 +184,13 @@ class WanBlock(nn.Module):
     def _linear(self, x, wname, bname):
         return F_.linear(x, self._p(wname), self._p(bname))
 
-    def _fused_linear(self, x, first, last, n_out):
-        """One GEMM over adjacent weight slots ``first..last`` (e.g. q|k|v)."""
+    def _fused_params(self, first, last, n_out):
+        """Views over the adjacent weight / bias slots ``first..last`` (e.g. q|k|v), wired to the flat
+        gradient buffers when gradients are on."""
         d_in = self.unit.slots[first + ".weight"].shape[1]
-        if not x.is_cuda or (torch.is_grad_enabled() and self.unit.grad is None):
-            names = {"q": ("q", "k", "v"), "k": ("k", "v")}[first.rsplit(".", 1)[1]]
-            pre = first.rsplit(".", 1)[0]
-            w = torch.cat([self._p(f"{pre}.{n}.weight") for n in names], 0)
-            b = torch.cat([self._p(f"{pre}.{n}.bias") for n in names], 0)
-            return F_.linear(x, w, b)
         w = self.unit.span(first + ".weight", last + ".weight", (n_out, d_in))
         b = self.unit.span(first + ".bias", last + ".bias", (n_out,))
-        if torch.is_grad_enabled():
+        if torch.is_grad_enabled() and self.unit.grad is not None:
             w.main_grad = self.unit.grad_span(first + ".weight", last + ".weight", (n_out, d_in))
             b.main_grad = self.unit.grad_span(first + ".bias", last + ".bias", (n_out,))
             names = {"q": ("q", "k", "v"), "k": ("k", "v")}[first.rsplit(".", 1)[1]]
@@ -204,6 +199,18 @@ class WanBlock(nn.Module):
             b._anchors = tuple(self._p(f"{pre}.{n}.bias") for n in names)
             w.requires_grad_(True)
             b.requires_grad_(True)
+        return w, b
+
+    def _fused_linear(self, x, first, last, n_out):
+        """One GEMM over adjacent weight slots ``first..last`` (e.g. q|k|v)."""
+        if not x.is_cuda or (torch.is_grad_enabled() and self.unit.grad is None):
+            names = {"q": ("q", "k", "v"), "k": ("k", "v")}[first.rsplit(".", 1)[1]]
+            pre = first.rsplit(".", 1)[0]
+            w = torch.cat([self._p(f"{pre}.{n}.weight") for n in names], 0)
+            b = torch.cat([self._p(f"{pre}.{n}.bias") for n in names], 0)
+            return F_.linear(x, w, b)
+        w, b = self._fused_params(first, last, n_out)
+        if torch.is_grad_enabled():
             return F_._LinearMainGradFn.apply(x, w, b)
         return F_.gemm(x, w, F_.NT, bias=b)
 
@@ -217,15 +224,28 @@ class WanBlock(nn.Module):
 
         # ---- self attention
         xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], mode=0, eps=cfg.eps, **gk)
-        qkv = self._fused_linear(xm, "self_attn.q", "self_attn.v", 3 * D)
-        q = F_.rmsnorm_rope(qkv[:, :D], self._p("self_attn.norm_q.weight").float(), rope, eps=cfg.eps)
-        k = F_.rmsnorm_rope(qkv[:, D:2 * D], self._p("self_attn.norm_k.weight").float(), rope, eps=cfg.eps)
-        v = qkv[:, 2 * D:]
         Ll = x.shape[0] // B
-        q, k, v = (t.reshape(B, Ll, H, hd) for t in (q, k, v))
-        q, k, v = sp.scatter_heads(q, k, v)
-        o = ops.attention(q, k, v, memo=None if memo is None else (memo, "self"))
-        o = sp.gather_heads(o).reshape(B * Ll, D)
+        fused_sp = bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
+            (not torch.is_grad_enabled() or self.unit.grad is not None)
+        if fused_sp:
+            # Ulysses exchanges ride on the producing kernels (parallel/fused_ulysses.py)
+            from ..parallel.fused_ulysses import FusedAttention, FusedQKV
+
+            parity = sp.next_parity()
+            w, b = self._fused_params("self_attn.q", "self_attn.v", 3 * D)
+            recv = FusedQKV.apply(xm, w, b, self._p("self_attn.norm_q.weight"), self._p("self_attn.norm_k.weight"),
+                                  rope, cfg.eps, sp, parity, None)
+            o = FusedAttention.apply(recv, 1.0 / math.sqrt(hd), sp, parity,
+                                     None if memo is None else (memo, "self"))
+        else:
+            qkv = self._fused_linear(xm, "self_attn.q", "self_attn.v", 3 * D)
+            q = F_.rmsnorm_rope(qkv[:, :D], self._p("self_attn.norm_q.weight").float(), rope, eps=cfg.eps)
+            k = F_.rmsnorm_rope(qkv[:, D:2 * D], self._p("self_attn.norm_k.weight").float(), rope, eps=cfg.eps)
+            v = qkv[:, 2 * D:]
+            q, k, v = (t.reshape(B, Ll, H, hd) for t in (q, k, v))
+            q, k, v = sp.scatter_heads(q, k, v)
+            o = ops.attention(q, k, v, memo=None if memo is None else (memo, "self"))
+            o = sp.gather_heads(o).reshape(B * Ll, D)
         y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
         x = F_.gated_residual(x, y, mod[:, 2], **gk)
 

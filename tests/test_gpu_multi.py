@@ -1,0 +1,116 @@
+"""Two-GPU checks (skipped with fewer devices): the fused NVLink Ulysses path against the NCCL
+collective path -- same forward output and the same parameter gradients -- and the peer-memory
+runtime's push/flag protocol including a bounded wait that is made to run out."""
+import os
+from datetime import timedelta
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_two():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+
+
+def _worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=timedelta(seconds=120),
+                            device_id=torch.device("cuda", rank))
+    from solarwm_b200 import ops
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+    from solarwm_b200.parallel.fused_ulysses import FusedUlysses
+    from solarwm_b200.parallel.symm import SymmetricHeap
+    from solarwm_b200.parallel.ulysses import UlyssesCollective
+
+    result = {}
+    # ---- runtime: push + flags, then a wait nobody satisfies (bounded, reports a status)
+    heap = SymmetricHeap(1 << 20, None)
+    buf, off = heap.alloc((world, 1024), torch.float32)
+    slot = heap.new_flag()
+    src = torch.full((1024,), float(rank + 1), device="cuda")
+    lib = heap.lib
+    import ctypes
+
+    rc = lib.solar_comm_push(ctypes.c_void_p(src.data_ptr()), heap.peer_ptr_array(off), ctypes.c_int(world),
+                             ctypes.c_longlong(rank * 4096), ctypes.c_longlong(4096), heap.flag_ptrs(slot),
+                             heap.counter_ptr(slot), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    heap.wait(slot, heap.expect(slot))
+    torch.cuda.synchronize()
+    result["push_ok"] = bool(all(torch.all(buf[r] == r + 1).item() for r in range(world)))
+    heap.wait(slot, heap.expect(slot), limit_seconds=0.3)       # no producer: must give up by itself
+    torch.cuda.synchronize()
+    try:
+        ops.check_status()
+        result["timeout_reported"] = False
+    except ops.NativeError as exc:
+        result["timeout_reported"] = "code 5" in str(exc)
+    dist.barrier()
+
+    # ---- fused vs collective Ulysses on a small DiT
+    cfg = WanConfig(model_type="t2v", in_dim=16, out_dim=16, dim=256, ffn_dim=512, num_heads=2, num_layers=2,
+                    text_dim=128, text_len=64, freq_dim=64)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 16, 5, 16, 16, generator=g).cuda()
+    ctx = torch.randn(1, 64, 128, generator=g).cuda()
+    t = torch.tensor([[50.0, 300.0, 500.0, 700.0, 950.0]]).cuda()
+    tgt = torch.randn(1, 16, 5, 16, 16, generator=g).cuda()
+    outs = {}
+    fused = FusedUlysses(None, max_tokens=5 * 64, dim=256, num_heads=2)
+    for name, sp in (("nccl", UlyssesCollective(None)), ("fused", fused)):
+        for mode in ("none", "selective"):
+            model = WanDiT(cfg, device="cuda", dtype=torch.bfloat16, seed=3)
+            with torch.no_grad():
+                model.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator(device="cuda").manual_seed(1))
+            model.sp = sp
+            model.checkpointing = mode
+            model.ensure_grads()
+            ops.reset_counters()
+            out = model(x, t, ctx)
+            ((out.float() - tgt) ** 2).mean().backward()
+            model.finalize_grads()
+            sp.sum_gradients_([gr for u in model.units() for gr in (u.grad, u.grad_v)])
+            torch.cuda.synchronize()
+            ops.check_status()
+            outs[(name, mode)] = (out.detach().float().cpu(),
+                                  {n: p.main_grad.float().cpu() for n, p in model.named_parameters()},
+                                  dict(ops.COUNTERS))
+    with torch.no_grad():
+        model.sp = fused
+        outs["fused_infer"] = model(x, t, ctx).float().cpu()
+    ref_out, ref_grads, _ = outs[("nccl", "none")]
+    worst = 0.0
+    for key in (("fused", "none"), ("fused", "selective"), ("nccl", "selective")):
+        o, gr, counters = outs[key]
+        result[f"out_{key[0]}_{key[1]}"] = ((o - ref_out).norm() / ref_out.norm()).item()
+        for n, r in ref_grads.items():
+            if r.norm() > 1e-6:
+                worst = max(worst, ((gr[n] - r).norm() / r.norm()).item())
+        if key[0] == "fused":
+            result[f"fused_kernels_{key[1]}"] = (counters.get("gemm_scatter", 0), counters.get("attn_fwd_scatter", 0))
+    result["worst_grad_rel"] = worst
+    result["infer_rel"] = ((outs["fused_infer"] - ref_out).norm() / ref_out.norm()).item()
+    torch.save(result, f"{out}.{rank}")
+    fused.close()
+    heap.close()
+    dist.destroy_process_group()
+
+
+def test_fused_ulysses_matches_collective_on_two_gpus(tmp_path):
+    _need_two()
+    import torch.multiprocessing as mp
+
+    out = str(tmp_path / "res")
+    mp.spawn(_worker, args=(2, 29541, out), nprocs=2, join=True)
+    for rank in range(2):
+        r = torch.load(f"{out}.{rank}", weights_only=True)
+        assert r["push_ok"] and r["timeout_reported"], r
+        assert r["out_fused_none"] < 2e-2 and r["out_fused_selective"] < 2e-2 and r["out_nccl_selective"] < 1e-6, r
+        assert r["infer_rel"] < 2e-2 and r["worst_grad_rel"] < 6e-2, r
+        assert r["fused_kernels_none"] == (2, 2) and r["fused_kernels_selective"] == (4, 2), r
