@@ -23,9 +23,10 @@ _scratch: dict[int, torch.Tensor] = {}
 
 def status_word(device) -> torch.Tensor:
     """Per-device int32 word that kernels with bounded waits set when a wait gave up."""
-    idx = torch.device(device).index or 0
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
     if idx not in _status:
-        _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
     return _status[idx]
 
 
@@ -39,9 +40,10 @@ def check_status(device="cuda") -> None:
 
 
 def _scratch_f32(device, n=2048) -> torch.Tensor:
-    idx = torch.device(device).index or 0
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
     if idx not in _scratch or _scratch[idx].numel() < n:
-        _scratch[idx] = torch.empty(n, dtype=torch.float32, device=device)
+        _scratch[idx] = torch.empty(n, dtype=torch.float32, device=torch.device("cuda", idx))
     return _scratch[idx]
 
 

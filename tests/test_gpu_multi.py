@@ -15,7 +15,7 @@ def _need_two():
         pytest.skip("needs two CUDA devices")
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out_path):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -46,8 +46,12 @@ def _worker(rank, world, port, out):
     result["push_ok"] = bool(all(torch.all(buf[r] == r + 1).item() for r in range(world)))
     heap.wait(slot, heap.expect(slot), limit_seconds=0.3)       # no producer: must give up by itself
     torch.cuda.synchronize()
+    from solarwm_b200.ops.functional import status_word
+
+    result["raw_status"] = int(status_word(heap.device).item())
+    result["raw_flag"] = int(heap._bytes[4 * slot:4 * slot + 4].view(torch.int32).item())
     try:
-        ops.check_status()
+        ops.check_status(heap.device)
         result["timeout_reported"] = False
     except ops.NativeError as exc:
         result["timeout_reported"] = "code 5" in str(exc)
@@ -96,7 +100,7 @@ def _worker(rank, world, port, out):
             result[f"fused_kernels_{key[1]}"] = (counters.get("gemm_scatter", 0), counters.get("attn_fwd_scatter", 0))
     result["worst_grad_rel"] = worst
     result["infer_rel"] = ((outs["fused_infer"] - ref_out).norm() / ref_out.norm()).item()
-    torch.save(result, f"{out}.{rank}")
+    torch.save(result, f"{out_path}.{rank}")
     fused.close()
     heap.close()
     dist.destroy_process_group()
