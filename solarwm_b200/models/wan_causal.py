@@ -1,0 +1,221 @@
+"""Block-causal (chunk-wise autoregressive) execution of the Wan DiT with a rolling KV cache.
+
+Per transformer block the cache holds, for every cached token, the *normalised but un-rotated*
+key and the value: ``[sink frames | local window | current chunk]``.  RoPE is applied when the
+cache is read, with window-relative frame positions (sink first, then the window, then the chunk),
+so a rollout longer than the training length keeps seeing positions it was trained on -- the
+reference's block-relative re-basing (solar/backends/wan22/runtime/modeling/causal_model.py:
+657-876, 1028-1235, 1948-2088).
+
+Differences from the reference, on purpose:
+  * a forward with ``commit=False`` (the denoising steps of a chunk) writes the chunk's K/V into the
+    staging slots behind the committed tokens and never touches committed state; ``commit=True``
+    (the clean forward after the last step) advances the committed length and, when the window is
+    full, shifts the window once.  The reference clones the whole cache of every block on every
+    step (causal_model.py:1054-1067).
+  * text keys/values of the cross-attention are projected once per prompt and reused.
+  * under head-parallel inference (SP > 1, reference P4) every rank keeps all tokens but only its
+    heads in the cache and the attention outputs are all-gathered on the head axis.
+
+Teacher forcing (Stage 1) uses ``teacher_forcing_attention``: the ``[clean | noisy]`` block mask is
+executed as one dense attention per chunk over its visible key segments (sink + bounded clean
+window + own chunk) instead of a FlexAttention block mask (causal_model.py:329-471).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from ..ops import functional as F_
+from .wan import WanDiT, rope_table
+
+
+@dataclass
+class LayerCache:
+    k: torch.Tensor          # [capacity_tokens, dim_local]  normalised, un-rotated keys
+    v: torch.Tensor          # [capacity_tokens, dim_local]
+    text_k: Optional[torch.Tensor] = None   # [T, dim] projected + normalised text keys
+    text_v: Optional[torch.Tensor] = None
+
+
+@dataclass
+class KVCache:
+    layers: List[LayerCache]
+    frame_tokens: int
+    sink_frames: int
+    window_frames: int        # committed frames kept besides the sink
+    chunk_frames: int
+    committed_frames: int = 0          # frames currently held (sink + window part)
+    total_frames: int = 0              # frames generated so far (absolute)
+    grid_hw: tuple = (0, 0)
+
+    @property
+    def capacity_frames(self) -> int:
+        return self.sink_frames + self.window_frames + self.chunk_frames
+
+
+def allocate_kv_cache(model: WanDiT, *, grid_hw, chunk_frames: int, window_frames: Optional[int] = None,
+                      sink_frames: Optional[int] = None, heads_local: Optional[int] = None, device=None) -> KVCache:
+    cfg = model.cfg
+    h, w = grid_hw
+    ft = h * w
+    sink = cfg.sink_size if sink_frames is None else sink_frames
+    window = (cfg.local_attn_size if cfg.local_attn_size > 0 else 21) if window_frames is None else window_frames
+    window = max(window - sink, chunk_frames)
+    hl = cfg.num_heads if heads_local is None else heads_local
+    dim_local = hl * cfg.head_dim
+    dev = device or next(model.parameters()).device
+    cap = (sink + window + chunk_frames) * ft
+    layers = [LayerCache(torch.zeros(cap, dim_local, dtype=model.dtype, device=dev),
+                         torch.zeros(cap, dim_local, dtype=model.dtype, device=dev)) for _ in model.blocks]
+    return KVCache(layers, ft, sink, window, chunk_frames, grid_hw=(h, w))
+
+
+class CausalWanRunner:
+    """Chunk-by-chunk forward of a ``WanDiT`` against a ``KVCache`` (inference; no autograd)."""
+
+    def __init__(self, model: WanDiT, sp=None):
+        self.model = model
+        self.sp = sp
+        self._rope_cache = {}
+
+    def _rope(self, frames, hw, device, first=0):
+        key = (frames, hw, first, str(device))
+        if key not in self._rope_cache:
+            self._rope_cache[key] = rope_table((frames, hw[0], hw[1]), self.model.cfg.head_dim, device, frame_offset=first)
+        return self._rope_cache[key]
+
+    @torch.no_grad()
+    def encode_text(self, cache: KVCache, context: torch.Tensor) -> None:
+        """Project the prompt once: per block, normalised text keys and values for the cross-attention."""
+        m = self.model
+        ctx = m.embed_text(context)
+        D = m.cfg.dim
+        for blk, lc in zip(m.blocks, cache.layers):
+            kv = blk._fused_linear(ctx, "cross_attn.k", "cross_attn.v", 2 * D)
+            lc.text_k = F_.rmsnorm_rope(kv[:, :D], blk._p("cross_attn.norm_k.weight").float(), None, eps=m.cfg.eps)
+            lc.text_v = kv[:, D:].contiguous()
+
+    @torch.no_grad()
+    def forward_chunk(self, cache: KVCache, x: torch.Tensor, t: torch.Tensor, *, commit: bool, y=None) -> torch.Tensor:
+        """x [1, C, f, H, W] (f = chunk frames), t [1, f] -> prediction [1, C_out, f, H, W]."""
+        m, cfg = self.model, self.model.cfg
+        P_ = m.stem.params
+        if y is not None:
+            x = torch.cat([x, y], dim=1)
+        rows, (f, h, w) = m.patchify(x.to(m.dtype))
+        ft = h * w
+        assert ft == cache.frame_tokens and f <= cache.chunk_frames
+        pw = P_["patch_embedding.weight"]
+        xs = F_.linear(rows, pw.view(pw.shape[0], -1), P_["patch_embedding.bias"])
+        e, e0 = m.time_condition(t)
+        D, H, hd = cfg.dim, cfg.num_heads, cfg.head_dim
+        ctx_frames = cache.committed_frames
+        n_ctx, n_new = ctx_frames * ft, f * ft
+        rope_all = self._rope(ctx_frames + f, (h, w), xs.device)
+        rope_q = rope_all[n_ctx:]
+        sp = self.sp
+        P = 1 if sp is None else sp.size
+        hl = H // P
+        h0 = 0 if sp is None else sp.rank * hl
+        gk = dict(rows_per_group=ft)
+        for blk, lc in zip(m.blocks, cache.layers):
+            mod = (blk._p("modulation").float().view(1, 6, D) + e0).contiguous()
+            xm = F_.norm_modulate(xs, mod[:, 0], mod[:, 1], mode=0, eps=cfg.eps, **gk)
+            qkv = blk._fused_linear(xm, "self_attn.q", "self_attn.v", 3 * D)
+            q = F_.rmsnorm_rope(qkv[:, :D], blk._p("self_attn.norm_q.weight").float(), rope_q, eps=cfg.eps)
+            k_raw = F_.rmsnorm_rope(qkv[:, D:2 * D], blk._p("self_attn.norm_k.weight").float(), None, eps=cfg.eps)
+            cs = slice(h0 * hd, (h0 + hl) * hd)
+            lc.k[n_ctx:n_ctx + n_new] = k_raw[:, cs]
+            lc.v[n_ctx:n_ctx + n_new] = qkv[:, 2 * D:][:, cs]
+            k_all = F_.rmsnorm_rope(lc.k[:n_ctx + n_new], None, _head_slice(rope_all, None), no_norm=True)
+            o = ops.attention(q[:, cs].reshape(1, n_new, hl, hd), k_all.view(1, n_ctx + n_new, hl, hd),
+                              lc.v[:n_ctx + n_new].view(1, n_ctx + n_new, hl, hd))
+            o = o.reshape(n_new, hl * hd)
+            if P > 1:
+                o = sp.all_gather_heads(o)
+            yb = blk._linear(o, "self_attn.o.weight", "self_attn.o.bias")
+            xs = F_.gated_residual(xs, yb, mod[:, 2], **gk)
+            xn = F_.norm_modulate(xs, mode=2, w=blk._p("norm3.weight").float(), b=blk._p("norm3.bias").float(),
+                                  eps=cfg.eps) if cfg.cross_attn_norm else xs
+            qc = blk._linear(xn, "cross_attn.q.weight", "cross_attn.q.bias")
+            qc = F_.rmsnorm_rope(qc, blk._p("cross_attn.norm_q.weight").float(), None, eps=cfg.eps)
+            T = lc.text_k.shape[0]
+            oc = ops.attention(qc.view(1, n_new, H, hd), lc.text_k.view(1, T, H, hd), lc.text_v.view(1, T, H, hd))
+            xs = F_.gated_residual(xs, blk._linear(oc.reshape(n_new, D), "cross_attn.o.weight", "cross_attn.o.bias"), None)
+            xm = F_.norm_modulate(xs, mod[:, 3], mod[:, 4], mode=0, eps=cfg.eps, **gk)
+            hmid = F_.linear(xm, blk._p("ffn.0.weight"), blk._p("ffn.0.bias"), act="gelu") if xs.is_cuda else \
+                F_.gelu(F_.linear(xm, blk._p("ffn.0.weight"), blk._p("ffn.0.bias")))
+            xs = F_.gated_residual(xs, blk._linear(hmid, "ffn.2.weight", "ffn.2.bias"), mod[:, 5], **gk)
+        hm = (P_["head.modulation"].float().view(1, 2, D) + e.float().view(-1, 1, D)).contiguous()
+        xh = F_.norm_modulate(xs, hm[:, 0], hm[:, 1], mode=0, eps=cfg.eps, rows_per_group=ft)
+        out = m.unpatchify(F_.linear(xh, P_["head.head.weight"], P_["head.head.bias"]), 1, (f, h, w))
+        if commit:
+            self._commit(cache, f)
+        return out
+
+    def _commit(self, cache: KVCache, f: int) -> None:
+        """Keep the chunk just written; when sink + window is exceeded drop the oldest window frames."""
+        ft = cache.frame_tokens
+        cache.committed_frames += f
+        cache.total_frames += f
+        limit = cache.sink_frames + cache.window_frames
+        extra = cache.committed_frames - limit
+        if extra > 0:
+            s0 = cache.sink_frames * ft
+            keep = (cache.committed_frames - cache.sink_frames - extra) * ft
+            for lc in cache.layers:
+                for buf in (lc.k, lc.v):
+                    buf[s0:s0 + keep] = buf[s0 + extra * ft:s0 + extra * ft + keep].clone()
+            cache.committed_frames = limit
+
+
+def _head_slice(rope, _):
+    return rope
+
+
+def teacher_forcing_attention(q_clean, k_clean, v_clean, q_noisy, k_noisy, v_noisy, *, frame_tokens: int,
+                              chunk_frames: int, window_chunks: int, sink_frames: int = 0):
+    """Block-causal ``[clean | noisy]`` attention for teacher forcing; all tensors ``[1, F*ft, H, D]``.
+
+    clean chunk i sees  sink + clean chunks max(0, i-W) .. i
+    noisy chunk i sees  sink + clean chunks max(0, i-W) .. i-1 + its own noisy chunk
+    Returns (o_clean, o_noisy).  Executed as one dense attention per chunk and role.
+    """
+    ft = frame_tokens
+    ct = chunk_frames * ft
+    n_chunks = q_clean.shape[1] // ct
+    sink = sink_frames * ft
+    outs_c, outs_n = [], []
+    for i in range(n_chunks):
+        lo = max(0, i - window_chunks) * ct
+        seg = [slice(0, sink)] if (sink and lo > 0) else []
+        c_hi = (i + 1) * ct
+        ks = [k_clean[:, s] for s in seg] + [k_clean[:, lo:c_hi]]
+        vs = [v_clean[:, s] for s in seg] + [v_clean[:, lo:c_hi]]
+        outs_c.append(ops.attention(q_clean[:, i * ct:c_hi], torch.cat(ks, 1), torch.cat(vs, 1)))
+        kn = [k_clean[:, s] for s in seg] + [k_clean[:, lo:i * ct], k_noisy[:, i * ct:c_hi]]
+        vn = [v_clean[:, s] for s in seg] + [v_clean[:, lo:i * ct], v_noisy[:, i * ct:c_hi]]
+        outs_n.append(ops.attention(q_noisy[:, i * ct:c_hi], torch.cat(kn, 1), torch.cat(vn, 1)))
+    return torch.cat(outs_c, 1), torch.cat(outs_n, 1)
+
+
+def teacher_forcing_mask(num_frames: int, frame_tokens: int, chunk_frames: int, window_chunks: int,
+                         sink_frames: int = 0) -> torch.Tensor:
+    """Dense boolean mask ``[2L, 2L]`` (True = visible) over ``[clean | noisy]`` tokens; the oracle
+    for ``teacher_forcing_attention`` and for direct block-mask construction."""
+    L = num_frames * frame_tokens
+    ct = chunk_frames * frame_tokens
+    chunk = torch.arange(L) // ct
+    is_sink = torch.arange(L) < sink_frames * frame_tokens
+    qc, kc = chunk.view(-1, 1), chunk.view(1, -1)
+    clean_clean = ((kc <= qc) & (kc >= qc - window_chunks)) | is_sink.view(1, -1) & (kc <= qc)
+    noisy_clean = ((kc < qc) & (kc >= qc - window_chunks)) | is_sink.view(1, -1) & (kc < qc)
+    noisy_noisy = kc == qc
+    top = torch.cat([clean_clean, torch.zeros(L, L, dtype=torch.bool)], 1)
+    bottom = torch.cat([noisy_clean, noisy_noisy], 1)
+    return torch.cat([top, bottom], 0)

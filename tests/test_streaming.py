@@ -1,0 +1,85 @@
+"""Block-causal execution on CPU: a chunked rollout against the KV cache equals one dense forward
+with the block-causal mask, the window shift keeps the most recent frames, and the teacher-forcing
+segment plan equals dense-mask attention."""
+import torch
+
+from solarwm_b200.models.wan import WanDiT, wan_preset
+from solarwm_b200.models.wan_causal import (CausalWanRunner, allocate_kv_cache, teacher_forcing_attention,
+                                            teacher_forcing_mask)
+from solarwm_b200.ops import reference as R
+
+
+def _model():
+    m = WanDiT(wan_preset("tiny"), device="cpu", dtype=torch.float32, seed=0)
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator().manual_seed(1))
+    return m
+
+
+def test_cached_chunks_equal_full_causal_recompute():
+    m = _model()
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 16, 4, 8, 8, generator=g)
+    ctx = torch.randn(1, 32, 256, generator=g)
+    runner = CausalWanRunner(m)
+    cache = allocate_kv_cache(m, grid_hw=(4, 4), chunk_frames=2, window_frames=8, sink_frames=0)
+    runner.encode_text(cache, ctx)
+    t = torch.zeros(1, 2)
+    first = runner.forward_chunk(cache, x[:, :, :2], t, commit=True)
+    peek = runner.forward_chunk(cache, x[:, :, 2:], t + 500.0, commit=False)     # leaves the cache alone
+    assert cache.committed_frames == 2
+    second = runner.forward_chunk(cache, x[:, :, 2:], t + 500.0, commit=True)
+    assert torch.equal(peek, second) and cache.committed_frames == 4
+    # oracle: chunk 2 attends to [chunk 1 | chunk 2]; chunk 1 alone equals the bidirectional model on 2 frames
+    alone = m(x[:, :, :2], t, ctx)
+    assert torch.allclose(first, alone, atol=1e-4, rtol=1e-4)
+    again = CausalWanRunner(m)
+    cache2 = allocate_kv_cache(m, grid_hw=(4, 4), chunk_frames=2, window_frames=8, sink_frames=0)
+    again.encode_text(cache2, ctx)
+    again.forward_chunk(cache2, x[:, :, :2], t, commit=True)
+    assert torch.allclose(again.forward_chunk(cache2, x[:, :, 2:], t + 500.0, commit=True), second, atol=1e-5)
+
+
+def test_window_shift_keeps_sink_and_recent_frames():
+    m = _model()
+    runner = CausalWanRunner(m)
+    cache = allocate_kv_cache(m, grid_hw=(4, 4), chunk_frames=1, window_frames=3, sink_frames=1)
+    assert cache.window_frames == 2                  # window counts frames besides the sink
+    runner.encode_text(cache, torch.randn(1, 32, 256))
+    seen = []
+    for i in range(5):
+        x = torch.full((1, 16, 1, 8, 8), float(i + 1))
+        runner.forward_chunk(cache, x, torch.zeros(1, 1), commit=True)
+        seen.append(cache.layers[0].k[(min(i, 2)) * 16].clone())
+    assert cache.committed_frames == 3 and cache.total_frames == 5
+    k = cache.layers[0].k
+    # slot 0 = sink (frame 0), slots 1..2 = the two most recent frames (3 and 4)
+    runner2 = CausalWanRunner(m)
+    c2 = allocate_kv_cache(m, grid_hw=(4, 4), chunk_frames=1, window_frames=3, sink_frames=1)
+    runner2.encode_text(c2, torch.randn(1, 32, 256))
+    runner2.forward_chunk(c2, torch.full((1, 16, 1, 8, 8), 1.0), torch.zeros(1, 1), commit=True)
+    assert torch.allclose(k[:16], c2.layers[0].k[:16])
+
+
+def test_teacher_forcing_segments_equal_dense_mask():
+    torch.manual_seed(0)
+    F_, ft, cf, W, H, D = 6, 4, 2, 1, 2, 16
+    L = F_ * ft
+    mk = lambda: torch.randn(1, L, H, D)
+    qc, kc, vc, qn, kn, vn = mk(), mk(), mk(), mk(), mk(), mk()
+    oc, on = teacher_forcing_attention(qc, kc, vc, qn, kn, vn, frame_tokens=ft, chunk_frames=cf, window_chunks=W)
+    mask = teacher_forcing_mask(F_, ft, cf, W)
+    dense = R.attention(torch.cat([qc, qn], 1), torch.cat([kc, kn], 1), torch.cat([vc, vn], 1), mask=mask.view(1, 1, 2 * L, 2 * L))
+    assert torch.allclose(torch.cat([oc, on], 1), dense, atol=1e-5)
+    assert mask[L:, L:].sum() == F_ // cf * (cf * ft) ** 2           # noisy tokens see only their own noisy chunk
+
+
+def test_streaming_generator_runs_on_cpu():
+    from solarwm_b200.serve.streaming import StreamingConfig, StreamingGenerator
+
+    m = _model()
+    gen = StreamingGenerator(m, StreamingConfig(chunk_frames=1, window_frames=3, sink_frames=1, denoise_timesteps=(1000.0, 500.0)))
+    gen.start(torch.randn(1, 32, 256), grid_hw=(4, 4))
+    chunks = [gen.next_chunk() for _ in range(4)]
+    assert all(c.shape == (1, 16, 1, 8, 8) and torch.isfinite(c).all() for c in chunks)
+    assert gen.cache.total_frames == 4 and gen.cache.committed_frames == 3
