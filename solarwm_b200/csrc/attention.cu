@@ -124,6 +124,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (warp == 0) {
     // -------------------------------------------------------------- TMA producer
+    setmaxnreg_dec<72>();
     if (lane == 0) {
       mbar_expect_tx(q_full, 2 * L::TILE_BYTES);
 #pragma unroll
@@ -151,6 +152,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
+    setmaxnreg_dec<72>();
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, KT, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, HD, 0, 1);
@@ -212,8 +214,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    setmaxnreg_dec<72>();                       // idle warps of the producer warpgroup release registers too
+  } else {
     // -------------------------------------------------------------- softmax (2 x 4 warps)
+    setmaxnreg_inc<208>();
     const int t = (warp - 4) >> 2;              // Q tile of this warpgroup
     const int quarter = warp & 3;               // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;        // row inside the Q tile
@@ -227,22 +232,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(&s_ready[t], j & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int kv_valid = p.Sk - j * KT;       // >= 128 except on the last tile
-      // pass 1: row maximum of the raw scores
-      float mx = -INFINITY;
+      // the whole 128-score row of this thread in registers: four loads in flight, one wait
+      uint32_t s[128];
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + cc * 32, r);
-        tmem_ld_wait();
-        if (kv_valid < KT) {
+      for (int cc = 0; cc < 4; ++cc) tmem_ld_32x32_at(tS + cc * 32, s + cc * 32);
+      tmem_ld_wait();
+      if (kv_valid < KT) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (cc * 32 + e < kv_valid) mx = fmaxf(mx, __uint_as_float(r[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-        }
+        for (int e = 0; e < 128; ++e)
+          if (e >= kv_valid) s[e] = __float_as_uint(-INFINITY);
       }
+      float mx = fmaxf(__uint_as_float(s[0]), __uint_as_float(s[1]));
+#pragma unroll
+      for (int e = 2; e < 128; e += 2) mx = max3f(mx, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
       if (j == 0) {
         m_used = mx;
       } else {
@@ -267,27 +269,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st_wait();
         }
       }
-      // pass 2: P = exp2(s * c - m * c), packed to bf16 over the first 64 columns of S_t
-      const float neg_mc = -m_used * c;
+      // P = exp2(s * c - m * c) with packed fp32x2 arithmetic, bf16 pairs over the first 64 columns of S_t
+      const float2 c2 = make_float2(c, c);
+      const float2 n2 = make_float2(-m_used * c, -m_used * c);
+      float2 l2 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + cc * 32, r);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float a = exp2_fast(fmaf(__uint_as_float(r[2 * e]), c, neg_mc));
-          float b = exp2_fast(fmaf(__uint_as_float(r[2 * e + 1]), c, neg_mc));
-          if (kv_valid < KT) {
-            if (cc * 32 + 2 * e >= kv_valid) a = 0.f;
-            if (cc * 32 + 2 * e + 1 >= kv_valid) b = 0.f;
-          }
-          l += a + b;
-          pk[e] = pack_bf16x2(a, b);
-        }
-        tmem_st_32x16(tS + cc * 16, pk);
+      for (int e = 0; e < 64; ++e) {
+        const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, n2);
+        const float2 pp = make_float2(exp2_fast(tt.x), exp2_fast(tt.y));
+        l2 = __fadd2_rn(l2, pp);
+        s[e] = pack_bf16x2(pp.x, pp.y);
       }
+      l += l2.x + l2.y;
+      tmem_st_32x32_at(tS, s);
+      tmem_st_32x32_at(tS + 32, s + 32);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[t]);

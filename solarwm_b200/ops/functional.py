@@ -651,3 +651,55 @@ def rgb8(frame_chw, mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225)):
     if not ok:
         raise FloatingPointError("nonfinite RGB pixel")
     return out, None
+
+
+# --------------------------------------------------------------------------------------
+# per-head RMSNorm + MM-RoPE + PRoPE (H3 attention path)
+# --------------------------------------------------------------------------------------
+class _HeadOpFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, cos, sin, mats, heads, rot_dims, sections, eps):
+        x = _rowmajor(x)
+        S = x.shape[0]
+        y = torch.empty((S, x.shape[1]), dtype=x.dtype, device=x.device)
+        rstd = torch.empty((S, heads), dtype=torch.float32, device=x.device) if w is not None else None
+        lib = _lib.load()
+        rc = lib.solar_headop(ptr(x), c_ll(x.stride(0)), ptr(y), c_ll(y.stride(0)), ptr(w), ptr(cos), ptr(sin), ptr(mats),
+                              ptr(rstd), c_ll(S), c_int(heads), c_int(128), c_int(rot_dims), c_int(sections), c_float(eps),
+                              c_int(0), stream_handle())
+        check(rc, "solar_headop")
+        count("headop_fwd")
+        ctx.save_for_backward(x, w, cos, sin, mats, rstd)
+        ctx.cfg = (heads, rot_dims, sections, eps)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, cos, sin, mats, rstd = ctx.saved_tensors
+        heads, rot_dims, sections, eps = ctx.cfg
+        dy = _rowmajor(dy)
+        S = x.shape[0]
+        g = torch.empty_like(x)
+        lib = _lib.load()
+        rc = lib.solar_headop(ptr(dy), c_ll(dy.stride(0)), ptr(g), c_ll(g.stride(0)), ptr(None), ptr(cos), ptr(sin), ptr(mats),
+                              ptr(None), c_ll(S), c_int(heads), c_int(128), c_int(rot_dims), c_int(sections), c_float(eps),
+                              c_int(1), stream_handle())
+        check(rc, "solar_headop")
+        count("headop_bwd")
+        if w is not None:
+            dx = torch.empty_like(x)
+            rc = lib.solar_headnorm_bwd(ptr(g), c_ll(g.stride(0)), ptr(x), c_ll(x.stride(0)), ptr(dx), c_ll(dx.stride(0)),
+                                        ptr(w), ptr(rstd), c_ll(S), c_int(heads), stream_handle())
+            check(rc, "solar_headnorm_bwd")
+            count("headnorm_bwd")
+            g = dx
+        return g, None, None, None, None, None, None, None, None
+
+
+def head_norm_rope_prope(x, w=None, cos=None, sin=None, mats=None, *, heads, rot_dims=96, sections=2, eps=1e-6):
+    """y = PRoPE(MM-RoPE(RMSNorm_head(x) * w)) for head_dim 128 (weights are frozen: only dx is produced)."""
+    if not x.is_cuda:
+        return reference.head_norm_rope_prope(x, w, cos, sin, mats, heads=heads, rot_dims=rot_dims, sections=sections, eps=eps)
+    for t in (w, cos, sin, mats):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    return _HeadOpFn.apply(x, w, cos, sin, mats, int(heads), int(rot_dims), int(sections), float(eps))

@@ -120,3 +120,27 @@ def weighted_masked_mse(pred, target, weight=None, mask=None):
     per = diff.pow(2) * wt.view(shape)
     denom = mk.sum().clamp_min(1.0) * (p.numel() // G)
     return per.sum() / denom
+
+
+def head_norm_rope_prope(x, w, cos, sin, mats, *, heads: int, rot_dims: int = 96, sections: int = 2, eps: float = 1e-6):
+    """Per-head RMSNorm * w, rotate-half RoPE inside each of ``sections`` blocks of the first
+    ``rot_dims`` channels, then a 4x4 matrix on every 4-vector of the remaining channels.
+    x [S, heads*128]; cos/sin [S, rot_dims]; mats [S, 4, 4]; any of w / cos / mats may be None."""
+    S = x.shape[0]
+    v = x.float().view(S, heads, -1)
+    hd = v.shape[-1]
+    if w is not None:
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    if cos is not None:
+        sec = rot_dims // sections
+        rot = v[..., :rot_dims].reshape(S, heads, sections, sec)
+        a, b = rot[..., :sec // 2], rot[..., sec // 2:]
+        half = torch.cat([-b, a], dim=-1)
+        c = cos.float().view(S, 1, sections, sec)
+        s_ = sin.float().view(S, 1, sections, sec)
+        v = torch.cat([(rot * c + half * s_).reshape(S, heads, rot_dims), v[..., rot_dims:]], dim=-1)
+    if mats is not None:
+        cam = v[..., rot_dims:].reshape(S, heads, (hd - rot_dims) // 4, 4)
+        cam = torch.einsum("sij,shnj->shni", mats.float().view(S, 4, 4), cam)
+        v = torch.cat([v[..., :rot_dims], cam.reshape(S, heads, hd - rot_dims)], dim=-1)
+    return v.reshape(S, heads * hd).to(x.dtype)
