@@ -1,0 +1,141 @@
+"""LTX backend boundary: Stage0.5 rectified-flow training (full parameters or with SP), 8-step
+inference (reference: LTX25Backend, solar/backends/ltx25/backend.py:165-487)."""
+from __future__ import annotations
+
+import io
+import json
+from typing import Any, Mapping
+
+import torch
+
+from ... import ops
+from ...config.routes import validate_route
+from ...engine.inference_engine import GeneratedSample, InferenceCase, InferenceEngine
+from ...engine.optim import FlatAdamW
+from ...errors import BackendContractError, ConfigurationError
+from ...models.ltx import LTXDiT, ltx_preset
+from ...runtime.output_layout import output_root
+from .flow import masked_flow_loss, noisy_input_and_target, sample_sigmas
+
+
+def _arch(config):
+    arch = config["model"].get("architecture", "ltx_video_2b")
+    return ltx_preset(arch) if isinstance(arch, str) else ltx_preset("tiny")
+
+
+class LTXTrainer:
+    """One rectified-flow step: sigma sampling, clean first frame, DiT, masked loss, fused AdamW."""
+
+    def __init__(self, cfg, device, lr=1e-4, seed=0, sp=None, checkpointing="none"):
+        dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
+        self.model = LTXDiT(cfg, device=device, dtype=dtype, seed=seed)
+        with torch.no_grad():
+            self.model.get_parameter("head.head.weight").normal_(0, 0.02)
+        if sp is not None:
+            self.model.sp = sp
+        self.sp = sp
+        self.model.checkpointing = checkpointing
+        self.model.ensure_grads()
+        self.opt = FlatAdamW(self.model.units(), lr=lr)
+        self.device = torch.device(device)
+        self.gen = torch.Generator(device=self.device).manual_seed(seed * 100003)
+
+    def train_step(self, latents, text):
+        """latents [B, C, F, H, W], text [B, T, text_dim]"""
+        lat = latents.to(self.device, non_blocking=True).to(self.model.dtype)
+        txt = text.to(self.device, non_blocking=True)
+        B, C, F, H, W = lat.shape
+        sigma = sample_sigmas(B, F * H * W, generator=self.gen, device=self.device)
+        noise = torch.randn(lat.shape, generator=self.gen, device=self.device, dtype=torch.float32).to(lat.dtype)
+        if self.sp is not None and self.sp.size > 1:
+            self.sp.broadcast_(sigma, noise)
+        x_t, target, per_frame = noisy_input_and_target(lat, noise, sigma)
+        pred = self.model(x_t, per_frame * 1000.0, txt)
+        loss = masked_flow_loss(pred, target)
+        (loss / (1 if self.sp is None else self.sp.size)).backward()
+        self.model.finalize_grads()
+        if self.sp is not None and self.sp.size > 1:
+            self.sp.sum_gradients_([g for u in self.model.units() for g in (u.grad, u.grad_v)])
+        norm = self.opt.local_grad_sumsq().sqrt()
+        self.opt.set_clip(norm, 1.0)
+        self.opt.step()
+        self.model.zero_grads()
+        return loss.detach()
+
+
+@torch.no_grad()
+def sample(model, text, *, frames, height, width, steps=8, seed=0, first_frame=None):
+    """Euler sampler on the linear sigma grid 1 -> 0 (one-stage LTX sampler)."""
+    dev = next(model.parameters()).device
+    g = torch.Generator(device=dev).manual_seed(int(seed))
+    x = torch.randn(1, model.cfg.out_dim, frames, height, width, generator=g, device=dev).to(model.dtype)
+    sig = torch.linspace(1.0, 0.0, steps + 1, device=dev)
+    for i in range(steps):
+        t = sig[i].expand(1, frames).clone()
+        if first_frame is not None:
+            x[:, :, 0] = first_frame
+            t[:, 0] = 0.0
+        v = model(x, t * 1000.0, text)
+        x = (x.float() + (sig[i + 1] - sig[i]) * v.float()).to(x.dtype)
+    if first_frame is not None:
+        x[:, :, 0] = first_frame
+    return x
+
+
+class _Adapter:
+    family = "ltx25_video"
+
+    def __init__(self, model, config):
+        self.model, self.config = model, config
+
+    def generate(self, case: InferenceCase, *, weights_id: str) -> GeneratedSample:
+        inf = self.config.get("inference", {}) or {}
+        cfg = self.model.cfg
+        dev = next(self.model.parameters()).device
+        g = torch.Generator().manual_seed(case.noise_seed)
+        text = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(dev, self.model.dtype)
+        lat = sample(self.model, text, frames=int(inf.get("latent_frames", 4)), height=int(inf.get("latent_height", 8)),
+                     width=int(inf.get("latent_width", 8)), steps=int(inf.get("steps", 8)), seed=case.noise_seed)
+        buf = io.BytesIO()
+        torch.save(lat.float().cpu(), buf)
+        return GeneratedSample({"latents.pt": buf.getvalue()}, tuple(lat.shape), "bfloat16",
+                               provenance={"sampler": "euler", "steps": int(inf.get("steps", 8))})
+
+
+class LTX25Backend:
+    def __init__(self, family: str):
+        if family != "ltx25_video":
+            raise BackendContractError(f"not the LTX family: {family!r}")
+        self.family = family
+
+    def validate_config(self, config: Mapping[str, Any]) -> None:
+        if not config.get("runtime", {}).get("output_dir"):
+            raise ConfigurationError("runtime.output_dir is required")
+        sp = int((config.get("distributed", {}) or {}).get("sequence_parallel_size", 1))
+        if _arch(config).num_heads % sp:
+            raise ConfigurationError("sequence_parallel_size must divide the head count")
+
+    def train(self, config):
+        validate_route(config)
+        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
+        cfg = _arch(config)
+        tr = LTXTrainer(cfg, dev, lr=float(config["train"].get("optimizer", {}).get("lr", 1e-4)),
+                        seed=int(config["data"].get("seed", 0)))
+        data = config["data"]
+        g = torch.Generator().manual_seed(int(data.get("seed", 0)))
+        shape = (1, cfg.in_dim, int(data.get("latent_frames", 4)), int(data.get("latent_height", 8)), int(data.get("latent_width", 8)))
+        losses = []
+        for _ in range(int(config["train"]["max_steps"])):
+            lat = torch.randn(shape, generator=g)
+            losses.append(float(tr.train_step(lat, torch.randn(1, cfg.text_len, cfg.text_dim, generator=g)).item()))
+        return {"final_step": len(losses), "last_loss": losses[-1], "native_launches": ops.total_launches()}
+
+    def infer(self, config):
+        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
+        model = LTXDiT(_arch(config), device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32)
+        cases = [InferenceCase(i, f"case-{i}", "synthetic", 0, 1000 + i, "none") for i in range(int(config.get("inference", {}).get("cases", 1)))]
+        s = InferenceEngine(_Adapter(model, config)).run(cases, weights_id="init:random", output_dir=output_root(config) / "generate")
+        return {"output_dir": str(s.output_dir), "cases": s.cases}
+
+    def preencode(self, config):
+        raise BackendContractError("LTX preencoding needs the official codec weights, which are not available offline")

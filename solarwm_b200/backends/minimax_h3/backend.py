@@ -1,0 +1,123 @@
+"""H3 backend boundary and the Stage0.5 LoRA flow-matching runtime
+(reference: MiniMaxH3Backend solar/backends/minimax_h3/backend.py:15-44, H3TrainingRuntime
+runtime.py:491-1316, H3Stage0p5Core stage0p5.py:37-300).  The frozen bf16 base is never saved; the
+checkpoint holds ``adapter.pt`` (schema solarwm.minimax-h3-lora.v1), ``optimizer.pt``,
+``scheduler.pt``, ``rank-state.pt`` and ``runtime.pt``."""
+from __future__ import annotations
+
+import time
+from typing import Any, Mapping
+
+import torch
+
+from ... import ops
+from ...checkpoint.store import CheckpointContract, CheckpointTransaction
+from ...config.routes import validate_route
+from ...engine.master_adamw import FP32MasterAdamW
+from ...errors import BackendContractError, ConfigurationError
+from ...models.h3 import H3DiT, h3_preset
+from ...runtime.output_layout import checkpoint_model_dir, output_root
+from . import flow
+from .layout import build_layout, expand_cameras, patchify_latents
+
+
+class H3Stage0p5Trainer:
+    def __init__(self, cfg, device, lr=1e-4, seed=0):
+        dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
+        self.model = H3DiT(cfg, device=device, dtype=dtype, seed=seed)
+        self.opt = FP32MasterAdamW(self.model.trainable_parameters(), lr=lr)
+        self.device = torch.device(device)
+        self.gen = torch.Generator(device=self.device).manual_seed(seed * 100003)
+
+    def train_step(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        dev, dt = self.device, self.model.dtype
+        lat = sample["target_latents"].to(dev)                   # [C, F, H, W]
+        anchor = sample["anchor_latents"].to(dev)
+        prompt = sample["prompt_embeds"].to(dev)
+        C, F, H, W = lat.shape
+        u = torch.rand(1, generator=self.gen, device=dev)
+        t_video = float(1.0 - flow.shifted_sigma(u, flow.VIDEO_SHIFT))
+        layout = build_layout(n_text=prompt.shape[0], latent_frames=F, grid_hw=(H // 2, W // 2), t_video=t_video)
+        noise = torch.randn(lat.shape, generator=self.gen, device=dev, dtype=torch.float32).to(lat.dtype)
+        x_t = flow.interpolate(lat, noise, t_video)
+        a_noise = torch.randn(anchor.shape, generator=self.gen, device=dev, dtype=torch.float32).to(lat.dtype)
+        anchor_t = flow.interpolate(anchor, a_noise, 0.999)
+        cams = sample.get("camera_w2c")
+        view = None if cams is None else expand_cameras(layout, cams)
+        vid, _ = self.model(video_rows=patchify_latents(x_t).to(dt), text_rows=prompt.to(dt),
+                            anchor_rows=patchify_latents(anchor_t).to(dt), timesteps=layout.timesteps,
+                            t_index=layout.t_index.to(dev), tags=layout.tags.to(dev),
+                            position_ids=layout.position_ids, viewmats=view)
+        tgt = patchify_latents(flow.target(lat, noise).to(lat.dtype)).float()
+        loss = (vid.float() - tgt).pow(2).mean()
+        loss.backward()
+        self.opt.gather_grads()
+        self.opt.clip_(1.0)
+        self.opt.step()
+        self.opt.zero_grad()
+        return loss.detach()
+
+
+class MiniMaxH3Backend:
+    def __init__(self, family: str):
+        if family != "minimax_h3":
+            raise BackendContractError(f"not the H3 family: {family!r}")
+        self.family = family
+
+    def validate_config(self, config: Mapping[str, Any]) -> None:
+        if str(config["model"].get("camera_translation_transform", "")) != "logd4":
+            raise ConfigurationError("MiniMax-H3 requires camera_translation_transform: logd4")
+        if not config.get("runtime", {}).get("output_dir"):
+            raise ConfigurationError("runtime.output_dir is required")
+        d = config.get("distributed", {}) or {}
+        if int(d.get("context_parallel_size", 1)) != 1:
+            raise ConfigurationError("context_parallel_size must be 1 (sequence scaling is Ulysses SP)")
+
+    def _cfg(self, config):
+        arch = config["model"].get("architecture", "h3_33b")
+        cfg = h3_preset(arch)
+        cfg.lora_rank = int((config["model"].get("adapter", {}) or {}).get("rank", 8 if arch == "tiny" else 384))
+        return cfg
+
+    def train(self, config):
+        route = validate_route(config)
+        if route.stage != "stage0p5":
+            raise BackendContractError(f"H3 runtime for {route.key} is provided by engine.anyflow / engine.sgf "
+                                       "objectives on top of this trainer and is not wired to the CLI yet")
+        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
+        from ...data.synthetic import h3_sample
+
+        data = config["data"]
+        tr = H3Stage0p5Trainer(self._cfg(config), dev, lr=float(config["train"].get("optimizer", {}).get("lr", 1e-4)),
+                               seed=int(data.get("seed", 0)))
+        losses, t0 = [], time.time()
+        for step in range(int(config["train"]["max_steps"])):
+            s = h3_sample(latent_frames=int(data.get("latent_frames", 3)), height=int(data.get("latent_height", 8)),
+                          width=int(data.get("latent_width", 8)), prompt_len=int(data.get("prompt_len", 8)),
+                          text_dim=tr.model.cfg.text_dim, seed=step)
+            s["camera_w2c"] = torch.eye(4).repeat(s["target_latents"].shape[1] + 1, 1, 1)
+            losses.append(float(tr.train_step(s).item()))
+            print(f"[h3-stage0p5] step={step + 1} loss={losses[-1]:.5f} lr={tr.opt.lr:g} compute_time_s={time.time() - t0:.2f}")
+        root = output_root(config)
+        target = checkpoint_model_dir(root, len(losses))
+        with CheckpointTransaction(target) as tx:
+            adapter = {n: p.detach().cpu() for n, p in tr.model.named_parameters() if p.requires_grad}
+            torch.save({"schema": "solarwm.minimax-h3-lora.v1", "state": adapter, "rank": tr.model.cfg.lora_rank}, tx.path / "adapter.pt")
+            torch.save(tr.opt.state_dict(), tx.path / "optimizer.pt")
+            torch.save({"last_step": len(losses)}, tx.path / "scheduler.pt")
+            torch.save({"torch_cpu": torch.get_rng_state()}, tx.path / "rank-state.pt")
+            torch.save({"global_step": len(losses)}, tx.path / "runtime.pt")
+            tx.commit(step=len(losses), contract=CheckpointContract(
+                family="minimax_h3", stage="stage0p5", causal_mode="bidirectional", objective="flow_matching",
+                objective_variant="", camera_translation_transform="logd4", parameterization="lora", sp_size=1,
+                data_generation="synthetic"), required_components=["adapter.pt", "optimizer.pt", "scheduler.pt",
+                                                                    "rank-state.pt", "runtime.pt"], metadata={})
+        return {"final_step": len(losses), "last_loss": losses[-1], "checkpoint": str(target),
+                "native_launches": ops.total_launches()}
+
+    def infer(self, config):
+        raise BackendContractError("H3 source-length inference needs released condition files; use serve.h3_realtime "
+                                   "for synthetic streaming generation")
+
+    def preencode(self, config):
+        raise BackendContractError("H3 preencoding needs the official codec weights, which are not available offline")

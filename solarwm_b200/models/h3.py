@@ -1,0 +1,269 @@
+"""MiniMax-H3-shaped DiT: one packed heterogeneous token document, per-row adaLN tables, per-head
+q/k RMSNorm + MM-RoPE + camera PRoPE, SwiGLU FFN, LoRA adapters on a frozen bf16 base.
+
+The H3 architecture itself is external to the reference (it subclasses a diffusers model); the
+dimensions used here are the ones recoverable from it (hidden 5376, head_dim 128, 56 heads ->
+attention width 7168, FFN 14336, 50 blocks + 2 text-refiner blocks, text width 5120, 24-channel
+latents patched 1x2x2 -> 96-wide rows, 32-wide audio rows; solar/backends/minimax_h3/model.py:
+346-879, lora.py:55-71, stage0p5.py:72-76) and are all configurable.
+
+Packed document  [text | anchor | observations | audio | video]  as ONE ``[S, hidden]`` matrix:
+  * every row carries a modality tag (0 video, 1 text, 2 audio) and a timestep index; the adaLN
+    vectors of a row are looked up as ``table[t_idx * 3 + tag]`` (K1/K2 of the reference's Triton set,
+    here ``ops.norm_modulate(table=...)`` / ``ops.gated_residual(table=...)``)
+  * position ids ``[S, 3]`` (t, h, w) feed the MM-RoPE tables; rows with a camera carry a 4x4
+    projection on head channels [96, 128): ``P^T`` for queries, ``P^-1`` for keys and values, ``P`` for
+    the attention output (``ops.head_norm_rope_prope``)
+  * attention is plain bidirectional attention over the document (segment plans of block-causal
+    variants come from ``models.wan_causal.teacher_forcing_attention``-style chunk loops)
+
+LoRA: ``y = x W^T + (x A^T) B^T``; the low-rank product is accumulated into the base GEMM's output
+by the GEMM epilogue's reduce-add store (``accumulate=True``), so no extra pass over ``y``
+(reference: torch.addmm epilogue, solar/backends/minimax_h3/lora.py:402-471).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..ops import functional as F_
+
+TAG_VIDEO, TAG_TEXT, TAG_AUDIO = 0, 1, 2
+
+
+@dataclass
+class H3Config:
+    hidden_size: int = 5376
+    num_attention_heads: int = 56
+    attention_head_dim: int = 128
+    num_layers: int = 50
+    num_refiner_layers: int = 2
+    ffn_dim: int = 14336
+    text_dim: int = 5120
+    latent_row_dim: int = 96          # 24 channels x (1,2,2) patch
+    audio_row_dim: int = 32
+    time_embed_hidden_dim: int = 256
+    time_embed_dim: int = 1024
+    rot_dims: int = 96
+    rope_sections: int = 2
+    lora_rank: int = 0                # 0 = no adapters
+    eps: float = 1e-5
+
+    @property
+    def attn_dim(self) -> int:
+        return self.num_attention_heads * self.attention_head_dim
+
+
+def h3_preset(name: str) -> H3Config:
+    if name in ("h3_33b", "minimax_h3"):
+        return H3Config()
+    if name == "tiny":
+        return H3Config(hidden_size=256, num_attention_heads=2, num_layers=2, num_refiner_layers=1, ffn_dim=512,
+                        text_dim=64, time_embed_hidden_dim=32, time_embed_dim=64)
+    raise KeyError(name)
+
+
+class _LoRAFn(torch.autograd.Function):
+    """y = x W^T + (x A^T) B^T with frozen W; gradients for x, A and B."""
+
+    @staticmethod
+    def forward(ctx, x, w, a, b):
+        y = F_.gemm(x, w, F_.NT)
+        t = F_.gemm(x, a, F_.NT)
+        F_.gemm(t, b, F_.NT, out=y, accumulate=True)
+        ctx.save_for_backward(x, w, a, b, t)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, a, b, t = ctx.saved_tensors
+        dy = F_._rowmajor(dy)
+        dt = F_.gemm(dy, b, F_.NN)                      # [M, r]
+        dx = F_.gemm(dy, w, F_.NN)
+        F_.gemm(dt, a, F_.NN, out=dx, accumulate=True)
+        da = F_.gemm(dt, x, F_.TN, out_dtype=a.dtype)
+        db = F_.gemm(dy, t, F_.TN, out_dtype=b.dtype)
+        return dx, None, da, db
+
+
+class LoRALinear(nn.Module):
+    def __init__(self, d_in, d_out, rank, device, dtype, gen):
+        super().__init__()
+        bound = math.sqrt(6.0 / (d_in + d_out))
+        self.weight = nn.Parameter(((torch.rand(d_out, d_in, generator=gen) * 2 - 1) * bound).to(device, dtype),
+                                   requires_grad=rank == 0)
+        self.rank = rank
+        if rank > 0:
+            self.lora_A = nn.Parameter((torch.randn(rank, d_in, generator=gen) / math.sqrt(d_in)).to(device, dtype))
+            self.lora_B = nn.Parameter(torch.zeros(d_out, rank, device=device, dtype=dtype))
+
+    def forward(self, x):
+        if self.rank == 0:
+            return F_.linear(x, self.weight)
+        if not x.is_cuda:
+            return (x.float() @ self.weight.float().t() + (x.float() @ self.lora_A.float().t()) @ self.lora_B.float().t()).to(x.dtype)
+        return _LoRAFn.apply(x, self.weight, self.lora_A, self.lora_B)
+
+    @torch.no_grad()
+    def merge_(self):
+        """Fold the adapter into the base weight (released-weight merge)."""
+        if self.rank > 0:
+            self.weight.add_((self.lora_B.float() @ self.lora_A.float()).to(self.weight.dtype))
+            self.lora_B.zero_()
+
+
+class H3Block(nn.Module):
+    def __init__(self, cfg: H3Config, device, dtype, gen, modulated=True):
+        super().__init__()
+        self.cfg, self.modulated = cfg, modulated
+        h, a, f, r = cfg.hidden_size, cfg.attn_dim, cfg.ffn_dim, cfg.lora_rank
+        mk = lambda i, o: LoRALinear(i, o, r, device, dtype, gen)
+        self.to_q, self.to_k, self.to_v, self.to_out = mk(h, a), mk(h, a), mk(h, a), mk(a, h)
+        self.ffn_gate_up, self.ffn_down = mk(h, 2 * f), mk(f, h)
+        self.norm1 = nn.Parameter(torch.ones(h, device=device), requires_grad=False)
+        self.norm2 = nn.Parameter(torch.ones(h, device=device), requires_grad=False)
+        self.norm_q = nn.Parameter(torch.ones(cfg.attention_head_dim, device=device), requires_grad=False)
+        self.norm_k = nn.Parameter(torch.ones(cfg.attention_head_dim, device=device), requires_grad=False)
+        if modulated:
+            self.adaln_proj = nn.Parameter((torch.randn(3 * 6 * h, cfg.time_embed_dim, generator=gen) * 0.02).to(device, dtype),
+                                           requires_grad=False)
+
+    def tables(self, temb):
+        """temb [T, time_embed_dim] -> adaLN table fp32 [T*3, 6, hidden] (row = t_idx*3 + tag)."""
+        t = F_.linear(torch.nn.functional.silu(temb.float()).to(temb.dtype), self.adaln_proj)
+        return t.float().view(-1, 6, self.cfg.hidden_size).contiguous()
+
+    def forward(self, x, table, idx, rope_cos, rope_sin, cam_q, cam_kv, cam_o, sp=None, attn_fn=None):
+        cfg = self.cfg
+        H, hd = cfg.num_attention_heads, cfg.attention_head_dim
+        kw = dict(rot_dims=cfg.rot_dims, sections=cfg.rope_sections, eps=cfg.eps)
+        if self.modulated:
+            xm = F_.norm_modulate(x, table[:, 0], table[:, 1], mode=1, w=self.norm1, eps=cfg.eps, table=idx)
+        else:
+            xm = F_.norm_modulate(x, mode=1, w=self.norm1, eps=cfg.eps)
+        q = ops.head_norm_rope_prope(self.to_q(xm), self.norm_q, rope_cos, rope_sin, cam_q, heads=H, **kw)
+        k = ops.head_norm_rope_prope(self.to_k(xm), self.norm_k, rope_cos, rope_sin, cam_kv, heads=H, **kw)
+        v = self.to_v(xm)
+        if cam_kv is not None:
+            v = ops.head_norm_rope_prope(v, None, None, None, cam_kv, heads=H, **kw)
+        S = x.shape[0]
+        q, k, v = (t.view(1, S, H, hd) for t in (q, k, v))
+        if sp is not None and sp.size > 1:
+            q, k, v = sp.scatter_heads(q, k, v)
+        o = attn_fn(q, k, v) if attn_fn is not None else ops.attention(q, k, v)
+        if sp is not None and sp.size > 1:
+            o = sp.gather_heads(o)
+        o = o.reshape(S, H * hd)
+        if cam_o is not None:
+            o = ops.head_norm_rope_prope(o, None, None, None, cam_o, heads=H, **kw)
+        y = self.to_out(o)
+        x = F_.gated_residual(x, y, table[:, 2], table=idx) if self.modulated else F_.gated_residual(x, y, None)
+        if self.modulated:
+            xm = F_.norm_modulate(x, table[:, 3], table[:, 4], mode=1, w=self.norm2, eps=cfg.eps, table=idx)
+        else:
+            xm = F_.norm_modulate(x, mode=1, w=self.norm2, eps=cfg.eps)
+        y = self.ffn_down(F_.swiglu(self.ffn_gate_up(xm)))
+        return F_.gated_residual(x, y, table[:, 5], table=idx) if self.modulated else F_.gated_residual(x, y, None)
+
+
+def mm_rope_tables(position_ids: torch.Tensor, rot_dims: int = 96, sections: int = 2, theta: float = 10000.0):
+    """position_ids [S, 3] (t, h, w; float64) -> (cos, sin) fp32 [S, rot_dims] in rotate-half layout:
+    each section holds its frequencies twice (first half | second half).  The rot_dims/2 frequency
+    slots are dealt to the three axes in equal thirds."""
+    S = position_ids.shape[0]
+    pairs = rot_dims // 2
+    per_axis = pairs // 3
+    pos = position_ids.to(torch.float64)
+    ang = []
+    for axis in range(3):
+        n = per_axis if axis < 2 else pairs - 2 * per_axis
+        inv = 1.0 / torch.pow(theta, torch.arange(n, dtype=torch.float64, device=pos.device) / n)
+        ang.append(pos[:, axis:axis + 1] * inv)
+    ang = torch.cat(ang, dim=1)                                     # [S, pairs]
+    per_sec = pairs // sections
+    blocks = [torch.cat([ang[:, s * per_sec:(s + 1) * per_sec]] * 2, dim=1) for s in range(sections)]
+    full = torch.cat(blocks, dim=1)
+    return torch.cos(full).float().contiguous(), torch.sin(full).float().contiguous()
+
+
+def prope_row_matrices(viewmats: torch.Tensor, fx: float, fy: float):
+    """viewmats [S, 4, 4] (identity for rows without a camera) -> (P^T for q, P^-1 for k/v, P for the output),
+    each fp32 [S, 4, 4], with P = diag(fx, fy, 1, 1) @ view."""
+    v = viewmats.to(torch.float64)
+    lift = torch.diag(torch.tensor([fx, fy, 1.0, 1.0], dtype=torch.float64, device=v.device))
+    P = lift @ v
+    Pinv = torch.linalg.inv(P)
+    f = lambda m: m.float().contiguous()
+    return f(P.transpose(-1, -2)), f(Pinv), f(P)
+
+
+class H3DiT(nn.Module):
+    def __init__(self, cfg: H3Config, device="cpu", dtype=torch.bfloat16, seed: int = 0):
+        super().__init__()
+        self.cfg, self.dtype = cfg, dtype
+        g = torch.Generator().manual_seed(seed)
+        h = cfg.hidden_size
+        lin = lambda i, o, s=None: nn.Parameter((torch.randn(o, i, generator=g) * (s or 1.0 / math.sqrt(i))).to(device, dtype),
+                                                requires_grad=False)
+        self.proj_in, self.audio_proj_in = lin(cfg.latent_row_dim, h), lin(cfg.audio_row_dim, h)
+        self.context_embedder = lin(cfg.text_dim, h)
+        self.time_in, self.time_out = lin(cfg.time_embed_hidden_dim, cfg.time_embed_dim), lin(cfg.time_embed_dim, cfg.time_embed_dim)
+        self.refiner = nn.ModuleList([H3Block(cfg, device, dtype, g, modulated=False) for _ in range(cfg.num_refiner_layers)])
+        self.blocks = nn.ModuleList([H3Block(cfg, device, dtype, g) for _ in range(cfg.num_layers)])
+        self.norm_out = nn.Parameter(torch.ones(h, device=device), requires_grad=False)
+        self.proj_out, self.audio_proj_out = lin(h, cfg.latent_row_dim, 0.02), lin(h, cfg.audio_row_dim, 0.02)
+        self.sp = None
+
+    def trainable_parameters(self):
+        return [p for p in self.parameters() if p.requires_grad]
+
+    def time_embed(self, timesteps):
+        """unique timesteps [T] in [0, 1] -> [T, time_embed_dim]"""
+        from .wan import sinusoidal_embedding
+
+        e = sinusoidal_embedding(self.cfg.time_embed_hidden_dim, timesteps * 1000.0).to(self.dtype)
+        e = F_.linear(e, self.time_in)
+        return F_.linear(torch.nn.functional.silu(e.float()).to(self.dtype), self.time_out)
+
+    def forward(self, *, video_rows, text_rows, audio_rows=None, anchor_rows=None, timesteps, t_index, tags,
+                position_ids, viewmats=None, fx=0.505, fy=0.898):
+        """Rows are packed in the order [text | anchor | audio | video]; ``t_index`` / ``tags`` /
+        ``position_ids`` / ``viewmats`` are per packed row.  Returns (video prediction [Nv, 96],
+        audio prediction [Na, 32] or None)."""
+        cfg = self.cfg
+        dt = self.dtype
+        parts, n_text = [], text_rows.shape[0]
+        txt = F_.linear(text_rows.to(dt), self.context_embedder)
+        cos, sin = mm_rope_tables(position_ids.to(txt.device), cfg.rot_dims, cfg.rope_sections)
+        for blk in self.refiner:       # text-only refiner blocks (no modulation, no camera)
+            txt = blk(txt, None, None, cos[:n_text].contiguous(), sin[:n_text].contiguous(), None, None, None)
+        parts.append(txt)
+        if anchor_rows is not None:
+            parts.append(F_.linear(anchor_rows.to(dt), self.proj_in))
+        n_audio = 0
+        if audio_rows is not None:
+            n_audio = audio_rows.shape[0]
+            parts.append(F_.linear(audio_rows.to(dt), self.audio_proj_in))
+        n_video = video_rows.shape[0]
+        parts.append(F_.linear(video_rows.to(dt), self.proj_in))
+        x = torch.cat(parts, dim=0)
+        S = x.shape[0]
+        assert t_index.shape[0] == S and tags.shape[0] == S and position_ids.shape[0] == S
+        idx = (t_index.to(torch.int32) * 3 + tags.to(torch.int32)).contiguous()
+        temb = self.time_embed(timesteps.to(x.device).float())
+        cam_q = cam_kv = cam_o = None
+        if viewmats is not None:
+            cam_q, cam_kv, cam_o = prope_row_matrices(viewmats.to(x.device), fx, fy)
+        for blk in self.blocks:
+            x = blk(x, blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o, sp=self.sp)
+        xn = F_.norm_modulate(x, mode=1, w=self.norm_out, eps=cfg.eps)
+        vid = F_.linear(xn[S - n_video:], self.proj_out)
+        aud = None
+        if n_audio:
+            aud = F_.linear(xn[S - n_video - n_audio:S - n_video], self.audio_proj_out)
+        return vid, aud

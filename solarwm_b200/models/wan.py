@@ -54,6 +54,7 @@ class WanConfig:
     flow_objective: str = "flow_matching"   # or "anyflow_forward_map"
     anyflow_gate: float = 0.25
     camera_attention_mode: str = "none"     # "none" | "fused_prope"
+    norm_type: str = "layer"                # "layer": LayerNorm without affine (Wan); "rms": RMSNorm (LTX)
 
     @property
     def head_dim(self) -> int:
@@ -71,6 +72,10 @@ def wan_preset(name: str) -> WanConfig:
     if name in ("i2v_a14b", "wan22_i2v_a14b"):
         return WanConfig(model_type="i2v", in_dim=36, out_dim=16, dim=5120, ffn_dim=13824, num_heads=40,
                          num_layers=40, local_attn_size=21, sink_size=0)
+    if name in ("ltx_video_2b", "ltx25_video"):
+        # LTX-Video-2B-shaped: 28 blocks, dim 2048, 32 heads x 64, 128-channel latents, patch 1, RMSNorm
+        return WanConfig(model_type="t2v", patch_size=(1, 1, 1), in_dim=128, out_dim=128, dim=2048, ffn_dim=8192,
+                         num_heads=32, num_layers=28, text_dim=4096, text_len=128, norm_type="rms", cross_attn_norm=False)
     if name == "tiny":
         return WanConfig(model_type="t2v", in_dim=16, out_dim=16, dim=128, ffn_dim=512, num_heads=4,
                          num_layers=2, text_dim=256, text_len=32, freq_dim=64)
@@ -181,6 +186,15 @@ class WanBlock(nn.Module):
     def _use_main_grad(self) -> bool:
         return self.unit.grad is not None and torch.is_grad_enabled()
 
+    def _norm_kw(self, x):
+        """Pre-modulation norm: LayerNorm without affine (Wan) or weight-free RMSNorm (LTX)."""
+        if self.cfg.norm_type == "layer":
+            return {"mode": 0}
+        ones = getattr(self, "_ones", None)
+        if ones is None or ones.device != x.device:
+            ones = self._ones = torch.ones(self.cfg.dim, dtype=torch.float32, device=x.device)
+        return {"mode": 1, "w": ones}
+
     def _linear(self, x, wname, bname):
         return F_.linear(x, self._p(wname), self._p(bname))
 
@@ -223,7 +237,8 @@ class WanBlock(nn.Module):
         gk = dict(rows_per_group=frame_tokens, group_offset=group_offset)
 
         # ---- self attention
-        xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], mode=0, eps=cfg.eps, **gk)
+        nk = self._norm_kw(x)
+        xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
         Ll = x.shape[0] // B
         fused_sp = bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
             (not torch.is_grad_enabled() or self.unit.grad is not None)
@@ -267,7 +282,7 @@ class WanBlock(nn.Module):
         x = F_.gated_residual(x, yc, None)
 
         # ---- feed forward
-        xm = F_.norm_modulate(x, mod[:, 3], mod[:, 4], mode=0, eps=cfg.eps, **gk)
+        xm = F_.norm_modulate(x, mod[:, 3], mod[:, 4], eps=cfg.eps, **nk, **gk)
         h = self._linear(xm, "ffn.0.weight", "ffn.0.bias")
         a = F_.gelu(h)
         y = self._linear(a, "ffn.2.weight", "ffn.2.bias")
@@ -481,6 +496,7 @@ class WanDiT(nn.Module):
             xs = sp.gather_sequence(xs, B)
         # head
         hm = (P["head.modulation"].float().view(1, 2, cfg.dim) + e.float().view(-1, 1, cfg.dim)).contiguous()
-        xh = F_.norm_modulate(xs, hm[:, 0], hm[:, 1], mode=0, eps=cfg.eps, rows_per_group=frame_tokens)
+        xh = F_.norm_modulate(xs, hm[:, 0], hm[:, 1], eps=cfg.eps, rows_per_group=frame_tokens,
+                              **self.blocks[0]._norm_kw(xs))
         out = F_.linear(xh, P["head.head.weight"], P["head.head.bias"])
         return self.unpatchify(out, B, grid)
