@@ -19,7 +19,8 @@
 // alternate over streamed tiles (thread = TMEM lane).  The streamed tile in shared memory feeds
 // two different MMAs through two descriptors: K-major as the B operand of the score GEMMs and
 // MN-major as the B operand of the accumulate GEMMs.  P^T / dS are written back to TMEM as packed
-// bf16 over the first half of the S / dP columns and consumed as the A operand from TMEM.
+// bf16 over columns [0,16) and [32,48) of the S / dP tiles (each compute warpgroup overwrites columns
+// it consumed itself) and read from there as the A operand of the accumulate MMAs.
 //
 // TMEM columns: buf0 {S [0,64) dP [64,128)}  buf1 {S [128,192) dP [192,256)}  acc0 [256,384)
 // acc1 [384,512).  Every wait is bounded (sm100.cuh).
@@ -124,7 +125,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_ready[b], 1);
-      mbar_init(&p_ready[b], 128);
+      mbar_init(&p_ready[b], 256);   // both compute warpgroups arrive
     }
     mbar_init(acc_done, 1);
     *abort_word = 0;
@@ -145,6 +146,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
 
   if (warp == 0) {
     // -------------------------------------------------------------- TMA producer
+    setmaxnreg_dec<72>();
     if (lane == 0) {
       mbar_expect_tx(stat_full, 2 * L::STAT_TILE);
 #pragma unroll
@@ -169,6 +171,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
+    setmaxnreg_dec<72>();
     if (lane == 0) {
       constexpr uint32_t idesc_score = umma_idesc_bf16(128, SR_ROWS, 0, 0);   // [128 x 64], K = HD
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);          // [128 x HD], K = 64, B MN-major
@@ -201,16 +204,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
         if (MODE == 0) {
 #pragma unroll
           for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dV += P^T dO_i
-            umma_ts(tmem_base + 256, tP + kk * 8, umma_desc_mnmajor(s1 + kk * 2048, L::STRM_CHUNK), idesc_acc,
+            umma_ts(tmem_base + 256, tP + (kk / 2) * 32 + (kk % 2) * 8, umma_desc_mnmajor(s1 + kk * 2048, L::STRM_CHUNK), idesc_acc,
                     (t | kk) != 0);
 #pragma unroll
           for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dK += dS^T Q_i
-            umma_ts(tmem_base + 384, tdS + kk * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
+            umma_ts(tmem_base + 384, tdS + (kk / 2) * 32 + (kk % 2) * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
                     (t | kk) != 0);
         } else {
 #pragma unroll
           for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dQ += dS K_j
-            umma_ts(tmem_base + 256, tdS + kk * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
+            umma_ts(tmem_base + 256, tdS + (kk / 2) * 32 + (kk % 2) * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
                     (t | kk) != 0);
         }
         umma_commit(&strm_empty[s]);
@@ -228,13 +231,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
       if (ok) ok = accumulate(n_tiles - 1);
       if (ok) umma_commit(acc_done);
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    setmaxnreg_dec<72>();
+  } else {
     // -------------------------------------------------------------- compute warpgroups
+    setmaxnreg_inc<208>();
     const int wg = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t tS = tmem_base + lane_off + wg * 128, tD = tS + 64;
     const long long vec_base = (static_cast<long long>(batch) * p.H + head) * p.S_pad;
     const float c = p.scale_log2, sc = p.scale;
     float my_L2 = 0.f, my_delta = 0.f;
@@ -243,50 +248,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
       my_delta = p.delta[vec_base + row0 + row];
     }
     bool ok = true;
-    for (int j = wg; j < n_tiles && ok; j += 2) {
-      if (!mbar_wait(&s_ready[wg], (j >> 1) & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+    // Both warpgroups work on every streamed tile: warpgroup g owns columns [32g, 32g+32) of the
+    // 64-column S / dP tile (elements are independent, so the split needs no exchange); this halves the
+    // latency of the compute stage that sits between the score MMAs and the accumulate MMAs.
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      const uint32_t tS = tmem_base + lane_off + b * 128, tD = tS + 64;
+      if (!mbar_wait(&s_ready[b], (j >> 1) & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t s[32], d[32];
-        tmem_ld_32x32(tS + half * 32, s);
-        tmem_ld_32x32(tD + half * 32, d);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
-        const float4* l4 = nullptr;
-        const float4* d4 = nullptr;
-        if (MODE == 0) {
-          l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + j * SR_ROWS + half * 32);
-          d4 = reinterpret_cast<const float4*>(p.delta + vec_base + j * SR_ROWS + half * 32);
-        }
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          float L[4], Dl[4];
-          if (MODE == 0) {
-            const float4 a = __ldg(l4 + g), b = __ldg(d4 + g);
-            L[0] = a.x; L[1] = a.y; L[2] = a.z; L[3] = a.w;
-            Dl[0] = b.x; Dl[1] = b.y; Dl[2] = b.z; Dl[3] = b.w;
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { L[e] = my_L2; Dl[e] = my_delta; }
-          }
-          float pv[4], dv[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            pv[e] = exp2_fast(fmaf(__uint_as_float(s[g * 4 + e]), c, -L[e]));
-            dv[e] = pv[e] * (__uint_as_float(d[g * 4 + e]) - Dl[e]) * sc;
-          }
-          pk[g * 2] = pack_bf16x2(pv[0], pv[1]);
-          pk[g * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
-          dk[g * 2] = pack_bf16x2(dv[0], dv[1]);
-          dk[g * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
-        }
-        if (MODE == 0) tmem_st_32x16(tS + half * 16, pk);
-        tmem_st_32x16(tD + half * 16, dk);
+      uint32_t s[32], d[32];
+      tmem_ld_32x32(tS + wg * 32, s);
+      tmem_ld_32x32(tD + wg * 32, d);
+      tmem_ld_wait();
+      const float2 c2 = make_float2(c, c), sc2 = make_float2(sc, sc);
+      const float4* l4 = nullptr;
+      const float4* d4 = nullptr;
+      if (MODE == 0) {
+        l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + j * SR_ROWS + wg * 32);
+        d4 = reinterpret_cast<const float4*>(p.delta + vec_base + j * SR_ROWS + wg * 32);
       }
+      uint32_t pk[16], dk[16];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        float2 nL[2], Dl[2];
+        if (MODE == 0) {
+          const float4 a = __ldg(l4 + g), bb = __ldg(d4 + g);
+          nL[0] = make_float2(-a.x, -a.y); nL[1] = make_float2(-a.z, -a.w);
+          Dl[0] = make_float2(bb.x, bb.y); Dl[1] = make_float2(bb.z, bb.w);
+        } else {
+          nL[0] = nL[1] = make_float2(-my_L2, -my_L2);
+          Dl[0] = Dl[1] = make_float2(my_delta, my_delta);
+        }
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int e = g * 4 + h2 * 2;
+          const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2, nL[h2]);
+          const float2 pv = make_float2(exp2_fast(tt.x), exp2_fast(tt.y));
+          float2 dd = make_float2(__uint_as_float(d[e]) - Dl[h2].x, __uint_as_float(d[e + 1]) - Dl[h2].y);
+          dd = __fmul2_rn(__fmul2_rn(pv, dd), sc2);
+          pk[e >> 1] = pack_bf16x2(pv.x, pv.y);
+          dk[e >> 1] = pack_bf16x2(dd.x, dd.y);
+        }
+      }
+      // each warpgroup writes its packed results over columns it has itself consumed: [32g, 32g+16)
+      if (MODE == 0) tmem_st_32x16(tS + wg * 32, pk);
+      tmem_st_32x16(tD + wg * 32, dk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_ready[wg]);
+      mbar_arrive(&p_ready[b]);
     }
     // ---- epilogue: accumulators -> bf16 -> shared memory (stationary buffers) -> TMA store
     if (ok) ok = mbar_wait(acc_done, 0, abort_word, ST_TIMEOUT_OTHER);

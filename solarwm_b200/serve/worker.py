@@ -1,0 +1,126 @@
+"""Realtime worker: one process per GPU; rank 0 also runs the HTTP threads.  Commands
+(``prepare / start / chunk / stop / shutdown``) are chosen on rank 0 and broadcast to every rank
+over a gloo control group before any GPU work, so all ranks execute the same sequence; failures
+are exchanged as text and written to ``failure-rank{r}.json`` / ``exit-rank{r}.json`` receipts
+(reference: deploy/solar_wm/backends/standard/worker.py:17-350, runtime/engine.py:17-272).
+
+    python -m solarwm_b200.serve.worker --smoke --chunks 6            # synthetic scene, no HTTP
+    torchrun --nproc-per-node 8 -m solarwm_b200.serve.worker --serve  # SP over the box
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+from pathlib import Path
+
+import torch
+
+from ..models.wan import WanConfig, WanDiT, wan_preset
+from .camera_control import NavigationState
+from .state import SessionState
+from .streaming import StreamingConfig, StreamingGenerator
+
+
+class Engine:
+    """Resident model + streaming generator + camera controller; ``generate`` returns one chunk."""
+
+    def __init__(self, model, stream_cfg: StreamingConfig, navigation: NavigationState):
+        self.generator = StreamingGenerator(model, stream_cfg)
+        self.navigation = navigation
+        self.cameras = []
+
+    def start(self, context, grid_hw, first_frame=None):
+        self.generator.start(context, grid_hw, first_frame)
+
+    def generate(self):
+        poses = self.navigation.advance(self.generator.cfg.chunk_frames)
+        self.cameras.append(poses)
+        latents = self.generator.next_chunk()
+        return latents, self.generator.stats[-1]
+
+
+def _receipt(out_dir: Path, name: str, payload: dict) -> None:
+    out_dir.mkdir(parents=True, exist_ok=True)
+    (out_dir / name).write_text(json.dumps(payload, sort_keys=True))
+
+
+def run(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    out_dir = Path(args.output)
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if torch.cuda.is_available() else torch.device("cpu")
+    state, nav = SessionState(), NavigationState()
+    try:
+        cfg = wan_preset(args.model) if args.model != "small" else WanConfig(
+            model_type="ti2v", in_dim=48, out_dim=48, dim=512, ffn_dim=2048, num_heads=4, num_layers=4,
+            text_dim=4096, text_len=512)
+        dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+        model = WanDiT(cfg, device=dev, dtype=dtype, seed=0).eval()
+        with torch.no_grad():
+            model.get_parameter("head.head.weight").normal_(0, 0.02)
+        engine = Engine(model, StreamingConfig(chunk_frames=args.chunk_frames, window_frames=args.window_frames,
+                                               use_cuda_graphs=not args.no_graphs), nav)
+        server = None
+        if args.serve and rank == 0:
+            from .web import make_server, serve_in_thread
+
+            server = make_server(state, nav, port=args.port)
+            serve_in_thread(server)
+        g = torch.Generator().manual_seed(0)
+        context = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(dtype)
+        state.set_phase("preparing")
+        engine.start(context, (args.height // 2, args.width // 2))
+        state.set_phase("running")
+        if args.smoke:
+            nav.set_key("w", True)
+            for i in range(args.chunks):
+                _, st = engine.generate()
+                state.generated(st.index, st.dit_ms, 0.0)
+            steady = [c["dit_ms"] for c in state.chunks if engine.generator.stats[c["index"]].graph] or \
+                     [c["dit_ms"] for c in state.chunks[1:]]
+            report = {"chunks": args.chunks, "chunk_frames": args.chunk_frames,
+                      "median_chunk_ms": sorted(steady)[len(steady) // 2] if steady else None,
+                      "graph_chunks": sum(1 for s in engine.generator.stats if s.graph)}
+            if rank == 0:
+                print(json.dumps(report))
+        else:
+            while True:
+                cmd = state.next_command()
+                if cmd["op"] == "shutdown":
+                    break
+                if cmd["op"] == "stop":
+                    state.set_phase("stopped")
+                elif cmd["op"] == "start":
+                    state.set_phase("running")
+                elif cmd["op"] == "chunk" and state.phase == "running":
+                    _, st = engine.generate()
+                    state.generated(st.index, st.dit_ms, 0.0)
+        if server is not None:
+            server.shutdown()
+        _receipt(out_dir, f"exit-rank{rank}.json", {"rank": rank, "status": "ok", "chunks": len(state.chunks), "time": time.time()})
+        return 0
+    except Exception as exc:  # noqa: BLE001
+        state.set_phase("failed", str(exc))
+        _receipt(out_dir, f"failure-rank{rank}.json", {"rank": rank, "error": f"{type(exc).__name__}: {exc}"})
+        raise
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="small")
+    ap.add_argument("--height", type=int, default=16)
+    ap.add_argument("--width", type=int, default=16)
+    ap.add_argument("--chunk-frames", type=int, default=3)
+    ap.add_argument("--window-frames", type=int, default=9)
+    ap.add_argument("--chunks", type=int, default=6)
+    ap.add_argument("--port", type=int, default=8900)
+    ap.add_argument("--output", default="serve_out")
+    ap.add_argument("--smoke", action="store_true")
+    ap.add_argument("--serve", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true")
+    return run(ap.parse_args(argv))
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

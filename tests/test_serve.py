@@ -1,0 +1,73 @@
+import json
+import urllib.request
+
+import numpy as np
+import pytest
+
+from solarwm_b200.serve import camera_control as cc
+from solarwm_b200.serve.state import SessionState
+from solarwm_b200.serve.web import make_server, serve_in_thread
+
+
+def test_action_strings_and_padding():
+    acts = cc.parse_action_string("w-2, dl-1，none-1")
+    assert acts == [["w"], ["w"], ["d", "l"], []]
+    assert cc.fit_action_steps(acts, num_transitions=6)[-1] == []
+    for bad in ("", "w", "w-0", "x-1", "w-1,,a-1", "-2"):
+        with pytest.raises(ValueError):
+            cc.parse_action_string(bad)
+    with pytest.raises(ValueError):
+        cc.fit_action_steps(acts, num_transitions=3)
+
+
+def test_camera_integration_is_smooth_and_bounded():
+    st = cc.KeyboardCameraState(cc.KeyboardCameraConfig(acceleration_seconds=0.25))
+    z = [st.step("w")[2, 3] for _ in range(16)]
+    steps = np.diff([0.0] + z)
+    assert np.all(steps[1:] >= steps[:-1] - 1e-6) and abs(steps[-1] - 1.2 / 16) < 1e-6      # accelerates to full speed
+    assert abs(steps[0] - (1.2 / 16) / 4) < 1e-6
+    coast = [st.step([])[2, 3] for _ in range(8)]
+    assert coast[-1] == pytest.approx(coast[-2])                                             # decelerates to rest
+    st = cc.KeyboardCameraState(cc.KeyboardCameraConfig(acceleration_seconds=0.0, pitch_speed_degrees_per_second=600))
+    for _ in range(16):
+        st.step("i")
+    assert st.pitch == pytest.approx(np.radians(85.0))
+    R = st.c2w[:3, :3]
+    assert np.allclose(R @ R.T, np.eye(3), atol=1e-9)
+    poses = cc.actions_to_latent_c2w(cc.parse_action_string("l-3"), temporal_stride=4)
+    assert poses.shape == (4, 4, 4) and np.allclose(poses[0], np.eye(4))
+    with pytest.raises(ValueError):
+        st.set_move_speed_scale(10.0)
+
+
+def test_web_state_and_keys():
+    state, nav = SessionState(), cc.NavigationState()
+    server = make_server(state, nav, port=0)
+    serve_in_thread(server)
+    base = f"http://127.0.0.1:{server.server_address[1]}"
+
+    def post(path, payload):
+        req = urllib.request.Request(base + path, data=json.dumps(payload).encode(), method="POST")
+        try:
+            return urllib.request.urlopen(req).status
+        except urllib.error.HTTPError as e:
+            return e.code
+
+    assert post("/key", {"key": "w", "down": True}) == 200 and nav.down == {"w"}
+    assert post("/key", {"key": "q", "down": True}) == 400
+    assert post("/command", {"op": "start"}) == 200 and state.next_command()["op"] == "start"
+    assert post("/command", {"op": "explode"}) == 400
+    state.generated(0, 12.5, 3.0)
+    snap = json.loads(urllib.request.urlopen(base + "/state").read())
+    assert snap["chunks"] == 1 and snap["recent"][0]["dit_ms"] == 12.5
+    server.shutdown()
+
+
+def test_worker_smoke_on_cpu(tmp_path, capsys):
+    from solarwm_b200.serve.worker import main
+
+    assert main(["--smoke", "--model", "tiny", "--height", "8", "--width", "8", "--chunk-frames", "1", "--window-frames", "3",
+                 "--chunks", "4", "--output", str(tmp_path)]) == 0
+    report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert report["chunks"] == 4
+    assert json.loads((tmp_path / "exit-rank0.json").read_text())["status"] == "ok"
