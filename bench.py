@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--height", type=int, default=44)
     ap.add_argument("--width", type=int, default=80)
     ap.add_argument("--checkpointing", default="auto", choices=["auto", "none", "full", "selective"])
+    ap.add_argument("--keep-blocks", type=int, default=-1,
+                    help="blocks exempt from recompute under checkpointing (-1: sized from free HBM)")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
     ap.add_argument("--sp-transport", default="fused", choices=["fused", "nccl"],
                     help="Ulysses exchange: fused into the kernels over NVLink peer memory, or NCCL all-to-all")
@@ -174,8 +176,20 @@ def run_ours(args):
     ckpt = args.checkpointing
     if ckpt == "auto":
         ckpt = "selective" if (args.model == "ti2v_5b" and world < 4) else "none"
+    keep = args.keep_blocks
+    if keep < 0:
+        keep = 0
+        if ckpt == "selective":
+            # resident bytes of one un-checkpointed block: ~17 [S, dim] and 2 [S, ffn] bf16 tensors
+            s_local = args.frames * (args.height // 2) * (args.width // 2) / world
+            per_block = s_local * (17 * cfg.dim + 2 * cfg.ffn_dim) * 2
+            n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
+            fixed = 18.0 * n_params  # bf16 weight + fp32 grad + fp32 master/m/v
+            total = torch.cuda.get_device_properties(local).total_memory
+            keep = int(max(0.0, 0.92 * total - fixed - 0.6e9 * cfg.num_layers - 12e9) // per_block)
+            keep = min(keep, cfg.num_layers)
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
-                           max_grad_norm=1.0, seed=0)
+                           keep_blocks=keep, max_grad_norm=1.0, seed=0)
     trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp)
     with torch.no_grad():  # a zero head would zero every upstream gradient; keep the step representative
         trainer.model.get_parameter("head.head.weight").normal_(0, 0.02)
@@ -219,7 +233,7 @@ def run_ours(args):
             "config": {"model": "wan22_ti2v_5b-shaped" if args.model == "ti2v_5b" else "small-debug",
                        "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
                        "latent": [1, cfg.in_dim, args.frames, args.height, args.width],
-                       "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt,
+                       "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt, "keep_blocks": keep,
                        "attention_backend": ops.get_backend(), "optimizer": "AdamW fp32 master (in timed region)",
                        "l2": "no flush: per-step working set (>=10 GB of weights) exceeds the 126 MB L2",
                        "peak_allocated_gib": round(peak_gib, 2)},

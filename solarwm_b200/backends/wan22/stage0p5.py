@@ -37,6 +37,7 @@ class Stage0p5Options:
     grad_accum: int = 1
     ema_decay: Optional[float] = None
     checkpointing: str = "none"
+    keep_blocks: int = 0
     seed: int = 0
 
 
@@ -50,6 +51,7 @@ class WanStage0p5Trainer:
         if sp is not None:
             self.model.sp = sp
         self.model.checkpointing = opts.checkpointing
+        self.model.keep_blocks = opts.keep_blocks
         self.model.ensure_grads()
         self.optimizer = FlatAdamW(self.model.units(), lr=opts.lr, betas=opts.betas, eps=opts.eps,
                                    weight_decay=opts.weight_decay, ema_decay=opts.ema_decay)

@@ -323,6 +323,7 @@ class WanDiT(nn.Module):
         self.blocks = nn.ModuleList([WanBlock(cfg, device, dtype, shard_pad) for _ in range(cfg.num_layers)])
         self.sp = _NoSP()
         self.checkpointing = "none"  # "none" | "full" | "selective"
+        self.keep_blocks = 0         # the last ``keep_blocks`` blocks keep their activations (no recompute)
         self._rope_cache: dict = {}
         if seed is not None:
             self.init_weights(seed)
@@ -436,12 +437,14 @@ class WanDiT(nn.Module):
         c = F_.gelu(c)
         return F_.linear(c, P["text_embedding.2.weight"], P["text_embedding.2.bias"])
 
-    def _run_block(self, block, x, e0, rope, ctx, kw):
+    def _run_block(self, block, x, e0, rope, ctx, kw, index=0):
         """``checkpointing``: "none" keeps every activation; "full" recomputes the whole block in
         backward; "selective" recomputes the block except its two attention calls, whose outputs are
         carried across the recompute (the reference's saved-attention policy,
-        solar/backends/minimax_h3/fsdp.py:146-165)."""
-        if self.checkpointing in ("full", "selective") and torch.is_grad_enabled():
+        solar/backends/minimax_h3/fsdp.py:146-165).  The last ``keep_blocks`` blocks are exempt: with
+        memory to spare their activations stay resident and their recompute is saved."""
+        exempt = index >= len(self.blocks) - int(self.keep_blocks)
+        if self.checkpointing in ("full", "selective") and torch.is_grad_enabled() and not exempt:
             from torch.utils.checkpoint import checkpoint
 
             memo = {"__store__": True} if (self.checkpointing == "selective" and x.is_cuda) else None
@@ -490,8 +493,8 @@ class WanDiT(nn.Module):
             e0_l, goff = e0, f0 if sp.size > 1 else 0
         kw = dict(B=B, L=L, frame_tokens=frame_tokens, group_offset=goff, sp=sp)
         xs = tok
-        for block in self.blocks:
-            xs = self._run_block(block, xs, e0_l, rope, ctx, kw)
+        for bi, block in enumerate(self.blocks):
+            xs = self._run_block(block, xs, e0_l, rope, ctx, kw, index=bi)
         if sp.size > 1:
             xs = sp.gather_sequence(xs, B)
         # head
