@@ -50,7 +50,8 @@ def synthetic_batches(config, arch, device) -> Iterator[dict]:
 class WanStage0p5Runtime:
     """Adapts ``WanStage0p5Trainer`` to the engine's 11-hook protocol."""
 
-    def __init__(self, config: Mapping[str, Any]):
+    def __init__(self, config: Mapping[str, Any], trainer_cls=WanStage0p5Trainer, options_cls=Stage0p5Options,
+                 extra_options: Mapping[str, Any] = None):
         self.config = config
         self.route = validate_route(config)
         dist_cfg = config.get("distributed", {}) or {}
@@ -62,7 +63,7 @@ class WanStage0p5Runtime:
         opt = train.get("optimizer", {}) or {}
         ema = train.get("ema", {}) or {}
         seed = int(config["data"].get("seed", 0))
-        opts = Stage0p5Options(
+        opts = options_cls(
             lr=float(opt.get("lr", 1e-4)), betas=tuple(opt.get("betas", (0.9, 0.999))), eps=float(opt.get("eps", 1e-8)),
             weight_decay=float(opt.get("weight_decay", 0.01)), max_grad_norm=float(opt.get("grad_clip", 1.0)),
             timestep_shift=float(config["model"].get("timestep_shift", 5.0)),
@@ -71,7 +72,7 @@ class WanStage0p5Runtime:
             grad_accum=int(train.get("grad_accum", train.get("gradient_accumulation_steps", 1))),
             ema_decay=float(ema["decay"]) if ema.get("enabled") else None,
             checkpointing="full" if (train.get("fsdp", {}) or {}).get("activation_checkpointing") else "none",
-            seed=seed)
+            seed=seed, **dict(extra_options or {}))
         dtype = torch.bfloat16 if self.ctx.device.type == "cuda" else torch.float32
         from ...models.wan import WanDiT
 
@@ -80,7 +81,10 @@ class WanStage0p5Runtime:
         if bool(config["model"].get("nonzero_head_init", False)):
             with torch.no_grad():
                 model.get_parameter("head.head.weight").normal_(0, 0.02)
-        self.trainer = WanStage0p5Trainer(self.arch, self.ctx.device, opts, sp=self.ctx.sp, dtype=dtype, model=model)
+        if trainer_cls is WanStage0p5Trainer:
+            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, dtype=dtype, model=model)
+        else:
+            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, model=model)
         self.trainer.gen.manual_seed(objective_seed(seed, topo.dp_rank))
         self.scheduler = WarmupCosine(self.trainer.optimizer, warmup_steps=int(train.get("warmup_steps", 0)),
                                       total_steps=int(train["max_steps"]),
@@ -210,8 +214,22 @@ class WanStage0p5Runtime:
         dist_init.shutdown(self.ctx)
 
 
-def run_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
-    runtime = WanStage0p5Runtime(config)
+class _TrainingRun:
+    def __init__(self, config, **kw):
+        self.config, self.kw = config, kw
+
+    def run(self):
+        return run_training(self.config, **self.kw)
+
+
+def build_training_run(config: Mapping[str, Any], *, trainer_cls, options_cls, extra_options=None) -> _TrainingRun:
+    """Stage1 / Stage2 reuse the Stage0.5 runtime shell (data, checkpoints, engine hooks) with their own
+    trainer and option classes."""
+    return _TrainingRun(config, trainer_cls=trainer_cls, options_cls=options_cls, extra_options=extra_options)
+
+
+def run_training(config: Mapping[str, Any], **runtime_kw) -> Mapping[str, Any]:
+    runtime = WanStage0p5Runtime(config, **runtime_kw)
     try:
         train, rt = config["train"], config.get("runtime", {})
         max_steps = int(rt.get("max_steps_override") or train["max_steps"])

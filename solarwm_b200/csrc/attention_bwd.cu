@@ -14,7 +14,7 @@
 // kernel and are padded to a multiple of 128 rows (L2 = +large, delta = 0 in the padding), which
 // together with TMA zero-fill removes every boundary mask from the main loops.
 //
-// Roles: warp 0 TMA producer (stationary tiles once, then a 3-deep ring of streamed tile pairs),
+// Roles: warp 0 TMA producer (stationary tiles once, then a 5-deep ring of streamed tile pairs),
 // warp 1 TMEM allocation + every tcgen05.mma, warps 4..7 / 8..11 two compute warpgroups that
 // alternate over streamed tiles (thread = TMEM lane).  The streamed tile in shared memory feeds
 // two different MMAs through two descriptors: K-major as the B operand of the score GEMMs and
@@ -35,7 +35,7 @@ namespace solar {
 constexpr int BW_THREADS = 384;
 constexpr int ST_ROWS = 128;   // stationary tile rows
 constexpr int SR_ROWS = 64;    // streamed tile rows
-constexpr int BW_STAGES = 3;
+constexpr int BW_STAGES = 5;   // TMA latency (~1 us) spans more than one tile-time: prefetch three tiles ahead
 
 struct AttnBwdParams {
   int S_stat, S_stream, H, B;
@@ -44,7 +44,12 @@ struct AttnBwdParams {
   const float* L2;       // [B, H, S_pad]
   const float* delta;    // [B, H, S_pad]
   int* status;
+  long long* trace;      // optional cycle counters of CTA (0,0,0): see solar_attn_bwd_trace
 };
+
+// trace slots (per mode, 8 each): 0 MMA loop cycles, 1 MMA wait strm_full, 2 MMA wait p_ready,
+// 3 compute loop cycles, 4 compute wait s_ready, 5 producer wait strm_empty, 6 tiles
+__device__ long long g_bwd_trace[16];
 
 template <int HD>
 struct BwdSmem {
@@ -116,6 +121,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int n_tiles = (p.S_stream + SR_ROWS - 1) / SR_ROWS;
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   if (threadIdx.x == 0) {
     mbar_init(stat_full, 1);
@@ -155,10 +161,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
         tma_load_4d(smem + L::STAT_OFF + L::STAT_TILE + c * L::STAT_CHUNK, &tmStat1, stat_full, c * 64, head,
                     row0, batch);
       }
+      long long w_empty = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % BW_STAGES;
         const uint32_t ph = (j / BW_STAGES) & 1;
+        const long long c0 = tracing ? clock64() : 0;
         if (!mbar_wait(&strm_empty[s], ph ^ 1, abort_word, ST_TIMEOUT_EMPTY)) break;
+        if (tracing) w_empty += clock64() - c0;
         mbar_expect_tx(&strm_full[s], 2 * L::STRM_TILE);
         uint8_t* base = smem + L::STRM_OFF + s * 2 * L::STRM_TILE;
 #pragma unroll
@@ -168,6 +177,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
                       j * SR_ROWS, batch);
         }
       }
+      if (tracing) p.trace[MODE * 8 + 5] = w_empty;
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
@@ -195,9 +205,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
         }
         umma_commit(&s_ready[b]);
       };
+      long long w_full = 0, w_p = 0;
       auto accumulate = [&](int t) -> bool {
         const int b = t & 1, s = t % BW_STAGES;
+        const long long c0 = tracing ? clock64() : 0;
         if (!mbar_wait(&p_ready[b], (t >> 1) & 1, abort_word, ST_TIMEOUT_OTHER)) return false;
+        if (tracing) w_p += clock64() - c0;
         tc_fence_after();
         const uint32_t s0 = strm + s * 2 * L::STRM_TILE, s1 = s0 + L::STRM_TILE;
         const uint32_t tP = tmem_base + b * 128, tdS = tP + 64;
@@ -220,16 +233,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
         return true;
       };
       bool ok = mbar_wait(stat_full, 0, abort_word, ST_TIMEOUT_FULL);
+      const long long loop0 = tracing ? clock64() : 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % BW_STAGES;
         const uint32_t ph = (j / BW_STAGES) & 1;
+        const long long c0 = tracing ? clock64() : 0;
         if (!mbar_wait(&strm_full[s], ph, abort_word, ST_TIMEOUT_FULL)) { ok = false; break; }
+        if (tracing) w_full += clock64() - c0;
         tc_fence_after();
         score(j & 1, s);
         if (j >= 1) ok = accumulate(j - 1);
       }
       if (ok) ok = accumulate(n_tiles - 1);
       if (ok) umma_commit(acc_done);
+      if (tracing) {
+        p.trace[MODE * 8 + 0] = clock64() - loop0;
+        p.trace[MODE * 8 + 1] = w_full;
+        p.trace[MODE * 8 + 2] = w_p;
+        p.trace[MODE * 8 + 6] = n_tiles;
+      }
     }
   } else if (warp < 4) {
     setmaxnreg_dec<72>();
@@ -248,13 +270,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
       my_delta = p.delta[vec_base + row0 + row];
     }
     bool ok = true;
+    long long w_s = 0;
+    const long long cloop0 = tracing ? clock64() : 0;
     // Both warpgroups work on every streamed tile: warpgroup g owns columns [32g, 32g+32) of the
     // 64-column S / dP tile (elements are independent, so the split needs no exchange); this halves the
     // latency of the compute stage that sits between the score MMAs and the accumulate MMAs.
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
       const uint32_t tS = tmem_base + lane_off + b * 128, tD = tS + 64;
+      const long long c0 = tracing ? clock64() : 0;
       if (!mbar_wait(&s_ready[b], (j >> 1) & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (tracing) w_s += clock64() - c0;
       tc_fence_after();
       uint32_t s[32], d[32];
       tmem_ld_32x32(tS + wg * 32, s);
@@ -296,6 +322,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[b]);
+    }
+    if (tracing && threadIdx.x == 128) {
+      p.trace[MODE * 8 + 3] = clock64() - cloop0;
+      p.trace[MODE * 8 + 4] = w_s;
     }
     // ---- epilogue: accumulators -> bf16 -> shared memory (stationary buffers) -> TMA store
     if (ok) ok = mbar_wait(acc_done, 0, abort_word, ST_TIMEOUT_OTHER);
@@ -401,6 +431,15 @@ static int launch_bwd(const CUtensorMap* maps, const AttnBwdParams& p, cudaStrea
 
 using namespace solar;
 
+static int g_trace_enabled = 0;
+// Profiling aid: with tracing on, CTA (0,0,0) of each backward kernel records cycle counters of its
+// roles (how long each waited on which barrier).  `out16` receives the 16 counters of the last call.
+extern "C" int solar_attn_bwd_trace(int enable, long long* out16) {
+  g_trace_enabled = enable;
+  if (out16 != nullptr) SOLAR_CUDA_OK(cudaMemcpyFromSymbol(out16, g_bwd_trace, 16 * sizeof(long long)));
+  return 0;
+}
+
 // All tensors are [B, S, H, D] bf16 with unit stride on D and stride D on H; *_ss / *_sb are the
 // element strides of the sequence and batch axes.  lse [B,H,Sq] fp32 (natural log, from the
 // forward kernel).  scratch: 2 * B*H*Sq_pad fp32 of caller-provided memory, Sq_pad = Sq rounded
@@ -429,6 +468,8 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
   p.H = H; p.B = B; p.S_pad = Sq_pad;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.L2 = L2; p.delta = delta; p.status = status;
+  p.trace = nullptr;
+  if (g_trace_enabled) SOLAR_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.trace), g_bwd_trace));
   const long long c_ss = static_cast<long long>(H) * D;   // contiguous outputs
   int rc;
   {

@@ -228,7 +228,7 @@ class WanBlock(nn.Module):
             return F_._LinearMainGradFn.apply(x, w, b)
         return F_.gemm(x, w, F_.NT, bias=b)
 
-    def forward(self, x, e0, rope, context, *, B, L, frame_tokens, group_offset=0, sp=None, memo=None):
+    def forward(self, x, e0, rope, context, *, B, L, frame_tokens, group_offset=0, sp=None, memo=None, attn_fn=None):
         """x [B*L_local, dim]; e0 fp32 [G, 6, dim] (G = B * frames); context [B*T, dim]."""
         cfg = self.cfg
         D, H, hd = cfg.dim, cfg.num_heads, cfg.head_dim
@@ -240,7 +240,7 @@ class WanBlock(nn.Module):
         nk = self._norm_kw(x)
         xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
         Ll = x.shape[0] // B
-        fused_sp = bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
+        fused_sp = attn_fn is None and bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
             (not torch.is_grad_enabled() or self.unit.grad is not None)
         if fused_sp:
             # Ulysses exchanges ride on the producing kernels (parallel/fused_ulysses.py)
@@ -259,7 +259,10 @@ class WanBlock(nn.Module):
             v = qkv[:, 2 * D:]
             q, k, v = (t.reshape(B, Ll, H, hd) for t in (q, k, v))
             q, k, v = sp.scatter_heads(q, k, v)
-            o = ops.attention(q, k, v, memo=None if memo is None else (memo, "self"))
+            if attn_fn is not None:     # structured (block-causal / teacher-forcing) self attention
+                o = attn_fn(q, k, v)
+            else:
+                o = ops.attention(q, k, v, memo=None if memo is None else (memo, "self"))
             o = sp.gather_heads(o).reshape(B * Ll, D)
         y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
         x = F_.gated_residual(x, y, mod[:, 2], **gk)

@@ -1,0 +1,129 @@
+"""Teacher-forcing and cache-free sliding-window forwards of the causal Wan DiT.
+
+``forward_teacher_forcing``: one pass over the concatenated ``[clean | noisy]`` token sequence;
+clean frames carry timestep 0, noisy frames their sampled timestep (and AnyFlow target time
+``r``), both halves share RoPE positions, and self-attention follows the block-causal window
+rule of ``teacher_forcing_mask`` (reference: CausalWanModel.forward_train_tf,
+solar/backends/wan22/runtime/modeling/causal_model.py:2093-2345, which builds a FlexAttention
+block mask; here each chunk and role runs one dense attention over its visible key span).
+
+``forward_window``: cache-free inference over ``[history window | current chunk]`` with per-frame
+timesteps and absolute frame positions (reference: forward_inference_window, :2350-2619).
+
+With sequence parallelism the ``2F`` (or window) frames are sharded whole-frame over the ranks and
+the Ulysses exchange hands every rank the full sequence for ``H / P`` heads, so the structured
+attention runs unchanged on the exchanged tensors.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..ops import functional as F_
+from .wan import WanDiT, rope_table
+from .wan_causal import teacher_forcing_attention
+
+
+def block_causal_attention(q, k, v, *, frame_tokens: int, chunk_frames: int, window_chunks: int,
+                           sink_frames: int = 0):
+    """Chunk i attends sink + chunks max(0, i-W) .. i of the same sequence; tensors [1, L, H, D]."""
+    ct = chunk_frames * frame_tokens
+    n = (q.shape[1] + ct - 1) // ct
+    sink = sink_frames * frame_tokens
+    outs = []
+    for i in range(n):
+        lo = max(0, i - window_chunks) * ct
+        hi = min((i + 1) * ct, q.shape[1])
+        if sink and lo > 0:
+            kk = torch.cat([k[:, :sink], k[:, lo:hi]], 1)
+            vv = torch.cat([v[:, :sink], v[:, lo:hi]], 1)
+        else:
+            kk, vv = k[:, lo:hi], v[:, lo:hi]
+        outs.append(ops.attention(q[:, i * ct:hi], kk, vv))
+    return torch.cat(outs, 1)
+
+
+def _run(model: WanDiT, tok, t_frames, r_frames, context, frame_positions, grid_hw, attn_fn, out_frames):
+    """Shared body: tok [F_all*ft, dim] (B = 1), per-frame times, explicit frame positions."""
+    cfg = model.cfg
+    P = model.stem.params
+    h, w = grid_hw
+    ft = h * w
+    f_all = tok.shape[0] // ft
+    e, e0 = model.time_condition(t_frames, r_frames)
+    ctx = model.embed_text(context)
+    sp = model.sp
+    f0, fl = 0, f_all
+    if sp.size > 1:
+        base, rem = divmod(f_all, sp.size)
+        fl = base + int(sp.rank < rem)
+        f0 = sp.rank * base + min(sp.rank, rem)
+        tok = tok[f0 * ft:(f0 + fl) * ft]
+        sp.set_layout(1, f_all, ft)
+    rope = rope_table((fl, h, w), cfg.head_dim, tok.device, frame_positions=frame_positions[f0:f0 + fl])
+    kw = dict(B=1, L=f_all * ft, frame_tokens=ft, group_offset=f0 if sp.size > 1 else 0, sp=sp, attn_fn=attn_fn)
+    xs = tok
+    for bi, block in enumerate(model.blocks):
+        if model.checkpointing != "none" and torch.is_grad_enabled():
+            from torch.utils.checkpoint import checkpoint
+
+            xs = checkpoint(lambda a, b, c, blk=block: blk(a, b, rope, c, **kw), xs, e0, ctx, use_reentrant=False)
+        else:
+            xs = block(xs, e0, rope, ctx, **kw)
+    if sp.size > 1:
+        xs = sp.gather_sequence(xs, 1)
+    lo, hi = out_frames
+    xs = xs[lo * ft:hi * ft]
+    hm = (P["head.modulation"].float().view(1, 2, cfg.dim) + e.float().view(-1, 1, cfg.dim)[lo:hi]).contiguous()
+    xh = F_.norm_modulate(xs, hm[:, 0], hm[:, 1], eps=cfg.eps, rows_per_group=ft, **model.blocks[0]._norm_kw(xs))
+    out = F_.linear(xh, P["head.head.weight"], P["head.head.bias"])
+    return model.unpatchify(out, 1, (hi - lo, h, w))
+
+
+def _embed(model: WanDiT, x):
+    rows, grid = model.patchify(x.to(model.dtype))
+    pw = model.stem.params["patch_embedding.weight"]
+    return F_.linear(rows, pw.view(pw.shape[0], -1), model.stem.params["patch_embedding.bias"]), grid
+
+
+def forward_teacher_forcing(model: WanDiT, clean, noisy, t, context, *, r: Optional[torch.Tensor] = None,
+                            chunk_frames: int = 3, window_chunks: int = 6, sink_frames: int = 0):
+    """clean / noisy [1, C, F, H, W]; t (and r) [1, F] on the 1000-step grid; returns the prediction
+    for the noisy half [1, C_out, F, H, W]."""
+    if clean.shape[0] != 1:
+        raise ValueError("teacher forcing packs one video per call")
+    tok_c, grid = _embed(model, clean)
+    tok_n, _ = _embed(model, noisy)
+    f, h, w = grid
+    ft = h * w
+    zeros = torch.zeros_like(t)
+    t_all = torch.cat([zeros, t], dim=1)
+    r_all = None if r is None else torch.cat([zeros, r], dim=1)
+    pos = torch.arange(f).repeat(2)
+
+    def attn(q, k, v):
+        L = f * ft
+        oc, on = teacher_forcing_attention(q[:, :L], k[:, :L], v[:, :L], q[:, L:], k[:, L:], v[:, L:],
+                                           frame_tokens=ft, chunk_frames=chunk_frames,
+                                           window_chunks=window_chunks, sink_frames=sink_frames)
+        return torch.cat([oc, on], 1)
+
+    return _run(model, torch.cat([tok_c, tok_n], 0), t_all, r_all, context, pos, (h, w), attn, (f, 2 * f))
+
+
+def forward_window(model: WanDiT, frames, t, context, *, first_frame: int, current_frames: int,
+                   chunk_frames: int = 3, window_chunks: int = 6, r: Optional[torch.Tensor] = None):
+    """frames [1, C, Fw, H, W] = clean history followed by the current noisy chunk; t [1, Fw] (0 on the
+    history); ``first_frame`` = absolute index of the window's first frame.  Returns the prediction for
+    the last ``current_frames`` frames."""
+    tok, grid = _embed(model, frames)
+    f, h, w = grid
+    pos = torch.arange(f) + int(first_frame)
+
+    def attn(q, k, v):
+        return block_causal_attention(q, k, v, frame_tokens=h * w, chunk_frames=chunk_frames,
+                                      window_chunks=window_chunks)
+
+    return _run(model, tok, t, r, context, pos, (h, w), attn, (f - current_frames, f))

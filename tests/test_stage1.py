@@ -1,0 +1,83 @@
+"""Teacher-forcing forward and Stage1 trainers (CPU, fp32 oracle path)."""
+import torch
+
+from solarwm_b200.models.wan import WanConfig, WanDiT
+from solarwm_b200.models.wan_causal import teacher_forcing_mask
+from solarwm_b200.models import wan_tf
+from solarwm_b200.ops import reference as R
+
+
+def tiny():
+    cfg = WanConfig(model_type="ti2v", in_dim=4, out_dim=4, dim=64, ffn_dim=128, num_heads=2, num_layers=2,
+                    text_dim=32, text_len=8, freq_dim=32)
+    m = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05)
+    return cfg, m
+
+
+def test_teacher_forcing_matches_dense_mask(monkeypatch):
+    cfg, m = tiny()
+    F, H, W = 4, 4, 4
+    g = torch.Generator().manual_seed(0)
+    clean = torch.randn(1, 4, F, H, W, generator=g)
+    noisy = torch.randn(1, 4, F, H, W, generator=g)
+    t = torch.tensor([[700.0, 700.0, 300.0, 300.0]])
+    ctx = torch.randn(1, 8, 32, generator=g)
+    out = wan_tf.forward_teacher_forcing(m, clean, noisy, t, ctx, chunk_frames=2, window_chunks=1)
+    ft = (H // 2) * (W // 2)
+    mask = teacher_forcing_mask(F, ft, 2, 1)
+
+    def dense(qc, kc, vc, qn, kn, vn, **kw):
+        q, k, v = torch.cat([qc, qn], 1), torch.cat([kc, kn], 1), torch.cat([vc, vn], 1)
+        o = R.attention(q, k, v, mask=mask.view(1, 1, *mask.shape))
+        L = qc.shape[1]
+        return o[:, :L], o[:, L:]
+
+    monkeypatch.setattr(wan_tf, "teacher_forcing_attention", dense)
+    ref = wan_tf.forward_teacher_forcing(m, clean, noisy, t, ctx, chunk_frames=2, window_chunks=1)
+    assert out.shape == (1, 4, F, H, W)
+    assert torch.allclose(out, ref, atol=1e-5, rtol=1e-4)
+
+
+def test_first_chunk_equals_plain_forward():
+    cfg, m = tiny()
+    g = torch.Generator().manual_seed(1)
+    clean = torch.randn(1, 4, 4, 4, 4, generator=g)
+    noisy = torch.randn(1, 4, 4, 4, 4, generator=g)
+    t = torch.tensor([[500.0, 500.0, 200.0, 200.0]])
+    ctx = torch.randn(1, 8, 32, generator=g)
+    out = wan_tf.forward_teacher_forcing(m, clean, noisy, t, ctx, chunk_frames=2, window_chunks=3)
+    plain = m(noisy[:, :, :2], t[:, :2], ctx)
+    assert torch.allclose(out[:, :, :2], plain, atol=1e-5, rtol=1e-4)
+
+
+def test_window_forward_matches_teacher_forcing_last_chunk():
+    cfg, m = tiny()
+    g = torch.Generator().manual_seed(2)
+    clean = torch.randn(1, 4, 4, 4, 4, generator=g)
+    noisy = torch.randn(1, 4, 4, 4, 4, generator=g)
+    t = torch.tensor([[500.0, 500.0, 200.0, 200.0]])
+    ctx = torch.randn(1, 8, 32, generator=g)
+    tf = wan_tf.forward_teacher_forcing(m, clean, noisy, t, ctx, chunk_frames=2, window_chunks=3)
+    frames = torch.cat([clean[:, :, :2], noisy[:, :, 2:]], dim=2)
+    tw = torch.tensor([[0.0, 0.0, 200.0, 200.0]])
+    win = wan_tf.forward_window(m, frames, tw, ctx, first_frame=0, current_frames=2, chunk_frames=2, window_chunks=3)
+    assert torch.allclose(win, tf[:, :, 2:], atol=1e-5, rtol=1e-4)
+
+
+def test_stage1_trainers_step():
+    from solarwm_b200.backends.wan22.stage1 import Stage1Options, WanStage1Trainer
+
+    cfg, m = tiny()
+    for objective in ("tf_fm", "anyflow"):
+        tr = WanStage1Trainer(cfg, "cpu", Stage1Options(objective=objective, chunk_frames=2, window_chunks=2, lr=1e-3,
+                                                        diffusion_ratio=0.34, consistency_ratio=0.33),
+                              model=WanDiT(cfg, device="cpu", dtype=torch.float32, seed=0))
+        with torch.no_grad():
+            tr.model.get_parameter("head.head.weight").normal_(0, 0.05)
+        before = tr.model.get_parameter("blocks.0.ffn.0.weight").detach().clone()
+        batch = {"latents": torch.randn(1, 6, 4, 4, 4), "text": torch.randn(1, 8, 32)}
+        loss = tr.train_step(batch)
+        assert torch.isfinite(loss)
+        assert not torch.equal(before, tr.model.get_parameter("blocks.0.ffn.0.weight"))
