@@ -1,0 +1,115 @@
+"""Wan pre-encoding: raw clips + captions -> latent / text-embedding shards.
+
+Commit-last corpus assembly: every shard is written under a temporary name and published
+create-only, the encoder contract next, and the index last; a crashed run leaves no index, and a
+rerun refuses to overwrite published shards.  Ranks split the work by ``ordinal % world`` and write
+disjoint shard prefixes; rank 0 merges the per-rank indices after a collective error exchange
+(reference: solar/backends/wan22/runtime/preencode.py:277-699, solar/preencode/shards.py).
+
+Sources: ``preencode.source: synthetic`` (deterministic random clips; used by tests and smoke runs)
+or ``index`` (rows of a raw dataset index whose members are ``.npy`` videos ``[T, H, W, 3]`` uint8 and a
+caption; decoding of compressed video is the data plane's job and not repeated here).
+"""
+from __future__ import annotations
+
+import io
+from pathlib import Path
+from typing import Any, Iterator, Mapping, Tuple
+
+import numpy as np
+import torch
+
+from ...data.index import read_index, write_index
+from ...errors import BackendContractError
+from ...models.t5 import T5Config, WanTextEncoder
+from ...models.vae import VAEConfig, VideoVAE
+from ...preencode.contracts import wan_contract
+from ...preencode.shards import EncodedShardWriter
+from .contracts import PROFILES
+
+
+def _clips(config: Mapping[str, Any], rank: int, world: int) -> Iterator[Tuple[str, torch.Tensor, str]]:
+    pre = config["preencode"]
+    data = config["data"]
+    T, H, W = int(data["pixel_frames"]), int(data["pixel_height"]), int(data["pixel_width"])
+    if str(pre.get("source", "synthetic")) == "synthetic":
+        n = int(pre.get("num_samples", 4))
+        for i in range(rank, n, world):
+            g = torch.Generator().manual_seed(int(data.get("seed", 0)) * 7919 + i)
+            yield f"synthetic-{i:06d}", torch.rand(3, T, H, W, generator=g) * 2 - 1, f"synthetic clip {i}"
+        return
+    from ...data.archive import TarShardReader
+
+    root = Path(pre["raw_root"])
+    reader = TarShardReader()
+    try:
+        for row in read_index(pre["raw_index"]):
+            if row.ordinal % world != rank:
+                continue
+            members = row.values.get("members", {})
+            got = reader.read_members(root / row.shard, [members["video"], members["caption"]])
+            vid = np.load(io.BytesIO(got[members["video"]]), allow_pickle=False)
+            if vid.ndim != 4 or vid.shape[-1] != 3 or vid.shape[0] < T:
+                raise BackendContractError(f"{row.sample_id}: video must be [T>={T}, H, W, 3] uint8")
+            clip = torch.from_numpy(vid[:T]).permute(3, 0, 1, 2).float() / 127.5 - 1.0
+            if clip.shape[2:] != (H, W):
+                clip = torch.nn.functional.interpolate(clip.permute(1, 0, 2, 3), size=(H, W), mode="bilinear",
+                                                       align_corners=False).permute(1, 0, 2, 3)
+            yield row.sample_id, clip, got[members["caption"]].decode("utf-8").strip()
+    finally:
+        reader.close()
+
+
+def run_preencode(config: Mapping[str, Any], family: str) -> Mapping[str, Any]:
+    import torch.distributed as dist
+
+    from ...runtime import distributed as rdist
+
+    prof = PROFILES[family]
+    pre, data = config["preencode"], config["data"]
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    device = torch.device(str(config.get("runtime", {}).get("device", "cpu")).replace("auto", "cuda" if torch.cuda.is_available() else "cpu"))
+    dtype = torch.bfloat16
+    codecs = pre.get("codecs", {}) or {}
+    vcfg = VAEConfig(z_dim=int(codecs.get("z_dim", prof.latent_channels)), base=int(codecs.get("vae_base", 16)))
+    tcfg = T5Config(**codecs["t5"]) if "t5" in codecs else T5Config.tiny()
+    vae = VideoVAE(vcfg).to(device=device, dtype=torch.float32).eval()
+    text = WanTextEncoder(tcfg, device=device, dtype=torch.float32)
+    if codecs.get("vae_checkpoint"):
+        vae.load_state_dict(torch.load(codecs["vae_checkpoint"], map_location=device, weights_only=True))
+    if codecs.get("t5_checkpoint"):
+        text.model.load_state_dict(torch.load(codecs["t5_checkpoint"], map_location=device, weights_only=True))
+    t_stride = 2 ** sum(vcfg.temporal_ups)
+    s_stride = 2 ** len(vcfg.temporal_ups)
+    contract = wan_contract(family, pixel_frames=int(data["pixel_frames"]), height=int(data["pixel_height"]),
+                            width=int(data["pixel_width"]), z_dim=vcfg.z_dim, text_len=tcfg.text_len,
+                            text_dim=tcfg.dim, temporal_stride=t_stride, spatial_stride=s_stride,
+                            video_codec=str(codecs.get("video_codec", "causal-vae-random-init")),
+                            text_codec=str(codecs.get("text_codec", "t5-random-init")))
+    out = Path(pre["output_root"])
+    writer = EncodedShardWriter(out, contract, samples_per_shard=int(pre.get("samples_per_shard", 64)),
+                                prefix=f"encoded-r{rank:03d}")
+    error = None
+    try:
+        for sample_id, clip, caption in _clips(config, rank, world):
+            with torch.no_grad():
+                z = vae.encode(clip.unsqueeze(0).to(device))[0].permute(1, 0, 2, 3)      # [F, z, h, w]
+                e = text([caption])[0]
+            writer.add(sample_id, {"latents": z.to(dtype).cpu(), "text": e.to(dtype).cpu()}, {"caption": caption})
+        index = writer.finish(index_name=f"index-r{rank:03d}.jsonl") if writer.rows or writer._pending else None
+    except Exception as exc:  # noqa: BLE001 - exchanged so that every rank fails together
+        error, index = exc, None
+    rdist.propagate_collective_error(None if error is None else f"{type(error).__name__}: {error}",
+                                     dist=dist if world > 1 else None, label="wan preencode")
+    if world > 1:
+        dist.barrier()
+    total = 0
+    if rank == 0:
+        rows = []
+        for r in range(world):
+            part = out / f"index-r{r:03d}.jsonl"
+            if part.exists():
+                rows.extend(dict(x.values) for x in read_index(part))
+        total = write_index(out / "index.jsonl", rows)     # the corpus index is the last file written
+    return {"samples": total, "contract_digest": contract.digest, "output_root": str(out)}

@@ -1,0 +1,279 @@
+"""Wan Stage2: self-gradient forcing (distribution-matching distillation of a few-step causal student).
+
+Three networks share one architecture:
+  * **student** (trainable, block-causal): rolls a video out chunk by chunk with its own KV cache;
+  * **teacher** (frozen, bidirectional): the "real" score, evaluated with classifier-free guidance;
+  * **critic** (trainable, bidirectional): the "fake" score, trained by flow matching on the
+    student's samples.
+
+One outer step (``train_outer_step``):
+  1. ``rollout``: no-grad chunked rollout through the denoising grid with the rolling KV cache; a
+     random exit index (shared by all chunks and SP ranks) picks the step whose input the gradient
+     pass will see; every chunk is committed clean to the cache.
+  2. one gradient pass: teacher-forcing replay of the whole clip, ``[generated clean | re-noised at
+     the exit step]`` -> student x0 ``out``.
+  3. critic update (every step): flow matching on ``add_noise(out.detach(), t')``.
+  4. student update (every ``critic_updates_per_student``-th step): ``g = (fake_x0 - real_x0) /
+     mean|out - real_x0|`` and the surrogate ``0.5 ||out - (out - g).detach()||^2``.
+
+Reference: stage2_camera_rollout, _stage2_self_forcing_latents and Wan5BStage2Runtime.train_outer_step
+(solar/backends/wan22/runtime/stage2.py:408-771, 2055), solar/training/sgf.py:9-78.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Mapping, Optional, Sequence
+
+import torch
+
+from ... import ops
+from ...engine.flow import FlowMatchScheduler
+from ...engine.optim import FlatAdamW
+from ...engine.sgf import sgf_kl_gradient, sgf_student_loss, should_update_student
+from ...models.wan import WanConfig, WanDiT
+from ...models.wan_causal import CausalWanRunner, allocate_kv_cache
+from ...models.wan_tf import forward_teacher_forcing
+
+
+@dataclass
+class Stage2Options:
+    lr_student: float = 2e-6
+    lr_critic: float = 4e-7
+    betas: tuple = (0.0, 0.999)
+    weight_decay: float = 0.01
+    max_grad_norm: Optional[float] = 10.0
+    timestep_shift: float = 5.0
+    denoising_steps: Sequence[float] = (1000.0, 750.0, 500.0, 250.0)
+    chunk_frames: int = 3
+    window_chunks: int = 6
+    sink_frames: int = 0
+    critic_updates_per_student: int = 5
+    guidance_scale: float = 3.0
+    min_score_t: float = 20.0
+    max_score_t: float = 980.0
+    checkpointing: str = "none"
+    seed: int = 0
+
+
+def _to_bcfhw(x):
+    return x.permute(0, 2, 1, 3, 4)
+
+
+class WanStage2Trainer:
+    def __init__(self, cfg: WanConfig, device, opts: Stage2Options = Stage2Options(), sp=None,
+                 dtype=torch.bfloat16, student: Optional[WanDiT] = None, teacher: Optional[WanDiT] = None,
+                 critic: Optional[WanDiT] = None):
+        self.cfg, self.opts, self.device = cfg, opts, torch.device(device)
+        self.sp = sp
+        self.sp_size = 1 if sp is None else sp.size
+        mk = lambda seed: WanDiT(cfg, device=device, dtype=dtype, seed=seed)   # noqa: E731
+        self.student = student or mk(opts.seed)
+        self.teacher = teacher or mk(opts.seed)
+        self.critic = critic or mk(opts.seed)
+        for m in (self.student, self.teacher, self.critic):
+            if sp is not None:
+                m.sp = sp
+            m.checkpointing = opts.checkpointing
+        for p in self.teacher.parameters():
+            p.requires_grad_(False)
+        self.student.ensure_grads()
+        self.critic.ensure_grads()
+        kw = dict(betas=opts.betas, eps=1e-8, weight_decay=opts.weight_decay)
+        self.opt_student = FlatAdamW(self.student.units(), lr=opts.lr_student, **kw)
+        self.opt_critic = FlatAdamW(self.critic.units(), lr=opts.lr_critic, **kw)
+        self.scheduler = FlowMatchScheduler(shift=opts.timestep_shift)
+        self.gen = torch.Generator(device=self.device).manual_seed(opts.seed * 100003 + 7)
+        self.global_step = 0
+
+    # ------------------------------------------------------------------------------------
+    def _sigma(self, t):
+        return (torch.as_tensor(t, device=self.device, dtype=torch.float32) / self.scheduler.num_train_timesteps)
+
+    def _add_noise(self, x0, noise, t_frames):
+        """x0 / noise [1, F, C, H, W], t_frames [F] -> x_t [1, F, C, H, W]."""
+        x_t, _ = ops.add_noise(x0[0].contiguous(), noise[0].contiguous(), self._sigma(t_frames))
+        return x_t.unsqueeze(0)
+
+    def _x0(self, x_t, v, t_frames):
+        return ops.flow_to_x0(x_t[0].contiguous(), v[0].contiguous(), self._sigma(t_frames)).unsqueeze(0)
+
+    def _randn(self, shape, dtype):
+        return torch.randn(shape, generator=self.gen, device=self.device, dtype=torch.float32).to(dtype)
+
+    # ------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def rollout(self, text, shape, dtype, exit_index: Optional[int] = None):
+        """Chunked no-grad rollout.  Returns (generated x0 [1,F,C,H,W], exit timestep, exit_index)."""
+        o = self.opts
+        _, F, C, H, W = shape
+        steps = list(o.denoising_steps)
+        if exit_index is None:
+            idx = torch.randint(0, len(steps), (1,), generator=self.gen, device=self.device)
+            if self.sp is not None and self.sp.size > 1:
+                self.sp.broadcast_(idx)
+            exit_index = int(idx.item())
+        runner = CausalWanRunner(self.student, sp=None)
+        ph, pw = self.cfg.patch_size[1], self.cfg.patch_size[2]
+        cache = allocate_kv_cache(self.student, grid_hw=(H // ph, W // pw), chunk_frames=o.chunk_frames,
+                                  window_frames=o.window_chunks * o.chunk_frames + o.sink_frames,
+                                  sink_frames=o.sink_frames, device=self.device)
+        runner.encode_text(cache, text)
+        outs = []
+        for f0 in range(0, F, o.chunk_frames):
+            f = min(o.chunk_frames, F - f0)
+            x = self._randn((1, f, C, H, W), dtype)
+            x0 = x
+            for si, t in enumerate(steps):
+                tt = torch.full((1, f), float(t), device=self.device)
+                v = runner.forward_chunk(cache, _to_bcfhw(x), tt, commit=False)
+                x0 = self._x0(x, _to_bcfhw(v), tt[0])
+                if si + 1 < len(steps):
+                    x = self._add_noise(x0, self._randn(x0.shape, dtype), torch.full((f,), float(steps[si + 1])))
+            runner.forward_chunk(cache, _to_bcfhw(x0), torch.zeros((1, f), device=self.device), commit=True)
+            outs.append(x0)
+        return torch.cat(outs, dim=1), float(steps[exit_index]), exit_index
+
+    def student_replay(self, generated, text, exit_t: float):
+        """One gradient pass over the clip: the student denoises ``generated`` re-noised at ``exit_t`` while
+        attending to the clean ``generated`` history.  Returns x0 [1,F,C,H,W] with grad."""
+        o = self.opts
+        F = generated.shape[1]
+        t = torch.full((F,), float(exit_t), device=self.device)
+        noisy = self._add_noise(generated, self._randn(generated.shape, generated.dtype), t)
+        v = forward_teacher_forcing(self.student, _to_bcfhw(generated), _to_bcfhw(noisy), t.view(1, F), text,
+                                    chunk_frames=o.chunk_frames, window_chunks=o.window_chunks,
+                                    sink_frames=o.sink_frames)
+        v = _to_bcfhw(v)
+        sig = self._sigma(t).view(1, F, 1, 1, 1)
+        return (noisy.float() - sig * v.float())
+
+    def _score_x0(self, model, x_t, t_frames, text, null_text=None, scale: float = 1.0):
+        F = x_t.shape[1]
+        tt = t_frames.view(1, F)
+        v = model(_to_bcfhw(x_t), tt, text)
+        if null_text is not None and scale != 1.0:
+            vu = model(_to_bcfhw(x_t), tt, null_text)
+            v = vu + scale * (v - vu)
+        sig = self._sigma(t_frames).view(1, F, 1, 1, 1)
+        return x_t.float() - sig * _to_bcfhw(v).float()
+
+    def _apply(self, model, opt):
+        model.finalize_grads()
+        if self.sp is not None and self.sp.size > 1:
+            self.sp.sum_gradients_([g for u in model.units() for g in (u.grad, u.grad_v)])
+        norm = opt.local_grad_sumsq().sqrt()
+        opt.set_clip(norm, self.opts.max_grad_norm)
+        opt.step()
+        model.zero_grads()
+        return norm
+
+    def train_outer_step(self, batch: Mapping[str, Any]):
+        """batch: ``latents`` (shape/dtype template only; SGF trains data-free), ``text`` and optional
+        ``null_text`` [1, T, text_dim].  Returns a dict of scalar losses."""
+        o = self.opts
+        dev = self.device
+        lat = batch["latents"].to(dev, non_blocking=True)
+        text = batch["text"].to(dev, non_blocking=True)
+        null = batch.get("null_text")
+        null = torch.zeros_like(text) if null is None else null.to(dev, non_blocking=True)
+        F = lat.shape[1]
+        generated, exit_t, _ = self.rollout(text, lat.shape, lat.dtype)
+        update_student = should_update_student(self.global_step, o.critic_updates_per_student)
+        result = {}
+        with torch.set_grad_enabled(update_student):
+            out = self.student_replay(generated, text, exit_t)                      # fp32 [1,F,C,H,W]
+        # one score timestep per clip, shared by both score networks and by the SP group
+        u = torch.rand(1, generator=self.gen, device=dev)
+        if self.sp is not None and self.sp.size > 1:
+            self.sp.broadcast_(u)
+        t_score = (o.min_score_t + (o.max_score_t - o.min_score_t) * u).expand(F).contiguous()
+        noise = self._randn(out.shape, lat.dtype)
+        if update_student:
+            x_t = self._add_noise(out.detach().to(lat.dtype), noise, t_score)
+            with torch.no_grad():
+                real = self._score_x0(self.teacher, x_t, t_score, text, null, o.guidance_scale)
+                fake = self._score_x0(self.critic, x_t, t_score, text)
+            g = sgf_kl_gradient(fake_x0=fake, real_x0=real, student_output=out.detach())
+            loss_s = sgf_student_loss(out, g)
+            (loss_s / self.sp_size).backward()
+            result["student"] = float(loss_s.detach())
+            result["student_grad_norm"] = float(self._apply(self.student, self.opt_student))
+        # critic: flow matching on the student's sample
+        x0 = out.detach().to(lat.dtype)
+        u2 = torch.rand(1, generator=self.gen, device=dev)
+        if self.sp is not None and self.sp.size > 1:
+            self.sp.broadcast_(u2)
+        t_c = (o.min_score_t + (o.max_score_t - o.min_score_t) * u2).expand(F).contiguous()
+        noise_c = self._randn(out.shape, lat.dtype)
+        x_tc, target = ops.add_noise(x0[0].contiguous(), noise_c[0].contiguous(), self._sigma(t_c))
+        pred = self.critic(_to_bcfhw(x_tc.unsqueeze(0)), t_c.view(1, F), text)
+        pred = _to_bcfhw(pred)[0].contiguous()
+        loss_c = ops.weighted_masked_mse(pred, target[:, :pred.shape[1]].contiguous(),
+                                         torch.ones(F, device=dev), torch.ones(F, device=dev))
+        (loss_c / self.sp_size).backward()
+        result["critic"] = float(loss_c.detach())
+        result["critic_grad_norm"] = float(self._apply(self.critic, self.opt_critic))
+        self.global_step += 1
+        return result
+
+    # -- role checkpoints ------------------------------------------------------------------
+    def role_state(self) -> Mapping[str, Any]:
+        return {"student": self.student.state_dict(), "critic": self.critic.state_dict(),
+                "opt_student": self.opt_student.state_dict(), "opt_critic": self.opt_critic.state_dict(),
+                "global_step": self.global_step, "objective_gen": self.gen.get_state().cpu()}
+
+    def load_role_state(self, state: Mapping[str, Any]) -> None:
+        self.student.load_state_dict(state["student"])
+        self.critic.load_state_dict(state["critic"])
+        self.opt_student.load_state_dict(state["opt_student"])
+        self.opt_critic.load_state_dict(state["opt_critic"])
+        self.global_step = int(state["global_step"])
+        self.gen.set_state(state["objective_gen"])
+
+
+def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
+    """Config-driven entry: synthetic prompts (or the configured reader), ``max_steps`` outer steps, role
+    checkpoints through the transactional store."""
+    from ...checkpoint.store import CheckpointTransaction
+    from ...config.routes import validate_route
+    from ...parallel import dist_init
+    from ...runtime.output_layout import checkpoint_model_dir, output_root
+    from .checkpoint import build_contract
+    from .contracts import architecture
+    from .runtime import synthetic_batches
+
+    dist_cfg = config.get("distributed", {}) or {}
+    ctx = dist_init.initialize(int(dist_cfg.get("sequence_parallel_size", 1)),
+                               device=str(config.get("runtime", {}).get("device", "auto")))
+    try:
+        arch = architecture(config)
+        train = config["train"]
+        causal = config["model"].get("causal", {}) or {}
+        opts = Stage2Options(
+            lr_student=float((train.get("optimizer", {}) or {}).get("lr", 2e-6)),
+            lr_critic=float((train.get("critic_optimizer", {}) or {}).get("lr", 4e-7)),
+            timestep_shift=float(config["model"].get("timestep_shift", 5.0)),
+            denoising_steps=tuple(train.get("denoising_steps", (1000.0, 750.0, 500.0, 250.0))),
+            chunk_frames=int(causal.get("chunk_frames", 3)), window_chunks=int(causal.get("window_chunks", 6)),
+            sink_frames=int(causal.get("sink_frames", 0)),
+            critic_updates_per_student=int(train.get("critic_updates_per_student", 5)),
+            guidance_scale=float(train.get("guidance_scale", 3.0)), seed=int(config["data"].get("seed", 0)))
+        dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
+        trainer = WanStage2Trainer(arch, ctx.device, opts, sp=ctx.sp, dtype=dtype)
+        batches = synthetic_batches(config, arch, ctx.device)
+        max_steps = int(config.get("runtime", {}).get("max_steps_override") or train["max_steps"])
+        last = {}
+        for _ in range(max_steps):
+            last = trainer.train_outer_step(next(batches))
+        ident = None
+        if ctx.topology.is_main and int(config.get("runtime", {}).get("save_every", 0)) > 0:
+            target = checkpoint_model_dir(output_root(config), trainer.global_step)
+            with CheckpointTransaction(target) as tx:
+                torch.save(dict(trainer.role_state()), tx.path / "role.pt")
+                done = tx.commit(step=trainer.global_step,
+                                 contract=build_contract(config, validate_route(config), ctx.topology.sp_size),
+                                 required_components=("role.pt",), metadata={"roles": ["student", "critic"]})
+            ident = done.manifest_digest
+        return {"final_step": trainer.global_step, "losses": last, "checkpoint": ident}
+    finally:
+        dist_init.shutdown(ctx)

@@ -14,16 +14,24 @@
 // kernel and are padded to a multiple of 128 rows (L2 = +large, delta = 0 in the padding), which
 // together with TMA zero-fill removes every boundary mask from the main loops.
 //
-// Roles: warp 0 TMA producer (stationary tiles once, then a 5-deep ring of streamed tile pairs),
-// warp 1 TMEM allocation + every tcgen05.mma, warps 4..7 / 8..11 two compute warpgroups that
-// alternate over streamed tiles (thread = TMEM lane).  The streamed tile in shared memory feeds
-// two different MMAs through two descriptors: K-major as the B operand of the score GEMMs and
-// MN-major as the B operand of the accumulate GEMMs.  P^T / dS are written back to TMEM as packed
-// bf16 over columns [0,16) and [32,48) of the S / dP tiles (each compute warpgroup overwrites columns
-// it consumed itself) and read from there as the A operand of the accumulate MMAs.
+// Roles: warp 0 TMA producer (a 5-deep ring of streamed tile pairs), warp 1 TMEM allocation + every
+// tcgen05.mma, warps 4..7 / 8..11 two compute warpgroups (thread = TMEM lane; warpgroup g owns columns
+// [32g, 32g+32) of every 64-column S / dP tile).
 //
-// TMEM columns: buf0 {S [0,64) dP [64,128)}  buf1 {S [128,192) dP [192,256)}  acc0 [256,384)
-// acc1 [384,512).  Every wait is bounded (sm100.cuh).
+// The stationary rows never touch shared memory: the compute warps read them from global memory once
+// and store them in TMEM as packed bf16 (64 columns per tensor), where they serve as the A operand of
+// the score MMAs.  An MMA whose A operand comes from shared memory re-reads 4 KiB of A per
+// instruction, which made the [128 x 64 x 16] score MMAs operand-fetch bound (measured ~84 cycles
+// each against 32 cycles of math); from TMEM only the 2 KiB B slice is fetched.  The streamed tile in
+// shared memory feeds two MMAs through two descriptors: K-major as B of the score GEMMs and MN-major
+// as B of the accumulate GEMMs.  P^T / dS are written back to TMEM as packed bf16 over columns
+// [32g, 32g+16) of the S / dP tiles and read from there as the A operand of the accumulate MMAs.
+//
+// TMEM columns: stat0 [0,64) stat1 [64,128);
+//   dQ mode:     buf0 {S [128,192) dP [192,256)}  buf1 {S [256,320) dP [320,384)}  dQ [384,512)
+//   dK/dV mode:  S [128,192)  dP [192,256)  dV [256,384)  dK [384,512); with single tiles the tensor
+//                pipe is kept busy by the order  S_j dP_j dV_j S_j+1 dK_j dP_j+1 ...
+// Every wait is bounded (sm100.cuh).
 //
 // Replaces the flash_attn / cuDNN SDPA backward used by the reference
 // (solar/backends/wan22/runtime/modeling/attention.py:98-135, solar/backends/minimax_h3/fast_attention.py:103).
@@ -44,6 +52,8 @@ struct AttnBwdParams {
   const float* L2;       // [B, H, S_pad]
   const float* delta;    // [B, H, S_pad]
   int* status;
+  const __nv_bfloat16* stat0; long long stat0_ss, stat0_sb;   // stationary tensors (element strides)
+  const __nv_bfloat16* stat1; long long stat1_ss, stat1_sb;
   long long* trace;      // optional cycle counters of CTA (0,0,0): see solar_attn_bwd_trace
 };
 
@@ -97,8 +107,7 @@ __device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint8_t* region, int
 // MODE 0 = dK/dV, MODE 1 = dQ.
 template <int HD, int MODE>
 __global__ void __launch_bounds__(BW_THREADS, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_constant__ CUtensorMap tmStat1,
-                const __grid_constant__ CUtensorMap tmStrm0, const __grid_constant__ CUtensorMap tmStrm1,
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_constant__ CUtensorMap tmStrm1,
                 const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
                 const AttnBwdParams p) {
   using L = BwdSmem<HD>;
@@ -106,12 +115,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* stat_full = bars;                        // 1
+  uint64_t* stat_ready = bars;                       // 1 (256 arrivals)
   uint64_t* strm_full = bars + 1;                    // BW_STAGES
   uint64_t* strm_empty = strm_full + BW_STAGES;      // BW_STAGES
   uint64_t* s_ready = strm_empty + BW_STAGES;        // 2
-  uint64_t* p_ready = s_ready + 2;                   // 2
-  uint64_t* acc_done = p_ready + 2;                  // 1
+  uint64_t* p_ready = s_ready + 2;                   // 2 (256 arrivals)
+  uint64_t* dp_ready = p_ready + 2;                  // 1 (dK/dV mode)
+  uint64_t* ds_ready = dp_ready + 1;                 // 1 (dK/dV mode, 256 arrivals)
+  uint64_t* acc_done = ds_ready + 1;                 // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -124,7 +135,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
   const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   if (threadIdx.x == 0) {
-    mbar_init(stat_full, 1);
+    mbar_init(stat_ready, 256);
     for (int s = 0; s < BW_STAGES; ++s) {
       mbar_init(&strm_full[s], 1);
       mbar_init(&strm_empty[s], 1);
@@ -133,11 +144,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
       mbar_init(&s_ready[b], 1);
       mbar_init(&p_ready[b], 256);   // both compute warpgroups arrive
     }
+    mbar_init(dp_ready, 1);
+    mbar_init(ds_ready, 256);
     mbar_init(acc_done, 1);
     *abort_word = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tmStat0);
-    tma_prefetch_desc(&tmStat1);
     tma_prefetch_desc(&tmStrm0);
     tma_prefetch_desc(&tmStrm1);
   }
@@ -148,19 +159,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base_v = *tmem_slot;
+  const uint32_t tmem_base = tmem_base_v;
+  // TMEM columns of the working tiles (see the header comment)
+  constexpr uint32_t COL_STAT1 = 64;
+  constexpr uint32_t COL_BUF = 128;                       // S at +0, dP at +64 (second buffer +128 in dQ mode)
+  constexpr uint32_t COL_ACC0 = MODE == 0 ? 256 : 384;    // dV or dQ
+  constexpr uint32_t COL_ACC1 = 384;                      // dK
 
   if (warp == 0) {
-    // -------------------------------------------------------------- TMA producer
+    // -------------------------------------------------------------- TMA producer (streamed ring)
     setmaxnreg_dec<72>();
     if (lane == 0) {
-      mbar_expect_tx(stat_full, 2 * L::STAT_TILE);
-#pragma unroll
-      for (int c = 0; c < L::CHUNKS; ++c) {
-        tma_load_4d(smem + L::STAT_OFF + c * L::STAT_CHUNK, &tmStat0, stat_full, c * 64, head, row0, batch);
-        tma_load_4d(smem + L::STAT_OFF + L::STAT_TILE + c * L::STAT_CHUNK, &tmStat1, stat_full, c * 64, head,
-                    row0, batch);
-      }
       long long w_empty = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % BW_STAGES;
@@ -181,72 +191,113 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
+    // The whole warp runs the loop so that addresses and descriptors stay warp-uniform; one elected
+    // lane issues each tcgen05 instruction.
     setmaxnreg_dec<72>();
-    if (lane == 0) {
+    {
+      const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_v, 0);
       constexpr uint32_t idesc_score = umma_idesc_bf16(128, SR_ROWS, 0, 0);   // [128 x 64], K = HD
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);          // [128 x HD], K = 64, B MN-major
-      const uint32_t stat0 = smem_u32(smem + L::STAT_OFF);
-      const uint32_t stat1 = stat0 + L::STAT_TILE;
-      const uint32_t strm = smem_u32(smem + L::STRM_OFF);
-      auto score = [&](int b, int s) {
-        const uint32_t s0 = strm + s * 2 * L::STRM_TILE, s1 = s0 + L::STRM_TILE;
-        const uint32_t tS = tmem_base + b * 128, tD = tS + 64;
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t oa = (kk / 4) * L::STAT_CHUNK + (kk % 4) * 32;
-          const uint32_t ob = (kk / 4) * L::STRM_CHUNK + (kk % 4) * 32;
-          umma_ss(tS, umma_desc_kmajor(stat0 + oa), umma_desc_kmajor(s0 + ob), idesc_score, kk != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t oa = (kk / 4) * L::STAT_CHUNK + (kk % 4) * 32;
-          const uint32_t ob = (kk / 4) * L::STRM_CHUNK + (kk % 4) * 32;
-          umma_ss(tD, umma_desc_kmajor(stat1 + oa), umma_desc_kmajor(s1 + ob), idesc_score, kk != 0);
-        }
-        umma_commit(&s_ready[b]);
-      };
+      const uint32_t strm = __shfl_sync(0xffffffffu, smem_u32(smem + L::STRM_OFF), 0);
       long long w_full = 0, w_p = 0;
-      auto accumulate = [&](int t) -> bool {
-        const int b = t & 1, s = t % BW_STAGES;
-        const long long c0 = tracing ? clock64() : 0;
-        if (!mbar_wait(&p_ready[b], (t >> 1) & 1, abort_word, ST_TIMEOUT_OTHER)) return false;
-        if (tracing) w_p += clock64() - c0;
-        tc_fence_after();
-        const uint32_t s0 = strm + s * 2 * L::STRM_TILE, s1 = s0 + L::STRM_TILE;
-        const uint32_t tP = tmem_base + b * 128, tdS = tP + 64;
-        if (MODE == 0) {
-#pragma unroll
-          for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dV += P^T dO_i
-            umma_ts(tmem_base + 256, tP + (kk / 2) * 32 + (kk % 2) * 8, umma_desc_mnmajor(s1 + kk * 2048, L::STRM_CHUNK), idesc_acc,
-                    (t | kk) != 0);
-#pragma unroll
-          for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dK += dS^T Q_i
-            umma_ts(tmem_base + 384, tdS + (kk / 2) * 32 + (kk % 2) * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
-                    (t | kk) != 0);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < SR_ROWS / 16; ++kk)   // dQ += dS K_j
-            umma_ts(tmem_base + 256, tdS + (kk / 2) * 32 + (kk % 2) * 8, umma_desc_mnmajor(s0 + kk * 2048, L::STRM_CHUNK), idesc_acc,
-                    (t | kk) != 0);
-        }
-        umma_commit(&strm_empty[s]);
-        return true;
+      // warp-wide wait: every lane polls, the verdict is made uniform so the lanes never part ways
+      auto wwait = [&](uint64_t* bar, uint32_t parity, volatile int* aw, int code) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, aw, code));
       };
-      bool ok = mbar_wait(stat_full, 0, abort_word, ST_TIMEOUT_FULL);
+      // score GEMM: A = stationary rows held in TMEM (packed bf16, 8 columns per K step of 16),
+      // B = streamed tile (K-major in shared memory)
+      auto score_mma = [&](uint32_t t_dst, uint32_t t_stat, uint32_t s_tile) {
+        // one descriptor per tile; a K step moves the 14-bit start-address field by a constant
+        const uint64_t d0 = umma_desc_kmajor(s_tile);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t ob = (kk / 4) * L::STRM_CHUNK + (kk % 4) * 32;
+          if (elect_one()) umma_ts(t_dst, t_stat + kk * 8, d0 + (ob >> 4), idesc_score, kk != 0);
+        }
+      };
+      // accumulate GEMM: A = packed P / dS in TMEM (two 16-column groups, one per compute warpgroup),
+      // B = streamed tile read MN-major
+      auto acc_mma = [&](uint32_t t_dst, uint32_t t_a, uint32_t s_tile, int t) {
+        const uint64_t d0 = umma_desc_mnmajor(s_tile, L::STRM_CHUNK);
+#pragma unroll
+        for (int kk = 0; kk < SR_ROWS / 16; ++kk)
+          if (elect_one())
+            umma_ts(t_dst, t_a + (kk / 2) * 32 + (kk % 2) * 8, d0 + ((kk * 2048) >> 4), idesc_acc, (t | kk) != 0);
+      };
+      bool ok = wwait(stat_ready, 0, abort_word, ST_TIMEOUT_FULL);
+      tc_fence_after();
       const long long loop0 = tracing ? clock64() : 0;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % BW_STAGES;
-        const uint32_t ph = (j / BW_STAGES) & 1;
-        const long long c0 = tracing ? clock64() : 0;
-        if (!mbar_wait(&strm_full[s], ph, abort_word, ST_TIMEOUT_FULL)) { ok = false; break; }
-        if (tracing) w_full += clock64() - c0;
-        tc_fence_after();
-        score(j & 1, s);
-        if (j >= 1) ok = accumulate(j - 1);
+      if (MODE == 1) {
+        // dQ: two S/dP buffers; the score MMAs of tile j+1 overlap the compute stage of tile j
+        auto accumulate = [&](int t) -> bool {
+          const int b = t & 1, s = t % BW_STAGES;
+          const long long c0 = tracing ? clock64() : 0;
+          if (!wwait(&p_ready[b], (t >> 1) & 1, abort_word, ST_TIMEOUT_OTHER)) return false;
+          if (tracing) w_p += clock64() - c0;
+          tc_fence_after();
+          acc_mma(tmem_base + COL_ACC0, tmem_base + COL_BUF + b * 128 + 64, strm + s * 2 * L::STRM_TILE, t);
+          if (elect_one()) umma_commit(&strm_empty[s]);
+          return true;
+        };
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const int s = j % BW_STAGES, b = j & 1;
+          const uint32_t ph = (j / BW_STAGES) & 1;
+          const long long c0 = tracing ? clock64() : 0;
+          if (!wwait(&strm_full[s], ph, abort_word, ST_TIMEOUT_FULL)) { ok = false; break; }
+          if (tracing) w_full += clock64() - c0;
+          tc_fence_after();
+          const uint32_t s0 = strm + s * 2 * L::STRM_TILE;
+          score_mma(tmem_base + COL_BUF + b * 128, tmem_base, s0);
+          score_mma(tmem_base + COL_BUF + b * 128 + 64, tmem_base + COL_STAT1, s0 + L::STRM_TILE);
+          if (elect_one()) umma_commit(&s_ready[b]);
+          if (j >= 1) ok = accumulate(j - 1);
+        }
+        if (ok) ok = accumulate(n_tiles - 1);
+      } else {
+        // dK/dV: one S and one dP tile; the tensor pipe runs  S_j  dP_j  dV_j  S_j+1  dK_j  dP_j+1 ...
+        // so that S_j+1 / dP_j+1 execute while the compute warpgroups turn dP_j / S_j+1 into dS_j / P_j+1.
+        const uint32_t tS = tmem_base + COL_BUF, tD = tS + 64;
+        auto wait_full = [&](int j) -> bool {
+          const long long c0 = tracing ? clock64() : 0;
+          const bool r = wwait(&strm_full[j % BW_STAGES], (j / BW_STAGES) & 1, abort_word, ST_TIMEOUT_FULL);
+          if (tracing) w_full += clock64() - c0;
+          tc_fence_after();
+          return r;
+        };
+        if (ok) ok = wait_full(0);
+        if (ok) {
+          score_mma(tS, tmem_base, strm);
+          if (elect_one()) umma_commit(&s_ready[0]);
+          score_mma(tD, tmem_base + COL_STAT1, strm + L::STRM_TILE);
+          if (elect_one()) umma_commit(dp_ready);
+        }
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const int s = j % BW_STAGES, sn = (j + 1) % BW_STAGES;
+          const uint32_t s0 = strm + s * 2 * L::STRM_TILE, n0 = strm + sn * 2 * L::STRM_TILE;
+          long long c0 = tracing ? clock64() : 0;
+          if (!wwait(&p_ready[0], j & 1, abort_word, ST_TIMEOUT_OTHER)) { ok = false; break; }
+          if (tracing) w_p += clock64() - c0;
+          tc_fence_after();
+          acc_mma(tmem_base + COL_ACC0, tS, s0 + L::STRM_TILE, j);          // dV += P^T dO_j
+          if (j + 1 < n_tiles) {
+            if (!wait_full(j + 1)) { ok = false; break; }
+            score_mma(tS, tmem_base, n0);                                    // S_j+1 (after dV_j in pipe order)
+            if (elect_one()) umma_commit(&s_ready[0]);
+          }
+          c0 = tracing ? clock64() : 0;
+          if (!wwait(ds_ready, j & 1, abort_word, ST_TIMEOUT_OTHER)) { ok = false; break; }
+          if (tracing) w_p += clock64() - c0;
+          tc_fence_after();
+          acc_mma(tmem_base + COL_ACC1, tD, s0, j);                          // dK += dS^T Q_j
+          if (elect_one()) umma_commit(&strm_empty[s]);
+          if (j + 1 < n_tiles) {
+            score_mma(tD, tmem_base + COL_STAT1, n0 + L::STRM_TILE);         // dP_j+1 (after dK_j)
+            if (elect_one()) umma_commit(dp_ready);
+          }
+        }
       }
-      if (ok) ok = accumulate(n_tiles - 1);
-      if (ok) umma_commit(acc_done);
-      if (tracing) {
+      if (ok && elect_one()) umma_commit(acc_done);
+      if (tracing && lane == 0) {
         p.trace[MODE * 8 + 0] = clock64() - loop0;
         p.trace[MODE * 8 + 1] = w_full;
         p.trace[MODE * 8 + 2] = w_p;
@@ -264,6 +315,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const long long vec_base = (static_cast<long long>(batch) * p.H + head) * p.S_pad;
     const float c = p.scale_log2, sc = p.scale;
+    // ---- stationary rows: global -> registers -> TMEM as packed bf16 (warpgroup g loads tensor g).
+    // Rows past the end are zero; their results are never stored.
+    {
+      const __nv_bfloat16* src = wg == 0 ? p.stat0 : p.stat1;
+      const long long ss = wg == 0 ? p.stat0_ss : p.stat1_ss, sb = wg == 0 ? p.stat0_sb : p.stat1_sb;
+      const int grow = row0 + row;
+      const uint4* g4 = reinterpret_cast<const uint4*>(src + batch * sb + static_cast<long long>(grow) * ss +
+                                                       static_cast<long long>(head) * HD);
+#pragma unroll
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t r[16];
+        if (grow < p.S_stat) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint4 v4 = __ldg(g4 + cc * 4 + q4);
+            r[q4 * 4 + 0] = v4.x; r[q4 * 4 + 1] = v4.y; r[q4 * 4 + 2] = v4.z; r[q4 * 4 + 3] = v4.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = 0u;
+        }
+        tmem_st_32x16(tmem_base + lane_off + wg * COL_STAT1 + cc * 16, r);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(stat_ready);
+    }
     float my_L2 = 0.f, my_delta = 0.f;
     if (MODE == 1) {
       my_L2 = p.L2[vec_base + row0 + row];
@@ -272,21 +350,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
     bool ok = true;
     long long w_s = 0;
     const long long cloop0 = tracing ? clock64() : 0;
+    const float2 c2 = make_float2(c, c), sc2 = make_float2(sc, sc);
     // Both warpgroups work on every streamed tile: warpgroup g owns columns [32g, 32g+32) of the
-    // 64-column S / dP tile (elements are independent, so the split needs no exchange); this halves the
-    // latency of the compute stage that sits between the score MMAs and the accumulate MMAs.
+    // 64-column S / dP tile and writes its packed bf16 results over columns [32g, 32g+16).
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1;
-      const uint32_t tS = tmem_base + lane_off + b * 128, tD = tS + 64;
-      const long long c0 = tracing ? clock64() : 0;
-      if (!mbar_wait(&s_ready[b], (j >> 1) & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      const int b = MODE == 1 ? (j & 1) : 0;
+      const uint32_t par = MODE == 1 ? ((j >> 1) & 1) : (j & 1);
+      const uint32_t tS = tmem_base + lane_off + COL_BUF + b * 128 + wg * 32, tD = tS + 64;
+      long long c0 = tracing ? clock64() : 0;
+      if (!mbar_wait(&s_ready[b], par, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       if (tracing) w_s += clock64() - c0;
       tc_fence_after();
       uint32_t s[32], d[32];
-      tmem_ld_32x32(tS + wg * 32, s);
-      tmem_ld_32x32(tD + wg * 32, d);
+      tmem_ld_32x32(tS, s);
+      if (MODE == 1) tmem_ld_32x32(tD, d);
       tmem_ld_wait();
-      const float2 c2 = make_float2(c, c), sc2 = make_float2(sc, sc);
       const float4* l4 = nullptr;
       const float4* d4 = nullptr;
       if (MODE == 0) {
@@ -294,47 +372,73 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
         d4 = reinterpret_cast<const float4*>(p.delta + vec_base + j * SR_ROWS + wg * 32);
       }
       uint32_t pk[16], dk[16];
+      // P = exp2(S * c - L2); kept as fp32 in s[] for the dS product
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
-        float2 nL[2], Dl[2];
+        float2 nL[2];
         if (MODE == 0) {
-          const float4 a = __ldg(l4 + g), bb = __ldg(d4 + g);
+          const float4 a = __ldg(l4 + g);
           nL[0] = make_float2(-a.x, -a.y); nL[1] = make_float2(-a.z, -a.w);
-          Dl[0] = make_float2(bb.x, bb.y); Dl[1] = make_float2(bb.z, bb.w);
         } else {
           nL[0] = nL[1] = make_float2(-my_L2, -my_L2);
-          Dl[0] = Dl[1] = make_float2(my_delta, my_delta);
         }
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
           const int e = g * 4 + h2 * 2;
           const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2, nL[h2]);
           const float2 pv = make_float2(exp2_fast(tt.x), exp2_fast(tt.y));
+          s[e] = __float_as_uint(pv.x); s[e + 1] = __float_as_uint(pv.y);
+          pk[e >> 1] = pack_bf16x2(pv.x, pv.y);
+        }
+      }
+      if (MODE == 0) {
+        tmem_st_32x16(tS, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_ready[0]);
+        c0 = tracing ? clock64() : 0;
+        if (!mbar_wait(dp_ready, par, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (tracing) w_s += clock64() - c0;
+        tc_fence_after();
+        tmem_ld_32x32(tD, d);
+        tmem_ld_wait();
+      }
+      // dS = P * (dP - delta) * scale
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        float2 Dl[2];
+        if (MODE == 0) {
+          const float4 bb = __ldg(d4 + g);
+          Dl[0] = make_float2(bb.x, bb.y); Dl[1] = make_float2(bb.z, bb.w);
+        } else {
+          Dl[0] = Dl[1] = make_float2(my_delta, my_delta);
+        }
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int e = g * 4 + h2 * 2;
+          const float2 pv = make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1]));
           float2 dd = make_float2(__uint_as_float(d[e]) - Dl[h2].x, __uint_as_float(d[e + 1]) - Dl[h2].y);
           dd = __fmul2_rn(__fmul2_rn(pv, dd), sc2);
-          pk[e >> 1] = pack_bf16x2(pv.x, pv.y);
           dk[e >> 1] = pack_bf16x2(dd.x, dd.y);
         }
       }
-      // each warpgroup writes its packed results over columns it has itself consumed: [32g, 32g+16)
-      if (MODE == 0) tmem_st_32x16(tS + wg * 32, pk);
-      tmem_st_32x16(tD + wg * 32, dk);
+      tmem_st_32x16(tD, dk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_ready[b]);
+      mbar_arrive(MODE == 0 ? ds_ready : &p_ready[b]);
     }
     if (tracing && threadIdx.x == 128) {
       p.trace[MODE * 8 + 3] = clock64() - cloop0;
       p.trace[MODE * 8 + 4] = w_s;
     }
-    // ---- epilogue: accumulators -> bf16 -> shared memory (stationary buffers) -> TMA store
+    // ---- epilogue: accumulators -> bf16 -> shared memory staging -> TMA store
     if (ok) ok = mbar_wait(acc_done, 0, abort_word, ST_TIMEOUT_OTHER);
     if (ok) {
       tc_fence_after();
       if (MODE == 0) {
         // warpgroup 0 drains dV (acc0), warpgroup 1 drains dK (acc1)
         uint8_t* region = smem + L::STAT_OFF + wg * L::STAT_TILE;
-        acc_to_smem<HD>(tmem_base + lane_off + 256 + wg * 128, region, L::STAT_CHUNK, row);
+        acc_to_smem<HD>(tmem_base + lane_off + (wg == 0 ? COL_ACC0 : COL_ACC1), region, L::STAT_CHUNK, row);
         fence_proxy_async_smem();
         named_bar_sync(1 + wg, 128);
         if (quarter == 0 && lane == 0) {
@@ -349,7 +453,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat0, const __grid_consta
         // dQ (acc0): each warpgroup drains one 64-column chunk
         if (wg < L::CHUNKS) {
           uint8_t* region = smem + L::STAT_OFF + wg * L::STAT_CHUNK;
-          acc_to_smem<64>(tmem_base + lane_off + 256 + wg * 64, region, L::STAT_CHUNK, row);
+          acc_to_smem<64>(tmem_base + lane_off + COL_ACC0 + wg * 64, region, L::STAT_CHUNK, row);
           fence_proxy_async_smem();
           named_bar_sync(1 + wg, 128);
           if (quarter == 0 && lane == 0) {
@@ -422,7 +526,7 @@ static int launch_bwd(const CUtensorMap* maps, const AttnBwdParams& p, cudaStrea
     configured = true;
   }
   dim3 grid((p.S_stat + ST_ROWS - 1) / ST_ROWS, p.H, p.B);
-  kern<<<grid, BW_THREADS, BwdSmem<HD>::TOTAL, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  kern<<<grid, BW_THREADS, BwdSmem<HD>::TOTAL, st>>>(maps[2], maps[3], maps[4], maps[5], p);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -475,8 +579,8 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
   {
     // dK / dV: stationary K, V (128-row boxes); streamed Q, dO (64-row boxes)
     CUtensorMap m[6];
-    if ((rc = bshd_map(&m[0], k, B, Sk, H, D, k_ss, k_sb, ST_ROWS))) return rc;
-    if ((rc = bshd_map(&m[1], v, B, Sk, H, D, v_ss, v_sb, ST_ROWS))) return rc;
+    p.stat0 = (const __nv_bfloat16*)k; p.stat0_ss = k_ss; p.stat0_sb = k_sb;
+    p.stat1 = (const __nv_bfloat16*)v; p.stat1_ss = v_ss; p.stat1_sb = v_sb;
     if ((rc = bshd_map(&m[2], q, B, Sq, H, D, q_ss, q_sb, SR_ROWS))) return rc;
     if ((rc = bshd_map(&m[3], dout, B, Sq, H, D, do_ss, do_sb, SR_ROWS))) return rc;
     if ((rc = bshd_map(&m[4], dv, B, Sk, H, D, c_ss, c_ss * Sk, ST_ROWS))) return rc;
@@ -488,8 +592,8 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
   {
     // dQ: stationary Q, dO; streamed K, V
     CUtensorMap m[6];
-    if ((rc = bshd_map(&m[0], q, B, Sq, H, D, q_ss, q_sb, ST_ROWS))) return rc;
-    if ((rc = bshd_map(&m[1], dout, B, Sq, H, D, do_ss, do_sb, ST_ROWS))) return rc;
+    p.stat0 = (const __nv_bfloat16*)q; p.stat0_ss = q_ss; p.stat0_sb = q_sb;
+    p.stat1 = (const __nv_bfloat16*)dout; p.stat1_ss = do_ss; p.stat1_sb = do_sb;
     if ((rc = bshd_map(&m[2], k, B, Sk, H, D, k_ss, k_sb, SR_ROWS))) return rc;
     if ((rc = bshd_map(&m[3], v, B, Sk, H, D, v_ss, v_sb, SR_ROWS))) return rc;
     if ((rc = bshd_map(&m[4], dq, B, Sq, H, D, c_ss, c_ss * Sq, ST_ROWS))) return rc;

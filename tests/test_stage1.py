@@ -81,3 +81,30 @@ def test_stage1_trainers_step():
         loss = tr.train_step(batch)
         assert torch.isfinite(loss)
         assert not torch.equal(before, tr.model.get_parameter("blocks.0.ffn.0.weight"))
+
+
+def test_stage2_outer_steps_and_role_state():
+    from solarwm_b200.backends.wan22.stage2 import Stage2Options, WanStage2Trainer
+
+    cfg, _ = tiny()
+    tr = WanStage2Trainer(cfg, "cpu", Stage2Options(chunk_frames=2, window_chunks=2, critic_updates_per_student=2,
+                                                    denoising_steps=(1000.0, 500.0)), dtype=torch.float32)
+    for m in (tr.student, tr.teacher, tr.critic):
+        with torch.no_grad():
+            m.get_parameter("head.head.weight").normal_(0, 0.05)
+    batch = {"latents": torch.randn(1, 4, 4, 4, 4), "text": torch.randn(1, 8, 32)}
+    teacher_before = tr.teacher.get_parameter("blocks.0.ffn.0.weight").detach().clone()
+    student_before = tr.student.get_parameter("blocks.0.ffn.0.weight").detach().clone()
+    r0 = tr.train_outer_step(batch)
+    assert "critic" in r0 and "student" not in r0            # step 0 trains the critic only
+    assert torch.equal(student_before, tr.student.get_parameter("blocks.0.ffn.0.weight"))
+    tr.train_outer_step(batch)
+    r2 = tr.train_outer_step(batch)                           # step 2: student too
+    assert "student" in r2 and r2["student"] == r2["student"]
+    assert not torch.equal(student_before, tr.student.get_parameter("blocks.0.ffn.0.weight"))
+    assert torch.equal(teacher_before, tr.teacher.get_parameter("blocks.0.ffn.0.weight"))
+    state = tr.role_state()
+    tr2 = WanStage2Trainer(cfg, "cpu", tr.opts, dtype=torch.float32)
+    tr2.load_role_state(state)
+    assert tr2.global_step == 3
+    assert torch.equal(tr2.student.get_parameter("blocks.0.ffn.0.weight"), tr.student.get_parameter("blocks.0.ffn.0.weight"))
