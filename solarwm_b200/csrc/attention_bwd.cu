@@ -14,8 +14,8 @@
 // kernel and are padded to a multiple of 128 rows (L2 = +large, delta = 0 in the padding), which
 // together with TMA zero-fill removes every boundary mask from the main loops.
 //
-// Roles: warp 0 TMA producer (a 5-deep ring of streamed tile pairs), warp 1 TMEM allocation + every
-// tcgen05.mma, warps 4..7 / 8..11 two compute warpgroups (thread = TMEM lane; warpgroup g owns columns
+// Roles: warp 0 TMA producer (a 5-deep ring of streamed tile pairs), warp 1 TMEM allocation + the score
+// MMAs, warp 2 the accumulate MMAs, warps 4..7 / 8..11 two compute warpgroups (thread = TMEM lane; warpgroup g owns columns
 // [32g, 32g+32) of every 64-column S / dP tile).
 //
 // The stationary rows never touch shared memory: the compute warps read them from global memory once
@@ -29,8 +29,8 @@
 //
 // TMEM columns: stat0 [0,64) stat1 [64,128);
 //   dQ mode:     buf0 {S [128,192) dP [192,256)}  buf1 {S [256,320) dP [320,384)}  dQ [384,512)
-//   dK/dV mode:  S [128,192)  dP [192,256)  dV [256,384)  dK [384,512); with single tiles the tensor
-//                pipe is kept busy by the order  S_j dP_j dV_j S_j+1 dK_j dP_j+1 ...
+//   dK/dV mode:  S [128,192)  dP [192,256)  dV [256,384)  dK [384,512); with single tiles the chains
+//                S_j -> P_j -> dV_j -> S_j+1  and  dP_j -> dS_j -> dK_j -> dP_j+1  run side by side
 // Every wait is bounded (sm100.cuh).
 //
 // Replaces the flash_attn / cuDNN SDPA backward used by the reference
@@ -57,8 +57,9 @@ struct AttnBwdParams {
   long long* trace;      // optional cycle counters of CTA (0,0,0): see solar_attn_bwd_trace
 };
 
-// trace slots (per mode, 8 each): 0 MMA loop cycles, 1 MMA wait strm_full, 2 MMA wait p_ready,
-// 3 compute loop cycles, 4 compute wait s_ready, 5 producer wait strm_empty, 6 tiles
+// trace slots (per mode, 8 each): 0 score-warp loop cycles, 1 score-warp wait strm_full, 2 score-warp
+// wait s_free/dp_free, 3 compute loop cycles, 4 compute waits, 5 producer wait strm_empty, 6 tiles,
+// 7 accumulate-warp wait p_ready/ds_ready
 __device__ long long g_bwd_trace[16];
 
 template <int HD>
@@ -122,7 +123,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
   uint64_t* p_ready = s_ready + 2;                   // 2 (256 arrivals)
   uint64_t* dp_ready = p_ready + 2;                  // 1 (dK/dV mode)
   uint64_t* ds_ready = dp_ready + 1;                 // 1 (dK/dV mode, 256 arrivals)
-  uint64_t* acc_done = ds_ready + 1;                 // 1
+  uint64_t* s_free = ds_ready + 1;                   // 2 (commit of the accumulate warp)
+  uint64_t* dp_free = s_free + 2;                    // 1 (dK/dV mode)
+  uint64_t* acc_done = dp_free + 1;                  // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -146,6 +149,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     }
     mbar_init(dp_ready, 1);
     mbar_init(ds_ready, 256);
+    mbar_init(&s_free[0], 1);
+    mbar_init(&s_free[1], 1);
+    mbar_init(dp_free, 1);
     mbar_init(acc_done, 1);
     *abort_word = 0;
     mbar_fence_init();
@@ -190,24 +196,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       if (tracing) p.trace[MODE * 8 + 5] = w_empty;
     }
   } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issuer
-    // The whole warp runs the loop so that addresses and descriptors stay warp-uniform; one elected
-    // lane issues each tcgen05 instruction.
+    // -------------------------------------------------------------- score MMA warp
+    // Two warps issue tcgen05.mma: warp 1 the score GEMMs (S, dP), warp 2 the accumulate GEMMs, so a
+    // wait of one never delays the other's issue; every cross-warp dependency is an mbarrier fed by
+    // tcgen05.commit.  The whole warp runs the loop so that addresses and descriptors stay
+    // warp-uniform; one elected lane issues each tcgen05 instruction.
     setmaxnreg_dec<72>();
     {
       const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_v, 0);
       constexpr uint32_t idesc_score = umma_idesc_bf16(128, SR_ROWS, 0, 0);   // [128 x 64], K = HD
-      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);          // [128 x HD], K = 64, B MN-major
       const uint32_t strm = __shfl_sync(0xffffffffu, smem_u32(smem + L::STRM_OFF), 0);
-      long long w_full = 0, w_p = 0;
-      // warp-wide wait: every lane polls, the verdict is made uniform so the lanes never part ways
-      auto wwait = [&](uint64_t* bar, uint32_t parity, volatile int* aw, int code) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity, aw, code));
+      long long w_full = 0, w_free = 0;
+      auto wwait = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_word, code));
       };
-      // score GEMM: A = stationary rows held in TMEM (packed bf16, 8 columns per K step of 16),
+      // A = stationary rows held in TMEM (packed bf16, 8 columns per K step of 16),
       // B = streamed tile (K-major in shared memory)
       auto score_mma = [&](uint32_t t_dst, uint32_t t_stat, uint32_t s_tile) {
-        // one descriptor per tile; a K step moves the 14-bit start-address field by a constant
         const uint64_t d0 = umma_desc_kmajor(s_tile);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
@@ -215,7 +220,52 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
           if (elect_one()) umma_ts(t_dst, t_stat + kk * 8, d0 + (ob >> 4), idesc_score, kk != 0);
         }
       };
-      // accumulate GEMM: A = packed P / dS in TMEM (two 16-column groups, one per compute warpgroup),
+      bool ok = wwait(stat_ready, 0, ST_TIMEOUT_FULL);
+      tc_fence_after();
+      const long long loop0 = tracing ? clock64() : 0;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % BW_STAGES;
+        const int b = MODE == 1 ? (j & 1) : 0;
+        const uint32_t free_par = (MODE == 1 ? ((j >> 1) & 1) : (j & 1)) ^ 1;
+        const uint32_t s0 = strm + s * 2 * L::STRM_TILE;
+        const uint32_t tS = tmem_base + COL_BUF + b * 128, tD = tS + 64;
+        long long c0 = tracing ? clock64() : 0;
+        if (!wwait(&strm_full[s], (j / BW_STAGES) & 1, ST_TIMEOUT_FULL)) { ok = false; break; }
+        if (tracing) w_full += clock64() - c0;
+        c0 = tracing ? clock64() : 0;
+        if (!wwait(&s_free[b], free_par, ST_TIMEOUT_OTHER)) { ok = false; break; }   // readers of the old S / P are done
+        if (tracing) w_free += clock64() - c0;
+        tc_fence_after();
+        score_mma(tS, tmem_base, s0);
+        if (MODE == 0) {
+          if (elect_one()) umma_commit(&s_ready[0]);
+          c0 = tracing ? clock64() : 0;
+          if (!wwait(dp_free, free_par, ST_TIMEOUT_OTHER)) { ok = false; break; }      // readers of the old dP / dS are done
+          if (tracing) w_free += clock64() - c0;
+          tc_fence_after();
+        }
+        score_mma(tD, tmem_base + COL_STAT1, s0 + L::STRM_TILE);
+        if (elect_one()) umma_commit(MODE == 0 ? dp_ready : &s_ready[b]);
+      }
+      if (tracing && lane == 0) {
+        p.trace[MODE * 8 + 0] = clock64() - loop0;
+        p.trace[MODE * 8 + 1] = w_full;
+        p.trace[MODE * 8 + 2] = w_free;
+        p.trace[MODE * 8 + 6] = n_tiles;
+      }
+    }
+  } else if (warp == 2) {
+    // -------------------------------------------------------------- accumulate MMA warp
+    setmaxnreg_dec<72>();
+    {
+      const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_v, 0);
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);          // [128 x HD], K = 64, B MN-major
+      const uint32_t strm = __shfl_sync(0xffffffffu, smem_u32(smem + L::STRM_OFF), 0);
+      long long w_p = 0;
+      auto wwait = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_word, code));
+      };
+      // A = packed P / dS in TMEM (two 16-column groups, one per compute warpgroup),
       // B = streamed tile read MN-major
       auto acc_mma = [&](uint32_t t_dst, uint32_t t_a, uint32_t s_tile, int t) {
         const uint64_t d0 = umma_desc_mnmajor(s_tile, L::STRM_CHUNK);
@@ -224,87 +274,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
           if (elect_one())
             umma_ts(t_dst, t_a + (kk / 2) * 32 + (kk % 2) * 8, d0 + ((kk * 2048) >> 4), idesc_acc, (t | kk) != 0);
       };
-      bool ok = wwait(stat_ready, 0, abort_word, ST_TIMEOUT_FULL);
-      tc_fence_after();
-      const long long loop0 = tracing ? clock64() : 0;
-      if (MODE == 1) {
-        // dQ: two S/dP buffers; the score MMAs of tile j+1 overlap the compute stage of tile j
-        auto accumulate = [&](int t) -> bool {
-          const int b = t & 1, s = t % BW_STAGES;
-          const long long c0 = tracing ? clock64() : 0;
-          if (!wwait(&p_ready[b], (t >> 1) & 1, abort_word, ST_TIMEOUT_OTHER)) return false;
-          if (tracing) w_p += clock64() - c0;
-          tc_fence_after();
-          acc_mma(tmem_base + COL_ACC0, tmem_base + COL_BUF + b * 128 + 64, strm + s * 2 * L::STRM_TILE, t);
-          if (elect_one()) umma_commit(&strm_empty[s]);
-          return true;
-        };
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          const int s = j % BW_STAGES, b = j & 1;
-          const uint32_t ph = (j / BW_STAGES) & 1;
-          const long long c0 = tracing ? clock64() : 0;
-          if (!wwait(&strm_full[s], ph, abort_word, ST_TIMEOUT_FULL)) { ok = false; break; }
-          if (tracing) w_full += clock64() - c0;
-          tc_fence_after();
-          const uint32_t s0 = strm + s * 2 * L::STRM_TILE;
-          score_mma(tmem_base + COL_BUF + b * 128, tmem_base, s0);
-          score_mma(tmem_base + COL_BUF + b * 128 + 64, tmem_base + COL_STAT1, s0 + L::STRM_TILE);
-          if (elect_one()) umma_commit(&s_ready[b]);
-          if (j >= 1) ok = accumulate(j - 1);
-        }
-        if (ok) ok = accumulate(n_tiles - 1);
-      } else {
-        // dK/dV: one S and one dP tile; the tensor pipe runs  S_j  dP_j  dV_j  S_j+1  dK_j  dP_j+1 ...
-        // so that S_j+1 / dP_j+1 execute while the compute warpgroups turn dP_j / S_j+1 into dS_j / P_j+1.
-        const uint32_t tS = tmem_base + COL_BUF, tD = tS + 64;
-        auto wait_full = [&](int j) -> bool {
-          const long long c0 = tracing ? clock64() : 0;
-          const bool r = wwait(&strm_full[j % BW_STAGES], (j / BW_STAGES) & 1, abort_word, ST_TIMEOUT_FULL);
-          if (tracing) w_full += clock64() - c0;
-          tc_fence_after();
-          return r;
-        };
-        if (ok) ok = wait_full(0);
-        if (ok) {
-          score_mma(tS, tmem_base, strm);
-          if (elect_one()) umma_commit(&s_ready[0]);
-          score_mma(tD, tmem_base + COL_STAT1, strm + L::STRM_TILE);
-          if (elect_one()) umma_commit(dp_ready);
-        }
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          const int s = j % BW_STAGES, sn = (j + 1) % BW_STAGES;
-          const uint32_t s0 = strm + s * 2 * L::STRM_TILE, n0 = strm + sn * 2 * L::STRM_TILE;
-          long long c0 = tracing ? clock64() : 0;
-          if (!wwait(&p_ready[0], j & 1, abort_word, ST_TIMEOUT_OTHER)) { ok = false; break; }
-          if (tracing) w_p += clock64() - c0;
-          tc_fence_after();
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % BW_STAGES;
+        const int b = MODE == 1 ? (j & 1) : 0;
+        const uint32_t par = MODE == 1 ? ((j >> 1) & 1) : (j & 1);
+        const uint32_t s0 = strm + s * 2 * L::STRM_TILE;
+        const uint32_t tS = tmem_base + COL_BUF + b * 128, tD = tS + 64;
+        // the stage was filled before the score MMAs ran; observing its barrier orders this warp after the copy
+        if (!wwait(&strm_full[s], (j / BW_STAGES) & 1, ST_TIMEOUT_FULL)) { ok = false; break; }
+        long long c0 = tracing ? clock64() : 0;
+        if (!wwait(&p_ready[b], par, ST_TIMEOUT_OTHER)) { ok = false; break; }
+        if (tracing) w_p += clock64() - c0;
+        tc_fence_after();
+        if (MODE == 0) {
           acc_mma(tmem_base + COL_ACC0, tS, s0 + L::STRM_TILE, j);          // dV += P^T dO_j
-          if (j + 1 < n_tiles) {
-            if (!wait_full(j + 1)) { ok = false; break; }
-            score_mma(tS, tmem_base, n0);                                    // S_j+1 (after dV_j in pipe order)
-            if (elect_one()) umma_commit(&s_ready[0]);
-          }
+          if (elect_one()) umma_commit(&s_free[0]);
           c0 = tracing ? clock64() : 0;
-          if (!wwait(ds_ready, j & 1, abort_word, ST_TIMEOUT_OTHER)) { ok = false; break; }
+          if (!wwait(ds_ready, par, ST_TIMEOUT_OTHER)) { ok = false; break; }
           if (tracing) w_p += clock64() - c0;
           tc_fence_after();
           acc_mma(tmem_base + COL_ACC1, tD, s0, j);                          // dK += dS^T Q_j
-          if (elect_one()) umma_commit(&strm_empty[s]);
-          if (j + 1 < n_tiles) {
-            score_mma(tD, tmem_base + COL_STAT1, n0 + L::STRM_TILE);         // dP_j+1 (after dK_j)
-            if (elect_one()) umma_commit(dp_ready);
-          }
+          if (elect_one()) umma_commit(dp_free);
+        } else {
+          acc_mma(tmem_base + COL_ACC0, tD, s0, j);                          // dQ += dS K_j
+          if (elect_one()) umma_commit(&s_free[b]);
         }
+        if (elect_one()) umma_commit(&strm_empty[s]);
       }
       if (ok && elect_one()) umma_commit(acc_done);
-      if (tracing && lane == 0) {
-        p.trace[MODE * 8 + 0] = clock64() - loop0;
-        p.trace[MODE * 8 + 1] = w_full;
-        p.trace[MODE * 8 + 2] = w_p;
-        p.trace[MODE * 8 + 6] = n_tiles;
-      }
+      if (tracing && lane == 0) p.trace[MODE * 8 + 7] = w_p;
     }
-  } else if (warp < 4) {
+  } else if (warp == 3) {
     setmaxnreg_dec<72>();
   } else {
     // -------------------------------------------------------------- compute warpgroups
@@ -351,6 +352,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     long long w_s = 0;
     const long long cloop0 = tracing ? clock64() : 0;
     const float2 c2 = make_float2(c, c), sc2 = make_float2(sc, sc);
+    // dK/dV mode: the per-query L2 / delta values of a tile are the same for every thread and change
+    // with the tile; they are fetched one tile ahead so their L2-cache latency never sits between a
+    // barrier and the TMEM round trip that follows it.
+    float4 vL[8], vD[8];
+    if (MODE == 0) {
+      const float4* l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + wg * 32);
+      const float4* d4 = reinterpret_cast<const float4*>(p.delta + vec_base + wg * 32);
+#pragma unroll
+      for (int g = 0; g < 8; ++g) { vL[g] = __ldg(l4 + g); vD[g] = __ldg(d4 + g); }
+    }
     // Both warpgroups work on every streamed tile: warpgroup g owns columns [32g, 32g+32) of the
     // 64-column S / dP tile and writes its packed bf16 results over columns [32g, 32g+16).
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -365,11 +376,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       tmem_ld_32x32(tS, s);
       if (MODE == 1) tmem_ld_32x32(tD, d);
       tmem_ld_wait();
-      const float4* l4 = nullptr;
-      const float4* d4 = nullptr;
+      float4 cL[8], cD[8];
       if (MODE == 0) {
-        l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + j * SR_ROWS + wg * 32);
-        d4 = reinterpret_cast<const float4*>(p.delta + vec_base + j * SR_ROWS + wg * 32);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) { cL[g] = vL[g]; cD[g] = vD[g]; }
+        if (j + 1 < n_tiles) {
+          const float4* l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + (j + 1) * SR_ROWS + wg * 32);
+          const float4* d4 = reinterpret_cast<const float4*>(p.delta + vec_base + (j + 1) * SR_ROWS + wg * 32);
+#pragma unroll
+          for (int g = 0; g < 8; ++g) { vL[g] = __ldg(l4 + g); vD[g] = __ldg(d4 + g); }
+        }
       }
       uint32_t pk[16], dk[16];
       // P = exp2(S * c - L2); kept as fp32 in s[] for the dS product
@@ -377,7 +393,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       for (int g = 0; g < 8; ++g) {
         float2 nL[2];
         if (MODE == 0) {
-          const float4 a = __ldg(l4 + g);
+          const float4 a = cL[g];
           nL[0] = make_float2(-a.x, -a.y); nL[1] = make_float2(-a.z, -a.w);
         } else {
           nL[0] = nL[1] = make_float2(-my_L2, -my_L2);
@@ -408,7 +424,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       for (int g = 0; g < 8; ++g) {
         float2 Dl[2];
         if (MODE == 0) {
-          const float4 bb = __ldg(d4 + g);
+          const float4 bb = cD[g];
           Dl[0] = make_float2(bb.x, bb.y); Dl[1] = make_float2(bb.z, bb.w);
         } else {
           Dl[0] = Dl[1] = make_float2(my_delta, my_delta);

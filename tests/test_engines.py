@@ -147,3 +147,33 @@ def test_inference_failure_never_publishes_and_waves_are_collective(tmp_path):
         GeneratedSample({"a": b"1", "a/b": b"2"}, (1,), "u8")
     with pytest.raises(BackendContractError):
         InferenceEngine(FakeAdapter()).run([_cases(1)[0], _cases(1)[0]], weights_id="w", output_dir=tmp_path / "q")
+
+
+def test_comparison_view_and_validation_plan(tmp_path):
+    import json
+
+    import pytest
+    import torch
+
+    from solarwm_b200.engine.comparison import side_by_side, write_comparison
+    from solarwm_b200.engine.validation_plan import build_plan, load_plan, publish_plan
+    from solarwm_b200.errors import SolarWMError
+
+    g, s = torch.zeros(5, 3, 16, 24), torch.ones(4, 3, 8, 16) * 0.5
+    view = side_by_side(g, s, separator=4)
+    assert view.shape == (4, 3, 16, 24 + 4 + 16)
+    assert float(view[0, 0, 0, 30]) == -1.0 and float(view[0, 0, 8, 30]) == 0.5      # letter-boxed source
+    info = write_comparison(tmp_path / "cmp", g, s, use_ffmpeg=False, meta={"sample_id": "a"})
+    assert info["frames"] == 4 and json.loads((tmp_path / "cmp" / "comparison.json").read_text())["sample_id"] == "a"
+
+    rows = [{"sample_id": f"v{i}", "caption": f"c{i}"} for i in range(5)]
+    plan = build_plan(rows, run_id="r", step=10, pass_name="main", count=4, dp_world=2, base_seed=7)
+    again = build_plan(rows, run_id="r", step=10, pass_name="main", count=4, dp_world=2, base_seed=7)
+    assert plan.digest == again.digest
+    assert [c.slot for c in plan.for_rank(1)] == [1, 3]
+    path = publish_plan(plan, tmp_path / "val")
+    assert load_plan(path).digest == plan.digest
+    with pytest.raises(FileExistsError):
+        publish_plan(plan, tmp_path / "val")                   # create-only
+    with pytest.raises(SolarWMError):
+        build_plan(rows, run_id="r", step=10, pass_name="main", count=9)

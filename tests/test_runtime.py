@@ -155,3 +155,70 @@ def test_seed_domains_layout_and_secrets():
         provenance.reject_inline_secrets({"data": {"api_key": "abc123"}})
     with pytest.raises(ConfigurationError):
         provenance.reject_inline_secrets({"x": ["ghp_" + "a" * 36]})
+
+
+def test_validation_publish_partition_and_receipts(tmp_path):
+    import json
+
+    import pytest
+
+    from solarwm_b200.errors import SolarWMError
+    from solarwm_b200.runtime.validation_publish import owner_node, publish_validation
+
+    src = tmp_path / "validation" / "step_000010_main"
+    (src / "slot-000000").mkdir(parents=True)
+    (src / "slot-000000" / "video.mp4").write_bytes(b"abc")
+    (src / "slot-000000" / "manifest.json").write_text("{}")
+    (src / "COMPLETE.json").write_text("{}")
+    dest = tmp_path / "published"
+    total = 0
+    for node in range(2):
+        out = publish_validation(src, f"file://{dest}", node=node, nodes=2)
+        total += out["objects_sent"]
+    assert total == 3
+    assert (dest / "step_000010_main" / "slot-000000" / "video.mp4").read_bytes() == b"abc"
+    receipt = json.loads((src / ".published" / "node-0000.json").read_text())
+    assert all(owner_node(o["key"].split("/", 1)[1], 2) == 0 for o in receipt["objects"])
+    again = publish_validation(src, f"file://{dest}", node=0, nodes=2)       # re-runnable
+    assert again["skipped_passes"] == 1 and again["objects_sent"] == 0
+    with pytest.raises(SolarWMError):
+        publish_validation(tmp_path / "validation", f"file://{dest}", node=2, nodes=2)
+
+
+def test_gcs_uploader_create_only_and_retry():
+    import io
+    import json
+    import urllib.error
+
+    import pytest
+
+    from solarwm_b200.runtime.gcs_upload import GCSUploader, UploadError
+
+    calls = []
+
+    class _Resp(io.BytesIO):
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *a):
+            return False
+
+    def opener(req):
+        calls.append(req)
+        if len(calls) == 1:
+            raise urllib.error.HTTPError(req.full_url, 503, "busy", {}, None)
+        if "exists" in req.full_url:
+            raise urllib.error.HTTPError(req.full_url, 412, "precondition", {}, None)
+        return _Resp(json.dumps({"generation": "42"}).encode())
+
+    import tempfile
+
+    with tempfile.NamedTemporaryFile() as fh:
+        fh.write(b"payload")
+        fh.flush()
+        up = GCSUploader("bucket", lambda: "tok", prefix="runs/x", opener=opener, sleep=lambda s: None)
+        r = up.upload(fh.name, "a/b.bin")
+        assert r["generation"] == "42" and r["key"] == "runs/x/a/b.bin" and len(calls) == 2
+        assert "ifGenerationMatch=0" in calls[-1].full_url and calls[-1].headers["Authorization"] == "Bearer tok"
+        with pytest.raises(UploadError):
+            up.upload(fh.name, "exists.bin")
