@@ -152,38 +152,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
+    // The whole warp runs the loop so that addresses and descriptors stay warp-uniform (an issue loop
+    // confined to one lane computes them per thread and pays a register-file crossing per operand,
+    // which made instruction issue the bottleneck); one elected lane issues each tcgen05 instruction.
     setmaxnreg_dec<72>();
-    if (lane == 0) {
+    {
+      auto wwait = [&](uint64_t* bar, uint32_t parity, volatile int* aw, int code) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, aw, code));
+      };
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, KT, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, HD, 0, 1);
-      const uint32_t q_smem = smem_u32(smem + L::Q_OFF);
-      const uint32_t k_smem = smem_u32(smem + L::K_OFF);
-      const uint32_t v_smem = smem_u32(smem + L::V_OFF);
+      const uint32_t q_smem = __shfl_sync(0xffffffffu, smem_u32(smem + L::Q_OFF), 0);
+      const uint32_t k_smem = __shfl_sync(0xffffffffu, smem_u32(smem + L::K_OFF), 0);
+      const uint32_t v_smem = __shfl_sync(0xffffffffu, smem_u32(smem + L::V_OFF), 0);
       auto issue_qk = [&](int t, int s) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * L::CHUNK_BYTES + (kk % 4) * 32;
-          umma_ss(TS[t], umma_desc_kmajor(q_smem + t * L::TILE_BYTES + off),
+          if (elect_one()) umma_ss(TS[t], umma_desc_kmajor(q_smem + t * L::TILE_BYTES + off),
                   umma_desc_kmajor(k_smem + s * L::TILE_BYTES + off), idesc_qk, kk != 0);
         }
-        umma_commit(&s_ready[t]);
+        if (elect_one()) umma_commit(&s_ready[t]);
       };
       auto issue_pv = [&](int t, int s, int j) {
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
-          umma_ts(TO[t], TS[t] + kk * 8,
+          if (elect_one()) umma_ts(TO[t], TS[t] + kk * 8,
                   umma_desc_mnmajor(v_smem + s * L::TILE_BYTES + kk * 2048, L::CHUNK_BYTES), idesc_pv,
                   (j | kk) != 0);
         }
-        umma_commit(&o_done[t]);
+        if (elect_one()) umma_commit(&o_done[t]);
       };
-      bool ok = mbar_wait(q_full, 0, abort_word, ST_TIMEOUT_FULL);
-      if (ok) ok = mbar_wait(&k_full[0], 0, abort_word, ST_TIMEOUT_FULL);
+      bool ok = wwait(q_full, 0, abort_word, ST_TIMEOUT_FULL);
+      if (ok) ok = wwait(&k_full[0], 0, abort_word, ST_TIMEOUT_FULL);
       if (ok) {
         tc_fence_after();
         issue_qk(0, 0);
         if (tile1_live) issue_qk(1, 0);
-        umma_commit(&k_empty[0]);
+        if (elect_one()) umma_commit(&k_empty[0]);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j % KV_STAGES;
@@ -191,26 +197,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int sn = (j + 1) % KV_STAGES;
         const uint32_t phn = ((j + 1) / KV_STAGES) & 1;
         const bool more = (j + 1) < n_kv;
-        if (!mbar_wait(&v_full[s], ph, abort_word, ST_TIMEOUT_FULL)) break;
+        if (!wwait(&v_full[s], ph, abort_word, ST_TIMEOUT_FULL)) break;
         // ---- tile 0
-        if (!mbar_wait(&p_ready[0], j & 1, abort_word, ST_TIMEOUT_OTHER)) break;
+        if (!wwait(&p_ready[0], j & 1, abort_word, ST_TIMEOUT_OTHER)) break;
         tc_fence_after();
         issue_pv(0, s, j);
         if (more) {
-          if (!mbar_wait(&k_full[sn], phn, abort_word, ST_TIMEOUT_FULL)) break;
+          if (!wwait(&k_full[sn], phn, abort_word, ST_TIMEOUT_FULL)) break;
           tc_fence_after();
           issue_qk(0, sn);
         }
         // ---- tile 1
         if (tile1_live) {
-          if (!mbar_wait(&p_ready[1], j & 1, abort_word, ST_TIMEOUT_OTHER)) break;
+          if (!wwait(&p_ready[1], j & 1, abort_word, ST_TIMEOUT_OTHER)) break;
           tc_fence_after();
           issue_pv(1, s, j);
         }
-        umma_commit(&v_empty[s]);
+        if (elect_one()) umma_commit(&v_empty[s]);
         if (more) {
           if (tile1_live) issue_qk(1, sn);
-          umma_commit(&k_empty[sn]);
+          if (elect_one()) umma_commit(&k_empty[sn]);
         }
       }
     }

@@ -60,7 +60,7 @@ struct AttnBwdParams {
 // trace slots (per mode, 8 each): 0 score-warp loop cycles, 1 score-warp wait strm_full, 2 score-warp
 // wait s_free/dp_free, 3 compute loop cycles, 4 compute waits, 5 producer wait strm_empty, 6 tiles,
 // 7 accumulate-warp wait p_ready/ds_ready
-__device__ long long g_bwd_trace[16];
+__device__ long long g_bwd_trace[32];
 
 template <int HD>
 struct BwdSmem {
@@ -103,6 +103,14 @@ __device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint8_t* region, int
       *reinterpret_cast<uint4*>(dst + ((piece ^ (row & 7)) << 4)) = o;
     }
   }
+}
+
+// A load the compiler may not sink to its first use: the prefetch below has to leave a whole tile
+// ahead of the values being needed.
+__device__ __forceinline__ float4 ld_f4_early(const float4* ptr) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr));
+  return v;
 }
 
 // MODE 0 = dK/dV, MODE 1 = dQ.
@@ -350,6 +358,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     }
     bool ok = true;
     long long w_s = 0;
+    long long seg[6] = {0, 0, 0, 0, 0, 0};   // ld S | P math | st P + arrive | ld dP | dS math | st dS + arrive
     const long long cloop0 = tracing ? clock64() : 0;
     const float2 c2 = make_float2(c, c), sc2 = make_float2(sc, sc);
     // dK/dV mode: the per-query L2 / delta values of a tile are the same for every thread and change
@@ -360,7 +369,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       const float4* l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + wg * 32);
       const float4* d4 = reinterpret_cast<const float4*>(p.delta + vec_base + wg * 32);
 #pragma unroll
-      for (int g = 0; g < 8; ++g) { vL[g] = __ldg(l4 + g); vD[g] = __ldg(d4 + g); }
+      for (int g = 0; g < 8; ++g) { vL[g] = ld_f4_early(l4 + g); vD[g] = ld_f4_early(d4 + g); }
     }
     // Both warpgroups work on every streamed tile: warpgroup g owns columns [32g, 32g+32) of the
     // 64-column S / dP tile and writes its packed bf16 results over columns [32g, 32g+16).
@@ -373,9 +382,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       if (tracing) w_s += clock64() - c0;
       tc_fence_after();
       uint32_t s[32], d[32];
+      long long q0 = tracing ? clock64() : 0;
       tmem_ld_32x32(tS, s);
       if (MODE == 1) tmem_ld_32x32(tD, d);
       tmem_ld_wait();
+      if (tracing) { const long long q1 = clock64(); seg[0] += q1 - q0; q0 = q1; }
       float4 cL[8], cD[8];
       if (MODE == 0) {
 #pragma unroll
@@ -384,7 +395,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
           const float4* l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + (j + 1) * SR_ROWS + wg * 32);
           const float4* d4 = reinterpret_cast<const float4*>(p.delta + vec_base + (j + 1) * SR_ROWS + wg * 32);
 #pragma unroll
-          for (int g = 0; g < 8; ++g) { vL[g] = __ldg(l4 + g); vD[g] = __ldg(d4 + g); }
+          for (int g = 0; g < 8; ++g) { vL[g] = ld_f4_early(l4 + g); vD[g] = ld_f4_early(d4 + g); }
         }
       }
       uint32_t pk[16], dk[16];
@@ -407,17 +418,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
           pk[e >> 1] = pack_bf16x2(pv.x, pv.y);
         }
       }
+      if (tracing) { const long long q1 = clock64(); seg[1] += q1 - q0; q0 = q1; }
       if (MODE == 0) {
         tmem_st_32x16(tS, pk);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_ready[0]);
+        if (tracing) { const long long q1 = clock64(); seg[2] += q1 - q0; q0 = q1; }
         c0 = tracing ? clock64() : 0;
         if (!mbar_wait(dp_ready, par, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         if (tracing) w_s += clock64() - c0;
         tc_fence_after();
+        q0 = tracing ? clock64() : 0;
         tmem_ld_32x32(tD, d);
         tmem_ld_wait();
+        if (tracing) { const long long q1 = clock64(); seg[3] += q1 - q0; q0 = q1; }
       }
       // dS = P * (dP - delta) * scale
 #pragma unroll
@@ -438,14 +453,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
           dk[e >> 1] = pack_bf16x2(dd.x, dd.y);
         }
       }
+      if (tracing) { const long long q1 = clock64(); seg[4] += q1 - q0; q0 = q1; }
       tmem_st_32x16(tD, dk);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(MODE == 0 ? ds_ready : &p_ready[b]);
+      if (tracing) { const long long q1 = clock64(); seg[5] += q1 - q0; q0 = q1; }
     }
     if (tracing && threadIdx.x == 128) {
       p.trace[MODE * 8 + 3] = clock64() - cloop0;
       p.trace[MODE * 8 + 4] = w_s;
+      for (int i = 0; i < 6; ++i) p.trace[16 + MODE * 8 + i] = seg[i];
     }
     // ---- epilogue: accumulators -> bf16 -> shared memory staging -> TMA store
     if (ok) ok = mbar_wait(acc_done, 0, abort_word, ST_TIMEOUT_OTHER);
@@ -556,7 +574,7 @@ static int g_trace_enabled = 0;
 // roles (how long each waited on which barrier).  `out16` receives the 16 counters of the last call.
 extern "C" int solar_attn_bwd_trace(int enable, long long* out16) {
   g_trace_enabled = enable;
-  if (out16 != nullptr) SOLAR_CUDA_OK(cudaMemcpyFromSymbol(out16, g_bwd_trace, 16 * sizeof(long long)));
+  if (out16 != nullptr) SOLAR_CUDA_OK(cudaMemcpyFromSymbol(out16, g_bwd_trace, 32 * sizeof(long long)));
   return 0;
 }
 

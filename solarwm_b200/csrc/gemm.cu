@@ -146,7 +146,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // Every lane runs the loop (warp-uniform addresses and descriptors); one elected lane issues.
+    {
+      auto wwait = [&](uint64_t* bar, uint32_t parity, volatile int* aw, int code) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, aw, code));
+      };
+      const uint32_t smem_base = __shfl_sync(0xffffffffu, smem_u32(smem), 0);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
@@ -155,16 +161,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_word, ST_TIMEOUT_TMEM_EMPTY)) break;
+        if (!wwait(&tempty_bar[acc], acc_phase ^ 1, abort_word, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_u + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_word, ST_TIMEOUT_FULL)) {
+          if (!wwait(&full_bar[stage], phase, abort_word, ST_TIMEOUT_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
@@ -172,15 +178,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                         : umma_desc_kmajor(sa + kk * 32);
             const uint64_t bdesc = B_MN ? umma_desc_mnmajor(sb + kk * 2048, 64 * BK * 2)
                                         : umma_desc_kmajor(sb + kk * 32);
-            umma_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
+            if (elect_one()) umma_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
           }
-          umma_commit(&empty_bar[stage]);
+          if (elect_one()) umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) umma_commit(&tfull_bar[acc]);
+        if (ok && elect_one()) umma_commit(&tfull_bar[acc]);
       }
     }
   } else {

@@ -131,6 +131,18 @@ class FlatUnit:
             if not p.grad_live:
                 p.main_grad.zero_()
 
+    def move_grads_(self, grad: torch.Tensor, grad_v: torch.Tensor) -> None:
+        """Put the flat gradient buffers onto caller-provided storage (e.g. symmetric memory)."""
+        assert grad.numel() == self.numel_m and grad_v.numel() == self.numel_v
+        if self.grad is not None:
+            grad.copy_(self.grad)
+            grad_v.copy_(self.grad_v)
+        else:
+            grad.zero_()
+            grad_v.zero_()
+        self.grad, self.grad_v = grad, grad_v
+        self.ensure_grads()
+
     def move_(self, flat: torch.Tensor, flat_v: torch.Tensor) -> None:
         """Re-home the unit onto caller-provided storage (e.g. symmetric memory)."""
         flat.copy_(self.flat)

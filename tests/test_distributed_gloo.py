@@ -103,3 +103,54 @@ def test_tiny_wan_sp2_matches_single_process_oracle(tmp_path):
             worst = max(worst, err)
             assert err < 2e-4, (name, err)
     assert torch.equal(got[0]["grads"]["blocks.0.ffn.0.weight"], got[1]["grads"]["blocks.0.ffn.0.weight"])
+
+
+def _zero_worker(rank, world, path, out):
+    from solarwm_b200.engine.optim import FlatAdamW
+    from solarwm_b200.parallel.flat import FlatUnit
+    from solarwm_b200.parallel.zero import ZeroAdamW
+
+    _init(rank, world, path)
+    specs = [("a.weight", (24, 16), False), ("a.bias", (24,), False), ("n.weight", (16,), True)]
+
+    def make():
+        torch.manual_seed(0)
+        u = FlatUnit(specs, "cpu", dtype=torch.float32, pad_to=world)
+        for n, _, _ in specs:
+            u.parameter(n)
+        u.flat.normal_()
+        u.flat_v.normal_()
+        u.ensure_grads()
+        return u
+
+    u_ref, u_z = make(), make()
+    ref = FlatAdamW([u_ref], lr=1e-2, weight_decay=0.1)
+    zero = ZeroAdamW([u_z], None, lr=1e-2, weight_decay=0.1)
+    for step in range(3):
+        grads = []
+        for r in range(world):                       # the gradient every rank would hold
+            g = torch.Generator().manual_seed(100 * step + r)
+            grads.append((torch.randn(u_ref.numel_m, generator=g), torch.randn(u_ref.numel_v, generator=g)))
+        u_ref.grad.copy_(sum(g[0] for g in grads))
+        u_ref.grad_v.copy_(sum(g[1] for g in grads))
+        n_ref = ref.local_grad_sumsq().sqrt().clone()
+        ref.set_clip(n_ref, 1.0)
+        ref.step()
+        u_z.grad.copy_(grads[rank][0])
+        u_z.grad_v.copy_(grads[rank][1])
+        n_z = zero.sharded_step(1.0)
+        assert torch.allclose(n_z, n_ref, rtol=1e-5), (n_z, n_ref)
+    torch.save({"flat": u_z.flat.clone(), "flat_v": u_z.flat_v.clone(), "ref": u_ref.flat.clone(),
+                "ref_v": u_ref.flat_v.clone(), "state_numel": zero.state[0]["m"]["exp_avg"].numel(),
+                "full": u_z.numel_m}, f"{out}.{rank}")
+    dist.destroy_process_group()
+
+
+def test_zero_sharded_adamw_matches_unsharded(tmp_path):
+    out = str(tmp_path / "zero")
+    mp.spawn(_zero_worker, args=(2, str(tmp_path / "rdv"), out), nprocs=2, join=True)
+    for r in range(2):
+        got = torch.load(f"{out}.{r}", weights_only=True)
+        assert got["state_numel"] * 2 == got["full"]            # each rank holds half of the moments
+        assert torch.allclose(got["flat"], got["ref"], atol=1e-6)
+        assert torch.allclose(got["flat_v"], got["ref_v"], atol=1e-6)
