@@ -72,19 +72,22 @@ class WanStage0p5Runtime:
             grad_accum=int(train.get("grad_accum", train.get("gradient_accumulation_steps", 1))),
             ema_decay=float(ema["decay"]) if ema.get("enabled") else None,
             checkpointing="full" if (train.get("fsdp", {}) or {}).get("activation_checkpointing") else "none",
+            zero=bool((train.get("fsdp", {}) or {}).get("enabled", False)) and topo.raw_world_size > 1,
             seed=seed, **dict(extra_options or {}))
         dtype = torch.bfloat16 if self.ctx.device.type == "cuda" else torch.float32
         from ...models.wan import WanDiT
 
         model = WanDiT(self.arch, device=self.ctx.device, dtype=dtype,
-                       seed=model_init_seed(self.route.family, seed))
+                       seed=model_init_seed(self.route.family, seed), shard_pad=topo.raw_world_size)
         if bool(config["model"].get("nonzero_head_init", False)):
             with torch.no_grad():
                 model.get_parameter("head.head.weight").normal_(0, 0.02)
         if trainer_cls is WanStage0p5Trainer:
-            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, dtype=dtype, model=model)
+            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, dtype=dtype, model=model,
+                                       dp_group=self.ctx.dp_group, dp_size=topo.dp_size)
         else:
-            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, model=model)
+            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, model=model,
+                                       dp_group=self.ctx.dp_group, dp_size=topo.dp_size)
         self.trainer.gen.manual_seed(objective_seed(seed, topo.dp_rank))
         self.scheduler = WarmupCosine(self.trainer.optimizer, warmup_steps=int(train.get("warmup_steps", 0)),
                                       total_steps=int(train["max_steps"]),
@@ -154,9 +157,18 @@ class WanStage0p5Runtime:
     def prepare_optimizer_step(self) -> GradientStatus:
         tr = self.trainer
         tr.model.finalize_grads()
-        if tr.sp is not None and tr.sp.size > 1:
-            tr.sp.sum_gradients_([g for u in tr.model.units() for g in (u.grad, u.grad_v)])
-        norm = tr.optimizer.local_grad_sumsq().sqrt()
+        if hasattr(tr.optimizer, "sharded_step"):
+            norm = tr.optimizer.global_grad_norm(tr.optimizer.reduce_scatter_grads())
+        else:
+            flat = [g for u in tr.model.units() for g in (u.grad, u.grad_v)]
+            if tr.sp is not None and tr.sp.size > 1:
+                tr.sp.sum_gradients_(flat)
+            if tr.dp_size > 1:
+                import torch.distributed as dist
+
+                for g in flat:
+                    dist.all_reduce(g, op=dist.ReduceOp.SUM, group=tr.dp_group)
+            norm = tr.optimizer.local_grad_sumsq().sqrt()
         tr.optimizer.set_clip(norm, tr.opts.max_grad_norm)
         value = float(norm.item())
         tr.last_grad_norm = norm

@@ -38,23 +38,33 @@ class Stage0p5Options:
     ema_decay: Optional[float] = None
     checkpointing: str = "none"
     keep_blocks: int = 0
+    zero: bool = False                 # shard optimizer state + gradient reduction over all ranks (own FSDP)
+    zero_transport: str = "collective"  # or "fused" (NVLink peer reduce / push; needs a symmetric heap)
     seed: int = 0
 
 
 class WanStage0p5Trainer:
     def __init__(self, cfg: WanConfig, device, opts: Stage0p5Options = Stage0p5Options(), sp=None,
-                 dtype=torch.bfloat16, model: Optional[WanDiT] = None):
+                 dtype=torch.bfloat16, model: Optional[WanDiT] = None, dp_group=None, dp_size: int = 1, heap=None):
         self.cfg, self.opts, self.device = cfg, opts, torch.device(device)
         self.sp = sp
         self.sp_size = 1 if sp is None else sp.size
+        self.dp_group, self.dp_size = dp_group, int(dp_size)
         self.model = model or WanDiT(cfg, device=device, dtype=dtype, seed=opts.seed)
         if sp is not None:
             self.model.sp = sp
         self.model.checkpointing = opts.checkpointing
         self.model.keep_blocks = opts.keep_blocks
         self.model.ensure_grads()
-        self.optimizer = FlatAdamW(self.model.units(), lr=opts.lr, betas=opts.betas, eps=opts.eps,
-                                   weight_decay=opts.weight_decay, ema_decay=opts.ema_decay)
+        okw = dict(lr=opts.lr, betas=opts.betas, eps=opts.eps, weight_decay=opts.weight_decay, ema_decay=opts.ema_decay)
+        if opts.zero and self.sp_size * self.dp_size > 1:
+            from ...parallel.zero import ZeroAdamW
+
+            # gradients are SUMMED over every rank (SP partial sums and DP replicas alike; the loss carries
+            # the 1 / (accum * sp * dp) factor), so the shard group is the whole job
+            self.optimizer = ZeroAdamW(self.model.units(), None, transport=opts.zero_transport, heap=heap, **okw)
+        else:
+            self.optimizer = FlatAdamW(self.model.units(), **okw)
         self.scheduler = FlowMatchScheduler(shift=opts.timestep_shift)
         self.gen = torch.Generator(device=self.device).manual_seed(opts.seed * 100003)
         self.global_step = 0
@@ -96,17 +106,26 @@ class WanStage0p5Trainer:
         weight = self.scheduler.training_weight(t_video).view(B, 1).expand(B, F).reshape(B * F)
         loss = ops.weighted_masked_mse(pred, target[:, :pred.shape[1]], weight.float(),
                                        mask.reshape(B * F).float())
-        (loss / (o.grad_accum * self.sp_size)).backward()
+        (loss / (o.grad_accum * self.sp_size * self.dp_size)).backward()
         return loss.detach()
 
     def optimizer_step(self) -> torch.Tensor:
         self.model.finalize_grads()
         opt = self.optimizer
-        if self.sp is not None and self.sp.size > 1:
-            self.sp.sum_gradients_([g for u in self.model.units() for g in (u.grad, u.grad_v)])
-        norm = opt.local_grad_sumsq().sqrt()
-        opt.set_clip(norm, self.opts.max_grad_norm)
-        opt.step()
+        if hasattr(opt, "sharded_step"):
+            norm = opt.sharded_step(self.opts.max_grad_norm)      # reduce-scatter, clip, AdamW, all-gather
+        else:
+            flat = [g for u in self.model.units() for g in (u.grad, u.grad_v)]
+            if self.sp is not None and self.sp.size > 1:
+                self.sp.sum_gradients_(flat)
+            if self.dp_size > 1:
+                import torch.distributed as dist
+
+                for g in flat:
+                    dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.dp_group)
+            norm = opt.local_grad_sumsq().sqrt()
+            opt.set_clip(norm, self.opts.max_grad_norm)
+            opt.step()
         self.model.zero_grads()
         self.global_step += 1
         self.last_grad_norm = norm

@@ -40,9 +40,8 @@ class Stage1Options(Stage0p5Options):
 
 
 class WanStage1Trainer(WanStage0p5Trainer):
-    def __init__(self, cfg, device, opts: Stage1Options = Stage1Options(), sp=None, model=None, dp_group=None):
-        super().__init__(cfg, device, opts, sp=sp, model=model)
-        self.dp_group = dp_group
+    def __init__(self, cfg, device, opts: Stage1Options = Stage1Options(), sp=None, model=None, dp_group=None, **kw):
+        super().__init__(cfg, device, opts, sp=sp, model=model, dp_group=dp_group, **kw)
 
     # ------------------------------------------------------------------------------------
     def _per_chunk(self, values: torch.Tensor, F: int) -> torch.Tensor:
@@ -85,7 +84,7 @@ class WanStage1Trainer(WanStage0p5Trainer):
             loss = self._anyflow_loss(latents, noise, text, n_chunks)
         else:
             raise ValueError(f"unknown stage1 objective {o.objective!r}")
-        (loss / (o.grad_accum * self.sp_size)).backward()
+        (loss / (o.grad_accum * self.sp_size * self.dp_size)).backward()
         return loss.detach()
 
     def _anyflow_loss(self, latents, noise, text, n_chunks):

@@ -1,6 +1,7 @@
 """Two-GPU checks (skipped with fewer devices): the fused NVLink Ulysses path against the NCCL
-collective path -- same forward output and the same parameter gradients -- and the peer-memory
-runtime's push/flag protocol including a bounded wait that is made to run out."""
+collective path -- same forward output and the same parameter gradients --, the peer-memory
+runtime's push/flag protocol including a bounded wait that is made to run out, and the
+ZeRO-sharded AdamW with fused peer reduce / push against its NCCL form."""
 import os
 from datetime import timedelta
 
@@ -100,7 +101,47 @@ def _worker(rank, world, port, out_path):
             result[f"fused_kernels_{key[1]}"] = (counters.get("gemm_scatter", 0), counters.get("attn_fwd_scatter", 0))
     result["worst_grad_rel"] = worst
     result["infer_rel"] = ((outs["fused_infer"] - ref_out).norm() / ref_out.norm()).item()
+    # ---- ZeRO-sharded AdamW: fused peer reduce / push against the NCCL collectives
+    from solarwm_b200.parallel.flat import FlatUnit
+    from solarwm_b200.parallel.zero import ZeroAdamW
+
+    specs = [("a.weight", (512, 256), False), ("a.bias", (512,), False), ("n.weight", (256,), True)]
+
+    def make_unit():
+        u = FlatUnit(specs, "cuda", dtype=torch.bfloat16, pad_to=world)
+        for n, _, _ in specs:
+            u.parameter(n)
+        gg = torch.Generator(device="cuda").manual_seed(5)
+        u.flat.copy_(torch.randn(u.numel_m, generator=gg, device="cuda") * 0.1)
+        u.flat_v.copy_(torch.randn(u.numel_v, generator=gg, device="cuda"))
+        u.ensure_grads()
+        return u
+
+    zheap = SymmetricHeap(8 << 20, None)
+    u_c, u_f = make_unit(), make_unit()
+    z_c = ZeroAdamW([u_c], None, transport="collective", lr=1e-2, weight_decay=0.1, ema_decay=0.9)
+    z_f = ZeroAdamW([u_f], None, transport="fused", heap=zheap, lr=1e-2, weight_decay=0.1, ema_decay=0.9)
+    norms = []
+    for step in range(3):
+        gg = torch.Generator(device="cuda").manual_seed(100 * step + rank)
+        gm = torch.randn(u_c.numel_m, generator=gg, device="cuda")
+        gv = torch.randn(u_c.numel_v, generator=gg, device="cuda")
+        for u in (u_c, u_f):
+            u.grad.copy_(gm)
+            u.grad_v.copy_(gv)
+        norms.append((float(z_c.sharded_step(1.0)), float(z_f.sharded_step(1.0))))
+        torch.cuda.synchronize()
+        dist.barrier()
+    ops.check_status()
+    result["zero_norms"] = norms
+    result["zero_param_diff"] = float((u_c.flat.float() - u_f.flat.float()).abs().max())
+    result["zero_vec_diff"] = float((u_c.flat_v - u_f.flat_v).abs().max())
+    result["zero_ema_diff"] = float((z_c.state[0]["m"]["ema"] - z_f.state[0]["m"]["ema"]).abs().max())
+    gathered = [torch.empty_like(u_f.flat) for _ in range(world)]
+    dist.all_gather(gathered, u_f.flat)
+    result["zero_ranks_agree"] = bool(all(torch.equal(gathered[0], t) for t in gathered))
     torch.save(result, f"{out_path}.{rank}")
+    zheap.close()
     fused.close()
     heap.close()
     dist.destroy_process_group()
@@ -118,3 +159,5 @@ def test_fused_ulysses_matches_collective_on_two_gpus(tmp_path):
         assert r["out_fused_none"] < 2e-2 and r["out_fused_selective"] < 2e-2 and r["out_nccl_selective"] < 1e-6, r
         assert r["infer_rel"] < 2e-2 and r["worst_grad_rel"] < 6e-2, r
         assert r["fused_kernels_none"] == (2, 2) and r["fused_kernels_selective"] == (4, 2), r
+        assert r["zero_ranks_agree"] and r["zero_param_diff"] < 1e-2 and r["zero_vec_diff"] < 1e-5, r
+        assert r["zero_ema_diff"] < 1e-5 and all(abs(a - b) < 1e-3 * max(a, 1.0) for a, b in r["zero_norms"]), r
