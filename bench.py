@@ -43,6 +43,9 @@ def parse_args():
     ap.add_argument("--height", type=int, default=44)
     ap.add_argument("--width", type=int, default=80)
     ap.add_argument("--checkpointing", default="auto", choices=["auto", "none", "full", "selective"])
+    ap.add_argument("--zero", default="fused", choices=["off", "collective", "fused"],
+                    help="N > 1: shard optimizer state and gradient reduction over the ranks (own FSDP); "
+                         "fused = NVLink peer reduce + AdamW + parameter push kernels")
     ap.add_argument("--keep-blocks", type=int, default=-1,
                     help="blocks exempt from recompute under checkpointing (-1: sized from free HBM)")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
@@ -184,13 +187,24 @@ def run_ours(args):
             s_local = args.frames * (args.height // 2) * (args.width // 2) / world
             per_block = s_local * (17 * cfg.dim + 2 * cfg.ffn_dim) * 2
             n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
-            fixed = 18.0 * n_params  # bf16 weight + fp32 grad + fp32 master/m/v
+            zero_on = world > 1 and args.zero != "off"
+            fixed = (6.0 + 12.0 / (world if zero_on else 1)) * n_params  # bf16 weight + fp32 grad + fp32 master/m/v
             total = torch.cuda.get_device_properties(local).total_memory
             keep = int(max(0.0, 0.92 * total - fixed - 0.6e9 * cfg.num_layers - 12e9) // per_block)
             keep = min(keep, cfg.num_layers)
+    zero = world > 1 and args.zero != "off"
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
-                           keep_blocks=keep, max_grad_norm=1.0, seed=0)
-    trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp)
+                           keep_blocks=keep, max_grad_norm=1.0, seed=0, zero=zero, zero_transport=args.zero)
+    model = heap = None
+    if zero:
+        from solarwm_b200.models.wan import WanDiT
+
+        model = WanDiT(cfg, device=f"cuda:{local}", dtype=torch.bfloat16, seed=0, shard_pad=world)
+        if args.zero == "fused":
+            from solarwm_b200.parallel.symm import SymmetricHeap
+
+            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()), None)
+    trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp, model=model, heap=heap)
     with torch.no_grad():  # a zero head would zero every upstream gradient; keep the step representative
         trainer.model.get_parameter("head.head.weight").normal_(0, 0.02)
     batch = make_batch(cfg, args)
@@ -232,6 +246,7 @@ def run_ours(args):
             "impl": "ours",
             "config": {"model": "wan22_ti2v_5b-shaped" if args.model == "ti2v_5b" else "small-debug",
                        "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
+                       "optimizer_sharding": (f"zero-{args.zero}" if zero else "none"),
                        "latent": [1, cfg.in_dim, args.frames, args.height, args.width],
                        "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt, "keep_blocks": keep,
                        "attention_backend": ops.get_backend(), "optimizer": "AdamW fp32 master (in timed region)",
