@@ -95,11 +95,11 @@ class LoRALinear(nn.Module):
     def __init__(self, d_in, d_out, rank, device, dtype, gen):
         super().__init__()
         bound = math.sqrt(6.0 / (d_in + d_out))
-        self.weight = nn.Parameter(((torch.rand(d_out, d_in, generator=gen) * 2 - 1) * bound).to(device, dtype),
+        self.weight = nn.Parameter(((torch.rand(d_out, d_in, generator=gen, device=gen.device) * 2 - 1) * bound).to(device, dtype),
                                    requires_grad=rank == 0)
         self.rank = rank
         if rank > 0:
-            self.lora_A = nn.Parameter((torch.randn(rank, d_in, generator=gen) / math.sqrt(d_in)).to(device, dtype))
+            self.lora_A = nn.Parameter((torch.randn(rank, d_in, generator=gen, device=gen.device) / math.sqrt(d_in)).to(device, dtype))
             self.lora_B = nn.Parameter(torch.zeros(d_out, rank, device=device, dtype=dtype))
 
     def forward(self, x):
@@ -130,7 +130,7 @@ class H3Block(nn.Module):
         self.norm_q = nn.Parameter(torch.ones(cfg.attention_head_dim, device=device), requires_grad=False)
         self.norm_k = nn.Parameter(torch.ones(cfg.attention_head_dim, device=device), requires_grad=False)
         if modulated:
-            self.adaln_proj = nn.Parameter((torch.randn(3 * 6 * h, cfg.time_embed_dim, generator=gen) * 0.02).to(device, dtype),
+            self.adaln_proj = nn.Parameter((torch.randn(3 * 6 * h, cfg.time_embed_dim, generator=gen, device=gen.device) * 0.02).to(device, dtype),
                                            requires_grad=False)
 
     def tables(self, temb):
@@ -206,9 +206,9 @@ class H3DiT(nn.Module):
     def __init__(self, cfg: H3Config, device="cpu", dtype=torch.bfloat16, seed: int = 0):
         super().__init__()
         self.cfg, self.dtype = cfg, dtype
-        g = torch.Generator().manual_seed(seed)
+        g = torch.Generator(device=device).manual_seed(seed)   # weights are drawn on the target device
         h = cfg.hidden_size
-        lin = lambda i, o, s=None: nn.Parameter((torch.randn(o, i, generator=g) * (s or 1.0 / math.sqrt(i))).to(device, dtype),
+        lin = lambda i, o, s=None: nn.Parameter((torch.randn(o, i, generator=g, device=g.device) * (s or 1.0 / math.sqrt(i))).to(device, dtype),
                                                 requires_grad=False)
         self.proj_in, self.audio_proj_in = lin(cfg.latent_row_dim, h), lin(cfg.audio_row_dim, h)
         self.context_embedder = lin(cfg.text_dim, h)
