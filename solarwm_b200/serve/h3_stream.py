@@ -144,6 +144,7 @@ class H3StreamingGenerator:
         self._out = torch.zeros(self.chunk_rows, mc.latent_row_dim, dtype=dt, device=dev)
         self._video_tags = torch.full((self.chunk_rows,), TAG_VIDEO, dtype=torch.int32, device=dev)
         self._pos_cache = {}
+        self._lift = torch.tensor([cfg.fx, cfg.fy, 1.0, 1.0], device=dev)
         self._commit_condition()
 
     def _local(self, n_rows: int):
@@ -198,7 +199,7 @@ class H3StreamingGenerator:
         """Rigid view matrices [S, 4, 4] -> (P^T, P^-1, P) with P = diag(fx, fy, 1, 1) @ view, in closed form
         (R^T, -R^T t) so that the computation is plain device arithmetic and can sit inside a CUDA graph."""
         v = view.to(self.device, torch.float32)
-        lift = torch.tensor([self.cfg.fx, self.cfg.fy, 1.0, 1.0], device=self.device)
+        lift = self._lift
         P = v * lift.view(1, 4, 1)
         R, t = v[:, :3, :3], v[:, :3, 3:]
         inv = torch.zeros_like(v)
