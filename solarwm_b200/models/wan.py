@@ -228,7 +228,8 @@ class WanBlock(nn.Module):
             return F_._LinearMainGradFn.apply(x, w, b)
         return F_.gemm(x, w, F_.NT, bias=b)
 
-    def forward(self, x, e0, rope, context, *, B, L, frame_tokens, group_offset=0, sp=None, memo=None, attn_fn=None):
+    def forward(self, x, e0, rope, context, *, B, L, frame_tokens, group_offset=0, sp=None, memo=None, attn_fn=None,
+                camera=None):
         """x [B*L_local, dim]; e0 fp32 [G, 6, dim] (G = B * frames); context [B*T, dim]."""
         cfg = self.cfg
         D, H, hd = cfg.dim, cfg.num_heads, cfg.head_dim
@@ -240,7 +241,7 @@ class WanBlock(nn.Module):
         nk = self._norm_kw(x)
         xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
         Ll = x.shape[0] // B
-        fused_sp = attn_fn is None and bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
+        fused_sp = attn_fn is None and camera is None and bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
             (not torch.is_grad_enabled() or self.unit.grad is not None)
         if fused_sp:
             # Ulysses exchanges ride on the producing kernels (parallel/fused_ulysses.py)
@@ -257,6 +258,12 @@ class WanBlock(nn.Module):
             q = F_.rmsnorm_rope(qkv[:, :D], self._p("self_attn.norm_q.weight").float(), rope, eps=cfg.eps)
             k = F_.rmsnorm_rope(qkv[:, D:2 * D], self._p("self_attn.norm_k.weight").float(), rope, eps=cfg.eps)
             v = qkv[:, 2 * D:]
+            if camera is not None:          # PRoPE on the whole head: q <- P^T, k / v <- P^-1 (per local row)
+                from . import camera_prope
+
+                q = camera_prope.apply(q, camera[0], H)
+                k = camera_prope.apply(k, camera[1], H)
+                v = camera_prope.apply(v, camera[1], H)
             q, k, v = (t.reshape(B, Ll, H, hd) for t in (q, k, v))
             q, k, v = sp.scatter_heads(q, k, v)
             if attn_fn is not None:     # structured (block-causal / teacher-forcing) self attention
@@ -264,6 +271,8 @@ class WanBlock(nn.Module):
             else:
                 o = ops.attention(q, k, v, memo=None if memo is None else (memo, "self"))
             o = sp.gather_heads(o).reshape(B * Ll, D)
+            if camera is not None:
+                o = camera_prope.apply(o, camera[2], H)
         y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
         x = F_.gated_residual(x, y, mod[:, 2], **gk)
 
@@ -454,9 +463,11 @@ class WanDiT(nn.Module):
             return checkpoint(lambda a, b, c: block(a, b, rope, c, memo=memo, **kw), x, e0, ctx, use_reentrant=False)
         return block(x, e0, rope, ctx, **kw)
 
-    def forward(self, x, t, context, y=None, r=None):
+    def forward(self, x, t, context, y=None, r=None, y_camera=None):
         """x [B, C, F, H, W] noisy latents; t [B, F] (or [B]) timesteps in [0, 1000];
-        context [B, T, text_dim]; y optional channel-concatenated conditioning (I2V)."""
+        context [B, T, text_dim]; y optional channel-concatenated conditioning (I2V);
+        y_camera optional ``{"viewmats": [B, F, 4, 4], "Ks": [B, F, 3, 3] or None, "transform": str}``:
+        PRoPE camera conditioning of the self-attention (reference: causal_model.py:925-1000)."""
         cfg = self.cfg
         P = self.stem.params
         if y is not None:
@@ -495,6 +506,14 @@ class WanDiT(nn.Module):
         else:
             e0_l, goff = e0, f0 if sp.size > 1 else 0
         kw = dict(B=B, L=L, frame_tokens=frame_tokens, group_offset=goff, sp=sp)
+        if y_camera is not None:
+            from . import camera_prope
+
+            vm = y_camera["viewmats"][:, f0:f0 + fl].reshape(B * fl, 4, 4).to(tok.device)
+            Ks = y_camera.get("Ks")
+            Ks = None if Ks is None else Ks[:, f0:f0 + fl].reshape(B * fl, 3, 3).to(tok.device)
+            mats = camera_prope.prope_matrices(vm, Ks, transform=y_camera.get("transform", "linear"))
+            kw["camera"] = tuple(camera_prope.per_row(m, frame_tokens) for m in mats)
         xs = tok
         for bi, block in enumerate(self.blocks):
             xs = self._run_block(block, xs, e0_l, rope, ctx, kw, index=bi)

@@ -76,3 +76,46 @@ def test_sgf_gradient_masks_before_reducing():
     loss = sgf.sgf_student_loss(out, g, mask=mask)
     loss.backward()
     assert torch.allclose(out.grad[:, 1:], g[:, 1:] / (2 * 2 * 4), atol=1e-6) and out.grad[:, 0].abs().sum() == 0
+
+
+def test_prope_matrices_and_wan_camera_path():
+    import torch
+
+    from solarwm_b200.models import camera_prope
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+
+    q, _ = torch.linalg.qr(torch.randn(3, 3, 3))
+    view = torch.eye(4).repeat(3, 1, 1)
+    view[:, :3, :3] = q
+    view[:, :3, 3] = torch.randn(3, 3)
+    Ks = torch.eye(3).repeat(3, 1, 1)
+    Ks[:, 0, 0], Ks[:, 1, 1], Ks[:, 0, 2] = 0.6, 0.9, 0.5
+    PT, Pinv, P = camera_prope.prope_matrices(view, Ks)
+    assert torch.allclose(P @ Pinv, torch.eye(4).expand(3, 4, 4), atol=1e-5)
+    assert torch.allclose(PT, P.transpose(1, 2))
+    # attention logits are invariant to a common rigid change of the world frame
+    g = torch.eye(4)
+    g[:3, :3] = torch.linalg.qr(torch.randn(3, 3))[0]
+    g[:3, 3] = torch.randn(3)
+    PT2, Pinv2, _ = camera_prope.prope_matrices(view @ g, Ks)
+    a, b = torch.randn(4), torch.randn(4)
+    s1 = (PT[0] @ a) @ (Pinv[1] @ b)
+    s2 = (PT2[0] @ a) @ (Pinv2[1] @ b)
+    assert torch.allclose(s1, s2, atol=1e-4)
+    # logd4 compresses long translations, keeps rotation
+    far = view.clone()
+    far[:, :3, 3] *= 100
+    z = camera_prope.transform_translation(far, "logd4")
+    assert torch.equal(z[:, :3, :3], far[:, :3, :3]) and (z[:, :3, 3].norm(dim=-1) < far[:, :3, 3].norm(dim=-1)).all()
+    # Wan forward with identity cameras equals the forward without cameras; other cameras change it
+    cfg = WanConfig(model_type="t2v", in_dim=4, out_dim=4, dim=256, ffn_dim=256, num_heads=2, num_layers=1,
+                    text_dim=32, text_len=8, freq_dim=32)
+    m = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05)
+    x, t, ctx = torch.randn(1, 4, 3, 4, 4), torch.tensor([[100.0, 500.0, 900.0]]), torch.randn(1, 8, 32)
+    base = m(x, t, ctx)
+    ident = {"viewmats": torch.eye(4).repeat(1, 3, 1, 1), "Ks": None}
+    assert torch.allclose(m(x, t, ctx, y_camera=ident), base, atol=1e-5)
+    moved = {"viewmats": view.unsqueeze(0), "Ks": Ks.unsqueeze(0), "transform": "logd4"}
+    assert not torch.allclose(m(x, t, ctx, y_camera=moved), base, atol=1e-4)
