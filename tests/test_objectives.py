@@ -154,3 +154,39 @@ def test_unipc_exact_for_constant_data_and_beats_euler():
     uni = sample(vel, noise.double(), num_steps=10, shift=1.0, order=2)
     err_uni, err_euler = (uni - ref).abs().max(), (euler(10) - ref).abs().max()
     assert err_uni < 0.1 * err_euler, (err_uni, err_euler)
+
+
+def test_a14b_expert_switch_and_i2v_condition():
+    import pytest
+    import torch
+
+    from solarwm_b200.backends.wan22.experts import (ExpertPair, expert_for_sigma, pack_i2v_condition,
+                                                     sample_expert_sigmas)
+
+    assert expert_for_sigma(0.9) == "high_noise" and expert_for_sigma(0.875) == "high_noise"
+    assert expert_for_sigma(0.5) == "low_noise"
+    g = torch.Generator().manual_seed(0)
+    hi = sample_expert_sigmas(1000, "high_noise", generator=g)
+    lo = sample_expert_sigmas(1000, "low_noise", generator=g)
+    assert hi.min() >= 0.875 - 1e-6 and hi.max() <= 1.0 and lo.max() < 0.875 + 1e-6 and lo.min() >= 0
+    y = pack_i2v_condition(torch.ones(1, 16, 1, 4, 4), frames=5)
+    assert y.shape == (1, 20, 5, 4, 4) and y[:, :4, 0].min() == 1 and y[:, :4, 1:].abs().max() == 0
+    assert y[:, 4:, 0].min() == 1 and y[:, 4:, 1:].abs().max() == 0
+    calls = []
+
+    class M(torch.nn.Module):
+        def __init__(self, name):
+            super().__init__()
+            self.name = name
+
+        def forward(self, x, t, c, **kw):
+            calls.append(self.name)
+            return x
+
+    pair = ExpertPair(low_noise=M("low"), load=lambda n: M("loaded-" + n))
+    x = torch.zeros(1, 4, 3, 2, 2)
+    pair(x, torch.tensor([[0.0, 950.0, 950.0]]), None)
+    pair(x, torch.tensor([[0.0, 300.0, 300.0]]), None)
+    assert calls == ["loaded-high_noise", "low"]
+    with pytest.raises(ValueError):
+        pair(x, torch.tensor([[0.0, 950.0, 300.0]]), None)

@@ -71,3 +71,37 @@ def test_worker_smoke_on_cpu(tmp_path, capsys):
     report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert report["chunks"] == 4
     assert json.loads((tmp_path / "exit-rank0.json").read_text())["status"] == "ok"
+
+
+def test_memory_retrieval_prefers_overlapping_views_outside_recent_window():
+    import numpy as np
+    import torch
+
+    from solarwm_b200.serve.memory import LatentMemoryBank, RetrievalCameras, retrieval_scores, select_memory
+
+    K = np.array([[0.5, 0, 0.5], [0, 0.9, 0.5], [0, 0, 1.0]])
+
+    def cam(x=0.0, yaw=0.0):
+        c = np.eye(4)
+        c[0, 3] = x
+        c[:3, :3] = np.array([[np.cos(yaw), 0, np.sin(yaw)], [0, 1, 0], [-np.sin(yaw), 0, np.cos(yaw)]])
+        return c
+
+    q = cam()
+    s = retrieval_scores(q, [cam(), cam(x=8.0), cam(yaw=np.pi)], K)
+    assert s[0] > s[1] > s[2] and abs(s[0] - 1.0) < 1e-9          # identical view: full overlap, no penalty
+    # a walk away and back: at chunk 8 the best memory is the start of the walk, never the recent chunks
+    cams = RetrievalCameras()
+    xs = list(np.linspace(0, 40, 25)) + list(np.linspace(40, 0, 20))
+    for x in xs:
+        cams.append(cam(x=float(x)), K)
+    idx, sc = cams.select(8)
+    assert len(idx) == 5 and idx.max() < (8 - 5) * 5 and list(sc) == sorted(sc, reverse=True)
+    assert 0 in idx
+    none, _ = select_memory(np.stack(cams.c2w), np.stack(cams.K), 3)
+    assert len(none) == 0
+    bank = LatentMemoryBank()
+    for i in range(3):
+        bank.commit(torch.full((1, 2, 5, 2, 2), float(i)), i)
+    got = bank.gather([1, 7, 14], torch.zeros(1, 2, 5, 2, 2))
+    assert got.shape == (1, 2, 3, 2, 2) and got[0, 0, :, 0, 0].tolist() == [0.0, 1.0, 2.0]
