@@ -231,7 +231,7 @@ class H3DiT(nn.Module):
         return F_.linear(torch.nn.functional.silu(e.float()).to(self.dtype), self.time_out)
 
     def forward(self, *, video_rows, text_rows, audio_rows=None, anchor_rows=None, timesteps, t_index, tags,
-                position_ids, viewmats=None, fx=0.505, fy=0.898):
+                position_ids, viewmats=None, fx=0.505, fy=0.898, attn_fn=None):
         """Rows are packed in the order [text | anchor | audio | video]; ``t_index`` / ``tags`` /
         ``position_ids`` / ``viewmats`` are per packed row.  Returns (video prediction [Nv, 96],
         audio prediction [Na, 32] or None)."""
@@ -260,7 +260,7 @@ class H3DiT(nn.Module):
         if viewmats is not None:
             cam_q, cam_kv, cam_o = prope_row_matrices(viewmats.to(x.device), fx, fy)
         for blk in self.blocks:
-            x = blk(x, blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o, sp=self.sp)
+            x = blk(x, blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o, sp=self.sp, attn_fn=attn_fn)
         xn = F_.norm_modulate(x, mode=1, w=self.norm_out, eps=cfg.eps)
         vid = F_.linear(xn[S - n_video:], self.proj_out)
         aud = None
