@@ -32,3 +32,26 @@ def test_h3_stage1_trainers_step():
         loss = tr.train_step(s)
         assert torch.isfinite(loss)
         assert any(not torch.equal(a, b) for a, b in zip(before, tr.model.trainable_parameters()))
+
+
+def test_h3_stage2_outer_steps_share_one_base():
+    from solarwm_b200.backends.minimax_h3.stage2 import H3Stage2Trainer
+    from solarwm_b200.models.h3 import LoRALinear
+
+    cfg = h3_preset("tiny")
+    cfg.lora_rank = 4
+    tr = H3Stage2Trainer(cfg, "cpu", chunk_latents=2, window_chunks=1, denoise_steps=2, grid_hw=(2, 2),
+                         critic_updates_per_student=2, lr_student=1e-3, lr_critic=1e-3)
+    s_mods = [m for m in tr.student.modules() if isinstance(m, LoRALinear)]
+    c_mods = [m for m in tr.critic.modules() if isinstance(m, LoRALinear)]
+    assert all(a.weight is b.weight for a, b in zip(s_mods, c_mods))            # one frozen base
+    assert all(a.lora_A is not b.lora_A for a, b in zip(s_mods, c_mods))        # private adapters
+    s = h3_sample(latent_frames=4, height=4, width=4, prompt_len=6, text_dim=cfg.text_dim, seed=0)
+    s["camera_w2c"] = torch.eye(4).repeat(5, 1, 1)
+    r0 = tr.train_outer_step(s, n_chunks=2)
+    assert "critic" in r0 and "student" not in r0
+    tr.train_outer_step(s, n_chunks=2)
+    before = s_mods[0].lora_B.detach().clone()
+    r2 = tr.train_outer_step(s, n_chunks=2)
+    assert "student" in r2 and r2["student"] == r2["student"]
+    assert not torch.equal(before, s_mods[0].lora_B)
