@@ -157,6 +157,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // which made instruction issue the bottleneck); one elected lane issues each tcgen05 instruction.
     setmaxnreg_dec<72>();
     {
+      const bool leader = elect_one();   // one lane issues; elected once, not per instruction
       auto wwait = [&](uint64_t* bar, uint32_t parity, volatile int* aw, int code) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, aw, code));
       };
@@ -169,7 +170,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * L::CHUNK_BYTES + (kk % 4) * 32;
-          if (elect_one()) umma_ss(TS[t], umma_desc_kmajor(q_smem + t * L::TILE_BYTES + off),
+          if (leader) umma_ss(TS[t], umma_desc_kmajor(q_smem + t * L::TILE_BYTES + off),
                   umma_desc_kmajor(k_smem + s * L::TILE_BYTES + off), idesc_qk, kk != 0);
         }
         if (elect_one()) umma_commit(&s_ready[t]);
@@ -177,7 +178,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto issue_pv = [&](int t, int s, int j) {
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
-          if (elect_one()) umma_ts(TO[t], TS[t] + kk * 8,
+          if (leader) umma_ts(TO[t], TS[t] + kk * 8,
                   umma_desc_mnmajor(v_smem + s * L::TILE_BYTES + kk * 2048, L::CHUNK_BYTES), idesc_pv,
                   (j | kk) != 0);
         }

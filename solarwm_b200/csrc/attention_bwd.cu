@@ -27,10 +27,12 @@
 // as B of the accumulate GEMMs.  P^T / dS are written back to TMEM as packed bf16 over columns
 // [32g, 32g+16) of the S / dP tiles and read from there as the A operand of the accumulate MMAs.
 //
-// TMEM columns: stat0 [0,64) stat1 [64,128);
-//   dQ mode:     buf0 {S [128,192) dP [192,256)}  buf1 {S [256,320) dP [320,384)}  dQ [384,512)
-//   dK/dV mode:  S [128,192)  dP [192,256)  dV [256,384)  dK [384,512); with single tiles the chains
-//                S_j -> P_j -> dV_j -> S_j+1  and  dP_j -> dS_j -> dK_j -> dP_j+1  run side by side
+// TMEM columns:
+//   dQ mode:     Q [0,64)  dO [64,128)  buf0 {S [128,192) dP [192,256)}  buf1 {S [256,320) dP [320,384)}  dQ [384,512)
+//   dK/dV mode:  K [0,64)  S0 [64,128)  S1 [128,192)  dP [192,256)  dV [256,384)  dK [384,512); V stays in
+//                shared memory (its score MMAs take both operands from there) so that S has two buffers:
+//                S_j+1 is computed while the compute warpgroups turn S_j into P_j, which shortens the
+//                S_j -> P_j -> dV_j chain that otherwise paces this mode
 // Every wait is bounded (sm100.cuh).
 //
 // Replaces the flash_attn / cuDNN SDPA backward used by the reference
@@ -43,7 +45,7 @@ namespace solar {
 constexpr int BW_THREADS = 384;
 constexpr int ST_ROWS = 128;   // stationary tile rows
 constexpr int SR_ROWS = 64;    // streamed tile rows
-constexpr int BW_STAGES = 5;   // TMA latency (~1 us) spans more than one tile-time: prefetch three tiles ahead
+constexpr int BW_STAGES = 4;
 
 struct AttnBwdParams {
   int S_stat, S_stream, H, B;
@@ -72,7 +74,8 @@ struct BwdSmem {
   static constexpr int STAT_OFF = 0;                        // stat0 | stat1
   static constexpr int STRM_OFF = 2 * STAT_TILE;            // BW_STAGES x (stream0 | stream1)
   static constexpr int BAR_OFF = STRM_OFF + BW_STAGES * 2 * STRM_TILE;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int VEC_OFF = BAR_OFF + 256;             // per compute warp: 32 L2 + 32 delta floats
+  static constexpr int TOTAL = VEC_OFF + 8 * 64 * 4 + 1024;
 };
 
 __device__ __forceinline__ void bw_tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2,
@@ -107,16 +110,17 @@ __device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint8_t* region, int
 
 // A load the compiler may not sink to its first use: the prefetch below has to leave a whole tile
 // ahead of the values being needed.
-__device__ __forceinline__ float4 ld_f4_early(const float4* ptr) {
-  float4 v;
-  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr));
+__device__ __forceinline__ float ld_f1_early(const float* ptr) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
   return v;
 }
 
 // MODE 0 = dK/dV, MODE 1 = dQ.
 template <int HD, int MODE>
 __global__ void __launch_bounds__(BW_THREADS, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_constant__ CUtensorMap tmStrm1,
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
+                const __grid_constant__ CUtensorMap tmStrm0, const __grid_constant__ CUtensorMap tmStrm1,
                 const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
                 const AttnBwdParams p) {
   using L = BwdSmem<HD>;
@@ -134,7 +138,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
   uint64_t* s_free = ds_ready + 1;                   // 2 (commit of the accumulate warp)
   uint64_t* dp_free = s_free + 2;                    // 1 (dK/dV mode)
   uint64_t* acc_done = dp_free + 1;                  // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* stat_full = acc_done + 1;                // 1 (dK/dV mode: V tile landed in shared memory)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_full + 1);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -161,8 +166,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     mbar_init(&s_free[1], 1);
     mbar_init(dp_free, 1);
     mbar_init(acc_done, 1);
+    mbar_init(stat_full, 1);
     *abort_word = 0;
     mbar_fence_init();
+    tma_prefetch_desc(&tmStat1);
     tma_prefetch_desc(&tmStrm0);
     tma_prefetch_desc(&tmStrm1);
   }
@@ -176,16 +183,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
   const uint32_t tmem_base_v = *tmem_slot;
   const uint32_t tmem_base = tmem_base_v;
   // TMEM columns of the working tiles (see the header comment)
-  constexpr uint32_t COL_STAT1 = 64;
-  constexpr uint32_t COL_BUF = 128;                       // S at +0, dP at +64 (second buffer +128 in dQ mode)
+  constexpr uint32_t COL_STAT1 = 64;                      // dQ mode only (dK/dV keeps V in shared memory)
   constexpr uint32_t COL_ACC0 = MODE == 0 ? 256 : 384;    // dV or dQ
   constexpr uint32_t COL_ACC1 = 384;                      // dK
+  // S tile of buffer b (two buffers in both modes) and the dP tile that goes with it
+  auto col_S = [](int b) -> uint32_t { return MODE == 0 ? 64u + 64u * b : 128u + 128u * b; };
+  auto col_D = [](int b) -> uint32_t { return MODE == 0 ? 192u : 192u + 128u * b; };
 
   if (warp == 0) {
     // -------------------------------------------------------------- TMA producer (streamed ring)
     setmaxnreg_dec<72>();
     if (lane == 0) {
       long long w_empty = 0;
+      if (MODE == 0) {
+        mbar_expect_tx(stat_full, L::STAT_TILE);
+#pragma unroll
+        for (int c = 0; c < L::CHUNKS; ++c)
+          tma_load_4d(smem + L::STAT_OFF + L::STAT_TILE + c * L::STAT_CHUNK, &tmStat1, stat_full, c * 64, head, row0, batch);
+      }
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % BW_STAGES;
         const uint32_t ph = (j / BW_STAGES) & 1;
@@ -211,6 +226,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     // warp-uniform; one elected lane issues each tcgen05 instruction.
     setmaxnreg_dec<72>();
     {
+      const bool leader = elect_one();
       const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_v, 0);
       constexpr uint32_t idesc_score = umma_idesc_bf16(128, SR_ROWS, 0, 0);   // [128 x 64], K = HD
       const uint32_t strm = __shfl_sync(0xffffffffu, smem_u32(smem + L::STRM_OFF), 0);
@@ -225,18 +241,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t ob = (kk / 4) * L::STRM_CHUNK + (kk % 4) * 32;
-          if (elect_one()) umma_ts(t_dst, t_stat + kk * 8, d0 + (ob >> 4), idesc_score, kk != 0);
+          if (leader) umma_ts(t_dst, t_stat + kk * 8, d0 + (ob >> 4), idesc_score, kk != 0);
+        }
+      };
+      // dK/dV mode: dP^T = V dO^T reads V from shared memory (A and B both shared-memory descriptors)
+      const uint32_t stat1_smem = __shfl_sync(0xffffffffu, smem_u32(smem + L::STAT_OFF + L::STAT_TILE), 0);
+      auto score_mma_ss = [&](uint32_t t_dst, uint32_t a_tile, uint32_t s_tile) {
+        const uint64_t a0 = umma_desc_kmajor(a_tile), d0 = umma_desc_kmajor(s_tile);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t oa = (kk / 4) * L::STAT_CHUNK + (kk % 4) * 32;
+          const uint32_t ob = (kk / 4) * L::STRM_CHUNK + (kk % 4) * 32;
+          if (leader) umma_ss(t_dst, a0 + (oa >> 4), d0 + (ob >> 4), idesc_score, kk != 0);
         }
       };
       bool ok = wwait(stat_ready, 0, ST_TIMEOUT_FULL);
+      if (ok && MODE == 0) ok = wwait(stat_full, 0, ST_TIMEOUT_FULL);
       tc_fence_after();
       const long long loop0 = tracing ? clock64() : 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % BW_STAGES;
-        const int b = MODE == 1 ? (j & 1) : 0;
-        const uint32_t free_par = (MODE == 1 ? ((j >> 1) & 1) : (j & 1)) ^ 1;
+        const int b = j & 1;
+        const uint32_t free_par = ((j >> 1) & 1) ^ 1;
         const uint32_t s0 = strm + s * 2 * L::STRM_TILE;
-        const uint32_t tS = tmem_base + COL_BUF + b * 128, tD = tS + 64;
+        const uint32_t tS = tmem_base + col_S(b), tD = tmem_base + col_D(b);
         long long c0 = tracing ? clock64() : 0;
         if (!wwait(&strm_full[s], (j / BW_STAGES) & 1, ST_TIMEOUT_FULL)) { ok = false; break; }
         if (tracing) w_full += clock64() - c0;
@@ -246,14 +274,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
         tc_fence_after();
         score_mma(tS, tmem_base, s0);
         if (MODE == 0) {
-          if (elect_one()) umma_commit(&s_ready[0]);
+          if (elect_one()) umma_commit(&s_ready[b]);
           c0 = tracing ? clock64() : 0;
-          if (!wwait(dp_free, free_par, ST_TIMEOUT_OTHER)) { ok = false; break; }      // readers of the old dP / dS are done
+          if (!wwait(dp_free, (j & 1) ^ 1, ST_TIMEOUT_OTHER)) { ok = false; break; }   // readers of the old dP / dS are done
           if (tracing) w_free += clock64() - c0;
           tc_fence_after();
+          score_mma_ss(tD, stat1_smem, s0 + L::STRM_TILE);
+          if (elect_one()) umma_commit(dp_ready);
+        } else {
+          score_mma(tD, tmem_base + COL_STAT1, s0 + L::STRM_TILE);
+          if (elect_one()) umma_commit(&s_ready[b]);
         }
-        score_mma(tD, tmem_base + COL_STAT1, s0 + L::STRM_TILE);
-        if (elect_one()) umma_commit(MODE == 0 ? dp_ready : &s_ready[b]);
       }
       if (tracing && lane == 0) {
         p.trace[MODE * 8 + 0] = clock64() - loop0;
@@ -266,6 +297,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     // -------------------------------------------------------------- accumulate MMA warp
     setmaxnreg_dec<72>();
     {
+      const bool leader = elect_one();
       const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_v, 0);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);          // [128 x HD], K = 64, B MN-major
       const uint32_t strm = __shfl_sync(0xffffffffu, smem_u32(smem + L::STRM_OFF), 0);
@@ -279,16 +311,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
         const uint64_t d0 = umma_desc_mnmajor(s_tile, L::STRM_CHUNK);
 #pragma unroll
         for (int kk = 0; kk < SR_ROWS / 16; ++kk)
-          if (elect_one())
+          if (leader)
             umma_ts(t_dst, t_a + (kk / 2) * 32 + (kk % 2) * 8, d0 + ((kk * 2048) >> 4), idesc_acc, (t | kk) != 0);
       };
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % BW_STAGES;
-        const int b = MODE == 1 ? (j & 1) : 0;
-        const uint32_t par = MODE == 1 ? ((j >> 1) & 1) : (j & 1);
+        const int b = j & 1;
+        const uint32_t par = (j >> 1) & 1;
         const uint32_t s0 = strm + s * 2 * L::STRM_TILE;
-        const uint32_t tS = tmem_base + COL_BUF + b * 128, tD = tS + 64;
+        const uint32_t tS = tmem_base + col_S(b), tD = tmem_base + col_D(b);
         // the stage was filled before the score MMAs ran; observing its barrier orders this warp after the copy
         if (!wwait(&strm_full[s], (j / BW_STAGES) & 1, ST_TIMEOUT_FULL)) { ok = false; break; }
         long long c0 = tracing ? clock64() : 0;
@@ -297,9 +329,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
         tc_fence_after();
         if (MODE == 0) {
           acc_mma(tmem_base + COL_ACC0, tS, s0 + L::STRM_TILE, j);          // dV += P^T dO_j
-          if (elect_one()) umma_commit(&s_free[0]);
+          if (elect_one()) umma_commit(&s_free[b]);
           c0 = tracing ? clock64() : 0;
-          if (!wwait(ds_ready, par, ST_TIMEOUT_OTHER)) { ok = false; break; }
+          if (!wwait(ds_ready, j & 1, ST_TIMEOUT_OTHER)) { ok = false; break; }
           if (tracing) w_p += clock64() - c0;
           tc_fence_after();
           acc_mma(tmem_base + COL_ACC1, tD, s0, j);                          // dK += dS^T Q_j
@@ -326,7 +358,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     const float c = p.scale_log2, sc = p.scale;
     // ---- stationary rows: global -> registers -> TMEM as packed bf16 (warpgroup g loads tensor g).
     // Rows past the end are zero; their results are never stored.
-    {
+    if (MODE == 1 || wg == 0) {
       const __nv_bfloat16* src = wg == 0 ? p.stat0 : p.stat1;
       const long long ss = wg == 0 ? p.stat0_ss : p.stat1_ss, sb = wg == 0 ? p.stat0_sb : p.stat1_sb;
       const int grow = row0 + row;
@@ -349,8 +381,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(stat_ready);
     }
+    mbar_arrive(stat_ready);
     float my_L2 = 0.f, my_delta = 0.f;
     if (MODE == 1) {
       my_L2 = p.L2[vec_base + row0 + row];
@@ -358,27 +390,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
     }
     bool ok = true;
     long long w_s = 0;
-    long long seg[6] = {0, 0, 0, 0, 0, 0};   // ld S | P math | st P + arrive | ld dP | dS math | st dS + arrive
+    long long seg[7] = {0, 0, 0, 0, 0, 0, 0};   // ld S | P math | st P + arrive | ld dP | dS math | st dS + arrive
     const long long cloop0 = tracing ? clock64() : 0;
     const float2 c2 = make_float2(c, c), sc2 = make_float2(sc, sc);
     // dK/dV mode: the per-query L2 / delta values of a tile are the same for every thread and change
-    // with the tile; they are fetched one tile ahead so their L2-cache latency never sits between a
-    // barrier and the TMEM round trip that follows it.
-    float4 vL[8], vD[8];
+    // with the tile.  Lane l of every warp fetches element l of the next tile's two vectors a whole tile
+    // ahead (two registers); at the start of a tile the warp parks them in its own 256 bytes of shared
+    // memory and reads them back as broadcast float4s, so no global-load latency sits inside a tile.
+    float* vec_smem = reinterpret_cast<float*>(smem + L::VEC_OFF) + (warp - 4) * 64;
+    float nxtL = 0.f, nxtD = 0.f;
     if (MODE == 0) {
-      const float4* l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + wg * 32);
-      const float4* d4 = reinterpret_cast<const float4*>(p.delta + vec_base + wg * 32);
-#pragma unroll
-      for (int g = 0; g < 8; ++g) { vL[g] = ld_f4_early(l4 + g); vD[g] = ld_f4_early(d4 + g); }
+      nxtL = __ldg(p.L2 + vec_base + wg * 32 + lane);
+      nxtD = __ldg(p.delta + vec_base + wg * 32 + lane);
     }
     // Both warpgroups work on every streamed tile: warpgroup g owns columns [32g, 32g+32) of the
     // 64-column S / dP tile and writes its packed bf16 results over columns [32g, 32g+16).
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = MODE == 1 ? (j & 1) : 0;
-      const uint32_t par = MODE == 1 ? ((j >> 1) & 1) : (j & 1);
-      const uint32_t tS = tmem_base + lane_off + COL_BUF + b * 128 + wg * 32, tD = tS + 64;
+    auto tile = [&](const int j) -> bool {
+      const int b = j & 1;
+      const uint32_t par = (j >> 1) & 1;
+      const uint32_t tS = tmem_base + lane_off + col_S(b) + wg * 32, tD = tmem_base + lane_off + col_D(b) + wg * 32;
       long long c0 = tracing ? clock64() : 0;
-      if (!mbar_wait(&s_ready[b], par, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait(&s_ready[b], par, abort_word, ST_TIMEOUT_TMEM_FULL)) return false;
       if (tracing) w_s += clock64() - c0;
       tc_fence_after();
       uint32_t s[32], d[32];
@@ -387,17 +419,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       if (MODE == 1) tmem_ld_32x32(tD, d);
       tmem_ld_wait();
       if (tracing) { const long long q1 = clock64(); seg[0] += q1 - q0; q0 = q1; }
-      float4 cL[8], cD[8];
+      const float4* cL = reinterpret_cast<const float4*>(vec_smem);
+      const float4* cD = reinterpret_cast<const float4*>(vec_smem + 32);
       if (MODE == 0) {
-#pragma unroll
-        for (int g = 0; g < 8; ++g) { cL[g] = vL[g]; cD[g] = vD[g]; }
+        __syncwarp();                       // the previous tile's reads of the parking area are done
+        vec_smem[lane] = -nxtL;             // both vectors are parked negated: the math below only adds them
+        vec_smem[32 + lane] = -nxtD;
+        __syncwarp();
         if (j + 1 < n_tiles) {
-          const float4* l4 = reinterpret_cast<const float4*>(p.L2 + vec_base + (j + 1) * SR_ROWS + wg * 32);
-          const float4* d4 = reinterpret_cast<const float4*>(p.delta + vec_base + (j + 1) * SR_ROWS + wg * 32);
-#pragma unroll
-          for (int g = 0; g < 8; ++g) { vL[g] = ld_f4_early(l4 + g); vD[g] = ld_f4_early(d4 + g); }
+          nxtL = ld_f1_early(p.L2 + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
+          nxtD = ld_f1_early(p.delta + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
         }
       }
+      if (tracing) { const long long q1 = clock64(); seg[6] += q1 - q0; q0 = q1; }
       uint32_t pk[16], dk[16];
       // P = exp2(S * c - L2); kept as fp32 in s[] for the dS product
 #pragma unroll
@@ -405,7 +439,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
         float2 nL[2];
         if (MODE == 0) {
           const float4 a = cL[g];
-          nL[0] = make_float2(-a.x, -a.y); nL[1] = make_float2(-a.z, -a.w);
+          nL[0] = make_float2(a.x, a.y); nL[1] = make_float2(a.z, a.w);
         } else {
           nL[0] = nL[1] = make_float2(-my_L2, -my_L2);
         }
@@ -423,10 +457,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
         tmem_st_32x16(tS, pk);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&p_ready[0]);
+        mbar_arrive(&p_ready[b]);
         if (tracing) { const long long q1 = clock64(); seg[2] += q1 - q0; q0 = q1; }
         c0 = tracing ? clock64() : 0;
-        if (!mbar_wait(dp_ready, par, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (!mbar_wait(dp_ready, j & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) return false;
         if (tracing) w_s += clock64() - c0;
         tc_fence_after();
         q0 = tracing ? clock64() : 0;
@@ -437,18 +471,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       // dS = P * (dP - delta) * scale
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
-        float2 Dl[2];
+        float2 nD[2];                        // minus delta
         if (MODE == 0) {
           const float4 bb = cD[g];
-          Dl[0] = make_float2(bb.x, bb.y); Dl[1] = make_float2(bb.z, bb.w);
+          nD[0] = make_float2(bb.x, bb.y); nD[1] = make_float2(bb.z, bb.w);
         } else {
-          Dl[0] = Dl[1] = make_float2(my_delta, my_delta);
+          nD[0] = nD[1] = make_float2(-my_delta, -my_delta);
         }
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
           const int e = g * 4 + h2 * 2;
           const float2 pv = make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1]));
-          float2 dd = make_float2(__uint_as_float(d[e]) - Dl[h2].x, __uint_as_float(d[e + 1]) - Dl[h2].y);
+          float2 dd = __fadd2_rn(make_float2(__uint_as_float(d[e]), __uint_as_float(d[e + 1])), nD[h2]);
           dd = __fmul2_rn(__fmul2_rn(pv, dd), sc2);
           dk[e >> 1] = pack_bf16x2(dd.x, dd.y);
         }
@@ -459,11 +493,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStrm0, const __grid_consta
       tc_fence_before();
       mbar_arrive(MODE == 0 ? ds_ready : &p_ready[b]);
       if (tracing) { const long long q1 = clock64(); seg[5] += q1 - q0; q0 = q1; }
-    }
+      return true;
+    };
+#pragma unroll 1
+    for (int j = 0; j < n_tiles && ok; ++j) ok = tile(j);
     if (tracing && threadIdx.x == 128) {
       p.trace[MODE * 8 + 3] = clock64() - cloop0;
       p.trace[MODE * 8 + 4] = w_s;
-      for (int i = 0; i < 6; ++i) p.trace[16 + MODE * 8 + i] = seg[i];
+      for (int i = 0; i < 7; ++i) p.trace[16 + MODE * 8 + i] = seg[i];
     }
     // ---- epilogue: accumulators -> bf16 -> shared memory staging -> TMA store
     if (ok) ok = mbar_wait(acc_done, 0, abort_word, ST_TIMEOUT_OTHER);
@@ -560,7 +597,7 @@ static int launch_bwd(const CUtensorMap* maps, const AttnBwdParams& p, cudaStrea
     configured = true;
   }
   dim3 grid((p.S_stat + ST_ROWS - 1) / ST_ROWS, p.H, p.B);
-  kern<<<grid, BW_THREADS, BwdSmem<HD>::TOTAL, st>>>(maps[2], maps[3], maps[4], maps[5], p);
+  kern<<<grid, BW_THREADS, BwdSmem<HD>::TOTAL, st>>>(maps[1], maps[2], maps[3], maps[4], maps[5], p);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -615,6 +652,7 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
     CUtensorMap m[6];
     p.stat0 = (const __nv_bfloat16*)k; p.stat0_ss = k_ss; p.stat0_sb = k_sb;
     p.stat1 = (const __nv_bfloat16*)v; p.stat1_ss = v_ss; p.stat1_sb = v_sb;
+    if ((rc = bshd_map(&m[1], v, B, Sk, H, D, v_ss, v_sb, ST_ROWS))) return rc;     // V stays in shared memory
     if ((rc = bshd_map(&m[2], q, B, Sq, H, D, q_ss, q_sb, SR_ROWS))) return rc;
     if ((rc = bshd_map(&m[3], dout, B, Sq, H, D, do_ss, do_sb, SR_ROWS))) return rc;
     if ((rc = bshd_map(&m[4], dv, B, Sk, H, D, c_ss, c_ss * Sk, ST_ROWS))) return rc;
@@ -632,6 +670,7 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
     if ((rc = bshd_map(&m[3], v, B, Sk, H, D, v_ss, v_sb, SR_ROWS))) return rc;
     if ((rc = bshd_map(&m[4], dq, B, Sq, H, D, c_ss, c_ss * Sq, ST_ROWS))) return rc;
     m[5] = m[4];
+    m[1] = m[4];   // the stationary-tile map is unused in dQ mode
     p.S_stat = Sq; p.S_stream = Sk;
     rc = D == 128 ? launch_bwd<128, 1>(m, p, st) : launch_bwd<64, 1>(m, p, st);
     if (rc) return rc;

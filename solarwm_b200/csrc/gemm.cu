@@ -148,6 +148,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ MMA issuer
     // Every lane runs the loop (warp-uniform addresses and descriptors); one elected lane issues.
     {
+      const bool leader = elect_one();   // one lane issues; elected once, not per instruction
       auto wwait = [&](uint64_t* bar, uint32_t parity, volatile int* aw, int code) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, aw, code));
       };
@@ -178,7 +179,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                         : umma_desc_kmajor(sa + kk * 32);
             const uint64_t bdesc = B_MN ? umma_desc_mnmajor(sb + kk * 2048, 64 * BK * 2)
                                         : umma_desc_kmajor(sb + kk * 32);
-            if (elect_one()) umma_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
+            if (leader) umma_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
           }
           if (elect_one()) umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) {

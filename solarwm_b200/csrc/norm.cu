@@ -143,6 +143,84 @@ __global__ void __launch_bounds__(ROW_THREADS) norm_modulate_fwd_kernel(NormModP
   }
 }
 
+
+// Warp-per-row variant of the forward: lane l owns the 16-byte vectors l, l+32, ... of the row (NV of
+// them), all loads of a row are in flight at once and both reductions are warp shuffles -- no shared
+// memory and no block barrier.  Used whenever the row fits (D <= NV * 256).
+template <int NV>
+__global__ void __launch_bounds__(256) norm_modulate_fwd_warp_kernel(NormModParams p, long long rows) {
+  const long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int nvec = p.D >> 3;
+  const __nv_bfloat16* xr = p.x + row * p.ldx;
+  uint4 raw[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = lane + i * 32;
+    raw[i] = vi < nvec ? *reinterpret_cast<const uint4*>(xr + vi * 8) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const float2 a = unpack_bf16x2(raw[i].x), b = unpack_bf16x2(raw[i].y), c = unpack_bf16x2(raw[i].z),
+                 d = unpack_bf16x2(raw[i].w);
+    s += (a.x + a.y) + (b.x + b.y) + (c.x + c.y) + (d.x + d.y);
+  }
+  float mean = 0.f;
+  if (p.mode != 1) mean = warp_sum(s) / p.D;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + i * 32 < nvec) {
+      const float2 a = unpack_bf16x2(raw[i].x), b = unpack_bf16x2(raw[i].y), c = unpack_bf16x2(raw[i].z),
+                   d = unpack_bf16x2(raw[i].w);
+      const float e[8] = {a.x - mean, a.y - mean, b.x - mean, b.y - mean, c.x - mean, c.y - mean, d.x - mean, d.y - mean};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += e[k] * e[k];
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / p.D + p.eps);
+  if (lane == 0 && p.stats) {
+    p.stats[row * 2] = mean;
+    p.stats[row * 2 + 1] = rstd;
+  }
+  const float* sh = nullptr; const float* sc = nullptr;
+  if (p.scale) {
+    const long long g = p.gm(row);
+    sc = p.scale + g * p.mod_stride;
+    sh = p.shift + g * p.mod_stride;
+  }
+  __nv_bfloat16* yr = p.y + row * p.ldy;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      const float2 a0 = unpack_bf16x2(raw[i].x), b0 = unpack_bf16x2(raw[i].y), c0 = unpack_bf16x2(raw[i].z),
+                   d0 = unpack_bf16x2(raw[i].w);
+      float o[8] = {a0.x, a0.y, b0.x, b0.y, c0.x, c0.y, d0.x, d0.y}, a[8], c[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (o[e] - mean) * rstd;
+      if (p.mode >= 1) {
+        load8f(p.w + vi * 8, a);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] *= a[e];
+      }
+      if (p.mode == 2) {
+        load8f(p.b + vi * 8, a);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += a[e];
+      }
+      if (sc) {
+        load8f(sc + vi * 8, a);
+        load8f(sh + vi * 8, c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = o[e] * (1.f + a[e]) + c[e];
+      }
+      store8(yr + vi * 8, o);
+    }
+  }
+}
+
 // dx for the row.  dy is the gradient of the modulated output.
 struct NormModBwdParams {
   const __nv_bfloat16* dy; long long lddy;
@@ -526,7 +604,13 @@ extern "C" int solar_norm_modulate_fwd(const void* x, long long ldx, void* y, lo
   NormModParams p{(const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)y, ldy, stats, w, b, shift, scale,
                   mod_stride, GroupMap{group_table, rows_per_group > 0 ? rows_per_group : 1, group_offset},
                   D, eps, mode};
-  norm_modulate_fwd_kernel<<<(unsigned)rows, ROW_THREADS, 0, (cudaStream_t)stream>>>(p);
+  const unsigned grid8 = static_cast<unsigned>((rows + 7) / 8);
+  if (D <= 12 * 256)
+    norm_modulate_fwd_warp_kernel<12><<<grid8, 256, 0, (cudaStream_t)stream>>>(p, rows);
+  else if (D <= 24 * 256)
+    norm_modulate_fwd_warp_kernel<24><<<grid8, 256, 0, (cudaStream_t)stream>>>(p, rows);
+  else
+    norm_modulate_fwd_kernel<<<(unsigned)rows, ROW_THREADS, 0, (cudaStream_t)stream>>>(p);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }
