@@ -1,0 +1,67 @@
+"""``solar-renderer``: train / distill / render on the configured (or synthetic) data.
+
+    python -m solarwm_b200.renderer.cli train   --steps N [--arch tiny] [--patterns shared=1,known_frames=1]
+    python -m solarwm_b200.renderer.cli distill --steps N
+    python -m solarwm_b200.renderer.cli render  --out DIR [--steps 8]
+
+(reference: solar/renderer/__main__.py, render.py)."""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from ..data.synthetic import h3_sample
+from ..models.h3 import h3_preset
+from .core import OmniFlowTrainer, render
+from .dmd import RendererDMDTrainer
+from .known_degree import ObservationProfile
+
+
+def _sample(cfg, seed, frames=4, size=8):
+    s = h3_sample(latent_frames=frames, height=size, width=size, prompt_len=8, text_dim=cfg.text_dim, seed=seed)
+    s["structure_latents"] = torch.randn(s["target_latents"].shape, generator=torch.Generator().manual_seed(seed + 7))
+    s["camera_w2c"] = torch.eye(4).repeat(frames + 1, 1, 1)
+    s["shape"] = tuple(s["target_latents"].shape)
+    return s
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="solar-renderer")
+    ap.add_argument("command", choices=["train", "distill", "render"])
+    ap.add_argument("--arch", default="tiny")
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--lora-rank", type=int, default=4)
+    ap.add_argument("--patterns", default="shared=1,known_frames=1,known_region=1,confidence_map=1,ramp=1")
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    args = ap.parse_args(argv)
+    cfg = h3_preset(args.arch)
+    cfg.lora_rank = args.lora_rank
+    if args.command == "train":
+        prof = ObservationProfile(patterns=tuple((k, float(v)) for k, v in (p.split("=") for p in args.patterns.split(","))))
+        tr = OmniFlowTrainer(cfg, args.device, prof, lr=1e-3)
+        for i in range(args.steps):
+            loss = tr.train_step(_sample(cfg, i))
+            print(json.dumps({"step": i + 1, "loss": float(loss), "pattern": tr.last_plan.pattern,
+                              "generated_fraction": tr.last_plan.generated_fraction}))
+    elif args.command == "distill":
+        tr = RendererDMDTrainer(cfg, args.device, critic_updates_per_student=2, lr_student=1e-3, lr_critic=1e-3)
+        for i in range(args.steps):
+            print(json.dumps({"step": i + 1, **tr.train_outer_step(_sample(cfg, i))}))
+    else:
+        from ..models.h3 import H3DiT
+
+        model = H3DiT(cfg, device=args.device, dtype=torch.bfloat16 if args.device == "cuda" else torch.float32)
+        lat = render(model, _sample(cfg, 0), steps=max(args.steps, 2))
+        if args.out:
+            Path(args.out).mkdir(parents=True, exist_ok=True)
+            torch.save(lat.cpu(), Path(args.out) / "latents.pt")
+        print(json.dumps({"latents": list(lat.shape), "finite": bool(torch.isfinite(lat.float()).all())}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

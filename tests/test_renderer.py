@@ -1,0 +1,62 @@
+"""Renderer: observation plans, omni flow-matching trainer, pinned rendering, DMD distillation (CPU)."""
+import numpy as np
+import pytest
+import torch
+
+from solarwm_b200.renderer import known_degree as kd
+
+
+def test_observation_plans_cover_patterns_and_invariants():
+    prof = kd.ObservationProfile(patterns=tuple((p, 1.0) for p in kd.PATTERNS), dropout=(("camera", 0.5), ("observation", 0.3)))
+    rng = np.random.default_rng(0)
+    seen = set()
+    for _ in range(200):
+        plan = kd.sample_plan(prof, frames=6, grid_height=6, grid_width=8, base_time=float(rng.random()), shift=12.0, rng=rng,
+                              given=np.clip(rng.random((6, 6, 8)) - 0.3, 0, 1))
+        seen.add(plan.pattern)
+        assert plan.row_times.shape == (6 * 6 * 8,) and plan.loss_rows.any()
+        assert plan.row_times.min() >= 0 and plan.row_times.max() <= prof.hard_level + 1e-6
+        assert np.allclose(plan.row_times * prof.levels, np.round(plan.row_times * prof.levels), atol=1e-3)
+        assert (plan.row_times[plan.loss_rows] < prof.hard_level).all()
+        assert (plan.row_times >= min(plan.base_time, plan.row_times.min()) - 1e-6).all()
+    assert seen == set(kd.PATTERNS)
+    # same generator state -> same plan
+    a = kd.sample_plan(prof, frames=4, grid_height=3, grid_width=3, base_time=0.3, shift=12.0, rng=np.random.default_rng(5))
+    b = kd.sample_plan(prof, frames=4, grid_height=3, grid_width=3, base_time=0.3, shift=12.0, rng=np.random.default_rng(5))
+    assert a.pattern == b.pattern and np.array_equal(a.row_times, b.row_times)
+    assert kd.confidence_to_known_degree(0.0) == 1.0 and kd.confidence_to_known_degree(np.inf) == 0.0
+    with pytest.raises(ValueError):
+        kd.ObservationProfile(patterns=(("nope", 1.0),))
+    assert abs(kd.unshift_time(float(kd.shift_time(0.37, 12.0)), 12.0) - 0.37) < 1e-12
+
+
+def test_trainer_render_and_distillation():
+    from solarwm_b200.renderer.cli import _sample, main
+    from solarwm_b200.renderer.core import OmniFlowTrainer, render
+    from solarwm_b200.renderer.dmd import RendererDMDTrainer, structure_guided
+    from solarwm_b200.models.h3 import h3_preset
+
+    cfg = h3_preset("tiny")
+    cfg.lora_rank = 4
+    prof = kd.ObservationProfile(patterns=(("known_frames", 1.0), ("known_region", 1.0)))
+    tr = OmniFlowTrainer(cfg, "cpu", prof, lr=1e-3)
+    before = [p.detach().clone() for p in tr.model.trainable_parameters()]
+    loss = tr.train_step(_sample(cfg, 0))
+    assert torch.isfinite(loss) and 0 < tr.last_plan.generated_fraction < 1
+    assert any(not torch.equal(a, b) for a, b in zip(before, tr.model.trainable_parameters()))
+    # rendering with fully known rows returns them (degree 1 rows are pinned to the known clip)
+    s = _sample(cfg, 1)
+    known = s["target_latents"]
+    deg = torch.zeros(4 * 4 * 4)
+    deg[:16] = 1.0                                    # the first frame is given
+    out = render(tr.model, s, steps=3, known=known, known_degree=deg)
+    assert out.shape == known.shape and torch.isfinite(out).all()
+    assert torch.allclose(out[:, 0].float(), known[:, 0].float(), atol=2e-2)
+    assert not torch.allclose(out[:, 1].float(), known[:, 1].float(), atol=1e-1)
+    assert torch.equal(structure_guided(torch.ones(2), torch.zeros(2), 2.0), torch.full((2,), 2.0))
+    d = RendererDMDTrainer(cfg, "cpu", student_steps=2, critic_updates_per_student=2, lr_student=1e-3, lr_critic=1e-3)
+    r0 = d.train_outer_step(s)
+    d.train_outer_step(s)
+    r2 = d.train_outer_step(s)
+    assert "student" not in r0 and "student" in r2 and r2["critic"] == r2["critic"]
+    assert main(["train", "--steps", "1", "--device", "cpu"]) == 0
