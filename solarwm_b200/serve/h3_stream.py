@@ -47,6 +47,7 @@ class H3StreamConfig:
     fx: float = 0.505
     fy: float = 0.898
     use_cuda_graph: bool = True
+    memory_latents: int = 0            # capacity of the retrieved-memory segment (0 = no memory rows)
     seed: int = 0
 
 
@@ -124,7 +125,11 @@ class H3StreamingGenerator:
             view[self.n_text:] = anchor_w2c.float()
         self.cond_view = view
         # ---- caches
-        cap = self.n_cond + (cfg.window_chunks + 1) * self.chunk_rows
+        # cache rows: [memory segment | condition | history chunks | current chunk]; the memory segment is filled
+        # from its END backwards, so the live rows always form one contiguous range
+        self.o_cond = cfg.memory_latents * rows
+        self.mem_rows = 0
+        cap = self.o_cond + self.n_cond + (cfg.window_chunks + 1) * self.chunk_rows
         a_local = self.heads_local * mc.attention_head_dim
         self.kv = [_LayerKV(torch.zeros(cap, a_local, dtype=dt, device=dev), torch.zeros(cap, a_local, dtype=dt, device=dev))
                    for _ in m.blocks]
@@ -155,10 +160,14 @@ class H3StreamingGenerator:
         return slice(self.sp.rank * per, (self.sp.rank + 1) * per)
 
     # ------------------------------------------------------------------------------------ network
-    def _evaluate(self, x_rows, t_scalar, pos, tags, view, key_base: int, n_rows: int, write_only: bool = False):
+    def _evaluate(self, x_rows, t_scalar, pos, tags, view, key_base: int, n_rows: int, write_only: bool = False,
+                  key_lo: int = None, key_hi: int = None):
         """Run the 50 blocks on ``n_rows`` new rows (sharded over SP) whose keys / values are written at
-        cache rows ``[key_base, key_base + n_rows)`` and which attend to cache rows ``[0, key_base + n_rows)``.
-        Returns the output rows of this rank (or None with ``write_only``, used for the condition rows)."""
+        cache rows ``[key_base, key_base + n_rows)`` and which attend to cache rows ``[key_lo, key_hi)``
+        (default: everything from the first live row up to and including the new rows).
+        Returns the output rows of this rank (or None with ``write_only``, used for condition / memory rows)."""
+        key_lo = self.o_cond - self.mem_rows if key_lo is None else key_lo
+        key_hi = key_base + n_rows if key_hi is None else key_hi
         m, mc = self.model, self.model.cfg
         H, hd, hl = mc.num_attention_heads, mc.attention_head_dim, self.heads_local
         loc = self._local(n_rows)
@@ -181,9 +190,9 @@ class H3StreamingGenerator:
                 q, k, v = self.sp.scatter_heads(q, k, v)
             kv.k[key_base:key_base + n_rows] = k.reshape(n_rows, hl * hd)
             kv.v[key_base:key_base + n_rows] = v.reshape(n_rows, hl * hd)
-            n_keys = key_base + n_rows
-            o = ops.attention(q.reshape(1, n_rows, hl, hd), kv.k[:n_keys].view(1, n_keys, hl, hd),
-                              kv.v[:n_keys].view(1, n_keys, hl, hd))
+            n_keys = key_hi - key_lo
+            o = ops.attention(q.reshape(1, n_rows, hl, hd), kv.k[key_lo:key_hi].view(1, n_keys, hl, hd),
+                              kv.v[key_lo:key_hi].view(1, n_keys, hl, hd))
             if self.P > 1:
                 o = self.sp.gather_heads(o)
             o = ops.head_norm_rope_prope(o.reshape(S, H * hd), None, None, None, cam_o, heads=H, **kw)
@@ -216,12 +225,13 @@ class H3StreamingGenerator:
     def _commit_condition(self) -> None:
         """Text + anchor rows attend among themselves; their keys / values head the cache for good."""
         self._evaluate(self.cond_x, torch.tensor([0.999], device=self.device), self._tables(self.cond_pos, self.n_cond),
-                       self.cond_tags, self.cond_view, key_base=0, n_rows=self.n_cond, write_only=True)
+                       self.cond_tags, self.cond_view, key_base=self.o_cond, n_rows=self.n_cond, write_only=True,
+                       key_lo=self.o_cond)
 
     def _chunk_eval(self) -> None:
         """Evaluate the chunk in the static input slots against the current window -> ``self._out``."""
         cfg = self.cfg
-        base = self.n_cond + self.hist_chunks * self.chunk_rows
+        base = self.o_cond + self.n_cond + self.hist_chunks * self.chunk_rows
         first = 1 + self.hist_chunks * cfg.chunk_latents
         if first not in self._pos_cache:                               # built outside any graph capture
             pos = self._frame_pos([float(self._tpos[first + i]) for i in range(cfg.chunk_latents)])
@@ -241,13 +251,43 @@ class H3StreamingGenerator:
         if self.hist_chunks < cfg.window_chunks:
             self.hist_chunks += 1
             return
-        a, n = self.n_cond, cfg.window_chunks * self.chunk_rows
+        a, n = self.o_cond + self.n_cond, cfg.window_chunks * self.chunk_rows
         for kv in self.kv:
             kv.k[a:a + n] = kv.k[a + self.chunk_rows:a + self.chunk_rows + n].clone()
             kv.v[a:a + n] = kv.v[a + self.chunk_rows:a + self.chunk_rows + n].clone()
             kv.k[a:a + n] = ops.head_norm_rope_prope(kv.k[a:a + n], None, self._delta_cos, self._delta_sin, None,
                                                      heads=self.heads_local, rot_dims=mc.rot_dims,
                                                      sections=mc.rope_sections, eps=mc.eps)
+
+    # ------------------------------------------------------------------------------------ memory
+    @torch.no_grad()
+    def set_memory(self, latents: Optional[torch.Tensor], w2c: Optional[torch.Tensor] = None) -> None:
+        """Install retrieved latents [C, k, H, W] (k <= memory_latents) with their cameras [k, 4, 4] as extra
+        key rows for the following chunks.  The memory rows run through the network once as clean rows that
+        see the condition rows and one another; they sit temporally before the anchor frame.  ``None`` clears
+        the segment (reference: memory-bank rows of the packed document, memory_inference.py:126)."""
+        from ..backends.minimax_h3.layout import patchify_latents
+
+        cfg, m = self.cfg, self.model
+        rows = self.rows_per_latent
+        k = 0 if latents is None else latents.shape[1]
+        if k > cfg.memory_latents:
+            raise ValueError(f"{k} memory latents exceed the configured capacity {cfg.memory_latents}")
+        if k * rows != self.mem_rows:
+            self._graphs = None                 # the key range changes: a captured graph no longer applies
+        self.mem_rows = k * rows
+        if k == 0:
+            return
+        assert (k * rows) % self.P == 0, "memory rows must split evenly over the SP ranks"
+        span = float(self._tpos[2] - self._tpos[1])
+        t_mem = [float(self._tpos[0]) - (k - i) * span for i in range(k)]
+        pos = self._tables(self._frame_pos(t_mem), k * rows)
+        x = F_.linear(patchify_latents(latents.to(self.device, m.dtype)), m.proj_in)
+        view = torch.eye(4).repeat(k * rows, 1, 1) if w2c is None else w2c.float().repeat_interleave(rows, dim=0)
+        tags = torch.full((k * rows,), TAG_VIDEO, dtype=torch.int32, device=self.device)
+        lo = self.o_cond - k * rows
+        self._evaluate(x, torch.ones(1, device=self.device), pos, tags, view, key_base=lo, n_rows=k * rows,
+                       write_only=True, key_lo=lo, key_hi=self.o_cond + self.n_cond)
 
     # ------------------------------------------------------------------------------------ rollout
     def _noise(self):

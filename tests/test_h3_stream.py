@@ -70,3 +70,57 @@ def test_same_seed_same_stream():
     b, _ = _gen()
     for _ in range(3):
         assert torch.equal(a.next_chunk(None), b.next_chunk(None))
+
+
+def test_memory_rows_change_the_stream_and_can_be_cleared():
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+
+    def run(mem):
+        scfg = H3StreamConfig(grid_hw=(2, 3), chunk_latents=2, window_chunks=2, denoise_steps=2, use_cuda_graph=False,
+                              memory_latents=3)
+        g = H3StreamingGenerator(model, scfg)
+        torch.manual_seed(0)
+        g.start(torch.randn(6, cfg.text_dim), torch.randn(24, 1, 4, 6), torch.eye(4))
+        first = g.next_chunk(None)
+        if mem == "set":
+            g.set_memory(torch.randn(24, 2, 4, 6, generator=torch.Generator().manual_seed(9)), torch.eye(4).repeat(2, 1, 1))
+        elif mem == "set-clear":
+            g.set_memory(torch.randn(24, 2, 4, 6, generator=torch.Generator().manual_seed(9)), None)
+            g.set_memory(None)
+        return first, g.next_chunk(None), g
+
+    f0, plain, _ = run("none")
+    f1, with_mem, g = run("set")
+    f2, cleared, _ = run("set-clear")
+    assert torch.equal(f0, f1) and torch.equal(f0, f2)
+    assert g.mem_rows == 2 * 6 and not torch.allclose(plain, with_mem)
+    assert torch.equal(plain, cleared)
+
+
+def test_full_length_generation_with_memory_and_streaming_decode(tmp_path):
+    import json
+
+    from solarwm_b200.models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+    from solarwm_b200.serve.h3_full_inference import generate_full_length
+
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    vcfg = ViTDecoderConfig(latent_channels=24, dim=64, depth=1, heads=2, dim_head=32, ffn_dim=128, registers=2, patch=2)
+    dec = StreamingViTDecoder(ViTVideoDecoder(vcfg, device="cpu", dtype=torch.float32), (4, 6))
+    n_chunks, k = 8, 2
+    c2w = torch.eye(4).repeat(1 + n_chunks * k, 1, 1)
+    xs = torch.cat([torch.linspace(0, 12, 9), torch.linspace(12, 0, 8)])          # walk away and come back
+    c2w[:, 0, 3] = xs
+    K = torch.tensor([[0.5, 0, 0.5], [0, 0.9, 0.5], [0, 0, 1.0]]).repeat(1 + n_chunks * k, 1, 1)
+    frames = []
+    scfg = H3StreamConfig(grid_hw=(2, 3), chunk_latents=k, window_chunks=2, denoise_steps=1, use_cuda_graph=False,
+                          memory_latents=2)
+    torch.manual_seed(0)
+    man = generate_full_length(model, text=torch.randn(6, cfg.text_dim), anchor_latent=torch.randn(24, 1, 4, 6), c2w=c2w,
+                               intrinsics=K, stream_cfg=scfg, decoder=dec, frame_sink=frames.append, use_memory=True,
+                               top_k=2, out_dir=tmp_path)
+    assert man["chunks"] == n_chunks and man["frames"] == sum(f.shape[1] for f in frames) > 0
+    assert all(torch.isfinite(f).all() for f in frames) and frames[0].shape[-2:] == (8, 12)
+    assert man["memory"]["retrieved"][0] == [] and len(man["memory"]["retrieved"][-1]) == 2
+    assert json.loads((tmp_path / "manifest.json").read_text())["latents"] == n_chunks * k
