@@ -368,3 +368,65 @@ class StreamingViTDecoder:
             for j, i in enumerate(owned):
                 tiles[i] = fr[j]
         return blend_tiles(tiles, self.plan, self.h, self.w, self.tile, self.overlap, c.patch)
+
+
+class TensorParallelViT:
+    """Head / FFN-column tensor parallelism of ``ViTVideoDecoder`` blocks over a process group.
+
+    Rank r keeps heads ``[r H/P, (r+1) H/P)`` of the fused q|k|v projection with the matching input columns
+    of the output projection, and FFN columns ``[r F/P, (r+1) F/P)`` of gate / up with the matching input
+    columns of the down projection.  The two row-parallel products give partial sums that are formed in
+    fp32, summed with one all-reduce each, and only then rounded to the activation dtype -- the same
+    rounding point as the unsharded product (reference: deploy/solar_wm/shared/vae/streamrender_tp.py:63-113).
+    Every rank holds all tokens; keys / values are cached per rank for its own heads only.
+    """
+
+    def __init__(self, model: ViTVideoDecoder, group=None):
+        import torch.distributed as dist
+
+        self.m, self.cfg, self.group = model, model.cfg, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        c = self.cfg
+        if c.heads % self.world or c.ffn_dim % self.world:
+            raise ValueError("heads and ffn_dim must be divisible by the tensor-parallel size")
+        self.hl, self.fl = c.heads // self.world, c.ffn_dim // self.world
+        a, al = c.heads * c.dim_head, self.hl * c.dim_head
+        r = self.rank
+        self.shards = []
+        for blk in model.blocks:
+            qkv = torch.cat([blk.qkv[i * a + r * al:i * a + (r + 1) * al] for i in range(3)]).contiguous()
+            gate_up = torch.cat([blk.gate_up[r * self.fl:(r + 1) * self.fl],
+                                 blk.gate_up[c.ffn_dim + r * self.fl:c.ffn_dim + (r + 1) * self.fl]]).contiguous()
+            self.shards.append({"qkv": qkv, "out": blk.out[:, r * al:(r + 1) * al].contiguous(), "gate_up": gate_up,
+                                "down": blk.down[:, r * self.fl:(r + 1) * self.fl].contiguous()})
+
+    def _row_parallel(self, x, w):
+        import torch.distributed as dist
+
+        part = x.float() @ w.float().t()                          # fp32 partial sum of this rank's input columns
+        dist.all_reduce(part, group=self.group)
+        return part.to(x.dtype)
+
+    def block(self, li: int, x, cos, sin, k_cache=None, v_cache=None, lo: int = 0):
+        """x [B, N, dim] -> [B, N, dim].  With caches ([B, rows, hl*dh]) the new keys / values are written at
+        ``[lo, lo+N)`` and attention reads ``[0, lo+N)``."""
+        c, blk, sh = self.cfg, self.m.blocks[li], self.shards[li]
+        B, N, _ = x.shape
+        al = self.hl * c.dim_head
+        xm = F_.norm_modulate(x.reshape(B * N, -1), mode=1, w=blk.norm1, eps=c.eps)
+        qkv = F_.linear(xm, sh["qkv"]).view(B, N, 3 * al)
+        q = _head_rms(qkv[..., :al], blk.q_norm, self.hl, c.eps)
+        k = _head_rms(qkv[..., al:2 * al], blk.k_norm, self.hl, c.eps)
+        v = qkv[..., 2 * al:]
+        if cos is not None:
+            q, k = apply_rope(q, cos, sin, self.hl), apply_rope(k, cos, sin, self.hl)
+        if k_cache is not None:
+            k_cache[:, lo:lo + N], v_cache[:, lo:lo + N] = k, v
+            k, v = k_cache[:, :lo + N], v_cache[:, :lo + N]
+        Nk = k.shape[1]
+        o = ops.attention(q.reshape(B, N, self.hl, c.dim_head), k.reshape(B, Nk, self.hl, c.dim_head),
+                          v.reshape(B, Nk, self.hl, c.dim_head)).reshape(B * N, al)
+        x2 = F_.gated_residual(x.reshape(B * N, -1), self._row_parallel(o, sh["out"]), None)
+        xm = F_.norm_modulate(x2, mode=1, w=blk.norm2, eps=c.eps)
+        y = self._row_parallel(F_.swiglu(F_.linear(xm, sh["gate_up"])), sh["down"])
+        return F_.gated_residual(x2, y, None).view(B, N, -1)

@@ -154,3 +154,31 @@ def test_zero_sharded_adamw_matches_unsharded(tmp_path):
         assert got["state_numel"] * 2 == got["full"]            # each rank holds half of the moments
         assert torch.allclose(got["flat"], got["ref"], atol=1e-6)
         assert torch.allclose(got["flat_v"], got["ref_v"], atol=1e-6)
+
+
+def _tp_worker(rank, world, path, out):
+    from solarwm_b200.models.vit_decoder import TensorParallelViT, ViTDecoderConfig, ViTVideoDecoder, rope_tables
+
+    _init(rank, world, path)
+    cfg = ViTDecoderConfig(latent_channels=4, dim=64, depth=2, heads=4, dim_head=16, ffn_dim=96, registers=2, patch=2)
+    m = ViTVideoDecoder(cfg, device="cpu", dtype=torch.float32, seed=0)
+    tp = TensorParallelViT(m)
+    x = torch.randn(2, 12, 64, generator=torch.Generator().manual_seed(3))
+    cos, sin = rope_tables(1, cfg.window, 3, 4, cfg.dim_head)
+    want = x
+    for blk in m.blocks:
+        q, k, v = m.block_qkv(blk, want, cos, sin)
+        want = m.block_finish(blk, want, m.attend(q, k, v))
+    got = x
+    for li in range(cfg.depth):
+        got = tp.block(li, got, cos, sin)
+    torch.save({"err": float((got - want).abs().max()), "shard_rows": tp.shards[0]["qkv"].shape[0]}, f"{out}.{rank}")
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_vit_block_matches_unsharded(tmp_path):
+    out = str(tmp_path / "tp")
+    mp.spawn(_tp_worker, args=(2, str(tmp_path / "rdv"), out), nprocs=2, join=True)
+    for r in range(2):
+        got = torch.load(f"{out}.{r}", weights_only=True)
+        assert got["err"] < 1e-4 and got["shard_rows"] == 3 * 2 * 16
