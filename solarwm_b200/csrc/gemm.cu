@@ -59,6 +59,104 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / rows;
 }
 
+// Drain one accumulator tile: this warp's 32 TMEM lanes (rows row0 .. row0+31 of C) x BN columns starting at
+// column n0 -> bias / activation -> staged through shared memory -> TMA store, reduce-add or peer scatter.
+template <int OUT_F32>
+__device__ __forceinline__ void epilogue_tile(const CUtensorMap& tmC, const GemmParams& p, const ColScatter& sc,
+                                              uint32_t t_row, int row0, int n0, uint8_t* my_buf, int& buf, int lane) {
+  constexpr int CHUNK = OUT_F32 ? 32 : 64;  // columns per 128-byte staged row
+  const bool rows_live = (row0) < p.M;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+    const int ncol = n0 + c0;
+    if (ncol >= p.N) break;
+    if (lane == 0) tma_store_wait_read<1>();
+    __syncwarp();
+    uint8_t* dst = my_buf + buf * EPI_BUF_BYTES + lane * 128;
+    if (OUT_F32) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = __uint_as_float(r[g * 4 + e]);
+        if (p.bias != nullptr && ncol + g * 4 < p.N) {
+          const uint2 bb = *reinterpret_cast<const uint2*>(p.bias + ncol + g * 4);
+          const float2 b01 = unpack_bf16x2(bb.x), b23 = unpack_bf16x2(bb.y);
+          v[0] += b01.x; v[1] += b01.y; v[2] += b23.x; v[3] += b23.y;
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = gelu_tanh(v[e]);
+        }
+        uint4 o = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]),
+                             __float_as_uint(v[2]), __float_as_uint(v[3]));
+        *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
+      }
+    } else {
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(t_row + c0, r0);
+      tmem_ld_32x32(t_row + c0 + 32, r1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          v[e] = __uint_as_float(g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e]);
+        if (p.bias != nullptr && ncol + g * 8 < p.N) {
+          const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + ncol + g * 8);
+          const float2 b0 = unpack_bf16x2(bb.x), b1 = unpack_bf16x2(bb.y),
+                       b2 = unpack_bf16x2(bb.z), b3 = unpack_bf16x2(bb.w);
+          v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y;
+          v[4] += b2.x; v[5] += b2.y; v[6] += b3.x; v[7] += b3.y;
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+        }
+        uint4 o = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                             pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+        *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
+      }
+    }
+    if (!OUT_F32 && sc.active() && ncol >= sc.first_col) {
+      // Ulysses scatter: this 64-column chunk belongs to one head, hence to one rank.  The
+      // thread owns one output row; it copies its 128 staged bytes straight into the owning
+      // rank's receive buffer over NVLink (the staging pass above already applied the epilogue).
+      __syncwarp();
+      const int grow = row0 + lane;
+      if (grow < p.M) {
+        uint4* out = reinterpret_cast<uint4*>(sc.addr(grow, ncol, 2));
+#pragma unroll
+        for (int g = 0; g < 8; ++g) out[g] = *reinterpret_cast<const uint4*>(dst + ((g ^ (lane & 7)) << 4));
+      }
+      __syncwarp();
+      if (lane == 0) tma_store_commit();   // empty group: keeps the two-deep staging count aligned
+      buf ^= 1;
+      continue;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && rows_live) {
+      const void* src = my_buf + buf * EPI_BUF_BYTES;
+      if (p.accumulate) {
+        asm volatile(
+            "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::
+                "l"(reinterpret_cast<uint64_t>(&tmC)),
+            "r"(smem_u32(src)), "r"(ncol), "r"(row0)
+            : "memory");
+      } else {
+        tma_store_2d(&tmC, src, ncol, row0);
+      }
+      tma_store_commit();
+    }
+    buf ^= 1;
+  }
+}
+
 template <int A_MN, int B_MN, int OUT_F32>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -194,7 +292,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint8_t* my_buf = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
-    constexpr int CHUNK = OUT_F32 ? 32 : 64;  // columns per 128-byte staged row
     int local = 0;
     int buf = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
@@ -206,96 +303,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      const bool rows_live = (m0 + q * 32) < p.M;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += CHUNK) {
-        const int ncol = n0 + c0;
-        if (ncol >= p.N) break;
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-        uint8_t* dst = my_buf + buf * EPI_BUF_BYTES + lane * 128;
-        if (OUT_F32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c0, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float v[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) v[e] = __uint_as_float(r[g * 4 + e]);
-            if (p.bias != nullptr && ncol + g * 4 < p.N) {
-              const uint2 bb = *reinterpret_cast<const uint2*>(p.bias + ncol + g * 4);
-              const float2 b01 = unpack_bf16x2(bb.x), b23 = unpack_bf16x2(bb.y);
-              v[0] += b01.x; v[1] += b01.y; v[2] += b23.x; v[3] += b23.y;
-            }
-            if (p.act == 1) {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) v[e] = gelu_tanh(v[e]);
-            }
-            uint4 o = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]),
-                                 __float_as_uint(v[2]), __float_as_uint(v[3]));
-            *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
-          }
-        } else {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32(t_row + c0, r0);
-          tmem_ld_32x32(t_row + c0 + 32, r1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              v[e] = __uint_as_float(g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e]);
-            if (p.bias != nullptr && ncol + g * 8 < p.N) {
-              const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + ncol + g * 8);
-              const float2 b0 = unpack_bf16x2(bb.x), b1 = unpack_bf16x2(bb.y),
-                           b2 = unpack_bf16x2(bb.z), b3 = unpack_bf16x2(bb.w);
-              v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y;
-              v[4] += b2.x; v[5] += b2.y; v[6] += b3.x; v[7] += b3.y;
-            }
-            if (p.act == 1) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
-            }
-            uint4 o = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                 pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-            *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
-          }
-        }
-        if (!OUT_F32 && sc.active() && ncol >= sc.first_col) {
-          // Ulysses scatter: this 64-column chunk belongs to one head, hence to one rank.  The
-          // thread owns one output row; it copies its 128 staged bytes straight into the owning
-          // rank's receive buffer over NVLink (the staging pass above already applied the epilogue).
-          __syncwarp();
-          const int grow = m0 + q * 32 + lane;
-          if (grow < p.M) {
-            uint4* out = reinterpret_cast<uint4*>(sc.addr(grow, ncol, 2));
-#pragma unroll
-            for (int g = 0; g < 8; ++g) out[g] = *reinterpret_cast<const uint4*>(dst + ((g ^ (lane & 7)) << 4));
-          }
-          __syncwarp();
-          if (lane == 0) tma_store_commit();   // empty group: keeps the two-deep staging count aligned
-          buf ^= 1;
-          continue;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0 && rows_live) {
-          const void* src = my_buf + buf * EPI_BUF_BYTES;
-          if (p.accumulate) {
-            asm volatile(
-                "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::
-                    "l"(reinterpret_cast<uint64_t>(&tmC)),
-                "r"(smem_u32(src)), "r"(ncol), "r"(m0 + q * 32)
-                : "memory");
-          } else {
-            tma_store_2d(&tmC, src, ncol, m0 + q * 32);
-          }
-          tma_store_commit();
-        }
-        buf ^= 1;
-      }
+      epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane);
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
     }
@@ -331,6 +339,242 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   return 0;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): a cluster of two CTAs computes a 256 x 256 tile.  Each CTA loads
+// its own 128 rows of A and only HALF of the B tile (128 of the 256 columns) -- the tensor core of
+// either SM reads the other half from the partner's shared memory -- and keeps its 128 x 256 half
+// of the accumulator in its own TMEM.  Per MMA step a CTA now stages 32 KiB instead of 48 KiB, which
+// lifts the shared-memory operand bandwidth limit of the single-CTA kernel, and one instruction
+// issue drives two SMs.  The pair leader (cluster rank 0) issues every MMA; completion is
+// committed to the barriers of both CTAs; both CTAs' TMA loads credit the leader's "full" barrier.
+// ---------------------------------------------------------------------------------------------
+constexpr int P_BN_HALF = BN / 2;                       // B columns staged per CTA
+constexpr int P_B_BYTES = P_BN_HALF * BK * 2;           // 16 KiB
+constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES;      // 32 KiB
+constexpr int P_STAGES = 6;
+constexpr int P_SMEM_MAIN = P_STAGES * P_STAGE_BYTES + EPI_BYTES;
+constexpr int P_SMEM_TOTAL = P_SMEM_MAIN + 256 + 1024;
+
+template <int A_MN, int B_MN, int OUT_F32>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmC, const GemmParams p,
+                      const __grid_constant__ ColScatter sc) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_smem = smem + P_STAGES * P_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_SMEM_MAIN);   // used in the leader only
+  uint64_t* empty_bar = full_bar + P_STAGES;                              // one set per CTA
+  uint64_t* tfull_bar = empty_bar + P_STAGES;                             // one set per CTA
+  uint64_t* tempty_bar = tfull_bar + 2;                                   // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();            // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;        // tiles_m counts 256-row tiles here
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2 * EPI_WARPS * 32);   // the epilogue threads of both CTAs
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();          // barriers of both CTAs are initialised before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM;
+        const int nb0 = tn * BN + static_cast<int>(rank) * P_BN_HALF;      // this CTA's half of the B tile
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, ST_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * P_STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          const uint32_t full_leader = mapa_u32(smem_u32(&full_bar[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);   // both CTAs' bytes
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sa + c * (64 * BK * 2), &tmA, full_leader, m0 + c * 64, k0);
+          } else {
+            tma_load_2d_pair(sa, &tmA, full_leader, k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < P_BN_HALF / 64; ++c)
+              tma_load_2d_pair(sb + c * (64 * BK * 2), &tmB, full_leader, nb0 + c * 64, k0);
+          } else {
+            tma_load_2d_pair(sb, &tmB, full_leader, k0, nb0);
+          }
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0) {
+      const bool leader = elect_one();
+      auto wwait = [&](uint64_t* bar, uint32_t parity, volatile int* aw, int code) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, aw, code));
+      };
+      const uint32_t smem_base = __shfl_sync(0xffffffffu, smem_u32(smem), 0);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint32_t bar_base = __shfl_sync(0xffffffffu, smem_u32(full_bar), 0);
+      const uint32_t bar_peer = mapa_u32(bar_base, 1);
+      // a barrier of this CTA and the same barrier of the partner
+      auto commit_both = [&](uint64_t* bar) {
+        const uint32_t off = smem_u32(bar) - bar_base;
+        if (leader) {
+          umma_commit_pair(bar_base + off);
+          umma_commit_pair(bar_peer + off);
+        }
+      };
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!wwait(&tempty_bar[acc], acc_phase ^ 1, abort_word, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_u + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wwait(&full_bar[stage], phase, abort_word, ST_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t adesc = A_MN ? umma_desc_mnmajor(sa + kk * 2048, 64 * BK * 2)
+                                        : umma_desc_kmajor(sa + kk * 32);
+            const uint64_t bdesc = B_MN ? umma_desc_mnmajor(sb + kk * 2048, 64 * BK * 2)
+                                        : umma_desc_kmajor(sb + kk * 32);
+            if (leader) umma_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0);
+          }
+          commit_both(&empty_bar[stage]);
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) commit_both(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps, both CTAs)
+    const int q = warp & 3;
+    uint8_t* my_buf = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
+    const uint32_t tempty_leader = mapa_u32(smem_u32(tempty_bar), 0);
+    int local = 0;
+    int buf = 0;
+    for (int tile = pair; tile < num_tiles; tile += n_pairs, ++local) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM, n0 = tn * BN;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane);
+      tc_fence_before();
+      mbar_arrive_cluster(tempty_leader + acc * 8);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_word != 0) bounded_drain_pause();
+  tc_fence_before();
+  cluster_sync_all();          // the partner's shared memory and TMEM stay alive until both are done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicExch(p.status, *abort_word);
+  if (sc.active()) cta_done_signal_peers(sc.flags);
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+static int launch_gemm_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
+                            const GemmParams& p, int max_ctas, cudaStream_t stream, const ColScatter& sc) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL));
+    configured = true;
+  }
+  int pairs = p.tiles_m * p.tiles_n;
+  const int cap = (max_ctas > 0 ? max_ctas : sm_count()) / 2;
+  if (pairs > cap) pairs = cap;
+  if (pairs < 1) pairs = 1;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM_TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  // clusters that cannot be co-resident would start only after others finish and unbalance the persistent loop
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    SOLAR_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
+    if (max_clusters < 1) return fail("gemm pair: no cluster of two CTAs can be resident%s");
+  }
+  if (pairs > max_clusters) {
+    pairs = max_clusters;
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+  }
+  SOLAR_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tA, tB, tC, p, sc));
+  return 0;
+}
+
 }  // namespace solar
 
 using namespace solar;
@@ -339,6 +583,14 @@ using namespace solar;
 // dimensions in elements of the row-major arrays as they sit in memory.
 // out_f32: C is fp32 instead of bf16.  accumulate: C += (atomic-free TMA reduce-add).
 // status: optional device int that receives a non-zero code if a bounded wait gave up.
+// -1: choose per problem; 0: single-CTA kernel only; 1: CTA-pair kernel whenever legal.
+static int g_pair_mode = -1;
+extern "C" int solar_gemm_pair_mode(int mode) {
+  const int old = g_pair_mode;
+  if (mode >= -1 && mode <= 1) g_pair_mode = mode;
+  return old;
+}
+
 static int gemm_entry(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                       long long ldb, long long ldc, int layout, int act, int out_f32, int accumulate, int* status,
                       int max_ctas, void* stream, const ColScatter& sc) {
@@ -354,8 +606,12 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
     rc = make_tmap_2d(&tA, A, bf, 2, M, K, lda, BM, BK);
   }
   if (rc) return rc;
+  // CTA pairs pay off once there are enough 256-row tiles to fill the machine; small problems and the
+  // scatter epilogue (whose last-CTA signalling counts single CTAs) stay on the single-CTA kernel.
+  const bool use_pair = g_pair_mode == 1 || (g_pair_mode < 0 && sc.dst.n == 0 &&
+                        static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) >= sm_count() / 2);
   if (layout == 0) {  // B stored [N, K]
-    rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, BN, BK);
+    rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, use_pair ? P_BN_HALF : BN, BK);
   } else {            // B stored [K, N]
     rc = make_tmap_2d(&tB, B, bf, 2, K, N, ldb, BK, 64);
   }
@@ -368,13 +624,23 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   if (rc) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_m = use_pair ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.act = act;
   p.accumulate = accumulate;
   p.status = status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (use_pair) {
+    switch (layout * 2 + (out_f32 ? 1 : 0)) {
+      case 0: return launch_gemm_pair<0, 0, 0>(tA, tB, tC, p, max_ctas, st, sc);
+      case 1: return launch_gemm_pair<0, 0, 1>(tA, tB, tC, p, max_ctas, st, sc);
+      case 2: return launch_gemm_pair<0, 1, 0>(tA, tB, tC, p, max_ctas, st, sc);
+      case 3: return launch_gemm_pair<0, 1, 1>(tA, tB, tC, p, max_ctas, st, sc);
+      case 4: return launch_gemm_pair<1, 1, 0>(tA, tB, tC, p, max_ctas, st, sc);
+      default: return launch_gemm_pair<1, 1, 1>(tA, tB, tC, p, max_ctas, st, sc);
+    }
+  }
   switch (layout * 2 + (out_f32 ? 1 : 0)) {
     case 0: return launch_gemm<0, 0, 0>(tA, tB, tC, p, max_ctas, st, sc);
     case 1: return launch_gemm<0, 0, 1>(tA, tB, tC, p, max_ctas, st, sc);
