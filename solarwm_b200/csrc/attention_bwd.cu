@@ -110,6 +110,11 @@ __device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint8_t* region, int
 
 // A load the compiler may not sink to its first use: the prefetch below has to leave a whole tile
 // ahead of the values being needed.
+__device__ __forceinline__ float4 lds_f4_early(const float* ptr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(ptr)));
+  return v;
+}
 __device__ __forceinline__ float ld_f1_early(const float* ptr) {
   float v;
   asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
@@ -409,6 +414,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
       const int b = j & 1;
       const uint32_t par = (j >> 1) & 1;
       const uint32_t tS = tmem_base + lane_off + col_S(b) + wg * 32, tD = tmem_base + lane_off + col_D(b) + wg * 32;
+      // park this tile's vectors and pull them into registers BEFORE waiting for the S tile: the
+      // shared-memory round trip hides in the wait instead of stalling the math loops one load at a time
+      float4 cL[8], cD[8];
+      if (MODE == 0) {
+        __syncwarp();                       // the previous tile's reads of the parking area are done
+        vec_smem[lane] = -nxtL;             // both vectors are parked negated: the math below only adds them
+        vec_smem[32 + lane] = -nxtD;
+        __syncwarp();
+        if (j + 1 < n_tiles) {
+          nxtL = ld_f1_early(p.L2 + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
+          nxtD = ld_f1_early(p.delta + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          cL[g] = lds_f4_early(vec_smem + 4 * g);
+          cD[g] = lds_f4_early(vec_smem + 32 + 4 * g);
+        }
+      }
       long long c0 = tracing ? clock64() : 0;
       if (!mbar_wait(&s_ready[b], par, abort_word, ST_TIMEOUT_TMEM_FULL)) return false;
       if (tracing) w_s += clock64() - c0;
@@ -419,18 +442,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
       if (MODE == 1) tmem_ld_32x32(tD, d);
       tmem_ld_wait();
       if (tracing) { const long long q1 = clock64(); seg[0] += q1 - q0; q0 = q1; }
-      const float4* cL = reinterpret_cast<const float4*>(vec_smem);
-      const float4* cD = reinterpret_cast<const float4*>(vec_smem + 32);
-      if (MODE == 0) {
-        __syncwarp();                       // the previous tile's reads of the parking area are done
-        vec_smem[lane] = -nxtL;             // both vectors are parked negated: the math below only adds them
-        vec_smem[32 + lane] = -nxtD;
-        __syncwarp();
-        if (j + 1 < n_tiles) {
-          nxtL = ld_f1_early(p.L2 + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
-          nxtD = ld_f1_early(p.delta + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
-        }
-      }
       if (tracing) { const long long q1 = clock64(); seg[6] += q1 - q0; q0 = q1; }
       uint32_t pk[16], dk[16];
       // P = exp2(S * c - L2); kept as fp32 in s[] for the dS product
