@@ -182,3 +182,32 @@ def test_tensor_parallel_vit_block_matches_unsharded(tmp_path):
     for r in range(2):
         got = torch.load(f"{out}.{r}", weights_only=True)
         assert got["err"] < 1e-4 and got["shard_rows"] == 3 * 2 * 16
+
+
+def _h3_stream_worker(rank, world, path, out):
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.parallel.ulysses import UlyssesCollective
+    from solarwm_b200.serve.h3_stream import H3StreamConfig, H3StreamingGenerator
+
+    _init(rank, world, path)
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    scfg = H3StreamConfig(grid_hw=(2, 4), chunk_latents=2, window_chunks=2, denoise_steps=2, use_cuda_graph=False, seed=5)
+    g = torch.Generator().manual_seed(1)
+    text, anchor = torch.randn(8, cfg.text_dim, generator=g), torch.randn(24, 1, 4, 8, generator=g)
+    outs = {}
+    for name, sp in (("single", None), ("sp", UlyssesCollective(None))):
+        gen = H3StreamingGenerator(model, scfg, sp=sp)
+        gen.start(text, anchor, torch.eye(4))
+        outs[name] = torch.stack([gen.next_chunk(None) for _ in range(4)])
+    torch.save({"err": float((outs["single"] - outs["sp"]).abs().max()), "scale": float(outs["single"].abs().max())},
+               f"{out}.{rank}")
+    dist.destroy_process_group()
+
+
+def test_h3_streaming_with_ulysses_matches_single_rank(tmp_path):
+    out = str(tmp_path / "h3sp")
+    mp.spawn(_h3_stream_worker, args=(2, str(tmp_path / "rdv"), out), nprocs=2, join=True)
+    for r in range(2):
+        got = torch.load(f"{out}.{r}", weights_only=True)
+        assert got["err"] < 1e-4 * max(got["scale"], 1.0), got
