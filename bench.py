@@ -38,7 +38,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="ti2v_5b", choices=["ti2v_5b", "small"])
+    ap.add_argument("--model", default="ti2v_5b", choices=["ti2v_5b", "ltx_2b", "small"],
+                    help="ltx_2b: LTX-Video-2B shape (pass --frames 16 --height 16 --width 24 for its 6,144-token clip)")
     ap.add_argument("--mode", default="train", choices=["train", "realtime"],
                     help="train: the headline training step; realtime: H3-shaped block-causal streaming (FPS)")
     ap.add_argument("--h3", default="h3_33b", choices=["h3_33b", "tiny"], help="realtime mode: model preset")
@@ -115,7 +116,12 @@ def model_config(args):
     if args.model == "small":
         return WanConfig(model_type="ti2v", in_dim=48, out_dim=48, dim=512, ffn_dim=2048, num_heads=8,
                          num_layers=4, text_dim=4096, text_len=512)
-    return wan_preset("ti2v_5b")
+    return wan_preset("ltx_video_2b" if args.model == "ltx_2b" else "ti2v_5b")
+
+
+def n_tokens(cfg, args) -> int:
+    pt, ph, pw = cfg.patch_size
+    return (args.frames // pt) * (args.height // ph) * (args.width // pw)
 
 
 def make_batch(cfg, args, pinned=True):
@@ -167,7 +173,7 @@ def run_ours(args):
             from solarwm_b200.parallel.fused_ulysses import FusedUlysses
 
             mc = model_config(args)
-            sp = FusedUlysses(None, max_tokens=args.frames * (args.height // 2) * (args.width // 2), dim=mc.dim,
+            sp = FusedUlysses(None, max_tokens=n_tokens(mc, args), dim=mc.dim,
                               num_heads=mc.num_heads)
         else:
             from solarwm_b200.parallel.ulysses import UlyssesCollective
@@ -188,7 +194,7 @@ def run_ours(args):
         keep = 0
         if ckpt == "selective":
             # resident bytes of one un-checkpointed block: ~17 [S, dim] and 2 [S, ffn] bf16 tensors
-            s_local = args.frames * (args.height // 2) * (args.width // 2) / world
+            s_local = n_tokens(cfg, args) / world
             per_block = s_local * (17 * cfg.dim + 2 * cfg.ffn_dim) * 2
             n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
             zero_on = world > 1 and args.zero != "off"
@@ -213,7 +219,7 @@ def run_ours(args):
         trainer.model.get_parameter("head.head.weight").normal_(0, 0.02)
     batch = make_batch(cfg, args)
     dev_batch = {k: v.to(f"cuda:{local}") for k, v in batch.items()}
-    tokens = args.frames * (args.height // 2) * (args.width // 2)
+    tokens = n_tokens(cfg, args)
     h2d = sum(v.numel() * v.element_size() for v in batch.values())
 
     def step_device():
@@ -242,13 +248,14 @@ def run_ours(args):
         value = tokens * args.steps / (ms / 1e3)
         e2e = tokens * args.steps / (ms_e2e / 1e3)
         out = {
-            "metric": "DiT train tokens/s/box (Wan2.2 TI2V-5B-shaped flow-matching step)",
+            "metric": "DiT train tokens/s/box (Wan2.2 TI2V-5B-shaped flow-matching step)" if args.model != "ltx_2b"
+            else "DiT train tokens/s/box (LTX-Video-2B-shaped flow-matching step)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None if BASELINE_TOKENS_PER_S is None else value / BASELINE_TOKENS_PER_S,
             "dtype": "bf16", "data": "synthetic latents/text of the named shapes, random-init weights",
             "impl": "ours",
-            "config": {"model": "wan22_ti2v_5b-shaped" if args.model == "ti2v_5b" else "small-debug",
+            "config": {"model": {"ti2v_5b": "wan22_ti2v_5b-shaped", "ltx_2b": "ltx_video_2b-shaped"}.get(args.model, "small-debug"),
                        "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
                        "optimizer_sharding": (f"zero-{args.zero}" if zero else "none"),
                        "latent": [1, cfg.in_dim, args.frames, args.height, args.width],

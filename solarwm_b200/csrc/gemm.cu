@@ -606,9 +606,9 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
     rc = make_tmap_2d(&tA, A, bf, 2, M, K, lda, BM, BK);
   }
   if (rc) return rc;
-  // CTA pairs pay off once there are enough 256-row tiles to fill the machine; small problems and the
-  // scatter epilogue (whose last-CTA signalling counts single CTAs) stay on the single-CTA kernel.
-  const bool use_pair = g_pair_mode == 1 || (g_pair_mode < 0 && sc.dst.n == 0 &&
+  // CTA pairs pay off once there are enough 256-row tiles to fill the machine; small problems stay on the
+  // single-CTA kernel.  (The scatter epilogue and its last-CTA signalling are per CTA and work in both.)
+  const bool use_pair = g_pair_mode == 1 || (g_pair_mode < 0 &&
                         static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) >= sm_count() / 2);
   if (layout == 0) {  // B stored [N, K]
     rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, use_pair ? P_BN_HALF : BN, BK);

@@ -69,3 +69,38 @@ def test_resume_contract_and_validation():
         _contract(family="")
     with pytest.raises(CheckpointError):
         _contract(sp_size=0)
+
+
+def test_safetensors_inventory_and_strict_load(tmp_path):
+    import json
+
+    import pytest
+    import torch
+    from safetensors.torch import save_file
+
+    from solarwm_b200.backends.wan22.loader import ARCHITECTURES, inventory, strict_load
+    from solarwm_b200.errors import BackendContractError
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+
+    assert ARCHITECTURES["ti2v_5b"]["num_layers"] == 30 and ARCHITECTURES["i2v_a14b"]["dim"] == 5120
+    cfg = WanConfig(model_type="t2v", in_dim=4, out_dim=4, dim=64, ffn_dim=128, num_heads=2, num_layers=2, text_dim=32,
+                    text_len=8, freq_dim=32)
+    src = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=1)
+    state = {k: v.clone().contiguous() for k, v in src.state_dict().items()}
+    names = sorted(state)
+    half = len(names) // 2
+    save_file({k: state[k] for k in names[:half]}, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file({k: state[k] for k in names[half:]}, str(tmp_path / "model-00002-of-00002.safetensors"))
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {
+        **{k: "model-00001-of-00002.safetensors" for k in names[:half]},
+        **{k: "model-00002-of-00002.safetensors" for k in names[half:]}}}))
+    inv = inventory(tmp_path)
+    assert set(inv) == set(names) and inv[names[0]].dtype == "F32"
+    dst = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=2)
+    copied = strict_load(dst, tmp_path)
+    assert sum(copied.values()) == len(names)
+    assert all(torch.equal(dst.state_dict()[k], state[k]) for k in names)
+    other = WanDiT(WanConfig(model_type="t2v", in_dim=4, out_dim=4, dim=64, ffn_dim=128, num_heads=2, num_layers=3,
+                             text_dim=32, text_len=8, freq_dim=32), device="cpu", dtype=torch.float32)
+    with pytest.raises(BackendContractError):
+        strict_load(other, tmp_path)

@@ -126,3 +126,25 @@ def test_tar_reader_and_local_transport(tmp_path):
     with pytest.raises(DataContractError):
         resolver_from_config({"transport": {"root": "gs://bucket/x"}})
     reader.close()
+
+
+def test_window_index_build_query_and_slices(tmp_path):
+    import pytest
+
+    from solarwm_b200.data.windows import WindowIndex, build_index, enumerate_windows
+    from solarwm_b200.errors import DataContractError
+
+    assert list(enumerate_windows(10, 4, 3)) == [0, 3, 6]
+    clips = [{"sample_id": "a", "shard": "s0.tar", "num_frames": 10}, {"sample_id": "b", "shard": "s1.tar", "num_frames": 3},
+             {"sample_id": "c", "shard": "s1.tar", "num_frames": 7}]
+    path = tmp_path / "windows.sqlite"
+    assert build_index(path, clips, window=4, stride=3) == 5
+    idx = WindowIndex(path)
+    assert len(idx) == 5 and idx[3] == (3, "c", "s1.tar", 0, 4)
+    assert [w.ordinal for w in idx.slice(1, 2)] == [1, 3]
+    idx.close()
+    with pytest.raises(DataContractError):
+        build_index(path, clips, window=4, stride=3)
+    with pytest.raises(DataContractError):
+        build_index(tmp_path / "none.sqlite", clips, window=64, stride=1)
+    assert not (tmp_path / "none.sqlite").exists()
