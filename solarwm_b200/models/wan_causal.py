@@ -52,6 +52,7 @@ class KVCache:
     committed_frames: int = 0          # frames currently held (sink + window part)
     total_frames: int = 0              # frames generated so far (absolute)
     grid_hw: tuple = (0, 0)
+    cam_inv: Optional[torch.Tensor] = None   # [capacity_frames, 4, 4] P^-1 of every cached frame (camera runs)
 
     @property
     def capacity_frames(self) -> int:
@@ -101,8 +102,14 @@ class CausalWanRunner:
             lc.text_v = kv[:, D:].contiguous()
 
     @torch.no_grad()
-    def forward_chunk(self, cache: KVCache, x: torch.Tensor, t: torch.Tensor, *, commit: bool, y=None) -> torch.Tensor:
-        """x [1, C, f, H, W] (f = chunk frames), t [1, f] -> prediction [1, C_out, f, H, W]."""
+    def forward_chunk(self, cache: KVCache, x: torch.Tensor, t: torch.Tensor, *, commit: bool, y=None,
+                      y_camera=None) -> torch.Tensor:
+        """x [1, C, f, H, W] (f = chunk frames), t [1, f] -> prediction [1, C_out, f, H, W].
+
+        ``y_camera`` = ``{"viewmats": [1, f, 4, 4], "Ks": [1, f, 3, 3] or None, "transform": str}`` switches on
+        PRoPE with separate query / key cameras: queries take P^T of the chunk's cameras, every cached key
+        (after RoPE) and value takes the P^-1 of ITS OWN frame, the output takes P of the chunk
+        (reference: prope_qkv_separate, camera_prope.py:93-180)."""
         m, cfg = self.model, self.model.cfg
         P_ = m.stem.params
         if y is not None:
@@ -123,6 +130,19 @@ class CausalWanRunner:
         hl = H // P
         h0 = 0 if sp is None else sp.rank * hl
         gk = dict(rows_per_group=ft)
+        cam = None
+        if y_camera is not None:
+            from . import camera_prope
+
+            Ks = y_camera.get("Ks")
+            PT, Pinv, Pm = camera_prope.prope_matrices(y_camera["viewmats"][0].to(xs.device),
+                                                       None if Ks is None else Ks[0].to(xs.device),
+                                                       transform=y_camera.get("transform", "linear"))
+            if cache.cam_inv is None:
+                cache.cam_inv = torch.eye(4, device=xs.device).repeat(cache.capacity_frames, 1, 1)
+            cache.cam_inv[ctx_frames:ctx_frames + f] = Pinv
+            cam = (camera_prope.per_row(PT, ft), camera_prope.per_row(Pinv, ft), camera_prope.per_row(Pm, ft),
+                   camera_prope.per_row(cache.cam_inv[:ctx_frames + f], ft))
         for blk, lc in zip(m.blocks, cache.layers):
             mod = (blk._p("modulation").float().view(1, 6, D) + e0).contiguous()
             xm = F_.norm_modulate(xs, mod[:, 0], mod[:, 1], mode=0, eps=cfg.eps, **gk)
@@ -130,12 +150,21 @@ class CausalWanRunner:
             q = F_.rmsnorm_rope(qkv[:, :D], blk._p("self_attn.norm_q.weight").float(), rope_q, eps=cfg.eps)
             k_raw = F_.rmsnorm_rope(qkv[:, D:2 * D], blk._p("self_attn.norm_k.weight").float(), None, eps=cfg.eps)
             cs = slice(h0 * hd, (h0 + hl) * hd)
+            v_new = qkv[:, 2 * D:][:, cs]
+            q_loc = q[:, cs]
+            if cam is not None:
+                q_loc = camera_prope.apply(q_loc.contiguous(), cam[0], hl)
+                v_new = camera_prope.apply(v_new.contiguous(), cam[1], hl)       # values are cached transformed
             lc.k[n_ctx:n_ctx + n_new] = k_raw[:, cs]
-            lc.v[n_ctx:n_ctx + n_new] = qkv[:, 2 * D:][:, cs]
+            lc.v[n_ctx:n_ctx + n_new] = v_new
             k_all = F_.rmsnorm_rope(lc.k[:n_ctx + n_new], None, _head_slice(rope_all, None), no_norm=True)
-            o = ops.attention(q[:, cs].reshape(1, n_new, hl, hd), k_all.view(1, n_ctx + n_new, hl, hd),
+            if cam is not None:
+                k_all = camera_prope.apply(k_all, cam[3], hl)                    # after RoPE, each key with its own camera
+            o = ops.attention(q_loc.reshape(1, n_new, hl, hd), k_all.view(1, n_ctx + n_new, hl, hd),
                               lc.v[:n_ctx + n_new].view(1, n_ctx + n_new, hl, hd))
             o = o.reshape(n_new, hl * hd)
+            if cam is not None:
+                o = camera_prope.apply(o, cam[2], hl)
             if P > 1:
                 o = sp.all_gather_heads(o)
             yb = blk._linear(o, "self_attn.o.weight", "self_attn.o.bias")
@@ -171,6 +200,9 @@ class CausalWanRunner:
             for lc in cache.layers:
                 for buf in (lc.k, lc.v):
                     buf[s0:s0 + keep] = buf[s0 + extra * ft:s0 + extra * ft + keep].clone()
+            if cache.cam_inv is not None:
+                fs, fk = cache.sink_frames, keep // ft
+                cache.cam_inv[fs:fs + fk] = cache.cam_inv[fs + extra:fs + extra + fk].clone()
             cache.committed_frames = limit
 
 

@@ -83,3 +83,46 @@ def test_streaming_generator_runs_on_cpu():
     chunks = [gen.next_chunk() for _ in range(4)]
     assert all(c.shape == (1, 16, 1, 8, 8) and torch.isfinite(c).all() for c in chunks)
     assert gen.cache.total_frames == 4 and gen.cache.committed_frames == 3
+
+
+def test_cache_runner_camera_prope_matches_bidirectional_first_chunk():
+    import torch
+
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+    from solarwm_b200.models.wan_causal import CausalWanRunner, allocate_kv_cache
+
+    cfg = WanConfig(model_type="t2v", in_dim=4, out_dim=4, dim=256, ffn_dim=256, num_heads=2, num_layers=2, text_dim=32,
+                    text_len=8, freq_dim=32)
+    m = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05)
+    g = torch.Generator().manual_seed(0)
+    x, ctx = torch.randn(1, 4, 2, 4, 4, generator=g), torch.randn(1, 8, 32, generator=g)
+    t = torch.tensor([[400.0, 400.0]])
+    q, _ = torch.linalg.qr(torch.randn(2, 3, 3, generator=g))
+    view = torch.eye(4).repeat(1, 2, 1, 1)
+    view[0, :, :3, :3] = q
+    view[0, :, :3, 3] = torch.randn(2, 3, generator=g) * 0.3
+    Ks = torch.eye(3).repeat(1, 2, 1, 1)
+    Ks[0, :, 0, 0], Ks[0, :, 1, 1] = 0.7, 1.1
+    cam = {"viewmats": view, "Ks": Ks}
+    want = m(x, t, ctx, y_camera=cam)
+    runner = CausalWanRunner(m)
+    cache = allocate_kv_cache(m, grid_hw=(2, 2), chunk_frames=2, window_frames=4, sink_frames=0)
+    runner.encode_text(cache, ctx)
+    got = runner.forward_chunk(cache, x, t, commit=True, y_camera=cam)
+    assert torch.allclose(got, want, atol=1e-4)
+    # a second chunk sees the first through its own cached camera; identity cameras reproduce the camera-free path
+    plain_cache = allocate_kv_cache(m, grid_hw=(2, 2), chunk_frames=2, window_frames=4, sink_frames=0)
+    runner.encode_text(plain_cache, ctx)
+    runner.forward_chunk(plain_cache, x, t, commit=True)
+    ident = {"viewmats": torch.eye(4).repeat(1, 2, 1, 1), "Ks": None}
+    id_cache = allocate_kv_cache(m, grid_hw=(2, 2), chunk_frames=2, window_frames=4, sink_frames=0)
+    runner.encode_text(id_cache, ctx)
+    runner.forward_chunk(id_cache, x, t, commit=True, y_camera=ident)
+    x2 = torch.randn(1, 4, 2, 4, 4, generator=g)
+    a = runner.forward_chunk(plain_cache, x2, t, commit=False)
+    b = runner.forward_chunk(id_cache, x2, t, commit=False, y_camera=ident)
+    assert torch.allclose(a, b, atol=1e-4)
+    c = runner.forward_chunk(cache, x2, t, commit=False, y_camera=cam)
+    assert not torch.allclose(a, c, atol=1e-3)
