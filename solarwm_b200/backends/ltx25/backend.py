@@ -82,6 +82,91 @@ def sample(model, text, *, frames, height, width, steps=8, seed=0, first_frame=N
     return x
 
 
+def guided_x0(cond, uncond, perturbed, *, cfg_scale: float = 1.0, stg_scale: float = 0.0, rescale: float = 0.0):
+    """x0 = cond + (cfg - 1)(cond - uncond) + stg (cond - perturbed), optionally pulled back towards the
+    conditional prediction's spread: factor = rescale * std(cond) / std(x0) + 1 - rescale
+    (reference: _guided_x0, solar/backends/ltx25/torch_inference.py:197-218)."""
+    c = cond.float()
+    x0 = c + (cfg_scale - 1.0) * (c - uncond.float()) + stg_scale * (c - perturbed.float())
+    if rescale != 0.0:
+        std = x0.std()
+        if not bool(torch.isfinite(std)) or float(std) <= 0:
+            raise BackendContractError("LTX guidance prediction has invalid variance")
+        x0 = x0 * (rescale * c.std() / std + 1.0 - rescale)
+    return x0
+
+
+@torch.no_grad()
+def sample_guided(model, text, negative_text, *, frames, height, width, steps=8, seed=0, first_frame=None,
+                  cfg_scale=3.0, stg_scale=1.0, rescale=0.7, stg_blocks=(1,)):
+    """The guided one-stage sampler ("stg-euler"): per step a conditional, an unconditional and a perturbed
+    evaluation (self-attention skipped in ``stg_blocks``), combined on the x0 side, then an Euler move
+    towards the guided x0."""
+    dev = next(model.parameters()).device
+    g = torch.Generator(device=dev).manual_seed(int(seed))
+    x = torch.randn(1, model.cfg.out_dim, frames, height, width, generator=g, device=dev).to(model.dtype)
+    sig = torch.linspace(1.0, 0.0, steps + 1, device=dev)
+    for i in range(steps):
+        t = sig[i].expand(1, frames).clone()
+        if first_frame is not None:
+            x[:, :, 0] = first_frame
+            t[:, 0] = 0.0
+        s = float(sig[i])
+        x0 = lambda v: x.float() - s * v.float()   # noqa: E731
+        cond = x0(model(x, t * 1000.0, text))
+        unc = x0(model(x, t * 1000.0, negative_text)) if cfg_scale != 1.0 else cond
+        per = x0(model(x, t * 1000.0, text, perturb_blocks=stg_blocks)) if stg_scale != 0.0 else cond
+        target = guided_x0(cond, unc, per, cfg_scale=cfg_scale, stg_scale=stg_scale, rescale=rescale)
+        v = (x.float() - target) / max(s, 1e-6)
+        x = (x.float() + (float(sig[i + 1]) - s) * v).to(x.dtype)
+    if first_frame is not None:
+        x[:, :, 0] = first_frame
+    return x
+
+
+class RuntimeProvider:
+    """What the backend boundary needs from a heavy runtime, resolved lazily so that configuration checks,
+    readiness probes and the CLI never import or allocate a model: ``readiness()`` (dependency / device /
+    asset report), ``training()``, ``inference()`` and ``preencode()`` bundles
+    (reference: LTX25RuntimeProvider, solar/backends/ltx25/runtime.py:119-140)."""
+
+    def __init__(self, config: Mapping[str, Any]):
+        self.config = config
+
+    def readiness(self) -> Mapping[str, Any]:
+        from ...ops import _lib
+
+        report = {"torch": torch.__version__, "cuda": torch.cuda.is_available(), "native_library": False, "problems": []}
+        try:
+            _lib.load()
+            report["native_library"] = True
+        except Exception as exc:  # noqa: BLE001 - reported, not raised
+            report["problems"].append(f"native library: {exc}")
+        assets = (self.config.get("model", {}) or {}).get("assets", {}) or {}
+        for name, path in assets.items():
+            import os
+
+            if not os.path.exists(str(path)):
+                report["problems"].append(f"asset {name} missing: {path}")
+        report["ready"] = not report["problems"]
+        return report
+
+    def _device(self):
+        return "cuda" if torch.cuda.is_available() and self.config.get("runtime", {}).get("device") != "cpu" else "cpu"
+
+    def training(self) -> "LTXTrainer":
+        return LTXTrainer(_arch(self.config), self._device(),
+                          lr=float(self.config.get("train", {}).get("optimizer", {}).get("lr", 1e-4)),
+                          seed=int(self.config.get("data", {}).get("seed", 0)))
+
+    def inference(self) -> LTXDiT:
+        dev = self._device()
+        return LTXDiT(_arch(self.config), device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32)
+
+    def preencode(self):
+        raise BackendContractError("LTX preencoding needs the official codec weights, which are not available offline")
+
+
 class _Adapter:
     family = "ltx25_video"
 
@@ -94,12 +179,19 @@ class _Adapter:
         dev = next(self.model.parameters()).device
         g = torch.Generator().manual_seed(case.noise_seed)
         text = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(dev, self.model.dtype)
-        lat = sample(self.model, text, frames=int(inf.get("latent_frames", 4)), height=int(inf.get("latent_height", 8)),
-                     width=int(inf.get("latent_width", 8)), steps=int(inf.get("steps", 8)), seed=case.noise_seed)
+        geo = dict(frames=int(inf.get("latent_frames", 4)), height=int(inf.get("latent_height", 8)),
+                   width=int(inf.get("latent_width", 8)), steps=int(inf.get("steps", 8)), seed=case.noise_seed)
+        gd = inf.get("guidance")
+        if gd:
+            lat = sample_guided(self.model, text, torch.zeros_like(text), cfg_scale=float(gd.get("cfg_scale", 3.0)),
+                                stg_scale=float(gd.get("stg_scale", 1.0)), rescale=float(gd.get("rescale_scale", 0.7)),
+                                stg_blocks=tuple(gd.get("stg_blocks", (1,))), **geo)
+        else:
+            lat = sample(self.model, text, **geo)
         buf = io.BytesIO()
         torch.save(lat.float().cpu(), buf)
         return GeneratedSample({"latents.pt": buf.getvalue()}, tuple(lat.shape), "bfloat16",
-                               provenance={"sampler": "euler", "steps": int(inf.get("steps", 8))})
+                               provenance={"sampler": "stg-euler" if gd else "euler", "steps": int(inf.get("steps", 8))})
 
 
 class LTX25Backend:

@@ -124,6 +124,11 @@ def sinusoidal_embedding(dim: int, position: torch.Tensor) -> torch.Tensor:
     return torch.cat([torch.cos(s), torch.sin(s)], dim=1)
 
 
+def _identity_attention(q, k, v):
+    """Skipped attention: the output of a token is its own value."""
+    return v
+
+
 class _NoSP:
     size = 1
     rank = 0
@@ -463,11 +468,13 @@ class WanDiT(nn.Module):
             return checkpoint(lambda a, b, c: block(a, b, rope, c, memo=memo, **kw), x, e0, ctx, use_reentrant=False)
         return block(x, e0, rope, ctx, **kw)
 
-    def forward(self, x, t, context, y=None, r=None, y_camera=None):
+    def forward(self, x, t, context, y=None, r=None, y_camera=None, perturb_blocks=()):
         """x [B, C, F, H, W] noisy latents; t [B, F] (or [B]) timesteps in [0, 1000];
         context [B, T, text_dim]; y optional channel-concatenated conditioning (I2V);
         y_camera optional ``{"viewmats": [B, F, 4, 4], "Ks": [B, F, 3, 3] or None, "transform": str}``:
-        PRoPE camera conditioning of the self-attention (reference: causal_model.py:925-1000)."""
+        PRoPE camera conditioning of the self-attention (reference: causal_model.py:925-1000);
+        ``perturb_blocks``: indices of blocks whose self-attention is skipped (every token keeps its own
+        value) -- the perturbed evaluation of spatio-temporal guidance."""
         cfg = self.cfg
         P = self.stem.params
         if y is not None:
@@ -515,8 +522,10 @@ class WanDiT(nn.Module):
             mats = camera_prope.prope_matrices(vm, Ks, transform=y_camera.get("transform", "linear"))
             kw["camera"] = tuple(camera_prope.per_row(m, frame_tokens) for m in mats)
         xs = tok
+        skip = {int(i) for i in perturb_blocks}
         for bi, block in enumerate(self.blocks):
-            xs = self._run_block(block, xs, e0_l, rope, ctx, kw, index=bi)
+            kw_b = dict(kw, attn_fn=_identity_attention) if bi in skip else kw
+            xs = self._run_block(block, xs, e0_l, rope, ctx, kw_b, index=bi)
         if sp.size > 1:
             xs = sp.gather_sequence(xs, B)
         # head

@@ -190,3 +190,34 @@ def test_a14b_expert_switch_and_i2v_condition():
     assert calls == ["loaded-high_noise", "low"]
     with pytest.raises(ValueError):
         pair(x, torch.tensor([[0.0, 950.0, 300.0]]), None)
+
+
+def test_ltx_guided_sampler_and_provider():
+    import torch
+
+    from solarwm_b200.backends.ltx25.backend import RuntimeProvider, guided_x0, sample, sample_guided
+    from solarwm_b200.models.ltx import LTXDiT, ltx_preset
+
+    c, u, p = torch.full((4,), 2.0), torch.full((4,), 1.0), torch.full((4,), 0.5)
+    assert torch.allclose(guided_x0(c, u, p, cfg_scale=3.0, stg_scale=1.0), torch.full((4,), 2.0 + 2.0 + 1.5))
+    r = torch.randn(64)
+    out = guided_x0(r, 0.5 * r, 0.5 * r, cfg_scale=3.0, stg_scale=1.0, rescale=1.0)
+    assert abs(float(out.std()) - float(r.std())) < 1e-5               # full rescale restores the conditional spread
+    m = LTXDiT(ltx_preset("tiny"), device="cpu", dtype=torch.float32, seed=0)
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05)
+    text = torch.randn(1, 16, 64)
+    x = torch.randn(1, 16, 2, 4, 4)
+    t = torch.full((1, 2), 500.0)
+    base, pert = m(x, t, text), m(x, t, text, perturb_blocks=(0,))
+    assert not torch.allclose(base, pert, atol=1e-4)
+    plain = sample(m, text, frames=2, height=4, width=4, steps=2, seed=1)
+    same = sample_guided(m, text, torch.zeros_like(text), frames=2, height=4, width=4, steps=2, seed=1, cfg_scale=1.0,
+                         stg_scale=0.0, rescale=0.0)
+    assert torch.allclose(plain, same, atol=1e-5)                        # no guidance = the plain Euler sampler
+    guided = sample_guided(m, text, torch.zeros_like(text), frames=2, height=4, width=4, steps=2, seed=1)
+    assert torch.isfinite(guided).all() and not torch.allclose(plain, guided, atol=1e-3)
+    prov = RuntimeProvider({"model": {"architecture": "tiny", "assets": {"vae": "/nonexistent/vae.pt"}},
+                            "runtime": {"device": "cpu"}})
+    rep = prov.readiness()
+    assert not rep["ready"] and any("vae" in p for p in rep["problems"])
