@@ -55,3 +55,24 @@ def test_h3_stage2_outer_steps_share_one_base():
     r2 = tr.train_outer_step(s, n_chunks=2)
     assert "student" in r2 and r2["student"] == r2["student"]
     assert not torch.equal(before, s_mods[0].lora_B)
+
+
+def test_h3_backend_routes_stage1_and_stage2(tmp_path):
+    from solarwm_b200.backends.minimax_h3.backend import MiniMaxH3Backend
+    from solarwm_b200.checkpoint.store import verify_checkpoint
+
+    base = {"schema": "solarwm.run.v1", "action": "train",
+            "model": {"family": "minimax_h3", "architecture": "tiny", "adapter": {"rank": 4},
+                      "camera_translation_transform": "logd4", "causal": {"chunk_latents": 2, "window_chunks": 1}},
+            "data": {"seed": 0, "latent_frames": 4, "latent_height": 4, "latent_width": 4, "prompt_len": 6, "pixel_frames": 158},
+            "runtime": {"device": "cpu"}}
+    be = MiniMaxH3Backend("minimax_h3")
+    for stage, mode, objective, variant in (("stage1", "teacher_forcing", "anyflow_forward_map", "v1_5"),
+                                            ("stage2", "self_gradient_forcing", "flow_matching", "")):
+        cfg = dict(base, runtime={"device": "cpu", "output_dir": str(tmp_path / stage)},
+                   train={"stage": stage, "causal_mode": mode, "objective": objective, "objective_variant": variant,
+                          "max_steps": 1, "optimizer": {"lr": 1e-3}, "denoise_steps": 1, "critic_updates_per_student": 1})
+        out = be.train(cfg)
+        assert out["final_step"] == 1
+        ok = verify_checkpoint(out["checkpoint"])
+        assert ok.contract.stage == stage and ok.step == 1
