@@ -88,6 +88,42 @@ class FrameAttention(nn.Module):
         return x + o.view(B, T, C, H, W).permute(0, 2, 1, 3, 4)
 
 
+class AvgDown3D(nn.Module):
+    """Parameter-free shortcut of a down-sampling stage: fold ``ft x fs x fs`` neighbourhoods into channels,
+    then average channel groups down to ``cout`` (the first temporal group is padded causally)."""
+
+    def __init__(self, cin, cout, factor_t, factor_s):
+        super().__init__()
+        self.cin, self.cout, self.ft, self.fs = cin, cout, factor_t, factor_s
+        self.group = cin * factor_t * factor_s * factor_s // cout
+
+    def forward(self, x):
+        B, C, T, H, W = x.shape
+        pad_t = (self.ft - T % self.ft) % self.ft
+        x = F.pad(x, (0, 0, 0, 0, pad_t, 0))
+        T2 = x.shape[2]
+        x = x.view(B, C, T2 // self.ft, self.ft, H // self.fs, self.fs, W // self.fs, self.fs)
+        x = x.permute(0, 1, 3, 5, 7, 2, 4, 6).reshape(B, C * self.ft * self.fs * self.fs, T2 // self.ft, H // self.fs, W // self.fs)
+        return x.view(B, self.cout, self.group, *x.shape[2:]).mean(dim=2)
+
+
+class DupUp3D(nn.Module):
+    """Parameter-free shortcut of an up-sampling stage: repeat channels, then unfold them into ``ft x fs x fs``
+    neighbourhoods (the first chunk drops the leading ``ft - 1`` frames, like the learned path)."""
+
+    def __init__(self, cin, cout, factor_t, factor_s):
+        super().__init__()
+        self.cin, self.cout, self.ft, self.fs = cin, cout, factor_t, factor_s
+        self.repeats = cout * factor_t * factor_s * factor_s // cin
+
+    def forward(self, x, first_chunk=False):
+        B, C, T, H, W = x.shape
+        x = x.repeat_interleave(self.repeats, dim=1)
+        x = x.view(B, self.cout, self.ft, self.fs, self.fs, T, H, W).permute(0, 1, 5, 2, 6, 3, 7, 4)
+        x = x.reshape(B, self.cout, T * self.ft, H * self.fs, W * self.fs)
+        return x[:, :, self.ft - 1:] if first_chunk else x
+
+
 class Upsample(nn.Module):
     def __init__(self, dim, temporal: bool):
         super().__init__()

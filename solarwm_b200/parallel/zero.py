@@ -35,8 +35,13 @@ from ..ops._lib import check, ptr, stream_handle
 
 
 class ZeroAdamW(FlatAdamW):
-    def __init__(self, units: Iterable, group=None, *, transport: str = "collective", heap=None, **kw):
+    def __init__(self, units: Iterable, group=None, *, transport: str = "collective", heap=None, replica_group=None,
+                 **kw):
+        """``group``: the ranks one copy of the optimizer state is sharded over.  ``replica_group`` (hybrid
+        sharding): the ranks that hold the SAME shard in other shard groups (e.g. one per node); the reduced
+        gradient shard is summed over it before the update, so every replica applies the identical step."""
         self.group = group
+        self.replica_group = replica_group
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         units = list(units)
@@ -109,10 +114,31 @@ class ZeroAdamW(FlatAdamW):
             store[(i, key)] = torch.empty(n, dtype=torch.float32, device=device)
         return store[(i, key)]
 
+    def _replica_sum(self) -> None:
+        """Hybrid sharding: sum this rank's reduced gradient shards over its replica group."""
+        if self.replica_group is None or dist.get_world_size(self.replica_group) == 1:
+            return
+        for i, key, buf, g, s in self._buffers():
+            a, b = s["range"]
+            shard = self._reduced(i, key, b - a, g.device) if (self.transport == "fused" and self.world > 1) else g[a:b]
+            dist.all_reduce(shard, op=dist.ReduceOp.SUM, group=self.replica_group)
+
     def global_grad_norm(self, sumsq: torch.Tensor) -> torch.Tensor:
+        if self.replica_group is not None and dist.get_world_size(self.replica_group) > 1:
+            self._replica_sum()
+            sumsq = self._shard_sumsq()              # the shards changed: recompute their sum of squares
         if self.world > 1:
             dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
         return sumsq.sqrt()
+
+    def _shard_sumsq(self) -> torch.Tensor:
+        first = True
+        for i, key, buf, g, s in self._buffers():
+            a, b = s["range"]
+            shard = self._reduced(i, key, b - a, g.device) if (self.transport == "fused" and self.world > 1) else g[a:b]
+            ops.sumsq(shard, out=self._norm_sq, accumulate=not first)
+            first = False
+        return self._norm_sq
 
     def step(self) -> None:
         if self.world == 1 or self.transport != "fused":

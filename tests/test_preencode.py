@@ -79,3 +79,18 @@ def test_vae_streaming_decode_matches_full():
     assert torch.allclose(torch.cat(parts, dim=2), full, atol=1e-5)
     enc = vae.encode(torch.randn(1, 3, 17, 32, 32))
     assert enc.shape == (1, 4, 5, 4, 4)
+
+
+def test_parameter_free_resample_shortcuts():
+    from solarwm_b200.models.vae import AvgDown3D, DupUp3D
+
+    x = torch.arange(2 * 4 * 4 * 4 * 4, dtype=torch.float32).view(2, 4, 4, 4, 4)
+    down = AvgDown3D(4, 8, factor_t=2, factor_s=2)(x)
+    assert down.shape == (2, 8, 2, 2, 2)
+    assert torch.allclose(down.mean(), x.mean())                       # averaging preserves the mean
+    up = DupUp3D(8, 4, factor_t=2, factor_s=2)(down)
+    assert up.shape == (2, 4, 4, 4, 4)
+    first = DupUp3D(8, 4, factor_t=2, factor_s=2)(down, first_chunk=True)
+    assert first.shape == (2, 4, 3, 4, 4) and torch.equal(first, up[:, :, 1:])
+    const = torch.full((1, 4, 3, 2, 2), 1.5)
+    assert torch.allclose(AvgDown3D(4, 4, 2, 2)(const)[:, :, 1:], torch.full((1, 4, 1, 1, 1), 1.5))
