@@ -5,7 +5,7 @@
         --master-port P bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...      # the unmodified reference installed in baseline/_ref
 
-Config (BASELINE config 2): 30 blocks, dim 3072, 24 heads, FFN 14336, 48 latent channels, patch
+Config (the headline benchmark shape): 30 blocks, dim 3072, 24 heads, FFN 14336, 48 latent channels, patch
 1x2x2; one sample of latent [1,48,31,44,80] (27,280 tokens), text embedding [1,512,4096], bf16,
 logit-normal sigmas with shift 5; Ulysses SP = N over the N GPUs (the one sample is split, so
 scaling is strong), gradients summed over the SP group, AdamW update inside the timed region.

@@ -63,7 +63,7 @@ class FlowMatchScheduler:
 
 
 def logit_normal_sigmas(n: int, shift: float, generator=None, device="cpu", mean=0.0, std=1.0):
-    """Logit-normal sigma sampling with timestep shift (BASELINE training recipe for Wan-5B shapes)."""
+    """Logit-normal sigma sampling with timestep shift (the training recipe of the Wan-5B-shaped benchmark)."""
     u = torch.randn(n, generator=generator, device=device) * std + mean
     return apply_timestep_shift(torch.sigmoid(u), shift)
 

@@ -1,5 +1,5 @@
 """Real two-process gloo runs on CPU: fail-together error propagation, the data-readiness side
-channel with a failing and a slow reader, and BASELINE config 1 -- the tiny Wan-style DiT trained
+channel with a failing and a slow reader, and the tiny Wan-style DiT (2 blocks, dim 128, SP=2 on gloo) trained
 with Ulysses SP=2 matches the single-process oracle in loss and in every parameter gradient."""
 import os
 import time

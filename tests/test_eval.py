@@ -23,7 +23,7 @@ def test_metrics_identity_and_degradation():
 
 def test_pair_verdict_and_bradley_terry():
     assert ratings.pair_verdict("1", "2", "a", "b") == "a"      # a wins in both orders
-    assert ratings.pair_verdict("1", "1", "a", "b") is None     # the judge followed the slot
+    assert ratings.pair_verdict("1", "1", "a", "b") is None     # the answer followed the slot, not the content
     games = [("a", "b", "a")] * 8 + [("a", "b", "b")] * 2 + [("b", "c", "b")] * 7 + [("b", "c", None)] * 3 + \
             [("a", "c", "a")] * 9 + [("a", "c", "c")]
     r = ratings.fit_bradley_terry(games)
