@@ -193,9 +193,9 @@ def run_ours(args):
     if keep < 0:
         keep = 0
         if ckpt == "selective":
-            # resident bytes of one un-checkpointed block: ~17 [S, dim] and 2 [S, ffn] bf16 tensors
+            # resident bytes of one un-checkpointed block: ~17 [S, dim] and 1 [S, ffn] bf16 tensors
             s_local = n_tokens(cfg, args) / world
-            per_block = s_local * (17 * cfg.dim + 2 * cfg.ffn_dim) * 2
+            per_block = s_local * (17 * cfg.dim + cfg.ffn_dim) * 2      # the GELU output is rebuilt in backward, not kept
             n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
             zero_on = world > 1 and args.zero != "off"
             fixed = (6.0 + 12.0 / (world if zero_on else 1)) * n_params  # bf16 weight + fp32 grad + fp32 master/m/v

@@ -301,8 +301,7 @@ class WanBlock(nn.Module):
         # ---- feed forward
         xm = F_.norm_modulate(x, mod[:, 3], mod[:, 4], eps=cfg.eps, **nk, **gk)
         h = self._linear(xm, "ffn.0.weight", "ffn.0.bias")
-        a = F_.gelu(h)
-        y = self._linear(a, "ffn.2.weight", "ffn.2.bias")
+        y = F_.gelu_linear(h, self._p("ffn.2.weight"), self._p("ffn.2.bias"))
         x = F_.gated_residual(x, y, mod[:, 5], **gk)
         return x
 

@@ -455,6 +455,54 @@ def gelu(x):
     return _GeluFn.apply(x)
 
 
+def _gelu_launch(x, dy, out, backward: int):
+    lib = _lib.load()
+    check(lib.solar_gelu(ptr(x), ptr(dy), ptr(out), ptr(None), c_ll(x.numel()), c_int(backward), stream_handle()), "solar_gelu")
+    count("gelu_bwd" if backward else "gelu_fwd")
+
+
+class _GeluLinearMainGradFn(torch.autograd.Function):
+    """``linear(gelu(h), w, b)`` that keeps only ``h`` for backward: the activation ``gelu(h)`` (the widest
+    tensor of a transformer block) is rebuilt by one elementwise pass when the weight gradient needs it,
+    instead of living in memory from forward to backward."""
+
+    @staticmethod
+    def forward(ctx, h, w, b):
+        h = h.contiguous()
+        a = torch.empty_like(h)
+        _gelu_launch(h, None, a, 0)
+        ctx.save_for_backward(h)
+        ctx.w, ctx.b = w, b
+        return gemm(a, w, NT, bias=b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (h,) = ctx.saved_tensors
+        w, b = ctx.w, ctx.b
+        dy = _rowmajor(dy)
+        if w.requires_grad:
+            a = torch.empty_like(h)
+            _gelu_launch(h, None, a, 0)
+            gemm(dy, a, TN, out=w.main_grad, accumulate=_grad_is_live(w))
+            _mark_grad_live(w)
+            del a
+        if b is not None and b.requires_grad:
+            accumulate_main_grad(b, colsum(dy))
+        dh = None
+        if ctx.needs_input_grad[0]:
+            da = gemm(dy, w, NN)
+            dh = torch.empty_like(h)
+            _gelu_launch(h, da, dh, 1)
+        return dh, None, None
+
+
+def gelu_linear(h, w, b=None):
+    """``linear(gelu_tanh(h), w, b)``; on the device with flat-gradient parameters the activation is not kept."""
+    if h.is_cuda and hasattr(w, "main_grad") and torch.is_grad_enabled():
+        return _GeluLinearMainGradFn.apply(h, w, b)
+    return linear(gelu(h), w, b)
+
+
 class _SwigluFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gu):
