@@ -97,3 +97,38 @@ def test_linear_autograd_matches_reference():
         rel = ((got.float() - ref).norm() / ref.norm()).item()
         assert rel < 6e-3, rel
     assert ops.COUNTERS.get("gemm", 0) >= 3
+
+
+@pytest.mark.parametrize("layout", [ops.NT, ops.NN, ops.TN])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (300, 520, 192), (1000, 776, 200), (4096, 3072, 1024)])
+def test_cta_pair_kernel_is_bit_identical_to_single_cta(layout, shape):
+    """The cta_group::2 kernel (256-row tiles over two SMs) against the single-CTA kernel and the fp32 reference,
+    including tails in M (the second CTA of the last pair owns no rows) and in N and K."""
+    import ctypes
+
+    from solarwm_b200.ops import _lib
+
+    M, N, K = shape
+    if layout == ops.TN and M % 8:
+        pytest.skip("TN needs a 16-byte aligned row stride of A")
+    lib = _lib.load()
+    lib.solar_gemm_pair_mode.argtypes = [ctypes.c_int]
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    a, b = _operands(M, N, K, layout, gen)
+    bias = (torch.randn(N, generator=gen, device="cuda") * 0.1).to(torch.bfloat16)
+    old = lib.solar_gemm_pair_mode(0)
+    try:
+        single = ops.gemm(a, b, layout, bias=bias)
+        single32 = ops.gemm(a, b, layout, out_dtype=torch.float32)
+        lib.solar_gemm_pair_mode(1)
+        pair = ops.gemm(a, b, layout, bias=bias)
+        pair32 = ops.gemm(a, b, layout, out_dtype=torch.float32)
+        acc = pair32.clone()
+        ops.gemm(a, b, layout, out=acc, accumulate=True)
+    finally:
+        lib.solar_gemm_pair_mode(old)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(single, pair) and torch.equal(single32, pair32)
+    _check(pair32, _ref(a, b, layout), K)
+    assert torch.allclose(acc, 2 * pair32, rtol=1e-6, atol=1e-6)
