@@ -153,3 +153,44 @@ class StreamingGenerator:
         self.stats.append(ChunkStats(self.index, ms, use_graph))
         self.index += 1
         return out
+
+
+@torch.no_grad()
+def camera_rollout(model, context: torch.Tensor, grid_hw, viewmats: torch.Tensor, Ks: Optional[torch.Tensor] = None, *,
+                   cfg: StreamingConfig = StreamingConfig(), first_frame: Optional[torch.Tensor] = None,
+                   transform: str = "linear", sp=None) -> torch.Tensor:
+    """Camera-length rollout: as many chunks as the camera path has frames.  ``viewmats`` [1, F, 4, 4]
+    (first-frame-relative world-to-camera), ``Ks`` [1, F, 3, 3] or None.  Every evaluation of a chunk carries
+    the chunk's cameras (queries) while cached keys / values keep the cameras of their own frames.
+    Returns the latents [1, C, F, H, W] (reference: camera-length rollout of the inference adapter,
+    solar/backends/wan22/runtime/inference.py:1647-1714)."""
+    gen = StreamingGenerator(model, cfg, sp=sp)
+    gen.start(context, grid_hw, first_frame=None)
+    F_total = viewmats.shape[1]
+    f0 = 0
+    outs = []
+
+    def cams(a, b):
+        return {"viewmats": viewmats[:, a:b], "Ks": None if Ks is None else Ks[:, a:b], "transform": transform}
+
+    if first_frame is not None:
+        t0 = torch.zeros(1, 1, device=gen.device)
+        gen.runner.forward_chunk(gen.cache, first_frame.to(gen.device), t0, commit=True, y_camera=cams(0, 1))
+        outs.append(first_frame.to(gen.device, model.dtype))
+        f0 = 1
+    while f0 < F_total:
+        f = min(cfg.chunk_frames, F_total - f0)
+        cam = cams(f0, f0 + f)
+        x = gen._noise(f)
+        x0 = x
+        for k in range(len(gen.sigmas) - 1):
+            s, s_next = gen.sigmas[k], gen.sigmas[k + 1]
+            t = torch.full((1, f), s * 1000.0, device=gen.device)
+            v = gen.runner.forward_chunk(gen.cache, x, t, commit=False, y_camera=cam)
+            x0 = (x.float() - s * v.float()).to(x.dtype)
+            if s_next > 0:
+                x = ((1 - s_next) * x0.float() + s_next * gen._noise(f).float()).to(x.dtype)
+        gen.runner.forward_chunk(gen.cache, x0, torch.zeros(1, f, device=gen.device), commit=True, y_camera=cam)
+        outs.append(x0)
+        f0 += f
+    return torch.cat(outs, dim=2)

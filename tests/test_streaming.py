@@ -126,3 +126,25 @@ def test_cache_runner_camera_prope_matches_bidirectional_first_chunk():
     assert torch.allclose(a, b, atol=1e-4)
     c = runner.forward_chunk(cache, x2, t, commit=False, y_camera=cam)
     assert not torch.allclose(a, c, atol=1e-3)
+
+
+def test_camera_length_rollout():
+    import torch
+
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+    from solarwm_b200.serve.streaming import StreamingConfig, camera_rollout
+
+    cfg = WanConfig(model_type="t2v", in_dim=4, out_dim=4, dim=256, ffn_dim=256, num_heads=2, num_layers=1, text_dim=32,
+                    text_len=8, freq_dim=32)
+    m = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05)
+    scfg = StreamingConfig(chunk_frames=2, window_frames=4, sink_frames=0, denoise_timesteps=(1000.0, 500.0), use_cuda_graphs=False, seed=3)
+    view = torch.eye(4).repeat(1, 7, 1, 1)
+    view[0, :, 0, 3] = torch.linspace(0, 0.6, 7)
+    ctx = torch.randn(1, 8, 32)
+    first = torch.randn(1, 4, 1, 4, 4)
+    out = camera_rollout(m, ctx, (2, 2), view, None, cfg=scfg, first_frame=first)
+    assert out.shape == (1, 4, 7, 4, 4) and torch.isfinite(out).all() and torch.equal(out[:, :, :1], first)
+    still = camera_rollout(m, ctx, (2, 2), torch.eye(4).repeat(1, 7, 1, 1), None, cfg=scfg, first_frame=first)
+    assert not torch.allclose(out[:, :, 3:], still[:, :, 3:], atol=1e-4)          # the camera path matters
