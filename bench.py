@@ -169,6 +169,13 @@ def run_ours(args):
 
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
+        # the fused transports need peer access between every pair of GPUs; all ranks agree on the answer before
+        # any symmetric buffer is exchanged, and fall back to the NCCL forms together otherwise
+        can = all(torch.cuda.can_device_access_peer(local, d) for d in range(world) if d != local)
+        agree = torch.tensor([1 if can else 0], device=f"cuda:{local}")
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            args.sp_transport, args.zero = "nccl", ("collective" if args.zero == "fused" else args.zero)
         if args.sp_transport == "fused":
             from solarwm_b200.parallel.fused_ulysses import FusedUlysses
 
