@@ -234,6 +234,13 @@ class CompensationTable:
         z = torch.zeros(window, 3, frames)
         return cls(z.clone(), z.clone(), z.clone())
 
+    def folded_affine(self, slot: int, frame: int, mean: torch.Tensor, std: torch.Tensor):
+        """Per-channel constants (std', mean') such that ``x * std' + mean'`` equals de-normalising the
+        compensated pixel ``(x - (a + b x)) * std + mean``: the linear part of the compensation rides on the
+        RGB8 conversion kernel's own affine step, so emitting a frame stays one pass over the pixels."""
+        a, b = self.a[slot, :, frame].to(std), self.b[slot, :, frame].to(std)
+        return std * (1.0 - b), mean - a * std
+
     def apply(self, frames: torch.Tensor, slot: int, first_of_stream: bool) -> torch.Tensor:
         """frames [3, F, H, W] (F <= frames_per_latent, the last F positions of the slot)."""
         F_n = frames.shape[1]

@@ -54,3 +54,16 @@ def test_compensation_table():
     assert torch.allclose(y[0], torch.full((4, 2, 2), 0.5)) and torch.allclose(y[1], torch.full((4, 2, 2), 0.9))
     first = t.apply(torch.ones(3, 1, 2, 2), slot=0, first_of_stream=True)
     assert torch.allclose(first, torch.full((3, 1, 2, 2), -1.0))
+
+
+def test_compensation_folds_into_the_pixel_affine():
+    t = CompensationTable.zeros(7, 4)
+    t.a[3] = torch.rand(3, 4) * 0.1
+    t.b[3] = torch.rand(3, 4) * 0.2
+    mean, std = torch.tensor([0.4, 0.5, 0.6]), torch.tensor([0.2, 0.25, 0.3])
+    x = torch.randn(3, 4, 5, 6)
+    want = t.apply(x, slot=3, first_of_stream=False) * std.view(3, 1, 1, 1) + mean.view(3, 1, 1, 1)
+    for f in range(4):
+        s2, m2 = t.folded_affine(3, f, mean, std)
+        got = x[:, f] * s2.view(3, 1, 1) + m2.view(3, 1, 1)
+        assert torch.allclose(got, want[:, f], atol=1e-6)
