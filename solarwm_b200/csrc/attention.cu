@@ -284,7 +284,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int e = 0; e < 64; ++e) {
         const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, n2);
         // every other pair takes the FMA-pipe exponential so that MUFU and FMA pipes share the load
-        const float2 pp = (e & 1) ? exp2_poly2(tt) : make_float2(exp2_fast(tt.x), exp2_fast(tt.y));
+        const float2 pp = ((e & 3) == 3) ? exp2_poly2(tt) : make_float2(exp2_fast(tt.x), exp2_fast(tt.y));
         l2 = __fadd2_rn(l2, pp);
         s[e] = pack_bf16x2(pp.x, pp.y);
       }
