@@ -200,14 +200,16 @@ def run_ours(args):
     if keep < 0:
         keep = 0
         if ckpt == "selective":
-            # resident bytes of one un-checkpointed block: ~17 [S, dim] and 1 [S, ffn] bf16 tensors
+            # calibrated on this model (peak_allocated with 11 / 13 / 15 resident blocks): an un-checkpointed block
+            # keeps ~14.5 [S, dim] and 1 [S, ffn] bf16 tensors (the GELU output is rebuilt in backward); a checkpointed
+            # one its input and the two attention outputs; 18 GB covers those plus workspace at S = 27,280
             s_local = n_tokens(cfg, args) / world
-            per_block = s_local * (17 * cfg.dim + cfg.ffn_dim) * 2      # the GELU output is rebuilt in backward, not kept
+            per_block = s_local * (14.5 * cfg.dim + cfg.ffn_dim) * 2
             n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
             zero_on = world > 1 and args.zero != "off"
             fixed = (6.0 + 12.0 / (world if zero_on else 1)) * n_params  # bf16 weight + fp32 grad + fp32 master/m/v
             total = torch.cuda.get_device_properties(local).total_memory
-            keep = int(max(0.0, 0.92 * total - fixed - 0.6e9 * cfg.num_layers - 12e9) // per_block)
+            keep = int(max(0.0, 0.88 * total - fixed - 18e9 / world) // per_block)
             keep = min(keep, cfg.num_layers)
     zero = world > 1 and args.zero != "off"
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
