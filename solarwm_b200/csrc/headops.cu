@@ -133,6 +133,63 @@ __global__ void __launch_bounds__(256) headnorm_bwd_kernel(HeadNormBwdParams p) 
   *reinterpret_cast<uint2*>(p.dx + tok * p.lddx + head * 128 + c0) = out;
 }
 
+// Streaming ViT decoder step: per-head RMSNorm of q and k, rotate-half rotary over the whole head, and the
+// write of k / v straight into their slot of the window cache.  One warp per (row, head); lane l owns the
+// channel pairs (j, j + dh/2) for j = l, l + 32, ...  The qkv row is read once; q goes to a packed buffer,
+// k and v to cache rows [lo, lo + N) of each batch entry.  Replaces the reference's Triton kernel for the
+// decoder step (deploy/.../streaming.py:311-412).
+struct VitQkvParams {
+  const __nv_bfloat16* qkv; long long ld;     // [B*N, 3*H*dh]
+  const float* qw; const float* kw;           // [dh]
+  const float* cos_t; const float* sin_t;     // [N, dh] or null
+  __nv_bfloat16* q_out;                       // [B*N, H*dh]
+  __nv_bfloat16* k_cache; __nv_bfloat16* v_cache; long long cache_batch; long long lo;   // [B, rows, H*dh]
+  long long B, N; int H, dh; float eps;
+};
+
+__global__ void __launch_bounds__(256) vit_qkv_kernel(VitQkvParams p) {
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= p.B * p.N * p.H) return;
+  const long long row = gw / p.H;
+  const int head = static_cast<int>(gw - row * p.H);
+  const long long b = row / p.N, n = row - b * p.N;
+  const int half = p.dh >> 1, a = p.H * p.dh;
+  const __nv_bfloat16* src = p.qkv + row * p.ld + head * p.dh;
+  const long long crow = b * p.cache_batch + (p.lo + n) * a + head * p.dh;
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* x = src + which * a;
+    const float* w = which == 0 ? p.qw : p.kw;
+    __nv_bfloat16* dst = which == 0 ? p.q_out + row * a + head * p.dh : p.k_cache + crow;
+    float ss = 0.f;
+    for (int j = lane; j < half; j += 32) {
+      const float x0 = __bfloat162float(x[j]), x1 = __bfloat162float(x[j + half]);
+      ss += x0 * x0 + x1 * x1;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / static_cast<float>(p.dh) + p.eps);
+    for (int j = lane; j < half; j += 32) {
+      // the normalised value is rounded to bf16 before the rotation, as the unfused composition does
+      float y0 = __bfloat162float(__float2bfloat16(__bfloat162float(x[j]) * rstd * w[j]));
+      float y1 = __bfloat162float(__float2bfloat16(__bfloat162float(x[j + half]) * rstd * w[j + half]));
+      if (p.cos_t != nullptr) {
+        const float* c = p.cos_t + n * p.dh;
+        const float* s = p.sin_t + n * p.dh;
+        const float r0 = y0 * c[j] - y1 * s[j];
+        const float r1 = y1 * c[j + half] + y0 * s[j + half];
+        y0 = r0; y1 = r1;
+      }
+      dst[j] = __float2bfloat16(y0);
+      dst[j + half] = __float2bfloat16(y1);
+    }
+  }
+  const __nv_bfloat16* v = src + 2 * a;
+  __nv_bfloat16* vd = p.v_cache + crow;
+  for (int j = lane; j < p.dh; j += 32) vd[j] = v[j];
+}
+
 }  // namespace solar
 
 using namespace solar;
@@ -163,6 +220,19 @@ extern "C" int solar_headnorm_bwd(const void* g, long long ldg, const void* xin,
   HeadNormBwdParams p{(const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)xin, ldx, (__nv_bfloat16*)dx, lddx, w, rstd, S, H};
   const long long blocks = (S * H * 32 + 255) / 256;
   headnorm_bwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int solar_vit_qkv(const void* qkv, long long ld, const float* qw, const float* kw, const float* cos_t,
+                             const float* sin_t, void* q_out, void* k_cache, void* v_cache, long long cache_batch,
+                             long long lo, long long B, long long N, int H, int dh, float eps, void* stream) {
+  if (dh < 2 || dh % 2 != 0) return fail("vit_qkv: head_dim must be even%s");
+  if (B <= 0 || N <= 0 || H <= 0) return 0;
+  VitQkvParams p{(const __nv_bfloat16*)qkv, ld, qw, kw, cos_t, sin_t, (__nv_bfloat16*)q_out,
+                 (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, cache_batch, lo, B, N, H, dh, eps};
+  const long long blocks = (B * N * H * 32 + 255) / 256;
+  vit_qkv_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }

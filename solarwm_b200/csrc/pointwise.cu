@@ -291,6 +291,64 @@ __global__ void rgb8_kernel(Rgb8Params p) {
   }
 }
 
+// Tile blend + compensation of the streaming decoder's output: every output pixel is the ramp-weighted
+// mean of the tiles that cover it (linear ramps across the overlaps, weights normalised to one), followed
+// by x - (a + b x + c x^2) with per (channel, frame) constants.  One thread per output pixel, all channels
+// and frames of it in registers; every tile pixel is read once.
+struct TileBlendParams {
+  const __nv_bfloat16* tiles; long long st, sc, sf;   // [T, 3, F, tH, tW], inner two dims contiguous
+  float* out;                                         // [3, F, H, W]
+  int T, F, tH, tW, H, W, ov;
+  int py[32], px[32];                                 // pixel offsets of the tiles
+  float a[3][4], b[3][4], c[3][4];                    // compensation constants (zero = none)
+};
+
+__device__ __forceinline__ float ramp_weight(int l, int n, bool lo, bool hi, int ov) {
+  float w = 1.f;
+  if (ov > 0) {
+    const float step = 1.f / static_cast<float>(ov + 1);
+    if (lo && l < ov) w = static_cast<float>(l + 1) * step;
+    if (hi && l >= n - ov) w = 1.f - static_cast<float>(l - (n - ov) + 1) * step;
+  }
+  return w;
+}
+
+__global__ void tile_blend_kernel(TileBlendParams p) {
+  const long long hw = (long long)p.H * p.W;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < hw;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int Y = static_cast<int>(i / p.W), X = static_cast<int>(i - (long long)Y * p.W);
+    float acc[3][4];
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+#pragma unroll
+      for (int f = 0; f < 4; ++f) acc[c][f] = 0.f;
+    float wsum = 0.f;
+    for (int t = 0; t < p.T; ++t) {
+      const int ly = Y - p.py[t], lx = X - p.px[t];
+      if (ly < 0 || ly >= p.tH || lx < 0 || lx >= p.tW) continue;
+      const float w = ramp_weight(ly, p.tH, p.py[t] > 0, p.py[t] + p.tH < p.H, p.ov) *
+                      ramp_weight(lx, p.tW, p.px[t] > 0, p.px[t] + p.tW < p.W, p.ov);
+      wsum += w;
+      const __nv_bfloat16* src = p.tiles + t * p.st + (long long)ly * p.tW + lx;
+#pragma unroll
+      for (int c = 0; c < 3; ++c)
+#pragma unroll
+        for (int f = 0; f < 4; ++f)
+          if (f < p.F) acc[c][f] += w * __bfloat162float(src[c * p.sc + f * p.sf]);
+    }
+    const float inv = 1.f / fmaxf(wsum, 1e-8f);
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+#pragma unroll
+      for (int f = 0; f < 4; ++f)
+        if (f < p.F) {
+          const float x = acc[c][f] * inv;
+          p.out[((long long)c * p.F + f) * hw + i] = x - (p.a[c][f] + p.b[c][f] * x) - p.c[c][f] * x * x;
+        }
+  }
+}
+
 static inline int grid_for(long long work, int block) {
   long long g = (work + block - 1) / block;
   const long long cap = static_cast<long long>(sm_count()) * 16;
@@ -383,6 +441,28 @@ extern "C" int solar_rgb8(const void* chw, void* hwc, int H, int W, long long sc
   for (int c = 0; c < 3; ++c) { p.mean[c] = mean3[c]; p.std_[c] = std3[c]; }
   p.nonfinite = nonfinite;
   rgb8_kernel<<<grid_for((long long)H * W, 256), 256, 0, (cudaStream_t)stream>>>(p);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// coef: [3 (a, b, c), 3 channels, F] fp32 on the HOST, or null for no compensation.
+extern "C" int solar_tile_blend(const void* tiles, long long st, long long sc, long long sf, void* out, int T,
+                                int F, int tH, int tW, int H, int W, int ov, const int* py, const int* px,
+                                const float* coef, void* stream) {
+  if (T < 1 || T > 32) return fail("tile_blend: 1..32 tiles%s");
+  if (F < 1 || F > 4) return fail("tile_blend: 1..4 frames per call%s");
+  TileBlendParams p;
+  p.tiles = (const __nv_bfloat16*)tiles; p.st = st; p.sc = sc; p.sf = sf; p.out = (float*)out;
+  p.T = T; p.F = F; p.tH = tH; p.tW = tW; p.H = H; p.W = W; p.ov = ov;
+  for (int t = 0; t < 32; ++t) { p.py[t] = t < T ? py[t] : 0; p.px[t] = t < T ? px[t] : 0; }
+  for (int c = 0; c < 3; ++c)
+    for (int f = 0; f < 4; ++f) {
+      const bool on = coef != nullptr && f < F;
+      p.a[c][f] = on ? coef[(0 * 3 + c) * F + f] : 0.f;
+      p.b[c][f] = on ? coef[(1 * 3 + c) * F + f] : 0.f;
+      p.c[c][f] = on ? coef[(2 * 3 + c) * F + f] : 0.f;
+    }
+  tile_blend_kernel<<<grid_for((long long)H * W, 256), 256, 0, (cudaStream_t)stream>>>(p);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }

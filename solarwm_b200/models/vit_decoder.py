@@ -136,6 +136,15 @@ class ViTVideoDecoder(nn.Module):
             q, k = apply_rope(q, cos, sin, c.heads), apply_rope(k, cos, sin, c.heads)
         return q, k, qkv[..., 2 * a:]
 
+    def block_q_cached(self, blk: ViTBlock, x, cos, sin, k_cache, v_cache, lo: int):
+        """The streaming form of ``block_qkv``: q is returned, k / v land in cache rows [lo, lo + N) through
+        one fused kernel (head norms, rotary and the cache write share one pass over the qkv rows)."""
+        c = self.cfg
+        B, N, _ = x.shape
+        xm = F_.norm_modulate(x.reshape(B * N, -1), mode=1, w=blk.norm1, eps=c.eps)
+        qkv = F_.linear(xm, blk.qkv).view(B, N, -1)
+        return F_.vit_qkv_to_cache(qkv, blk.q_norm, blk.k_norm, cos, sin, k_cache, v_cache, lo, heads=c.heads, eps=c.eps)
+
     def block_finish(self, blk: ViTBlock, x, o):
         c = self.cfg
         B, N, _ = x.shape
@@ -241,6 +250,15 @@ class CompensationTable:
         a, b = self.a[slot, :, frame].to(std), self.b[slot, :, frame].to(std)
         return std * (1.0 - b), mean - a * std
 
+    def coefficients(self, slot: int, n_frames: int, first_of_stream: bool) -> torch.Tensor:
+        """Host tensor [3 (a, b, c), 3 channels, n_frames] for the last ``n_frames`` positions of ``slot``;
+        the quadratic term is kept for the first emitted frame of a stream only."""
+        out = torch.zeros(3, 3, n_frames)
+        out[0], out[1] = self.a[slot, :, -n_frames:], self.b[slot, :, -n_frames:]
+        if first_of_stream and self.c is not None:
+            out[2, :, 0] = self.c[slot, :, -n_frames:][:, 0]
+        return out
+
     def apply(self, frames: torch.Tensor, slot: int, first_of_stream: bool) -> torch.Tensor:
         """frames [3, F, H, W] (F <= frames_per_latent, the last F positions of the slot)."""
         F_n = frames.shape[1]
@@ -282,7 +300,7 @@ class StreamingViTDecoder:
         self.v = [torch.zeros(n, rows, a, dtype=self.m.dtype, device=dev) for _ in self.m.blocks]
         self.count = 0                      # latents received
         self.recent: List[torch.Tensor] = []   # the last window - stride latents (for the shift refill)
-        self._rope = {s: tuple(t.to(dev) for t in rope_tables(s, c.window, self.th, self.tw, c.dim_head))
+        self._rope = {s: tuple(t.to(dev, torch.float32).contiguous() for t in rope_tables(s, c.window, self.th, self.tw, c.dim_head))
                       for s in range(c.window)}
         self._registers_ready = False
 
@@ -302,9 +320,8 @@ class StreamingViTDecoder:
         self._reg_x = []
         for li, blk in enumerate(m.blocks):
             self._reg_x.append(x)
-            q, k, v = m.block_qkv(blk, x, None, None)
-            self.k[li][:, :c.registers], self.v[li][:, :c.registers] = k, v
-            x = m.block_finish(blk, x, m.attend(q, k, v))
+            q = m.block_q_cached(blk, x, None, None, self.k[li], self.v[li], 0)
+            x = m.block_finish(blk, x, m.attend(q, self.k[li][:, :c.registers], self.v[li][:, :c.registers]))
         self._registers_ready = True
 
     def _run_slot(self, latent: torch.Tensor, slot: int, emit: bool):
@@ -317,8 +334,7 @@ class StreamingViTDecoder:
         cos, sin = self._rope[slot]
         lo = c.registers + slot * hw
         for li, blk in enumerate(m.blocks):
-            q, k, v = m.block_qkv(blk, x, cos, sin)
-            self.k[li][:, lo:lo + hw], self.v[li][:, lo:lo + hw] = k, v
+            q = m.block_q_cached(blk, x, cos, sin, self.k[li], self.v[li], lo)
             o = m.attend(q, self.k[li][:, :lo + hw], self.v[li][:, :lo + hw])
             x = m.block_finish(blk, x, o)
         return x if emit else None
@@ -350,6 +366,11 @@ class StreamingViTDecoder:
         if first_of_group:
             frames = frames[:, :, -1:]
         self.count += 1
+        if self.world == 1 and frames.is_cuda and frames.dtype == torch.bfloat16 and len(self.plan) <= 32:
+            # one pass over the pixels: ramp-weighted tile mean and the compensation polynomial together
+            coef = None if self.table is None else self.table.coefficients(slot, frames.shape[2], first_of_stream=(i == 0))
+            offs = [(y * c.patch, x * c.patch) for (y, x) in self.plan]
+            return F_.tile_blend(frames, offs, self.h * c.patch, self.w * c.patch, self.overlap * c.patch, coef)
         out = self._gather(frames)
         if out is None:
             return None

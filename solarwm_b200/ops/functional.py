@@ -702,6 +702,73 @@ def rgb8(frame_chw, mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225)):
 
 
 # --------------------------------------------------------------------------------------
+# streaming ViT decoder step: q/k head RMSNorm + rotary + k/v cache write; tile blend + compensation
+# --------------------------------------------------------------------------------------
+def vit_qkv_to_cache(qkv, q_w, k_w, cos, sin, k_cache, v_cache, lo: int, *, heads: int, eps: float = 1e-6):
+    """qkv bf16 ``[B, N, 3*heads*dh]`` -> q ``[B, N, heads*dh]``; k and v are written into rows
+    ``[lo, lo + N)`` of ``k_cache`` / ``v_cache`` ``[B, rows, heads*dh]`` (no autograd; inference only).
+
+    Same arithmetic as per-head RMSNorm (rounded to bf16) followed by rotate-half rotary with per-row
+    ``cos`` / ``sin`` ``[N, dh]`` (``None`` = no rotation)."""
+    B, N, three_a = qkv.shape
+    a = three_a // 3
+    dh = a // heads
+    if not qkv.is_cuda:
+        def norm(x, w):
+            v = x.reshape(B, N, heads, dh).float()
+            return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(qkv.dtype)
+
+        def rot(x):
+            if cos is None:
+                return x
+            v = x.float()
+            r = torch.cat([-v[..., dh // 2:], v[..., :dh // 2]], dim=-1)
+            return (v * cos.view(1, N, 1, dh) + r * sin.view(1, N, 1, dh)).to(qkv.dtype)
+
+        q = rot(norm(qkv[..., :a], q_w)).reshape(B, N, a)
+        k_cache[:, lo:lo + N] = rot(norm(qkv[..., a:2 * a], k_w)).reshape(B, N, a)
+        v_cache[:, lo:lo + N] = qkv[..., 2 * a:]
+        return q
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(2) == 1 and qkv.stride(0) == N * qkv.stride(1)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[2] == a
+    assert q_w.dtype == torch.float32 and k_w.dtype == torch.float32
+    if cos is not None:
+        assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape == (N, dh)
+    q = torch.empty((B, N, a), dtype=qkv.dtype, device=qkv.device)
+    rc = _lib.load().solar_vit_qkv(ptr(qkv), c_ll(qkv.stride(1)), ptr(q_w), ptr(k_w), ptr(cos), ptr(sin), ptr(q),
+                                   ptr(k_cache), ptr(v_cache), c_ll(k_cache.stride(0)), c_ll(lo), c_ll(B), c_ll(N),
+                                   c_int(heads), c_int(dh), c_float(eps), stream_handle())
+    check(rc, "solar_vit_qkv")
+    count("vit_qkv")
+    return q
+
+
+def tile_blend(tiles, offsets, H: int, W: int, overlap_px: int, coef=None):
+    """tiles bf16 ``[T, 3, F, tH, tW]`` on CUDA (inner two dims contiguous), ``offsets`` the pixel ``(y, x)`` of
+    each tile -> fp32 ``[3, F, H, W]``: ramp-weighted mean over the tiles that cover a pixel, then
+    ``x - (a + b x + c x^2)`` with ``coef`` a host fp32 tensor ``[3 (a, b, c), 3, F]`` (``None`` = identity)."""
+    import ctypes
+
+    T, C, F_n, tH, tW = tiles.shape
+    assert tiles.is_cuda and tiles.dtype == torch.bfloat16 and C == 3
+    assert tiles.stride(4) == 1 and tiles.stride(3) == tW and len(offsets) == T
+    out = torch.empty((3, F_n, H, W), dtype=torch.float32, device=tiles.device)
+    py = (ctypes.c_int * T)(*[int(o[0]) for o in offsets])
+    px = (ctypes.c_int * T)(*[int(o[1]) for o in offsets])
+    cf = None
+    if coef is not None:
+        flat = coef.detach().to("cpu", torch.float32).contiguous().view(-1).tolist()
+        assert len(flat) == 9 * F_n
+        cf = (ctypes.c_float * len(flat))(*flat)
+    rc = _lib.load().solar_tile_blend(ptr(tiles), c_ll(tiles.stride(0)), c_ll(tiles.stride(1)), c_ll(tiles.stride(2)),
+                                      ptr(out), c_int(T), c_int(F_n), c_int(tH), c_int(tW), c_int(H), c_int(W),
+                                      c_int(overlap_px), py, px, cf, stream_handle())
+    check(rc, "solar_tile_blend")
+    count("tile_blend")
+    return out
+
+
+# --------------------------------------------------------------------------------------
 # per-head RMSNorm + MM-RoPE + PRoPE (H3 attention path)
 # --------------------------------------------------------------------------------------
 class _HeadOpFn(torch.autograd.Function):

@@ -51,6 +51,70 @@ def test_vit_decoder_streaming_matches_window_oracle_on_gpu():
         assert err < 3e-2, (i, float(err))
 
 
+def test_vit_qkv_kernel_matches_unfused_composition():
+    from solarwm_b200.models.vit_decoder import _head_rms, apply_rope
+    from solarwm_b200.ops import functional as F_
+
+    g = torch.Generator().manual_seed(0)
+    for heads, dh in ((2, 64), (3, 128), (2, 32)):
+        B, N, rows, lo = 3, 37, 100, 11
+        a = heads * dh
+        qkv = torch.randn(B, N, 3 * a, generator=g).cuda().bfloat16()
+        qw, kw = (torch.rand(dh, generator=g) + 0.5).cuda(), (torch.rand(dh, generator=g) + 0.5).cuda()
+        ang = torch.rand(N, dh, generator=g) * 6.0
+        cos, sin = torch.cos(ang).cuda(), torch.sin(ang).cuda()
+        for use_rope in (True, False):
+            kc = torch.zeros(B, rows, a, device="cuda", dtype=torch.bfloat16)
+            vc = torch.zeros_like(kc)
+            q = F_.vit_qkv_to_cache(qkv, qw, kw, cos if use_rope else None, sin if use_rope else None, kc, vc, lo,
+                                    heads=heads, eps=1e-6)
+            q_ref = _head_rms(qkv[..., :a], qw, heads, 1e-6)
+            k_ref = _head_rms(qkv[..., a:2 * a], kw, heads, 1e-6)
+            if use_rope:
+                q_ref, k_ref = apply_rope(q_ref, cos, sin, heads), apply_rope(k_ref, cos, sin, heads)
+            assert (q.float() - q_ref.float()).abs().max() < 4e-2
+            assert (kc[:, lo:lo + N].float() - k_ref.float()).abs().max() < 4e-2
+            assert torch.equal(vc[:, lo:lo + N], qkv[..., 2 * a:])
+            assert kc[:, :lo].abs().sum() == 0 and kc[:, lo + N:].abs().sum() == 0 and vc[:, lo + N:].abs().sum() == 0
+
+
+def test_tile_blend_kernel_matches_reference_blend_and_compensation():
+    from solarwm_b200.models.vit_decoder import CompensationTable, blend_tiles, tile_plan
+    from solarwm_b200.ops import functional as F_
+
+    g = torch.Generator().manual_seed(0)
+    h, w, tile, overlap, patch, F = 6, 10, 4, 2, 4, 4
+    plan = tile_plan(h, w, tile, overlap)
+    tiles = torch.randn(len(plan), 3, F, tile * patch, tile * patch, generator=g).cuda().bfloat16()
+    table = CompensationTable(torch.randn(7, 3, F, generator=g) * 0.1, torch.randn(7, 3, F, generator=g) * 0.1,
+                              torch.randn(7, 3, F, generator=g) * 0.1)
+    offs = [(y * patch, x * patch) for (y, x) in plan]
+    for n_frames, first in ((F, False), (1, True), (F, True)):
+        t = tiles[:, :, -n_frames:]
+        want = blend_tiles([t[j] for j in range(t.shape[0])], plan, h, w, tile, overlap, patch)
+        plain = F_.tile_blend(t, offs, h * patch, w * patch, overlap * patch, None)
+        assert (plain - want).abs().max() < 1e-5
+        got = F_.tile_blend(t, offs, h * patch, w * patch, overlap * patch, table.coefficients(3, n_frames, first))
+        assert (got - table.apply(want, 3, first)).abs().max() < 1e-5
+
+
+def test_vit_decoder_tiled_streaming_runs_fused_kernels():
+    from solarwm_b200.models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+    from solarwm_b200.ops import _lib
+
+    cfg = ViTDecoderConfig(latent_channels=8, dim=128, depth=2, heads=2, dim_head=64, ffn_dim=256, registers=8, patch=2)
+    m = ViTVideoDecoder(cfg, device="cuda", dtype=torch.bfloat16, seed=0)
+    lat = torch.randn(3, 8, 8, 12, generator=torch.Generator().manual_seed(1)).cuda()
+    dec = StreamingViTDecoder(m, (8, 12), tile=8, overlap=4)
+    before = dict(_lib.COUNTERS)
+    outs = [dec.push(lat[i]) for i in range(3)]
+    after = _lib.COUNTERS
+    assert after.get("tile_blend", 0) - before.get("tile_blend", 0) == 3
+    assert after.get("vit_qkv", 0) > before.get("vit_qkv", 0)
+    assert outs[0].shape == (3, 1, 16, 24) and outs[1].shape == (3, cfg.frames_per_latent, 16, 24)
+    assert all(torch.isfinite(o).all() for o in outs)
+
+
 def test_wan_teacher_forcing_matches_cpu_fp32():
     from solarwm_b200.models import wan_tf
     from solarwm_b200.models.wan import WanConfig, WanDiT
