@@ -41,14 +41,6 @@ struct AttnParams {
   int* status;
 };
 
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2,
-                                             int c3) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(m)),
-               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-               : "memory");
-}
-
 template <int HD>
 struct AttnSmem {
   static constexpr int CHUNKS = HD / 64;                 // 64-element (128-byte) column chunks

@@ -37,7 +37,22 @@ constexpr int SMEM_TOTAL = SMEM_MAIN + 256 + 1024;  // barriers + alignment slac
 constexpr int GEMM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
+// Implicit-GEMM convolution on channels-last activations [T, H, W, C]: a 128-row tile of the "A" operand is a
+// 16 x 8 pixel box of one frame, fetched by ONE 4-D TMA load per (tap, 64-channel block) at the box origin
+// shifted by the tap's (dt, dh, dw); positions outside the tensor read zeros (the spatial "same" padding and
+// the causal temporal padding need no padded copy).  The K loop runs over taps x channel blocks against
+// weights stored [Cout, taps * kb_per_tap * 64].  The epilogue stores each warp's 2 x 16 pixels with a 4-D TMA
+// store, which clips at the frame border.
+constexpr int CONV_BOX_W = 16, CONV_BOX_H = 8;
+struct ConvPlan {
+  int taps;                 // 0: plain GEMM
+  int kb_per_tap;
+  int tiles_w, tiles_h;
+  signed char dt[28], dh[28], dw[28];
+};
+
 struct GemmParams {
+  ConvPlan conv;
   int M, N, K;
   int tiles_m, tiles_n;
   const __nv_bfloat16* bias;  // [N] or null
@@ -63,7 +78,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // column n0 -> bias / activation -> staged through shared memory -> TMA store, reduce-add or peer scatter.
 template <int OUT_F32>
 __device__ __forceinline__ void epilogue_tile(const CUtensorMap& tmC, const GemmParams& p, const ColScatter& sc,
-                                              uint32_t t_row, int row0, int n0, uint8_t* my_buf, int& buf, int lane) {
+                                              uint32_t t_row, int row0, int n0, uint8_t* my_buf, int& buf, int lane,
+                                              int cw = 0, int ch = 0, int ct = 0) {
   constexpr int CHUNK = OUT_F32 ? 32 : 64;  // columns per 128-byte staged row
   const bool rows_live = (row0) < p.M;
 #pragma unroll 1
@@ -142,7 +158,9 @@ __device__ __forceinline__ void epilogue_tile(const CUtensorMap& tmC, const Gemm
     __syncwarp();
     if (lane == 0 && rows_live) {
       const void* src = my_buf + buf * EPI_BUF_BYTES;
-      if (p.accumulate) {
+      if (p.conv.taps != 0) {
+        tma_store_4d(&tmC, src, ncol, cw, ch, ct);   // this warp's 2 x 16 pixels x 64 channels
+      } else if (p.accumulate) {
         asm volatile(
             "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::
                 "l"(reinterpret_cast<uint64_t>(&tmC)),
@@ -225,6 +243,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
               tma_load_2d(sa + c * (64 * BK * 2), &tmA, &full_bar[stage], m0 + c * 64, k0);
+          } else if (p.conv.taps != 0) {
+            const int tap = kb / p.conv.kb_per_tap;
+            const int tw = tm % p.conv.tiles_w, rest = tm / p.conv.tiles_w;
+            const int th = rest % p.conv.tiles_h, tt = rest / p.conv.tiles_h;
+            tma_load_4d(sa, &tmA, &full_bar[stage], (kb - tap * p.conv.kb_per_tap) * BK,
+                        tw * CONV_BOX_W + p.conv.dw[tap], th * CONV_BOX_H + p.conv.dh[tap], tt + p.conv.dt[tap]);
           } else {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
           }
@@ -303,7 +327,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane);
+      if (p.conv.taps != 0) {
+        const int tw = tm % p.conv.tiles_w, rest = tm / p.conv.tiles_w;
+        const int th = rest % p.conv.tiles_h, tt = rest / p.conv.tiles_h;
+        epilogue_tile<OUT_F32>(tmC, p, sc, t_row, 0, n0, my_buf, buf, lane, tw * CONV_BOX_W,
+                               th * CONV_BOX_H + q * 2, tt);
+      } else {
+        epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane);
+      }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
     }
@@ -623,6 +654,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   }
   if (rc) return rc;
   GemmParams p;
+  memset(&p.conv, 0, sizeof(p.conv));
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = use_pair ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
@@ -692,6 +724,57 @@ extern "C" int solar_gemm_bf16_scatter(const void* A, const void* B, void* C, co
   sc.first_col = first_col;
   sc.col_base = col_base;
   return gemm_entry(A, B, C, bias, M, N, K, lda, ldb, ldc, layout, act, 0, 0, status, max_ctas, stream, sc);
+}
+
+// Stride-1 convolution over channels-last bf16 activations, "same" padding in H and W, causal in T:
+//   x [Tin, H, W, Cin]   w [Cout, taps * kb_per_tap * 64] (tap-major, each tap's Cin zero-padded to 64s)
+//   y [Tout, H, W, Cout] = conv(x) + bias;  output frame t reads input frames t + t_shift + (0 .. kt-1)
+// (t_shift = -(kt-1) with Tin == Tout: zero history; t_shift = 0 with Tin == Tout + kt - 1: the history frames
+// lead the input).  Cin and Cout must be multiples of 8.
+extern "C" int solar_conv3d_bf16(const void* x, const void* w, void* y, const void* bias, int Tin, int H, int W,
+                                 int Cin, int Tout, int Cout, int kt, int kh, int kw, int t_shift, int* status,
+                                 int max_ctas, void* stream) {
+  if (Tin <= 0 || Tout <= 0 || H <= 0 || W <= 0) return fail("conv3d: empty problem%s");
+  if (Cin % 8 != 0 || Cout % 8 != 0) return fail("conv3d: channel counts must be multiples of 8%s");
+  if (kt < 1 || kh < 1 || kw < 1 || kt * kh * kw > 27 || kh % 2 == 0 || kw % 2 == 0)
+    return fail("conv3d: kernel must be odd in H / W and have at most 27 taps%s");
+  const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  GemmParams p;
+  memset(&p.conv, 0, sizeof(p.conv));
+  p.conv.taps = kt * kh * kw;
+  p.conv.kb_per_tap = (Cin + BK - 1) / BK;
+  p.conv.tiles_w = (W + CONV_BOX_W - 1) / CONV_BOX_W;
+  p.conv.tiles_h = (H + CONV_BOX_H - 1) / CONV_BOX_H;
+  int tap = 0;
+  for (int a = 0; a < kt; ++a)
+    for (int b = 0; b < kh; ++b)
+      for (int c = 0; c < kw; ++c, ++tap) {
+        p.conv.dt[tap] = static_cast<signed char>(a + t_shift);
+        p.conv.dh[tap] = static_cast<signed char>(b - kh / 2);
+        p.conv.dw[tap] = static_cast<signed char>(c - kw / 2);
+      }
+  const int K = p.conv.taps * p.conv.kb_per_tap * BK;
+  CUtensorMap tA, tB, tC;
+  const uint64_t da[4] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, (uint64_t)Tin};
+  const uint64_t sa[3] = {(uint64_t)Cin * 2, (uint64_t)W * Cin * 2, (uint64_t)H * W * Cin * 2};
+  const uint32_t ba[4] = {BK, CONV_BOX_W, CONV_BOX_H, 1};
+  int rc = make_tmap_4d(&tA, x, bf, da, sa, ba);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tB, w, bf, 2, Cout, K, K, BN, BK);
+  if (rc) return rc;
+  const uint64_t dc[4] = {(uint64_t)Cout, (uint64_t)W, (uint64_t)H, (uint64_t)Tout};
+  const uint64_t sc4[3] = {(uint64_t)Cout * 2, (uint64_t)W * Cout * 2, (uint64_t)H * W * Cout * 2};
+  const uint32_t bc[4] = {64, CONV_BOX_W, 2, 1};
+  rc = make_tmap_4d(&tC, y, bf, dc, sc4, bc);
+  if (rc) return rc;
+  p.tiles_m = Tout * p.conv.tiles_h * p.conv.tiles_w;
+  p.tiles_n = (Cout + BN - 1) / BN;
+  p.M = p.tiles_m * BM; p.N = Cout; p.K = K;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.act = 0; p.accumulate = 0; p.status = status;
+  ColScatter none;
+  memset(&none, 0, sizeof(none));
+  return launch_gemm<0, 0, 0>(tA, tB, tC, p, max_ctas, reinterpret_cast<cudaStream_t>(stream), none);
 }
 
 extern "C" const char* solar_last_error() { return last_error_buf(); }

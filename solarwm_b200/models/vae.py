@@ -10,9 +10,11 @@ Building blocks (reference: solar/backends/wan22/runtime/modeling/vae.py:19-868)
     frames per input frame, the first latent frame excepted)
   * ``Decoder3d`` / ``Encoder3d`` and ``VideoVAE.encode / decode / cached_decode``
 
-The convolutions run on cuDNN through ``torch.nn.functional.conv3d`` (library kernels); the
-normalisation, activation and pixel conversion around them use this package's kernels where a
-fused one exists (``ops.rgb8``).  ``StreamingDecoder`` owns the per-layer caches and is what the
+On a B200 the stride-1 convolutions of inference (every convolution of the decoder) run on this package's
+implicit-GEMM kernel over channels-last activations (``ops.functional.conv3d_channels_last``: tcgen05 MMAs fed
+by 4-D TMA box loads whose out-of-range reads supply the spatial and the causal padding); training-time,
+strided (encoder down-sampling) and CPU convolutions go through ``torch.nn.functional.conv3d``.  Pixel
+conversion uses ``ops.rgb8``.  ``StreamingDecoder`` owns the per-layer caches and is what the
 realtime server calls once per generated chunk.
 """
 from __future__ import annotations
@@ -32,8 +34,40 @@ class CausalConv3d(nn.Conv3d):
         self.pad_t = k[0] - 1
         self.pad_hw = (k[2] // 2, k[2] // 2, k[1] // 2, k[1] // 2)
 
+    def _native_ok(self, x) -> bool:
+        # inference on a B200: bf16 activations, stride 1, channel count the TMA strides allow
+        return (x.is_cuda and x.dtype == torch.bfloat16 and tuple(self.stride) == (1, 1, 1) and x.shape[1] % 8 == 0
+                and not (torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad)))
+
+    def _forward_native(self, x, cache, key):
+        """Channels-last implicit-GEMM kernel: no padded copy, the border and the causal history are TMA fills.
+        The result is returned as an NCDHW view of channels-last memory, so a following convolution's layout
+        change is free."""
+        from ..ops import functional as F_
+
+        tag = (self.weight.data_ptr(), self.weight._version, str(x.device))
+        if getattr(self, "_packed_tag", None) != tag:
+            self._packed = F_.pack_conv_weight(self.weight, self.bias)
+            self._packed_tag = tag
+        w, b = self._packed
+        xc = x.permute(0, 2, 3, 4, 1).contiguous()                      # [B, T, H, W, C]
+        ck = None if key is None else key + "#cl"
+        outs = []
+        hist = cache.get(ck) if (cache is not None and self.pad_t) else None
+        for i in range(xc.shape[0]):
+            outs.append(F_.conv3d_channels_last(xc[i], w, b, self.kernel_size, history=None if hist is None else hist[i],
+                                                out_channels=self.out_channels))
+        if cache is not None and self.pad_t:
+            full = xc if hist is None else torch.cat([hist, xc], 1)
+            if full.shape[1] < self.pad_t:
+                full = torch.cat([full.new_zeros(full.shape[0], self.pad_t - full.shape[1], *full.shape[2:]), full], 1)
+            cache[ck] = full[:, -self.pad_t:].detach().contiguous()
+        return torch.stack(outs).permute(0, 4, 1, 2, 3)
+
     def forward(self, x, cache: Optional[dict] = None, key: Optional[str] = None):
         """x [B, C, T, H, W].  With a cache dict the temporal left context comes from the previous call."""
+        if self._native_ok(x):
+            return self._forward_native(x, cache, key)
         x = F.pad(x, self.pad_hw)
         if self.pad_t:
             if cache is not None and key in cache:
@@ -141,9 +175,28 @@ class Upsample(nn.Module):
                 y = y[:, :, 1:]             # the first latent frame maps to a single pixel-time step
             x = y
             T = x.shape[2]
+        if (x.is_cuda and x.dtype == torch.bfloat16 and C % 8 == 0
+                and not (torch.is_grad_enabled() and (x.requires_grad or self.conv.weight.requires_grad))):
+            return self._spatial_native(x)
         y = x.permute(0, 2, 1, 3, 4).reshape(B * T, C, H, W)
         y = self.conv(F.interpolate(y.float(), scale_factor=2.0, mode="nearest").to(x.dtype))
         return y.view(B, T, C // 2, 2 * H, 2 * W).permute(0, 2, 1, 3, 4)
+
+    def _spatial_native(self, x):
+        """Nearest 2x in channels-last memory, then the 3 x 3 convolution as a one-frame-deep implicit GEMM."""
+        from ..ops import functional as F_
+
+        B, C, T, H, W = x.shape
+        w = self.conv.weight
+        tag = (w.data_ptr(), w._version, str(x.device))
+        if getattr(self, "_packed_tag", None) != tag:
+            self._packed = F_.pack_conv_weight(w.unsqueeze(2), self.conv.bias)
+            self._packed_tag = tag
+        pw, pb = self._packed
+        xc = x.permute(0, 2, 3, 4, 1)                                    # [B, T, H, W, C] view
+        up = xc.reshape(B, T, H, 1, W, 1, C).expand(B, T, H, 2, W, 2, C).reshape(B, T, 2 * H, 2 * W, C)
+        outs = [F_.conv3d_channels_last(up[i], pw, pb, (1, 3, 3), out_channels=C // 2) for i in range(B)]
+        return torch.stack(outs).permute(0, 4, 1, 2, 3)
 
 
 @dataclass

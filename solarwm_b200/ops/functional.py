@@ -769,6 +769,46 @@ def tile_blend(tiles, offsets, H: int, W: int, overlap_px: int, coef=None):
 
 
 # --------------------------------------------------------------------------------------
+# implicit-GEMM convolution on channels-last activations (VAE)
+# --------------------------------------------------------------------------------------
+def pack_conv_weight(weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """``[Cout, Cin, kt, kh, kw]`` -> bf16 ``[Cout8, taps * ceil(Cin/64) * 64]`` (tap-major, each tap's input
+    channels zero-padded to a multiple of 64; Cout rounded up to a multiple of 8) and the matching bf16 bias."""
+    cout, cin, kt, kh, kw = weight.shape
+    kpt = (cin + 63) // 64
+    c8 = (cout + 7) // 8 * 8
+    packed = torch.zeros(c8, kt * kh * kw, kpt * 64, dtype=torch.bfloat16, device=weight.device)
+    packed[:cout, :, :cin] = weight.detach().permute(0, 2, 3, 4, 1).reshape(cout, kt * kh * kw, cin).to(torch.bfloat16)
+    b = torch.zeros(c8, dtype=torch.bfloat16, device=weight.device)
+    if bias is not None:
+        b[:cout] = bias.detach().to(torch.bfloat16)
+    return packed.view(c8, -1), b
+
+
+def conv3d_channels_last(x, packed_w, packed_b, kernel, *, history=None, out_channels: Optional[int] = None):
+    """Stride-1 convolution of bf16 ``x [T, H, W, Cin]`` ("same" padding in H / W, causal in T) with weights from
+    ``pack_conv_weight``.  ``history`` ``[kt-1, H, W, Cin]`` supplies the frames before ``x`` (zeros if None).
+    Returns ``[T, H, W, Cout8]`` (slice with ``out_channels`` to drop the channel padding).  CUDA only."""
+    kt, kh, kw = kernel
+    T, H, W, cin = x.shape
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and cin % 8 == 0
+    if history is not None and kt > 1:
+        xin = torch.cat([history, x], 0)
+        shift = 0
+    else:
+        xin, shift = x, -(kt - 1)
+    c8 = packed_w.shape[0]
+    assert packed_w.shape[1] == kt * kh * kw * ((cin + 63) // 64) * 64
+    y = torch.empty((T, H, W, c8), dtype=torch.bfloat16, device=x.device)
+    rc = _lib.load().solar_conv3d_bf16(ptr(xin), ptr(packed_w), ptr(y), ptr(packed_b), c_int(xin.shape[0]), c_int(H),
+                                       c_int(W), c_int(cin), c_int(T), c_int(c8), c_int(kt), c_int(kh), c_int(kw),
+                                       c_int(shift), ptr(status_word(x.device)), c_int(0), stream_handle())
+    check(rc, "solar_conv3d_bf16")
+    count("conv3d")
+    return y if out_channels is None or out_channels == c8 else y[..., :out_channels]
+
+
+# --------------------------------------------------------------------------------------
 # per-head RMSNorm + MM-RoPE + PRoPE (H3 attention path)
 # --------------------------------------------------------------------------------------
 class _HeadOpFn(torch.autograd.Function):

@@ -148,6 +148,32 @@ def bench_rowops(R, D, iters=10):
     return out
 
 
+def bench_conv(T, H, W, cin, cout, kernel=(3, 3, 3), iters=5):
+    """Implicit-GEMM causal convolution on channels-last bf16 against torch's convolution (cuDNN) on the same
+    problem in its channels_last_3d layout."""
+    import torch.nn.functional as F
+
+    from ..ops import functional as F_
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(T, H, W, cin, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(cout, cin, *kernel, device="cuda", generator=g) / (cin * 27) ** 0.5).bfloat16()
+    b = torch.zeros(cout, device="cuda").bfloat16()
+    pw, pb = F_.pack_conv_weight(w, b)
+    ms = time_fn(lambda: F_.conv3d_channels_last(x, pw, pb, kernel), iters)
+    kt, kh, kw = kernel
+    xl = F.pad(x.permute(3, 0, 1, 2).unsqueeze(0), (kw // 2, kw // 2, kh // 2, kh // 2, kt - 1, 0))
+    xl = xl.contiguous(memory_format=torch.channels_last_3d)
+    wl = w.contiguous(memory_format=torch.channels_last_3d)
+    ms_lib = time_fn(lambda: F.conv3d(xl, wl, b), iters)
+    fl = 2.0 * T * H * W * cin * cout * kt * kh * kw
+    pk = peaks()
+    return {"op": "conv3d", "T": T, "H": H, "W": W, "cin": cin, "cout": cout, "kernel": list(kernel),
+            "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+            "frac_of_peak": round(fl / ms / 1e9 / pk["bf16_tflops"], 3), "peak_src": pk["src"],
+            "cudnn_ms": round(ms_lib, 4), "speedup_vs_cudnn": round(ms_lib / ms, 3)}
+
+
 def wan5b_suite(seq=27280):
     d, f = 3072, 14336
     rows = []
@@ -178,6 +204,13 @@ def main():
     r = sub.add_parser("rowops")
     r.add_argument("--rows", type=int, default=27280)
     r.add_argument("--dim", type=int, default=3072)
+    c = sub.add_parser("conv")
+    c.add_argument("--frames", type=int, default=4)
+    c.add_argument("--height", type=int, default=176)
+    c.add_argument("--width", type=int, default=320)
+    c.add_argument("--cin", type=int, default=256)
+    c.add_argument("--cout", type=int, default=256)
+    c.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("suite")
     s.add_argument("--seq", type=int, default=27280)
     args = ap.parse_args()
@@ -185,6 +218,8 @@ def main():
         print(json.dumps(bench_gemm(args.m, args.n, args.k, args.layout, args.f32, args.iters)))
     elif args.cmd == "attention":
         print(json.dumps(bench_attention(args.seq, args.heads, args.head_dim, args.kv, args.backward, args.iters)))
+    elif args.cmd == "conv":
+        print(json.dumps(bench_conv(args.frames, args.height, args.width, args.cin, args.cout, iters=args.iters)))
     elif args.cmd == "rowops":
         for row in bench_rowops(args.rows, args.dim):
             print(json.dumps(row))
