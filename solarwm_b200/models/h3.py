@@ -218,6 +218,9 @@ class H3DiT(nn.Module):
         self.norm_out = nn.Parameter(torch.ones(h, device=device), requires_grad=False)
         self.proj_out, self.audio_proj_out = lin(h, cfg.latent_row_dim, 0.02), lin(h, cfg.audio_row_dim, 0.02)
         self.sp = None
+        # inference-only caches installed by renderer.service (None = off)
+        self.fixed_tables = None        # {tuple of unique timesteps: [per-block adaLN tables]}
+        self.text_cache = None          # {"input": rows, "output": refined rows, "hits": n}
 
     def trainable_parameters(self):
         return [p for p in self.parameters() if p.requires_grad]
@@ -238,10 +241,18 @@ class H3DiT(nn.Module):
         cfg = self.cfg
         dt = self.dtype
         parts, n_text = [], text_rows.shape[0]
-        txt = F_.linear(text_rows.to(dt), self.context_embedder)
-        cos, sin = mm_rope_tables(position_ids.to(txt.device), cfg.rot_dims, cfg.rope_sections)
-        for blk in self.refiner:       # text-only refiner blocks (no modulation, no camera)
-            txt = blk(txt, None, None, cos[:n_text].contiguous(), sin[:n_text].contiguous(), None, None, None)
+        cos, sin = mm_rope_tables(position_ids.to(self.proj_in.device), cfg.rot_dims, cfg.rope_sections)
+        tc = self.text_cache if not torch.is_grad_enabled() else None
+        if tc is not None and tc.get("input") is not None and tc["input"].shape == text_rows.shape \
+                and torch.equal(tc["input"], text_rows):
+            txt = tc["output"]
+            tc["hits"] = tc.get("hits", 0) + 1
+        else:
+            txt = F_.linear(text_rows.to(dt), self.context_embedder)
+            for blk in self.refiner:       # text-only refiner blocks (no modulation, no camera)
+                txt = blk(txt, None, None, cos[:n_text].contiguous(), sin[:n_text].contiguous(), None, None, None)
+            if tc is not None:
+                tc["input"], tc["output"] = text_rows.detach().clone(), txt
         parts.append(txt)
         if anchor_rows is not None:
             parts.append(F_.linear(anchor_rows.to(dt), self.proj_in))
@@ -255,12 +266,20 @@ class H3DiT(nn.Module):
         S = x.shape[0]
         assert t_index.shape[0] == S and tags.shape[0] == S and position_ids.shape[0] == S
         idx = (t_index.to(torch.int32) * 3 + tags.to(torch.int32)).contiguous()
-        temb = self.time_embed(timesteps.to(x.device).float())
+        tables = None
+        if self.fixed_tables is not None and not torch.is_grad_enabled():
+            key = tuple(round(float(t), 6) for t in timesteps.float().cpu().tolist())
+            if key not in self.fixed_tables:
+                raise ValueError(f"timestep set {key} was not prepared; refusing to use stale modulation tables")
+            tables = self.fixed_tables[key]
+        else:
+            temb = self.time_embed(timesteps.to(x.device).float())
         cam_q = cam_kv = cam_o = None
         if viewmats is not None:
             cam_q, cam_kv, cam_o = prope_row_matrices(viewmats.to(x.device), fx, fy)
-        for blk in self.blocks:
-            x = blk(x, blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o, sp=self.sp, attn_fn=attn_fn)
+        for bi, blk in enumerate(self.blocks):
+            x = blk(x, tables[bi] if tables is not None else blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o,
+                    sp=self.sp, attn_fn=attn_fn)
         xn = F_.norm_modulate(x, mode=1, w=self.norm_out, eps=cfg.eps)
         vid = F_.linear(xn[S - n_video:], self.proj_out)
         aud = None

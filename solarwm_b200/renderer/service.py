@@ -1,0 +1,79 @@
+"""Inference host of the renderer: the caches that make the fixed few-step schedule cheap.
+
+* **Precomputed modulation**: a distilled renderer only ever sees a handful of timestep sets (one per denoise
+  step: ``{text, anchor, t_k}``), so the time MLP and every block's adaLN projection are evaluated once per set
+  and the per-block tables kept; the projection weights (``18 * hidden * time_embed_dim`` per block) can then be
+  dropped.  An unprepared set is refused rather than served from a stale table.
+* **Text cache**: the embedded + refined prompt rows are kept while the prompt tensor stays bit-identical.
+* **Tile-parallel decode**: frames leave through ``models.vit_decoder.StreamingViTDecoder(distributed=True)``.
+
+Reference behaviour: deploy/solar_renderer/reactor/solarrenderer_optimizations.py:18-110 (one-entry exact-input
+cache, modulation tables, refusal of unprepared timestep sets), solarrenderer_distributed.py:10-108.
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from ..backends.minimax_h3 import flow
+from ..models.h3 import H3DiT
+from . import core
+
+TEXT_TIME, ANCHOR_TIME = 1.0, 0.999
+
+
+def time_key(values: Iterable[float]) -> Tuple[float, ...]:
+    """Sorted unique timesteps, rounded the way ``H3DiT.forward`` looks them up."""
+    t = torch.unique(torch.tensor(list(values), dtype=torch.float32))
+    return tuple(round(float(v), 6) for v in t.tolist())
+
+
+def schedule_time_sets(steps: int, shift: float = flow.VIDEO_SHIFT) -> List[List[float]]:
+    """The timestep sets ``core.render`` produces without pinned rows: text, anchor and the step's own time."""
+    return [[TEXT_TIME, ANCHOR_TIME, float(t)] for t in flow.rollout_times(steps, shift)[:steps]]
+
+
+@torch.no_grad()
+def precompute_modulation(model: H3DiT, time_sets: Sequence[Sequence[float]], *, free_projection: bool = False) -> Dict:
+    """Evaluate the adaLN tables of every block for each timestep set and install them on ``model``."""
+    dev = model.proj_in.device
+    tables = {}
+    for ts in time_sets:
+        key = time_key(ts)
+        exact = torch.unique(torch.tensor(list(ts), dtype=torch.float32))      # the lookup key is rounded, the values are not
+        temb = model.time_embed(exact.to(dev))
+        tables[key] = [blk.tables(temb) for blk in model.blocks]
+    model.fixed_tables = tables
+    freed = 0
+    if free_projection:
+        for blk in model.blocks:
+            freed += blk.adaln_proj.numel() * blk.adaln_proj.element_size()
+            blk.adaln_proj.data = blk.adaln_proj.data.new_empty(0)
+    return {"time_sets": list(tables), "adaln_weight_bytes_removed": freed,
+            "table_bytes": sum(t.numel() * t.element_size() for ts in tables.values() for t in ts)}
+
+
+def enable_text_cache(model: H3DiT) -> None:
+    model.text_cache = {"input": None, "output": None, "hits": 0}
+
+
+class RenderService:
+    """``prepare`` once, then ``render`` per request on the prepared schedule."""
+
+    def __init__(self, model: H3DiT, *, steps: int = 4, shift: float = flow.VIDEO_SHIFT, free_projection: bool = False):
+        self.model, self.steps, self.shift = model, steps, shift
+        self.free_projection = free_projection
+        self.report: Optional[Mapping] = None
+
+    def prepare(self) -> Mapping:
+        self.report = precompute_modulation(self.model, schedule_time_sets(self.steps, self.shift),
+                                            free_projection=self.free_projection)
+        enable_text_cache(self.model)
+        return self.report
+
+    @torch.no_grad()
+    def render(self, sample: Mapping[str, torch.Tensor], *, seed: int = 0) -> torch.Tensor:
+        if self.report is None:
+            raise RuntimeError("RenderService.prepare() must run before render()")
+        return core.render(self.model, sample, steps=self.steps, seed=seed, shift=self.shift)

@@ -60,3 +60,29 @@ def test_trainer_render_and_distillation():
     r2 = d.train_outer_step(s)
     assert "student" not in r0 and "student" in r2 and r2["critic"] == r2["critic"]
     assert main(["train", "--steps", "1", "--device", "cpu"]) == 0
+
+
+def test_render_service_caches_reproduce_the_plain_renderer_and_refuse_unprepared_times():
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.renderer.cli import _sample
+    from solarwm_b200.renderer.core import render
+    from solarwm_b200.renderer.service import RenderService, schedule_time_sets
+
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    s = _sample(cfg, 3)
+    with torch.no_grad():
+        want = render(model, s, steps=3, seed=5)
+    svc = RenderService(model, steps=3, free_projection=True)
+    with pytest.raises(RuntimeError):
+        svc.render(s)
+    report = svc.prepare()
+    assert len(report["time_sets"]) == 3 == len(schedule_time_sets(3)) and report["adaln_weight_bytes_removed"] > 0
+    assert all(blk.adaln_proj.numel() == 0 for blk in model.blocks)       # projection weights are gone
+    got = svc.render(s, seed=5)
+    assert torch.equal(got, want)
+    assert model.text_cache["hits"] == 2                                     # steps 2 and 3 reuse the refined prompt
+    svc.render(_sample(cfg, 4), seed=5)                                      # another prompt: cache refills, no stale hit
+    assert model.text_cache["hits"] == 4
+    with torch.no_grad(), pytest.raises(ValueError, match="not prepared"):
+        render(model, s, steps=2, seed=5)                                    # a different grid of times
