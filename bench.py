@@ -44,6 +44,9 @@ def parse_args():
                     help="train: the headline training step; realtime: H3-shaped block-causal streaming (FPS)")
     ap.add_argument("--h3", default="h3_33b", choices=["h3_33b", "tiny"], help="realtime mode: model preset")
     ap.add_argument("--prompt-tokens", type=int, default=512)
+    ap.add_argument("--decode", default="vit", choices=["vit", "none"],
+                    help="realtime mode: decode every generated latent to RGB8 frames with the streaming ViT decoder "
+                         "(tiles dealt to the ranks) inside the timed region")
     ap.add_argument("--frames", type=int, default=31)
     ap.add_argument("--height", type=int, default=44)
     ap.add_argument("--width", type=int, default=80)
@@ -325,30 +328,80 @@ def run_realtime(args):
     ops.reset_counters()
     host = torch.empty(scfg.latent_channels, scfg.chunk_latents, 2 * scfg.grid_hw[0], 2 * scfg.grid_hw[1],
                        dtype=torch.bfloat16).pin_memory()
+    dec = frames_host = None
+    lh, lw = 2 * scfg.grid_hw[0], 2 * scfg.grid_hw[1]
+    if args.decode == "vit":
+        from solarwm_b200.models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+        from solarwm_b200.ops import functional as F_
+
+        vcfg = ViTDecoderConfig(latent_channels=scfg.latent_channels) if args.h3 == "h3_33b" else \
+            ViTDecoderConfig(latent_channels=scfg.latent_channels, dim=128, depth=2, heads=2, dim_head=64, ffn_dim=256)
+        vit = ViTVideoDecoder(vcfg, device=f"cuda:{local}", dtype=torch.bfloat16, seed=1)
+        tiled = lh > 16 and lw > 16
+        dec = StreamingViTDecoder(vit, (lh, lw), tile=16 if tiled else None, overlap=4 if tiled else 0,
+                                  distributed=world > 1)
+        if rank == 0:
+            frames_host = torch.empty(scfg.chunk_latents * vcfg.frames_per_latent, lh * vcfg.patch, lw * vcfg.patch, 3,
+                                      dtype=torch.uint8).pin_memory()
+    dit_ev, dec_ev, emitted = [], [], []
+
+    def decode(latents):
+        """latents [C, n, H, W] -> RGB8 frames in pinned host memory on rank 0."""
+        n_out = 0
+        for j in range(latents.shape[1]):
+            fr = dec.push(latents[:, j])
+            if fr is None:
+                continue
+            fr = fr.to(torch.bfloat16)
+            for f in range(fr.shape[1]):
+                rgb, _ = F_.rgb8(fr[:, f], mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5))
+                frames_host[n_out].copy_(rgb, non_blocking=True)
+                n_out += 1
+        return n_out
+
+    if dec is not None:                                          # the decoder's first window, outside the timed region
+        decode(torch.zeros(scfg.latent_channels, 7, lh, lw, device=f"cuda:{local}", dtype=torch.bfloat16))
+        torch.cuda.synchronize()
 
     def chunk():
         cams[:, 0, 3] += 0.01                                   # a moving camera, copied from pinned memory
-        host.copy_(gen.next_chunk(cams))                        # the generated latent chunk is read back
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        lat = gen.next_chunk(cams)
+        host.copy_(lat)                                         # the generated latent chunk is read back
+        e[1].record()
+        if dec is not None:
+            emitted.append(decode(lat))
+        e[2].record()
+        dit_ev.append((e[0], e[1]))
+        dec_ev.append((e[1], e[2]))
 
     ms = timed_region(args.steps, chunk, dist, torch)
+    dit_ms = sum(a.elapsed_time(b) for a, b in dit_ev[-args.steps:]) / args.steps
+    dec_ms = sum(a.elapsed_time(b) for a, b in dec_ev[-args.steps:]) / args.steps
     launches = ops.total_launches()
     clocks = sampler.stop()
     ops.check_status(f"cuda:{local}")
     if rank == 0:
-        frames = 4 * scfg.chunk_latents
+        # with the decoder on, count the frames it actually emitted (a latent that opens a group yields one)
+        frames = emitted[-1] if emitted else 4 * scfg.chunk_latents
         fps = frames * args.steps / (ms / 1e3)
         print(json.dumps({
-            "metric": "realtime generation FPS (H3-shaped block-causal streaming, DiT only)", "value": fps,
+            "metric": "realtime generation FPS (H3-shaped block-causal streaming"
+                      + (", DiT + streaming ViT decode to RGB8)" if dec is not None else ", DiT only)"), "value": fps,
             "unit": "frames/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic prompt/anchor/cameras, random-init weights", "impl": "ours",
             "config": {"model": args.h3, "chunk_latents": scfg.chunk_latents, "window_chunks": scfg.window_chunks,
                        "denoise_steps": scfg.denoise_steps, "rows_per_latent": gen.rows_per_latent,
+                       "frames_per_chunk": frames,
                        "prompt_tokens": args.prompt_tokens, "parallelism": f"sp{world}",
-                       "cuda_graph": bool(gen.timings[-1].graph), "vae_decode": "not included"},
-            "clocks": clocks, "chunk_latency_ms": ms / args.steps,
+                       "cuda_graph": bool(gen.timings[-1].graph),
+                       "decode": "streaming ViT decoder, 16 x 16 latent tiles dealt to the ranks, RGB8 frames to "
+                                 "pinned host memory" if dec is not None else "not included"},
+            "clocks": clocks, "chunk_latency_ms": {"total": ms / args.steps, "dit": dit_ms, "decode": dec_ms},
             "e2e": {"value": fps, "unit": "frames/s", "h2d_bytes_per_step": int(cams.numel() * 4),
-                    "d2h_bytes_per_step": int(host.numel() * 2)},
+                    "d2h_bytes_per_step": int(host.numel() * 2 + (frames_host.numel() if frames_host is not None else 0))},
             "gpu_launches": launches}))
     if dist is not None:
         dist.destroy_process_group()

@@ -349,6 +349,62 @@ __global__ void tile_blend_kernel(TileBlendParams p) {
   }
 }
 
+// Channel RMS norm (+ SiLU) of channels-last activations: y = x / max(||x||_2, 1e-12) * sqrt(C) * gamma, then
+// optionally y * sigmoid(y).  One warp per pixel row; a lane keeps its 8-channel vectors in registers between
+// the sum of squares and the write (C <= 1024).  The normalised value is rounded to bf16 before the gain and
+// before the activation, as the unfused composition of the VAE blocks does.
+__global__ void __launch_bounds__(256) rms_silu_cl_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          __nv_bfloat16* __restrict__ y,
+                                                          const float* __restrict__ gamma, long long rows, int C,
+                                                          int silu) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int nvec = C >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(x + row * C);
+  uint4 v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = lane + 32 * k;
+    if (i < nvec) {
+      v[k] = src[i];
+      const float2 a = unpack_bf16x2(v[k].x), b = unpack_bf16x2(v[k].y), c = unpack_bf16x2(v[k].z),
+                   d = unpack_bf16x2(v[k].w);
+      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+  const float root_c = sqrtf(static_cast<float>(C));
+  uint4* dst = reinterpret_cast<uint4*>(y + row * C);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = lane + 32 * k;
+    if (i < nvec) {
+      const uint32_t in[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+      uint32_t out[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(in[e]);
+        const int ch = i * 8 + e * 2;
+        float r[2] = {f.x * inv, f.y * inv};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          float t = __bfloat162float(__float2bfloat16(r[u]));                              // normalize -> bf16
+          t = __bfloat162float(__float2bfloat16(t * root_c));                               // * sqrt(C)
+          t = __bfloat162float(__float2bfloat16(t * __bfloat162float(__float2bfloat16(gamma[ch + u]))));
+          if (silu) t = t / (1.f + __expf(-t));
+          r[u] = t;
+        }
+        out[e] = pack_bf16x2(r[0], r[1]);
+      }
+      dst[i] = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+  }
+}
+
 static inline int grid_for(long long work, int block) {
   long long g = (work + block - 1) / block;
   const long long cap = static_cast<long long>(sm_count()) * 16;
@@ -463,6 +519,17 @@ extern "C" int solar_tile_blend(const void* tiles, long long st, long long sc, l
       p.c[c][f] = on ? coef[(2 * 3 + c) * F + f] : 0.f;
     }
   tile_blend_kernel<<<grid_for((long long)H * W, 256), 256, 0, (cudaStream_t)stream>>>(p);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int solar_rms_silu_cl(const void* x, void* y, const float* gamma, long long rows, int C, int silu,
+                                 void* stream) {
+  if (C % 8 != 0 || C > 1024 || C < 8) return fail("rms_silu_cl: C must be a multiple of 8 in [8, 1024]%s");
+  if (rows <= 0) return 0;
+  const long long blocks = (rows * 32 + 255) / 256;
+  rms_silu_cl_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, gamma, rows, C, silu);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -88,8 +88,18 @@ class RMSNormC(nn.Module):
         self.gamma = nn.Parameter(torch.ones(dim))
         self.scale = dim ** 0.5
 
-    def forward(self, x):
-        return F.normalize(x.float(), dim=1).to(x.dtype) * self.scale * self.gamma.view(1, -1, 1, 1, 1).to(x.dtype)
+    def forward(self, x, silu: bool = False):
+        """Channel RMS norm of ``x [B, C, T, H, W]``; ``silu=True`` also applies the activation that follows it in
+        every block (one kernel on channels-last bf16 CUDA activations at inference)."""
+        C = x.shape[1]
+        if (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 5 and C % 8 == 0 and C <= 1024
+                and not (torch.is_grad_enabled() and (x.requires_grad or self.gamma.requires_grad))):
+            from ..ops import functional as F_
+
+            xc = x.permute(0, 2, 3, 4, 1).contiguous()                  # free when x already is channels-last memory
+            return F_.rms_silu_channels_last(xc, self.gamma, silu).permute(0, 4, 1, 2, 3)
+        y = F.normalize(x.float(), dim=1).to(x.dtype) * self.scale * self.gamma.view(1, -1, 1, 1, 1).to(x.dtype)
+        return F.silu(y) if silu else y
 
 
 class ResBlock(nn.Module):
@@ -100,8 +110,8 @@ class ResBlock(nn.Module):
         self.skip = CausalConv3d(cin, cout, 1) if cin != cout else None
 
     def forward(self, x, cache=None, key=""):
-        h = self.c1(F.silu(self.n1(x)), cache, key + ".c1")
-        h = self.c2(F.silu(self.n2(h)), cache, key + ".c2")
+        h = self.c1(self.n1(x, silu=True), cache, key + ".c1")
+        h = self.c2(self.n2(h, silu=True), cache, key + ".c2")
         return h + (x if self.skip is None else self.skip(x))
 
 
@@ -226,7 +236,7 @@ class Decoder3d(nn.Module):
         x = self.mid2(self.mid_attn(self.mid1(x, cache, "m1")), cache, "m2")
         for i, (r1, r2, up) in enumerate(self.stages):
             x = up(r2(r1(x, cache, f"s{i}.r1"), cache, f"s{i}.r2"), cache, f"s{i}.up", first_chunk)
-        return self.conv_out(F.silu(self.norm_out(x)), cache, "out")
+        return self.conv_out(self.norm_out(x, silu=True), cache, "out")
 
 
 class Encoder3d(nn.Module):

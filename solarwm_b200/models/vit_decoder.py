@@ -345,7 +345,13 @@ class StreamingViTDecoder:
         (F = 1 for a latent that opens a group of ``stride``, else ``frames_per_latent``); other ranks get None."""
         c = self.cfg
         if not self.my_tiles:
+            i = self.count
             self.count += 1
+            if self.m.embed.is_cuda and self.m.dtype == torch.bfloat16 and len(self.plan) <= 32:
+                n_f = 1 if i % c.stride == 0 else c.frames_per_latent      # join the device gather with no tiles
+                self._gather_device(torch.zeros(0, 3, n_f, self.th * c.patch, self.tw * c.patch, dtype=self.m.dtype,
+                                                device=self.m.embed.device))
+                return None
             return self._gather(None)
         if not self._registers_ready:
             self._fill_registers()
@@ -366,17 +372,38 @@ class StreamingViTDecoder:
         if first_of_group:
             frames = frames[:, :, -1:]
         self.count += 1
-        if self.world == 1 and frames.is_cuda and frames.dtype == torch.bfloat16 and len(self.plan) <= 32:
+        if frames is not None and frames.is_cuda and frames.dtype == torch.bfloat16 and len(self.plan) <= 32:
             # one pass over the pixels: ramp-weighted tile mean and the compensation polynomial together
+            tiles = frames if self.world == 1 else self._gather_device(frames)
+            if tiles is None:
+                return None
             coef = None if self.table is None else self.table.coefficients(slot, frames.shape[2], first_of_stream=(i == 0))
-            offs = [(y * c.patch, x * c.patch) for (y, x) in self.plan]
-            return F_.tile_blend(frames, offs, self.h * c.patch, self.w * c.patch, self.overlap * c.patch, coef)
+            order = [t for r in range(self.world) for t in range(len(self.plan)) if t % self.world == r]
+            offs = [(self.plan[t][0] * c.patch, self.plan[t][1] * c.patch) for t in order]
+            return F_.tile_blend(tiles, offs, self.h * c.patch, self.w * c.patch, self.overlap * c.patch, coef)
         out = self._gather(frames)
         if out is None:
             return None
         if self.table is not None:
             out = self.table.apply(out, slot, first_of_stream=(i == 0))
         return out
+
+    def _gather_device(self, frames: torch.Tensor) -> Optional[torch.Tensor]:
+        """Tiles of every rank -> rank 0, on the device (one gather collective): [all tiles in rank-major order,
+        3, F, th*p, tw*p] on rank 0, None elsewhere.  Ranks own ceil or floor of tiles / world; all send the
+        padded count."""
+        import torch.distributed as dist
+
+        per = -(-len(self.plan) // self.world)
+        send = frames.contiguous()
+        if send.shape[0] < per:
+            send = torch.cat([send, send.new_zeros(per - send.shape[0], *send.shape[1:])])
+        bufs = [torch.empty_like(send) for _ in range(self.world)] if self.rank == 0 else None
+        dist.gather(send, bufs, dst=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
+        if self.rank != 0:
+            return None
+        counts = [len([t for t in range(len(self.plan)) if t % self.world == r]) for r in range(self.world)]
+        return torch.cat([b[:n] for b, n in zip(bufs, counts)])
 
     def _gather(self, frames: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         c = self.cfg

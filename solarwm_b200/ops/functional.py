@@ -808,6 +808,19 @@ def conv3d_channels_last(x, packed_w, packed_b, kernel, *, history=None, out_cha
     return y if out_channels is None or out_channels == c8 else y[..., :out_channels]
 
 
+def rms_silu_channels_last(x, gamma, silu: bool = True):
+    """bf16 ``x [..., C]`` (contiguous, channels last) -> ``x / max(||x||, 1e-12) * sqrt(C) * gamma`` (then SiLU), one pass."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+    C = x.shape[-1]
+    g = gamma.detach().float().contiguous()
+    y = torch.empty_like(x)
+    rc = _lib.load().solar_rms_silu_cl(ptr(x), ptr(y), ptr(g), c_ll(x.numel() // C), c_int(C), c_int(1 if silu else 0),
+                                       stream_handle())
+    check(rc, "solar_rms_silu_cl")
+    count("rms_silu_cl")
+    return y
+
+
 # --------------------------------------------------------------------------------------
 # per-head RMSNorm + MM-RoPE + PRoPE (H3 attention path)
 # --------------------------------------------------------------------------------------

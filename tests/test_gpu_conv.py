@@ -69,3 +69,20 @@ def test_vae_decoder_on_native_convolutions_matches_library_path_and_streams():
     streamed = torch.cat(parts, 2).float()
     assert (streamed - native).abs().max() / native.abs().max() < 2e-2
     assert isinstance(vae.decoder.conv_in, CausalConv3d)
+
+
+@pytest.mark.parametrize("C", [16, 64, 160, 1024])
+def test_rms_silu_channels_last_matches_unfused_composition(C):
+    from solarwm_b200.models.vae import RMSNormC
+    from solarwm_b200.ops import functional as F_
+
+    g = torch.Generator().manual_seed(C)
+    x = (torch.randn(2, 3, 5, 7, C, generator=g) * 3).cuda().bfloat16()
+    norm = RMSNormC(C).cuda()
+    norm.gamma.data = (torch.rand(C, generator=g) + 0.5).cuda()
+    for silu in (False, True):
+        got = F_.rms_silu_channels_last(x, norm.gamma, silu)
+        xf = x.float()
+        want = xf / xf.norm(dim=-1, keepdim=True).clamp_min(1e-12) * C ** 0.5 * norm.gamma.float()
+        want = F.silu(want) if silu else want
+        assert (got.float() - want).abs().max() < 4e-2 * want.abs().max()

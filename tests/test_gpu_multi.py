@@ -140,6 +140,20 @@ def _worker(rank, world, port, out_path):
     gathered = [torch.empty_like(u_f.flat) for _ in range(world)]
     dist.all_gather(gathered, u_f.flat)
     result["zero_ranks_agree"] = bool(all(torch.equal(gathered[0], t) for t in gathered))
+    # ---- tile-parallel streaming decode: tiles dealt to the ranks, gathered on the device, blended on rank 0
+    from solarwm_b200.models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+
+    vcfg = ViTDecoderConfig(latent_channels=8, dim=128, depth=2, heads=2, dim_head=64, ffn_dim=256, registers=8, patch=2)
+    vit = ViTVideoDecoder(vcfg, device="cuda", dtype=torch.bfloat16, seed=0)
+    lat = torch.randn(3, 8, 8, 16, generator=torch.Generator().manual_seed(1)).cuda()
+    par = StreamingViTDecoder(vit, (8, 16), tile=8, overlap=4, distributed=True)       # three tiles over two ranks
+    outs = [par.push(lat[i]) for i in range(3)]
+    if rank == 0:
+        one = StreamingViTDecoder(vit, (8, 16), tile=8, overlap=4)
+        want = [one.push(lat[i]) for i in range(3)]
+        result["tile_parallel_diff"] = max(float((a - b).abs().max()) for a, b in zip(outs, want))
+    else:
+        result["tile_parallel_diff"] = 0.0 if all(o is None for o in outs) else 1e9
     torch.save(result, f"{out_path}.{rank}")
     zheap.close()
     fused.close()
@@ -160,4 +174,5 @@ def test_fused_ulysses_matches_collective_on_two_gpus(tmp_path):
         assert r["infer_rel"] < 2e-2 and r["worst_grad_rel"] < 6e-2, r
         assert r["fused_kernels_none"] == (2, 2) and r["fused_kernels_selective"] == (4, 2), r
         assert r["zero_ranks_agree"] and r["zero_param_diff"] < 1e-2 and r["zero_vec_diff"] < 1e-5, r
+        assert r["tile_parallel_diff"] < 1e-5, r
         assert r["zero_ema_diff"] < 1e-5 and all(abs(a - b) < 1e-3 * max(a, 1.0) for a, b in r["zero_norms"]), r
