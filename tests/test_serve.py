@@ -105,3 +105,39 @@ def test_memory_retrieval_prefers_overlapping_views_outside_recent_window():
         bank.commit(torch.full((1, 2, 5, 2, 2), float(i)), i)
     got = bank.gather([1, 7, 14], torch.zeros(1, 2, 5, 2, 2))
     assert got.shape == (1, 2, 3, 2, 2) and got[0, 0, :, 0, 0].tolist() == [0.0, 1.0, 2.0]
+
+
+def test_decode_backends_switch_orders_chunks_and_refuses_nonfinite_pixels():
+    import pytest
+    import torch
+
+    from solarwm_b200.models.vae import StreamingDecoder, VAEConfig, VideoVAE
+    from solarwm_b200.models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+    from solarwm_b200.serve.decode_backends import DecodeBackends, finite_host
+
+    torch.manual_seed(0)
+    vcfg = ViTDecoderConfig.tiny()
+    vit = ViTVideoDecoder(vcfg, device="cpu", dtype=torch.float32, seed=0)
+    vae = VideoVAE(VAEConfig(z_dim=4, base=8, temporal_ups=(True, False), out_channels=3)).eval()
+    backends = DecodeBackends({"vit": lambda: StreamingViTDecoder(vit, (4, 6)), "conv": lambda: StreamingDecoder(vae)}, pin=False)
+    with pytest.raises(ValueError):
+        DecodeBackends({"nope": lambda: None})
+    pieces = []
+    with pytest.raises(RuntimeError, match="reordered"):
+        backends.push(0, torch.zeros(4, 5, 4, 6), lambda *a: pieces.append(a))     # not started
+    for kind, first, rest in (("vit", 1, vcfg.frames_per_latent), ("conv", 1, 2)):
+        pieces.clear()
+        backends.start(kind)
+        ms = backends.push(0, torch.randn(4, 5, 4, 6), lambda *a: pieces.append(a))
+        assert ms > 0 and [p[1] for p in pieces] == [0, 1, 2, 3, 4] and all(p[0] == 0 for p in pieces)
+        assert pieces[0][2].shape[1] == first and pieces[1][2].shape[1] == rest
+        assert pieces[1][3] >= pieces[0][3]
+        with pytest.raises(RuntimeError, match="reordered"):
+            backends.push(5, torch.randn(4, 5, 4, 6), lambda *a: None)
+        backends.push(1, torch.randn(4, 5, 4, 6), lambda *a: pieces.append(a))
+        assert len(pieces) == 10
+        with pytest.raises(FloatingPointError):
+            backends.push(2, torch.full((4, 5, 4, 6), float("nan")), lambda *a: None)
+        backends.finish()
+    assert finite_host(torch.ones(3, dtype=torch.bfloat16)) and not finite_host(torch.tensor([float("inf")], dtype=torch.bfloat16))
+    backends.close()
