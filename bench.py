@@ -56,6 +56,9 @@ def parse_args():
                          "fused = NVLink peer reduce + AdamW + parameter push kernels")
     ap.add_argument("--keep-blocks", type=int, default=-1,
                     help="blocks exempt from recompute under checkpointing (-1: sized from free HBM)")
+    ap.add_argument("--lean", default="auto", choices=["auto", "on", "off"],
+                    help="resident blocks drop their norm outputs and FFN hidden activation and rebuild them in "
+                         "backward (auto: on whenever activation memory is the constraint, i.e. with 'selective')")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
     ap.add_argument("--sp-transport", default="fused", choices=["fused", "nccl"],
                     help="Ulysses exchange: fused into the kernels over NVLink peer memory, or NCCL all-to-all")
@@ -199,6 +202,7 @@ def run_ours(args):
     ckpt = args.checkpointing
     if ckpt == "auto":
         ckpt = "selective" if (args.model == "ti2v_5b" and world < 4) else "none"
+    lean = args.lean == "on" or (args.lean == "auto" and ckpt == "selective")
     keep = args.keep_blocks
     if keep < 0:
         keep = 0
@@ -208,6 +212,8 @@ def run_ours(args):
             # one its input and the two attention outputs; 18 GB covers those plus workspace at S = 27,280
             s_local = n_tokens(cfg, args) / world
             per_block = s_local * (14.5 * cfg.dim + cfg.ffn_dim) * 2
+            if lean:        # three [S, dim] norm outputs and the [S, ffn] hidden activation are not kept
+                per_block -= s_local * (3 * cfg.dim + cfg.ffn_dim) * 2
             n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
             zero_on = world > 1 and args.zero != "off"
             fixed = (6.0 + 12.0 / (world if zero_on else 1)) * n_params  # bf16 weight + fp32 grad + fp32 master/m/v
@@ -216,7 +222,8 @@ def run_ours(args):
             keep = min(keep, cfg.num_layers)
     zero = world > 1 and args.zero != "off"
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
-                           keep_blocks=keep, max_grad_norm=1.0, seed=0, zero=zero, zero_transport=args.zero)
+                           keep_blocks=keep, lean_kept=lean, max_grad_norm=1.0, seed=0, zero=zero,
+                           zero_transport=args.zero)
     model = heap = None
     if zero:
         from solarwm_b200.models.wan import WanDiT
@@ -272,6 +279,7 @@ def run_ours(args):
                        "optimizer_sharding": (f"zero-{args.zero}" if zero else "none"),
                        "latent": [1, cfg.in_dim, args.frames, args.height, args.width],
                        "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt, "keep_blocks": keep,
+                       "lean_resident_blocks": lean,
                        "attention_backend": ops.get_backend(), "optimizer": "AdamW fp32 master (in timed region)",
                        "l2": "no flush: per-step working set (>=10 GB of weights) exceeds the 126 MB L2",
                        "peak_allocated_gib": round(peak_gib, 2)},

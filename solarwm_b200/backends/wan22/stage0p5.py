@@ -38,6 +38,7 @@ class Stage0p5Options:
     ema_decay: Optional[float] = None
     checkpointing: str = "none"
     keep_blocks: int = 0
+    lean_kept: bool = False          # resident blocks rebuild their norm outputs / FFN hidden in backward
     zero: bool = False                 # shard optimizer state + gradient reduction over all ranks (own FSDP)
     zero_transport: str = "collective"  # or "fused" (NVLink peer reduce / push; needs a symmetric heap)
     seed: int = 0
@@ -55,6 +56,7 @@ class WanStage0p5Trainer:
             self.model.sp = sp
         self.model.checkpointing = opts.checkpointing
         self.model.keep_blocks = opts.keep_blocks
+        self.model.lean_kept = bool(opts.lean_kept)
         self.model.ensure_grads()
         okw = dict(lr=opts.lr, betas=opts.betas, eps=opts.eps, weight_decay=opts.weight_decay, ema_decay=opts.ema_decay)
         if opts.zero and self.sp_size * self.dp_size > 1:

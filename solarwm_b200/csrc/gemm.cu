@@ -53,6 +53,7 @@ struct ConvPlan {
 
 struct GemmParams {
   ConvPlan conv;
+  int ntile;                  // output columns per tile of the single-CTA kernel: BN, or 128 for narrow outputs
   int M, N, K;
   int tiles_m, tiles_n;
   const __nv_bfloat16* bias;  // [N] or null
@@ -79,11 +80,11 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int OUT_F32>
 __device__ __forceinline__ void epilogue_tile(const CUtensorMap& tmC, const GemmParams& p, const ColScatter& sc,
                                               uint32_t t_row, int row0, int n0, uint8_t* my_buf, int& buf, int lane,
-                                              int cw = 0, int ch = 0, int ct = 0) {
+                                              int cw = 0, int ch = 0, int ct = 0, int ncols = BN) {
   constexpr int CHUNK = OUT_F32 ? 32 : 64;  // columns per 128-byte staged row
   const bool rows_live = (row0) < p.M;
 #pragma unroll 1
-  for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+  for (int c0 = 0; c0 < ncols; c0 += CHUNK) {
     const int ncol = n0 + c0;
     if (ncol >= p.N) break;
     if (lane == 0) tma_store_wait_read<1>();
@@ -229,7 +230,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        const int m0 = tm * BM, n0 = tn * p.ntile;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -237,7 +238,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          mbar_expect_tx(&full_bar[stage], A_BYTES + p.ntile * BK * 2);
           const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
@@ -254,7 +255,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
+            for (int c = 0; c < p.ntile / 64; ++c)
               tma_load_2d(sb + c * (64 * BK * 2), &tmB, &full_bar[stage], n0 + c * 64, k0);
           } else {
             tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
@@ -276,7 +277,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       };
       const uint32_t smem_base = __shfl_sync(0xffffffffu, smem_u32(smem), 0);
       const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t idesc = umma_idesc_bf16(BM, p.ntile, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -321,7 +322,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-      const int m0 = tm * BM, n0 = tn * BN;
+      const int m0 = tm * BM, n0 = tn * p.ntile;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word, ST_TIMEOUT_TMEM_FULL)) break;
@@ -331,9 +332,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int tw = tm % p.conv.tiles_w, rest = tm / p.conv.tiles_w;
         const int th = rest % p.conv.tiles_h, tt = rest / p.conv.tiles_h;
         epilogue_tile<OUT_F32>(tmC, p, sc, t_row, 0, n0, my_buf, buf, lane, tw * CONV_BOX_W,
-                               th * CONV_BOX_H + q * 2, tt);
+                               th * CONV_BOX_H + q * 2, tt, p.ntile);
       } else {
-        epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane);
+        epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane, 0, 0, 0, p.ntile);
       }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
@@ -655,6 +656,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   if (rc) return rc;
   GemmParams p;
   memset(&p.conv, 0, sizeof(p.conv));
+  p.ntile = BN;
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = use_pair ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
@@ -760,7 +762,8 @@ extern "C" int solar_conv3d_bf16(const void* x, const void* w, void* y, const vo
   const uint32_t ba[4] = {BK, CONV_BOX_W, CONV_BOX_H, 1};
   int rc = make_tmap_4d(&tA, x, bf, da, sa, ba);
   if (rc) return rc;
-  rc = make_tmap_2d(&tB, w, bf, 2, Cout, K, K, BN, BK);
+  p.ntile = Cout <= 128 ? 128 : BN;      // narrow outputs: a 128-column tile wastes no MMA columns
+  rc = make_tmap_2d(&tB, w, bf, 2, Cout, K, K, p.ntile, BK);
   if (rc) return rc;
   const uint64_t dc[4] = {(uint64_t)Cout, (uint64_t)W, (uint64_t)H, (uint64_t)Tout};
   const uint64_t sc4[3] = {(uint64_t)Cout * 2, (uint64_t)W * Cout * 2, (uint64_t)H * W * Cout * 2};
@@ -768,7 +771,7 @@ extern "C" int solar_conv3d_bf16(const void* x, const void* w, void* y, const vo
   rc = make_tmap_4d(&tC, y, bf, dc, sc4, bc);
   if (rc) return rc;
   p.tiles_m = Tout * p.conv.tiles_h * p.conv.tiles_w;
-  p.tiles_n = (Cout + BN - 1) / BN;
+  p.tiles_n = (Cout + p.ntile - 1) / p.ntile;
   p.M = p.tiles_m * BM; p.N = Cout; p.K = K;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.act = 0; p.accumulate = 0; p.status = status;

@@ -244,10 +244,13 @@ class WanBlock(nn.Module):
 
         # ---- self attention
         nk = self._norm_kw(x)
-        xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
+        # lean: the three norm outputs and the FFN hidden activation are not kept; backward rebuilds them from the
+        # block's residual stream (two row passes and one GEMM) -- 8 of the block's 22 row-widths of activations
+        lean = bool(getattr(self, "lean", False)) and torch.is_grad_enabled()
         Ll = x.shape[0] // B
         fused_sp = attn_fn is None and camera is None and bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
             (not torch.is_grad_enabled() or self.unit.grad is not None)
+        xm = None if (lean and not fused_sp) else F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
         if fused_sp:
             # Ulysses exchanges ride on the producing kernels (parallel/fused_ulysses.py)
             from ..parallel.fused_ulysses import FusedAttention, FusedQKV
@@ -259,7 +262,13 @@ class WanBlock(nn.Module):
             o = FusedAttention.apply(recv, 1.0 / math.sqrt(hd), sp, parity,
                                      None if memo is None else (memo, "self"))
         else:
-            qkv = self._fused_linear(xm, "self_attn.q", "self_attn.v", 3 * D)
+            if lean:
+                qkv = F_.recompute_segment(
+                    lambda a, s0, s1: self._fused_linear(F_.norm_modulate(a, s0, s1, eps=cfg.eps, **nk, **gk),
+                                                         "self_attn.q", "self_attn.v", 3 * D),
+                    self._p("self_attn.q.weight"), x, mod[:, 0], mod[:, 1])
+            else:
+                qkv = self._fused_linear(xm, "self_attn.q", "self_attn.v", 3 * D)
             q = F_.rmsnorm_rope(qkv[:, :D], self._p("self_attn.norm_q.weight").float(), rope, eps=cfg.eps)
             k = F_.rmsnorm_rope(qkv[:, D:2 * D], self._p("self_attn.norm_k.weight").float(), rope, eps=cfg.eps)
             v = qkv[:, 2 * D:]
@@ -282,12 +291,19 @@ class WanBlock(nn.Module):
         x = F_.gated_residual(x, y, mod[:, 2], **gk)
 
         # ---- cross attention (text keys/values are replicated on every SP rank)
-        if cfg.cross_attn_norm:
-            xn = F_.norm_modulate(x, mode=2, w=self._p("norm3.weight").float(), b=self._p("norm3.bias").float(),
-                                  eps=cfg.eps)
+        if cfg.cross_attn_norm and lean:
+            qc = F_.recompute_segment(
+                lambda a: self._linear(F_.norm_modulate(a, mode=2, w=self._p("norm3.weight").float(),
+                                                        b=self._p("norm3.bias").float(), eps=cfg.eps),
+                                       "cross_attn.q.weight", "cross_attn.q.bias"),
+                self._p("cross_attn.q.weight"), x)
         else:
-            xn = x
-        qc = self._linear(xn, "cross_attn.q.weight", "cross_attn.q.bias")
+            if cfg.cross_attn_norm:
+                xn = F_.norm_modulate(x, mode=2, w=self._p("norm3.weight").float(), b=self._p("norm3.bias").float(),
+                                      eps=cfg.eps)
+            else:
+                xn = x
+            qc = self._linear(xn, "cross_attn.q.weight", "cross_attn.q.bias")
         qc = F_.rmsnorm_rope(qc, self._p("cross_attn.norm_q.weight").float(), None, eps=cfg.eps)
         kvc = self._fused_linear(context, "cross_attn.k", "cross_attn.v", 2 * D)
         kc = F_.rmsnorm_rope(kvc[:, :D], self._p("cross_attn.norm_k.weight").float(), None, eps=cfg.eps)
@@ -299,9 +315,11 @@ class WanBlock(nn.Module):
         x = F_.gated_residual(x, yc, None)
 
         # ---- feed forward
-        xm = F_.norm_modulate(x, mod[:, 3], mod[:, 4], eps=cfg.eps, **nk, **gk)
-        h = self._linear(xm, "ffn.0.weight", "ffn.0.bias")
-        y = F_.gelu_linear(h, self._p("ffn.2.weight"), self._p("ffn.2.bias"))
+        def ffn(a, s3, s4):
+            hm = F_.norm_modulate(a, s3, s4, eps=cfg.eps, **nk, **gk)
+            return F_.gelu_linear(self._linear(hm, "ffn.0.weight", "ffn.0.bias"), self._p("ffn.2.weight"), self._p("ffn.2.bias"))
+
+        y = F_.recompute_segment(ffn, self._p("ffn.2.weight"), x, mod[:, 3], mod[:, 4]) if lean else ffn(x, mod[:, 3], mod[:, 4])
         x = F_.gated_residual(x, y, mod[:, 5], **gk)
         return x
 
@@ -340,6 +358,7 @@ class WanDiT(nn.Module):
         self.sp = _NoSP()
         self.checkpointing = "none"  # "none" | "full" | "selective"
         self.keep_blocks = 0         # the last ``keep_blocks`` blocks keep their activations (no recompute)
+        self.lean_kept = False       # kept blocks drop their norm outputs and FFN hidden (rebuilt in backward)
         self._rope_cache: dict = {}
         if seed is not None:
             self.init_weights(seed)
@@ -464,7 +483,9 @@ class WanDiT(nn.Module):
             from torch.utils.checkpoint import checkpoint
 
             memo = {"__store__": True} if (self.checkpointing == "selective" and x.is_cuda) else None
+            block.lean = False
             return checkpoint(lambda a, b, c: block(a, b, rope, c, memo=memo, **kw), x, e0, ctx, use_reentrant=False)
+        block.lean = bool(self.lean_kept)
         return block(x, e0, rope, ctx, **kw)
 
     def forward(self, x, t, context, y=None, r=None, y_camera=None, perturb_blocks=()):

@@ -163,6 +163,49 @@ def linear(x, w, b=None, act=None):
     return _LinearFn.apply(x, w, b)
 
 
+# Weights (by address) whose forward product is not needed right now: the last GEMM of a segment that is being
+# re-run in backward only to rebuild what that GEMM's own backward keeps (its input), not its output.
+_SKIP_FORWARD: set = set()
+
+
+def _forward_needed(w) -> bool:
+    return not _SKIP_FORWARD or w.data_ptr() not in _SKIP_FORWARD
+
+
+class _SegmentFn(torch.autograd.Function):
+    """``fn(*args)`` that keeps only ``args`` for backward.  Backward re-runs ``fn`` with gradients on -- with the
+    forward product of the segment's LAST linear skipped (``tail_weight``), since nothing reads it -- and
+    back-propagates through the rebuilt graph.  Parameters used inside ``fn`` receive their gradients there."""
+
+    @staticmethod
+    def forward(ctx, fn, tail_weight, *args):
+        ctx.fn, ctx.tail = fn, tail_weight
+        ctx.save_for_backward(*args)
+        with torch.no_grad():
+            return fn(*args)
+
+    @staticmethod
+    def backward(ctx, dy):
+        args = [a.detach().requires_grad_(need) for a, need in zip(ctx.saved_tensors, ctx.needs_input_grad[2:])]
+        key = None if ctx.tail is None else ctx.tail.data_ptr()
+        with torch.enable_grad():
+            if key is not None:
+                _SKIP_FORWARD.add(key)
+            try:
+                out = ctx.fn(*args)
+            finally:
+                _SKIP_FORWARD.discard(key)
+        torch.autograd.backward(out, dy)
+        return (None, None) + tuple(a.grad for a in args)
+
+
+def recompute_segment(fn, tail_weight, *args):
+    """Run ``fn(*args)`` keeping only its inputs (see ``_SegmentFn``); plain call when gradients are off."""
+    if not torch.is_grad_enabled():
+        return fn(*args)
+    return _SegmentFn.apply(fn, tail_weight, *args)
+
+
 class _LinearMainGradFn(torch.autograd.Function):
     """Linear whose parameter gradients are written straight into flat ``main_grad`` buffers."""
 
@@ -170,6 +213,8 @@ class _LinearMainGradFn(torch.autograd.Function):
     def forward(ctx, x, w, b):
         ctx.save_for_backward(x)
         ctx.w, ctx.b = w, b
+        if not _forward_needed(w):
+            return x.new_empty((x.shape[0], w.shape[0]))
         return gemm(x, w, NT, bias=b)
 
     @staticmethod
@@ -469,10 +514,12 @@ class _GeluLinearMainGradFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, w, b):
         h = h.contiguous()
-        a = torch.empty_like(h)
-        _gelu_launch(h, None, a, 0)
         ctx.save_for_backward(h)
         ctx.w, ctx.b = w, b
+        if not _forward_needed(w):
+            return h.new_empty((h.shape[0], w.shape[0]))
+        a = torch.empty_like(h)
+        _gelu_launch(h, None, a, 0)
         return gemm(a, w, NT, bias=b)
 
     @staticmethod

@@ -101,3 +101,26 @@ def test_checkpointing_modes_give_identical_gradients(mode):
     ops.check_status()
     for n in grads["none"]:
         assert torch.equal(grads["none"][n], grads[mode][n]), n
+
+
+def test_lean_kept_blocks_give_identical_gradients_with_fewer_saved_activations():
+    cfg = _cfg()
+    x, t, ctx = _inputs()
+    grads, gemms = {}, {}
+    for lean in (False, True):
+        model = WanDiT(cfg, device="cuda", dtype=torch.bfloat16, seed=2)
+        with torch.no_grad():
+            model.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator(device="cuda").manual_seed(1))
+        model.lean_kept = lean
+        model.ensure_grads()
+        ops.reset_counters()
+        out = model(x.cuda(), t.cuda(), ctx.cuda())
+        out.float().pow(2).mean().backward()
+        model.finalize_grads()
+        grads[lean] = {n: p.main_grad.clone() for n, p in model.named_parameters()}
+        gemms[lean] = ops.COUNTERS.get("gemm", 0)
+    ops.check_status()
+    for n in grads[False]:
+        assert torch.equal(grads[False][n], grads[True][n]), n
+    # per block the backward re-runs ONE GEMM (FFN up-projection); the three tail products are skipped
+    assert gemms[True] - gemms[False] == cfg.num_layers, gemms

@@ -221,3 +221,28 @@ def test_ltx_guided_sampler_and_provider():
                             "runtime": {"device": "cpu"}})
     rep = prov.readiness()
     assert not rep["ready"] and any("vae" in p for p in rep["problems"])
+
+
+def test_lean_resident_blocks_rebuild_activations_with_identical_gradients():
+    """Blocks that drop their norm outputs and FFN hidden activation (rebuilt inside backward) give the same
+    parameter and input gradients as blocks that keep them."""
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+
+    cfg = WanConfig(dim=64, ffn_dim=128, num_heads=2, num_layers=2, in_dim=4, out_dim=4, text_dim=32, freq_dim=32, text_len=8)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 4, 3, 4, 4, generator=g)
+    t = torch.tensor([[500.0, 300.0, 100.0]])
+    ctx = torch.randn(1, 8, 32, generator=g)
+    grads = {}
+    for lean in (False, True):
+        m = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=2)
+        with torch.no_grad():
+            m.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator().manual_seed(1))
+        m.lean_kept = lean
+        xin = x.clone().requires_grad_(True)
+        m(xin, t, ctx).pow(2).mean().backward()
+        grads[lean] = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+        grads[lean]["__input__"] = xin.grad.clone()
+    assert set(grads[False]) == set(grads[True]) and len(grads[True]) > 20
+    for n in grads[False]:
+        assert torch.allclose(grads[False][n], grads[True][n], rtol=1e-5, atol=1e-7), n
