@@ -363,7 +363,7 @@ def run_realtime(args):
             fr = fr.to(torch.bfloat16)
             for f in range(fr.shape[1]):
                 rgb, _ = F_.rgb8(fr[:, f], mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5))
-                frames_host[n_out].copy_(rgb, non_blocking=True)
+                frames_host[n_out % frames_host.shape[0]].copy_(rgb, non_blocking=True)
                 n_out += 1
         return n_out
 
