@@ -147,8 +147,10 @@ def timed_region(steps, fn, dist, torch):
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
+    t0 = time.perf_counter()
     for _ in range(steps):
         fn()
+    timed_region.host_enqueue_ms = (time.perf_counter() - t0) * 1e3 / steps    # host time to issue one step
     stop.record()
     torch.cuda.synchronize()
     if dist is not None:
@@ -257,6 +259,7 @@ def run_ours(args):
     sampler.start()
     ops.reset_counters()
     ms = timed_region(args.steps, step_device, dist, torch)
+    host_ms = round(timed_region.host_enqueue_ms, 2)
     launches = ops.total_launches()
     counters = dict(ops.COUNTERS)
     ms_e2e = timed_region(args.steps, step_e2e, dist, torch)
@@ -286,7 +289,7 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
-            "gpu_launches": launches, "launch_counters": counters,
+            "gpu_launches": launches, "launch_counters": counters, "host_enqueue_ms_per_step": host_ms,
             "final_loss": losses[-1] if losses else None,
         }
         print(json.dumps(out))

@@ -39,6 +39,20 @@ def frame_split(num_frames: int, size: int):
     return out
 
 
+def balanced_lengths(total_rows: int, size: int):
+    """Balanced, descending row counts of a contiguous partition: the first ``total % size`` ranks hold one row
+    more (reference: deploy/solar_wm/.../attention/collectives.py:13-31)."""
+    if total_rows < size:
+        raise ValueError("every rank needs one row")
+    return [(total_rows + size - 1 - r) // size for r in range(size)]
+
+
+def balanced_bounds(total_rows: int, size: int, rank: int):
+    lengths = balanced_lengths(total_rows, size)
+    start = sum(lengths[:rank])
+    return start, start + lengths[rank]
+
+
 class _AllToAll(torch.autograd.Function):
     """all_to_all_single with explicit split sizes; backward is the reverse exchange."""
 
@@ -96,6 +110,12 @@ class UlyssesCollective:
     def set_layout(self, B: int, num_frames: int, frame_tokens: int) -> None:
         splits = frame_split(num_frames, self.size)
         self._layout = (B, [n * frame_tokens for _, n in splits])
+
+    def set_layout_rows(self, B: int, lengths) -> None:
+        """Arbitrary per-rank row counts (e.g. ``balanced_lengths``) instead of whole frames."""
+        if len(lengths) != self.size:
+            raise ValueError("one length per rank is required")
+        self._layout = (B, [int(n) for n in lengths])
 
     # [B, S_local, H, D] x3 -> [B, S, H/P, D] x3 -------------------------------------------
     def scatter_heads(self, q, k, v):

@@ -34,6 +34,7 @@ from ..backends.minimax_h3.flow import rollout_times
 from ..backends.minimax_h3.layout import TAG_TEXT, TAG_VIDEO, spatial_axis, temporal_positions
 from ..models.h3 import H3DiT, mm_rope_tables
 from ..ops import functional as F_
+from ..parallel.ulysses import balanced_lengths
 
 
 @dataclass
@@ -73,7 +74,7 @@ class H3StreamingGenerator:
         self.heads_local = mc.num_attention_heads // self.P
         self.rows_per_latent = cfg.grid_hw[0] * cfg.grid_hw[1]
         self.chunk_rows = cfg.chunk_latents * self.rows_per_latent
-        assert self.chunk_rows % self.P == 0, "chunk rows must split evenly over the SP ranks"
+        assert self.chunk_rows >= self.P, "every SP rank needs at least one row of a chunk"
         self.device = model.proj_in.device
         self.gen = torch.Generator(device=self.device).manual_seed(cfg.seed)
         self.times = rollout_times(cfg.denoise_steps, cfg.shift)[:cfg.denoise_steps]
@@ -116,7 +117,6 @@ class H3StreamingGenerator:
             txt = blk(txt, None, None, cos_t, sin_t, None, None, None)
         anchor_rows = F_.linear(patchify_latents(anchor_latent.to(dev, dt)), m.proj_in)
         self.n_cond = self.n_text + rows
-        assert self.n_cond % self.P == 0 or self.P == 1, "condition rows must split evenly over the SP ranks"
         self.cond_x = torch.cat([txt, anchor_rows], 0)
         self.cond_pos = torch.cat([pos_text, frame_pos([float(tpos[0])])], 0)
         self.cond_tags = torch.cat([torch.full((self.n_text,), TAG_TEXT), torch.full((rows,), TAG_VIDEO)]).to(dev, torch.int32)
@@ -156,8 +156,9 @@ class H3StreamingGenerator:
         """Row slice of this SP rank for a segment of ``n_rows`` rows."""
         if self.P == 1:
             return slice(0, n_rows)
-        per = n_rows // self.P
-        return slice(self.sp.rank * per, (self.sp.rank + 1) * per)
+        from ..parallel.ulysses import balanced_bounds
+
+        return slice(*balanced_bounds(n_rows, self.P, self.sp.rank))    # balanced, descending; need not be even
 
     # ------------------------------------------------------------------------------------ network
     def _evaluate(self, x_rows, t_scalar, pos, tags, view, key_base: int, n_rows: int, write_only: bool = False,
@@ -186,7 +187,7 @@ class H3StreamingGenerator:
             v = ops.head_norm_rope_prope(blk.to_v(xm), None, None, None, cam_kv, heads=H, **kw)
             q, k, v = (t.view(1, S, H, hd) for t in (q, k, v))
             if self.P > 1:
-                self.sp.set_layout(1, self.P, n_rows // self.P)         # even row split over the ranks
+                self.sp.set_layout_rows(1, balanced_lengths(n_rows, self.P))
                 q, k, v = self.sp.scatter_heads(q, k, v)
             kv.k[key_base:key_base + n_rows] = k.reshape(n_rows, hl * hd)
             kv.v[key_base:key_base + n_rows] = v.reshape(n_rows, hl * hd)
@@ -240,7 +241,7 @@ class H3StreamingGenerator:
         out = self._evaluate(x, self._t_in, self._pos_cache[first], self._video_tags, self._view_in, key_base=base,
                              n_rows=self.chunk_rows)
         if self.P > 1:
-            self.sp.set_layout(1, self.P, self.chunk_rows // self.P)
+            self.sp.set_layout_rows(1, balanced_lengths(self.chunk_rows, self.P))
             out = self.sp.gather_sequence(out, 1)
         self._out.copy_(out)
 
@@ -278,7 +279,6 @@ class H3StreamingGenerator:
         self.mem_rows = k * rows
         if k == 0:
             return
-        assert (k * rows) % self.P == 0, "memory rows must split evenly over the SP ranks"
         span = float(self._tpos[2] - self._tpos[1])
         t_mem = [float(self._tpos[0]) - (k - i) * span for i in range(k)]
         pos = self._tables(self._frame_pos(t_mem), k * rows)

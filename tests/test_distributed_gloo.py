@@ -194,7 +194,7 @@ def _h3_stream_worker(rank, world, path, out):
     model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
     scfg = H3StreamConfig(grid_hw=(2, 4), chunk_latents=2, window_chunks=2, denoise_steps=2, use_cuda_graph=False, seed=5)
     g = torch.Generator().manual_seed(1)
-    text, anchor = torch.randn(8, cfg.text_dim, generator=g), torch.randn(24, 1, 4, 8, generator=g)
+    text, anchor = torch.randn(9, cfg.text_dim, generator=g), torch.randn(24, 1, 4, 8, generator=g)
     outs = {}
     for name, sp in (("single", None), ("sp", UlyssesCollective(None))):
         gen = H3StreamingGenerator(model, scfg, sp=sp)
