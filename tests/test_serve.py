@@ -141,3 +141,52 @@ def test_decode_backends_switch_orders_chunks_and_refuses_nonfinite_pixels():
         backends.finish()
     assert finite_host(torch.ones(3, dtype=torch.bfloat16)) and not finite_host(torch.tensor([float("inf")], dtype=torch.bfloat16))
     backends.close()
+
+
+def test_scene_upload_validation_and_isolated_preparation(tmp_path):
+    import base64
+    import io
+    import os
+    import threading
+    import time
+
+    import pytest
+    from PIL import Image
+
+    from solarwm_b200.serve import scene_inputs as si
+
+    def png(w, h, fmt="PNG"):
+        buf = io.BytesIO()
+        Image.new("RGB", (w, h), (200, 100, 50)).save(buf, format=fmt)
+        return base64.b64encode(buf.getvalue()).decode()
+
+    row = si.store_upload(tmp_path, {"prompt": " a quiet street ", "image": png(32, 16)})
+    assert row["scene_id"].startswith("upload-") and row["prompt"] == "a quiet street" and os.path.exists(row["first"])
+    assert si.store_upload(tmp_path, {"prompt": "a quiet street", "image": png(32, 16)}) == row       # idempotent
+    assert si.store_upload(tmp_path, {"prompt": "another", "image": png(32, 16, "JPEG")})["scene_id"] != row["scene_id"]
+    for bad in ({"prompt": "", "image": png(4, 4)}, {"prompt": "x", "image": "@@@"}, {"prompt": "x", "image": png(4, 4, "BMP")},
+                {"prompt": "x", "image": "A" * (12 * 1024 * 1024)}, {"prompt": "x", "image": png(5000, 4000)},
+                {"prompt": "x" * 4001, "image": png(4, 4)}):
+        with pytest.raises(ValueError):
+            si.store_upload(tmp_path, bad)
+    # the conditioning function runs in another process, without the launcher's rank variables
+    os.environ["RANK"] = "3"
+    try:
+        req = {"callable": "solarwm_b200.serve.scene_inputs:image_statistics", "args": [row["first"]]}
+        seen = []
+        out = si.prepare_isolated(tmp_path, req, progress=seen.append)
+    finally:
+        del os.environ["RANK"]
+    assert out["pid"] != os.getpid() and abs(out["mean"][0] - 200 / 255) < 1e-3 and seen == ["encoding", "encoded"]
+    assert si.prepare_isolated(tmp_path, req, progress=seen.append) == out and seen == ["encoding", "encoded"]   # cached
+    with pytest.raises(RuntimeError, match="FileNotFoundError"):
+        si.prepare_isolated(tmp_path, {"callable": "solarwm_b200.serve.scene_inputs:image_statistics", "args": ["/nonexistent.png"]})
+    # cancellation and timeout end the child
+    flag = threading.Event()
+    threading.Timer(0.3, flag.set).start()
+    t0 = time.monotonic()
+    with pytest.raises(si.PreparationCancelled):
+        si.prepare_isolated(tmp_path, {"callable": "time:sleep", "args": [30]}, cancelled=flag.is_set)
+    with pytest.raises(TimeoutError):
+        si.prepare_isolated(tmp_path, {"callable": "time:sleep", "args": [31]}, timeout_s=0.3)
+    assert time.monotonic() - t0 < 20
