@@ -148,3 +148,37 @@ def test_camera_length_rollout():
     assert out.shape == (1, 4, 7, 4, 4) and torch.isfinite(out).all() and torch.equal(out[:, :, :1], first)
     still = camera_rollout(m, ctx, (2, 2), torch.eye(4).repeat(1, 7, 1, 1), None, cfg=scfg, first_frame=first)
     assert not torch.allclose(out[:, :, 3:], still[:, :, 3:], atol=1e-4)          # the camera path matters
+
+
+def test_wan_codec_adapters_btchw_contract_and_streaming_chunks():
+    import pytest
+    import torch
+
+    from solarwm_b200.backends.wan22.codec import Wan5BVAE, WanA14BVAE, WanVideoCodec, flow_to_x0
+    from solarwm_b200.errors import BackendContractError
+    from solarwm_b200.models.vae import VAEConfig, VideoVAE
+
+    torch.manual_seed(0)
+    codec = WanVideoCodec(VideoVAE(VAEConfig(z_dim=4, base=8, temporal_ups=(True, False)), [0.1] * 4, [2.0] * 4))
+    video = torch.rand(1, 5, 3, 16, 16) * 2 - 1
+    z = codec.encode(video)
+    assert z.shape == (1, 3, 4, 4, 4)                                   # 1 + (5 - 1) / 2 latent frames, 4x spatial
+    full = codec.decode(z)
+    assert full.shape == (1, 5, 3, 16, 16) and full.abs().max() <= 1.0
+    pieces = list(codec.decode_streaming_chunks(z, chunk_latent_frames=2))
+    assert [p.shape[1] for p in pieces] == [3, 2] and all(p.device.type == "cpu" for p in pieces)
+    assert torch.allclose(torch.cat(pieces, 1), full, atol=1e-5)
+    with pytest.raises(BackendContractError):
+        list(codec.decode_streaming_chunks(torch.cat([z, z]), chunk_latent_frames=2))
+    with pytest.raises(BackendContractError):
+        list(codec.decode_streaming_chunks(torch.full_like(z, float("nan"))))
+    with pytest.raises(BackendContractError):
+        codec.decode(z[:, :, :3])
+    with pytest.raises(BackendContractError):
+        Wan5BVAE.build([0.0] * 16, [1.0] * 16)
+    a14 = WanA14BVAE.build(base=8)
+    assert a14.vae.cfg.z_dim == 16 and abs(float(a14.vae.std.flatten()[0]) - 2.8184) < 1e-6
+    x_t, v = torch.randn(2, 3, 4, dtype=torch.bfloat16), torch.randn(2, 3, 4, dtype=torch.bfloat16)
+    x0 = flow_to_x0(x_t, v, torch.tensor([0.25, 0.5]))
+    assert x0.dtype == torch.bfloat16
+    assert torch.allclose(x0.float(), (x_t.double() - torch.tensor([0.25, 0.5]).view(2, 1, 1).double() * v.double()).float(), atol=2e-2)
