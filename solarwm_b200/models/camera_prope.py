@@ -69,4 +69,9 @@ def per_row(mats: torch.Tensor, rows_per_camera: int) -> torch.Tensor:
 def apply(x: torch.Tensor, mats: torch.Tensor, heads: int, rot_dims: int = 0) -> torch.Tensor:
     """x [rows, heads * 128]; mats fp32 [rows, 4, 4] -> every 4-vector of channels [rot_dims, 128) of
     each head multiplied by the row's matrix."""
+    hd = x.shape[1] // heads
+    if hd != 128 and rot_dims == 0 and x.shape[1] % 128 == 0:
+        # the matrix acts on every 4-vector of a row alike, so head boundaries do not matter to the camera-only
+        # transform: narrower heads (LTX: 64) ride the 128-wide kernel as pseudo-heads
+        heads = x.shape[1] // 128
     return ops.head_norm_rope_prope(x, None, None, None, mats.float().contiguous(), heads=heads, rot_dims=rot_dims)

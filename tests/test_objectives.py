@@ -246,3 +246,32 @@ def test_lean_resident_blocks_rebuild_activations_with_identical_gradients():
     assert set(grads[False]) == set(grads[True]) and len(grads[True]) > 20
     for n in grads[False]:
         assert torch.allclose(grads[False][n], grads[True][n], rtol=1e-5, atol=1e-7), n
+
+
+def test_ltx_fixed_focal_camera_condition_changes_only_with_the_cameras():
+    from solarwm_b200.models import camera_prope
+    from solarwm_b200.models.ltx import FIXED_FX_NORM, LTXDiT, ltx_camera_condition, ltx_preset
+
+    cfg = ltx_preset("tiny")                                  # 2 heads x 64
+    m = LTXDiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    g = torch.Generator().manual_seed(0)
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05, generator=g)     # the head starts at zero
+    x, t, ctx = torch.randn(1, 16, 3, 4, 4, generator=g), torch.tensor([[400.0, 400.0, 400.0]]), torch.randn(1, 16, 64, generator=g)
+    eye = torch.eye(4).repeat(1, 3, 1, 1)
+    moved = eye.clone()
+    moved[0, 1:, 0, 3] = 0.3
+    cond = ltx_camera_condition(eye)
+    assert abs(float(cond["Ks"][0, 0, 0, 0]) - FIXED_FX_NORM) < 1e-7 and cond["Ks"].shape == (1, 3, 3, 3)
+    with torch.no_grad():
+        plain, same, other = m(x, t, ctx), m(x, t, ctx, y_camera=cond), m(x, t, ctx, y_camera=ltx_camera_condition(moved, "logd4"))
+    # identical cameras: P cancels between q^T k and the output transform (same frame <-> same P), up to rounding
+    assert torch.allclose(plain, same, atol=1e-4)
+    assert (other - plain).abs().max() > 1e-4
+    # 64-wide heads ride the 128-wide camera kernel as pseudo-heads: same numbers as the dense 4x4 products
+    rows = torch.randn(5, 128, generator=g)
+    mats = torch.randn(5, 4, 4, generator=g)
+    want = torch.einsum("rij,rnj->rni", mats, rows.view(5, 32, 4)).reshape(5, 128)
+    assert torch.allclose(camera_prope.apply(rows, mats, heads=2), want, atol=1e-5)
+    with pytest.raises(ValueError):
+        ltx_camera_condition(torch.eye(4))
