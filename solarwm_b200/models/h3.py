@@ -138,7 +138,7 @@ class H3Block(nn.Module):
         t = F_.linear(torch.nn.functional.silu(temb.float()).to(temb.dtype), self.adaln_proj)
         return t.float().view(-1, 6, self.cfg.hidden_size).contiguous()
 
-    def forward(self, x, table, idx, rope_cos, rope_sin, cam_q, cam_kv, cam_o, sp=None, attn_fn=None):
+    def forward(self, x, table, idx, rope_cos, rope_sin, cam_q, cam_kv, cam_o, sp=None, attn_fn=None, memo=None):
         cfg = self.cfg
         H, hd = cfg.num_attention_heads, cfg.attention_head_dim
         kw = dict(rot_dims=cfg.rot_dims, sections=cfg.rope_sections, eps=cfg.eps)
@@ -155,7 +155,7 @@ class H3Block(nn.Module):
         q, k, v = (t.view(1, S, H, hd) for t in (q, k, v))
         if sp is not None and sp.size > 1:
             q, k, v = sp.scatter_heads(q, k, v)
-        o = attn_fn(q, k, v) if attn_fn is not None else ops.attention(q, k, v)
+        o = attn_fn(q, k, v) if attn_fn is not None else ops.attention(q, k, v, memo=None if memo is None else (memo, "self"))
         if sp is not None and sp.size > 1:
             o = sp.gather_heads(o)
         o = o.reshape(S, H * hd)
@@ -219,6 +219,10 @@ class H3DiT(nn.Module):
         self.proj_out, self.audio_proj_out = lin(h, cfg.latent_row_dim, 0.02), lin(h, cfg.audio_row_dim, 0.02)
         self.sp = None
         # inference-only caches installed by renderer.service (None = off)
+        # activation checkpointing of the main blocks: "none" | "full" (recompute the block in backward) |
+        # "selective" (recompute everything but the attention call, whose output is carried across the recompute;
+        # reference policy: solar/backends/minimax_h3/fsdp.py:146-165)
+        self.checkpointing = "none"
         self.fixed_tables = None        # {tuple of unique timesteps: [per-block adaLN tables]}
         self.text_cache = None          # {"input": rows, "output": refined rows, "hits": n}
 
@@ -277,7 +281,15 @@ class H3DiT(nn.Module):
         cam_q = cam_kv = cam_o = None
         if viewmats is not None:
             cam_q, cam_kv, cam_o = prope_row_matrices(viewmats.to(x.device), fx, fy)
+        ckpt = self.checkpointing if torch.is_grad_enabled() else "none"
         for bi, blk in enumerate(self.blocks):
+            if ckpt in ("full", "selective"):
+                from torch.utils.checkpoint import checkpoint
+
+                memo = {"__store__": True} if (ckpt == "selective" and x.is_cuda and attn_fn is None) else None
+                x = checkpoint(lambda a, te, b=blk, mm=memo: b(a, b.tables(te), idx, cos, sin, cam_q, cam_kv, cam_o, sp=self.sp,
+                                                              attn_fn=attn_fn, memo=mm), x, temb, use_reentrant=False)
+                continue
             x = blk(x, tables[bi] if tables is not None else blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o,
                     sp=self.sp, attn_fn=attn_fn)
         xn = F_.norm_modulate(x, mode=1, w=self.norm_out, eps=cfg.eps)

@@ -76,3 +76,32 @@ def test_h3_backend_routes_stage1_and_stage2(tmp_path):
         assert out["final_step"] == 1
         ok = verify_checkpoint(out["checkpoint"])
         assert ok.contract.stage == stage and ok.step == 1
+
+
+def test_h3_activation_checkpointing_modes_keep_the_gradients():
+    import torch
+
+    from solarwm_b200.backends.minimax_h3.stage1 import teacher_forcing_forward  # noqa: F401  (module import check)
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.renderer.cli import _sample
+    from solarwm_b200.renderer.core import packed_forward
+    from solarwm_b200.backends.minimax_h3.layout import patchify_latents
+
+    cfg = h3_preset("tiny")
+    cfg.lora_rank = 4
+    s = _sample(cfg, 0)
+    grads = {}
+    for mode in ("none", "full", "selective"):
+        m = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+        for p in m.trainable_parameters():
+            torch.nn.init.normal_(p, std=0.02, generator=torch.Generator().manual_seed(p.numel()))
+        m.checkpointing = mode
+        rows = patchify_latents(s["target_latents"]).float()
+        out = packed_forward(m, prompt=s["prompt_embeds"].float(), anchor_rows=patchify_latents(s["anchor_latents"]).float(),
+                             structure_rows=None, target_rows=rows, row_times=torch.full((rows.shape[0],), 0.4), grid_hw=(4, 4))
+        out.pow(2).mean().backward()
+        grads[mode] = [p.grad.clone() for p in m.trainable_parameters()]
+        assert len(grads[mode]) > 0 and any(g.abs().max() > 0 for g in grads[mode])
+    for mode in ("full", "selective"):
+        for a, b in zip(grads["none"], grads[mode]):
+            assert torch.allclose(a, b, rtol=1e-5, atol=1e-8)
