@@ -102,12 +102,32 @@ class LoRALinear(nn.Module):
             self.lora_A = nn.Parameter((torch.randn(rank, d_in, generator=gen, device=gen.device) / math.sqrt(d_in)).to(device, dtype))
             self.lora_B = nn.Parameter(torch.zeros(d_out, rank, device=device, dtype=dtype))
 
+        self._bank = None          # name of the active extra adapter bank (None: the primary lora_A / lora_B)
+
+    def add_bank(self, name: str, rank: int, gen) -> None:
+        """A second, independently trained adapter over the same frozen weight (e.g. the Memory adapter)."""
+        d_out, d_in = self.weight.shape
+        dev, dt = self.weight.device, self.weight.dtype
+        setattr(self, f"lora_A__{name}", nn.Parameter((torch.randn(rank, d_in, generator=gen, device=gen.device) / math.sqrt(d_in)).to(dev, dt)))
+        setattr(self, f"lora_B__{name}", nn.Parameter(torch.zeros(d_out, rank, device=dev, dtype=dt)))
+
+    def use_bank(self, name) -> None:
+        if name is not None and not hasattr(self, f"lora_A__{name}"):
+            raise KeyError(f"no adapter bank {name!r}")
+        self._bank = name
+
+    def _adapter(self):
+        if self._bank is not None:
+            return getattr(self, f"lora_A__{self._bank}"), getattr(self, f"lora_B__{self._bank}")
+        return (self.lora_A, self.lora_B) if self.rank > 0 else (None, None)
+
     def forward(self, x):
-        if self.rank == 0:
+        a, b = self._adapter()
+        if a is None:
             return F_.linear(x, self.weight)
         if not x.is_cuda:
-            return (x.float() @ self.weight.float().t() + (x.float() @ self.lora_A.float().t()) @ self.lora_B.float().t()).to(x.dtype)
-        return _LoRAFn.apply(x, self.weight, self.lora_A, self.lora_B)
+            return (x.float() @ self.weight.float().t() + (x.float() @ a.float().t()) @ b.float().t()).to(x.dtype)
+        return _LoRAFn.apply(x, self.weight, a, b)
 
     @torch.no_grad()
     def merge_(self):
@@ -228,6 +248,24 @@ class H3DiT(nn.Module):
 
     def trainable_parameters(self):
         return [p for p in self.parameters() if p.requires_grad]
+
+    # named adapter banks: independent LoRA sets over the same frozen base, one active at a time ----------
+    def add_adapter(self, name: str, rank: int, seed: int = 0) -> None:
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        for mod in self.modules():
+            if isinstance(mod, LoRALinear):
+                mod.add_bank(name, rank, gen)
+
+    def set_adapter(self, name) -> None:
+        """``None`` selects the primary adapter (or the bare base when ``lora_rank`` is 0)."""
+        for mod in self.modules():
+            if isinstance(mod, LoRALinear):
+                mod.use_bank(name)
+        self.active_adapter = name
+
+    def adapter_state(self, name: str) -> dict:
+        tag = f"__{name}"
+        return {k: v.detach().clone() for k, v in self.state_dict().items() if k.endswith(tag)}
 
     def time_embed(self, timesteps):
         """unique timesteps [T] in [0, 1] -> [T, time_embed_dim]"""

@@ -49,6 +49,8 @@ class H3StreamConfig:
     fy: float = 0.898
     use_cuda_graph: bool = True
     memory_latents: int = 0            # capacity of the retrieved-memory segment (0 = no memory rows)
+    memory_adapter: Optional[str] = None   # adapter bank active while memory rows are installed (fill and query
+                                       # evaluations); without memory rows the primary adapter serves
     seed: int = 0
 
 
@@ -276,6 +278,11 @@ class H3StreamingGenerator:
             raise ValueError(f"{k} memory latents exceed the configured capacity {cfg.memory_latents}")
         if k * rows != self.mem_rows:
             self._graphs = None                 # the key range changes: a captured graph no longer applies
+        if cfg.memory_adapter is not None:
+            want = cfg.memory_adapter if k > 0 else None
+            if getattr(m, "active_adapter", None) != want:
+                m.set_adapter(want)             # other weights: a captured graph no longer applies either
+                self._graphs = None
         self.mem_rows = k * rows
         if k == 0:
             return

@@ -1,4 +1,5 @@
 """H3 streaming generator: cache bookkeeping, window sliding by delta rotation, camera matrices (CPU)."""
+import pytest
 import torch
 
 from solarwm_b200.models.h3 import H3DiT, h3_preset, mm_rope_tables, prope_row_matrices
@@ -124,3 +125,37 @@ def test_full_length_generation_with_memory_and_streaming_decode(tmp_path):
     assert all(torch.isfinite(f).all() for f in frames) and frames[0].shape[-2:] == (8, 12)
     assert man["memory"]["retrieved"][0] == [] and len(man["memory"]["retrieved"][-1]) == 2
     assert json.loads((tmp_path / "manifest.json").read_text())["latents"] == n_chunks * k
+
+
+def test_memory_adapter_bank_is_active_only_while_memory_rows_are_installed():
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    model.add_adapter("memory", rank=4, seed=3)
+    with torch.no_grad():                       # a zero B would make the bank a no-op
+        for n, p in model.named_parameters():
+            if n.endswith("lora_B__memory"):
+                p.normal_(0, 0.05, generator=torch.Generator().manual_seed(p.numel()))
+    assert len(model.adapter_state("memory")) == 2 * sum(1 for _ in model.modules() if type(_).__name__ == "LoRALinear")
+    mem = torch.randn(24, 2, 4, 6, generator=torch.Generator().manual_seed(9))
+
+    def run(adapter):
+        scfg = H3StreamConfig(grid_hw=(2, 3), chunk_latents=2, window_chunks=2, denoise_steps=2, use_cuda_graph=False,
+                              memory_latents=3, memory_adapter=adapter)
+        g = H3StreamingGenerator(model, scfg)
+        torch.manual_seed(0)
+        g.start(torch.randn(6, cfg.text_dim), torch.randn(24, 1, 4, 6), torch.eye(4))
+        first = g.next_chunk(None)
+        g.set_memory(mem, None)
+        active = getattr(model, "active_adapter", None)
+        second = g.next_chunk(None)
+        g.set_memory(None)
+        third = g.next_chunk(None)
+        return first, second, third, active, getattr(model, "active_adapter", None)
+
+    a = run(None)
+    b = run("memory")
+    assert a[3] is None and b[3] == "memory" and b[4] is None           # switched on with the rows, off with them
+    assert torch.equal(a[0], b[0])                                        # before any memory: the same stream
+    assert not torch.allclose(a[1], b[1])                                 # memory rows served by the Memory adapter
+    with pytest.raises(KeyError):
+        model.set_adapter("nope")
