@@ -230,4 +230,8 @@ class LTX25Backend:
         return {"output_dir": str(s.output_dir), "cases": s.cases}
 
     def preencode(self, config):
-        raise BackendContractError("LTX preencoding needs the official codec weights, which are not available offline")
+        """Raw clips + captions -> 128-channel latent / text shards (8 x 32 x 32 codec geometry; random-init codecs
+        unless ``preencode.codecs`` names checkpoints) through the shared commit-last corpus assembly."""
+        from ..wan22.preencode import run_preencode
+
+        return run_preencode(config, "ltx25_video", latent_channels=128, temporal_ups=(True, True, True, False, False))

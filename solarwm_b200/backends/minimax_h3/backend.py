@@ -165,8 +165,48 @@ class MiniMaxH3Backend:
         return {"final_step": n, "last": last, "checkpoint": str(target), "native_launches": ops.total_launches()}
 
     def infer(self, config):
-        raise BackendContractError("H3 source-length inference needs released condition files; use serve.h3_realtime "
-                                   "for synthetic streaming generation")
+        """Camera-length generation: chunk-by-chunk streaming over the camera path with the latent memory bank
+        optional (``inference.memory``) and the manifest written under ``<output>/generate``.  Conditions come from
+        ``inference.conditions`` (a ``.pt`` with ``text``, ``anchor_latent``, ``c2w``, ``intrinsics``) or, with
+        ``inference.source: synthetic``, from seeded random tensors of the configured geometry."""
+        from ...serve.h3_full_inference import generate_full_length
+        from ...serve.h3_stream import H3StreamConfig
+
+        inf = config.get("inference", {}) or {}
+        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
+        cfg = self._cfg(config)
+        cfg.lora_rank = 0 if inf.get("merged_weights", True) else cfg.lora_rank
+        model = H3DiT(cfg, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, seed=int(inf.get("seed", 0)))
+        gh, gw = (int(v) for v in inf.get("grid_hw", (4, 6)))
+        k, chunks = int(inf.get("chunk_latents", 2)), int(inf.get("chunks", 2))
+        use_memory = bool(inf.get("memory", False))
+        scfg = H3StreamConfig(grid_hw=(gh, gw), chunk_latents=k, window_chunks=int(inf.get("window_chunks", 2)),
+                              denoise_steps=int(inf.get("denoise_steps", 4)), use_cuda_graph=dev == "cuda",
+                              memory_latents=int(inf.get("top_k", 2)) if use_memory else 0, seed=int(inf.get("seed", 0)))
+        if inf.get("conditions"):
+            cond = torch.load(inf["conditions"], map_location="cpu", weights_only=True)
+        elif str(inf.get("source", "synthetic")) == "synthetic":
+            g = torch.Generator().manual_seed(int(inf.get("seed", 0)) + 17)
+            n = 1 + k * chunks
+            c2w = torch.eye(4).repeat(n, 1, 1)
+            c2w[:, 2, 3] = torch.arange(n) * 0.05
+            K = torch.tensor([[cfg.fx if hasattr(cfg, "fx") else 0.505, 0.0, 0.5], [0.0, 0.898, 0.5], [0.0, 0.0, 1.0]])
+            cond = {"text": torch.randn(int(inf.get("prompt_len", 8)), cfg.text_dim, generator=g),
+                    "anchor_latent": torch.randn(scfg.latent_channels, 1, 2 * gh, 2 * gw, generator=g),
+                    "c2w": c2w, "intrinsics": K.repeat(n, 1, 1)}
+        else:
+            raise BackendContractError("inference.conditions (a .pt file) is required unless inference.source is synthetic")
+        out_dir = output_root(config) / "generate"
+        out_dir.mkdir(parents=True, exist_ok=True)
+        manifest = generate_full_length(model, text=cond["text"], anchor_latent=cond["anchor_latent"], c2w=cond["c2w"],
+                                        intrinsics=cond["intrinsics"], stream_cfg=scfg, use_memory=use_memory,
+                                        top_k=int(inf.get("top_k", 2)), out_dir=out_dir)
+        return {"output_dir": str(out_dir), "chunks": manifest.get("chunks"), "frames": manifest.get("frames"),
+                "native_launches": ops.total_launches()}
 
     def preencode(self, config):
-        raise BackendContractError("H3 preencoding needs the official codec weights, which are not available offline")
+        """Raw clips + captions -> 24-channel latent / text shards (4 x 16 x 16 codec geometry; random-init codecs
+        unless ``preencode.codecs`` names checkpoints) through the shared commit-last corpus assembly."""
+        from ..wan22.preencode import run_preencode
+
+        return run_preencode(config, "minimax_h3", latent_channels=24, temporal_ups=(True, True, False, False))

@@ -60,19 +60,26 @@ def _clips(config: Mapping[str, Any], rank: int, world: int) -> Iterator[Tuple[s
         reader.close()
 
 
-def run_preencode(config: Mapping[str, Any], family: str) -> Mapping[str, Any]:
+def run_preencode(config: Mapping[str, Any], family: str, *, latent_channels: int = None,
+                  temporal_ups: Tuple[bool, ...] = None) -> Mapping[str, Any]:
+    """``latent_channels`` / ``temporal_ups`` describe the codec geometry of families outside the Wan profiles
+    (LTX: 128 channels, 8 x 32 x 32; H3: 24 channels, 4 x 16 x 16); the corpus assembly is the same."""
     import torch.distributed as dist
 
     from ...runtime import distributed as rdist
 
-    prof = PROFILES[family]
+    prof = PROFILES.get(family)
+    if prof is None and latent_channels is None:
+        raise BackendContractError(f"no codec geometry known for family {family!r}")
     pre, data = config["preencode"], config["data"]
     rank = dist.get_rank() if dist.is_initialized() else 0
     world = dist.get_world_size() if dist.is_initialized() else 1
     device = torch.device(str(config.get("runtime", {}).get("device", "cpu")).replace("auto", "cuda" if torch.cuda.is_available() else "cpu"))
     dtype = torch.bfloat16
     codecs = pre.get("codecs", {}) or {}
-    vcfg = VAEConfig(z_dim=int(codecs.get("z_dim", prof.latent_channels)), base=int(codecs.get("vae_base", 16)))
+    ups = tuple(bool(u) for u in codecs.get("temporal_ups", temporal_ups or VAEConfig().temporal_ups))
+    vcfg = VAEConfig(z_dim=int(codecs.get("z_dim", latent_channels or prof.latent_channels)),
+                     base=int(codecs.get("vae_base", 16)), temporal_ups=ups)
     tcfg = T5Config(**codecs["t5"]) if "t5" in codecs else T5Config.tiny()
     vae = VideoVAE(vcfg).to(device=device, dtype=torch.float32).eval()
     text = WanTextEncoder(tcfg, device=device, dtype=torch.float32)
@@ -101,7 +108,7 @@ def run_preencode(config: Mapping[str, Any], family: str) -> Mapping[str, Any]:
     except Exception as exc:  # noqa: BLE001 - exchanged so that every rank fails together
         error, index = exc, None
     rdist.propagate_collective_error(None if error is None else f"{type(error).__name__}: {error}",
-                                     dist=dist if world > 1 else None, label="wan preencode")
+                                     dist=dist if world > 1 else None, label=f"{family} preencode")
     if world > 1:
         dist.barrier()
     total = 0

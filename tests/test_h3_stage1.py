@@ -105,3 +105,18 @@ def test_h3_activation_checkpointing_modes_keep_the_gradients():
     for mode in ("full", "selective"):
         for a, b in zip(grads["none"], grads[mode]):
             assert torch.allclose(a, b, rtol=1e-5, atol=1e-8)
+
+
+def test_h3_backend_infer_runs_camera_length_generation(tmp_path):
+    import json
+
+    from solarwm_b200.registry import load_backend
+
+    config = {"model": {"family": "minimax_h3", "architecture": "tiny", "camera_translation_transform": "logd4"},
+              "runtime": {"output_dir": str(tmp_path / "run"), "device": "cpu"},
+              "inference": {"source": "synthetic", "grid_hw": [2, 3], "chunk_latents": 2, "chunks": 3, "denoise_steps": 2,
+                            "memory": True, "top_k": 2, "seed": 4}}
+    out = load_backend("minimax_h3").infer(config)
+    manifest = json.loads((tmp_path / "run" / "generate" / "manifest.json").read_text())
+    assert out["chunks"] == 3 and manifest["latents"] == 6 and manifest["memory"]["enabled"] is True
+    assert len(manifest["chunk_seconds"]) == 3

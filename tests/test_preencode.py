@@ -94,3 +94,19 @@ def test_parameter_free_resample_shortcuts():
     assert first.shape == (2, 4, 3, 4, 4) and torch.equal(first, up[:, :, 1:])
     const = torch.full((1, 4, 3, 2, 2), 1.5)
     assert torch.allclose(AvgDown3D(4, 4, 2, 2)(const)[:, :, 1:], torch.full((1, 4, 1, 1, 1), 1.5))
+
+
+def test_ltx_and_h3_preencode_share_the_corpus_assembly(tmp_path):
+    from solarwm_b200.registry import load_backend
+
+    for family, z, frames, hw, shape in (("ltx25_video", 128, 9, 64, (2, 128, 2, 2)), ("minimax_h3", 24, 9, 32, (3, 24, 2, 2))):
+        out_root = tmp_path / family
+        cfg = {"data": {"pixel_frames": frames, "pixel_height": hw, "pixel_width": hw, "seed": 1}, "runtime": {"device": "cpu"},
+               "preencode": {"source": "synthetic", "num_samples": 2, "output_root": str(out_root), "codecs": {"vae_base": 4}}}
+        res = load_backend(family).preencode(cfg)
+        assert res["samples"] == 2
+        rows = read_index(out_root / "index.jsonl")
+        c = EncoderContract.from_dict(__import__("json").loads((out_root / "encoder-contract.json").read_text()))
+        assert c.family == family
+        s = read_encoded_sample(out_root, rows[0].values, c)
+        assert tuple(s["latents"].shape) == shape, s["latents"].shape
