@@ -7,8 +7,8 @@ disjoint shard prefixes; rank 0 merges the per-rank indices after a collective e
 (reference: solar/backends/wan22/runtime/preencode.py:277-699, solar/preencode/shards.py).
 
 Sources: ``preencode.source: synthetic`` (deterministic random clips; used by tests and smoke runs)
-or ``index`` (rows of a raw dataset index whose members are ``.npy`` videos ``[T, H, W, 3]`` uint8 and a
-caption; decoding of compressed video is the data plane's job and not repeated here).
+or ``index`` (rows of a raw dataset index whose members are a video -- a ``.npy`` array ``[T, H, W, 3]`` uint8 or a
+compressed container decoded by ``data.raw_video`` -- and a caption).
 """
 from __future__ import annotations
 
@@ -48,10 +48,10 @@ def _clips(config: Mapping[str, Any], rank: int, world: int) -> Iterator[Tuple[s
                 continue
             members = row.values.get("members", {})
             got = reader.read_members(root / row.shard, [members["video"], members["caption"]])
-            vid = np.load(io.BytesIO(got[members["video"]]), allow_pickle=False)
-            if vid.ndim != 4 or vid.shape[-1] != 3 or vid.shape[0] < T:
-                raise BackendContractError(f"{row.sample_id}: video must be [T>={T}, H, W, 3] uint8")
-            clip = torch.from_numpy(vid[:T]).permute(3, 0, 1, 2).float() / 127.5 - 1.0
+            from ...data.raw_video import load_clip
+
+            vid = load_clip(members["video"], got[members["video"]], T)     # .npy array or a compressed container
+            clip = torch.from_numpy(np.ascontiguousarray(vid)).permute(3, 0, 1, 2).float() / 127.5 - 1.0
             if clip.shape[2:] != (H, W):
                 clip = torch.nn.functional.interpolate(clip.permute(1, 0, 2, 3), size=(H, W), mode="bilinear",
                                                        align_corners=False).permute(1, 0, 2, 3)

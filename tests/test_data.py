@@ -148,3 +148,39 @@ def test_window_index_build_query_and_slices(tmp_path):
     with pytest.raises(DataContractError):
         build_index(tmp_path / "none.sqlite", clips, window=64, stride=1)
     assert not (tmp_path / "none.sqlite").exists()
+
+
+def test_raw_video_decode_matches_written_frames(tmp_path):
+    import numpy as np
+    import pytest
+
+    cv2 = pytest.importorskip("cv2")
+    from solarwm_b200.data import raw_video
+    from solarwm_b200.errors import DataContractError
+
+    path = str(tmp_path / "clip.mp4")
+    w = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"mp4v"), 24.0, (64, 48))
+    assert w.isOpened()
+    for i in range(80):
+        w.write(np.full((48, 64, 3), (i * 3, 255 - i * 3, 40), np.uint8))     # BGR
+    w.release()
+    blob = open(path, "rb").read()
+    info = raw_video.probe(blob)
+    assert info["frames"] == 80 and abs(info["fps"] - 24.0) < 1e-3 and (info["height"], info["width"]) == (48, 64)
+    idx = [0, 2, 2, 5, 70]                                   # a repeat and a jump beyond the seek threshold
+    got = raw_video.decode_frames(blob, idx)
+    assert got.shape == (5, 48, 64, 3) and got.dtype == np.uint8
+    for j, i in enumerate(idx):                              # RGB order, lossy codec: a few grey levels of slack
+        assert abs(float(got[j, ..., 2].mean()) - i * 3) < 6 and abs(float(got[j, ..., 0].mean()) - 40) < 6
+    assert raw_video.decode_frames(blob, [1, 3], size=(24, 32)).shape == (2, 24, 32, 3)
+    clip = raw_video.load_clip("a.mp4", blob, 4, offsets=[0, 3, 6, 9])
+    assert clip.shape == (4, 48, 64, 3)
+    buf = __import__("io").BytesIO()
+    np.save(buf, np.zeros((5, 4, 4, 3), np.uint8))
+    assert raw_video.load_clip("a.npy", buf.getvalue(), 3).shape == (3, 4, 4, 3)
+    with pytest.raises(DataContractError):
+        raw_video.decode_frames(blob, [3, 1])
+    with pytest.raises(DataContractError):
+        raw_video.decode_frames(blob, [200])
+    with pytest.raises(DataContractError):
+        raw_video.decode_frames(b"not a video", [0])
