@@ -627,6 +627,35 @@ extern "C" int solar_attn_bwd_trace(int enable, long long* out16) {
 }
 
 // All tensors are [B, S, H, D] bf16 with unit stride on D and stride D on H; *_ss / *_sb are the
+// Tail overlap: the dK/dV kernel and the dQ kernel are independent; with the switch on, the dQ kernel is launched
+// on a side stream (forked after the row-statistics kernel, joined before the entry returns control of the
+// caller's stream), so its CTAs fill the SMs that the last, partly empty wave of the dK/dV kernel leaves idle.
+// It matters when a rank owns few heads (sequence parallelism): 642 + 321 CTAs on 148 SMs run as 7 waves
+// instead of 5 + 3.  Off by default for bare callers of the C entry; the framework turns it on.
+static int g_bwd_overlap = 0;
+namespace {
+constexpr int kMaxDev = 64;
+cudaStream_t g_side_stream[kMaxDev] = {nullptr};
+cudaEvent_t g_fork_ev[kMaxDev] = {nullptr}, g_join_ev[kMaxDev] = {nullptr};
+int side_stream_for_device(int* dev_out) {
+  int dev = 0;
+  SOLAR_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDev) return fail("attention backward: device index out of range%s");
+  if (g_side_stream[dev] == nullptr) {
+    SOLAR_CUDA_OK(cudaStreamCreateWithFlags(&g_side_stream[dev], cudaStreamNonBlocking));
+    SOLAR_CUDA_OK(cudaEventCreateWithFlags(&g_fork_ev[dev], cudaEventDisableTiming));
+    SOLAR_CUDA_OK(cudaEventCreateWithFlags(&g_join_ev[dev], cudaEventDisableTiming));
+  }
+  *dev_out = dev;
+  return 0;
+}
+}  // namespace
+extern "C" int solar_attn_bwd_overlap(int enable) {
+  const int before = g_bwd_overlap;
+  if (enable >= 0) g_bwd_overlap = enable ? 1 : 0;
+  return before;
+}
+
 // element strides of the sequence and batch axes.  lse [B,H,Sq] fp32 (natural log, from the
 // forward kernel).  scratch: 2 * B*H*Sq_pad fp32 of caller-provided memory, Sq_pad = Sq rounded
 // up to 128.  Writes dq [B,Sq,H,D], dk and dv [B,Sk,H,D] (contiguous).
@@ -658,6 +687,16 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
   if (g_trace_enabled) SOLAR_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.trace), g_bwd_trace));
   const long long c_ss = static_cast<long long>(H) * D;   // contiguous outputs
   int rc;
+  cudaStream_t st_dq = st;
+  int dev = -1;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (g_bwd_overlap) SOLAR_CUDA_OK(cudaStreamIsCapturing(st, &capturing));
+  if (g_bwd_overlap && capturing == cudaStreamCaptureStatusNone) {
+    if ((rc = side_stream_for_device(&dev))) return rc;
+    st_dq = g_side_stream[dev];
+    SOLAR_CUDA_OK(cudaEventRecord(g_fork_ev[dev], st));            // after the row statistics
+    SOLAR_CUDA_OK(cudaStreamWaitEvent(st_dq, g_fork_ev[dev], 0));
+  }
   {
     // dK / dV: stationary K, V (128-row boxes); streamed Q, dO (64-row boxes)
     CUtensorMap m[6];
@@ -683,7 +722,11 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
     m[5] = m[4];
     m[1] = m[4];   // the stationary-tile map is unused in dQ mode
     p.S_stat = Sq; p.S_stream = Sk;
-    rc = D == 128 ? launch_bwd<128, 1>(m, p, st) : launch_bwd<64, 1>(m, p, st);
+    rc = D == 128 ? launch_bwd<128, 1>(m, p, st_dq) : launch_bwd<64, 1>(m, p, st_dq);
+    if (st_dq != st) {                                               // join even when the launch failed
+      cudaEventRecord(g_join_ev[dev], st_dq);
+      cudaStreamWaitEvent(st, g_join_ev[dev], 0);
+    }
     if (rc) return rc;
   }
   return 0;

@@ -9,7 +9,22 @@ from .attention_native import _bshd
 from .functional import status_word
 
 
+_overlap_set = False
+
+
+def set_tail_overlap(enable: bool) -> bool:
+    """dQ kernel on a side stream so that it fills the partly empty last wave of the dK/dV kernel (matters when a
+    rank owns few heads).  Returns the previous setting."""
+    global _overlap_set
+    _overlap_set = True
+    return bool(_lib.load().solar_attn_bwd_overlap(c_int(1 if enable else 0)))
+
+
 def attn_bwd_native(q, k, v, o, lse, do, scale: float):
+    if not _overlap_set:
+        import os
+
+        set_tail_overlap(os.environ.get("SOLAR_ATTN_BWD_OVERLAP", "1") != "0")
     q, k, v, o, do = _bshd(q), _bshd(k), _bshd(v), _bshd(o), _bshd(do)
     B, Sq, H, D = q.shape
     Sk = k.shape[1]

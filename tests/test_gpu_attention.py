@@ -87,3 +87,29 @@ def test_attention_autograd_path():
     o2.backward(g.float())
     for a, b in ((q.grad, q2.grad), (k.grad, k2.grad), (v.grad, v2.grad)):
         assert ((a.float() - b).norm() / b.norm()).item() < 2e-2
+
+
+def test_attention_backward_tail_overlap_is_bit_identical_and_ordered():
+    """dQ on the side stream: same gradients as the single-stream order, and work queued right after the call on
+    the caller's stream sees all three outputs complete."""
+    import math
+
+    from solarwm_b200.ops.attention_bwd_native import attn_bwd_native, set_tail_overlap
+    from solarwm_b200.ops.attention_native import attn_fwd
+
+    q, k, v, do = (_mk(1, n, 3, 128, s) for n, s in ((1500, 31), (1300, 32), (1300, 33), (1500, 34)))
+    scale = 1.0 / math.sqrt(128)
+    o, lse = attn_fwd(q, k, v, scale)
+    previous = set_tail_overlap(False)
+    try:
+        want = [t.clone() for t in attn_bwd_native(q, k, v, o, lse, do, scale)]
+        set_tail_overlap(True)
+        for _ in range(3):
+            got = attn_bwd_native(q, k, v, o, lse, do, scale)
+            sums = [t.float().sum() for t in got]          # consumers on the caller's stream, no host sync before
+            for a, b, s in zip(got, want, sums):
+                assert torch.equal(a, b)
+                assert float(s) == float(b.float().sum())
+    finally:
+        set_tail_overlap(previous)
+    ops.check_status()
