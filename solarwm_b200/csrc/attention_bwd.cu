@@ -631,7 +631,8 @@ extern "C" int solar_attn_bwd_trace(int enable, long long* out16) {
 // on a side stream (forked after the row-statistics kernel, joined before the entry returns control of the
 // caller's stream), so its CTAs fill the SMs that the last, partly empty wave of the dK/dV kernel leaves idle.
 // It matters when a rank owns few heads (sequence parallelism): 642 + 321 CTAs on 148 SMs run as 7 waves
-// instead of 5 + 3.  Off by default for bare callers of the C entry; the framework turns it on.
+// instead of 5 + 3; it is applied only while the dK/dV grid is under 8 waves.  Off by default for bare callers of
+// the C entry; the framework turns it on.
 static int g_bwd_overlap = 0;
 namespace {
 constexpr int kMaxDev = 64;
@@ -690,8 +691,12 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
   cudaStream_t st_dq = st;
   int dev = -1;
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-  if (g_bwd_overlap) SOLAR_CUDA_OK(cudaStreamIsCapturing(st, &capturing));
-  if (g_bwd_overlap && capturing == cudaStreamCaptureStatusNone) {
+  // only when the dK/dV grid is a few waves deep: with dozens of waves the partial last one costs nothing and
+  // two co-scheduled kernels only disturb each other's L2 reuse
+  const long long stat_ctas = static_cast<long long>((Sk + ST_ROWS - 1) / ST_ROWS) * H * B;
+  const bool few_waves = stat_ctas < 8LL * sm_count();
+  if (g_bwd_overlap && few_waves) SOLAR_CUDA_OK(cudaStreamIsCapturing(st, &capturing));
+  if (g_bwd_overlap && few_waves && capturing == cudaStreamCaptureStatusNone) {
     if ((rc = side_stream_for_device(&dev))) return rc;
     st_dq = g_side_stream[dev];
     SOLAR_CUDA_OK(cudaEventRecord(g_fork_ev[dev], st));            // after the row statistics
