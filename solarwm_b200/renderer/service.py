@@ -77,3 +77,72 @@ class RenderService:
         if self.report is None:
             raise RuntimeError("RenderService.prepare() must run before render()")
         return core.render(self.model, sample, steps=self.steps, seed=seed, shift=self.shift)
+
+
+# ------------------------------------------------------------------------------------------ HTTP transport
+def make_server(service: "RenderService", samples: Mapping[str, Mapping[str, torch.Tensor]], out_dir, *,
+                host: str = "127.0.0.1", port: int = 0):
+    """Stdlib HTTP front of the service: ``GET /health`` (the prepare report), ``GET /samples`` (ids),
+    ``POST /render {"sample": id, "seed": n}`` -> renders on the serving thread under a lock (one request on the
+    device at a time), saves the latents under ``out_dir`` and answers with the file name and the latency,
+    ``GET /jobs`` (history).  Unknown samples and malformed bodies are refused with 4xx, never forwarded."""
+    import json
+    import threading
+    import time
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+    from pathlib import Path
+
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    lock, jobs = threading.Lock(), []
+
+    class Handler(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            return
+
+        def _send(self, code, payload):
+            body = json.dumps(payload).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_GET(self):
+            if self.path == "/health":
+                rep = service.report
+                return self._send(200, {"prepared": rep is not None, "steps": service.steps,
+                                        "time_sets": None if rep is None else [list(k) for k in rep["time_sets"]]})
+            if self.path == "/samples":
+                return self._send(200, sorted(samples))
+            if self.path == "/jobs":
+                return self._send(200, list(jobs))
+            self._send(404, {"error": "not found"})
+
+        def do_POST(self):
+            if self.path != "/render":
+                return self._send(404, {"error": "not found"})
+            n = int(self.headers.get("Content-Length", "0"))
+            if n > 1 << 20:
+                return self._send(413, {"error": "body too large"})
+            try:
+                body = json.loads(self.rfile.read(n) or b"{}")
+                sid, seed = str(body["sample"]), int(body.get("seed", 0))
+            except (KeyError, ValueError, TypeError, json.JSONDecodeError) as exc:
+                return self._send(400, {"error": f"bad request: {exc}"})
+            if sid not in samples:
+                return self._send(404, {"error": f"unknown sample {sid!r}"})
+            with lock:
+                t0 = time.perf_counter()
+                try:
+                    latents = service.render(samples[sid], seed=seed)
+                except Exception as exc:  # noqa: BLE001 - reported to the client, the service stays up
+                    return self._send(500, {"error": f"{type(exc).__name__}: {exc}"})
+                name = f"{sid}-seed{seed}.pt"
+                torch.save(latents.detach().cpu(), out / name)
+                job = {"sample": sid, "seed": seed, "file": name, "seconds": round(time.perf_counter() - t0, 4),
+                       "shape": list(latents.shape)}
+                jobs.append(job)
+            self._send(200, job)
+
+    return ThreadingHTTPServer((host, port), Handler)

@@ -86,3 +86,34 @@ def test_render_service_caches_reproduce_the_plain_renderer_and_refuse_unprepare
     assert model.text_cache["hits"] == 4
     with torch.no_grad(), pytest.raises(ValueError, match="not prepared"):
         render(model, s, steps=2, seed=5)                                    # a different grid of times
+
+
+def test_render_service_http_transport(tmp_path):
+    import http.client
+    import json
+    import threading
+
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.renderer.cli import _sample
+    from solarwm_b200.renderer.service import RenderService, make_server
+
+    cfg = h3_preset("tiny")
+    svc = RenderService(H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0), steps=2)
+    svc.prepare()
+    server = make_server(svc, {"s0": _sample(cfg, 0)}, tmp_path / "out")
+    threading.Thread(target=server.serve_forever, daemon=True).start()
+    try:
+        def call(method, path, body=None):
+            c = http.client.HTTPConnection("127.0.0.1", server.server_address[1], timeout=60)
+            c.request(method, path, None if body is None else json.dumps(body), {"Content-Type": "application/json"})
+            r = c.getresponse()
+            return r.status, json.loads(r.read())
+
+        assert call("GET", "/health")[1]["prepared"] is True and call("GET", "/samples")[1] == ["s0"]
+        st, job = call("POST", "/render", {"sample": "s0", "seed": 3})
+        assert st == 200 and (tmp_path / "out" / job["file"]).exists() and job["shape"] == list(_sample(cfg, 0)["shape"])
+        assert torch.equal(torch.load(tmp_path / "out" / job["file"]), svc.render(_sample(cfg, 0), seed=3).cpu())
+        assert call("POST", "/render", {"sample": "nope"})[0] == 404 and call("POST", "/render", {"seed": 1})[0] == 400
+        assert call("GET", "/jobs")[1] == [job] and call("GET", "/x")[0] == 404
+    finally:
+        server.shutdown()
