@@ -117,3 +117,36 @@ def test_render_service_http_transport(tmp_path):
         assert call("GET", "/jobs")[1] == [job] and call("GET", "/x")[0] == 404
     finally:
         server.shutdown()
+
+
+def test_node_graph_front_end_follows_the_node_protocol_and_renders():
+    from solarwm_b200 import ops
+    from solarwm_b200.models.h3 import h3_preset
+    from solarwm_b200.renderer import comfy_nodes as cn
+    from solarwm_b200.renderer.cli import _sample
+
+    assert set(cn.NODE_CLASS_MAPPINGS) == set(cn.NODE_DISPLAY_NAME_MAPPINGS)
+    for cls in cn.NODE_CLASS_MAPPINGS.values():
+        spec = cls.INPUT_TYPES()
+        assert "required" in spec and isinstance(cls.RETURN_TYPES, tuple) and hasattr(cls, cls.FUNCTION) and cls.CATEGORY == "SolarRenderer"
+    (svc,) = cn.SolarRendererModelLoader().load(architecture="tiny", steps=2, device="cpu")
+    (sig,) = cn.SolarRendererSigmas().sigmas(2)
+    assert len(sig) == 3 and float(sig[0]) == 1.0 and float(sig[-1]) == 0.0
+    from solarwm_b200.ops.attention import get_backend
+
+    before = get_backend()
+    try:
+        (svc,) = cn.SolarRendererAttention().patch(svc, "auto")
+        with pytest.raises(RuntimeError):
+            cn.SolarRendererAttention().patch(svc, "native")
+        (prompt,) = cn.SolarRendererPrompt().build("near_depth", " a harbour at dusk ")
+        assert prompt.endswith("a harbour at dusk") and "depth map" in prompt
+        with pytest.raises(ValueError):
+            cn.SolarRendererPrompt().build("custom", "x", "")
+        s = _sample(h3_preset("tiny"), 2)
+        (lat,) = cn.SolarRendererSampler().sample(svc, s, seed=1, sigmas=sig)
+        assert lat["samples"].shape == (1, *s["shape"]) and torch.isfinite(lat["samples"]).all()
+        with pytest.raises(ValueError):
+            cn.SolarRendererSampler().sample(svc, s, seed=1, sigmas=sig[:2])
+    finally:
+        ops.set_backend(before)
