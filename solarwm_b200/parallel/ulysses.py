@@ -118,7 +118,10 @@ class UlyssesCollective:
         self._layout = (B, [int(n) for n in lengths])
 
     # [B, S_local, H, D] x3 -> [B, S, H/P, D] x3 -------------------------------------------
-    def scatter_heads(self, q, k, v):
+    def scatter_heads(self, q, k, v, contiguous: bool = True):
+        """``contiguous=False`` returns strided views of the exchange buffer (unit stride on D, sequence stride
+        3 * hp * D): the attention kernels read them through their tensor maps and a cache write is one strided
+        copy, so the three packing copies are saved."""
         B, seq = self._layout
         P, r = self.size, self.rank
         Sl, H, D = q.shape[1], q.shape[2], q.shape[3]
@@ -129,6 +132,8 @@ class UlyssesCollective:
         x = torch.stack([q, k, v], 0).view(3, B, Sl, P, hp, D).permute(3, 2, 0, 1, 4, 5).reshape(P * Sl, 3, B, hp, D)
         out = _AllToAll.apply(x, [Sl] * P, list(seq), self.group)   # [S, 3, B, hp, D]
         out = out.permute(1, 2, 0, 3, 4)                            # [3, B, S, hp, D]
+        if not contiguous:
+            return out[0], out[1], out[2]
         return out[0].contiguous(), out[1].contiguous(), out[2].contiguous()
 
     # [B, S, H/P, D] -> [B, S_local, H, D] --------------------------------------------------

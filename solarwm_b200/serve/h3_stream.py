@@ -147,6 +147,7 @@ class H3StreamingGenerator:
         # static input slots (pointer-stable for graph replay)
         self._x_in = torch.zeros(self.chunk_rows, mc.latent_row_dim, dtype=dt, device=dev)
         self._t_in = torch.ones(1, dtype=torch.float32, device=dev)
+        self._t_host, self._table_cache = None, {}
         self._view_in = torch.eye(4, device=dev).repeat(self.chunk_rows, 1, 1)
         self._out = torch.zeros(self.chunk_rows, mc.latent_row_dim, dtype=dt, device=dev)
         self._video_tags = torch.full((self.chunk_rows,), TAG_VIDEO, dtype=torch.int32, device=dev)
@@ -164,7 +165,7 @@ class H3StreamingGenerator:
 
     # ------------------------------------------------------------------------------------ network
     def _evaluate(self, x_rows, t_scalar, pos, tags, view, key_base: int, n_rows: int, write_only: bool = False,
-                  key_lo: int = None, key_hi: int = None):
+                  key_lo: int = None, key_hi: int = None, tables=None):
         """Run the 50 blocks on ``n_rows`` new rows (sharded over SP) whose keys / values are written at
         cache rows ``[key_base, key_base + n_rows)`` and which attend to cache rows ``[key_lo, key_hi)``
         (default: everything from the first live row up to and including the new rows).
@@ -177,12 +178,12 @@ class H3StreamingGenerator:
         x = x_rows[loc]
         cos, sin = pos                                                   # tables of this rank's rows (device)
         cam_q, cam_kv, cam_o = self._camera_mats(view[loc])
-        temb = m.time_embed(t_scalar.view(1))
+        temb = None if tables is not None else m.time_embed(t_scalar.view(1))
         idx = (tags[loc].to(torch.int32)).contiguous()                 # one timestep group: row = 0 * 3 + tag
         kw = dict(rot_dims=mc.rot_dims, sections=mc.rope_sections, eps=mc.eps)
         S = x.shape[0]
-        for blk, kv in zip(m.blocks, self.kv):
-            table = blk.tables(temb)
+        for bi, (blk, kv) in enumerate(zip(m.blocks, self.kv)):
+            table = tables[bi] if tables is not None else blk.tables(temb)
             xm = F_.norm_modulate(x, table[:, 0], table[:, 1], mode=1, w=blk.norm1, eps=mc.eps, table=idx)
             q = ops.head_norm_rope_prope(blk.to_q(xm), blk.norm_q, cos, sin, cam_q, heads=H, **kw)
             k = ops.head_norm_rope_prope(blk.to_k(xm), blk.norm_k, cos, sin, cam_kv, heads=H, **kw)
@@ -190,9 +191,9 @@ class H3StreamingGenerator:
             q, k, v = (t.view(1, S, H, hd) for t in (q, k, v))
             if self.P > 1:
                 self.sp.set_layout_rows(1, balanced_lengths(n_rows, self.P))
-                q, k, v = self.sp.scatter_heads(q, k, v)
-            kv.k[key_base:key_base + n_rows] = k.reshape(n_rows, hl * hd)
-            kv.v[key_base:key_base + n_rows] = v.reshape(n_rows, hl * hd)
+                q, k, v = self.sp.scatter_heads(q, k, v, contiguous=False)      # strided views of the exchange buffer
+            kv.k[key_base:key_base + n_rows].view(1, n_rows, hl, hd).copy_(k)     # one strided copy each
+            kv.v[key_base:key_base + n_rows].view(1, n_rows, hl, hd).copy_(v)
             n_keys = key_hi - key_lo
             o = ops.attention(q.reshape(1, n_rows, hl, hd), kv.k[key_lo:key_hi].view(1, n_keys, hl, hd),
                               kv.v[key_lo:key_hi].view(1, n_keys, hl, hd))
@@ -241,11 +242,24 @@ class H3StreamingGenerator:
             self._pos_cache[first] = self._tables(pos, self.chunk_rows)
         x = F_.linear(self._x_in, self.model.proj_in)
         out = self._evaluate(x, self._t_in, self._pos_cache[first], self._video_tags, self._view_in, key_base=base,
-                             n_rows=self.chunk_rows)
+                             n_rows=self.chunk_rows, tables=self._step_tables())
         if self.P > 1:
             self.sp.set_layout_rows(1, balanced_lengths(self.chunk_rows, self.P))
             out = self.sp.gather_sequence(out, 1)
         self._out.copy_(out)
+
+    def _step_tables(self):
+        """Per-block adaLN tables of the current denoise level, kept per level: the schedule has ``denoise_steps``
+        + 1 distinct times, so the eager path (one launch per kernel) skips the time MLP and 50 small projection
+        GEMMs in every evaluation.  Inside a graph capture the tables are computed from the device scalar instead,
+        so that one captured graph serves every level."""
+        t = self._t_host
+        if t is None or (self.device.type == "cuda" and torch.cuda.is_current_stream_capturing()):
+            return None
+        if t not in self._table_cache:
+            temb = self.model.time_embed(torch.full((1,), t, dtype=torch.float32, device=self.device))
+            self._table_cache[t] = [blk.tables(temb) for blk in self.model.blocks]
+        return self._table_cache[t]
 
     def _slide(self) -> None:
         """Commit bookkeeping: keep the chunk just written; with a full window drop the oldest chunk and
@@ -307,6 +321,7 @@ class H3StreamingGenerator:
         for i, t in enumerate(self.times):
             self._x_in.copy_(x.to(self._x_in.dtype))
             self._t_in.fill_(float(t))
+            self._t_host = float(t)
             eval_fn()
             x0 = x + (1.0 - float(t)) * self._out.float()
             if i + 1 < len(self.times):
@@ -338,6 +353,7 @@ class H3StreamingGenerator:
         # commit: clean forward writes the chunk's keys / values, then the window advances
         self._x_in.copy_(x0.to(self._x_in.dtype))
         self._t_in.fill_(1.0)
+        self._t_host = 1.0
         (self._graphs.replay if use_graph else self._chunk_eval)()
         self._slide()
         if self.device.type == "cuda":
