@@ -269,9 +269,9 @@ class WanBlock(nn.Module):
                     self._p("self_attn.q.weight"), x, mod[:, 0], mod[:, 1])
             else:
                 qkv = self._fused_linear(xm, "self_attn.q", "self_attn.v", 3 * D)
-            q = F_.rmsnorm_rope(qkv[:, :D], self._p("self_attn.norm_q.weight").float(), rope, eps=cfg.eps)
-            k = F_.rmsnorm_rope(qkv[:, D:2 * D], self._p("self_attn.norm_k.weight").float(), rope, eps=cfg.eps)
-            v = qkv[:, 2 * D:]
+            q_raw, k_raw, v = F_.split_columns(qkv, (D, D, D))
+            q = F_.rmsnorm_rope(q_raw, self._p("self_attn.norm_q.weight").float(), rope, eps=cfg.eps)
+            k = F_.rmsnorm_rope(k_raw, self._p("self_attn.norm_k.weight").float(), rope, eps=cfg.eps)
             if camera is not None:          # PRoPE on the whole head: q <- P^T, k / v <- P^-1 (per local row)
                 from . import camera_prope
 

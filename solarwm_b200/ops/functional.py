@@ -206,6 +206,34 @@ def recompute_segment(fn, tail_weight, *args):
     return _SegmentFn.apply(fn, tail_weight, *args)
 
 
+class _SplitColumnsFn(torch.autograd.Function):
+    """Column views of a fused projection output (q | k | v).  Plain slicing would have autograd build a zero-filled
+    full-width gradient per slice and add them up; here backward is one concatenation."""
+
+    @staticmethod
+    def forward(ctx, x, *sizes):
+        outs, c0 = [], 0
+        for n in sizes:
+            outs.append(x[:, c0:c0 + n])
+            c0 += n
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        return (torch.cat(grads, dim=1),) + (None,) * len(grads)
+
+
+def split_columns(x, sizes):
+    """``x [rows, sum(sizes)]`` -> column views, with a single-pass backward."""
+    if not (torch.is_grad_enabled() and x.requires_grad):
+        outs, c0 = [], 0
+        for n in sizes:
+            outs.append(x[:, c0:c0 + n])
+            c0 += n
+        return tuple(outs)
+    return _SplitColumnsFn.apply(x, *sizes)
+
+
 class _LinearMainGradFn(torch.autograd.Function):
     """Linear whose parameter gradients are written straight into flat ``main_grad`` buffers."""
 
