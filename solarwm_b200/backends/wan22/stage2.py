@@ -29,6 +29,7 @@ import torch
 from ... import ops
 from ...engine.flow import FlowMatchScheduler
 from ...engine.optim import FlatAdamW
+from ...errors import BackendContractError
 from ...engine.sgf import sgf_kl_gradient, sgf_student_loss, should_update_student
 from ...models.wan import WanConfig, WanDiT
 from ...models.wan_causal import CausalWanRunner, allocate_kv_cache
@@ -52,6 +53,7 @@ class Stage2Options:
     min_score_t: float = 20.0
     max_score_t: float = 980.0
     checkpointing: str = "none"
+    ema_decay: Optional[float] = None      # per-role EMA: a fp32 shadow of the student, updated after each of its steps
     seed: int = 0
 
 
@@ -84,6 +86,11 @@ class WanStage2Trainer:
         self.scheduler = FlowMatchScheduler(shift=opts.timestep_shift)
         self.gen = torch.Generator(device=self.device).manual_seed(opts.seed * 100003 + 7)
         self.global_step = 0
+        self.ema_student = None
+        if opts.ema_decay is not None:
+            from ...engine.ema import ShardedEMA
+
+            self.ema_student = ShardedEMA(self.student, decay=float(opts.ema_decay), device=self.device, dtype=torch.float32)
 
     # ------------------------------------------------------------------------------------
     def _sigma(self, t):
@@ -198,6 +205,8 @@ class WanStage2Trainer:
             (loss_s / self.sp_size).backward()
             result["student"] = float(loss_s.detach())
             result["student_grad_norm"] = float(self._apply(self.student, self.opt_student))
+            if self.ema_student is not None:             # the role's own average: only student steps advance it
+                self.ema_student.update(self.student)
         # critic: flow matching on the student's sample
         x0 = out.detach().to(lat.dtype)
         u2 = torch.rand(1, generator=self.gen, device=dev)
@@ -220,7 +229,9 @@ class WanStage2Trainer:
     def role_state(self) -> Mapping[str, Any]:
         return {"student": self.student.state_dict(), "critic": self.critic.state_dict(),
                 "opt_student": self.opt_student.state_dict(), "opt_critic": self.opt_critic.state_dict(),
-                "global_step": self.global_step, "objective_gen": self.gen.get_state().cpu()}
+                "global_step": self.global_step, "objective_gen": self.gen.get_state().cpu(),
+                **({} if self.ema_student is None else {"ema_student": self.ema_student.state_dict(),
+                                                        "ema_student_updates": self.ema_student.num_updates})}
 
     def load_role_state(self, state: Mapping[str, Any]) -> None:
         self.student.load_state_dict(state["student"])
@@ -229,6 +240,10 @@ class WanStage2Trainer:
         self.opt_critic.load_state_dict(state["opt_critic"])
         self.global_step = int(state["global_step"])
         self.gen.set_state(state["objective_gen"])
+        if self.ema_student is not None:
+            if "ema_student" not in state:
+                raise BackendContractError("the checkpoint carries no student EMA but ema_decay is set")
+            self.ema_student.load_state_dict(state["ema_student"], num_updates=int(state["ema_student_updates"]))
 
 
 def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:

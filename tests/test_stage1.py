@@ -1,4 +1,5 @@
 """Teacher-forcing forward and Stage1 trainers (CPU, fp32 oracle path)."""
+import pytest
 import torch
 
 from solarwm_b200.models.wan import WanConfig, WanDiT
@@ -108,3 +109,34 @@ def test_stage2_outer_steps_and_role_state():
     tr2.load_role_state(state)
     assert tr2.global_step == 3
     assert torch.equal(tr2.student.get_parameter("blocks.0.ffn.0.weight"), tr.student.get_parameter("blocks.0.ffn.0.weight"))
+
+
+def test_stage2_student_ema_follows_student_steps_only_and_round_trips():
+    from solarwm_b200.backends.wan22.stage2 import Stage2Options, WanStage2Trainer
+    from solarwm_b200.errors import BackendContractError
+
+    cfg, _ = tiny()
+    opts = Stage2Options(chunk_frames=2, window_chunks=2, critic_updates_per_student=2, denoising_steps=(1000.0, 500.0),
+                         ema_decay=0.5, lr_student=1e-3)
+    tr = WanStage2Trainer(cfg, "cpu", opts, dtype=torch.float32)
+    for m in (tr.student, tr.teacher, tr.critic):
+        with torch.no_grad():
+            m.get_parameter("head.head.weight").normal_(0, 0.05)
+    tr.ema_student.load_state_dict({n: p.detach().float().clone() for n, p in tr.student.named_parameters()}, num_updates=0)
+    name = "blocks.0.ffn.0.weight"
+    start = tr.student.get_parameter(name).detach().clone()
+    batch = {"latents": torch.randn(1, 4, 4, 4, 4), "text": torch.randn(1, 8, 32)}
+    tr.train_outer_step(batch)
+    tr.train_outer_step(batch)
+    assert tr.ema_student.num_updates == 0                                   # critic-only steps leave the average alone
+    tr.train_outer_step(batch)
+    assert tr.ema_student.num_updates == 1
+    live = tr.student.get_parameter(name).detach()
+    assert torch.allclose(tr.ema_student.shadow[name], 0.5 * start + 0.5 * live, atol=1e-6)
+    state = tr.role_state()
+    tr2 = WanStage2Trainer(cfg, "cpu", opts, dtype=torch.float32)
+    tr2.load_role_state(state)
+    assert tr2.ema_student.num_updates == 1 and torch.equal(tr2.ema_student.shadow[name], tr.ema_student.shadow[name])
+    state.pop("ema_student")
+    with pytest.raises(BackendContractError):
+        tr2.load_role_state(state)
