@@ -3,7 +3,6 @@ inference (reference: LTX25Backend, solar/backends/ltx25/backend.py:165-487)."""
 from __future__ import annotations
 
 import io
-import json
 from typing import Any, Mapping
 
 import torch

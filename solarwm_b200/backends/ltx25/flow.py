@@ -4,7 +4,6 @@ clean as the image condition, velocity target ``noise - clean``, loss excludes f
 (reference: solar/backends/ltx25/torch_flow.py:14-118; NumPy twins in flow.py)."""
 from __future__ import annotations
 
-import math
 
 import numpy as np
 import torch

@@ -12,7 +12,6 @@ compressed container decoded by ``data.raw_video`` -- and a caption).
 """
 from __future__ import annotations
 
-import io
 from pathlib import Path
 from typing import Any, Iterator, Mapping, Tuple
 

@@ -23,8 +23,7 @@ window + own chunk) instead of a FlexAttention block mask (causal_model.py:329-4
 """
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional
 
 import torch

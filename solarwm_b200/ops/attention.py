@@ -17,7 +17,7 @@ import os
 import torch
 
 from . import _lib, reference
-from ._lib import c_float, c_int, c_ll, check, count, ptr, stream_handle
+from ._lib import count
 
 _BACKEND = os.environ.get("SOLAR_B200_ATTENTION", "native")
 

@@ -7,7 +7,6 @@ fallback on CUDA: if the native library cannot be loaded the call raises.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

@@ -29,7 +29,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
-from ..engine.optim import FlatAdamW, shard_bounds
+from ..engine.optim import FlatAdamW
 from ..ops import _lib
 from ..ops._lib import check, ptr, stream_handle
 

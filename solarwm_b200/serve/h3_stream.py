@@ -24,7 +24,7 @@ Flow convention: ``x_t = t x0 + (1 - t) n``; the network predicts ``x0 - n``; ``
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional
 
 import torch

@@ -27,7 +27,7 @@ import tempfile
 import time
 import warnings
 from pathlib import Path
-from typing import Callable, Mapping, Optional
+from typing import Callable, Mapping
 
 MAX_IMAGE_BYTES = 8 * 1024 * 1024
 MAX_PIXELS = 16_000_000

@@ -17,12 +17,11 @@ buffers); the first chunks run eagerly.  Per-chunk latency is measured with CUDA
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import torch
 
-from .. import ops
 from ..engine.flow import apply_timestep_shift
 from ..models.wan_causal import CausalWanRunner, KVCache, allocate_kv_cache
 
