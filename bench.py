@@ -204,7 +204,7 @@ def run_ours(args):
     ckpt = args.checkpointing
     if ckpt == "auto":
         ckpt = "selective" if (args.model == "ti2v_5b" and world < 4) else "none"
-    lean = args.lean == "on" or (args.lean == "auto" and ckpt == "selective")
+    lean = args.lean == "on"
     keep = args.keep_blocks
     if keep < 0:
         keep = 0
@@ -214,13 +214,19 @@ def run_ours(args):
             # one its input and the two attention outputs; 18 GB covers those plus workspace at S = 27,280
             s_local = n_tokens(cfg, args) / world
             per_block = s_local * (14.5 * cfg.dim + cfg.ffn_dim) * 2
-            if lean:        # three [S, dim] norm outputs and the [S, ffn] hidden activation are not kept
-                per_block -= s_local * (3 * cfg.dim + cfg.ffn_dim) * 2
             n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
             zero_on = world > 1 and args.zero != "off"
             fixed = (6.0 + 12.0 / (world if zero_on else 1)) * n_params  # bf16 weight + fp32 grad + fp32 master/m/v
             total = torch.cuda.get_device_properties(local).total_memory
-            keep = int(max(0.0, 0.88 * total - fixed - 18e9 / world) // per_block)
+            budget = max(0.0, 0.88 * total - fixed - 18e9 / world)
+            keep = int(budget // per_block)
+            if keep < cfg.num_layers and args.lean == "auto":
+                # not every block fits as it is: resident blocks drop three [S, dim] norm outputs and the [S, ffn]
+                # hidden activation and rebuild them in backward, which lets more (here: all) of them stay resident
+                lean = True
+            if lean:
+                per_block -= s_local * (3 * cfg.dim + cfg.ffn_dim) * 2
+                keep = int(budget // per_block)
             keep = min(keep, cfg.num_layers)
     zero = world > 1 and args.zero != "off"
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
