@@ -58,7 +58,7 @@ def parse_args():
                     help="blocks exempt from recompute under checkpointing (-1: sized from free HBM)")
     ap.add_argument("--lean", default="auto", choices=["auto", "on", "off"],
                     help="resident blocks drop their norm outputs and FFN hidden activation and rebuild them in "
-                         "backward (auto: on whenever activation memory is the constraint, i.e. with 'selective')")
+                         "backward (auto: on only when not every block would fit resident as it is)")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
     ap.add_argument("--sp-transport", default="fused", choices=["fused", "nccl"],
                     help="Ulysses exchange: fused into the kernels over NVLink peer memory, or NCCL all-to-all")
