@@ -161,6 +161,32 @@ def timed_region(steps, fn, dist, torch):
     return float(ms.item())
 
 
+def resident_block_plan(cfg, tokens, world, total_memory, *, zero_on, checkpointing, keep_blocks=-1, lean_mode="auto"):
+    """How many blocks keep their activations (the rest are recomputed under selective checkpointing) and whether
+    the resident ones run lean.  Calibrated on the 5B shape (peak_allocated with 11 / 13 / 15 / 19 resident blocks):
+    an un-checkpointed block keeps ~14.5 [S, dim] and 1 [S, ffn] bf16 tensors (the GELU output is rebuilt in
+    backward); a checkpointed one its input and the two attention outputs; 18 GB covers those plus workspace at
+    S = 27,280.  Lean blocks drop three [S, dim] norm outputs and the [S, ffn] hidden activation and rebuild them
+    in backward; ``auto`` turns that on only when not every block would fit resident as it is."""
+    lean = lean_mode == "on"
+    if keep_blocks >= 0:
+        return keep_blocks, lean
+    if checkpointing != "selective":
+        return 0, lean
+    s_local = tokens / world
+    per_block = s_local * (14.5 * cfg.dim + cfg.ffn_dim) * 2
+    n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
+    fixed = (6.0 + 12.0 / (world if zero_on else 1)) * n_params      # bf16 weight + fp32 grad + fp32 master / m / v
+    budget = max(0.0, 0.88 * total_memory - fixed - 18e9 / world)
+    keep = int(budget // per_block)
+    if keep < cfg.num_layers and lean_mode == "auto":
+        lean = True
+    if lean:
+        per_block -= s_local * (3 * cfg.dim + cfg.ffn_dim) * 2
+        keep = int(budget // per_block)
+    return min(keep, cfg.num_layers), lean
+
+
 def run_ours(args):
     import torch
 
@@ -204,30 +230,9 @@ def run_ours(args):
     ckpt = args.checkpointing
     if ckpt == "auto":
         ckpt = "selective" if (args.model == "ti2v_5b" and world < 4) else "none"
-    lean = args.lean == "on"
-    keep = args.keep_blocks
-    if keep < 0:
-        keep = 0
-        if ckpt == "selective":
-            # calibrated on this model (peak_allocated with 11 / 13 / 15 resident blocks): an un-checkpointed block
-            # keeps ~14.5 [S, dim] and 1 [S, ffn] bf16 tensors (the GELU output is rebuilt in backward); a checkpointed
-            # one its input and the two attention outputs; 18 GB covers those plus workspace at S = 27,280
-            s_local = n_tokens(cfg, args) / world
-            per_block = s_local * (14.5 * cfg.dim + cfg.ffn_dim) * 2
-            n_params = cfg.num_layers * (8 * cfg.dim * cfg.dim + 2 * cfg.dim * cfg.ffn_dim)
-            zero_on = world > 1 and args.zero != "off"
-            fixed = (6.0 + 12.0 / (world if zero_on else 1)) * n_params  # bf16 weight + fp32 grad + fp32 master/m/v
-            total = torch.cuda.get_device_properties(local).total_memory
-            budget = max(0.0, 0.88 * total - fixed - 18e9 / world)
-            keep = int(budget // per_block)
-            if keep < cfg.num_layers and args.lean == "auto":
-                # not every block fits as it is: resident blocks drop three [S, dim] norm outputs and the [S, ffn]
-                # hidden activation and rebuild them in backward, which lets more (here: all) of them stay resident
-                lean = True
-            if lean:
-                per_block -= s_local * (3 * cfg.dim + cfg.ffn_dim) * 2
-                keep = int(budget // per_block)
-            keep = min(keep, cfg.num_layers)
+    keep, lean = resident_block_plan(cfg, n_tokens(cfg, args), world, torch.cuda.get_device_properties(local).total_memory,
+                                     zero_on=world > 1 and args.zero != "off", checkpointing=ckpt,
+                                     keep_blocks=args.keep_blocks, lean_mode=args.lean)
     zero = world > 1 and args.zero != "off"
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
                            keep_blocks=keep, lean_kept=lean, max_grad_norm=1.0, seed=0, zero=zero,
