@@ -162,8 +162,11 @@ class RuntimeProvider:
         dev = self._device()
         return LTXDiT(_arch(self.config), device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32)
 
-    def preencode(self):
-        raise BackendContractError("LTX preencoding needs the official codec weights, which are not available offline")
+    def preencode(self) -> Mapping[str, Any]:
+        """Run the pre-encoding described by ``config['preencode']`` (128-channel latents, 8 x 32 x 32 geometry)."""
+        from ..wan22.preencode import run_preencode
+
+        return run_preencode(self.config, "ltx25_video", latent_channels=128, temporal_ups=(True, True, True, False, False))
 
 
 class _Adapter:

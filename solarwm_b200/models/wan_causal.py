@@ -219,13 +219,14 @@ def teacher_forcing_attention(q_clean, k_clean, v_clean, q_noisy, k_noisy, v_noi
     """
     ft = frame_tokens
     ct = chunk_frames * ft
-    n_chunks = q_clean.shape[1] // ct
+    L = q_clean.shape[1]
+    n_chunks = -(-L // ct)                       # the last chunk may hold fewer frames
     sink = sink_frames * ft
     outs_c, outs_n = [], []
     for i in range(n_chunks):
         lo = max(0, i - window_chunks) * ct
         seg = [slice(0, sink)] if (sink and lo > 0) else []
-        c_hi = (i + 1) * ct
+        c_hi = min((i + 1) * ct, L)
         ks = [k_clean[:, s] for s in seg] + [k_clean[:, lo:c_hi]]
         vs = [v_clean[:, s] for s in seg] + [v_clean[:, lo:c_hi]]
         outs_c.append(ops.attention(q_clean[:, i * ct:c_hi], torch.cat(ks, 1), torch.cat(vs, 1)))

@@ -48,3 +48,26 @@ def test_cli_errors_exit_2_and_helpers(tmp_path, monkeypatch, capsys):
     assert json.loads((tmp_path / "r.json").read_text())["schema"] == "solarwm.run.v1"
     assert main(["environment", "probe"]) == 0
     assert "native_library" in capsys.readouterr().out
+
+
+@pytest.mark.parametrize("rel,action", [
+    ("wan22_ti2v_5b/tiny_stage1_anyflow_cpu.yaml", "train"),
+    ("wan22_ti2v_5b/tiny_stage2_sgf_cpu.yaml", "train"),
+    ("wan22_ti2v_5b/tiny_preencode_cpu.yaml", "preencode"),
+    ("ltx25_video/tiny_stage0p5_cpu.yaml", "train"),
+    ("minimax_h3/tiny_stage0p5_cpu.yaml", "train"),
+    ("minimax_h3/tiny_infer_cpu.yaml", "infer"),
+])
+def test_example_configs_run_on_cpu(rel, action, tmp_path, monkeypatch):
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "out"))
+    config = str(Path(__file__).resolve().parent.parent / "configs" / rel)
+    assert main([action, "--config", config, "--set", "runtime.device=cpu"]) == 0
+    result = json.loads((tmp_path / "out" / "run-result.json").read_text())
+    assert result["schema"] == "solarwm.run-result.v1"
+
+
+def test_benchmark_shape_config_resolves_and_validates(tmp_path, monkeypatch, capsys):
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path))
+    config = str(Path(__file__).resolve().parent.parent / "configs" / "wan22_ti2v_5b" / "stage0p5_sp8.yaml")
+    assert main(["config", "resolve", "--config", config]) == 0
+    assert '"sequence_parallel_size":8' in capsys.readouterr().out

@@ -17,13 +17,14 @@ def tiny():
     return cfg, m
 
 
-def test_teacher_forcing_matches_dense_mask(monkeypatch):
+@pytest.mark.parametrize("F", [4, 5])          # 5 frames: the last chunk is ragged
+def test_teacher_forcing_matches_dense_mask(monkeypatch, F):
     cfg, m = tiny()
-    F, H, W = 4, 4, 4
+    H, W = 4, 4
     g = torch.Generator().manual_seed(0)
     clean = torch.randn(1, 4, F, H, W, generator=g)
     noisy = torch.randn(1, 4, F, H, W, generator=g)
-    t = torch.tensor([[700.0, 700.0, 300.0, 300.0]])
+    t = torch.tensor([[700.0, 700.0, 300.0, 300.0, 500.0][:F]])
     ctx = torch.randn(1, 8, 32, generator=g)
     out = wan_tf.forward_teacher_forcing(m, clean, noisy, t, ctx, chunk_frames=2, window_chunks=1)
     ft = (H // 2) * (W // 2)
