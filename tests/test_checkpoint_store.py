@@ -104,3 +104,49 @@ def test_safetensors_inventory_and_strict_load(tmp_path):
                              text_dim=32, text_len=8, freq_dim=32), device="cpu", dtype=torch.float32)
     with pytest.raises(BackendContractError):
         strict_load(other, tmp_path)
+
+
+def test_h3_released_layout_strict_mapped_load(tmp_path):
+    import pytest
+    import torch
+    from safetensors.torch import save_file
+
+    from solarwm_b200.backends.minimax_h3.loader import export_released_layout, plan_load, strict_load_mapped
+    from solarwm_b200.backends.wan22.loader import inventory
+    from solarwm_b200.errors import BackendContractError
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+
+    cfg = h3_preset("tiny")
+    cfg.lora_rank = 4
+    src = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=1)
+    released = export_released_layout(src)
+    assert "transformer_blocks.0.ffn.gate_proj.weight" in released and "token_refiner.0.attn.to_out.0.weight" in released
+    names = sorted(released)
+    half = len(names) // 2                                  # two shards, bf16 on disk
+    save_file({k: released[k].to(torch.bfloat16) for k in names[:half]}, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file({k: released[k].to(torch.bfloat16) for k in names[half:]}, str(tmp_path / "model-00002-of-00002.safetensors"))
+    dst = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=2)
+    lora_before = dst.blocks[0].to_q.lora_A.detach().clone()
+    copied = strict_load_mapped(dst, tmp_path)
+    assert sum(copied.values()) == len(names) and len(copied) == 2
+    for k, v in src.state_dict().items():
+        if "lora_" in k:
+            continue
+        assert torch.equal(dst.state_dict()[k], v.to(torch.bfloat16).to(v.dtype)), k
+    assert dst.blocks[0].norm1.dtype == torch.float32 and torch.equal(dst.blocks[0].to_q.lora_A, lora_before)   # adapters untouched
+    # refusals happen before any copy
+    entries = dict(inventory(tmp_path))
+    some = next(iter(entries.values()))
+    with pytest.raises(BackendContractError, match="match no rule"):
+        plan_load({**entries, "transformer_blocks.0.attn.rotary.weight": some}, dst)
+    entries = dict(inventory(tmp_path))
+    gone = entries.pop("transformer_blocks.1.ffn.up_proj.weight")
+    with pytest.raises(BackendContractError, match="do not tile|not in the checkpoint"):
+        plan_load(entries, dst)
+    entries["transformer_blocks.1.ffn.up_proj.weight"] = gone._replace(shape=(3, 3))
+    with pytest.raises(BackendContractError, match="do not tile"):
+        plan_load(entries, dst)
+    entries["transformer_blocks.1.ffn.up_proj.weight"] = gone
+    entries["norm_out.weight"] = entries["norm_out.weight"]._replace(shape=(7,))
+    with pytest.raises(BackendContractError, match="shape"):
+        plan_load(entries, dst)
