@@ -79,6 +79,18 @@ class MiniMaxH3Backend:
         cfg.lora_rank = int((config["model"].get("adapter", {}) or {}).get("rank", 8 if arch == "tiny" else 384))
         return cfg
 
+    @staticmethod
+    def _load_released(model, config) -> None:
+        """``model.weights_dir`` (safetensors shards in the released layout) is loaded strictly before anything runs;
+        ``model.weight_rules`` ([[pattern, target], ...]) replaces the default naming table."""
+        directory = config["model"].get("weights_dir")
+        if not directory:
+            return
+        from .loader import DEFAULT_RULES, strict_load_mapped
+
+        rules = config["model"].get("weight_rules")
+        strict_load_mapped(model, directory, DEFAULT_RULES if not rules else [tuple(r) for r in rules])
+
     def train(self, config):
         route = validate_route(config)
         if route.stage in ("stage1", "stage2"):
@@ -89,6 +101,7 @@ class MiniMaxH3Backend:
         data = config["data"]
         tr = H3Stage0p5Trainer(self._cfg(config), dev, lr=float(config["train"].get("optimizer", {}).get("lr", 1e-4)),
                                seed=int(data.get("seed", 0)))
+        self._load_released(tr.model, config)
         losses, t0 = [], time.time()
         for step in range(int(config["train"]["max_steps"])):
             s = h3_sample(latent_frames=int(data.get("latent_frames", 3)), height=int(data.get("latent_height", 8)),
@@ -177,6 +190,7 @@ class MiniMaxH3Backend:
         cfg = self._cfg(config)
         cfg.lora_rank = 0 if inf.get("merged_weights", True) else cfg.lora_rank
         model = H3DiT(cfg, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, seed=int(inf.get("seed", 0)))
+        self._load_released(model, config)
         gh, gw = (int(v) for v in inf.get("grid_hw", (4, 6)))
         k, chunks = int(inf.get("chunk_latents", 2)), int(inf.get("chunks", 2))
         use_memory = bool(inf.get("memory", False))

@@ -120,3 +120,28 @@ def test_h3_backend_infer_runs_camera_length_generation(tmp_path):
     manifest = json.loads((tmp_path / "run" / "generate" / "manifest.json").read_text())
     assert out["chunks"] == 3 and manifest["latents"] == 6 and manifest["memory"]["enabled"] is True
     assert len(manifest["chunk_seconds"]) == 3
+
+
+def test_h3_backend_infer_loads_released_weights(tmp_path):
+    import torch
+    from safetensors.torch import save_file
+
+    from solarwm_b200.backends.minimax_h3.loader import export_released_layout
+    from solarwm_b200.errors import BackendContractError
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.registry import load_backend
+
+    cfg = h3_preset("tiny")
+    weights = tmp_path / "weights"
+    weights.mkdir()
+    save_file(export_released_layout(H3DiT(cfg, device="cpu", dtype=torch.float32, seed=9)), str(weights / "model.safetensors"))
+    config = {"model": {"family": "minimax_h3", "architecture": "tiny", "camera_translation_transform": "logd4",
+                        "weights_dir": str(weights)},
+              "runtime": {"output_dir": str(tmp_path / "run"), "device": "cpu"},
+              "inference": {"source": "synthetic", "grid_hw": [2, 3], "chunk_latents": 2, "chunks": 1, "denoise_steps": 1}}
+    assert load_backend("minimax_h3").infer(config)["chunks"] == 1
+    config["model"]["weight_rules"] = [["^nothing$", "proj_in"]]
+    import pytest
+
+    with pytest.raises(BackendContractError, match="match no rule"):
+        load_backend("minimax_h3").infer(config)
