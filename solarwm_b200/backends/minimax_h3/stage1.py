@@ -66,9 +66,12 @@ def w6_mask(n_cond: int, chunk_rows: int, n_chunks: int, window_chunks: int) -> 
 
 
 def teacher_forcing_forward(model: H3DiT, *, prompt, anchor_rows, clean_rows, noisy_rows, t_chunks: torch.Tensor,
-                            grid_hw, chunk_latents: int, window_chunks: int, cameras: Optional[torch.Tensor] = None):
+                            grid_hw, chunk_latents: int, window_chunks: int, cameras: Optional[torch.Tensor] = None,
+                            capture: Optional[list] = None):
     """Rows are already patchified ([n, 96]); ``t_chunks`` [n_chunks] in [0, 1] (1 = clean).  Returns the
-    prediction for the noisy rows [L, 96]."""
+    prediction for the noisy rows [L, 96].  With ``capture`` (an empty list) every main block appends the detached
+    keys / values of the prefix rows ``[text | anchor | clean]``: under W6 those rows never see a noisy row, so
+    they are the same in every evaluation of the step and ``suffix_forward`` can reuse them."""
     h, w = grid_hw
     rows = h * w
     L = clean_rows.shape[0]
@@ -105,6 +108,8 @@ def teacher_forcing_forward(model: H3DiT, *, prompt, anchor_rows, clean_rows, no
         view = torch.cat([torch.eye(4).repeat(n_text, 1, 1), cameras[:1].float().repeat(anchor_rows.shape[0], 1, 1), per, per])
 
     def attn(q, k, v):
+        if capture is not None:
+            capture.append((k[:, :n_cond + L].detach(), v[:, :n_cond + L].detach()))
         return w6_attention(q, k, v, n_cond=n_cond, chunk_rows=chunk_rows, n_chunks=n_chunks, window_chunks=window_chunks)
 
     vid, _ = model(video_rows=torch.cat([clean_rows, noisy_rows]), text_rows=prompt, anchor_rows=anchor_rows,
@@ -113,10 +118,67 @@ def teacher_forcing_forward(model: H3DiT, *, prompt, anchor_rows, clean_rows, no
     return vid[L:]
 
 
+@torch.no_grad()
+def suffix_forward(model: H3DiT, *, captured, noisy_rows, t_chunks: torch.Tensor, n_text: int, n_anchor: int, grid_hw,
+                   chunk_latents: int, window_chunks: int, cameras: Optional[torch.Tensor] = None):
+    """The noisy half alone against captured prefix keys / values (one ``(k, v)`` pair per main block from
+    ``teacher_forcing_forward(capture=...)``): the same prediction as a full evaluation for these noisy rows, at
+    about half its cost -- the text, anchor and clean rows are not recomputed.  No-grad evaluations only (the
+    central-difference probes of the AnyFlow objective); reference: prefix-KV capture / suffix reuse,
+    solar/backends/minimax_h3/w6_attention.py:218-324."""
+    from ...models.h3 import mm_rope_tables, prope_row_matrices
+    from ...ops import functional as F_
+
+    cfg = model.cfg
+    h, w = grid_hw
+    rows = h * w
+    L = noisy_rows.shape[0]
+    F = L // rows
+    n_chunks = F // chunk_latents
+    chunk_rows = chunk_latents * rows
+    n_cond = n_text + n_anchor
+    dev = noisy_rows.device
+    if len(captured) != len(model.blocks):
+        raise ValueError("one captured (k, v) pair per main block is required")
+    uniq, inverse = torch.unique(t_chunks.detach().float().cpu(), return_inverse=True)
+    idx = (inverse.repeat_interleave(chunk_rows).to(torch.int32) * 3 + TAG_VIDEO).to(dev).contiguous()
+    ys, xs = spatial_axis(h, w), spatial_axis(w, h)
+    grid = torch.from_numpy(np.stack(np.meshgrid(ys, xs, indexing="ij"), -1).reshape(rows, 2))
+    tpos = torch.from_numpy(temporal_positions(F + 1, origin=float(n_text)))
+    pos = torch.zeros(L, 3, dtype=torch.float64)
+    pos[:, 0] = tpos[1:].to(torch.float64).repeat_interleave(rows)
+    pos[:, 1:] = grid.repeat(F, 1)
+    cos, sin = mm_rope_tables(pos.to(dev), cfg.rot_dims, cfg.rope_sections)
+    cam_q = cam_kv = cam_o = None
+    if cameras is not None:
+        cam_q, cam_kv, cam_o = prope_row_matrices(cameras[1:].float().repeat_interleave(rows, dim=0).to(dev), 0.505, 0.898)
+    temb = model.time_embed(uniq.to(dev))
+    layer = [0]
+
+    def attn(q, k, v):
+        pk, pv = captured[layer[0]]
+        layer[0] += 1
+        outs = []
+        for i in range(n_chunks):
+            lo = n_cond + max(0, i - window_chunks) * chunk_rows
+            hi = n_cond + i * chunk_rows                                   # clean chunks lo .. i-1
+            own = slice(i * chunk_rows, (i + 1) * chunk_rows)
+            kk = torch.cat([pk[:, :n_cond], pk[:, lo:hi], k[:, own]], 1)
+            vv = torch.cat([pv[:, :n_cond], pv[:, lo:hi], v[:, own]], 1)
+            outs.append(ops.attention(q[:, own], kk, vv))
+        return torch.cat(outs, 1)
+
+    x = F_.linear(noisy_rows.to(model.dtype), model.proj_in)
+    for blk in model.blocks:
+        x = blk(x, blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o, attn_fn=attn)
+    return F_.linear(F_.norm_modulate(x, mode=1, w=model.norm_out, eps=cfg.eps), model.proj_out)
+
+
 class H3Stage1Trainer:
     def __init__(self, cfg, device, *, objective: str = "tf_fm", chunk_latents: int = 5, window_chunks: int = 5,
                  lr: float = 1e-4, seed: int = 0, diffusion_ratio: float = 0.5, consistency_ratio: float = 0.25,
-                 epsilon: float = 0.005):
+                 epsilon: float = 0.005, reuse_prefix: bool = True):
+        self.reuse_prefix = bool(reuse_prefix)     # AnyFlow probes reuse the trainable evaluation's prefix K / V
         dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
         self.model = H3DiT(cfg, device=device, dtype=dtype, seed=seed)
         self.opt = FP32MasterAdamW(self.model.trainable_parameters(), lr=lr)
@@ -125,7 +187,7 @@ class H3Stage1Trainer:
         self.objective, self.chunk_latents, self.window_chunks = objective, chunk_latents, window_chunks
         self.ratios, self.epsilon = (diffusion_ratio, consistency_ratio), float(epsilon)
 
-    def _predict(self, sample, lat, noise, t_chunks):
+    def _predict(self, sample, lat, noise, t_chunks, capture=None, captured=None):
         dev, dt = self.device, self.model.dtype
         C, F, H, W = lat.shape
         rows = (H // 2) * (W // 2)
@@ -133,8 +195,13 @@ class H3Stage1Trainer:
         clean = patchify_latents(lat).to(dt)
         noisy = (t_rows * clean.float() + (1.0 - t_rows) * patchify_latents(noise).float()).to(dt)
         anchor = sample["anchor_latents"].to(dev)
+        if captured is not None:                   # probe: the noisy half against the captured prefix
+            return suffix_forward(self.model, captured=captured, noisy_rows=noisy, t_chunks=t_chunks,
+                                  n_text=sample["prompt_embeds"].shape[0], n_anchor=patchify_latents(anchor).shape[0],
+                                  grid_hw=(H // 2, W // 2), chunk_latents=self.chunk_latents,
+                                  window_chunks=self.window_chunks, cameras=sample.get("camera_w2c"))
         a_noise = torch.randn(anchor.shape, generator=self.gen, device=dev, dtype=torch.float32).to(anchor.dtype)
-        return teacher_forcing_forward(self.model, prompt=sample["prompt_embeds"].to(dev, dt),
+        return teacher_forcing_forward(self.model, capture=capture, prompt=sample["prompt_embeds"].to(dev, dt),
                                        anchor_rows=patchify_latents(flow.interpolate(anchor, a_noise, 0.999)).to(dt),
                                        clean_rows=clean, noisy_rows=noisy, t_chunks=t_chunks, grid_hw=(H // 2, W // 2),
                                        chunk_latents=self.chunk_latents, window_chunks=self.window_chunks,
@@ -161,13 +228,15 @@ class H3Stage1Trainer:
                                          generator=self.gen, device=dev)
             s = flow.shifted_sigma(pairs.t, flow.VIDEO_SHIFT)
             r = flow.shifted_sigma(pairs.r, flow.VIDEO_SHIFT)
-            u_pred = -self._predict(sample, lat, noise, 1.0 - s).float()
+            need_probes = bool((~pairs.is_diffusion).any())
+            prefix = [] if (self.reuse_prefix and need_probes) else None
+            u_pred = -self._predict(sample, lat, noise, 1.0 - s, capture=prefix).float()
             s_p, s_m = (s + self.epsilon).clamp(max=1.0), torch.maximum(s - self.epsilon, r)
             du = torch.zeros_like(u_pred)
-            if bool((~pairs.is_diffusion).any()):
+            if need_probes:
                 with torch.no_grad():
-                    up = -self._predict(sample, lat, noise, 1.0 - s_p).float()
-                    um = -self._predict(sample, lat, noise, 1.0 - s_m).float()
+                    up = -self._predict(sample, lat, noise, 1.0 - s_p, captured=prefix).float()
+                    um = -self._predict(sample, lat, noise, 1.0 - s_m, captured=prefix).float()
                     width = (s_p - s_m).clamp_min(1e-6).repeat_interleave(self.chunk_latents * rows).view(-1, 1)
                     du = (up - um) / width
             span = (s - r).repeat_interleave(self.chunk_latents * rows).view(-1, 1)

@@ -145,3 +145,48 @@ def test_h3_backend_infer_loads_released_weights(tmp_path):
 
     with pytest.raises(BackendContractError, match="match no rule"):
         load_backend("minimax_h3").infer(config)
+
+
+def test_suffix_forward_on_captured_prefix_matches_the_full_evaluation():
+    """AnyFlow probes: the noisy half evaluated against the captured prefix K / V equals the noisy half of a full
+    teacher-forcing evaluation, at other noise levels than the capturing evaluation used; and a trainer with the
+    reuse on takes the same step as one with it off."""
+    from solarwm_b200.backends.minimax_h3.layout import patchify_latents
+    from solarwm_b200.backends.minimax_h3.stage1 import suffix_forward, teacher_forcing_forward
+    from solarwm_b200.models.h3 import H3DiT
+
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    s = h3_sample(latent_frames=4, height=4, width=4, prompt_len=6, text_dim=cfg.text_dim, seed=1)
+    cams = torch.eye(4).repeat(5, 1, 1)
+    cams[1:, 0, 3] = torch.arange(4) * 0.1
+    g = torch.Generator().manual_seed(0)
+    clean = patchify_latents(s["target_latents"]).float()
+    anchor = patchify_latents(s["anchor_latents"]).float()
+    kw = dict(grid_hw=(2, 2), chunk_latents=2, window_chunks=1, cameras=cams)
+
+    def noisy_at(t):
+        return clean * 0.5 + torch.randn(clean.shape, generator=torch.Generator().manual_seed(int(t[0] * 1000)))
+
+    t0, t1 = torch.tensor([0.3, 0.7]), torch.tensor([0.35, 0.65])
+    with torch.no_grad():
+        prefix = []
+        teacher_forcing_forward(model, prompt=s["prompt_embeds"].float(), anchor_rows=anchor, clean_rows=clean,
+                                noisy_rows=noisy_at(t0), t_chunks=t0, capture=prefix, **kw)
+        assert len(prefix) == len(model.blocks) and prefix[0][0].shape[1] == 6 + anchor.shape[0] + clean.shape[0]
+        want = teacher_forcing_forward(model, prompt=s["prompt_embeds"].float(), anchor_rows=anchor, clean_rows=clean,
+                                       noisy_rows=noisy_at(t1), t_chunks=t1, **kw)
+        got = suffix_forward(model, captured=prefix, noisy_rows=noisy_at(t1), t_chunks=t1, n_text=6, n_anchor=anchor.shape[0], **kw)
+    assert got.shape == want.shape and torch.allclose(got, want, atol=2e-5, rtol=1e-4)
+    cfg.lora_rank = 4
+    losses = []
+    for reuse in (False, True):
+        tr = H3Stage1Trainer(cfg, "cpu", objective="anyflow", chunk_latents=2, window_chunks=1, lr=1e-3,
+                             diffusion_ratio=0.0, consistency_ratio=0.5, seed=3, reuse_prefix=reuse)
+        for p in tr.model.trainable_parameters():
+            torch.nn.init.normal_(p, std=0.02, generator=torch.Generator().manual_seed(p.numel()))
+        batch = dict(s, camera_w2c=cams)
+        losses.append(float(tr.train_step(batch)))
+    # without reuse every probe re-noises the anchor frame on its own, so the two steps agree closely, not bitwise
+    assert abs(losses[0] - losses[1]) < 1e-3 * max(1.0, abs(losses[0]))
+    del g
