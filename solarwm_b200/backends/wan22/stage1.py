@@ -22,7 +22,7 @@ import torch
 from ... import ops
 from ...engine import anyflow as af
 from ...engine.flow import logit_normal_sigmas
-from ...models.wan_tf import forward_teacher_forcing
+from ...models.wan_tf import forward_noisy_suffix, forward_teacher_forcing
 from .stage0p5 import Stage0p5Options, WanStage0p5Trainer
 
 
@@ -37,6 +37,7 @@ class Stage1Options(Stage0p5Options):
     difference_epsilon: float = 5.0
     dp_rank: int = 0
     dp_world: int = 1
+    reuse_prefix: bool = True           # AnyFlow probes reuse the clean half's keys / values of the trainable pass
 
 
 class WanStage1Trainer(WanStage0p5Trainer):
@@ -54,11 +55,14 @@ class WanStage1Trainer(WanStage0p5Trainer):
         x_t, target = ops.add_noise(latents[0], noise[0], sigma)
         return x_t.unsqueeze(0), target.unsqueeze(0)
 
-    def _predict(self, clean, x_t, t, text, r=None):
+    def _predict(self, clean, x_t, t, text, r=None, capture=None, captured=None):
         o = self.opts
-        pred = forward_teacher_forcing(self.model, clean.permute(0, 2, 1, 3, 4), x_t.permute(0, 2, 1, 3, 4), t, text,
-                                       r=r, chunk_frames=o.chunk_frames, window_chunks=o.window_chunks,
-                                       sink_frames=o.sink_frames)
+        kw = dict(r=r, chunk_frames=o.chunk_frames, window_chunks=o.window_chunks, sink_frames=o.sink_frames)
+        if captured is not None:                                # probe: the noisy half against the captured clean half
+            pred = forward_noisy_suffix(self.model, x_t.permute(0, 2, 1, 3, 4), t, text, captured, **kw)
+        else:
+            pred = forward_teacher_forcing(self.model, clean.permute(0, 2, 1, 3, 4), x_t.permute(0, 2, 1, 3, 4), t, text,
+                                           capture=capture, **kw)
         return pred.permute(0, 2, 1, 3, 4)                      # [1, F, C, H, W]
 
     def microbatch(self, latents: torch.Tensor, text: torch.Tensor, y: Optional[torch.Tensor] = None):
@@ -100,17 +104,24 @@ class WanStage1Trainer(WanStage0p5Trainer):
             self.sp.broadcast_(t_c, r_c, noise)
         t, r = self._per_chunk(t_c, F), self._per_chunk(r_c, F)
         x_t, target = self._noised(latents, noise, t)
-        u = self._predict(latents, x_t, t, text, r=r)
+        need = ~pairs.is_diffusion                                  # diffusion samples (r = t) have no du/dt term
+        probes = bool(need.any())
+        if self.sp is not None and self.sp.size > 1:                # SP peers take the same branch
+            flag = torch.tensor([float(probes)], device=self.device)
+            self.sp.broadcast_(flag)
+            probes = bool(flag.item())
+        # the clean half is the same in the trainable evaluation and in both probes: its keys / values are kept
+        prefix = [] if (probes and o.reuse_prefix) else None
+        u = self._predict(latents, x_t, t, text, r=r, capture=prefix)
         # central difference along the interpolation path x(t') = (1 - s') x0 + s' n, s' = t' / N
         tp_c, tm_c = af.difference_window(t_c, r_c, epsilon=o.difference_epsilon, num_train_timesteps=N)
-        need = ~pairs.is_diffusion                                  # diffusion samples (r = t) have no du/dt term
-        if bool(need.any()):
+        if probes:
             with torch.no_grad():
                 tp, tm = self._per_chunk(tp_c, F), self._per_chunk(tm_c, F)
                 x_p, _ = self._noised(latents, noise, tp)
                 x_m, _ = self._noised(latents, noise, tm)
-                u_p = self._predict(latents, x_p, tp, text, r=r)
-                u_m = self._predict(latents, x_m, tm, text, r=r)
+                u_p = self._predict(latents, x_p, tp, text, r=r, captured=prefix)
+                u_m = self._predict(latents, x_m, tm, text, r=r, captured=prefix)
                 du = af.central_difference(u_p[0], u_m[0], tp.reshape(F) / N, tm.reshape(F) / N)
         else:
             du = torch.zeros_like(u[0], dtype=torch.float32)

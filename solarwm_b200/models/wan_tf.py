@@ -89,9 +89,12 @@ def _embed(model: WanDiT, x):
 
 
 def forward_teacher_forcing(model: WanDiT, clean, noisy, t, context, *, r: Optional[torch.Tensor] = None,
-                            chunk_frames: int = 3, window_chunks: int = 6, sink_frames: int = 0):
+                            chunk_frames: int = 3, window_chunks: int = 6, sink_frames: int = 0,
+                            capture: Optional[list] = None):
     """clean / noisy [1, C, F, H, W]; t (and r) [1, F] on the 1000-step grid; returns the prediction
-    for the noisy half [1, C_out, F, H, W]."""
+    for the noisy half [1, C_out, F, H, W].  With ``capture`` (an empty list) every block appends the detached
+    keys / values of the clean half (this rank's heads): clean rows never see a noisy row, so they are the same in
+    every evaluation of a step and ``forward_noisy_suffix`` can reuse them."""
     if clean.shape[0] != 1:
         raise ValueError("teacher forcing packs one video per call")
     tok_c, grid = _embed(model, clean)
@@ -105,12 +108,48 @@ def forward_teacher_forcing(model: WanDiT, clean, noisy, t, context, *, r: Optio
 
     def attn(q, k, v):
         L = f * ft
+        if capture is not None and len(capture) < len(model.blocks):      # a checkpoint recompute must not append again
+            capture.append((k[:, :L].detach(), v[:, :L].detach()))
         oc, on = teacher_forcing_attention(q[:, :L], k[:, :L], v[:, :L], q[:, L:], k[:, L:], v[:, L:],
                                            frame_tokens=ft, chunk_frames=chunk_frames,
                                            window_chunks=window_chunks, sink_frames=sink_frames)
         return torch.cat([oc, on], 1)
 
     return _run(model, torch.cat([tok_c, tok_n], 0), t_all, r_all, context, pos, (h, w), attn, (f, 2 * f))
+
+
+@torch.no_grad()
+def forward_noisy_suffix(model: WanDiT, noisy, t, context, captured, *, r: Optional[torch.Tensor] = None,
+                         chunk_frames: int = 3, window_chunks: int = 6, sink_frames: int = 0):
+    """The noisy half alone against the clean keys / values captured by ``forward_teacher_forcing(capture=...)``:
+    the same prediction as the full teacher-forcing evaluation gives for these noisy frames, without recomputing
+    the clean half (about half the cost).  For the no-grad central-difference probes of the AnyFlow objective
+    (reference: prefix-KV capture / suffix reuse, solar/backends/minimax_h3/w6_attention.py:218-324, applied here to
+    the Wan teacher-forcing mask)."""
+    if len(captured) != len(model.blocks):
+        raise ValueError("one captured (k, v) pair per block is required")
+    tok_n, grid = _embed(model, noisy)
+    f, h, w = grid
+    ft = h * w
+    ct = chunk_frames * ft
+    L = f * ft
+    sink = sink_frames * ft
+    layer = [0]
+
+    def attn(q, k, v):
+        ck, cv = captured[layer[0]]
+        layer[0] += 1
+        outs = []
+        for i in range(-(-L // ct)):
+            lo = max(0, i - window_chunks) * ct
+            hi = min((i + 1) * ct, L)
+            seg = [slice(0, sink)] if (sink and lo > 0) else []
+            kk = [ck[:, s] for s in seg] + [ck[:, lo:i * ct], k[:, i * ct:hi]]
+            vv = [cv[:, s] for s in seg] + [cv[:, lo:i * ct], v[:, i * ct:hi]]
+            outs.append(ops.attention(q[:, i * ct:hi], torch.cat(kk, 1), torch.cat(vv, 1)))
+        return torch.cat(outs, 1)
+
+    return _run(model, tok_n, t, r, context, torch.arange(f), (h, w), attn, (0, f))
 
 
 def forward_window(model: WanDiT, frames, t, context, *, first_frame: int, current_frames: int,

@@ -141,3 +141,42 @@ def test_stage2_student_ema_follows_student_steps_only_and_round_trips():
     state.pop("ema_student")
     with pytest.raises(BackendContractError):
         tr2.load_role_state(state)
+
+
+@pytest.mark.parametrize("F,sink", [(4, 0), (5, 1)])
+def test_noisy_suffix_on_captured_clean_half_matches_full_teacher_forcing(F, sink):
+    cfg, m = tiny()
+    g = torch.Generator().manual_seed(0)
+    clean = torch.randn(1, 4, F, 4, 4, generator=g)
+    ctx = torch.randn(1, 8, 32, generator=g)
+    kw = dict(chunk_frames=2, window_chunks=1, sink_frames=sink)
+    t0 = torch.tensor([[700.0, 700.0, 300.0, 300.0, 500.0][:F]])
+    t1 = t0 + 5.0
+    with torch.no_grad():
+        prefix = []
+        wan_tf.forward_teacher_forcing(m, clean, torch.randn(1, 4, F, 4, 4, generator=g), t0, ctx, capture=prefix, **kw)
+        assert len(prefix) == len(m.blocks) and prefix[0][0].shape[1] == F * 4
+        noisy = torch.randn(1, 4, F, 4, 4, generator=g)
+        want = wan_tf.forward_teacher_forcing(m, clean, noisy, t1, ctx, **kw)
+        got = wan_tf.forward_noisy_suffix(m, noisy, t1, ctx, prefix, **kw)
+    assert got.shape == want.shape and torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+
+
+def test_stage1_anyflow_step_with_and_without_prefix_reuse_agree():
+    from solarwm_b200.backends.wan22.stage1 import Stage1Options, WanStage1Trainer
+
+    cfg, _ = tiny()
+    cfg.flow_objective = "anyflow_forward_map"
+    losses, grads = [], []
+    for reuse in (False, True):
+        opts = Stage1Options(objective="anyflow", chunk_frames=2, window_chunks=1, diffusion_ratio=0.0, consistency_ratio=0.5,
+                             seed=5, reuse_prefix=reuse)
+        tr = WanStage1Trainer(cfg, "cpu", opts, dtype=torch.float32)
+        with torch.no_grad():
+            tr.model.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator().manual_seed(1))
+        lat = torch.randn(1, 4, 4, 4, 4, generator=torch.Generator().manual_seed(2))
+        text = torch.randn(1, 8, 32, generator=torch.Generator().manual_seed(3))
+        losses.append(float(tr.microbatch(lat, text)))
+        grads.append(tr.model.get_parameter("blocks.0.ffn.0.weight").grad.clone())
+    assert abs(losses[0] - losses[1]) < 1e-5 * max(1.0, abs(losses[0]))
+    assert torch.allclose(grads[0], grads[1], atol=1e-6, rtol=1e-4)
