@@ -46,6 +46,26 @@ def _receipt(out_dir: Path, name: str, payload: dict) -> None:
     (out_dir / name).write_text(json.dumps(payload, sort_keys=True))
 
 
+def _decode_backends(args, cfg, dev, dtype, rank):
+    """The decoder switch of the worker: ``conv`` = causal-conv VAE, ``vit`` = streaming ViT decoder (small random
+    instances sized to the model's latent channels; a deployment loads its released decoder instead)."""
+    if args.decoder == "none":
+        return None
+    from ..models.vae import StreamingDecoder, VAEConfig, VideoVAE
+    from ..models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+    from .decode_backends import DecodeBackends
+
+    def conv():
+        vae = VideoVAE(VAEConfig(z_dim=cfg.out_dim, base=16, temporal_ups=(True, False))).to(dev, dtype).eval()
+        return StreamingDecoder(vae)
+
+    def vit():
+        vcfg = ViTDecoderConfig(latent_channels=cfg.out_dim, dim=128, depth=2, heads=2, dim_head=64, ffn_dim=256, patch=4)
+        return StreamingViTDecoder(ViTVideoDecoder(vcfg, device=dev, dtype=dtype, seed=0), (args.height, args.width))
+
+    return DecodeBackends({"conv": conv, "vit": vit}, rank=rank)
+
+
 def run(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     out_dir = Path(args.output)
@@ -67,6 +87,29 @@ def run(args) -> int:
 
             server = make_server(state, nav, port=args.port)
             serve_in_thread(server)
+        decoders, decoded = _decode_backends(args, cfg, dev, dtype, rank), {"frames": 0}
+        sink = None
+        if decoders is not None:
+            decoders.start(args.decoder)
+
+        def decode(index, latents):
+            """latents [1, C, f, H, W] -> pixel pieces on rank 0; returns the milliseconds spent."""
+            nonlocal sink
+            if decoders is None:
+                return 0.0
+
+            def on_piece(_chunk, _offset, frames, _ns):
+                nonlocal sink
+                if sink is None:
+                    from .media import FrameSink
+
+                    sink = FrameSink(out_dir / "frames", frames.shape[-1], frames.shape[-2], use_ffmpeg=False)
+                for f in range(frames.shape[1]):
+                    sink.push(frames[:, f].float().clamp(-1, 1) * 0.5 + 0.5 if args.decoder == "conv" else frames[:, f].float())
+                    decoded["frames"] += 1
+
+            return decoders.push(index, latents[0].contiguous(), on_piece)
+
         g = torch.Generator().manual_seed(0)
         context = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(dtype)
         state.set_phase("preparing")
@@ -75,13 +118,15 @@ def run(args) -> int:
         if args.smoke:
             nav.set_key("w", True)
             for i in range(args.chunks):
-                _, st = engine.generate()
-                state.generated(st.index, st.dit_ms, 0.0)
+                lat, st = engine.generate()
+                state.generated(st.index, st.dit_ms, decode(i, lat))
             steady = [c["dit_ms"] for c in state.chunks if engine.generator.stats[c["index"]].graph] or \
                      [c["dit_ms"] for c in state.chunks[1:]]
             report = {"chunks": args.chunks, "chunk_frames": args.chunk_frames,
                       "median_chunk_ms": sorted(steady)[len(steady) // 2] if steady else None,
-                      "graph_chunks": sum(1 for s in engine.generator.stats if s.graph)}
+                      "graph_chunks": sum(1 for s in engine.generator.stats if s.graph),
+                      "decoder": args.decoder, "decoded_frames": decoded["frames"],
+                      "median_decode_ms": sorted(c["vae_ms"] for c in state.chunks)[len(state.chunks) // 2] if state.chunks else None}
             if rank == 0:
                 print(json.dumps(report))
         else:
@@ -94,10 +139,15 @@ def run(args) -> int:
                 elif cmd["op"] == "start":
                     state.set_phase("running")
                 elif cmd["op"] == "chunk" and state.phase == "running":
-                    _, st = engine.generate()
-                    state.generated(st.index, st.dit_ms, 0.0)
+                    lat, st = engine.generate()
+                    state.generated(st.index, st.dit_ms, decode(len(state.chunks), lat))
         if server is not None:
             server.shutdown()
+        if sink is not None:
+            sink.close()
+        if decoders is not None:
+            decoders.finish()
+            decoders.close()
         _receipt(out_dir, f"exit-rank{rank}.json", {"rank": rank, "status": "ok", "chunks": len(state.chunks), "time": time.time()})
         return 0
     except Exception as exc:  # noqa: BLE001
@@ -119,6 +169,8 @@ def main(argv=None) -> int:
     ap.add_argument("--smoke", action="store_true")
     ap.add_argument("--serve", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--decoder", default="none", choices=["none", "conv", "vit"],
+                    help="decode every generated chunk to pixel frames through the decoder switch")
     return run(ap.parse_args(argv))
 
 

@@ -190,3 +190,19 @@ def test_scene_upload_validation_and_isolated_preparation(tmp_path):
     with pytest.raises(TimeoutError):
         si.prepare_isolated(tmp_path, {"callable": "time:sleep", "args": [31]}, timeout_s=0.3)
     assert time.monotonic() - t0 < 20
+
+
+def test_worker_decodes_chunks_through_the_decoder_switch(tmp_path, capsys):
+    import pytest
+
+    from solarwm_b200.serve.worker import main
+
+    for kind in ("vit", "conv"):
+        out = tmp_path / kind
+        assert main(["--smoke", "--model", "tiny", "--height", "8", "--width", "8", "--chunk-frames", "1", "--window-frames", "3",
+                     "--chunks", "3", "--decoder", kind, "--output", str(out)]) == 0
+        report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert report["decoder"] == kind and report["decoded_frames"] >= 3 and report["median_decode_ms"] > 0
+        assert (out / "frames" / "video.rgb").stat().st_size > 0
+    with pytest.raises(SystemExit):
+        main(["--smoke", "--decoder", "nope"])
