@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--lean", default="auto", choices=["auto", "on", "off"],
                     help="resident blocks drop their norm outputs and FFN hidden activation and rebuild them in "
                          "backward (auto: on only when not every block would fit resident as it is)")
+    ap.add_argument("--phase-times", action="store_true",
+                    help="after the timed region, run one more step under the phase timer and add the forward / "
+                         "backward / optimizer split (CUDA events) to the JSON line")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
     ap.add_argument("--sp-transport", default="fused", choices=["fused", "nccl"],
                     help="Ulysses exchange: fused into the kernels over NVLink peer memory, or NCCL all-to-all")
@@ -275,6 +278,14 @@ def run_ours(args):
     counters = dict(ops.COUNTERS)
     ms_e2e = timed_region(args.steps, step_e2e, dist, torch)
     clocks = sampler.stop()
+    phases = None
+    if args.phase_times:
+        from solarwm_b200.utils.trace import PhaseTimer
+
+        timer = PhaseTimer(f"cuda:{local}")
+        with timer.installed():
+            step_device()
+        phases = {k: v["total_ms"] for k, v in timer.summary().items() if not k.startswith("block.")}
     ops.check_status(f"cuda:{local}")
     peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
@@ -301,6 +312,7 @@ def run_ours(args):
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "launch_counters": counters, "host_enqueue_ms_per_step": host_ms,
+            **({"phase_ms": phases} if phases is not None else {}),
             "final_loss": losses[-1] if losses else None,
         }
         print(json.dumps(out))

@@ -21,6 +21,7 @@ from ... import ops
 from ...engine.flow import FlowMatchScheduler, first_frame_loss_mask, logit_normal_sigmas
 from ...engine.optim import FlatAdamW
 from ...models.wan import WanConfig, WanDiT
+from ...utils.trace import span
 
 
 @dataclass
@@ -103,15 +104,21 @@ class WanStage0p5Trainer:
                                     noise.reshape(B * F, *latents.shape[2:]), sigma)
         x_in = x_t.view(B, F, *latents.shape[2:]).permute(0, 2, 1, 3, 4)
         y_in = None if y is None else y.permute(0, 2, 1, 3, 4)
-        pred = self.model(x_in, t, text, y=y_in)                       # [B, C, F, H, W]
-        pred = pred.permute(0, 2, 1, 3, 4).reshape(B * F, *pred.shape[1:2], *pred.shape[3:]).contiguous()
-        weight = self.scheduler.training_weight(t_video).view(B, 1).expand(B, F).reshape(B * F)
-        loss = ops.weighted_masked_mse(pred, target[:, :pred.shape[1]], weight.float(),
-                                       mask.reshape(B * F).float())
-        (loss / (o.grad_accum * self.sp_size * self.dp_size)).backward()
+        with span("forward"):
+            pred = self.model(x_in, t, text, y=y_in)                       # [B, C, F, H, W]
+            pred = pred.permute(0, 2, 1, 3, 4).reshape(B * F, *pred.shape[1:2], *pred.shape[3:]).contiguous()
+            weight = self.scheduler.training_weight(t_video).view(B, 1).expand(B, F).reshape(B * F)
+            loss = ops.weighted_masked_mse(pred, target[:, :pred.shape[1]], weight.float(),
+                                           mask.reshape(B * F).float())
+        with span("backward"):
+            (loss / (o.grad_accum * self.sp_size * self.dp_size)).backward()
         return loss.detach()
 
     def optimizer_step(self) -> torch.Tensor:
+        with span("optimizer"):
+            return self._optimizer_step()
+
+    def _optimizer_step(self) -> torch.Tensor:
         self.model.finalize_grads()
         opt = self.optimizer
         if hasattr(opt, "sharded_step"):

@@ -30,6 +30,7 @@ import torch.nn as nn
 from .. import ops
 from ..ops import functional as F_
 from ..parallel.flat import FlatUnit
+from ..utils.trace import span
 
 
 @dataclass
@@ -478,6 +479,10 @@ class WanDiT(nn.Module):
         carried across the recompute (the reference's saved-attention policy,
         solar/backends/minimax_h3/fsdp.py:146-165).  The last ``keep_blocks`` blocks are exempt: with
         memory to spare their activations stay resident and their recompute is saved."""
+        with span(f"block.{index:02d}"):
+            return self._run_block_inner(block, x, e0, rope, ctx, kw, index)
+
+    def _run_block_inner(self, block, x, e0, rope, ctx, kw, index):
         exempt = index >= len(self.blocks) - int(self.keep_blocks)
         if self.checkpointing in ("full", "selective") and torch.is_grad_enabled() and not exempt:
             from torch.utils.checkpoint import checkpoint
