@@ -41,6 +41,50 @@ class Engine:
         return latents, self.generator.stats[-1]
 
 
+class H3Engine:
+    """The same contract on the H3-shaped block-causal model: resident ``H3DiT`` + ``H3StreamingGenerator``; the
+    navigation poses of a chunk become first-frame-relative world-to-camera matrices of its latents
+    (reference: deploy/solar_wm/backends/standard/runtime/engine.py)."""
+
+    class _Stat:
+        def __init__(self, index, dit_ms, graph):
+            self.index, self.dit_ms, self.graph = index, dit_ms, graph
+
+    class _Cfg:
+        def __init__(self, chunk_frames):
+            self.chunk_frames = chunk_frames
+
+    class _Gen:
+        def __init__(self, cfg):
+            self.cfg, self.stats = cfg, []
+
+    def __init__(self, model, stream_cfg, navigation: NavigationState):
+        from .h3_stream import H3StreamingGenerator
+
+        self.h3 = H3StreamingGenerator(model, stream_cfg)
+        self.navigation = navigation
+        self.generator = H3Engine._Gen(H3Engine._Cfg(stream_cfg.chunk_latents))
+        self.cameras = []
+        self._first_w2c = None
+
+    def start(self, text, anchor_latent):
+        self.h3.start(text, anchor_latent, torch.eye(4))
+
+    def generate(self):
+        import numpy as np
+
+        c2w = self.navigation.advance(self.h3.cfg.chunk_latents)
+        self.cameras.append(c2w)
+        w2c = torch.from_numpy(np.linalg.inv(c2w.astype(np.float64))).float()
+        if self._first_w2c is None:                       # the session's first pose is the reference frame
+            self._first_w2c = torch.eye(4)
+        latents = self.h3.next_chunk(w2c @ torch.linalg.inv(self._first_w2c))
+        t = self.h3.timings[-1]
+        st = H3Engine._Stat(t.index, t.dit_ms, t.graph)
+        self.generator.stats.append(st)
+        return latents.unsqueeze(0), st
+
+
 def _receipt(out_dir: Path, name: str, payload: dict) -> None:
     out_dir.mkdir(parents=True, exist_ok=True)
     (out_dir / name).write_text(json.dumps(payload, sort_keys=True))
@@ -72,6 +116,8 @@ def run(args) -> int:
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if torch.cuda.is_available() else torch.device("cpu")
     state, nav = SessionState(), NavigationState()
     try:
+        if args.family == "h3":
+            return _run_h3(args, rank, out_dir, dev, state, nav)
         cfg = wan_preset(args.model) if args.model != "small" else WanConfig(
             model_type="ti2v", in_dim=48, out_dim=48, dim=512, ffn_dim=2048, num_heads=4, num_layers=4,
             text_dim=4096, text_len=512)
@@ -156,8 +202,67 @@ def run(args) -> int:
         raise
 
 
+def _run_h3(args, rank, out_dir, dev, state, nav) -> int:
+    """Smoke / command loop of the H3-shaped engine (``--family h3``; ``--model tiny`` or ``h3_33b``)."""
+    from types import SimpleNamespace
+
+    from ..models.h3 import H3DiT, h3_preset
+    from .h3_stream import H3StreamConfig
+
+    cfg = h3_preset("tiny" if args.model in ("small", "tiny") else args.model)
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    model = H3DiT(cfg, device=dev, dtype=dtype, seed=0)
+    scfg = H3StreamConfig(grid_hw=(args.height // 2, args.width // 2), chunk_latents=args.chunk_frames,
+                          window_chunks=max(1, args.window_frames // args.chunk_frames), use_cuda_graph=not args.no_graphs)
+    engine = H3Engine(model, scfg, nav)
+    decoders = _decode_backends(args, SimpleNamespace(out_dim=scfg.latent_channels), dev, dtype, rank)
+    decoded = {"frames": 0}
+    if decoders is not None:
+        decoders.start(args.decoder)
+    g = torch.Generator().manual_seed(0)
+    state.set_phase("preparing")
+    engine.start(torch.randn(16, cfg.text_dim, generator=g), torch.randn(scfg.latent_channels, 1, args.height, args.width, generator=g))
+    state.set_phase("running")
+    nav.set_key("w", True)
+
+    def on_piece(_c, _o, frames, _ns):
+        decoded["frames"] += frames.shape[1]
+
+    def one(i):
+        lat, st = engine.generate()
+        ms = 0.0 if decoders is None else decoders.push(i, lat[0].contiguous(), on_piece)
+        state.generated(st.index, st.dit_ms, ms)
+
+    if args.smoke:
+        for i in range(args.chunks):
+            one(i)
+        steady = [c["dit_ms"] for c in state.chunks[1:]] or [c["dit_ms"] for c in state.chunks]
+        if rank == 0:
+            print(json.dumps({"family": "h3", "chunks": args.chunks, "chunk_frames": args.chunk_frames,
+                              "median_chunk_ms": sorted(steady)[len(steady) // 2],
+                              "graph_chunks": sum(1 for s in engine.generator.stats if s.graph),
+                              "decoder": args.decoder, "decoded_frames": decoded["frames"]}))
+    else:
+        while True:
+            cmd = state.next_command()
+            if cmd["op"] == "shutdown":
+                break
+            if cmd["op"] == "stop":
+                state.set_phase("stopped")
+            elif cmd["op"] == "start":
+                state.set_phase("running")
+            elif cmd["op"] == "chunk" and state.phase == "running":
+                one(len(state.chunks))
+    if decoders is not None:
+        decoders.finish()
+        decoders.close()
+    _receipt(out_dir, f"exit-rank{rank}.json", {"rank": rank, "status": "ok", "chunks": len(state.chunks), "time": time.time()})
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--family", default="wan", choices=["wan", "h3"])
     ap.add_argument("--model", default="small")
     ap.add_argument("--height", type=int, default=16)
     ap.add_argument("--width", type=int, default=16)

@@ -206,3 +206,13 @@ def test_worker_decodes_chunks_through_the_decoder_switch(tmp_path, capsys):
         assert (out / "frames" / "video.rgb").stat().st_size > 0
     with pytest.raises(SystemExit):
         main(["--smoke", "--decoder", "nope"])
+
+
+def test_worker_h3_family_streams_and_decodes(tmp_path, capsys):
+    from solarwm_b200.serve.worker import main
+
+    assert main(["--smoke", "--family", "h3", "--model", "tiny", "--height", "4", "--width", "6", "--chunk-frames", "2",
+                 "--window-frames", "4", "--chunks", "4", "--decoder", "vit", "--no-graphs", "--output", str(tmp_path)]) == 0
+    report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert report["family"] == "h3" and report["chunks"] == 4 and report["decoded_frames"] > 0
+    assert json.loads((tmp_path / "exit-rank0.json").read_text())["chunks"] == 4
