@@ -1,6 +1,7 @@
 """Out-of-bounds and race checks that need no sanitizer: outputs carved out of canary-filled buffers (nothing
 outside the output may change, whatever the tile shapes) and repeated runs that must agree bit for bit (a data race
-or an unordered reduction shows up as a difference)."""
+or an unordered reduction shows up as a difference).  The file sorts near the end on purpose: a run that stops at
+the first failure has already run the functional tests."""
 import math
 
 import pytest
