@@ -222,3 +222,17 @@ def test_gcs_uploader_create_only_and_retry():
         assert "ifGenerationMatch=0" in calls[-1].full_url and calls[-1].headers["Authorization"] == "Bearer tok"
         with pytest.raises(UploadError):
             up.upload(fh.name, "exists.bin")
+
+
+def test_balanced_descending_sequence_partition():
+    import pytest
+
+    from solarwm_b200.parallel.ulysses import balanced_bounds, balanced_lengths
+
+    assert balanced_lengths(5040, 8) == [630] * 8
+    lens = balanced_lengths(2108, 8)                       # 1100 prompt tokens + 1008 anchor rows
+    assert sum(lens) == 2108 and lens == sorted(lens, reverse=True) and lens[0] - lens[-1] <= 1
+    spans = [balanced_bounds(2108, 8, r) for r in range(8)]
+    assert spans[0][0] == 0 and spans[-1][1] == 2108 and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    with pytest.raises(ValueError):
+        balanced_lengths(3, 8)
