@@ -221,7 +221,21 @@ def _run_h3(args, rank, out_dir, dev, state, nav) -> int:
         decoders.start(args.decoder)
     g = torch.Generator().manual_seed(0)
     state.set_phase("preparing")
-    engine.start(torch.randn(16, cfg.text_dim, generator=g), torch.randn(scfg.latent_channels, 1, args.height, args.width, generator=g))
+    from . import scene_guard
+
+    scene = {"text": torch.randn(16, cfg.text_dim, generator=g),
+             "anchor_latent": torch.randn(scfg.latent_channels, 1, args.height, args.width, generator=g)}
+    try:        # every rank checks its own copy; the verdicts are exchanged on the host before any device work
+        import torch.distributed as dist
+
+        scene_guard.admit_scene(scene_guard.check_scene(scene, text_dim=cfg.text_dim, latent_channels=scfg.latent_channels,
+                                                        grid_hw=scfg.grid_hw),
+                                dist=dist if dist.is_available() and dist.is_initialized() else None)
+    except scene_guard.SceneRejected as exc:
+        scene_guard.recover(exc, lambda: state.set_phase("stopped", str(exc)))       # parked: the model stays resident
+        _receipt(out_dir, f"exit-rank{rank}.json", {"rank": rank, "status": "scene_rejected", "stage": exc.stage, "time": time.time()})
+        return 0
+    engine.start(scene["text"], scene["anchor_latent"])
     state.set_phase("running")
     nav.set_key("w", True)
 

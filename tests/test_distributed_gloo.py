@@ -211,3 +211,43 @@ def test_h3_streaming_with_ulysses_matches_single_rank(tmp_path):
     for r in range(2):
         got = torch.load(f"{out}.{r}", weights_only=True)
         assert got["err"] < 1e-4 * max(got["scale"], 1.0), got
+
+
+def _scene_worker(rank, world, path, out):
+    from solarwm_b200.serve import scene_guard as sg
+
+    _init(rank, world, path)
+    good = {"text": torch.randn(6, 16), "anchor_latent": torch.randn(4, 1, 4, 6)}
+    bad = dict(good, anchor_latent=torch.full((4, 1, 4, 6), float("nan")))
+    kw = dict(text_dim=16, latent_channels=4, grid_hw=(2, 3))
+    result = {"parked": 0}
+    sg.admit_scene(sg.check_scene(good, **kw), dist=dist)                   # every rank agrees: proceeds
+    try:                                                                     # only rank 1 holds a bad copy
+        sg.admit_scene(sg.check_scene(bad if rank == 1 else good, **kw), dist=dist)
+        result["raised"] = False
+    except sg.SceneRejected as exc:
+        result.update(raised=True, message=str(exc), agreed=exc.pre_call_collective_agreement)
+        result["stage"] = sg.recover(exc, lambda: result.__setitem__("parked", result["parked"] + 1))
+    try:
+        sg.recover(sg.SceneRejected("local only", stage="x", pre_call_collective_agreement=False), lambda: None)
+        result["local_recoverable"] = True
+    except RuntimeError:
+        result["local_recoverable"] = False
+    sg.admit_scene(sg.check_scene(good, **kw), dist=dist)                   # the group is still usable afterwards
+    torch.save(result, f"{out}.{rank}")
+    dist.destroy_process_group()
+
+
+def test_scene_rejection_is_agreed_before_any_device_work_and_parks(tmp_path):
+    from solarwm_b200.serve.scene_guard import check_scene
+
+    out = str(tmp_path / "scene")
+    mp.spawn(_scene_worker, args=(2, str(tmp_path / "rdv"), out), nprocs=2, join=True)
+    got = [torch.load(f"{out}.{r}", weights_only=True) for r in range(2)]
+    assert all(g["raised"] and g["agreed"] and g["parked"] == 1 and g["stage"] == "scene_start" for g in got)
+    assert got[0]["message"] == got[1]["message"] and "rank 1" in got[0]["message"] and "non-finite" in got[0]["message"]
+    assert not got[0]["local_recoverable"]
+    kw = dict(text_dim=16, latent_channels=4, grid_hw=(2, 3))
+    assert "tokens" in check_scene({"text": torch.randn(0, 16), "anchor_latent": torch.randn(4, 1, 4, 6)}, **kw)
+    assert "anchor" in check_scene({"text": torch.randn(3, 16), "anchor_latent": torch.randn(4, 1, 4, 5)}, **kw)
+    assert "embedding" in check_scene({"text": torch.randn(3, 8), "anchor_latent": torch.randn(4, 1, 4, 6)}, **kw)
