@@ -194,6 +194,8 @@ def run(args) -> int:
         if decoders is not None:
             decoders.finish()
             decoders.close()
+        if rank == 0:       # the session's per-chunk timings (DiT / decode milliseconds), as the state endpoint reports them
+            _receipt(out_dir, "session.json", {"schema": "solarwm.serve-session.v1", "chunks": list(state.chunks)})
         _receipt(out_dir, f"exit-rank{rank}.json", {"rank": rank, "status": "ok", "chunks": len(state.chunks), "time": time.time()})
         return 0
     except Exception as exc:  # noqa: BLE001
@@ -270,6 +272,8 @@ def _run_h3(args, rank, out_dir, dev, state, nav) -> int:
     if decoders is not None:
         decoders.finish()
         decoders.close()
+    if rank == 0:       # the session's per-chunk timings (DiT / decode milliseconds), as the state endpoint reports them
+        _receipt(out_dir, "session.json", {"schema": "solarwm.serve-session.v1", "chunks": list(state.chunks)})
     _receipt(out_dir, f"exit-rank{rank}.json", {"rank": rank, "status": "ok", "chunks": len(state.chunks), "time": time.time()})
     return 0
 

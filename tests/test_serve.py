@@ -216,3 +216,5 @@ def test_worker_h3_family_streams_and_decodes(tmp_path, capsys):
     report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert report["family"] == "h3" and report["chunks"] == 4 and report["decoded_frames"] > 0
     assert json.loads((tmp_path / "exit-rank0.json").read_text())["chunks"] == 4
+    session = json.loads((tmp_path / "session.json").read_text())
+    assert session["schema"] == "solarwm.serve-session.v1" and len(session["chunks"]) == 4 and "dit_ms" in session["chunks"][0]
