@@ -54,6 +54,7 @@ class Stage2Options:
     max_score_t: float = 980.0
     checkpointing: str = "none"
     ema_decay: Optional[float] = None      # per-role EMA: a fp32 shadow of the student, updated after each of its steps
+    ema_start_step: int = 39               # until this outer step the shadow simply follows the student (decay 0)
     seed: int = 0
 
 
@@ -206,7 +207,10 @@ class WanStage2Trainer:
             result["student"] = float(loss_s.detach())
             result["student_grad_norm"] = float(self._apply(self.student, self.opt_student))
             if self.ema_student is not None:             # the role's own average: only student steps advance it
-                self.ema_student.update(self.student)
+                from ...engine.ema import ema_decay_for_step
+
+                self.ema_student.update(self.student, decay=ema_decay_for_step(
+                    target_decay=self.opts.ema_decay, global_step=self.global_step, warmup_steps=self.opts.ema_start_step))
         # critic: flow matching on the student's sample
         x0 = out.detach().to(lat.dtype)
         u2 = torch.rand(1, generator=self.gen, device=dev)

@@ -118,7 +118,7 @@ def test_stage2_student_ema_follows_student_steps_only_and_round_trips():
 
     cfg, _ = tiny()
     opts = Stage2Options(chunk_frames=2, window_chunks=2, critic_updates_per_student=2, denoising_steps=(1000.0, 500.0),
-                         ema_decay=0.5, lr_student=1e-3)
+                         ema_decay=0.5, ema_start_step=0, lr_student=1e-3)
     tr = WanStage2Trainer(cfg, "cpu", opts, dtype=torch.float32)
     for m in (tr.student, tr.teacher, tr.critic):
         with torch.no_grad():
@@ -141,6 +141,15 @@ def test_stage2_student_ema_follows_student_steps_only_and_round_trips():
     state.pop("ema_student")
     with pytest.raises(BackendContractError):
         tr2.load_role_state(state)
+    # before ``ema_start_step`` the shadow follows the student exactly
+    early = WanStage2Trainer(cfg, "cpu", Stage2Options(chunk_frames=2, window_chunks=2, critic_updates_per_student=1,
+                                                       denoising_steps=(1000.0, 500.0), ema_decay=0.9, lr_student=1e-3),
+                             dtype=torch.float32)
+    for m in (early.student, early.teacher, early.critic):
+        with torch.no_grad():
+            m.get_parameter("head.head.weight").normal_(0, 0.05)
+    early.train_outer_step(batch)
+    assert torch.equal(early.ema_student.shadow[name], early.student.get_parameter(name).detach().float())
 
 
 @pytest.mark.parametrize("F,sink", [(4, 0), (5, 1)])
