@@ -83,8 +83,12 @@ __device__ __forceinline__ void epilogue_tile(const CUtensorMap& tmC, const Gemm
                                               int cw = 0, int ch = 0, int ct = 0, int ncols = BN) {
   constexpr int CHUNK = OUT_F32 ? 32 : 64;  // columns per 128-byte staged row
   const bool rows_live = (row0) < p.M;
+  // act 2 (SwiGLU, bf16 output): the weight rows are interleaved in blocks of 64 (64 gate rows, their 64 up rows,
+  // ...), so 128 accumulator columns make 64 output columns = one staged row, stored at half the column offset
+  const bool swiglu = !OUT_F32 && p.act == 2;
+  const int step = swiglu ? 2 * CHUNK : CHUNK;
 #pragma unroll 1
-  for (int c0 = 0; c0 < ncols; c0 += CHUNK) {
+  for (int c0 = 0; c0 < ncols; c0 += step) {
     const int ncol = n0 + c0;
     if (ncol >= p.N) break;
     if (lane == 0) tma_store_wait_read<1>();
@@ -111,6 +115,41 @@ __device__ __forceinline__ void epilogue_tile(const CUtensorMap& tmC, const Gemm
         uint4 o = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]),
                              __float_as_uint(v[2]), __float_as_uint(v[3]));
         *reinterpret_cast<uint4*>(dst + ((g ^ (lane & 7)) << 4)) = o;
+      }
+    } else if (swiglu) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t rg[32], ru[32];
+        tmem_ld_32x32(t_row + c0 + 32 * h, rg);          // 32 gate columns
+        tmem_ld_32x32(t_row + c0 + 64 + 32 * h, ru);     // their 32 up columns
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float a[8], u[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            a[e] = __uint_as_float(rg[g * 8 + e]);
+            u[e] = __uint_as_float(ru[g * 8 + e]);
+          }
+          if (p.bias != nullptr) {
+            const uint4 ba = *reinterpret_cast<const uint4*>(p.bias + ncol + 32 * h + g * 8);
+            const uint4 bu = *reinterpret_cast<const uint4*>(p.bias + ncol + 64 + 32 * h + g * 8);
+            const uint32_t wa[4] = {ba.x, ba.y, ba.z, ba.w}, wu[4] = {bu.x, bu.y, bu.z, bu.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 fa = unpack_bf16x2(wa[e]), fu = unpack_bf16x2(wu[e]);
+              a[2 * e] += fa.x; a[2 * e + 1] += fa.y;
+              u[2 * e] += fu.x; u[2 * e + 1] += fu.y;
+            }
+          }
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = a[e] / (1.f + __expf(-a[e])) * u[e];
+          uint4 o = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                               pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+          const int piece = 4 * h + g;
+          *reinterpret_cast<uint4*>(dst + ((piece ^ (lane & 7)) << 4)) = o;
+        }
       }
     } else {
       uint32_t r0[32], r1[32];
@@ -168,7 +207,7 @@ __device__ __forceinline__ void epilogue_tile(const CUtensorMap& tmC, const Gemm
             "r"(smem_u32(src)), "r"(ncol), "r"(row0)
             : "memory");
       } else {
-        tma_store_2d(&tmC, src, ncol, row0);
+        tma_store_2d(&tmC, src, swiglu ? (ncol >> 1) : ncol, row0);
       }
       tma_store_commit();
     }
@@ -629,6 +668,8 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: empty problem%s");
   if (N % 8 != 0) return fail("gemm: N must be a multiple of 8%s");
   if (layout < 0 || layout > 2) return fail("gemm: bad layout%s");
+  if (act == 2 && (out_f32 || accumulate || sc.dst.n != 0 || N % 128 != 0))
+    return fail("gemm: the SwiGLU epilogue takes bf16 output, no accumulate, no scatter, N a multiple of 128%s");
   CUtensorMap tA, tB, tC;
   int rc;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -651,7 +692,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   if (out_f32) {
     rc = make_tmap_2d(&tC, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32);
   } else {
-    rc = make_tmap_2d(&tC, C, bf, 2, M, N, ldc, 32, 64);
+    rc = make_tmap_2d(&tC, C, bf, 2, M, act == 2 ? N / 2 : N, ldc, 32, 64);
   }
   if (rc) return rc;
   GemmParams p;

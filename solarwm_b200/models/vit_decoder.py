@@ -150,7 +150,16 @@ class ViTVideoDecoder(nn.Module):
         B, N, _ = x.shape
         x2 = F_.gated_residual(x.reshape(B * N, -1), F_.linear(o.reshape(B * N, -1), blk.out), None)
         xm = F_.norm_modulate(x2, mode=1, w=blk.norm2, eps=c.eps)
-        y = F_.linear(F_.swiglu(F_.linear(xm, blk.gate_up)), blk.down)
+        if xm.is_cuda and blk.gate_up.shape[0] % 128 == 0:
+            # gate|up product and SwiGLU in one kernel: the [rows, 2 * ffn] tensor is never written
+            il = getattr(blk, "_gate_up_interleaved", None)
+            if il is None or il.device != xm.device or il._version_src != blk.gate_up._version:
+                il = F_.interleave_gate_up(blk.gate_up.detach())
+                il._version_src = blk.gate_up._version
+                blk._gate_up_interleaved = il
+            y = F_.linear(F_.linear_swiglu(xm, il), blk.down)
+        else:
+            y = F_.linear(F_.swiglu(F_.linear(xm, blk.gate_up)), blk.down)
         return F_.gated_residual(x2, y, None).view(B, N, -1)
 
     def attend(self, q, k, v):

@@ -70,6 +70,9 @@ def gemm(a, b, layout=NT, *, bias=None, act=None, out=None, out_dtype=None, accu
             c = c + bias.float()
         if act == "gelu":
             c = torch.nn.functional.gelu(c, approximate="tanh")
+        elif act == "swiglu":
+            g, u = c.view(c.shape[0], -1, 2, 64).unbind(2)
+            c = (torch.nn.functional.silu(g) * u).reshape(c.shape[0], -1)
         dt = out_dtype or (out.dtype if out is not None else a.dtype)
         if out is not None:
             if accumulate:
@@ -92,11 +95,12 @@ def gemm(a, b, layout=NT, *, bias=None, act=None, out=None, out_dtype=None, accu
         K2, N = b.shape
     if K != K2:
         raise ValueError(f"gemm inner dimensions differ: {K} vs {K2}")
+    n_out = N // 2 if act == "swiglu" else N
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
+        out = torch.empty((M, n_out), dtype=out_dtype or torch.bfloat16, device=a.device)
         accumulate = False
     else:
-        if out.shape != (M, N) or out.stride(1) != 1:
+        if out.shape != (M, n_out) or out.stride(1) != 1:
             raise ValueError("gemm: bad output tensor")
     if bias is not None:
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous()
@@ -104,7 +108,7 @@ def gemm(a, b, layout=NT, *, bias=None, act=None, out=None, out_dtype=None, accu
     rc = lib.solar_gemm_bf16(
         ptr(a), ptr(b), ptr(out), ptr(bias), c_int(M), c_int(N), c_int(K),
         c_ll(a.stride(0)), c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(layout),
-        c_int(1 if act == "gelu" else 0), c_int(1 if out.dtype == torch.float32 else 0),
+        c_int({"gelu": 1, "swiglu": 2}.get(act, 0)), c_int(1 if out.dtype == torch.float32 else 0),
         c_int(1 if accumulate else 0), ptr(status_word(a.device)), c_int(max_ctas), stream_handle())
     check(rc, "solar_gemm_bf16")
     count("gemm")
@@ -773,6 +777,24 @@ def rgb8(frame_chw, mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225)):
     if not ok:
         raise FloatingPointError("nonfinite RGB pixel")
     return out, None
+
+
+def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """``[gate (F rows) | up (F rows)]`` -> rows in blocks of 64: 64 gate rows, their 64 up rows, ...  (F a multiple of
+    64), the layout the GEMM's SwiGLU epilogue reads; works for a bias vector too."""
+    f2 = w.shape[0]
+    if f2 % 128:
+        raise ValueError("the fused gate|up width must be a multiple of 128")
+    half = f2 // 2
+    g, u = w[:half], w[half:]
+    rest = w.shape[1:]
+    return torch.stack([g.reshape(half // 64, 64, *rest), u.reshape(half // 64, 64, *rest)], 1).reshape(f2, *rest).contiguous()
+
+
+def linear_swiglu(x, w_interleaved, b_interleaved=None):
+    """``silu(x Wg^T + bg) * (x Wu^T + bu)`` with the activation in the GEMM epilogue: the ``[rows, 2F]`` product is never
+    written.  Weights / bias in the ``interleave_gate_up`` layout.  Inference only (no autograd)."""
+    return gemm(x, w_interleaved, NT, bias=b_interleaved, act="swiglu")
 
 
 # --------------------------------------------------------------------------------------

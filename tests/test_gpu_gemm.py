@@ -132,3 +132,36 @@ def test_cta_pair_kernel_is_bit_identical_to_single_cta(layout, shape):
     assert torch.equal(single, pair) and torch.equal(single32, pair32)
     _check(pair32, _ref(a, b, layout), K)
     assert torch.allclose(acc, 2 * pair32, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,F,K,bias", [(300, 192, 256, False), (1000, 256, 128, True), (130, 704, 64, True)])
+def test_swiglu_epilogue_matches_fp32_reference(M, F, K, bias):
+    """silu(x Wg^T + bg) * (x Wu^T + bu) computed in the GEMM epilogue from block-interleaved weights, on both the
+    single-CTA and the CTA-pair kernel."""
+    import ctypes
+
+    from solarwm_b200 import ops
+    from solarwm_b200.ops import _lib
+    from solarwm_b200.ops import functional as F_
+
+    g = torch.Generator(device="cuda").manual_seed(M + F)
+    x = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, generator=g, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    b = (torch.randn(2 * F, generator=g, device="cuda") * 0.1).to(torch.bfloat16) if bias else None
+    xf, wf = x.float(), w.float()
+    gate, up = xf @ wf[:F].t(), xf @ wf[F:].t()
+    if bias:
+        gate, up = gate + b[:F].float(), up + b[F:].float()
+    want = torch.nn.functional.silu(gate) * up
+    lib = _lib.load()
+    lib.solar_gemm_pair_mode.argtypes = [ctypes.c_int]
+    for mode in (0, 1):
+        old = lib.solar_gemm_pair_mode(mode)
+        try:
+            got = F_.linear_swiglu(x, F_.interleave_gate_up(w), None if b is None else F_.interleave_gate_up(b))
+        finally:
+            lib.solar_gemm_pair_mode(old)
+        ops.check_status()
+        assert got.shape == (M, F)
+        err = (got.float() - want).abs().max() / want.abs().max()
+        assert err < 2e-2, (mode, float(err))
