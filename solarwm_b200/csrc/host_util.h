@@ -46,6 +46,20 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// The driver entry point needs a context bound to the calling thread.  A fresh thread whose device is already the
+// default one (an autograd worker for device 0: setting device 0 there is a no-op) has none until its first runtime
+// call, so an encode that is the thread's very first CUDA call fails with "invalid context": bind the current
+// device's primary context (cudaFree(nullptr) does exactly that) and try once more.
+template <class... Args>
+inline CUresult encode_with_context(EncodeTiledFn fn, Args... args) {
+  CUresult r = fn(args...);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    cudaFree(nullptr);
+    r = fn(args...);
+  }
+  return r;
+}
+
 // Row-major 2-D tensor [rows, cols] with leading dimension `ld` (elements); the box is
 // [box_rows, box_cols] and is stored in shared memory with the 128-byte swizzle, so
 // box_cols * elt_bytes must equal 128.
@@ -60,7 +74,7 @@ inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elt_bytes)};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = encode_with_context(fn, out, dt, 2u, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed (code %s%lld)", "", (long long)r);
@@ -80,7 +94,7 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   cuuint32_t box[3] = {b0, b1, b2};
   cuuint32_t estr[3] = {1, 1, 1};
   (void)elt_bytes;
-  CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = encode_with_context(fn, out, dt, 3u, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled(3d) failed (code %s%lld)", "", (long long)r);
@@ -99,7 +113,7 @@ inline int make_tmap_4d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   cuuint64_t s[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
   cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
   cuuint32_t e[4] = {1, 1, 1, 1};
-  CUresult r = fn(out, dt, 4, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = encode_with_context(fn, out, dt, 4u, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled(4d) failed (code %s%lld)", "", (long long)r);
