@@ -85,8 +85,16 @@ def run_inference(config: Mapping[str, Any], family: str) -> Mapping[str, Any]:
         weights_id = "init:random"
         c = config.get("checkpoint", {}) or {}
         if c.get("resume_from"):
+            source = c.get("weight_source")
+            if source in (None, "release"):          # a released package names its own default role
+                from ...checkpoint.release import NAME, resolve_default_weights
+                from pathlib import Path as _P
+
+                has_manifest = (_P(c["resume_from"]) / NAME).exists()
+                if source == "release" or has_manifest:
+                    source = resolve_default_weights(c["resume_from"])
             verified, _ = load_checkpoint(c["resume_from"], model=model, mode="weights_only",
-                                          weight_source=str(c.get("weight_source", "ema")), map_location=ctx.device)
+                                          weight_source=str(source or "ema"), map_location=ctx.device)
             weights_id = verified.manifest_digest
         inf = config.get("inference", {}) or {}
         cases = _cases(config, int(inf.get("cases", 1)))

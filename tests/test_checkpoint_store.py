@@ -150,3 +150,31 @@ def test_h3_released_layout_strict_mapped_load(tmp_path):
     entries["norm_out.weight"] = entries["norm_out.weight"]._replace(shape=(7,))
     with pytest.raises(BackendContractError, match="shape"):
         plan_load(entries, dst)
+
+
+def test_release_manifest_selects_the_default_weight_role(tmp_path):
+    import json
+
+    import pytest
+
+    from solarwm_b200.checkpoint.release import resolve_default_weights, write_release_manifest
+    from solarwm_b200.errors import BackendContractError
+
+    pkg = tmp_path / "pkg"
+    pkg.mkdir()
+    with pytest.raises(BackendContractError, match="readable"):
+        resolve_default_weights(pkg)
+    with pytest.raises(BackendContractError):
+        write_release_manifest(pkg, family="wan22_ti2v_5b", stage="stage2", weight_roles=["live"], default_weights="ema")
+    path = write_release_manifest(pkg, family="wan22_ti2v_5b", stage="stage2", weight_roles=["live", "ema"], default_weights="ema")
+    assert resolve_default_weights(pkg) == "ema" and resolve_default_weights(pkg / "model.pt") == "ema"
+    with pytest.raises(FileExistsError):
+        write_release_manifest(pkg, family="x", stage="y", weight_roles=["live"], default_weights="live")
+    m = json.loads(path.read_text())
+    for mutate in (lambda d: d.update(schema="other"), lambda d: d["load"].update(entrypoint="sub"),
+                   lambda d: d["load"].update(default_weights="teacher"), lambda d: d["identity"]["model"].update(weight_role="live")):
+        bad = json.loads(json.dumps(m))
+        mutate(bad)
+        path.write_text(json.dumps(bad))
+        with pytest.raises(BackendContractError):
+            resolve_default_weights(pkg)
