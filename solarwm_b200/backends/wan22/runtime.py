@@ -12,7 +12,7 @@ from ...config.routes import validate_route
 from ...engine.schedule import WarmupCosine
 from ...engine.train_engine import (BatchIdentity, GradientStatus, JsonlEventSink, MicrobatchResult, StepPolicy,
                                     TrainingEngine)
-from ...errors import BackendContractError
+from ...errors import BackendContractError, ConfigurationError
 from ...parallel import dist_init
 from ...runtime import distributed as rdist
 from ...runtime.output_layout import events_path, output_root
@@ -47,6 +47,34 @@ def synthetic_batches(config, arch, device) -> Iterator[dict]:
         yield batch
 
 
+def activation_and_sharding_options(train: Mapping[str, Any], world_size: int) -> Mapping[str, Any]:
+    """Trainer options out of the ``train`` section.
+
+    ``fsdp.activation_checkpointing``: false / true ("full") / "none" | "full" | "selective";
+    ``fsdp.saved_attention_blocks`` > 0 means "selective" (attention outputs are carried across the recompute);
+    ``activation_memory.keep_blocks`` / ``.lean``: how many of the last blocks stay resident, and whether resident
+    blocks rebuild their norm outputs and FFN hidden tensor in backward;
+    optimizer sharding is on with ``zero.enabled`` or ``fsdp.enabled`` (more than one rank), its transport is
+    ``zero.transport``: "collective" (NCCL) or "fused" (peer loads / stores over NVLink)."""
+    fsdp = train.get("fsdp", {}) or {}
+    ac = fsdp.get("activation_checkpointing", False)
+    if isinstance(ac, str):
+        mode = ac.strip().lower()
+        if mode not in ("none", "full", "selective"):
+            raise ConfigurationError("train.fsdp.activation_checkpointing must be a boolean or none / full / selective")
+    else:
+        mode = "full" if ac else "none"
+    if int(fsdp.get("saved_attention_blocks", 0) or 0) > 0 and mode != "none":
+        mode = "selective"
+    mem = train.get("activation_memory", {}) or {}
+    zero_cfg = train.get("zero", {}) or {}
+    transport = str(zero_cfg.get("transport", "collective"))
+    if transport not in ("collective", "fused"):
+        raise ConfigurationError("train.zero.transport must be collective or fused")
+    return dict(checkpointing=mode, keep_blocks=int(mem.get("keep_blocks", 0)), lean_kept=bool(mem.get("lean", False)),
+                zero=bool(zero_cfg.get("enabled", fsdp.get("enabled", False))) and world_size > 1, zero_transport=transport)
+
+
 class WanStage0p5Runtime:
     """Adapts ``WanStage0p5Trainer`` to the engine's 11-hook protocol."""
 
@@ -71,9 +99,7 @@ class WanStage0p5Runtime:
             image_dropout=float(train.get("i2v_image_condition_dropout", 0.0)),
             grad_accum=int(train.get("grad_accum", train.get("gradient_accumulation_steps", 1))),
             ema_decay=float(ema["decay"]) if ema.get("enabled") else None,
-            checkpointing="full" if (train.get("fsdp", {}) or {}).get("activation_checkpointing") else "none",
-            zero=bool((train.get("fsdp", {}) or {}).get("enabled", False)) and topo.raw_world_size > 1,
-            seed=seed, **dict(extra_options or {}))
+            seed=seed, **activation_and_sharding_options(train, topo.raw_world_size), **dict(extra_options or {}))
         dtype = torch.bfloat16 if self.ctx.device.type == "cuda" else torch.float32
         from ...models.wan import WanDiT
 
@@ -82,12 +108,13 @@ class WanStage0p5Runtime:
         if bool(config["model"].get("nonzero_head_init", False)):
             with torch.no_grad():
                 model.get_parameter("head.head.weight").normal_(0, 0.02)
+        sp_ctx, heap = self._fused_transports(dist_cfg, opts, model)
         if trainer_cls is WanStage0p5Trainer:
-            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, dtype=dtype, model=model,
-                                       dp_group=self.ctx.dp_group, dp_size=topo.dp_size)
+            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=sp_ctx, dtype=dtype, model=model,
+                                       dp_group=self.ctx.dp_group, dp_size=topo.dp_size, heap=heap)
         else:
-            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=self.ctx.sp, model=model,
-                                       dp_group=self.ctx.dp_group, dp_size=topo.dp_size)
+            self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=sp_ctx, model=model,
+                                       dp_group=self.ctx.dp_group, dp_size=topo.dp_size, heap=heap)
         self.trainer.gen.manual_seed(objective_seed(seed, topo.dp_rank))
         self.scheduler = WarmupCosine(self.trainer.optimizer, warmup_steps=int(train.get("warmup_steps", 0)),
                                       total_steps=int(train["max_steps"]),
@@ -127,6 +154,45 @@ class WanStage0p5Runtime:
     @property
     def global_step(self) -> int:
         return self._step
+
+    def _fused_transports(self, dist_cfg, opts, model):
+        """``distributed.sp_transport: fused`` and ``train.zero.transport: fused`` (both opt-in, CUDA, one node): the
+        Ulysses exchanges ride on the producing kernels and the optimizer reduces / pushes over peer memory.  Every
+        rank must be able to map every peer; the ranks agree on that before a symmetric buffer exists and fall back to
+        the NCCL forms together."""
+        sp_ctx, heap = self.ctx.sp, None
+        topo = self.ctx.topology
+        want_sp = str(dist_cfg.get("sp_transport", "nccl")) == "fused" and topo.sp_size > 1
+        want_zero = opts.zero and opts.zero_transport == "fused"
+        if not (want_sp or want_zero):
+            return sp_ctx, heap
+        if self.ctx.device.type != "cuda":
+            raise ConfigurationError("the fused transports need CUDA devices")
+        import torch.distributed as dist
+
+        local, n = self.ctx.device.index, torch.cuda.device_count()
+        can = n >= topo.raw_world_size and all(torch.cuda.can_device_access_peer(local, d) for d in range(topo.raw_world_size)
+                                               if d != local)
+        agree = torch.tensor([1 if can else 0], device=self.ctx.device)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            if want_zero:
+                opts.zero_transport = "collective"
+            return sp_ctx, heap
+        if want_sp:
+            from ...parallel.fused_ulysses import FusedUlysses
+
+            data = self.config["data"]
+            pt, ph, pw = self.arch.patch_size
+            frames = latent_frames(int(data["pixel_frames"]), PROFILES[self.route.family].vae_stride[0]) \
+                if "latent_frames" not in data else int(data["latent_frames"])
+            tokens = (frames // pt) * (int(data["latent_height"]) // ph) * (int(data["latent_width"]) // pw)
+            sp_ctx = FusedUlysses(self.ctx.sp_group, max_tokens=tokens, dim=self.arch.dim, num_heads=self.arch.num_heads)
+        if want_zero:
+            from ...parallel.symm import SymmetricHeap
+
+            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()), None)
+        return sp_ctx, heap
 
     def zero_grad(self) -> None:
         self.trainer.model.zero_grads()

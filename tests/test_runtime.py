@@ -236,3 +236,23 @@ def test_balanced_descending_sequence_partition():
     assert spans[0][0] == 0 and spans[-1][1] == 2108 and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
     with pytest.raises(ValueError):
         balanced_lengths(3, 8)
+
+
+def test_train_section_maps_to_activation_and_sharding_options():
+    import pytest
+
+    from solarwm_b200.backends.wan22.runtime import activation_and_sharding_options as opts
+    from solarwm_b200.errors import ConfigurationError
+
+    assert opts({}, 1) == dict(checkpointing="none", keep_blocks=0, lean_kept=False, zero=False, zero_transport="collective")
+    assert opts({"fsdp": {"activation_checkpointing": True}}, 8)["checkpointing"] == "full"
+    assert opts({"fsdp": {"activation_checkpointing": True, "saved_attention_blocks": 30}}, 8)["checkpointing"] == "selective"
+    assert opts({"fsdp": {"activation_checkpointing": "selective"}, "activation_memory": {"keep_blocks": 19, "lean": True}}, 1) == \
+        dict(checkpointing="selective", keep_blocks=19, lean_kept=True, zero=False, zero_transport="collective")
+    assert opts({"zero": {"enabled": True, "transport": "fused"}}, 8)["zero"] is True
+    assert opts({"zero": {"enabled": True}}, 1)["zero"] is False             # one rank: nothing to shard over
+    assert opts({"fsdp": {"enabled": True}}, 2)["zero"] is True
+    with pytest.raises(ConfigurationError):
+        opts({"fsdp": {"activation_checkpointing": "sometimes"}}, 1)
+    with pytest.raises(ConfigurationError):
+        opts({"zero": {"transport": "smoke-signals"}}, 2)
