@@ -154,6 +154,16 @@ class TrainingEngine:
         return self.runtime.global_step
 
     def step(self) -> None:
+        if os.environ.get("SOLAR_PHASE_TIMES", "0") == "1":
+            from ..utils.trace import PhaseTimer
+
+            timer = PhaseTimer()
+            with timer.installed():
+                self._step(timer)
+        else:
+            self._step(None)
+
+    def _step(self, timer) -> None:
         rt, policy = self.runtime, self.policy
         target = rt.global_step + 1
         rt.zero_grad()
@@ -166,11 +176,14 @@ class TrainingEngine:
         except Exception:
             rt.zero_grad()
             raise
-        status = rt.prepare_optimizer_step()
-        if not status.finite or not math.isfinite(status.norm):
-            rt.zero_grad()
-            raise BackendContractError(f"non-finite gradients before optimizer step {target}: {status.norm}")
-        rt.optimizer_step()
+        from ..utils.trace import span
+
+        with span("optimizer"):
+            status = rt.prepare_optimizer_step()
+            if not status.finite or not math.isfinite(status.norm):
+                rt.zero_grad()
+                raise BackendContractError(f"non-finite gradients before optimizer step {target}: {status.norm}")
+            rt.optimizer_step()
         rt.scheduler_step()
         rt.set_global_step(target)
         rt.ema_update(target)
@@ -178,6 +191,8 @@ class TrainingEngine:
         self.event_sink({
             "schema": STEP_SCHEMA, "event": "optimizer_step", "step": target, "grad_accum": policy.grad_accum,
             "gradient_norm": status.norm, "losses": mean_losses(done),
+            **({} if timer is None else {"phase_ms": {k: v["total_ms"] for k, v in timer.summary().items()
+                                                      if not k.startswith("block.")}}),
             "microbatches": [{"identity": asdict(r.identity), "losses": dict(r.losses)} for r in done]})
         boundary = False
         if policy.should_save(target):

@@ -44,3 +44,19 @@ def test_trainer_step_reports_forward_backward_optimizer_and_blocks():
             pass
     finally:
         trace.enable_nvtx(previous)
+
+
+def test_step_events_carry_the_phase_split_when_asked(tmp_path, monkeypatch):
+    import json
+    from pathlib import Path
+
+    from solarwm_b200.cli import main
+
+    config = str(Path(__file__).resolve().parent.parent / "configs" / "wan22_ti2v_5b" / "tiny_stage0p5_cpu.yaml")
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path))
+    monkeypatch.setenv("SOLAR_PHASE_TIMES", "1")
+    assert main(["train", "--config", config, "--set", "runtime.device=cpu", "--set", "train.max_steps=2",
+                 "--set", "runtime.save_every=0"]) == 0
+    events = [json.loads(l) for l in (tmp_path / "events" / "rank-00000.jsonl").read_text().splitlines()]
+    steps = [e for e in events if e["event"] == "optimizer_step"]
+    assert len(steps) == 2 and {"forward", "backward", "optimizer"} <= set(steps[0]["phase_ms"])
