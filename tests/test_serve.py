@@ -53,6 +53,9 @@ def test_web_state_and_keys():
         except urllib.error.HTTPError as e:
             return e.code
 
+    page = urllib.request.urlopen(base + "/")
+    html = page.read().decode()
+    assert page.headers["Content-Type"].startswith("text/html") and "/key" in html and "/state" in html and "wasdijkl" in html
     assert post("/key", {"key": "w", "down": True}) == 200 and nav.down == {"w"}
     assert post("/key", {"key": "q", "down": True}) == 400
     assert post("/command", {"op": "start"}) == 200 and state.next_command()["op"] == "start"
