@@ -229,7 +229,8 @@ def teacher_forcing_attention(q_clean, k_clean, v_clean, q_noisy, k_noisy, v_noi
         c_hi = min((i + 1) * ct, L)
         ks = [k_clean[:, s] for s in seg] + [k_clean[:, lo:c_hi]]
         vs = [v_clean[:, s] for s in seg] + [v_clean[:, lo:c_hi]]
-        outs_c.append(ops.attention(q_clean[:, i * ct:c_hi], torch.cat(ks, 1), torch.cat(vs, 1)))
+        kc, vc = (ks[0], vs[0]) if len(ks) == 1 else (torch.cat(ks, 1), torch.cat(vs, 1))   # one span: no copy
+        outs_c.append(ops.attention(q_clean[:, i * ct:c_hi], kc, vc))
         kn = [k_clean[:, s] for s in seg] + [k_clean[:, lo:i * ct], k_noisy[:, i * ct:c_hi]]
         vn = [v_clean[:, s] for s in seg] + [v_clean[:, lo:i * ct], v_noisy[:, i * ct:c_hi]]
         outs_n.append(ops.attention(q_noisy[:, i * ct:c_hi], torch.cat(kn, 1), torch.cat(vn, 1)))
