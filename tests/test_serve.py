@@ -221,3 +221,12 @@ def test_worker_h3_family_streams_and_decodes(tmp_path, capsys):
     assert json.loads((tmp_path / "exit-rank0.json").read_text())["chunks"] == 4
     session = json.loads((tmp_path / "session.json").read_text())
     assert session["schema"] == "solarwm.serve-session.v1" and len(session["chunks"]) == 4 and "dit_ms" in session["chunks"][0]
+
+
+def test_decode_parity_tool_reports_streaming_equals_one_shot(capsys):
+    from solarwm_b200.serve.decode_parity import main
+
+    for kind in ("conv", "vit"):
+        assert main(["--decoder", kind, "--frames", "9", "--device", "cpu", "--tolerance", "1e-4"]) == 0
+        report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert report["decoder"] == kind and report["max_abs_diff"] <= 1e-4
