@@ -288,6 +288,13 @@ def run_ours(args):
         phases = {k: v["total_ms"] for k, v in timer.summary().items() if not k.startswith("block.")}
     ops.check_status(f"cuda:{local}")
     peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
+    utilization = {}
+    try:        # model FLOPs (no recompute counted) against the measured sustained cuBLAS rate of this pool
+        from solarwm_b200.utils.roofline import step_utilization
+
+        utilization = {"utilization": dict(step_utilization(cfg, tokens, ms / args.steps, world))}
+    except Exception as exc:  # noqa: BLE001 - a reporting extra must never cost the measurement
+        utilization = {"utilization": {"error": f"{type(exc).__name__}: {exc}"[:120]}}
     if rank == 0:
         value = tokens * args.steps / (ms / 1e3)
         e2e = tokens * args.steps / (ms_e2e / 1e3)
@@ -313,6 +320,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "launch_counters": counters, "host_enqueue_ms_per_step": host_ms,
             **({"phase_ms": phases} if phases is not None else {}),
+            **utilization,
             "final_loss": losses[-1] if losses else None,
         }
         print(json.dumps(out))

@@ -36,3 +36,18 @@ def test_resident_block_plan_on_the_5b_shape():
     assert bench.resident_block_plan(cfg, 27280, 4, total, zero_on=True, checkpointing="none") == (0, False)
     small = bench.resident_block_plan(cfg, 27280, 1, 80 * 2 ** 30, zero_on=False, checkpointing="selective")
     assert small[0] == 0 and small[1] is True          # no room beyond weights and optimizer state: recompute all
+
+
+def test_model_flops_and_utilization_of_the_5b_shape(tmp_path):
+    from solarwm_b200.utils.roofline import block_forward_flops, measured_peaks, step_utilization, training_step_flops
+
+    cfg = SimpleNamespace(dim=3072, ffn_dim=14336, num_layers=30, text_len=512)
+    per_block = block_forward_flops(27280, 512, 3072, 14336)
+    assert abs(per_block / 1e12 - 17.2) < 0.4                       # 2.06 + 9.14 + ~1.2 + 4.81 TFLOP
+    total = training_step_flops(cfg, 27280)
+    assert abs(total / 1e15 - 1.55) < 0.05
+    (tmp_path / "MEASURED_PEAKS.json").write_text('{"hbm_gbs": 6540.5, "bf16_tflops": 1641.7, "bf16_tflops_sustained": 1390.9}')
+    u = step_utilization(cfg, 27280, 1894.0, 1, root=tmp_path)
+    assert u["peak_source"] == "measured" and 0.55 < u["fraction_of_sustained_peak"] < 0.62
+    assert abs(step_utilization(cfg, 27280, 319.0, 8, root=tmp_path)["fraction_of_sustained_peak"] - u["fraction_of_sustained_peak"] * 1894 / 319 / 8) < 2e-3
+    assert measured_peaks(tmp_path / "nowhere")["source"] == "fallback"
