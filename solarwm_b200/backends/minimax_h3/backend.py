@@ -102,6 +102,9 @@ class MiniMaxH3Backend:
         tr = H3Stage0p5Trainer(self._cfg(config), dev, lr=float(config["train"].get("optimizer", {}).get("lr", 1e-4)),
                                seed=int(data.get("seed", 0)))
         self._load_released(tr.model, config)
+        from ..wan22.runtime import activation_and_sharding_options
+
+        tr.model.checkpointing = activation_and_sharding_options(config["train"], 1)["checkpointing"]
         losses, t0 = [], time.time()
         for step in range(int(config["train"]["max_steps"])):
             s = h3_sample(latent_frames=int(data.get("latent_frames", 3)), height=int(data.get("latent_height", 8)),

@@ -190,3 +190,25 @@ def test_suffix_forward_on_captured_prefix_matches_the_full_evaluation():
     # without reuse every probe re-noises the anchor frame on its own, so the two steps agree closely, not bitwise
     assert abs(losses[0] - losses[1]) < 1e-3 * max(1.0, abs(losses[0]))
     del g
+
+
+def test_h3_backend_train_honours_activation_checkpointing_setting(tmp_path, monkeypatch):
+    from solarwm_b200.models import h3 as h3_model
+    from solarwm_b200.registry import load_backend
+
+    seen = []
+    original = h3_model.H3DiT.forward
+
+    def spy(self, **kw):
+        seen.append(self.checkpointing)
+        return original(self, **kw)
+
+    monkeypatch.setattr(h3_model.H3DiT, "forward", spy)
+    config = {"schema": "solarwm.run.v1", "action": "train",
+              "model": {"family": "minimax_h3", "architecture": "tiny", "adapter": {"rank": 4}, "camera_translation_transform": "logd4"},
+              "data": {"seed": 0, "latent_frames": 3, "latent_height": 4, "latent_width": 4, "prompt_len": 6, "pixel_frames": 158},
+              "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "max_steps": 1,
+                        "optimizer": {"lr": 1e-3}, "fsdp": {"activation_checkpointing": True, "saved_attention_blocks": 2}},
+              "runtime": {"device": "cpu", "output_dir": str(tmp_path)}}
+    out = load_backend("minimax_h3").train(config)
+    assert out["final_step"] == 1 and seen and set(seen) == {"selective"}
