@@ -51,3 +51,21 @@ def test_model_flops_and_utilization_of_the_5b_shape(tmp_path):
     assert u["peak_source"] == "measured" and 0.55 < u["fraction_of_sustained_peak"] < 0.62
     assert abs(step_utilization(cfg, 27280, 319.0, 8, root=tmp_path)["fraction_of_sustained_peak"] - u["fraction_of_sustained_peak"] * 1894 / 319 / 8) < 2e-3
     assert measured_peaks(tmp_path / "nowhere")["source"] == "fallback"
+
+
+def test_reference_arm_prints_an_unavailable_line_without_a_gpu():
+    import json
+    import subprocess
+
+    import torch
+
+    if torch.cuda.is_available():
+        import pytest
+
+        pytest.skip("the reference arm would really run here")
+    root = Path(__file__).resolve().parents[1]
+    out = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "3"],
+                         capture_output=True, text=True, timeout=300, cwd=str(root))
+    assert out.returncode == 0
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
