@@ -71,3 +71,31 @@ def test_benchmark_shape_config_resolves_and_validates(tmp_path, monkeypatch, ca
     config = str(Path(__file__).resolve().parent.parent / "configs" / "wan22_ti2v_5b" / "stage0p5_sp8.yaml")
     assert main(["config", "resolve", "--config", config]) == 0
     assert '"sequence_parallel_size":8' in capsys.readouterr().out
+
+
+def test_train_from_a_preencoded_corpus_and_resume_exactly(tmp_path, monkeypatch):
+    """preencode (synthetic clips, codecs sized to the tiny DiT) -> train from the corpus index -> resume mid-run:
+    the resumed steps read the same samples and reproduce the same losses."""
+    cfg_dir = Path(__file__).resolve().parent.parent / "configs" / "wan22_ti2v_5b"
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "pre"))
+    assert main(["preencode", "--config", str(cfg_dir / "tiny_preencode_cpu.yaml"), "--set", "preencode.num_samples=5",
+                 "--set", "data.pixel_frames=81", "--set", "preencode.codecs={z_dim: 16, vae_base: 8, t5: {vocab: 512, dim: 256, dim_attn: 32, dim_ffn: 64, "
+                          "num_heads: 2, num_layers: 1, text_len: 32}}"]) == 0
+    index = tmp_path / "pre" / "encoded" / "index.jsonl"
+    assert index.is_file()
+    common = ["--config", CONFIG, "--set", "runtime.device=cpu", "--set", "data.source=index", "--set", f"data.index={index}",
+              "--set", "data.pixel_frames=81", "--set", "data.latent_height=4", "--set", "data.latent_width=4",
+              "--set", "train.ema={enabled: false}", "--set", "runtime.validate_every=0"]
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "a"))
+    assert main(["train", *common]) == 0
+    ev_a = {e["step"]: e for e in _events(tmp_path / "a") if e["event"] == "optimizer_step"}
+    ids = [tuple(m["identity"]["sample_ids"]) for s in sorted(ev_a) for m in ev_a[s]["microbatches"]]
+    assert len(ids) == 4 and all(i[0].startswith("synthetic-") for i in ids) and len(set(ids)) >= 3     # real corpus samples
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "b"))
+    assert main(["train", *common, "--set", "checkpoint.mode=full_resume", "--set",
+                 f"checkpoint.resume_from={tmp_path / 'a' / 'checkpoint_model_000002'}", "--set", "runtime.save_every=0"]) == 0
+    ev_b = {e["step"]: e for e in _events(tmp_path / "b") if e["event"] == "optimizer_step"}
+    assert sorted(ev_b) == [3, 4]
+    for s in (3, 4):
+        assert ev_b[s]["losses"] == ev_a[s]["losses"]
+        assert ev_b[s]["microbatches"][0]["identity"]["sample_ids"] == ev_a[s]["microbatches"][0]["identity"]["sample_ids"]
