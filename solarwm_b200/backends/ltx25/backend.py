@@ -219,9 +219,20 @@ class LTX25Backend:
         g = torch.Generator().manual_seed(int(data.get("seed", 0)))
         shape = (1, cfg.in_dim, int(data.get("latent_frames", 4)), int(data.get("latent_height", 8)), int(data.get("latent_width", 8)))
         losses = []
+        corpus = None
+        if str(data.get("source", "synthetic")) == "index":         # a pre-encoded corpus written by ``preencode``
+            from ..wan22.runtime import iter_encoded_samples
+
+            corpus = iter_encoded_samples(data)
         for _ in range(int(config["train"]["max_steps"])):
-            lat = torch.randn(shape, generator=g)
-            losses.append(float(tr.train_step(lat, torch.randn(1, cfg.text_len, cfg.text_dim, generator=g)).item()))
+            if corpus is not None:
+                row, enc = next(corpus)
+                if enc["latents"].shape[1] != cfg.in_dim or tuple(enc["text"].shape) != (cfg.text_len, cfg.text_dim):
+                    raise BackendContractError(f"{row.sample_id}: latents / text do not match the architecture")
+                lat, txt = enc["latents"].permute(1, 0, 2, 3).unsqueeze(0).float(), enc["text"].unsqueeze(0).float()
+            else:
+                lat, txt = torch.randn(shape, generator=g), torch.randn(1, cfg.text_len, cfg.text_dim, generator=g)
+            losses.append(float(tr.train_step(lat, txt).item()))
         return {"final_step": len(losses), "last_loss": losses[-1], "native_launches": ops.total_launches()}
 
     def infer(self, config):

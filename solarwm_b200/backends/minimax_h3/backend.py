@@ -106,10 +106,23 @@ class MiniMaxH3Backend:
 
         tr.model.checkpointing = activation_and_sharding_options(config["train"], 1)["checkpointing"]
         losses, t0 = [], time.time()
+        corpus = None
+        if str(data.get("source", "synthetic")) == "index":         # a pre-encoded corpus: first latent = anchor frame
+            from ..wan22.runtime import iter_encoded_samples
+
+            corpus = iter_encoded_samples(data)
         for step in range(int(config["train"]["max_steps"])):
-            s = h3_sample(latent_frames=int(data.get("latent_frames", 3)), height=int(data.get("latent_height", 8)),
-                          width=int(data.get("latent_width", 8)), prompt_len=int(data.get("prompt_len", 8)),
-                          text_dim=tr.model.cfg.text_dim, seed=step)
+            if corpus is not None:
+                row, enc = next(corpus)
+                lat = enc["latents"]                                 # [F, C, h, w]
+                if lat.shape[0] < 2 or tuple(enc["text"].shape[1:]) != (tr.model.cfg.text_dim,):
+                    raise BackendContractError(f"{row.sample_id}: needs >= 2 latent frames and text of width {tr.model.cfg.text_dim}")
+                s = {"target_latents": lat[1:].permute(1, 0, 2, 3).contiguous(), "anchor_latents": lat[:1].permute(1, 0, 2, 3).contiguous(),
+                     "prompt_embeds": enc["text"]}
+            else:
+                s = h3_sample(latent_frames=int(data.get("latent_frames", 3)), height=int(data.get("latent_height", 8)),
+                              width=int(data.get("latent_width", 8)), prompt_len=int(data.get("prompt_len", 8)),
+                              text_dim=tr.model.cfg.text_dim, seed=step)
             s["camera_w2c"] = torch.eye(4).repeat(s["target_latents"].shape[1] + 1, 1, 1)
             losses.append(float(tr.train_step(s).item()))
             print(f"[h3-stage0p5] step={step + 1} loss={losses[-1]:.5f} lr={tr.opt.lr:g} compute_time_s={time.time() - t0:.2f}")

@@ -47,12 +47,12 @@ def synthetic_batches(config, arch, device) -> Iterator[dict]:
         yield batch
 
 
-def encoded_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) -> Iterator[dict]:
-    """Batches out of a pre-encoded corpus (``data.source: index``): ``data.index`` is the corpus index written by the
-    pre-encoding run, shards sit under ``data.root`` (default: beside the index).  Every epoch is one seeded
-    permutation of the rows; occurrence v of the permutation belongs to logical DP rank ``v % dp_size`` (SP peers read
-    the same samples), incomplete trailing groups are dropped.  The iterator is a pure function of (index, seed,
-    rank), so a resumed run that replays its consumed-batch count reads on exactly where it stopped."""
+def iter_encoded_samples(data: Mapping[str, Any], dp_rank: int = 0, dp_size: int = 1):
+    """``(index row, {name: tensor})`` pairs of a pre-encoded corpus, forever: ``data.index`` is the corpus index
+    written by the pre-encoding run, shards sit under ``data.root`` (default: beside the index).  Every epoch is one
+    seeded permutation of the rows; occurrence v of the permutation belongs to logical DP rank ``v % dp_size`` (SP
+    peers read the same samples).  A pure function of (index, seed, rank): a resumed run that replays its consumed
+    count reads on exactly where it stopped."""
     import json as _json
     from pathlib import Path
 
@@ -63,7 +63,6 @@ def encoded_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) ->
     from ...preencode.contracts import EncoderContract
     from ...preencode.shards import read_encoded_sample
 
-    data = config["data"]
     index = Path(str(data["index"]))
     root = Path(str(data.get("root") or index.parent))
     rows = read_index(index)
@@ -73,32 +72,41 @@ def encoded_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) ->
     cpath = root / "encoder-contract.json"
     if cpath.exists():
         contract = EncoderContract.from_dict(_json.loads(cpath.read_text()))
-    frames = latent_frames(int(data["pixel_frames"]), PROFILES[config["model"]["family"]].vae_stride[0])
-    micro = int(config["train"].get("micro_batch_size", 1))
-    seed = int(data.get("seed", 0))
-    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
-    epoch = 0
+    seed, epoch = int(data.get("seed", 0)), 0
     while True:
         order = np.random.default_rng([seed, epoch]).permutation(len(rows))
         mine = [rows[int(i)] for v, i in enumerate(order) if v % dp_size == dp_rank]
-        if len(mine) < micro:
-            raise DataContractError(f"rank {dp_rank} owns {len(mine)} samples per epoch, fewer than micro_batch_size {micro}")
-        for g in range(0, len(mine) - micro + 1, micro):
-            group = mine[g:g + micro]
-            samples = [read_encoded_sample(root, r.values, contract) for r in group]
-            for r, smp in zip(group, samples):
-                lat, txt = smp["latents"], smp["text"]
-                if lat.dim() != 4 or lat.shape[0] < frames or lat.shape[1] != arch.out_dim:
-                    raise DataContractError(f"{r.sample_id}: latents {tuple(lat.shape)} do not provide [{frames}+, {arch.out_dim}, h, w]")
-                if tuple(txt.shape) != (arch.text_len, arch.text_dim):
-                    raise DataContractError(f"{r.sample_id}: text {tuple(txt.shape)} is not ({arch.text_len}, {arch.text_dim})")
-            batch = {"latents": torch.stack([smp["latents"][:frames] for smp in samples]).to(dtype),
-                     "text": torch.stack([smp["text"] for smp in samples]).to(dtype),
-                     "sample_ids": [r.sample_id for r in group], "start_frames": [0] * micro}
-            if device.type == "cuda":
-                batch = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in batch.items()}
-            yield batch
+        if not mine:
+            raise DataContractError(f"rank {dp_rank} of {dp_size} owns no sample of {index}")
+        for row in mine:
+            yield row, read_encoded_sample(root, row.values, contract)
         epoch += 1
+
+
+def encoded_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) -> Iterator[dict]:
+    """Training batches out of a pre-encoded corpus (``data.source: index``): ``micro_batch_size`` consecutive samples of
+    this rank's stream, checked against the architecture (latent channels, text geometry, enough latent frames)."""
+    from ...errors import DataContractError
+
+    data = config["data"]
+    frames = latent_frames(int(data["pixel_frames"]), PROFILES[config["model"]["family"]].vae_stride[0])
+    micro = int(config["train"].get("micro_batch_size", 1))
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    stream = iter_encoded_samples(data, dp_rank, dp_size)
+    while True:
+        group = [next(stream) for _ in range(micro)]
+        for r, smp in group:
+            lat, txt = smp["latents"], smp["text"]
+            if lat.dim() != 4 or lat.shape[0] < frames or lat.shape[1] != arch.out_dim:
+                raise DataContractError(f"{r.sample_id}: latents {tuple(lat.shape)} do not provide [{frames}+, {arch.out_dim}, h, w]")
+            if tuple(txt.shape) != (arch.text_len, arch.text_dim):
+                raise DataContractError(f"{r.sample_id}: text {tuple(txt.shape)} is not ({arch.text_len}, {arch.text_dim})")
+        batch = {"latents": torch.stack([smp["latents"][:frames] for _, smp in group]).to(dtype),
+                 "text": torch.stack([smp["text"] for _, smp in group]).to(dtype),
+                 "sample_ids": [r.sample_id for r, _ in group], "start_frames": [0] * micro}
+        if device.type == "cuda":
+            batch = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in batch.items()}
+        yield batch
 
 
 def activation_and_sharding_options(train: Mapping[str, Any], world_size: int) -> Mapping[str, Any]:

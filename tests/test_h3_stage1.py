@@ -212,3 +212,22 @@ def test_h3_backend_train_honours_activation_checkpointing_setting(tmp_path, mon
               "runtime": {"device": "cpu", "output_dir": str(tmp_path)}}
     out = load_backend("minimax_h3").train(config)
     assert out["final_step"] == 1 and seen and set(seen) == {"selective"}
+
+
+def test_h3_backend_trains_from_its_own_preencoded_corpus(tmp_path):
+    from solarwm_b200.registry import load_backend
+
+    be = load_backend("minimax_h3")
+    pre = {"data": {"pixel_frames": 9, "pixel_height": 64, "pixel_width": 64, "seed": 1}, "runtime": {"device": "cpu"},
+           "preencode": {"source": "synthetic", "num_samples": 2, "output_root": str(tmp_path / "enc"),
+                         "codecs": {"vae_base": 4, "t5": {"vocab": 512, "dim": 64, "dim_attn": 32, "dim_ffn": 64, "num_heads": 2,
+                                                         "num_layers": 1, "text_len": 8}}}}
+    assert be.preencode(pre)["samples"] == 2
+    config = {"schema": "solarwm.run.v1", "action": "train",
+              "model": {"family": "minimax_h3", "architecture": "tiny", "adapter": {"rank": 4}, "camera_translation_transform": "logd4"},
+              "data": {"source": "index", "index": str(tmp_path / "enc" / "index.jsonl"), "seed": 0, "pixel_frames": 158},
+              "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "max_steps": 2,
+                        "optimizer": {"lr": 1e-3}},
+              "runtime": {"device": "cpu", "output_dir": str(tmp_path / "run")}}
+    out = be.train(config)
+    assert out["final_step"] == 2 and out["last_loss"] == out["last_loss"]

@@ -110,3 +110,22 @@ def test_ltx_and_h3_preencode_share_the_corpus_assembly(tmp_path):
         assert c.family == family
         s = read_encoded_sample(out_root, rows[0].values, c)
         assert tuple(s["latents"].shape) == shape, s["latents"].shape
+
+
+def test_ltx_backend_trains_from_its_own_preencoded_corpus(tmp_path):
+    from solarwm_b200.registry import load_backend
+
+    be = load_backend("ltx25_video")
+    pre = {"data": {"pixel_frames": 9, "pixel_height": 64, "pixel_width": 64, "seed": 1}, "runtime": {"device": "cpu"},
+           "preencode": {"source": "synthetic", "num_samples": 2, "output_root": str(tmp_path / "enc"),
+                         "codecs": {"z_dim": 16, "vae_base": 4, "t5": {"vocab": 512, "dim": 64, "dim_attn": 32, "dim_ffn": 64,
+                                                                      "num_heads": 2, "num_layers": 1, "text_len": 16}}}}
+    assert be.preencode(pre)["samples"] == 2
+    config = {"schema": "solarwm.run.v1", "action": "train",
+              "model": {"family": "ltx25_video", "architecture": "tiny", "camera_translation_transform": "linear"},
+              "data": {"source": "index", "index": str(tmp_path / "enc" / "index.jsonl"), "seed": 0, "pixel_frames": 153},
+              "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "native_rectified_flow", "max_steps": 2,
+                        "optimizer": {"lr": 1e-3}},
+              "runtime": {"device": "cpu", "output_dir": str(tmp_path / "run")}}
+    out = be.train(config)
+    assert out["final_step"] == 2 and out["last_loss"] == out["last_loss"]
