@@ -259,7 +259,7 @@ def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
     from ...runtime.output_layout import checkpoint_model_dir, output_root
     from .checkpoint import build_contract
     from .contracts import architecture
-    from .runtime import synthetic_batches
+    from .runtime import encoded_batches, synthetic_batches
 
     dist_cfg = config.get("distributed", {}) or {}
     ctx = dist_init.initialize(int(dist_cfg.get("sequence_parallel_size", 1)),
@@ -276,10 +276,15 @@ def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
             chunk_frames=int(causal.get("chunk_frames", 3)), window_chunks=int(causal.get("window_chunks", 6)),
             sink_frames=int(causal.get("sink_frames", 0)),
             critic_updates_per_student=int(train.get("critic_updates_per_student", 5)),
-            guidance_scale=float(train.get("guidance_scale", 3.0)), seed=int(config["data"].get("seed", 0)))
+            guidance_scale=float(train.get("guidance_scale", 3.0)), seed=int(config["data"].get("seed", 0)),
+            ema_decay=(float(train["ema"]["decay"]) if (train.get("ema", {}) or {}).get("enabled") else None),
+            ema_start_step=int((train.get("ema", {}) or {}).get("start_step", 39)))
         dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
         trainer = WanStage2Trainer(arch, ctx.device, opts, sp=ctx.sp, dtype=dtype)
-        batches = synthetic_batches(config, arch, ctx.device)
+        if str(config["data"].get("source", "synthetic")) == "index":       # prompts (and the shape template) from a corpus
+            batches = encoded_batches(config, arch, ctx.device, ctx.topology.dp_rank, ctx.topology.dp_size)
+        else:
+            batches = synthetic_batches(config, arch, ctx.device)
         max_steps = int(config.get("runtime", {}).get("max_steps_override") or train["max_steps"])
         last = {}
         for _ in range(max_steps):
