@@ -12,6 +12,7 @@ import torch
 
 from ... import ops
 from ...engine.flow import FlowMatchScheduler
+from ...errors import BackendContractError
 from ...engine.inference_engine import GeneratedSample, InferenceCase, InferenceEngine
 from ...runtime.output_layout import output_root, public_validation_dir
 from ...runtime.randomness import stable_validation_seed
@@ -43,13 +44,36 @@ def sample_bidirectional(model, text, *, frames, height, width, steps=8, shift=5
 class WanLatentAdapter:
     def __init__(self, family: str, model, config: Mapping[str, Any]):
         self.family, self.model, self.config = family, model, config
+        self._text_encoder = None
+
+    def _embed(self, case: InferenceCase, dev):
+        """The prompt's embedding: through the configured text encoder (``inference.text_encoder``: a ``T5Config``
+        mapping, optionally with ``checkpoint``), else a seeded stand-in of the right shape (synthetic runs)."""
+        cfg = self.model.cfg
+        spec = (self.config.get("inference", {}) or {}).get("text_encoder")
+        if spec:
+            if self._text_encoder is None:
+                from ...models.t5 import T5Config, WanTextEncoder
+
+                spec = dict(spec)
+                ckpt = spec.pop("checkpoint", None)
+                enc = WanTextEncoder(T5Config(**spec), device=dev, dtype=torch.float32)
+                if ckpt:
+                    enc.model.load_state_dict(torch.load(ckpt, map_location=dev, weights_only=True))
+                self._text_encoder = enc
+            text = self._text_encoder([case.prompt])
+            if tuple(text.shape[1:]) != (cfg.text_len, cfg.text_dim):
+                raise BackendContractError(f"the text encoder yields {tuple(text.shape[1:])}, the model takes "
+                                           f"({cfg.text_len}, {cfg.text_dim})")
+            return text.to(dev, self.model.dtype)
+        g = torch.Generator().manual_seed(stable_validation_seed("prompt", case.prompt, case.sample_id) % (2 ** 31))
+        return torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(dev, self.model.dtype)
 
     def generate(self, case: InferenceCase, *, weights_id: str) -> GeneratedSample:
         inf = self.config.get("inference", {}) or {}
         cfg = self.model.cfg
         dev = next(self.model.parameters()).device
-        g = torch.Generator().manual_seed(stable_validation_seed("prompt", case.prompt, case.sample_id) % (2 ** 31))
-        text = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(dev, self.model.dtype)
+        text = self._embed(case, dev)
         lat, sigmas = sample_bidirectional(
             self.model, text, frames=int(inf.get("latent_frames", 5)), height=int(inf.get("latent_height", 16)),
             width=int(inf.get("latent_width", 16)), steps=int(inf.get("steps", 8)),
@@ -65,6 +89,13 @@ class WanLatentAdapter:
 
 def _cases(config, count):
     seed = int((config.get("validation", {}) or {}).get("noise_seed", 42))
+    prompts = (config.get("inference", {}) or {}).get("prompts")
+    if prompts:                                   # one case per given prompt
+        if not all(isinstance(p, str) and p.strip() for p in prompts):
+            raise BackendContractError("inference.prompts must be non-empty strings")
+        return [InferenceCase(slot=i, sample_id=f"case-{i:04d}", prompt=p.strip(), start_frame=0,
+                              noise_seed=stable_validation_seed(seed, i) % (2 ** 31), camera_fingerprint="none")
+                for i, p in enumerate(prompts)]
     return [InferenceCase(slot=i, sample_id=f"case-{i:04d}", prompt=f"synthetic prompt {i}", start_frame=0,
                           noise_seed=stable_validation_seed(seed, i) % (2 ** 31), camera_fingerprint="none")
             for i in range(count)]

@@ -99,3 +99,18 @@ def test_train_from_a_preencoded_corpus_and_resume_exactly(tmp_path, monkeypatch
     for s in (3, 4):
         assert ev_b[s]["losses"] == ev_a[s]["losses"]
         assert ev_b[s]["microbatches"][0]["identity"]["sample_ids"] == ev_a[s]["microbatches"][0]["identity"]["sample_ids"]
+
+
+def test_infer_with_prompts_and_a_text_encoder(tmp_path, monkeypatch):
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path))
+    enc = "{vocab: 512, dim: 256, dim_attn: 32, dim_ffn: 64, num_heads: 2, num_layers: 1, text_len: 32}"
+    assert main(["infer", "--config", CONFIG, "--set", "action=infer", "--set", "runtime.device=cpu", "--set", "inference.steps=2",
+                 "--set", "inference.prompts=[a harbour at dusk, a street in the rain]", "--set", f"inference.text_encoder={enc}"]) == 0
+    out = tmp_path / "generate"
+    assert (out / "slot-000000" / "latents.pt").is_file() and (out / "slot-000001" / "latents.pt").is_file()
+    manifest = json.loads((out / "slot-000001" / "manifest.json").read_text())
+    assert "rain" in json.dumps(manifest)
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "bad"))
+    wrong = "{vocab: 512, dim: 64, dim_attn: 32, dim_ffn: 64, num_heads: 2, num_layers: 1, text_len: 32}"
+    assert main(["infer", "--config", CONFIG, "--set", "action=infer", "--set", "runtime.device=cpu", "--set", "inference.steps=1",
+                 "--set", "inference.prompts=[x]", "--set", f"inference.text_encoder={wrong}"]) == 2
