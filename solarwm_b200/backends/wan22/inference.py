@@ -46,6 +46,49 @@ class WanLatentAdapter:
         self.family, self.model, self.config = family, model, config
         self._text_encoder = None
 
+    def _decode(self, latents):
+        """``inference.vae`` (``{z_dim, base, temporal_ups, checkpoint?, fps?, chunk_latent_frames?}``) turns the sampled latents
+        [1, F, C, H, W] into an MP4 (streaming chunk decode through the codec adapter, OpenCV's encoder)."""
+        spec = (self.config.get("inference", {}) or {}).get("vae")
+        if not spec:
+            return None
+        import os
+        import tempfile
+
+        import cv2
+
+        from ...models.vae import VAEConfig, VideoVAE
+        from .codec import WanVideoCodec
+
+        if getattr(self, "_codec", None) is None:
+            spec = dict(spec)
+            ckpt, self._fps = spec.pop("checkpoint", None), float(spec.pop("fps", 16.0))
+            self._chunk = int(spec.pop("chunk_latent_frames", 8))
+            if "temporal_ups" in spec:
+                spec["temporal_ups"] = tuple(bool(u) for u in spec["temporal_ups"])
+            vae = VideoVAE(VAEConfig(**spec)).to(latents.device, latents.dtype)
+            if ckpt:
+                vae.load_state_dict(torch.load(ckpt, map_location=latents.device, weights_only=True))
+            self._codec = WanVideoCodec(vae)
+        fd, path = tempfile.mkstemp(suffix=".mp4")
+        os.close(fd)
+        writer = None
+        try:
+            for piece in self._codec.decode_streaming_chunks(latents, chunk_latent_frames=self._chunk):
+                rgb = ((piece[0].permute(0, 2, 3, 1) * 0.5 + 0.5).clamp(0, 1) * 255).round().to(torch.uint8).numpy()   # [T, H, W, 3]
+                if writer is None:
+                    writer = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"mp4v"), self._fps, (rgb.shape[2], rgb.shape[1]))
+                    if not writer.isOpened():
+                        raise BackendContractError("the video encoder could not be opened")
+                for frame in rgb:
+                    writer.write(cv2.cvtColor(frame, cv2.COLOR_RGB2BGR))
+            if writer is not None:
+                writer.release()
+            with open(path, "rb") as fh:
+                return fh.read()
+        finally:
+            os.unlink(path)
+
     def _embed(self, case: InferenceCase, dev):
         """The prompt's embedding: through the configured text encoder (``inference.text_encoder``: a ``T5Config``
         mapping, optionally with ``checkpoint``), else a seeded stand-in of the right shape (synthetic runs)."""
@@ -80,8 +123,11 @@ class WanLatentAdapter:
             shift=float(self.config["model"].get("timestep_shift", 5.0)), seed=case.noise_seed)
         buf = io.BytesIO()
         torch.save(lat.float().cpu(), buf)
-        return GeneratedSample({"latents.pt": buf.getvalue(),
-                                "schedule.json": json.dumps({"sigmas": sigmas}).encode()},
+        artifacts = {"latents.pt": buf.getvalue(), "schedule.json": json.dumps({"sigmas": sigmas}).encode()}
+        video = self._decode(lat)
+        if video is not None:
+            artifacts["video.mp4"] = video
+        return GeneratedSample(artifacts,
                                tuple(lat.shape), str(lat.dtype).replace("torch.", ""),
                                metrics={"latent_abs_mean": float(lat.float().abs().mean())},
                                provenance={"sampler": "euler-flow", "steps": len(sigmas) - 1})

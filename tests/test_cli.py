@@ -114,3 +114,16 @@ def test_infer_with_prompts_and_a_text_encoder(tmp_path, monkeypatch):
     wrong = "{vocab: 512, dim: 64, dim_attn: 32, dim_ffn: 64, num_heads: 2, num_layers: 1, text_len: 32}"
     assert main(["infer", "--config", CONFIG, "--set", "action=infer", "--set", "runtime.device=cpu", "--set", "inference.steps=1",
                  "--set", "inference.prompts=[x]", "--set", f"inference.text_encoder={wrong}"]) == 2
+
+
+def test_infer_decodes_to_a_video_when_a_vae_is_configured(tmp_path, monkeypatch):
+    pytest.importorskip("cv2")
+    from solarwm_b200.data import raw_video
+
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path))
+    assert main(["infer", "--config", CONFIG, "--set", "action=infer", "--set", "runtime.device=cpu", "--set", "inference.steps=1",
+                 "--set", "inference.latent_frames=3", "--set", "inference.latent_height=4", "--set", "inference.latent_width=6",
+                 "--set", "inference.vae={z_dim: 16, base: 8, temporal_ups: [true, false], fps: 8}"]) == 0
+    blob = (tmp_path / "generate" / "slot-000000" / "video.mp4").read_bytes()
+    info = raw_video.probe(blob)
+    assert info["frames"] == 5 and (info["height"], info["width"]) == (16, 24)        # 1 + 2 * 2 frames, 4 x spatial
