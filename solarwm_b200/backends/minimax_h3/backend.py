@@ -228,10 +228,30 @@ class MiniMaxH3Backend:
             raise BackendContractError("inference.conditions (a .pt file) is required unless inference.source is synthetic")
         out_dir = output_root(config) / "generate"
         out_dir.mkdir(parents=True, exist_ok=True)
+        decoder = sink = None
+        if inf.get("decoder"):                      # ``inference.decoder``: a ``ViTDecoderConfig`` mapping (+ ``checkpoint``)
+            from ...models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+            from ...serve.media import FrameSink
+
+            spec = dict(inf["decoder"])
+            ckpt = spec.pop("checkpoint", None)
+            vcfg = ViTDecoderConfig(latent_channels=scfg.latent_channels, **spec)
+            vit = ViTVideoDecoder(vcfg, device=dev, dtype=model.dtype, seed=0)
+            if ckpt:
+                vit.load_state_dict(torch.load(ckpt, map_location=dev, weights_only=True))
+            decoder = StreamingViTDecoder(vit, (2 * gh, 2 * gw))
+            frame_sink = FrameSink(out_dir / "frames", 2 * gw * vcfg.patch, 2 * gh * vcfg.patch, use_ffmpeg=False)
+
+            def sink(frames):                       # [3, F, H, W] in [-1, 1] -> one RGB8 frame at a time
+                for f in range(frames.shape[1]):
+                    frame_sink.push((frames[:, f].float().clamp(-1, 1) * 0.5 + 0.5))
         manifest = generate_full_length(model, text=cond["text"], anchor_latent=cond["anchor_latent"], c2w=cond["c2w"],
                                         intrinsics=cond["intrinsics"], stream_cfg=scfg, use_memory=use_memory,
-                                        top_k=int(inf.get("top_k", 2)), out_dir=out_dir)
+                                        top_k=int(inf.get("top_k", 2)), out_dir=out_dir, decoder=decoder, frame_sink=sink)
+        if decoder is not None:
+            manifest = dict(manifest, video=frame_sink.close())
         return {"output_dir": str(out_dir), "chunks": manifest.get("chunks"), "frames": manifest.get("frames"),
+                "video": manifest.get("video"),
                 "native_launches": ops.total_launches()}
 
     def preencode(self, config):

@@ -231,3 +231,15 @@ def test_h3_backend_trains_from_its_own_preencoded_corpus(tmp_path):
               "runtime": {"device": "cpu", "output_dir": str(tmp_path / "run")}}
     out = be.train(config)
     assert out["final_step"] == 2 and out["last_loss"] == out["last_loss"]
+
+
+def test_h3_backend_infer_decodes_frames_when_a_decoder_is_configured(tmp_path):
+    from solarwm_b200.registry import load_backend
+
+    config = {"model": {"family": "minimax_h3", "architecture": "tiny", "camera_translation_transform": "logd4"},
+              "runtime": {"output_dir": str(tmp_path / "run"), "device": "cpu"},
+              "inference": {"source": "synthetic", "grid_hw": [2, 3], "chunk_latents": 2, "chunks": 2, "denoise_steps": 1,
+                            "decoder": {"dim": 64, "depth": 1, "heads": 2, "dim_head": 32, "ffn_dim": 128, "registers": 2, "patch": 2}}}
+    out = load_backend("minimax_h3").infer(config)
+    assert out["frames"] > 0 and out["video"]["frames"] == out["frames"]
+    assert (tmp_path / "run" / "generate" / "frames" / "video.rgb").stat().st_size == out["frames"] * (4 * 2) * (6 * 2) * 3
