@@ -231,7 +231,7 @@ class MiniMaxH3Backend:
         decoder = sink = None
         if inf.get("decoder"):                      # ``inference.decoder``: a ``ViTDecoderConfig`` mapping (+ ``checkpoint``)
             from ...models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
-            from ...serve.media import FrameSink
+            from ...serve.media import SIGNED_UNIT, FrameSink
 
             spec = dict(inf["decoder"])
             ckpt = spec.pop("checkpoint", None)
@@ -240,11 +240,12 @@ class MiniMaxH3Backend:
             if ckpt:
                 vit.load_state_dict(torch.load(ckpt, map_location=dev, weights_only=True))
             decoder = StreamingViTDecoder(vit, (2 * gh, 2 * gw))
-            frame_sink = FrameSink(out_dir / "frames", 2 * gw * vcfg.patch, 2 * gh * vcfg.patch, use_ffmpeg=False)
+            frame_sink = FrameSink(out_dir / "frames", 2 * gw * vcfg.patch, 2 * gh * vcfg.patch, use_ffmpeg=False,
+                                   normalization=SIGNED_UNIT)
 
             def sink(frames):                       # [3, F, H, W] in [-1, 1] -> one RGB8 frame at a time
                 for f in range(frames.shape[1]):
-                    frame_sink.push((frames[:, f].float().clamp(-1, 1) * 0.5 + 0.5))
+                    frame_sink.push(frames[:, f])
         manifest = generate_full_length(model, text=cond["text"], anchor_latent=cond["anchor_latent"], c2w=cond["c2w"],
                                         intrinsics=cond["intrinsics"], stream_cfg=scfg, use_memory=use_memory,
                                         top_k=int(inf.get("top_k", 2)), out_dir=out_dir, decoder=decoder, frame_sink=sink)

@@ -15,17 +15,24 @@ import torch
 from .. import ops
 
 
-def frame_to_rgb8(frame_chw: torch.Tensor) -> np.ndarray:
+SIGNED_UNIT = ((0.5, 0.5, 0.5), (0.5, 0.5, 0.5))      # (mean, std) that maps decoder output in [-1, 1] to [0, 1]
+
+
+def frame_to_rgb8(frame_chw: torch.Tensor, normalization=None) -> np.ndarray:
     """bf16 [3, H, W] -> uint8 [H, W, 3]; conversion happens on the tensor's device, only the 8-bit
-    pixels cross PCIe.  Raises on non-finite pixels."""
-    rgb, flag = ops.rgb8(frame_chw.to(torch.bfloat16))
+    pixels cross PCIe.  ``normalization`` = (mean, std) of the pixel = x * std + mean step (default: the conversion
+    kernel's own constants; ``SIGNED_UNIT`` for frames in [-1, 1]).  Raises on non-finite pixels."""
+    kw = {} if normalization is None else {"mean": tuple(normalization[0]), "std": tuple(normalization[1])}
+    rgb, flag = ops.rgb8(frame_chw.to(torch.bfloat16), **kw)
     if flag is not None and int(flag.item()) != 0:
         raise FloatingPointError("nonfinite RGB pixel")
     return rgb.cpu().numpy()
 
 
 class FrameSink:
-    def __init__(self, out_dir, width: int, height: int, fps: float = 16.0, use_ffmpeg: Optional[bool] = None):
+    def __init__(self, out_dir, width: int, height: int, fps: float = 16.0, use_ffmpeg: Optional[bool] = None,
+                 normalization=None):
+        self.normalization = normalization
         self.dir = Path(out_dir)
         self.dir.mkdir(parents=True, exist_ok=True)
         self.width, self.height, self.fps = width, height, fps
@@ -41,7 +48,7 @@ class FrameSink:
             self.raw = (self.dir / "video.rgb").open("wb")
 
     def push(self, frame_chw: torch.Tensor) -> None:
-        rgb = frame_to_rgb8(frame_chw)
+        rgb = frame_to_rgb8(frame_chw, self.normalization)
         if rgb.shape[:2] != (self.height, self.width):
             raise ValueError(f"frame is {rgb.shape[:2]}, sink expects {(self.height, self.width)}")
         (self.proc.stdin if self.proc else self.raw).write(rgb.tobytes())

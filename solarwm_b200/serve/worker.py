@@ -147,11 +147,12 @@ def run(args) -> int:
             def on_piece(_chunk, _offset, frames, _ns):
                 nonlocal sink
                 if sink is None:
-                    from .media import FrameSink
+                    from .media import SIGNED_UNIT, FrameSink
 
-                    sink = FrameSink(out_dir / "frames", frames.shape[-1], frames.shape[-2], use_ffmpeg=False)
+                    sink = FrameSink(out_dir / "frames", frames.shape[-1], frames.shape[-2], use_ffmpeg=False,
+                                     normalization=SIGNED_UNIT)        # decoder output lives in [-1, 1]
                 for f in range(frames.shape[1]):
-                    sink.push(frames[:, f].float().clamp(-1, 1) * 0.5 + 0.5 if args.decoder == "conv" else frames[:, f].float())
+                    sink.push(frames[:, f])
                     decoded["frames"] += 1
 
             return decoders.push(index, latents[0].contiguous(), on_piece)

@@ -107,3 +107,18 @@ def test_frame_sink_writes_raw_rgb_and_checks_geometry(tmp_path):
     store = FragmentStore(keep=2)
     ids = [store.add(bytes([i])) for i in range(3)]
     assert ids == [0, 1, 2] and [i for i, _ in store.since(0)] == [1, 2]
+
+
+def test_frame_sink_normalization_maps_signed_unit_frames_to_full_range(tmp_path):
+    import numpy as np
+
+    from solarwm_b200.serve.media import SIGNED_UNIT, FrameSink, frame_to_rgb8
+
+    frame = torch.stack([torch.full((4, 4), -1.0), torch.zeros(4, 4), torch.ones(4, 4)])
+    rgb = frame_to_rgb8(frame, SIGNED_UNIT)
+    assert rgb.shape == (4, 4, 3) and (rgb[..., 0] == 0).all() and (rgb[..., 2] == 255).all() and abs(int(rgb[0, 0, 1]) - 128) <= 1
+    sink = FrameSink(tmp_path, 4, 4, use_ffmpeg=False, normalization=SIGNED_UNIT)
+    sink.push(frame)
+    sink.close()
+    raw = np.frombuffer((tmp_path / "video.rgb").read_bytes(), np.uint8).reshape(4, 4, 3)
+    assert np.array_equal(raw, rgb)
