@@ -251,3 +251,46 @@ def test_scene_rejection_is_agreed_before_any_device_work_and_parks(tmp_path):
     assert "tokens" in check_scene({"text": torch.randn(0, 16), "anchor_latent": torch.randn(4, 1, 4, 6)}, **kw)
     assert "anchor" in check_scene({"text": torch.randn(3, 16), "anchor_latent": torch.randn(4, 1, 4, 5)}, **kw)
     assert "embedding" in check_scene({"text": torch.randn(3, 8), "anchor_latent": torch.randn(4, 1, 4, 6)}, **kw)
+
+
+def _corpus_dp_worker(rank, world, path, out, index):
+    import json
+    import os
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world))
+    _init(rank, world, path)
+    from solarwm_b200.backends.wan22.runtime import run_training
+
+    root = f"{out}-run"
+    config = {"schema": "solarwm.run.v1", "action": "train", "name": "dp-corpus",
+              "model": {"family": "wan22_ti2v_5b", "architecture": "tiny", "timestep_shift": 5.0, "nonzero_head_init": True,
+                        "camera_translation_transform": "linear"},
+              "data": {"source": "index", "index": index, "seed": 0, "pixel_frames": 81, "latent_height": 4, "latent_width": 4},
+              "distributed": {"world_size": 2, "sequence_parallel_size": 1},
+              "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "micro_batch_size": 1,
+                        "grad_accum": 1, "global_batch_size": 2, "max_steps": 2, "warmup_steps": 0,
+                        "optimizer": {"lr": 1e-3, "betas": [0.9, 0.95], "eps": 1e-8, "weight_decay": 0.01, "grad_clip": 1.0}},
+              "checkpoint": {"mode": "none"}, "runtime": {"output_dir": root, "device": "cpu", "save_every": 0, "validate_every": 0}}
+    result = run_training(config)
+    events = [json.loads(l) for l in open(os.path.join(root, "events", f"rank-{rank:05d}.jsonl"))]
+    ids = [m["identity"]["sample_ids"][0] for e in events if e["event"] == "optimizer_step" for m in e["microbatches"]]
+    norms = [e["gradient_norm"] for e in events if e["event"] == "optimizer_step"]
+    torch.save({"ids": ids, "norms": norms, "final": result["final_step"]}, f"{out}.{rank}")
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def test_data_parallel_ranks_read_disjoint_corpus_samples(tmp_path):
+    from solarwm_b200.backends.wan22.preencode import run_preencode
+
+    pre = {"data": {"pixel_frames": 81, "pixel_height": 32, "pixel_width": 32, "seed": 3}, "runtime": {"device": "cpu"},
+           "preencode": {"source": "synthetic", "num_samples": 4, "output_root": str(tmp_path / "enc"), "samples_per_shard": 2,
+                         "codecs": {"z_dim": 16, "vae_base": 8, "t5": {"vocab": 512, "dim": 256, "dim_attn": 32, "dim_ffn": 64,
+                                                                      "num_heads": 2, "num_layers": 1, "text_len": 32}}}}
+    assert run_preencode(pre, "wan22_ti2v_5b")["samples"] == 4
+    out = str(tmp_path / "dp")
+    mp.spawn(_corpus_dp_worker, args=(2, str(tmp_path / "rdv"), out, str(tmp_path / "enc" / "index.jsonl")), nprocs=2, join=True)
+    got = [torch.load(f"{out}.{r}", weights_only=True) for r in range(2)]
+    assert got[0]["final"] == got[1]["final"] == 2
+    assert len(got[0]["ids"]) == 2 and not set(got[0]["ids"]) & set(got[1]["ids"])          # disjoint ownership
+    assert got[0]["norms"] == got[1]["norms"]                                               # one all-reduced gradient
