@@ -83,9 +83,8 @@ def test_train_from_a_preencoded_corpus_and_resume_exactly(tmp_path, monkeypatch
                           "num_heads: 2, num_layers: 1, text_len: 32}}"]) == 0
     index = tmp_path / "pre" / "encoded" / "index.jsonl"
     assert index.is_file()
-    common = ["--config", CONFIG, "--set", "runtime.device=cpu", "--set", "data.source=index", "--set", f"data.index={index}",
-              "--set", "data.pixel_frames=81", "--set", "data.latent_height=4", "--set", "data.latent_width=4",
-              "--set", "train.ema={enabled: false}", "--set", "runtime.validate_every=0"]
+    monkeypatch.setenv("SOLAR_CORPUS_INDEX", str(index))
+    common = ["--config", str(cfg_dir / "tiny_train_from_corpus_cpu.yaml"), "--set", "runtime.device=cpu"]
     monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "a"))
     assert main(["train", *common]) == 0
     ev_a = {e["step"]: e for e in _events(tmp_path / "a") if e["event"] == "optimizer_step"}
