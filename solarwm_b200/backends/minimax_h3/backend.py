@@ -215,6 +215,29 @@ class MiniMaxH3Backend:
                               memory_latents=int(inf.get("top_k", 2)) if use_memory else 0, seed=int(inf.get("seed", 0)))
         if inf.get("conditions"):
             cond = torch.load(inf["conditions"], map_location="cpu", weights_only=True)
+        elif str(inf.get("source", "synthetic")) == "index":
+            # prompt and anchor frame of a pre-encoded sample (``inference.sample``: its position in the corpus index),
+            # a straight dolly path unless ``inference.cameras`` (.pt with c2w / intrinsics) is given
+            from ...data.index import read_index
+            from ...preencode.shards import read_encoded_sample
+            from pathlib import Path as _P
+
+            index = _P(str(config["data"]["index"]))
+            rows = read_index(index)
+            row = rows[int(inf.get("sample", 0)) % len(rows)]
+            enc = read_encoded_sample(_P(str(config["data"].get("root") or index.parent)), row.values)
+            anchor = enc["latents"][:1].permute(1, 0, 2, 3).contiguous()             # [C, 1, H, W]
+            if tuple(anchor.shape) != (scfg.latent_channels, 1, 2 * gh, 2 * gw):
+                raise BackendContractError(f"{row.sample_id}: anchor latent {tuple(anchor.shape)} does not fit grid_hw {(gh, gw)}")
+            n = 1 + k * chunks
+            if inf.get("cameras"):
+                cams = torch.load(inf["cameras"], map_location="cpu", weights_only=True)
+                c2w, K = cams["c2w"][:n], cams["intrinsics"][:n]
+            else:
+                c2w = torch.eye(4).repeat(n, 1, 1)
+                c2w[:, 2, 3] = torch.arange(n) * 0.05
+                K = torch.tensor([[0.505, 0.0, 0.5], [0.0, 0.898, 0.5], [0.0, 0.0, 1.0]]).repeat(n, 1, 1)
+            cond = {"text": enc["text"], "anchor_latent": anchor, "c2w": c2w, "intrinsics": K}
         elif str(inf.get("source", "synthetic")) == "synthetic":
             g = torch.Generator().manual_seed(int(inf.get("seed", 0)) + 17)
             n = 1 + k * chunks

@@ -231,6 +231,11 @@ def test_h3_backend_trains_from_its_own_preencoded_corpus(tmp_path):
               "runtime": {"device": "cpu", "output_dir": str(tmp_path / "run")}}
     out = be.train(config)
     assert out["final_step"] == 2 and out["last_loss"] == out["last_loss"]
+    # the same corpus conditions a camera-length generation: prompt + anchor frame of sample 1
+    infer = dict(config, action="infer", runtime={"device": "cpu", "output_dir": str(tmp_path / "gen")},
+                 inference={"source": "index", "sample": 1, "grid_hw": [2, 2], "chunk_latents": 2, "chunks": 2, "denoise_steps": 1})
+    got = be.infer(infer)
+    assert got["chunks"] == 2 and (tmp_path / "gen" / "generate" / "manifest.json").is_file()
 
 
 def test_h3_backend_infer_decodes_frames_when_a_decoder_is_configured(tmp_path):
