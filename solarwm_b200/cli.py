@@ -140,6 +140,8 @@ def data_command(args) -> int:
         return 0
     resolved = load_config(args.config, args.overrides)
     data = resolved.values["data"]
+    if not data.get("index"):
+        raise ConfigurationError("this command reads the corpus index: set data.index (synthetic runs have no plan)")
     rows = index_mod.read_index(data["index"])
     if args.data_command == "warm-cache":
         from .data.prefetch import warm_cache
