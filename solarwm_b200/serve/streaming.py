@@ -143,12 +143,16 @@ class StreamingGenerator:
         if self.device.type == "cuda":
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
+        import time
+
+        t0 = time.perf_counter()
         out = self._chunk_graph(f) if use_graph else self._chunk_eager(f)
-        ms = 0.0
         if self.device.type == "cuda":
             b.record()
             b.synchronize()
             ms = a.elapsed_time(b)
+        else:
+            ms = (time.perf_counter() - t0) * 1e3              # host clock on CPU
         self.stats.append(ChunkStats(self.index, ms, use_graph))
         self.index += 1
         return out
