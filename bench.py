@@ -63,6 +63,9 @@ def parse_args():
                     help="after the timed region, run one more step under the phase timer and add the forward / "
                          "backward / optimizer split (CUDA events) to the JSON line")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="capture the whole training step in one CUDA graph and replay it (auto: on with the fused "
+                         "transports at N > 1, where the step contains no library collective)")
     ap.add_argument("--sp-transport", default="fused", choices=["fused", "nccl"],
                     help="Ulysses exchange: fused into the kernels over NVLink peer memory, or NCCL all-to-all")
     return ap.parse_args()
@@ -237,9 +240,11 @@ def run_ours(args):
                                      zero_on=world > 1 and args.zero != "off", checkpointing=ckpt,
                                      keep_blocks=args.keep_blocks, lean_mode=args.lean)
     zero = world > 1 and args.zero != "off"
+    graph = args.graph == "on" or (args.graph == "auto" and world > 1 and args.sp_transport == "fused"
+                                   and args.zero == "fused")
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
                            keep_blocks=keep, lean_kept=lean, max_grad_norm=1.0, seed=0, zero=zero,
-                           zero_transport=args.zero)
+                           zero_transport=args.zero, cuda_graph=graph)
     model = heap = None
     if zero:
         from solarwm_b200.models.wan import WanDiT
@@ -248,7 +253,7 @@ def run_ours(args):
         if args.zero == "fused":
             from solarwm_b200.parallel.symm import SymmetricHeap
 
-            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()), None)
+            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()) + (1 << 16), None)
     trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp, model=model, heap=heap)
     with torch.no_grad():  # a zero head would zero every upstream gradient; keep the step representative
         trainer.model.get_parameter("head.head.weight").normal_(0, 0.02)
@@ -309,6 +314,7 @@ def run_ours(args):
             "config": {"model": {"ti2v_5b": "wan22_ti2v_5b-shaped", "ltx_2b": "ltx_video_2b-shaped"}.get(args.model, "small-debug"),
                        "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
                        "optimizer_sharding": (f"zero-{args.zero}" if zero else "none"),
+                       "cuda_graph_step": bool(graph),
                        "latent": [1, cfg.in_dim, args.frames, args.height, args.width],
                        "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt, "keep_blocks": keep,
                        "lean_resident_blocks": lean,

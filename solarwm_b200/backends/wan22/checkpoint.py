@@ -27,9 +27,18 @@ def build_contract(config: Mapping[str, Any], route, sp_size: int) -> Checkpoint
         extras={"timestep_shift": float(model.get("timestep_shift", 5.0))})
 
 
-def save_checkpoint(root, step: int, *, model, optimizer, scheduler, contract: CheckpointContract, config,
+def save_checkpoint(root, step: int, *, model, scheduler, contract: CheckpointContract, config,
                     ema_state: Optional[Mapping[str, Any]], ema_num_updates: int, rank_states, is_main: bool,
-                    barrier=None) -> str:
+                    barrier=None, optimizer=None, optimizer_state=None) -> str:
+    """``optimizer_state``: the un-sharded ``optimizer.state_dict()`` gathered by the caller on every rank (a sharded
+    optimizer's ``state_dict`` is a collective, so it cannot be called from the main rank alone); ``optimizer`` is
+    accepted for single-rank callers and read here."""
+    if optimizer_state is None and is_main:
+        if optimizer is None:
+            raise CheckpointError("save_checkpoint needs optimizer_state (or an unsharded optimizer)")
+        if getattr(optimizer, "shard_world", 1) != 1:
+            raise CheckpointError("a sharded optimizer's state must be gathered by every rank before saving")
+        optimizer_state = optimizer.state_dict()
     target = checkpoint_model_dir(root, step)
     ident = ""
     if is_main:
@@ -37,7 +46,7 @@ def save_checkpoint(root, step: int, *, model, optimizer, scheduler, contract: C
             payload = {
                 "generator": {k: v.detach().cpu() for k, v in model.state_dict().items()},
                 "generator_ema": None if ema_state is None else {k: v.detach().cpu() for k, v in ema_state.items()},
-                "optimizer": optimizer.state_dict(),
+                "optimizer": optimizer_state,
                 "scheduler": scheduler.state_dict(),
                 "global_step": int(step),
                 "config": dict(config),

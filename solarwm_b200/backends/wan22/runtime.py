@@ -256,7 +256,7 @@ class WanStage0p5Runtime:
         if want_zero:
             from ...parallel.symm import SymmetricHeap
 
-            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()), None)
+            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()) + (1 << 16), None)
         return sp_ctx, heap
 
     def zero_grad(self) -> None:
@@ -303,7 +303,26 @@ class WanStage0p5Runtime:
         tr.optimizer.set_clip(norm, tr.opts.max_grad_norm)
         value = float(norm.item())
         tr.last_grad_norm = norm
+        self._check_device_waits(value)
         return GradientStatus(finite=value == value and value not in (float("inf"), float("-inf")), norm=value)
+
+    def _check_device_waits(self, norm_value: float) -> None:
+        """The fused transports' device-side waits are bounded: one that gives up sets a status word and lets the
+        consumer kernels run on whatever had arrived.  The sharded optimizer folds a non-zero word of ANY rank into
+        the gradient norm as infinity, so the common path costs nothing; on a non-finite norm every rank reads its own
+        word and all ranks raise the same message together, before the update and before any checkpoint."""
+        tr = self.trainer
+        fused = getattr(tr.sp, "fused", False) or getattr(tr.optimizer, "transport", "") == "fused"
+        if not fused or self.ctx.device.type != "cuda":
+            return
+        if norm_value == norm_value and norm_value not in (float("inf"), float("-inf")):
+            return
+        import torch.distributed as dist
+
+        from ... import ops
+
+        rdist.raise_if_device_wait_failed(ops.read_status(self.ctx.device),
+                                          dist=dist if self.ctx.topology.raw_world_size > 1 else None)
 
     def optimizer_step(self) -> None:
         self.trainer.optimizer.step()
@@ -330,18 +349,23 @@ class WanStage0p5Runtime:
         if topo.raw_world_size > 1:
             states = [None] * topo.raw_world_size
             dist.all_gather_object(states, state)
+        # the optimizer state is gathered into the un-sharded layout on every rank (a collective when the optimizer is
+        # sharded); the EMA weights are named out of the same gathered tensors
+        opt_state = self.trainer.optimizer.state_dict()
         ema_state = None
         if self.trainer.optimizer.ema_decay is not None:
             from ...engine.ema import FlatEMAView
 
-            ema_state = FlatEMAView(self.trainer.model, self.trainer.optimizer).state_dict()
+            ema_state = FlatEMAView(self.trainer.model, self.trainer.optimizer, gathered=opt_state).state_dict()
+        if not topo.is_main:
+            opt_state = ema_state = None
 
         def agree(ident):
             return rdist.collective_rank_zero_call(lambda: ident, dist=dist if topo.raw_world_size > 1 else None,
                                                    label="checkpoint commit")
 
         ident = ckpt.save_checkpoint(output_root(self.config), step, model=self.trainer.model,
-                                     optimizer=self.trainer.optimizer, scheduler=self.scheduler,
+                                     optimizer_state=opt_state, scheduler=self.scheduler,
                                      contract=self.contract, config=self.config, ema_state=ema_state,
                                      ema_num_updates=self.trainer.optimizer.step_count, rank_states=states,
                                      is_main=topo.is_main, barrier=agree)

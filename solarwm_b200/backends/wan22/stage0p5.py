@@ -42,6 +42,9 @@ class Stage0p5Options:
     lean_kept: bool = False          # resident blocks rebuild their norm outputs / FFN hidden in backward
     zero: bool = False                 # shard optimizer state + gradient reduction over all ranks (own FSDP)
     zero_transport: str = "collective"  # or "fused" (NVLink peer reduce / push; needs a symmetric heap)
+    cuda_graph: bool = False           # capture the whole step (forward, backward, optimizer) once and replay it; needs
+                                       # the fused transports (no library collective inside the step) and grad_accum 1
+    graph_warmup_steps: int = 2        # eager steps before the capture (lazy initialisation happens there)
     seed: int = 0
 
 
@@ -68,6 +71,9 @@ class WanStage0p5Trainer:
             self.optimizer = ZeroAdamW(self.model.units(), None, transport=opts.zero_transport, heap=heap, **okw)
         else:
             self.optimizer = FlatAdamW(self.model.units(), **okw)
+        if hasattr(self.optimizer, "unit_ready") and opts.grad_accum == 1:
+            # the sharded optimizer reduces a block's gradients as soon as the block's backward is done
+            self.model.grad_ready_hook = self.optimizer.unit_ready
         self.scheduler = FlowMatchScheduler(shift=opts.timestep_shift)
         self.gen = torch.Generator(device=self.device).manual_seed(opts.seed * 100003)
         self.global_step = 0
@@ -89,7 +95,10 @@ class WanStage0p5Trainer:
         t_video = self.sample_timesteps(B)
         noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32).to(latents.dtype)
         dropped = torch.rand(B, generator=self.gen, device=self.device) < o.image_dropout
-        if self.sp is not None and self.sp.size > 1:
+        if self.sp is not None and self.sp.size > 1 and not getattr(self.sp, "fused", False):
+            # SP peers must consume identical samples.  The collective transport broadcasts them; under the fused
+            # transport the peers draw from identically seeded generators (``objective_seed`` depends on the DP rank
+            # only) and the engine compares their identity fingerprints on the host, so the step needs no collective.
             d8 = dropped.to(torch.uint8)
             self.sp.broadcast_(t_video, noise, d8)
             dropped = d8.bool()
@@ -142,6 +151,8 @@ class WanStage0p5Trainer:
 
     def train_step(self, batch: dict) -> torch.Tensor:
         """batch: pinned host (or device) tensors ``latents`` [B,F,C,H,W], ``text`` [B,T,text_dim], optional ``y``."""
+        if self.opts.cuda_graph and self.device.type == "cuda":
+            return self._graphed_step(batch)
         dev = self.device
         lat = batch["latents"].to(dev, non_blocking=True)
         txt = batch["text"].to(dev, non_blocking=True)
@@ -150,3 +161,74 @@ class WanStage0p5Trainer:
         loss = self.microbatch(lat, txt, y)
         self.optimizer_step()
         return loss
+
+    # -- whole-step CUDA graph --------------------------------------------------------------------------------------
+    def _graph_supported(self) -> Optional[str]:
+        opt = self.optimizer
+        if self.opts.grad_accum != 1:
+            return "gradient accumulation"
+        if self.sp_size * self.dp_size == 1:
+            return "one rank (the unsharded optimizer passes its step-dependent scalars by value)"
+        if self.sp_size * self.dp_size > 1:
+            if not getattr(self.sp, "fused", False) or self.dp_size > 1:
+                return "a library collective inside the step (needs the fused sequence-parallel transport, dp 1)"
+            if not (hasattr(opt, "begin_step_host") and getattr(opt, "transport", "") == "fused"):
+                return "a library collective inside the optimizer (needs the fused sharded optimizer)"
+        return None
+
+    def _graphed_step(self, batch: dict) -> torch.Tensor:
+        """The step as ONE replayed CUDA graph: inputs are copied into fixed device buffers, the graph runs sampling,
+        forward, backward, the overlapped reduce-scatter, clipping and the sharded AdamW, and the loss is read from a
+        fixed device scalar.  The first ``graph_warmup_steps`` calls run eagerly; the capture happens on the next one.
+        Learning rate and bias corrections reach the captured optimizer through pinned host memory."""
+        why = self._graph_supported()
+        if why is not None:
+            raise RuntimeError(f"cuda_graph is not available with {why}")
+        st = self.__dict__.setdefault("_graph_state", {"eager": 0, "graph": None})
+        keys = [k for k in ("latents", "text", "y") if batch.get(k) is not None]
+        if st["graph"] is None and st["eager"] < int(self.opts.graph_warmup_steps):
+            st["eager"] += 1
+            dev = self.device
+            loss = self.microbatch(batch["latents"].to(dev, non_blocking=True), batch["text"].to(dev, non_blocking=True),
+                                   None if batch.get("y") is None else batch["y"].to(dev, non_blocking=True))
+            self.optimizer_step()
+            return loss
+        opt = self.optimizer
+        fused_opt = hasattr(opt, "begin_step_host") and getattr(opt, "transport", "") == "fused" and opt.world > 1
+        if st["graph"] is None:
+            st["inputs"] = {k: torch.empty(batch[k].shape, dtype=batch[k].dtype, device=self.device) for k in keys}
+            for k in keys:
+                st["inputs"][k].copy_(batch[k], non_blocking=True)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            graph.register_generator_state(self.gen)
+            if fused_opt:
+                opt.begin_step_host()
+                opt._host_prepared = True
+            step_before = self.global_step
+            counted = dict(ops.COUNTERS)
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                loss = self.microbatch(st["inputs"]["latents"], st["inputs"]["text"], st["inputs"].get("y"))
+                norm = self.optimizer_step()
+            self.global_step = step_before
+            # the launch counters advanced while capturing although nothing ran: take that back, and add the same
+            # amounts at every replay instead (a replay launches exactly the captured kernels)
+            per_replay = {k: v - counted.get(k, 0) for k, v in ops.COUNTERS.items() if v != counted.get(k, 0)}
+            for k, v in per_replay.items():
+                ops.COUNTERS[k] -= v
+            st.update(graph=graph, loss=loss, norm=norm, keys=keys, per_replay=per_replay)
+        else:
+            if keys != st["keys"] or any(batch[k].shape != st["inputs"][k].shape for k in keys):
+                raise RuntimeError("a captured step replays one batch geometry; this batch differs")
+            for k in keys:
+                st["inputs"][k].copy_(batch[k], non_blocking=True)
+            if fused_opt:
+                opt.begin_step_host()
+            elif hasattr(opt, "step_count"):
+                opt.step_count += 1
+        st["graph"].replay()
+        for k, v in st["per_replay"].items():
+            ops.count(k, v)
+        self.global_step += 1
+        self.last_grad_norm = st["norm"]
+        return st["loss"]

@@ -347,10 +347,9 @@ template <int HD>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const CUtensorMap& to, const AttnParams& p, cudaStream_t st, const RowScatter& rs) {
   auto kern = attn_fwd_kernel<HD>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is per device
+  if (configured.first()) {
     SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::TOTAL));
-    configured = true;
   }
   dim3 grid((p.Sq + 2 * QT - 1) / (2 * QT), p.H, p.B);
   kern<<<grid, ATT_THREADS, AttnSmem<HD>::TOTAL, st>>>(tq, tk, tv, to, p, rs);
@@ -414,8 +413,15 @@ extern "C" int solar_attn_fwd_scatter(const void* q, const void* k, const void* 
                                       int Sk, int H, int D, long long q_ss, long long k_ss, long long v_ss,
                                       long long o_ss, float scale, int* status, void* stream,
                                       void* const* dst_bases, void* const* flag_ptrs, unsigned* counter,
-                                      int n_ranks, long long dst_ld, const int* row_start, int col_offset) {
+                                      int n_ranks, long long dst_ld, long long dst_rows, const int* row_start,
+                                      int col_offset) {
   if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("attention scatter: rank count out of range%s");
+  // every destination buffer holds dst_rows rows: a rank's row range may not be larger (the stores would run past
+  // the buffer in the peer's memory)
+  for (int i = 0; i < n_ranks; ++i)
+    if (row_start[i + 1] < row_start[i] || row_start[i + 1] - row_start[i] > dst_rows)
+      return fail("attention scatter: a rank's rows exceed the destination buffer%s");
+  if (row_start[n_ranks] != Sq) return fail("attention scatter: row ranges must cover the sequence%s");
   RowScatter rs;
   memset(&rs, 0, sizeof(rs));
   rs.dst.n = n_ranks;

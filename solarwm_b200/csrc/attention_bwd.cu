@@ -37,6 +37,7 @@
 //
 // Replaces the flash_attn / cuDNN SDPA backward used by the reference
 // (solar/backends/wan22/runtime/modeling/attention.py:98-135, solar/backends/minimax_h3/fast_attention.py:103).
+#include "comm.cuh"
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -57,6 +58,7 @@ struct AttnBwdParams {
   const __nv_bfloat16* stat0; long long stat0_ss, stat0_sb;   // stationary tensors (element strides)
   const __nv_bfloat16* stat1; long long stat1_ss, stat1_sb;
   long long* trace;      // optional cycle counters of CTA (0,0,0): see solar_attn_bwd_trace
+  int scat_col[2];       // peer scatter: destination column of head 0 for output 0 (dV / dQ) and output 1 (dK)
 };
 
 // trace slots (per mode, 8 each): 0 score-warp loop cycles, 1 score-warp wait strm_full, 2 score-warp
@@ -108,6 +110,30 @@ __device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint8_t* region, int
   }
 }
 
+// fp32 accumulator rows (this thread's TMEM lane) -> bf16 -> 16-byte stores to `dst` (NCOLS * 2 contiguous bytes,
+// typically a row of another rank's buffer over NVLink).  `dst` is null for rows past the end; the TMEM loads are
+// warp-wide and run regardless.
+template <int NCOLS>
+__device__ __forceinline__ void acc_to_peer(uint32_t t_acc, uint4* dst) {
+#pragma unroll
+  for (int cc = 0; cc < NCOLS / 32; ++cc) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_acc + cc * 32, r);
+    tmem_ld_wait();
+    if (dst != nullptr) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        o.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+        o.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+        o.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+        o.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+        dst[cc * 4 + g] = o;
+      }
+    }
+  }
+}
+
 // A load the compiler may not sink to its first use: the prefetch below has to leave a whole tile
 // ahead of the values being needed.
 __device__ __forceinline__ float4 lds_f4_early(const float* ptr) {
@@ -127,7 +153,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
                 const __grid_constant__ CUtensorMap tmStrm0, const __grid_constant__ CUtensorMap tmStrm1,
                 const __grid_constant__ CUtensorMap tmOut0, const __grid_constant__ CUtensorMap tmOut1,
-                const AttnBwdParams p) {
+                const AttnBwdParams p, const __grid_constant__ RowScatter rs) {
   using L = BwdSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -517,7 +543,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
     if (ok) ok = mbar_wait(acc_done, 0, abort_word, ST_TIMEOUT_OTHER);
     if (ok) {
       tc_fence_after();
-      if (MODE == 0) {
+      if (rs.active()) {
+        // Reverse Ulysses exchange fused into the epilogue: every gradient row goes straight to the rank that owns
+        // the token, into that rank's [tokens, dq | dk | dv] buffer at this rank's head columns (peer stores over
+        // NVLink); nothing is written locally.
+        const int grow = row0 + row;
+        if (MODE == 0) {
+          uint4* dst = grow < p.S_stat
+                           ? reinterpret_cast<uint4*>(rs.addr(grow, p.scat_col[wg] + head * HD, 2)) : nullptr;
+          acc_to_peer<HD>(tmem_base + lane_off + (wg == 0 ? COL_ACC0 : COL_ACC1), dst);
+        } else if (wg < L::CHUNKS) {
+          uint4* dst = grow < p.S_stat
+                           ? reinterpret_cast<uint4*>(rs.addr(grow, p.scat_col[0] + head * HD + wg * 64, 2)) : nullptr;
+          acc_to_peer<64>(tmem_base + lane_off + COL_ACC0 + wg * 64, dst);
+        }
+      } else if (MODE == 0) {
         // warpgroup 0 drains dV (acc0), warpgroup 1 drains dK (acc1)
         uint8_t* region = smem + L::STAT_OFF + wg * L::STAT_TILE;
         acc_to_smem<HD>(tmem_base + lane_off + (wg == 0 ? COL_ACC0 : COL_ACC1), region, L::STAT_CHUNK, row);
@@ -556,6 +596,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
     tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicExch(p.status, *abort_word);
+  if (rs.active()) cta_done_signal_peers(rs.flags);
 }
 
 // L2[i] = log2(e) * lse[i], delta[i] = sum_d O[i,d] dO[i,d]; rows >= S get (+1e30, 0).
@@ -600,15 +641,14 @@ static int bshd_map(CUtensorMap* m, const void* ptr, int B, int S, int H, int D,
 }
 
 template <int HD, int MODE>
-static int launch_bwd(const CUtensorMap* maps, const AttnBwdParams& p, cudaStream_t st) {
+static int launch_bwd(const CUtensorMap* maps, const AttnBwdParams& p, cudaStream_t st, const RowScatter& rs) {
   auto kern = attn_bwd_kernel<HD, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is per device
+  if (configured.first()) {
     SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<HD>::TOTAL));
-    configured = true;
   }
   dim3 grid((p.S_stat + ST_ROWS - 1) / ST_ROWS, p.H, p.B);
-  kern<<<grid, BW_THREADS, BwdSmem<HD>::TOTAL, st>>>(maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  kern<<<grid, BW_THREADS, BwdSmem<HD>::TOTAL, st>>>(maps[1], maps[2], maps[3], maps[4], maps[5], p, rs);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -626,7 +666,6 @@ extern "C" int solar_attn_bwd_trace(int enable, long long* out16) {
   return 0;
 }
 
-// All tensors are [B, S, H, D] bf16 with unit stride on D and stride D on H; *_ss / *_sb are the
 // Tail overlap: the dK/dV kernel and the dQ kernel are independent; with the switch on, the dQ kernel is launched
 // on a side stream (forked after the row-statistics kernel, joined before the entry returns control of the
 // caller's stream), so its CTAs fill the SMs that the last, partly empty wave of the dK/dV kernel leaves idle.
@@ -657,14 +696,20 @@ extern "C" int solar_attn_bwd_overlap(int enable) {
   return before;
 }
 
-// element strides of the sequence and batch axes.  lse [B,H,Sq] fp32 (natural log, from the
-// forward kernel).  scratch: 2 * B*H*Sq_pad fp32 of caller-provided memory, Sq_pad = Sq rounded
-// up to 128.  Writes dq [B,Sq,H,D], dk and dv [B,Sk,H,D] (contiguous).
-extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                              const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq,
-                              int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
-                              long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
-                              long long do_ss, long long do_sb, float scale, int* status, void* stream) {
+// Scatter form of the outputs (B == 1): dq / dk / dv rows leave through `rs` into the token owners' buffers; the two
+// kernels signal through separate last-CTA counters because they may run at the same time.
+struct BwdScatter {
+  RowScatter rs;          // flags.local_counter is filled per kernel from counter_dkv / counter_dq
+  unsigned* counter_dkv;
+  unsigned* counter_dq;
+  int col_dq, col_dk, col_dv;   // destination column of head 0 of each gradient
+};
+
+static int attn_bwd_impl(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                         const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq, int Sk, int H,
+                         int D, long long q_ss, long long q_sb, long long k_ss, long long k_sb, long long v_ss,
+                         long long v_sb, long long o_ss, long long o_sb, long long do_ss, long long do_sb, float scale,
+                         int* status, void* stream, int allow_overlap, const BwdScatter* scat) {
   if (D != 64 && D != 128) return fail("attention backward: head_dim must be 64 or 128%s");
   if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0) return fail("attention backward: empty problem%s");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -685,8 +730,16 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.L2 = L2; p.delta = delta; p.status = status;
   p.trace = nullptr;
+  p.scat_col[0] = p.scat_col[1] = 0;
+  RowScatter rs;
+  memset(&rs, 0, sizeof(rs));
+  if (scat != nullptr) {
+    rs = scat->rs;
+    // with peer scatter nothing is stored locally; the output maps only have to be valid
+    dq = const_cast<void*>(q); dk = const_cast<void*>(k); dv = const_cast<void*>(v);
+  }
   if (g_trace_enabled) SOLAR_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.trace), g_bwd_trace));
-  const long long c_ss = static_cast<long long>(H) * D;   // contiguous outputs
+  const long long c_ss = scat != nullptr ? q_ss : static_cast<long long>(H) * D;   // contiguous outputs
   int rc;
   cudaStream_t st_dq = st;
   int dev = -1;
@@ -695,8 +748,9 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
   // two co-scheduled kernels only disturb each other's L2 reuse
   const long long stat_ctas = static_cast<long long>((Sk + ST_ROWS - 1) / ST_ROWS) * H * B;
   const bool few_waves = stat_ctas < 8LL * sm_count();
-  if (g_bwd_overlap && few_waves) SOLAR_CUDA_OK(cudaStreamIsCapturing(st, &capturing));
-  if (g_bwd_overlap && few_waves && capturing == cudaStreamCaptureStatusNone) {
+  const bool overlap = allow_overlap && few_waves;
+  if (overlap) SOLAR_CUDA_OK(cudaStreamIsCapturing(st, &capturing));
+  if (overlap && capturing == cudaStreamCaptureStatusNone) {
     if ((rc = side_stream_for_device(&dev))) return rc;
     st_dq = g_side_stream[dev];
     SOLAR_CUDA_OK(cudaEventRecord(g_fork_ev[dev], st));            // after the row statistics
@@ -713,7 +767,12 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
     if ((rc = bshd_map(&m[4], dv, B, Sk, H, D, c_ss, c_ss * Sk, ST_ROWS))) return rc;
     if ((rc = bshd_map(&m[5], dk, B, Sk, H, D, c_ss, c_ss * Sk, ST_ROWS))) return rc;
     p.S_stat = Sk; p.S_stream = Sq;
-    rc = D == 128 ? launch_bwd<128, 0>(m, p, st) : launch_bwd<64, 0>(m, p, st);
+    if (scat != nullptr) {
+      rs.flags.local_counter = scat->counter_dkv;
+      p.scat_col[0] = scat->col_dv;
+      p.scat_col[1] = scat->col_dk;
+    }
+    rc = D == 128 ? launch_bwd<128, 0>(m, p, st, rs) : launch_bwd<64, 0>(m, p, st, rs);
     if (rc) return rc;
   }
   {
@@ -727,7 +786,12 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
     m[5] = m[4];
     m[1] = m[4];   // the stationary-tile map is unused in dQ mode
     p.S_stat = Sq; p.S_stream = Sk;
-    rc = D == 128 ? launch_bwd<128, 1>(m, p, st_dq) : launch_bwd<64, 1>(m, p, st_dq);
+    if (scat != nullptr) {
+      rs.flags.local_counter = scat->counter_dq;
+      p.scat_col[0] = scat->col_dq;
+      p.scat_col[1] = scat->col_dq;
+    }
+    rc = D == 128 ? launch_bwd<128, 1>(m, p, st_dq, rs) : launch_bwd<64, 1>(m, p, st_dq, rs);
     if (st_dq != st) {                                               // join even when the launch failed
       cudaEventRecord(g_join_ev[dev], st_dq);
       cudaStreamWaitEvent(st, g_join_ev[dev], 0);
@@ -735,4 +799,66 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
     if (rc) return rc;
   }
   return 0;
+}
+
+// All tensors are [B, S, H, D] bf16 with unit stride on D and stride D on H; *_ss / *_sb are the
+// element strides of the sequence and batch axes.  lse [B,H,Sq] fp32 (natural log, from the
+// forward kernel).  scratch: 2 * B*H*Sq_pad fp32 of caller-provided memory, Sq_pad = Sq rounded
+// up to 128.  Writes dq [B,Sq,H,D], dk and dv [B,Sk,H,D] (contiguous).
+extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                              const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq,
+                              int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
+                              long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
+                              long long do_ss, long long do_sb, float scale, int* status, void* stream) {
+  return attn_bwd_impl(q, k, v, o, dout, lse, dq, dk, dv, scratch, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss,
+                       v_sb, o_ss, o_sb, do_ss, do_sb, scale, status, stream, g_bwd_overlap, nullptr);
+}
+
+// The same computation with all three kernels on the caller's stream whatever the tail-overlap switch says: no
+// side stream or event is ever created on this path.
+extern "C" int solar_attn_bwd_serial(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                     const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq,
+                                     int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
+                                     long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
+                                     long long do_ss, long long do_sb, float scale, int* status, void* stream) {
+  return attn_bwd_impl(q, k, v, o, dout, lse, dq, dk, dv, scratch, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss,
+                       v_sb, o_ss, o_sb, do_ss, do_sb, scale, status, stream, 0, nullptr);
+}
+
+// Attention backward over this rank's heads and the whole sequence (B == 1, Sq == Sk == S) whose gradients are not
+// written locally: row i of dq / dk / dv is stored into the buffer of the rank r that owns token i
+// (row_start[r] <= i < row_start[r+1]) at local row i - row_start[r], columns col_dq / col_dk / col_dv + head * D
+// of a [*, dst_ld] matrix -- the reverse Ulysses exchange fused into the epilogue.  Each of the two kernels adds 1 to
+// the flag word on every rank when its last CTA is done (2 signals per rank and call); counter_dkv / counter_dq are
+// two zero-initialised local words.  q, k, v share the sequence stride qkv_ss; o [S, H*D] and dout have their own.
+extern "C" int solar_attn_bwd_scatter(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                      const float* lse, float* scratch, int S, int H, int D, long long qkv_ss,
+                                      long long o_ss, long long do_ss, float scale, int* status, void* stream,
+                                      void* const* dst_bases, void* const* flag_ptrs, unsigned* counter_dkv,
+                                      unsigned* counter_dq, int n_ranks, long long dst_ld, long long dst_rows,
+                                      const int* row_start, int col_dq, int col_dk, int col_dv) {
+  if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("attention backward scatter: rank count out of range%s");
+  if ((col_dq | col_dk | col_dv) % 8 != 0 || dst_ld % 8 != 0)
+    return fail("attention backward scatter: destination columns must be multiples of 8 elements%s");
+  BwdScatter sc;
+  memset(&sc, 0, sizeof(sc));
+  sc.rs.dst.n = n_ranks;
+  sc.rs.flags.n = n_ranks;
+  for (int i = 0; i < n_ranks; ++i) {
+    sc.rs.dst.base[i] = dst_bases[i];
+    sc.rs.flags.flag[i] = static_cast<unsigned*>(flag_ptrs[i]);
+    sc.rs.row_start[i] = row_start[i];
+    if (row_start[i + 1] - row_start[i] > dst_rows || row_start[i + 1] < row_start[i])
+      return fail("attention backward scatter: a rank's rows exceed the destination buffer%s");
+  }
+  sc.rs.row_start[n_ranks] = row_start[n_ranks];
+  if (row_start[n_ranks] != S) return fail("attention backward scatter: row ranges must cover the sequence%s");
+  sc.rs.ld = dst_ld;
+  sc.rs.col_offset = 0;
+  sc.counter_dkv = counter_dkv;
+  sc.counter_dq = counter_dq;
+  sc.col_dq = col_dq; sc.col_dk = col_dk; sc.col_dv = col_dv;
+  return attn_bwd_impl(q, k, v, o, dout, lse, nullptr, nullptr, nullptr, scratch, 1, S, S, H, D, qkv_ss, qkv_ss * S,
+                       qkv_ss, qkv_ss * S, qkv_ss, qkv_ss * S, o_ss, o_ss * S, do_ss, do_ss * S, scale, status, stream,
+                       g_bwd_overlap, &sc);
 }

@@ -7,23 +7,23 @@
 // Work vectors of the backward pass (L2 and delta), shared by every call on this device.
 static __device__ __align__(256) float g_attn_bwd_scratch[SOLAR_ATTN_BWD_NOALLOC_MAX_FLOATS];
 
-extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+extern "C" int solar_attn_bwd_serial(const void* q, const void* k, const void* v, const void* o, const void* dout,
                               const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq,
                               int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
                               long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
-                              long long do_ss, long long do_sb, float scale, int* status, void* stream);
+                                     long long do_ss, long long do_sb, float scale, int* status, void* stream);
 
 namespace {
 
-constexpr int kMaxDevices = 64;
-float* g_scratch_addr[kMaxDevices] = {nullptr};
+// Filled without a lock: two host threads that race here both store the same address.
+float* g_scratch_addr[solar::kMaxDevices] = {nullptr};
 
 // In host code the array's name is only a handle; the address a kernel can use has to be asked
 // for, once per device, with that device current.
 int scratch_for_current_device(float** out) {
   int dev = 0;
   SOLAR_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return solar::fail("attention backward (no-alloc): device index out of range%s");
+  if (dev < 0 || dev >= solar::kMaxDevices) return solar::fail("attention backward (no-alloc): device index out of range%s");
   if (g_scratch_addr[dev] == nullptr) {
     void* p = nullptr;
     SOLAR_CUDA_OK(cudaGetSymbolAddress(&p, g_attn_bwd_scratch));
@@ -51,6 +51,7 @@ extern "C" int solar_attn_bwd_noalloc(const void* q, const void* k, const void* 
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != 0) return rc;
-  return solar_attn_bwd(q, k, v, o, dout, lse, dq, dk, dv, scratch, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss,
+  // the serial form: all kernels on the caller's stream, so no side stream or event is ever created from here
+  return solar_attn_bwd_serial(q, k, v, o, dout, lse, dq, dk, dv, scratch, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss,
                         v_sb, o_ss, o_sb, do_ss, do_sb, scale, status, stream);
 }

@@ -36,6 +36,70 @@ __global__ void comm_wait_kernel(const unsigned* flag, unsigned expected, int* s
   }
 }
 
+// Round wait whose expected value lives on the device: *epoch += add, then poll until the flag has reached it.
+// Nothing in the launch depends on how many rounds came before, so a captured CUDA graph can replay it.
+__global__ void comm_wait_round_kernel(const unsigned* flag, unsigned* epoch, unsigned add, int* status,
+                                       unsigned long long limit_ns) {
+  const unsigned expected = *epoch + add;
+  *epoch = expected;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int>(v - expected) >= 0) return;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      if (status) atomicExch(status, ST_TIMEOUT_PEER);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
+// Sum of a few fp32 values over the ranks without a library collective: one CTA stores this rank's `n` values into
+// slot `rank` of every peer's [n_ranks, n] table, signals, waits (bounded) for all ranks' signals of this round and
+// adds the rows in rank order, so every rank computes the identical sum.  Two tables alternate by round (`parity`
+// is read from the epoch word), which keeps a fast rank's next round from overwriting values a slow rank still reads.
+__global__ void comm_allsum_kernel(const float* src, int n, PeerTable tables, int rank, PeerFlags flags,
+                                   const unsigned* local_flag, unsigned* epoch, float* out, int* status,
+                                   unsigned long long limit_ns) {
+  __shared__ unsigned s_expected;
+  if (threadIdx.x == 0) {
+    s_expected = *epoch + static_cast<unsigned>(tables.n);
+    *epoch = s_expected;
+  }
+  __syncthreads();
+  const unsigned expected = s_expected;
+  const int parity = (expected / static_cast<unsigned>(tables.n)) & 1;
+  const long long table_elems = static_cast<long long>(tables.n) * n;
+  for (int r = 0; r < tables.n; ++r) {
+    float* dst = static_cast<float*>(tables.base[r]) + parity * table_elems + static_cast<long long>(rank) * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    signal_all_peers(flags);
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flag) : "memory");
+      if (static_cast<int>(v - expected) >= 0) break;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        if (status) atomicExch(status, ST_TIMEOUT_PEER);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  const volatile float* mine = static_cast<const float*>(tables.base[rank]) + parity * table_elems;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < tables.n; ++r) acc += mine[static_cast<long long>(r) * n + i];
+    out[i] = acc;
+  }
+}
+
 __global__ void comm_signal_kernel(PeerFlags flags) {
   if (threadIdx.x == 0 && blockIdx.x == 0) signal_all_peers(flags);
 }
@@ -112,6 +176,17 @@ extern "C" int solar_comm_wait(const void* flag, unsigned expected, int* status,
   return 0;
 }
 
+// Device-epoch form of solar_comm_wait: `epoch` is a local u32 that the kernel advances by `add` (the number of
+// signals one round delivers) before it polls; the launch is replayable inside a CUDA graph.
+extern "C" int solar_comm_wait_round(const void* flag, unsigned* epoch, unsigned add, int* status,
+                                     double limit_seconds, void* stream) {
+  const unsigned long long ns = static_cast<unsigned long long>(limit_seconds * 1e9);
+  comm_wait_round_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned*>(flag), epoch,
+                                                                             add, status, ns);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 static PeerFlags make_flags(void* const* flag_ptrs, int n, unsigned* counter) {
   PeerFlags f;
   f.n = n;
@@ -141,6 +216,25 @@ extern "C" int solar_comm_push(const void* src, void* const* dst_bases, int n, l
   if (grid < 1) grid = 1;
   comm_push_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), t, dst_off_bytes, n16, make_flags(flag_ptrs, n, counter));
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// out[0..n) = sum over ranks of src[0..n) (n <= 256 floats).  table_bases[r]: rank r's [2, n_ranks, n] fp32 table
+// in symmetric memory; flag_ptrs[r]: the round's flag word on rank r; epoch: a local u32 (device-side round count).
+extern "C" int solar_comm_allsum(const float* src, int n, void* const* table_bases, void* const* flag_ptrs,
+                                 int n_ranks, int rank, unsigned* epoch, float* out, int* status,
+                                 double limit_seconds, void* stream) {
+  if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("comm: peer count out of range%s");
+  if (n < 1 || n > 256) return fail("comm allsum: 1..256 values%s");
+  if (rank < 0 || rank >= n_ranks) return fail("comm allsum: rank out of range%s");
+  PeerTable t;
+  t.n = n_ranks;
+  for (int i = 0; i < kMaxPeers; ++i) t.base[i] = i < n_ranks ? table_bases[i] : nullptr;
+  const unsigned long long ns = static_cast<unsigned long long>(limit_seconds * 1e9);
+  comm_allsum_kernel<<<1, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      src, n, t, rank, make_flags(flag_ptrs, n_ranks, nullptr), static_cast<const unsigned*>(flag_ptrs[rank]), epoch,
+      out, status, ns);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -397,10 +397,9 @@ template <int A_MN, int B_MN, int OUT_F32>
 static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
                        const GemmParams& p, int max_ctas, cudaStream_t stream, const ColScatter& sc) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT_F32>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is per device
+  if (configured.first()) {
     SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-    configured = true;
   }
   int grid = p.tiles_m * p.tiles_n;
   int cap = max_ctas > 0 ? max_ctas : sm_count();
@@ -610,10 +609,9 @@ template <int A_MN, int B_MN, int OUT_F32>
 static int launch_gemm_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
                             const GemmParams& p, int max_ctas, cudaStream_t stream, const ColScatter& sc) {
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, OUT_F32>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is per device
+  if (configured.first()) {
     SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL));
-    configured = true;
   }
   int pairs = p.tiles_m * p.tiles_n;
   const int cap = (max_ctas > 0 ? max_ctas : sm_count()) / 2;

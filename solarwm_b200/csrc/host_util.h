@@ -120,15 +120,36 @@ inline int make_tmap_4d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   return 0;
 }
 
-inline int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
+constexpr int kMaxDevices = 64;
+
+inline int current_device_index() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev < 0 || dev >= kMaxDevices) ? 0 : dev;
 }
+
+// SM count of the CURRENT device (cached per device: a process may drive several GPUs).
+inline int sm_count() {
+  static int n[kMaxDevices] = {0};
+  const int dev = current_device_index();
+  if (n[dev] == 0) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    n[dev] = v > 0 ? v : 148;
+  }
+  return n[dev];
+}
+
+// Function attributes (the dynamic shared-memory limit) are per device: a launcher keeps one
+// `PerDeviceOnce` per kernel instantiation and sets the attribute the first time each device launches it.
+struct PerDeviceOnce {
+  bool done[kMaxDevices] = {false};
+  bool first() {
+    const int dev = current_device_index();
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
 
 }  // namespace solar

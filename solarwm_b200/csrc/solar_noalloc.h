@@ -20,7 +20,14 @@
 //     backward pass overwrites every element it later reads, so nothing has to be cleared, but
 //     two calls whose kernels may overlap on the GPU (different streams, no ordering between
 //     them) race on it.  Order such calls on one stream or with events.
-//   * The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+//   * The entry point calls no cudaMalloc / cudaFree and no allocating library routine: it runs
+//     its three kernels on the caller's stream (the tail-overlap switch of solar_attn_bwd, which
+//     creates a side stream and two events, does not apply here).  What its first call on a
+//     device does do, besides the address query, is set the kernels' shared-memory attribute
+//     (cudaFuncSetAttribute) -- and, in a host thread that has no CUDA context bound yet, bind
+//     the device's primary context -- so make that first call part of start-up.
+//   * The per-device address cache is filled without a lock; host threads that race on a
+//     device's first call store the same value.
 #pragma once
 
 #define SOLAR_ATTN_BWD_NOALLOC_MAX_FLOATS (1 << 20)

@@ -46,16 +46,28 @@ class FlowMatchScheduler:
             w = w - w.min()
             self.linear_timesteps_weights = w * (steps / w.sum())
 
+    def _on(self, name: str, device) -> torch.Tensor:
+        """The schedule table ``name`` on ``device`` (copied once per table and device, not once per step)."""
+        src = getattr(self, name)
+        if src.device == torch.device(device):
+            return src
+        cache = self.__dict__.setdefault("_device_tables", {})
+        hit = cache.get((name, str(device)))
+        if hit is None or hit[0] is not src:
+            hit = (src, src.to(device))
+            cache[(name, str(device))] = hit
+        return hit[1]
+
     def indices(self, timestep: torch.Tensor) -> torch.Tensor:
         v = timestep.flatten().float()
-        sched = self.timesteps.to(v.device)
+        sched = self._on("timesteps", v.device)
         return (sched.unsqueeze(0) - v.unsqueeze(1)).abs().argmin(dim=1)
 
     def sigma_of(self, timestep: torch.Tensor) -> torch.Tensor:
-        return self.sigmas.to(timestep.device)[self.indices(timestep)]
+        return self._on("sigmas", timestep.device)[self.indices(timestep)]
 
     def training_weight(self, timestep: torch.Tensor) -> torch.Tensor:
-        return self.linear_timesteps_weights.to(timestep.device)[self.indices(timestep)]
+        return self._on("linear_timesteps_weights", timestep.device)[self.indices(timestep)]
 
     def add_noise(self, clean, noise, timestep):
         """clean/noise ``[G, ...]`` with one timestep per leading row -> (x_t, velocity target)."""

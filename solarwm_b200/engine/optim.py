@@ -95,22 +95,67 @@ class FlatAdamW:
                            ema_decay=0.0 if self.ema_decay is None else self.ema_decay)
 
     # state -------------------------------------------------------------------------------
+    _STATE_TENSORS = ("master", "exp_avg", "exp_avg_sq", "ema")
+
+    def _gather_shard(self, shard: torch.Tensor, total: int) -> torch.Tensor:
+        """The un-sharded tensor a shard belongs to; the unsharded optimizer holds it already.  Sharded
+        subclasses make this a collective over their shard group."""
+        return shard
+
     def state_dict(self):
+        """State in the UN-SHARDED layout: every tensor covers the whole flat buffer, whatever the number of ranks the
+        optimizer is sharded over, so that a checkpoint can be resumed at another shard count.  With a sharded
+        optimizer this is a collective: every rank of the shard group must call it; all ranks receive the full
+        tensors (on the host) and the caller decides which rank writes them."""
         out = {"step": self.step_count, "lr": self.lr, "betas": self.betas, "eps": self.eps,
-               "weight_decay": self.weight_decay, "shard": (self.shard_rank, self.shard_world), "units": []}
-        for st in self.state:
-            out["units"].append({k: {n: (t if not torch.is_tensor(t) else t.detach().cpu())
-                                     for n, t in s.items()} for k, s in st.items()})
+               "weight_decay": self.weight_decay, "layout": "full", "units": []}
+        for u, st in zip(self.units, self.state):
+            entry = {}
+            for key, buf in (("m", u.flat), ("v", u.flat_v)):
+                s = st[key]
+                entry[key] = {"numel": int(buf.numel())}
+                for name in self._STATE_TENSORS:
+                    t = s[name]
+                    entry[key][name] = None if t is None else self._gather_shard(t.detach(), buf.numel()).cpu()
+            out["units"].append(entry)
         return out
 
     def load_state_dict(self, state) -> None:
-        if tuple(state["shard"]) != (self.shard_rank, self.shard_world):
-            raise ValueError("optimizer shard layout differs from the checkpoint")
+        """Accepts the un-sharded layout written by ``state_dict`` (each rank copies its own ``[a, b)`` range) and
+        refuses a checkpoint whose un-sharded sizes differ from this model's."""
+        if state.get("layout") != "full":
+            shard = tuple(state.get("shard", (0, 1)))
+            if shard != (0, 1):
+                raise ValueError("optimizer state was saved as one rank's shard; it cannot be resumed")
+        if len(state["units"]) != len(self.state):
+            raise ValueError("optimizer state has a different number of flat units")
         self.step_count = int(state["step"])
-        for st, saved in zip(self.state, state["units"]):
-            for k in ("m", "v"):
-                for n in ("master", "exp_avg", "exp_avg_sq", "ema"):
-                    if st[k][n] is not None and saved[k][n] is not None:
-                        if st[k][n].dtype != saved[k][n].dtype:
-                            raise ValueError("optimizer state dtype mismatch (casting is refused)")
-                        st[k][n].copy_(saved[k][n])
+        for u, st, saved in zip(self.units, self.state, state["units"]):
+            for k, buf in (("m", u.flat), ("v", u.flat_v)):
+                a, b = st[k]["range"]
+                total = int(saved[k].get("numel", buf.numel())) if isinstance(saved[k], dict) else buf.numel()
+                if total != buf.numel():
+                    raise ValueError(f"optimizer state covers {total} elements, the flat buffer {buf.numel()}")
+                for n in self._STATE_TENSORS:
+                    mine, theirs = st[k][n], saved[k].get(n)
+                    if mine is None or theirs is None:
+                        continue
+                    if mine.dtype != theirs.dtype:
+                        raise ValueError("optimizer state dtype mismatch (casting is refused)")
+                    if theirs.numel() != total:
+                        raise ValueError("optimizer state tensor does not cover the whole flat buffer")
+                    mine.copy_(theirs[a:b])
+
+    def ema_state_dict(self, model, gathered=None) -> dict:
+        """The EMA shadow under the model's parameter names (un-sharded).  ``gathered``: a ``state_dict()`` result to
+        take the shadows from (saves a second gather); collective when sharded, like ``state_dict``."""
+        if self.ema_decay is None:
+            raise ValueError("the optimizer was built without an EMA shadow")
+        state = gathered if gathered is not None else self.state_dict()
+        by_unit = {id(u): saved for u, saved in zip(self.units, state["units"])}
+        out = {}
+        for name, p in model.named_parameters():
+            unit, slot = p.flat_unit, p.flat_unit.slots[p.flat_name]
+            full = by_unit[id(unit)]["v" if slot.is_vector else "m"]["ema"]
+            out[name] = full[slot.offset:slot.offset + slot.numel].view(slot.shape).clone()
+        return out

@@ -130,6 +130,23 @@ def _identity_attention(q, k, v):
     return v
 
 
+class _UnitReady(torch.autograd.Function):
+    """Identity placed at a block's input.  Its backward runs when the gradient of the block input is complete,
+    i.e. after every node of the block (it is the block's oldest node and the engine runs newer ready nodes first),
+    and tells ``hook`` that the block's parameter gradients are final -- the sharded optimizer starts the block's
+    reduce-scatter there, under the backward of the blocks below."""
+
+    @staticmethod
+    def forward(ctx, x, hook, unit):
+        ctx.hook, ctx.unit = hook, unit
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.hook(ctx.unit)
+        return g, None, None
+
+
 class _NoSP:
     size = 1
     rank = 0
@@ -253,15 +270,15 @@ class WanBlock(nn.Module):
             (not torch.is_grad_enabled() or self.unit.grad is not None)
         xm = None if (lean and not fused_sp) else F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
         if fused_sp:
-            # Ulysses exchanges ride on the producing kernels (parallel/fused_ulysses.py)
-            from ..parallel.fused_ulysses import FusedAttention, FusedQKV
+            # Ulysses exchanges ride on the producing kernels in both directions (parallel/fused_ulysses.py); the
+            # out-projection belongs to the same function because its dgrad GEMM carries the backward exchange
+            from ..parallel.fused_ulysses import FusedSelfAttention
 
             parity = sp.next_parity()
             w, b = self._fused_params("self_attn.q", "self_attn.v", 3 * D)
-            recv = FusedQKV.apply(xm, w, b, self._p("self_attn.norm_q.weight"), self._p("self_attn.norm_k.weight"),
-                                  rope, cfg.eps, sp, parity, None)
-            o = FusedAttention.apply(recv, 1.0 / math.sqrt(hd), sp, parity,
-                                     None if memo is None else (memo, "self"))
+            y = FusedSelfAttention.apply(xm, w, b, self._p("self_attn.norm_q.weight"), self._p("self_attn.norm_k.weight"),
+                                         rope, self._p("self_attn.o.weight"), self._p("self_attn.o.bias"), cfg.eps,
+                                         1.0 / math.sqrt(hd), sp, parity, None if memo is None else (memo, "self"))
         else:
             if lean:
                 qkv = F_.recompute_segment(
@@ -288,7 +305,7 @@ class WanBlock(nn.Module):
             o = sp.gather_heads(o).reshape(B * Ll, D)
             if camera is not None:
                 o = camera_prope.apply(o, camera[2], H)
-        y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
+            y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
         x = F_.gated_residual(x, y, mod[:, 2], **gk)
 
         # ---- cross attention (text keys/values are replicated on every SP rank)
@@ -361,6 +378,7 @@ class WanDiT(nn.Module):
         self.keep_blocks = 0         # the last ``keep_blocks`` blocks keep their activations (no recompute)
         self.lean_kept = False       # kept blocks drop their norm outputs and FFN hidden (rebuilt in backward)
         self._rope_cache: dict = {}
+        self.grad_ready_hook = None  # callable(unit): a block's parameter gradients are final (set by the trainer)
         if seed is not None:
             self.init_weights(seed)
 
@@ -483,6 +501,8 @@ class WanDiT(nn.Module):
             return self._run_block_inner(block, x, e0, rope, ctx, kw, index)
 
     def _run_block_inner(self, block, x, e0, rope, ctx, kw, index):
+        if self.grad_ready_hook is not None and torch.is_grad_enabled() and x.requires_grad:
+            x = _UnitReady.apply(x, self.grad_ready_hook, block.unit)
         exempt = index >= len(self.blocks) - int(self.keep_blocks)
         if self.checkpointing in ("full", "selective") and torch.is_grad_enabled() and not exempt:
             from torch.utils.checkpoint import checkpoint

@@ -20,11 +20,16 @@ def set_tail_overlap(enable: bool) -> bool:
     return bool(_lib.load().solar_attn_bwd_overlap(c_int(1 if enable else 0)))
 
 
-def attn_bwd_native(q, k, v, o, lse, do, scale: float):
+def ensure_tail_overlap_default() -> None:
+    """First use: apply ``SOLAR_ATTN_BWD_OVERLAP`` (default on) unless ``set_tail_overlap`` was called already."""
     if not _overlap_set:
         import os
 
         set_tail_overlap(os.environ.get("SOLAR_ATTN_BWD_OVERLAP", "1") != "0")
+
+
+def attn_bwd_native(q, k, v, o, lse, do, scale: float):
+    ensure_tail_overlap_default()
     q, k, v, o, do = _bshd(q), _bshd(k), _bshd(v), _bshd(o), _bshd(do)
     B, Sq, H, D = q.shape
     Sk = k.shape[1]

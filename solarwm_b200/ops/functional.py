@@ -29,12 +29,20 @@ def status_word(device) -> torch.Tensor:
     return _status[idx]
 
 
-def check_status(device="cuda") -> None:
-    """Synchronising check of the bounded-wait status word (0 = every wait completed)."""
+def read_status(device="cuda", clear: bool = True) -> int:
+    """Synchronising read of the bounded-wait status word: 0 = every wait completed, otherwise the code of the wait
+    that gave up (5 = a peer's flag never arrived).  ``clear`` resets a non-zero word."""
     w = status_word(device)
     code = int(w.item())
-    if code != 0:
+    if code != 0 and clear:
         w.zero_()
+    return code
+
+
+def check_status(device="cuda") -> None:
+    """``read_status`` that raises on a non-zero word."""
+    code = read_status(device)
+    if code != 0:
         raise _lib.NativeError(f"a device-side bounded wait gave up (code {code})")
 
 
@@ -706,31 +714,35 @@ def euler_step(x_t, v, sigma, sigma_next):
 
 
 class _MseFn(torch.autograd.Function):
+    """The kernel sums ``w m^2 (pred - target)^2`` with a unit denominator; the division by ``denom`` (a host number or
+    a one-element device tensor) happens on the device afterwards, so a mask-dependent denominator costs no host read."""
+
     @staticmethod
     def forward(ctx, pred, target, weight, mask, denom):
         pred = pred.contiguous()
         target = target.contiguous()
         G = pred.shape[0]
         loss = torch.empty(1, dtype=torch.float32, device=pred.device)
+        inv = (1.0 / denom) if torch.is_tensor(denom) else torch.full((1,), 1.0 / float(denom), dtype=torch.float32,
+                                                                      device=pred.device)
         lib = _lib.load()
         rc = lib.solar_mse(ptr(pred), ptr(target), ptr(weight), ptr(mask), c_ll(pred.numel()),
-                           c_ll(pred.numel() // G), c_float(1.0 / denom), ptr(_scratch_f32(pred.device)),
+                           c_ll(pred.numel() // G), c_float(1.0), ptr(_scratch_f32(pred.device)),
                            ptr(loss), ptr(None), ptr(None), stream_handle())
         check(rc, "solar_mse")
         count("mse_fwd", 2)
-        ctx.save_for_backward(pred, target, weight, mask)
-        ctx.denom = denom
-        return loss.view(())
+        ctx.save_for_backward(pred, target, weight, mask, inv)
+        return (loss * inv).view(())
 
     @staticmethod
     def backward(ctx, gloss):
-        pred, target, weight, mask = ctx.saved_tensors
+        pred, target, weight, mask, inv = ctx.saved_tensors
         G = pred.shape[0]
         dpred = torch.empty_like(pred)
-        gl = gloss.reshape(1).float().contiguous()
+        gl = (gloss.reshape(1).float() * inv).contiguous()
         lib = _lib.load()
         rc = lib.solar_mse(ptr(pred), ptr(target), ptr(weight), ptr(mask), c_ll(pred.numel()),
-                           c_ll(pred.numel() // G), c_float(1.0 / ctx.denom), ptr(_scratch_f32(pred.device)),
+                           c_ll(pred.numel() // G), c_float(1.0), ptr(_scratch_f32(pred.device)),
                            ptr(None), ptr(dpred), ptr(gl), stream_handle())
         check(rc, "solar_mse")
         count("mse_bwd")
@@ -739,16 +751,16 @@ class _MseFn(torch.autograd.Function):
 
 def weighted_masked_mse(pred, target, weight=None, mask=None, denom=None):
     """sum_g w[g] m[g] |pred_g - target_g|^2 / denom with pred/target ``[G, ...]`` bf16.
-    ``denom`` defaults to (number of unmasked groups) x (elements per group)."""
+    ``denom`` defaults to (number of unmasked groups) x (elements per group), computed on the device."""
     if not pred.is_cuda:
         return reference.weighted_masked_mse(pred, target, weight, mask)
     G = pred.shape[0]
-    if denom is None:
-        sel = float(G) if mask is None else max(float(mask.sum().item()), 1.0)
-        denom = sel * (pred.numel() // G)
     weight = None if weight is None else weight.float().contiguous()
     mask = None if mask is None else mask.float().contiguous()
-    return _MseFn.apply(pred, target, weight, mask, float(denom))
+    if denom is None:
+        per_group = pred.numel() // G
+        denom = float(G * per_group) if mask is None else (mask.sum().clamp_min(1.0) * per_group).view(1)
+    return _MseFn.apply(pred, target, weight, mask, denom)
 
 
 def rgb8(frame_chw, mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225)):

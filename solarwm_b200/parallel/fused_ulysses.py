@@ -1,26 +1,33 @@
-"""Ulysses exchanges fused into the producing kernels (NVLink peer stores, no NCCL on the forward path).
+"""Ulysses exchanges fused into the producing kernels in BOTH directions (NVLink peer stores, no NCCL in the layer).
 
 Forward of one attention layer at SP = P, tokens sharded by whole frames, heads by rank:
 
-  1. QKV projection GEMM (tcgen05).  Its epilogue stores the V columns straight into the receive
-     buffer of the rank that owns each head (``solar_gemm_bf16_scatter``); Q and K columns stay local
-     because Wan normalises them over the full width first.
-  2. full-width RMSNorm + RoPE of Q and of K (row kernel) whose output stage is the same column
-     scatter (``solar_rmsnorm_rope_scatter``).  Every rank now holds ``[S, q_loc | k_loc | v_loc]``.
-  3. flash attention over the local heads and the whole sequence; its epilogue stores each output
-     row into the token owner's ``[S_local, dim]`` buffer (``solar_attn_fwd_scatter``).
+  1. QKV projection GEMM (tcgen05).  Its epilogue stores the V columns straight into the receive buffer of the rank
+     that owns each head (``solar_gemm_bf16_scatter``); Q and K columns stay local because Wan normalises them over
+     the full width first.
+  2. full-width RMSNorm + RoPE of Q and of K (row kernel) whose output stage is the same column scatter
+     (``solar_rmsnorm_rope_scatter``).  Every rank now holds ``[S, q_loc | k_loc | v_loc]``.
+  3. flash attention over the local heads and the whole sequence; its epilogue stores each output row into the token
+     owner's ``[S_local, dim]`` buffer (``solar_attn_fwd_scatter``).
   4. the out-projection GEMM reads that buffer.
 
-Each producer kernel's last CTA adds 1 to a flag word on every rank; consumers are preceded on the
-stream by a bounded device-side wait for ``3 * P`` (step 2) or ``P`` (step 3) new signals.  Receive
-buffers are double-buffered by layer parity, which is sufficient because every layer's wait depends
-on every peer having finished the previous layer's consumer.
+Backward runs the same exchanges in reverse, again from inside the producing kernels:
 
-The backward pass exchanges gradients with the collective transport of the parent class (the
-reverse all-to-all), and so does everything on CPU.  The reference performs steps 1-3 as three
-``nn.Linear`` + two norms + RoPE + three ``all_to_all_single`` with packing copies, and one more
-all-to-all after attention (solar/backends/wan22/runtime/modeling/causal_model.py:878-1027,
-sequence_parallel.py:446-524).
+  4'. the out-projection dgrad GEMM ``dY W_o`` leaves through the column scatter: every rank receives
+      ``dO [S, heads_local * hd]`` for its heads (``solar_gemm_bf16_scatter``, NN layout);
+  3'. the attention backward kernels store every row of dQ / dK / dV into the token owner's ``[S_local, 3 * dim]``
+      buffer at this rank's head columns (``solar_attn_bwd_scatter``); nothing is written locally;
+  2'. RMSNorm + RoPE backward of the q and k column blocks in place, then the QKV dgrad and wgrad GEMMs read the
+      buffer as it is.
+
+Each producer kernel's last CTA adds 1 to a flag word on every rank; consumers are preceded on the stream by a bounded
+device-side wait whose round counter lives on the device (``SymmetricHeap.wait``), so the whole layer is a fixed launch
+sequence that a CUDA graph can replay.  Buffers are double-buffered by layer parity, which is sufficient because every
+wait of a layer depends on every peer having finished the previous layer's consumer kernels (stream order).
+
+The reference performs the forward as three ``nn.Linear`` + two norms + RoPE + three ``all_to_all_single`` with packing
+copies and one more all-to-all after attention, and the backward as the reverse all-to-alls
+(solar/backends/wan22/runtime/modeling/causal_model.py:878-1027, sequence_parallel.py:407-541).
 """
 from __future__ import annotations
 
@@ -34,13 +41,31 @@ from ..ops import _lib, functional as F_
 from ..ops._lib import c_float, c_int, c_ll, check, count, ptr, stream_handle
 from ..ops.functional import status_word
 from .symm import SymmetricHeap
-from .ulysses import UlyssesCollective, _AllToAll
+from .ulysses import UlyssesCollective, frame_split
+
+
+class _GatherSeqFused(torch.autograd.Function):
+    """Sequence all-gather as peer pushes.  Every rank then evaluates the SAME head and loss on the full sequence,
+    so the upstream gradient is identical on all ranks; the reduce-scatter of the collective form (a sum of ``P``
+    identical tensors, then this rank's slice) is therefore the local slice times ``P``, exactly, with no traffic."""
+
+    @staticmethod
+    def forward(ctx, x, sp):
+        ctx.sp = sp
+        return sp._push_rows(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        sp = ctx.sp
+        a, b = sp._row_start[sp.rank], sp._row_start[sp.rank + 1]
+        return g[a:b] * float(sp.size), None
 
 
 class FusedUlysses(UlyssesCollective):
     fused = True
 
-    def __init__(self, group: Optional[dist.ProcessGroup], *, max_tokens: int, dim: int, num_heads: int):
+    def __init__(self, group: Optional[dist.ProcessGroup], *, max_tokens: int, dim: int, num_heads: int,
+                 max_frame_tokens: int = 4096):
         super().__init__(group)
         P = self.size
         if num_heads % P:
@@ -48,21 +73,32 @@ class FusedUlysses(UlyssesCollective):
         self.dim, self.heads, self.hd = dim, num_heads, dim // num_heads
         self.dl = dim // P                       # columns of one rank's head block
         self.max_tokens = int(max_tokens)
-        max_local = (self.max_tokens + P - 1) // P + 4096
-        need = 2 * self.max_tokens * 3 * self.dl * 2 + 2 * max_local * dim * 2 + 4096
+        # whole-frame sharding: a rank holds at most ceil(F / P) frames, i.e. at most one frame more than the mean
+        self.max_local = (self.max_tokens + P - 1) // P + int(max_frame_tokens)
+        ml, mt = self.max_local, self.max_tokens
+        need = 2 * (mt * 3 * self.dl + ml * dim + mt * self.dl + ml * 3 * dim) * 2 + mt * dim * 2 + (1 << 16)
         self.heap = SymmetricHeap(need, group)
-        self.recv, self.recv_off, self.obuf, self.obuf_off = [], [], [], []
-        for _ in range(2):
-            t, off = self.heap.alloc((self.max_tokens, 3 * self.dl))
-            self.recv.append(t)
-            self.recv_off.append(off)
-        for _ in range(2):
-            t, off = self.heap.alloc((max_local, dim))
-            self.obuf.append(t)
-            self.obuf_off.append(off)
+
+        def pair(shape):
+            tensors, offsets = [], []
+            for _ in range(2):
+                t, off = self.heap.alloc(shape)
+                tensors.append(t)
+                offsets.append(off)
+            return tensors, offsets
+
+        self.recv, self.recv_off = pair((mt, 3 * self.dl))          # forward: q | k | v of this rank's heads
+        self.obuf, self.obuf_off = pair((ml, dim))                  # forward: attention output of this rank's tokens
+        self.dobuf, self.dobuf_off = pair((mt, self.dl))            # backward: dO of this rank's heads
+        self.dqkv, self.dqkv_off = pair((ml, 3 * dim))              # backward: dq | dk | dv of this rank's tokens
+        self.seqbuf, self.seqbuf_off = self.heap.alloc((mt, dim))   # final sequence gather
         self.flag_qkv = [self.heap.new_flag() for _ in range(2)]
         self.flag_o = [self.heap.new_flag() for _ in range(2)]
+        self.flag_do = [self.heap.new_flag() for _ in range(2)]
+        self.flag_dqkv = [self.heap.new_flag() for _ in range(2)]
+        self.flag_seq = self.heap.new_flag()
         self._parity = 0
+        self._bwd_parity = 0
         self._row_start = None
 
     # layout -------------------------------------------------------------------------------
@@ -76,12 +112,23 @@ class FusedUlysses(UlyssesCollective):
             starts.append(starts[-1] + n)
         if starts[-1] > self.max_tokens:
             raise ValueError("sequence longer than the symmetric receive buffers")
+        if max(seq) > self.max_local:
+            # the attention epilogues store a rank's rows into per-rank buffers of max_local rows: refuse a layout
+            # whose largest shard does not fit instead of writing past the buffer in a peer's memory
+            raise ValueError(f"a rank would own {max(seq)} tokens but the per-rank buffers hold {self.max_local}; "
+                             f"build FusedUlysses with max_frame_tokens >= {frame_tokens}")
         self._row_start = starts
         self._row_start_c = (ctypes.c_int * (self.size + 1))(*starts)
 
     def next_parity(self) -> int:
         self._parity ^= 1
         return self._parity
+
+    def next_bwd_parity(self) -> int:
+        """Backward layers alternate their own buffer pair, counted at backward time: with recomputed blocks the
+        forward parity a layer was (re)run with says nothing about which backward layer came just before it."""
+        self._bwd_parity ^= 1
+        return self._bwd_parity
 
     # step 1 + 2 ---------------------------------------------------------------------------
     def qkv_exchange(self, xm, w_qkv, b_qkv, nq_w, nk_w, rope, eps, parity):
@@ -115,7 +162,7 @@ class FusedUlysses(UlyssesCollective):
             check(rc, "solar_rmsnorm_rope_scatter")
             count("rmsnorm_rope_scatter")
             rstd.append(r)
-        heap.wait(slot, heap.expect(slot, 3 * P))
+        heap.wait(slot, 3 * P)
         return qkv, rstd[0], rstd[1], self.recv[parity][:S]
 
     # step 3 -------------------------------------------------------------------------------
@@ -133,109 +180,146 @@ class FusedUlysses(UlyssesCollective):
                                         c_ll(3 * dl), c_ll(3 * dl), c_ll(3 * dl), c_ll(hp * hd), c_float(scale),
                                         ptr(status_word(recv.device)), stream_handle(),
                                         heap.peer_ptr_array(self.obuf_off[parity]), heap.flag_ptrs(slot),
-                                        heap.counter_ptr(slot), c_int(self.size), c_ll(self.dim), self._row_start_c,
-                                        c_int(self.rank * dl))
+                                        heap.counter_ptr(slot), c_int(self.size), c_ll(self.dim), c_ll(self.max_local),
+                                        self._row_start_c, c_int(self.rank * dl))
         check(rc, "solar_attn_fwd_scatter")
         count("attn_fwd_scatter")
-        heap.wait(slot, heap.expect(slot, self.size))
+        heap.wait(slot, self.size)
         Sl = self._row_start[self.rank + 1] - self._row_start[self.rank]
         return o, lse, self.obuf[parity][:Sl]
 
-    # reverse exchanges for the backward pass (collective transport) -------------------------
-    def heads_to_tokens_grad(self, d_recv):
-        """d_recv [S, 3*dl] (this rank's heads, all tokens) -> [Sl, 3, dim] (this rank's tokens, all heads)."""
-        _, seq = self._layout
-        P, hp, hd = self.size, self.heads // self.size, self.hd
-        Sl = seq[self.rank]
-        x = d_recv.reshape(-1, 3, hp, hd)
-        out = _AllToAll.apply(x, list(seq), [Sl] * P, self.group)          # [P*Sl, 3, hp, hd], source-major
-        return out.view(P, Sl, 3, hp * hd).permute(1, 2, 0, 3).reshape(Sl, 3, P * hp * hd)
+    # step 4' ------------------------------------------------------------------------------
+    def dgrad_exchange(self, dy, w_o, parity):
+        """dy [Sl, dim] (gradient of the out-projection output) -> dO view [S, dl] for this rank's heads: the dgrad
+        GEMM ``dy @ W_o`` whose epilogue stores each 64-column chunk into the head owner's buffer."""
+        lib = _lib.load()
+        D, dl, P = self.dim, self.dl, self.size
+        dy = F_._rowmajor(dy)
+        Sl = dy.shape[0]
+        heap = self.heap
+        slot = self.flag_do[parity]
+        rc = lib.solar_gemm_bf16_scatter(ptr(dy), ptr(w_o), ptr(dy), ptr(None), c_int(Sl), c_int(D), c_int(w_o.shape[0]),
+                                         c_ll(dy.stride(0)), c_ll(w_o.stride(0)), c_ll(dy.stride(0)), c_int(F_.NN), c_int(0),
+                                         ptr(status_word(dy.device)), c_int(0), stream_handle(),
+                                         heap.peer_ptr_array(self.dobuf_off[parity]), heap.flag_ptrs(slot),
+                                         heap.counter_ptr(slot), c_int(P), c_ll(dl), c_int(D), c_int(dl),
+                                         c_int(self._row_start[self.rank]), c_int(0), c_int(0))
+        check(rc, "solar_gemm_bf16_scatter")
+        count("gemm_scatter")
+        return slot
 
-    def tokens_to_heads_grad(self, d_tokens):
-        """d_tokens [Sl, dim] -> [S, dl] (gradient of the attention output in head layout)."""
-        _, seq = self._layout
-        P, dl = self.size, self.dl
-        Sl = d_tokens.shape[0]
-        x = d_tokens.view(Sl, P, dl).permute(1, 0, 2).reshape(P * Sl, dl)
-        return _AllToAll.apply(x, [Sl] * P, list(seq), self.group)        # [S, dl]
+    # step 3' ------------------------------------------------------------------------------
+    def attention_bwd_exchange(self, recv, o, lse, do, scale, parity):
+        """Attention backward over this rank's heads; dq | dk | dv rows land in the token owners' buffers.
+        Returns the local ``[Sl, 3 * dim]`` view (valid after the wait enqueued here)."""
+        from ..ops.attention_bwd_native import ensure_tail_overlap_default
+
+        ensure_tail_overlap_default()
+        lib = _lib.load()
+        S = recv.shape[0]
+        hp, hd, dl, D = self.heads // self.size, self.hd, self.dl, self.dim
+        q, k, v = recv[:, :dl], recv[:, dl:2 * dl], recv[:, 2 * dl:]
+        sq_pad = (S + 127) // 128 * 128
+        scratch = torch.empty(2 * hp * sq_pad, dtype=torch.float32, device=recv.device)
+        heap = self.heap
+        slot = self.flag_dqkv[parity]
+        col = self.rank * dl
+        rc = lib.solar_attn_bwd_scatter(ptr(q), ptr(k), ptr(v), ptr(o), ptr(do), ptr(lse), ptr(scratch), c_int(S), c_int(hp),
+                                        c_int(hd), c_ll(3 * dl), c_ll(hp * hd), c_ll(do.stride(0)), c_float(scale),
+                                        ptr(status_word(recv.device)), stream_handle(),
+                                        heap.peer_ptr_array(self.dqkv_off[parity]), heap.flag_ptrs(slot),
+                                        heap.counter_ptr(slot, 0), heap.counter_ptr(slot, 1), c_int(self.size),
+                                        c_ll(3 * D), c_ll(self.max_local), self._row_start_c, c_int(col), c_int(D + col),
+                                        c_int(2 * D + col))
+        check(rc, "solar_attn_bwd_scatter")
+        count("attn_bwd_scatter", 3)
+        heap.wait(slot, 2 * self.size)                 # the dK/dV kernel and the dQ kernel of every rank
+        Sl = self._row_start[self.rank + 1] - self._row_start[self.rank]
+        return self.dqkv[parity][:Sl]
+
+    # final sequence gather ------------------------------------------------------------------
+    def _push_rows(self, x):
+        lib = _lib.load()
+        x = x.contiguous()
+        heap, slot = self.heap, self.flag_seq
+        S = self._row_start[-1]
+        off = self._row_start[self.rank] * self.dim * 2
+        rc = lib.solar_comm_push(ptr(x), heap.peer_ptr_array(self.seqbuf_off), c_int(self.size), c_ll(off),
+                                 c_ll(x.numel() * 2), heap.flag_ptrs(slot), heap.counter_ptr(slot), stream_handle())
+        check(rc, "solar_comm_push")
+        count("comm_push")
+        heap.wait(slot, self.size)
+        return self.seqbuf[:S].clone()
+
+    def gather_sequence(self, x, B: int):
+        if not (x.is_cuda and B == 1 and x.dtype == torch.bfloat16 and x.shape[1] == self.dim):
+            return super().gather_sequence(x, B)
+        return _GatherSeqFused.apply(x, self)
 
     def close(self) -> None:
         self.heap.close()
 
 
-class FusedQKV(torch.autograd.Function):
-    """xm -> received [S, q_loc|k_loc|v_loc]; forward = steps 1-2 above, backward = reverse all-to-all,
-    RMSNorm/RoPE backward, dgrad and wgrad GEMMs (gradients go to the flat ``main_grad`` buffers)."""
+class FusedSelfAttention(torch.autograd.Function):
+    """Modulated input ``xm [Sl, dim]`` -> out-projection output ``[Sl, dim]`` of one self-attention layer; the four
+    exchanges of the layer (two forward, two backward) ride on the kernels listed in the module docstring.
+    Parameter gradients go to the flat ``main_grad`` buffers."""
 
     @staticmethod
-    def forward(ctx, xm, w, b, nq_w, nk_w, rope, eps, sp, parity, anchors):
+    def forward(ctx, xm, w, b, nq_w, nk_w, rope, w_o, b_o, eps, scale, sp, parity, memo):
+        grads_on = any(ctx.needs_input_grad)
         qkv, rstd_q, rstd_k, recv = sp.qkv_exchange(xm, w, b, nq_w, nk_w, rope, eps, parity)
-        # with autograd the receive buffer (reused two layers later) cannot be the saved tensor
-        out = recv.clone() if any(ctx.needs_input_grad) else recv
-        ctx.save_for_backward(xm, qkv, rstd_q, rstd_k, rope, nq_w, nk_w)
-        ctx.misc = (w, b, sp, eps, anchors)
-        return out
+        cached = None if memo is None else memo[0].pop(memo[1], None)
+        if cached is not None:                      # recompute under selective checkpointing: attention is carried
+            o, lse, tokens = cached
+        else:
+            o, lse, view = sp.attention_exchange(recv, scale, parity)
+            # the receive buffers are reused two layers later: what backward needs is copied out of them
+            storing = memo is not None and memo[0].get("__store__", False)
+            tokens = view.clone() if (grads_on or storing) else view
+            if storing:
+                memo[0][memo[1]] = (o, lse, tokens)
+        y = F_.gemm(tokens, w_o, F_.NT, bias=b_o) if F_._forward_needed(w_o) else tokens.new_empty((tokens.shape[0], w_o.shape[0]))
+        if grads_on:
+            ctx.save_for_backward(xm, qkv, rstd_q, rstd_k, rope, nq_w, nk_w, recv.clone(), o, lse, tokens)
+            ctx.misc = (w, b, w_o, b_o, sp, eps, scale)
+        return y
 
     @staticmethod
-    def backward(ctx, d_recv):
-        xm, qkv, rstd_q, rstd_k, rope, nq_w, nk_w = ctx.saved_tensors
-        w, b, sp, eps, anchors = ctx.misc
-        D = sp.dim
-        Sl = xm.shape[0]
-        g = sp.heads_to_tokens_grad(d_recv.contiguous())                    # [Sl, 3, D]
-        dqkv = torch.empty((Sl, 3 * D), dtype=xm.dtype, device=xm.device)
+    def backward(ctx, dy):
+        xm, qkv, rstd_q, rstd_k, rope, nq_w, nk_w, recv, o, lse, tokens = ctx.saved_tensors
+        w, b, w_o, b_o, sp, eps, scale = ctx.misc
+        parity = sp.next_bwd_parity()
+        D, dl = sp.dim, sp.dl
+        hp, hd = sp.heads // sp.size, sp.hd
+        Sl, S = xm.shape[0], recv.shape[0]
         lib = _lib.load()
+        dy = F_._rowmajor(dy)
+        # 4': dO leaves through the dgrad GEMM's epilogue; the weight / bias gradients run while it lands
+        slot_do = sp.dgrad_exchange(dy, w_o, parity)
+        F_.gemm(dy, tokens, F_.TN, out=w_o.main_grad, accumulate=F_._grad_is_live(w_o))
+        F_._mark_grad_live(w_o)
+        if b_o is not None:
+            F_.accumulate_main_grad(b_o, F_.colsum(dy))
+        sp.heap.wait(slot_do, sp.size)
+        do = sp.dobuf[parity][:S]
+        # 3': attention backward, gradients scattered to the token owners
+        g = sp.attention_bwd_exchange(recv, o, lse, do, scale, parity)          # [Sl, 3D]: dq | dk | dv, all heads
+        # 2': norm + RoPE backward of the q and k blocks in place (the kernel reads a row completely before it writes)
         dws = []
         for i, (nw, rstd) in enumerate(((nq_w, rstd_q), (nk_w, rstd_k))):
-            dy = g[:, i].contiguous()
+            gi = g[:, i * D:(i + 1) * D]
             x = qkv[:, i * D:(i + 1) * D]
-            dx = dqkv[:, i * D:(i + 1) * D]
             splits = F_._splits_for(D, 1)
             part = torch.empty((splits, D), dtype=torch.float32, device=xm.device)
-            rc = lib.solar_rmsnorm_rope_bwd(ptr(dy), c_ll(dy.stride(0)), ptr(x), c_ll(x.stride(0)), ptr(dx),
-                                            c_ll(dx.stride(0)), ptr(nw), ptr(rope), c_int(rope.shape[1]), ptr(rstd),
+            rc = lib.solar_rmsnorm_rope_bwd(ptr(gi), c_ll(gi.stride(0)), ptr(x), c_ll(x.stride(0)), ptr(gi),
+                                            c_ll(gi.stride(0)), ptr(nw), ptr(rope), c_int(rope.shape[1]), ptr(rstd),
                                             ptr(part), c_int(splits), c_ll(Sl), c_int(D), c_int(0), stream_handle())
             check(rc, "solar_rmsnorm_rope_bwd")
             count("rmsnorm_rope_bwd")
             dws.append(part.sum(0))
-        dqkv[:, 2 * D:] = g[:, 2]
-        dxm = F_.gemm(dqkv, w, F_.NN)
-        F_.gemm(dqkv, xm, F_.TN, out=w.main_grad, accumulate=F_._grad_is_live(w))
+        dxm = F_.gemm(g, w, F_.NN)
+        F_.gemm(g, xm, F_.TN, out=w.main_grad, accumulate=F_._grad_is_live(w))
         F_._mark_grad_live(w)
-        F_.accumulate_main_grad(b, F_.colsum(dqkv))
-        return dxm, None, None, dws[0], dws[1], None, None, None, None, None
-
-
-class FusedAttention(torch.autograd.Function):
-    """received q|k|v -> attention output in token layout [Sl, dim]; forward = step 3, backward =
-    reverse all-to-all of the output gradient + the attention backward kernels."""
-
-    @staticmethod
-    def forward(ctx, recv, scale, sp, parity, memo):
-        cached = None if memo is None else memo[0].pop(memo[1], None)
-        if cached is not None:
-            o, lse, tokens = cached
-        else:
-            o, lse, view = sp.attention_exchange(recv, scale, parity)
-            tokens = view.clone() if any(ctx.needs_input_grad) else view
-            if memo is not None and memo[0].get("__store__", False):
-                memo[0][memo[1]] = (o, lse, tokens)
-        ctx.save_for_backward(recv, o, lse)
-        ctx.misc = (scale, sp)
-        return tokens
-
-    @staticmethod
-    def backward(ctx, d_tokens):
-        from ..ops.attention_native import attn_bwd
-
-        recv, o, lse = ctx.saved_tensors
-        scale, sp = ctx.misc
-        S = recv.shape[0]
-        hp, hd, dl = sp.heads // sp.size, sp.hd, sp.dl
-        do = sp.tokens_to_heads_grad(d_tokens.contiguous()).view(1, S, hp, hd)
-        q = recv[:, :dl].view(1, S, hp, hd)
-        k = recv[:, dl:2 * dl].view(1, S, hp, hd)
-        v = recv[:, 2 * dl:].view(1, S, hp, hd)
-        dq, dk, dv = attn_bwd(q, k, v, o, lse, do, scale)
-        d_recv = torch.cat([dq.reshape(S, dl), dk.reshape(S, dl), dv.reshape(S, dl)], dim=1)
-        return d_recv, None, None, None, None
+        F_.accumulate_main_grad(b, F_.colsum(g))
+        return dxm, None, None, dws[0], dws[1], None, None, None, None, None, None, None, None

@@ -3,10 +3,13 @@
 ``SymmetricHeap(nbytes, group)`` allocates the same-size device buffer on every rank of the group,
 exchanges IPC handles through the process group (host-side plumbing, done once) and maps every
 peer's buffer into this process.  ``ptrs[r]`` is rank r's buffer as addressable from here;
-``tensor(...)`` gives torch views of the local buffer.  Flags are u32 words at the start of the
-heap: ``flag_ptrs(slot)`` returns, per rank, the address of that slot in the rank's memory;
-producers add 1 to it on every rank (``csrc/comm.cuh``) and ``wait(slot, expected)`` enqueues a
-bounded device-side wait on the local word.
+``alloc(...)`` gives torch views of the local buffer.  Flags are groups of four u32 words at the
+start of the heap -- the flag itself, two last-CTA counters for producer kernels and the round
+counter of the waiting side: ``flag_ptrs(slot)`` returns, per rank, the address of the flag word in
+that rank's memory; producers add 1 to it on every rank (``csrc/comm.cuh``) and
+``wait(slot, signals)`` enqueues a bounded device-side wait for ``signals`` more arrivals than the
+previous round had.  The round count lives on the device, so a launch sequence that contains waits
+can be captured once in a CUDA graph and replayed.
 """
 from __future__ import annotations
 
@@ -56,7 +59,6 @@ class SymmetricHeap:
             self.ptrs.append(int(out.value))
         self._bytes = torch.as_tensor(_RawCuda(self.local_ptr, self.nbytes), device=self.device)
         self._cursor = FLAG_BYTES
-        self._flag_epoch: dict[int, int] = {}
         self._next_slot = 0
         dist.barrier(group=group)
 
@@ -79,29 +81,59 @@ class SymmetricHeap:
 
     # -- flags ----------------------------------------------------------------------------
     def new_flag(self) -> int:
+        """A flag group: word ``slot`` is the flag, ``slot + 1`` / ``slot + 2`` are last-CTA counters for up to two
+        producer kernels that may run at the same time, ``slot + 3`` is the waiting side's round counter."""
         slot = self._next_slot
-        self._next_slot += 2           # slot: the flag word; slot + 1: the producer's local CTA counter
+        self._next_slot += 4
         if self._next_slot * 4 > FLAG_BYTES:
             raise MemoryError("out of flag slots")
-        self._flag_epoch[slot] = 0
         return slot
 
     def flag_ptrs(self, slot: int):
         return (ctypes.c_void_p * self.world)(*[p + 4 * slot for p in self.ptrs])
 
-    def counter_ptr(self, slot: int):
-        return ctypes.c_void_p(self.local_ptr + 4 * (slot + 1))
+    def counter_ptr(self, slot: int, which: int = 0):
+        return ctypes.c_void_p(self.local_ptr + 4 * (slot + 1 + int(which)))
 
-    def expect(self, slot: int, signals_per_round: Optional[int] = None) -> int:
-        """Advance the slot's epoch and return the value the local flag must reach."""
-        self._flag_epoch[slot] += signals_per_round if signals_per_round is not None else self.world
-        return self._flag_epoch[slot]
+    def epoch_ptr(self, slot: int):
+        return ctypes.c_void_p(self.local_ptr + 4 * (slot + 3))
 
-    def wait(self, slot: int, expected: int, limit_seconds: float = 20.0) -> None:
-        check(self.lib.solar_comm_wait(ctypes.c_void_p(self.local_ptr + 4 * slot), ctypes.c_uint(expected & 0xFFFFFFFF),
-                                       ptr(status_word(self.device)), ctypes.c_double(limit_seconds), stream_handle()),
-              "solar_comm_wait")
+    def wait(self, slot: int, signals: Optional[int] = None, limit_seconds: float = 20.0) -> None:
+        """Bounded device-side wait until ``signals`` (default: one per rank) more arrivals than the previous
+        round's total have reached this rank's flag word.  On a timeout the kernel sets the status word and
+        returns; ``ops.read_status`` / ``ops.check_status`` report it."""
+        add = self.world if signals is None else int(signals)
+        check(self.lib.solar_comm_wait_round(ctypes.c_void_p(self.local_ptr + 4 * slot), self.epoch_ptr(slot),
+                                             ctypes.c_uint(add), ptr(status_word(self.device)),
+                                             ctypes.c_double(limit_seconds), stream_handle()),
+              "solar_comm_wait_round")
         _lib.count("comm_wait")
+
+    def signal(self, slot: int) -> None:
+        """Add 1 to the flag word of ``slot`` on every rank, ordered after everything enqueued so far."""
+        check(self.lib.solar_comm_signal(self.flag_ptrs(slot), ctypes.c_int(self.world), stream_handle()),
+              "solar_comm_signal")
+        _lib.count("comm_signal")
+
+    def new_allsum(self, n: int):
+        """A small all-reduce (sum of ``n <= 256`` fp32 values over the ranks) that runs as one kernel of this
+        library; returns a callable ``(src, out) -> out``."""
+        table, off = self.alloc((2, self.world, int(n)), torch.float32)
+        slot = self.new_flag()
+        tables = self.peer_ptr_array(off)
+        flags = self.flag_ptrs(slot)
+
+        def allsum(src: torch.Tensor, out: torch.Tensor, limit_seconds: float = 20.0) -> torch.Tensor:
+            assert src.dtype == torch.float32 and out.dtype == torch.float32 and src.numel() == n == out.numel()
+            check(self.lib.solar_comm_allsum(ptr(src), ctypes.c_int(n), tables, flags, ctypes.c_int(self.world),
+                                             ctypes.c_int(self.rank), self.epoch_ptr(slot), ptr(out),
+                                             ptr(status_word(self.device)), ctypes.c_double(limit_seconds),
+                                             stream_handle()), "solar_comm_allsum")
+            _lib.count("comm_allsum")
+            return out
+
+        allsum.table = table
+        return allsum
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)

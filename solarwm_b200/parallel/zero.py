@@ -5,7 +5,7 @@ the full fp32 ``main_grad`` buffers, but owns the fp32 master weights, both Adam
 of one contiguous ``1 / world`` shard of every flat buffer.  One ``step``:
 
     reduce-scatter   this rank's shard of every gradient buffer = sum over ranks
-    clip             global norm from the shard sums of squares (one scalar all-reduce)
+    clip             global norm from the shard sums of squares (one small all-reduce)
     AdamW            fused kernel on the shard
     all-gather       refreshed bf16 parameters back into every rank's buffer
 
@@ -14,11 +14,18 @@ Two transports:
 * ``collective``: ``reduce_scatter_tensor`` / ``all_gather_into_tensor`` of the process group
   (NCCL on GPUs; on gloo, which has no reduce-scatter, an all-reduce followed by a local slice).
   This is what the reference gets from FSDP1 (solar/backends/wan22/runtime/distributed.py:73-123).
-* ``fused``: parameter and gradient buffers live in a ``SymmetricHeap``; ``solar_zero_reduce`` pulls
-  the shard from every peer over NVLink while summing, ``solar_zero_adamw_push`` applies Adam and
-  stores the new bf16 parameters straight into every peer's buffer (``csrc/zero.cu``).  Two flag
-  rounds fence the step: "my gradients are complete" before the pull and "my pushes have landed"
-  after it.
+* ``fused``: parameter and gradient buffers live in a ``SymmetricHeap`` and no library collective runs:
+
+  - reduce-scatter UNDER backward: as soon as a unit's gradients are final (``unit_ready``, called from the
+    model's backward as each block finishes) a side stream exchanges a flag round with the peers and
+    ``solar_zero_reduce`` pulls this rank's shard from every peer over NVLink while summing (and accumulating the
+    sum of squares), so only the last unit's reduction is exposed after backward;
+  - the global norm is one kernel (``SymmetricHeap.new_allsum``); a non-zero bounded-wait status word on ANY rank is
+    folded into it as infinity, so every rank sees a non-finite norm, skips the update and can stop together;
+  - ``solar_zero_adamw_push_multi`` applies AdamW to every shard of every buffer in ONE launch and stores the new
+    bf16 parameters straight into every peer's buffer; learning rate and bias corrections are read from device
+    memory, so the launch sequence of a step is identical from step to step (CUDA-graph replayable);
+  - one flag round ("my pushes have landed") fences the step.
 """
 from __future__ import annotations
 
@@ -32,14 +39,16 @@ from .. import ops
 from ..engine.optim import FlatAdamW
 from ..ops import _lib
 from ..ops._lib import check, ptr, stream_handle
+from ..ops.functional import status_word
 
 
 class ZeroAdamW(FlatAdamW):
     def __init__(self, units: Iterable, group=None, *, transport: str = "collective", heap=None, replica_group=None,
-                 **kw):
+                 reduce_ctas: int = 32, **kw):
         """``group``: the ranks one copy of the optimizer state is sharded over.  ``replica_group`` (hybrid
         sharding): the ranks that hold the SAME shard in other shard groups (e.g. one per node); the reduced
-        gradient shard is summed over it before the update, so every replica applies the identical step."""
+        gradient shard is summed over it before the update, so every replica applies the identical step.
+        ``reduce_ctas``: CTAs of one overlapped reduce launch (a small grid leaves the SMs to backward)."""
         self.group = group
         self.replica_group = replica_group
         world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -50,6 +59,7 @@ class ZeroAdamW(FlatAdamW):
                 raise ValueError("flat units must be padded to a multiple of 4 * shard world (FlatUnit pad_to)")
         self.transport = transport
         self.heap = heap
+        self.reduce_ctas = int(reduce_ctas)
         self._heap_off = {}
         if transport == "fused":
             if heap is None:
@@ -63,11 +73,23 @@ class ZeroAdamW(FlatAdamW):
                 u.move_(flat, flat_v)
                 u.move_grads_(grad, grad_v)
                 self._heap_off[i] = {"m": (off_p, off_g), "v": (off_pv, off_gv)}
-            self._flag_grads = heap.new_flag()
+            self._flag_unit = [heap.new_flag() for _ in units]
             self._flag_params = heap.new_flag()
+            self._allsum = heap.new_allsum(2)
             self._lib = _lib.load()
         super().__init__(units, shard_rank=rank, shard_world=world, **kw)
         self.world, self.rank = world, rank
+        self._reduced_units: set = set()
+        self._unit_index = {id(u): i for i, u in enumerate(self.units)}
+        if transport == "fused" and world > 1:
+            dev = self.units[0].device
+            self._comm_stream = torch.cuda.Stream(device=dev)
+            self._dyn = torch.zeros(4, dtype=torch.float32, device=dev)
+            self._dyn_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+            self._norm_in = torch.zeros(2, dtype=torch.float32, device=dev)
+            self._norm_out = torch.zeros(2, dtype=torch.float32, device=dev)
+            self._host_prepared = False
+            self._build_table()
 
     # ------------------------------------------------------------------------------------
     def _buffers(self):
@@ -75,30 +97,85 @@ class ZeroAdamW(FlatAdamW):
             for key, buf, g in (("m", u.flat, u.grad), ("v", u.flat_v, u.grad_v)):
                 yield i, key, buf, g, st[key]
 
-    def _signal_and_wait(self, slot: int) -> None:
-        h = self.heap
-        check(self._lib.solar_comm_signal(h.flag_ptrs(slot), ctypes.c_int(h.world), stream_handle()), "solar_comm_signal")
-        _lib.count("comm_signal")
-        h.wait(slot, h.expect(slot))
+    def _build_table(self) -> None:
+        """Device table of every shard (one entry per flat buffer) for the single-launch AdamW + push."""
+        lib = self._lib
+        lib.solar_zero_chunk_elems.restype = ctypes.c_longlong
+        seg_bytes, chunk = int(lib.solar_zero_segment_bytes()), int(lib.solar_zero_chunk_elems())
+        entries = list(self._buffers())
+        host = (ctypes.c_ubyte * (seg_bytes * len(entries)))()
+        chunks = 0
+        for idx, (i, key, buf, g, s) in enumerate(entries):
+            a, b = s["range"]
+            is_bf16 = buf.dtype == torch.bfloat16
+            master = s["master"]
+            if master is None:
+                if is_bf16:
+                    raise ValueError("bf16 buffers need an fp32 master copy")
+                # fp32 vector units: the live shard is its own master; the kernel updates a copy and pushes it
+                master = self.__dict__.setdefault("_vec_master", {}).setdefault((i, key), buf[a:b].clone())
+            check(lib.solar_zero_segment_fill(host, ctypes.c_int(idx), ctypes.c_longlong(self._heap_off[i][key][0]),
+                                              ctypes.c_longlong(a), ctypes.c_longlong(b - a), ctypes.c_longlong(chunks),
+                                              ptr(master), ptr(s["exp_avg"]), ptr(s["exp_avg_sq"]),
+                                              ptr(self._reduced(i, key, b - a, buf.device)),
+                                              ptr(s["ema"]) if s["ema"] is not None else None,
+                                              ctypes.c_int(1 if is_bf16 else 0)), "solar_zero_segment_fill")
+            chunks += (b - a + chunk - 1) // chunk
+        raw = torch.frombuffer(bytearray(host), dtype=torch.uint8).clone()
+        self._table = raw.to(self.units[0].device)
+        self._n_seg, self._n_chunks = len(entries), chunks
+
+    # reduce-scatter ------------------------------------------------------------------------
+    def unit_ready(self, unit_or_index) -> None:
+        """The gradients of one unit are final on this rank: start its reduce-scatter on the side stream.  Called
+        from backward (per block) by the model; units nobody announced are reduced by ``reduce_scatter_grads``.
+        No-op for the collective transport and for a single rank."""
+        if self.transport != "fused" or self.world == 1:
+            return
+        i = unit_or_index if isinstance(unit_or_index, int) else self._unit_index[id(unit_or_index)]
+        if i in self._reduced_units:
+            return
+        self._reduced_units.add(i)
+        self.units[i].finalize_grads()
+        main = torch.cuda.current_stream()
+        done = torch.cuda.Event()
+        done.record(main)
+        h, side = self.heap, self._comm_stream
+        with torch.cuda.stream(side):
+            side.wait_event(done)
+            slot = self._flag_unit[i]
+            h.signal(slot)                               # this rank's gradients of unit i are complete
+            h.wait(slot)                                 # ... and so are every peer's
+            u, st = self.units[i], self.state[i]
+            for key, g in (("m", u.grad), ("v", u.grad_v)):
+                a, b = st[key]["range"]
+                out = self._reduced(i, key, b - a, g.device)
+                check(self._lib.solar_zero_reduce(h.peer_ptr_array(self._heap_off[i][key][1]), ctypes.c_int(self.world),
+                                                  ctypes.c_longlong(a), ctypes.c_longlong(b - a), ptr(out),
+                                                  ptr(self._norm_sq), ctypes.c_int(self.reduce_ctas), stream_handle()),
+                      "solar_zero_reduce")
+                _lib.count("zero_reduce")
 
     def reduce_scatter_grads(self) -> torch.Tensor:
         """Leaves the group-summed gradient in this rank's shard of every ``main_grad`` buffer and
         returns the (device) sum of squares of the local shards."""
-        self._norm_sq.zero_()
         if self.world == 1:
+            self._norm_sq.zero_()
             return self.local_grad_sumsq()
         if self.transport == "fused":
-            self._signal_and_wait(self._flag_grads)          # every rank's backward is complete
-            for i, key, buf, g, s in self._buffers():
-                a, b = s["range"]
-                off_g = self._heap_off[i][key][1]
-                out = self._reduced(i, key, b - a, g.device)
-                check(self._lib.solar_zero_reduce(self.heap.peer_ptr_array(off_g), ctypes.c_int(self.world),
-                                                  ctypes.c_longlong(a), ctypes.c_longlong(b - a), ptr(out),
-                                                  ptr(self._norm_sq), ctypes.c_int(0), stream_handle()),
-                      "solar_zero_reduce")
-                _lib.count("zero_reduce")
+            for i in sorted(self._reduced_units):
+                # a gradient that autograd delivered after the unit's overlapped reduce started would be lost
+                late = [n for n, p in self.units[i].params.items() if p.grad is not None]
+                if late:
+                    raise RuntimeError(f"gradients arrived after unit {i} was announced ready: {late[:3]}")
+            for i in range(len(self.units)):
+                self.unit_ready(i)
+            joined = torch.cuda.Event()
+            joined.record(self._comm_stream)
+            torch.cuda.current_stream().wait_event(joined)
+            self._reduced_units.clear()
             return self._norm_sq
+        self._norm_sq.zero_()
         backend = dist.get_backend(self.group)
         for i, key, buf, g, s in self._buffers():
             a, b = s["range"]
@@ -127,6 +204,16 @@ class ZeroAdamW(FlatAdamW):
         if self.replica_group is not None and dist.get_world_size(self.replica_group) > 1:
             self._replica_sum()
             sumsq = self._shard_sumsq()              # the shards changed: recompute their sum of squares
+        if self.world > 1 and self.transport == "fused":
+            # [sum of squares, "a bounded wait gave up on this rank"] summed over the ranks by one kernel of this
+            # library; a failed wait anywhere makes the norm infinite everywhere (the update is then skipped)
+            self._norm_in[0:1].copy_(sumsq.view(1))
+            self._norm_in[1:2].copy_(status_word(sumsq.device).ne(0).to(torch.float32))
+            self._allsum(self._norm_in, self._norm_out)
+            total = torch.where(self._norm_out[1] > 0, torch.full_like(self._norm_out[0], float("inf")), self._norm_out[0])
+            if sumsq.data_ptr() == self._norm_sq.data_ptr():
+                self._norm_sq.zero_()                # consumed: the next step's overlapped reduces add into it again
+            return total.sqrt()
         if self.world > 1:
             dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
         return sumsq.sqrt()
@@ -140,32 +227,51 @@ class ZeroAdamW(FlatAdamW):
             first = False
         return self._norm_sq
 
+    # update ----------------------------------------------------------------------------------
+    def begin_step_host(self) -> None:
+        """Host half of a fused step: advance the step count and stage {lr, 1 - beta1^t, 1 - beta2^t} in pinned
+        memory.  ``step`` calls it itself; a caller that REPLAYS a captured step calls it before every replay (the
+        captured copy then picks the fresh values up) and sets ``_host_prepared`` while capturing."""
+        self.step_count += 1
+        b1, b2 = self.betas
+        self._dyn_host[0] = self.lr
+        self._dyn_host[1] = 1.0 - b1 ** self.step_count
+        self._dyn_host[2] = 1.0 - b2 ** self.step_count
+
     def step(self) -> None:
         if self.world == 1 or self.transport != "fused":
             super().step()
             if self.world > 1:
                 self.all_gather_params()
             return
-        self.step_count += 1
+        if not self._host_prepared:
+            self.begin_step_host()
+        self._dyn.copy_(self._dyn_host, non_blocking=True)
         b1, b2 = self.betas
-        for i, key, buf, g, s in self._buffers():
-            a, b = s["range"]
-            off_p = self._heap_off[i][key][0]
-            is_bf16 = buf.dtype == torch.bfloat16
-            master = s["master"] if s["master"] is not None else buf[a:b]
-            if s["master"] is None and not is_bf16:
-                # fp32 vector units: the live shard is its own master; push a copy to the peers
-                master = self.__dict__.setdefault("_vec_master", {}).setdefault((i, key), buf[a:b].clone())
-            check(self._lib.solar_zero_adamw_push(
-                self.heap.peer_ptr_array(off_p), ctypes.c_int(1 if is_bf16 else 0), ctypes.c_int(self.world),
-                ctypes.c_longlong(a), ctypes.c_longlong(b - a), ptr(master), ptr(s["exp_avg"]), ptr(s["exp_avg_sq"]),
-                ptr(self._reduced(i, key, b - a, buf.device)), ptr(s["ema"]) if s["ema"] is not None else None,
-                ctypes.c_float(self.lr), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(self.eps),
-                ctypes.c_float(self.weight_decay), ctypes.c_int(self.step_count),
-                ctypes.c_float(0.0 if self.ema_decay is None else self.ema_decay), ptr(self._scale), ptr(self._skip),
-                ctypes.c_int(0), stream_handle()), "solar_zero_adamw_push")
-            _lib.count("zero_adamw_push")
-        self._signal_and_wait(self._flag_params)              # every rank's pushes have landed here
+        h = self.heap
+        heaps = (ctypes.c_void_p * self.world)(*h.ptrs)
+        check(self._lib.solar_zero_adamw_push_multi(
+            ptr(self._table), ctypes.c_int(self._n_seg), ctypes.c_longlong(self._n_chunks), heaps,
+            ctypes.c_int(self.world), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(self.eps),
+            ctypes.c_float(self.weight_decay), ctypes.c_float(0.0 if self.ema_decay is None else self.ema_decay),
+            ptr(self._dyn), ptr(self._scale), ptr(self._skip), ctypes.c_int(0), stream_handle()),
+            "solar_zero_adamw_push_multi")
+        _lib.count("zero_adamw_push")
+        h.signal(self._flag_params)                    # every rank's pushes have landed here
+        h.wait(self._flag_params)
+
+    def _gather_shard(self, shard: torch.Tensor, total: int) -> torch.Tensor:
+        """All ranks' shards of one state tensor, concatenated in rank order (a collective over the shard group)."""
+        if self.world == 1:
+            return shard
+        shard = shard.contiguous()
+        if dist.get_backend(self.group) == "gloo":
+            parts = [torch.empty_like(shard) for _ in range(self.world)]
+            dist.all_gather(parts, shard, group=self.group)
+            return torch.cat(parts)
+        full = torch.empty(total, dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(full, shard, group=self.group)
+        return full
 
     def all_gather_params(self) -> None:
         backend = dist.get_backend(self.group)

@@ -88,6 +88,14 @@ def collective_rank_zero_call(call: Callable[[], T], *, dist, label: str, rank=N
     return box[0]
 
 
+def raise_if_device_wait_failed(code: int, *, dist, label: str = "fused transport", rank=None, world_size=None) -> None:
+    """``code``: this rank's bounded-wait status word (0 = every device-side wait completed).  All ranks exchange their
+    codes and, when any is non-zero, raise the SAME message before the next optimizer update or checkpoint: a wait that
+    gave up means a consumer kernel ran on a half-filled receive buffer, so the step's result must not be kept."""
+    text = "" if int(code) == 0 else f"a device-side bounded wait gave up (status code {int(code)})"
+    propagate_collective_error(text, dist=dist, label=label, rank=rank, world_size=world_size)
+
+
 class DataReadiness:
     """All ranks finish (or fail) their batch read together, on a CPU-side gloo group."""
 

@@ -294,3 +294,61 @@ def test_data_parallel_ranks_read_disjoint_corpus_samples(tmp_path):
     assert got[0]["final"] == got[1]["final"] == 2
     assert len(got[0]["ids"]) == 2 and not set(got[0]["ids"]) & set(got[1]["ids"])          # disjoint ownership
     assert got[0]["norms"] == got[1]["norms"]                                               # one all-reduced gradient
+
+
+def _sharded_ckpt_worker(rank, world, path, out, root, resume_from):
+    """SP = 2 with the optimizer (and its EMA shadow) sharded over both ranks: train, save, or resume and continue."""
+    import json
+    import os
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world))
+    _init(rank, world, path)
+    from solarwm_b200.backends.wan22.runtime import run_training
+
+    config = {"schema": "solarwm.run.v1", "action": "train", "name": "sharded-ckpt",
+              "model": {"family": "wan22_ti2v_5b", "architecture": "tiny", "timestep_shift": 5.0, "nonzero_head_init": True,
+                        "camera_translation_transform": "linear"},
+              "data": {"source": "synthetic", "seed": 0, "pixel_frames": 81, "latent_height": 4, "latent_width": 4},
+              "distributed": {"world_size": 2, "sequence_parallel_size": 2},
+              "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "micro_batch_size": 1,
+                        "grad_accum": 1, "global_batch_size": 1, "max_steps": 4, "warmup_steps": 1,
+                        "optimizer": {"lr": 1e-3, "betas": [0.9, 0.95], "eps": 1e-8, "weight_decay": 0.01, "grad_clip": 1.0},
+                        "ema": {"enabled": True, "decay": 0.9}, "zero": {"enabled": True, "transport": "collective"}},
+              "checkpoint": ({"mode": "full_resume", "resume_from": resume_from} if resume_from else {"mode": "none"}),
+              "runtime": {"output_dir": root, "device": "cpu", "save_every": 0 if resume_from else 2, "validate_every": 0}}
+    result = run_training(config)
+    events = [json.loads(l) for l in open(os.path.join(root, "events", f"rank-{rank:05d}.jsonl"))]
+    steps = {e["step"]: (e["losses"], e["gradient_norm"]) for e in events if e["event"] == "optimizer_step"}
+    torch.save({"steps": steps, "final": result["final_step"]}, f"{out}.{rank}")
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def test_sharded_optimizer_and_ema_checkpoint_resumes_exactly(tmp_path):
+    """Two ranks, optimizer state and EMA sharded over them: the checkpoint holds EVERY rank's share (un-sharded
+    layout), and a run resumed from step 2 reproduces steps 3 and 4 of the uninterrupted run."""
+    a, b = str(tmp_path / "a"), str(tmp_path / "b")
+    mp.spawn(_sharded_ckpt_worker, args=(2, str(tmp_path / "rdv-a"), str(tmp_path / "ra"), a, None), nprocs=2, join=True)
+    ckpt_dir = tmp_path / "a" / "checkpoint_model_000002"
+    payload = torch.load(ckpt_dir / "model.pt", map_location="cpu", weights_only=True)
+    opt = payload["optimizer"]
+    assert opt["layout"] == "full"
+    for unit in opt["units"]:
+        for key in ("m", "v"):
+            n = unit[key]["numel"]
+            assert unit[key]["exp_avg"].numel() == n and unit[key]["exp_avg_sq"].numel() == n and unit[key]["ema"].numel() == n
+    # second halves (rank 1's shards) are real state, not zeros
+    first = opt["units"][1]["m"]
+    half = first["numel"] // 2
+    assert first["exp_avg_sq"][half:].abs().sum() > 0 and first["exp_avg_sq"][:half].abs().sum() > 0
+    assert first["master"] is None or first["master"][half:].abs().sum() > 0      # fp32 runs have no separate master
+    assert set(payload["generator_ema"]) == set(payload["generator"])
+    name = "blocks.0.ffn.0.weight"
+    assert not torch.equal(payload["generator_ema"][name].float(), payload["generator"][name].float())
+    mp.spawn(_sharded_ckpt_worker, args=(2, str(tmp_path / "rdv-b"), str(tmp_path / "rb"), b, str(ckpt_dir)), nprocs=2, join=True)
+    ra = [torch.load(f"{tmp_path / 'ra'}.{r}", weights_only=True) for r in range(2)]
+    rb = [torch.load(f"{tmp_path / 'rb'}.{r}", weights_only=True) for r in range(2)]
+    assert sorted(rb[0]["steps"]) == [3, 4] and rb[0]["final"] == rb[1]["final"] == 4
+    for s in (3, 4):
+        for r in range(2):
+            assert rb[r]["steps"][s] == ra[r]["steps"][s], (s, r, rb[r]["steps"][s], ra[r]["steps"][s])

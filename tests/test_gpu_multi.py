@@ -1,7 +1,9 @@
-"""Two-GPU checks (skipped with fewer devices): the fused NVLink Ulysses path against the NCCL
-collective path -- same forward output and the same parameter gradients --, the peer-memory
-runtime's push/flag protocol including a bounded wait that is made to run out, and the
-ZeRO-sharded AdamW with fused peer reduce / push against its NCCL form."""
+"""Multi-GPU checks (skipped with fewer devices): the fused NVLink Ulysses path (forward AND backward exchanges
+inside the kernels) against the NCCL collective path -- same forward output and the same parameter gradients, on 2
+ranks and, where the box has them, on 4 / 8 ranks with 31 frames split unevenly --, the peer-memory runtime's
+push / flag protocol including a bounded wait that is made to run out, the ZeRO-sharded AdamW with overlapped peer
+reduce / single-launch push against its NCCL form, and the whole training step replayed as one CUDA graph against
+the same step run eagerly."""
 import os
 from datetime import timedelta
 
@@ -42,10 +44,17 @@ def _worker(rank, world, port, out_path):
                              ctypes.c_longlong(rank * 4096), ctypes.c_longlong(4096), heap.flag_ptrs(slot),
                              heap.counter_ptr(slot), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0
-    heap.wait(slot, heap.expect(slot))
+    heap.wait(slot)
     torch.cuda.synchronize()
     result["push_ok"] = bool(all(torch.all(buf[r] == r + 1).item() for r in range(world)))
-    heap.wait(slot, heap.expect(slot), limit_seconds=0.3)       # no producer: must give up by itself
+    # the small all-sum kernel (used for the gradient norm): twice, so that both table parities are exercised
+    allsum = heap.new_allsum(2)
+    got = torch.zeros(2, device="cuda")
+    for rnd in range(3):
+        allsum(torch.tensor([float(rank + 1 + rnd), 1.0], device="cuda"), got)
+        torch.cuda.synchronize()
+        result[f"allsum_{rnd}"] = got.tolist() == [float(sum(r + 1 + rnd for r in range(world))), float(world)]
+    heap.wait(slot, limit_seconds=0.3)       # no producer: must give up by itself
     torch.cuda.synchronize()
     from solarwm_b200.ops.functional import status_word
 
@@ -98,7 +107,8 @@ def _worker(rank, world, port, out_path):
             if r.norm() > 1e-6:
                 worst = max(worst, ((gr[n] - r).norm() / r.norm()).item())
         if key[0] == "fused":
-            result[f"fused_kernels_{key[1]}"] = (counters.get("gemm_scatter", 0), counters.get("attn_fwd_scatter", 0))
+            result[f"fused_kernels_{key[1]}"] = (counters.get("gemm_scatter", 0), counters.get("attn_fwd_scatter", 0),
+                                                 counters.get("attn_bwd_scatter", 0))
     result["worst_grad_rel"] = worst
     result["infer_rel"] = ((outs["fused_infer"] - ref_out).norm() / ref_out.norm()).item()
     # ---- ZeRO-sharded AdamW: fused peer reduce / push against the NCCL collectives
@@ -129,6 +139,8 @@ def _worker(rank, world, port, out_path):
         for u in (u_c, u_f):
             u.grad.copy_(gm)
             u.grad_v.copy_(gv)
+            for prm in u.params.values():
+                prm.grad_live = True                # written this step: finalize_grads must not clear them
         norms.append((float(z_c.sharded_step(1.0)), float(z_f.sharded_step(1.0))))
         torch.cuda.synchronize()
         dist.barrier()
@@ -169,10 +181,114 @@ def test_fused_ulysses_matches_collective_on_two_gpus(tmp_path):
     mp.spawn(_worker, args=(2, 29541, out), nprocs=2, join=True)
     for rank in range(2):
         r = torch.load(f"{out}.{rank}", weights_only=True)
-        assert r["push_ok"] and r["timeout_reported"], r
+        assert r["push_ok"] and r["timeout_reported"] and r["allsum_0"] and r["allsum_1"] and r["allsum_2"], r
         assert r["out_fused_none"] < 2e-2 and r["out_fused_selective"] < 2e-2 and r["out_nccl_selective"] < 1e-6, r
         assert r["infer_rel"] < 2e-2 and r["worst_grad_rel"] < 6e-2, r
-        assert r["fused_kernels_none"] == (2, 2) and r["fused_kernels_selective"] == (4, 2), r
+        # per layer: forward QKV GEMM scatter + backward dO GEMM scatter; attention forward scatter; three backward kernels
+        assert r["fused_kernels_none"] == (4, 2, 6) and r["fused_kernels_selective"] == (6, 2, 6), r
         assert r["zero_ranks_agree"] and r["zero_param_diff"] < 1e-2 and r["zero_vec_diff"] < 1e-5, r
         assert r["tile_parallel_diff"] < 1e-5, r
         assert r["zero_ema_diff"] < 1e-5 and all(abs(a - b) < 1e-3 * max(a, 1.0) for a, b in r["zero_norms"]), r
+
+
+def _wide_worker(rank, world, port, out_path):
+    """4 or 8 ranks, 31 latent frames (uneven whole-frame split), one head per rank: forward bit-identity and
+    gradients of the fused exchanges against the NCCL path; then trainer steps eager against graph replay."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=timedelta(seconds=180),
+                            device_id=torch.device("cuda", rank))
+    from solarwm_b200 import ops
+    from solarwm_b200.backends.wan22.stage0p5 import Stage0p5Options, WanStage0p5Trainer
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+    from solarwm_b200.parallel.fused_ulysses import FusedUlysses
+    from solarwm_b200.parallel.symm import SymmetricHeap
+    from solarwm_b200.parallel.ulysses import UlyssesCollective
+
+    result = {}
+    heads = world
+    cfg = WanConfig(model_type="ti2v", in_dim=16, out_dim=16, dim=128 * heads, ffn_dim=512, num_heads=heads, num_layers=3,
+                    text_dim=128, text_len=64, freq_dim=64)
+    F, H, W = 31, 8, 12                                     # 24 tokens per frame, 744 tokens, frames split unevenly
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 16, F, H, W, generator=g).cuda()
+    ctx = torch.randn(1, 64, 128, generator=g).cuda()
+    t = (torch.rand(1, F, generator=g) * 1000).cuda()
+    tgt = torch.randn(1, 16, F, H, W, generator=g).cuda()
+    tokens = F * (H // 2) * (W // 2)
+    fused = FusedUlysses(None, max_tokens=tokens, dim=cfg.dim, num_heads=heads, max_frame_tokens=64)
+    outs = {}
+    for name, sp in (("nccl", UlyssesCollective(None)), ("fused", fused)):
+        model = WanDiT(cfg, device="cuda", dtype=torch.bfloat16, seed=3)
+        with torch.no_grad():
+            model.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator(device="cuda").manual_seed(1))
+        model.sp = sp
+        model.ensure_grads()
+        out = model(x, t, ctx)
+        ((out.float() - tgt) ** 2).mean().backward()
+        model.finalize_grads()
+        UlyssesCollective.sum_gradients_(sp, [gr for u in model.units() for gr in (u.grad, u.grad_v)])
+        torch.cuda.synchronize()
+        ops.check_status()
+        outs[name] = (out.detach().float().cpu(), {n: p.main_grad.float().cpu() for n, p in model.named_parameters()})
+    result["forward_identical"] = bool(torch.equal(outs["nccl"][0], outs["fused"][0]))
+    worst, worst_name = 0.0, ""
+    for n, r in outs["nccl"][1].items():
+        if r.norm() > 1e-6:
+            rel = ((outs["fused"][1][n] - r).norm() / r.norm()).item()
+            if rel > worst:
+                worst, worst_name = rel, n
+    result["worst_grad_rel"], result["worst_grad_name"] = worst, worst_name
+    fused.close()
+    del model, outs
+    # ---- trainer: fused transports, eager steps against the captured-graph replay of the same steps
+    batch = {"latents": torch.randn(1, F, 16, H, W, generator=g).to(torch.bfloat16).pin_memory(),
+             "text": torch.randn(1, 64, 128, generator=g).to(torch.bfloat16).pin_memory()}
+    runs = {}
+    for mode in ("eager", "graph"):
+        sp = FusedUlysses(None, max_tokens=tokens, dim=cfg.dim, num_heads=heads, max_frame_tokens=64)
+        model = WanDiT(cfg, device="cuda", dtype=torch.bfloat16, seed=3, shard_pad=world)
+        with torch.no_grad():
+            model.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator(device="cuda").manual_seed(1))
+        heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()) + (1 << 16), None)
+        opts = Stage0p5Options(lr=1e-3, seed=0, zero=True, zero_transport="fused", cuda_graph=mode == "graph",
+                               graph_warmup_steps=1, max_grad_norm=1.0)
+        tr = WanStage0p5Trainer(cfg, "cuda", opts, sp=sp, model=model, heap=heap)
+        ops.reset_counters()
+        losses = []
+        for _ in range(5):
+            losses.append(float(tr.train_step(batch).item()))
+        torch.cuda.synchronize()
+        ops.check_status()
+        runs[mode] = (losses, model.get_parameter("blocks.1.ffn.0.weight").detach().float().cpu().clone(),
+                      float(tr.last_grad_norm.item()), ops.total_launches())
+        dist.barrier()
+        sp.close()
+        heap.close()
+        del tr, model
+    result["losses_eager"], result["losses_graph"] = runs["eager"][0], runs["graph"][0]
+    result["param_diff"] = float((runs["eager"][1] - runs["graph"][1]).abs().max())
+    result["norms"] = (runs["eager"][2], runs["graph"][2])
+    result["launches"] = (runs["eager"][3], runs["graph"][3])
+    torch.save(result, f"{out_path}.{rank}")
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_exchanges_uneven_frames_and_graph_replay(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
+    import torch.multiprocessing as mp
+
+    out = str(tmp_path / "wide")
+    mp.spawn(_wide_worker, args=(world, 29560 + world, out), nprocs=world, join=True)
+    for rank in range(world):
+        r = torch.load(f"{out}.{rank}", weights_only=True)
+        assert r["forward_identical"], r
+        assert r["worst_grad_rel"] < 1e-2, r
+        le, lg = r["losses_eager"], r["losses_graph"]
+        assert all(abs(a - b) <= 1e-3 * max(abs(a), 1.0) for a, b in zip(le, lg)), r
+        assert le[-1] < le[0] and r["param_diff"] < 1e-2, r
+        assert r["launches"][0] == r["launches"][1] > 0, r

@@ -256,3 +256,40 @@ def test_train_section_maps_to_activation_and_sharding_options():
         opts({"fsdp": {"activation_checkpointing": "sometimes"}}, 1)
     with pytest.raises(ConfigurationError):
         opts({"zero": {"transport": "smoke-signals"}}, 2)
+
+
+def test_device_wait_failure_is_raised_by_every_rank_with_one_message():
+    """A faked status word: rank 1's bounded wait gave up (code 5); both ranks must raise the same text, and a clean
+    exchange raises nothing."""
+    from solarwm_b200.errors import BackendContractError
+    from solarwm_b200.runtime.distributed import raise_if_device_wait_failed
+
+    class FakeDist:
+        def __init__(self, rank, records):
+            self.rank, self.records = rank, records
+
+        def is_initialized(self):
+            return True
+
+        def get_rank(self):
+            return self.rank
+
+        def get_world_size(self):
+            return 2
+
+        def all_gather_object(self, out, mine):
+            self.records[self.rank] = mine
+            out[:] = [self.records[0], self.records[1]]
+
+    codes = {0: 0, 1: 5}
+    messages = []
+    for rank in (0, 1):
+        records = {r: (r, "" if codes[r] == 0 else f"a device-side bounded wait gave up (status code {codes[r]})")
+                   for r in (0, 1)}
+        with pytest.raises(BackendContractError) as err:
+            raise_if_device_wait_failed(codes[rank], dist=FakeDist(rank, records))
+        messages.append(str(err.value))
+    assert messages[0] == messages[1] and "rank 1" in messages[0] and "status code 5" in messages[0]
+    clean = {0: (0, ""), 1: (1, "")}
+    raise_if_device_wait_failed(0, dist=FakeDist(0, clean))
+    raise_if_device_wait_failed(0, dist=None)
