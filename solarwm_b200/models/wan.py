@@ -327,8 +327,9 @@ class WanBlock(nn.Module):
         kc = F_.rmsnorm_rope(kvc[:, :D], self._p("cross_attn.norm_k.weight").float(), None, eps=cfg.eps)
         vc = kvc[:, D:]
         T = context.shape[0] // B
-        oc = ops.attention(qc.reshape(B, Ll, H, hd), kc.reshape(B, T, H, hd), vc.reshape(B, T, H, hd),
-                           memo=None if memo is None else (memo, "cross"))
+        with span("cross_attention"):
+            oc = ops.attention(qc.reshape(B, Ll, H, hd), kc.reshape(B, T, H, hd), vc.reshape(B, T, H, hd),
+                               memo=None if memo is None else (memo, "cross"))
         yc = self._linear(oc.reshape(B * Ll, D), "cross_attn.o.weight", "cross_attn.o.bias")
         x = F_.gated_residual(x, yc, None)
 
@@ -337,7 +338,8 @@ class WanBlock(nn.Module):
             hm = F_.norm_modulate(a, s3, s4, eps=cfg.eps, **nk, **gk)
             return F_.gelu_linear(self._linear(hm, "ffn.0.weight", "ffn.0.bias"), self._p("ffn.2.weight"), self._p("ffn.2.bias"))
 
-        y = F_.recompute_segment(ffn, self._p("ffn.2.weight"), x, mod[:, 3], mod[:, 4]) if lean else ffn(x, mod[:, 3], mod[:, 4])
+        with span("ffn.fwd"):
+            y = F_.recompute_segment(ffn, self._p("ffn.2.weight"), x, mod[:, 3], mod[:, 4]) if lean else ffn(x, mod[:, 3], mod[:, 4])
         x = F_.gated_residual(x, y, mod[:, 5], **gk)
         return x
 

@@ -40,8 +40,9 @@ import torch.distributed as dist
 from ..ops import _lib, functional as F_
 from ..ops._lib import c_float, c_int, c_ll, check, count, ptr, stream_handle
 from ..ops.functional import status_word
+from ..utils.trace import span
 from .symm import SymmetricHeap
-from .ulysses import UlyssesCollective, frame_split
+from .ulysses import UlyssesCollective
 
 
 class _GatherSeqFused(torch.autograd.Function):
@@ -268,12 +269,14 @@ class FusedSelfAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, xm, w, b, nq_w, nk_w, rope, w_o, b_o, eps, scale, sp, parity, memo):
         grads_on = any(ctx.needs_input_grad)
-        qkv, rstd_q, rstd_k, recv = sp.qkv_exchange(xm, w, b, nq_w, nk_w, rope, eps, parity)
+        with span("sa.fwd.qkv_exchange"):
+            qkv, rstd_q, rstd_k, recv = sp.qkv_exchange(xm, w, b, nq_w, nk_w, rope, eps, parity)
         cached = None if memo is None else memo[0].pop(memo[1], None)
         if cached is not None:                      # recompute under selective checkpointing: attention is carried
             o, lse, tokens = cached
         else:
-            o, lse, view = sp.attention_exchange(recv, scale, parity)
+            with span("sa.fwd.attention_exchange"):
+                o, lse, view = sp.attention_exchange(recv, scale, parity)
             # the receive buffers are reused two layers later: what backward needs is copied out of them
             storing = memo is not None and memo[0].get("__store__", False)
             tokens = view.clone() if (grads_on or storing) else view
@@ -296,15 +299,17 @@ class FusedSelfAttention(torch.autograd.Function):
         lib = _lib.load()
         dy = F_._rowmajor(dy)
         # 4': dO leaves through the dgrad GEMM's epilogue; the weight / bias gradients run while it lands
-        slot_do = sp.dgrad_exchange(dy, w_o, parity)
-        F_.gemm(dy, tokens, F_.TN, out=w_o.main_grad, accumulate=F_._grad_is_live(w_o))
-        F_._mark_grad_live(w_o)
-        if b_o is not None:
-            F_.accumulate_main_grad(b_o, F_.colsum(dy))
-        sp.heap.wait(slot_do, sp.size)
+        with span("sa.bwd.dgrad_exchange"):
+            slot_do = sp.dgrad_exchange(dy, w_o, parity)
+            F_.gemm(dy, tokens, F_.TN, out=w_o.main_grad, accumulate=F_._grad_is_live(w_o))
+            F_._mark_grad_live(w_o)
+            if b_o is not None:
+                F_.accumulate_main_grad(b_o, F_.colsum(dy))
+            sp.heap.wait(slot_do, sp.size)
         do = sp.dobuf[parity][:S]
         # 3': attention backward, gradients scattered to the token owners
-        g = sp.attention_bwd_exchange(recv, o, lse, do, scale, parity)          # [Sl, 3D]: dq | dk | dv, all heads
+        with span("sa.bwd.attention_exchange"):
+            g = sp.attention_bwd_exchange(recv, o, lse, do, scale, parity)      # [Sl, 3D]: dq | dk | dv, all heads
         # 2': norm + RoPE backward of the q and k blocks in place (the kernel reads a row completely before it writes)
         dws = []
         for i, (nw, rstd) in enumerate(((nq_w, rstd_q), (nk_w, rstd_k))):

@@ -22,6 +22,7 @@ import torch.distributed as dist
 from ..ops import _lib
 from ..ops._lib import check, ptr, stream_handle
 from ..ops.functional import status_word
+from ..utils.trace import span
 
 FLAG_BYTES = 4096          # 1024 flag / counter words at the start of every heap
 
@@ -103,6 +104,10 @@ class SymmetricHeap:
         round's total have reached this rank's flag word.  On a timeout the kernel sets the status word and
         returns; ``ops.read_status`` / ``ops.check_status`` report it."""
         add = self.world if signals is None else int(signals)
+        with span("comm_wait"):
+            self._wait_launch(slot, add, limit_seconds)
+
+    def _wait_launch(self, slot: int, add: int, limit_seconds: float) -> None:
         check(self.lib.solar_comm_wait_round(ctypes.c_void_p(self.local_ptr + 4 * slot), self.epoch_ptr(slot),
                                              ctypes.c_uint(add), ptr(status_word(self.device)),
                                              ctypes.c_double(limit_seconds), stream_handle()),

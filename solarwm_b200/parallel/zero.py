@@ -40,6 +40,7 @@ from ..engine.optim import FlatAdamW
 from ..ops import _lib
 from ..ops._lib import check, ptr, stream_handle
 from ..ops.functional import status_word
+from ..utils.trace import span
 
 
 class ZeroAdamW(FlatAdamW):
@@ -168,11 +169,12 @@ class ZeroAdamW(FlatAdamW):
                 late = [n for n, p in self.units[i].params.items() if p.grad is not None]
                 if late:
                     raise RuntimeError(f"gradients arrived after unit {i} was announced ready: {late[:3]}")
-            for i in range(len(self.units)):
-                self.unit_ready(i)
-            joined = torch.cuda.Event()
-            joined.record(self._comm_stream)
-            torch.cuda.current_stream().wait_event(joined)
+            with span("zero.reduce_tail"):              # what backward did not hide
+                for i in range(len(self.units)):
+                    self.unit_ready(i)
+                joined = torch.cuda.Event()
+                joined.record(self._comm_stream)
+                torch.cuda.current_stream().wait_event(joined)
             self._reduced_units.clear()
             return self._norm_sq
         self._norm_sq.zero_()
@@ -244,6 +246,10 @@ class ZeroAdamW(FlatAdamW):
             if self.world > 1:
                 self.all_gather_params()
             return
+        with span("zero.adamw_push"):
+            self._fused_update()
+
+    def _fused_update(self) -> None:
         if not self._host_prepared:
             self.begin_step_host()
         self._dyn.copy_(self._dyn_host, non_blocking=True)
