@@ -7,6 +7,7 @@
     solar data inspect --index FILE
     solar data plan --config FILE [--epoch N] [--limit N]
     solar data warm-cache --config FILE
+    solar data materialize-wan153f --train-index F --test-index F --train-window-index F --test-window-index F --output F
     solar environment probe
     solar publish-validation --source DIR --destination URI
 
@@ -63,6 +64,9 @@ def build_parser() -> argparse.ArgumentParser:
     pl.add_argument("--limit", type=int, default=16)
     w = data.add_parser("warm-cache")
     _add_config_args(w)
+    mw = data.add_parser("materialize-wan153f", help="join raw Wan 153-frame sources to the released fixed-window indexes")
+    for flag in ("--train-index", "--test-index", "--train-window-index", "--test-window-index", "--output"):
+        mw.add_argument(flag, required=True, type=Path)
     env = sub.add_parser("environment").add_subparsers(dest="environment_command", required=True)
     env.add_parser("probe")
     pub = sub.add_parser("publish-validation")
@@ -137,6 +141,13 @@ def data_command(args) -> int:
     if args.data_command == "inspect":
         inv = index_mod.inventory(args.index)
         print(json.dumps(inv.__dict__, sort_keys=True))
+        return 0
+    if args.data_command == "materialize-wan153f":
+        from .backends.wan22.windows import write_window_index
+
+        summary = write_window_index(args.train_index, args.test_index, args.train_window_index,
+                                     args.test_window_index, args.output)
+        print(json.dumps(summary.as_dict(), sort_keys=True))
         return 0
     resolved = load_config(args.config, args.overrides)
     data = resolved.values["data"]
