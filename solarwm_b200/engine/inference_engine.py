@@ -125,97 +125,117 @@ def _create(path: Path, data: bytes) -> None:
         raise BackendContractError(f"inference output file {path.name}: {exc}") from exc
 
 
+def _publish_artifact(dest: Path, name: str, value: Union[bytes, GeneratedFile]):
+    """Put one artifact at ``dest`` (bytes are written create-only, files are hard-linked); returns (size, digest)."""
+    if isinstance(value, GeneratedFile):
+        size, digest = _digest_file(value.path)
+        try:
+            link_file_create_only(value.path, dest)
+        except OSError as exc:
+            raise BackendContractError(f"inference generated file {name}: {exc}") from exc
+        return size, digest
+    _create(dest, value)
+    return len(value), hashlib.blake2s(value).hexdigest()
+
+
+class _Together:
+    """Runs the phases of a publication so that every rank learns of any rank's failure before the next phase: the
+    phase body runs (or is skipped on ranks that have nothing to do in it), its error text -- or None -- goes through
+    the ``exchange`` callable, which raises on every rank when any rank failed, and a local failure is raised here."""
+
+    def __init__(self, exchange: Optional[Callable[[Optional[str], str], None]]):
+        self.exchange = exchange or (lambda err, phase: None)
+
+    def phase(self, label: str, body: Callable[[], Any], *, active: bool = True):
+        result, error = None, None
+        if active:
+            try:
+                result = body()
+            except Exception as exc:  # noqa: BLE001 - only the text crosses ranks
+                error = f"{type(exc).__name__}: {exc}"
+        self.exchange(error, label)
+        if error is not None:
+            raise BackendContractError(f"inference {label} failed: {error}")
+        return result
+
+
 class InferenceEngine:
     def __init__(self, adapter: InferenceAdapter):
         self.adapter = adapter
 
+    # -- one case -------------------------------------------------------------------------------------------------
     def _emit_case(self, staging: Path, case: InferenceCase, weights_id: str) -> dict:
-        sample = None
+        sample = self.adapter.generate(case, weights_id=weights_id)
         try:
-            sample = self.adapter.generate(case, weights_id=weights_id)
             slot = f"slot-{case.slot:06d}"
             folder = staging / slot
             folder.mkdir()
-            records = []
-            for name, value in sorted(sample.artifacts.items()):
-                dest = folder / name
-                if isinstance(value, GeneratedFile):
-                    size, digest = _digest_file(value.path)
-                    try:
-                        link_file_create_only(value.path, dest)
-                    except OSError as exc:
-                        raise BackendContractError(f"inference generated file {name}: {exc}") from exc
-                else:
-                    _create(dest, value)
-                    size, digest = len(value), hashlib.blake2s(value).hexdigest()
-                records.append({"path": f"{slot}/{name}", "bytes": size, "digest": digest})
+            listing = []
+            for name in sorted(sample.artifacts):
+                size, digest = _publish_artifact(folder / name, name, sample.artifacts[name])
+                listing.append({"path": f"{slot}/{name}", "bytes": size, "digest": digest})
             manifest = {"schema": SAMPLE_SCHEMA, "family": self.adapter.family, "weights_id": weights_id,
                         "case": asdict(case), "shape": list(sample.shape), "dtype": sample.dtype,
-                        "metrics": dict(sample.metrics), "provenance": dict(sample.provenance), "artifacts": records}
+                        "metrics": dict(sample.metrics), "provenance": dict(sample.provenance), "artifacts": listing}
             _create(folder / "manifest.json", canonical_json(manifest))
             return manifest
         finally:
-            if sample is not None:
-                for value in sample.artifacts.values():
-                    if isinstance(value, GeneratedFile) and value.delete_after_publish:
-                        value.path.unlink(missing_ok=True)
+            for value in sample.artifacts.values():            # private names of linked files go away either way
+                if isinstance(value, GeneratedFile) and value.delete_after_publish:
+                    value.path.unlink(missing_ok=True)
 
-    def run(self, cases: Sequence[InferenceCase], *, weights_id: str, output_dir,
-            collective_error: Optional[Callable[[Optional[str], str], None]] = None,
-            collective_case_waves: Optional[int] = None) -> InferenceSummary:
+    # -- the plan -------------------------------------------------------------------------------------------------
+    @staticmethod
+    def _check_plan(cases: Sequence[InferenceCase], weights_id: str, collective_case_waves: Optional[int]) -> int:
         if not weights_id:
             raise BackendContractError("inference requires a stable weights_id")
         if not cases and collective_case_waves is None:
             raise BackendContractError("inference requires cases")
-        slots = [c.slot for c in cases]
-        if len(set(slots)) != len(slots):
+        if len({c.slot for c in cases}) != len(cases):
             raise BackendContractError("inference case slots are duplicated")
         waves = len(cases) if collective_case_waves is None else int(collective_case_waves)
         if waves < 1:
             raise BackendContractError("inference collective case waves must be positive")
         if waves < len(cases):
             raise BackendContractError("inference collective case waves are shorter than local cases")
-        exchange = collective_error or (lambda err, phase: None)
+        return waves
+
+    @staticmethod
+    def _open_staging(target: Path) -> Path:
+        if target.exists():
+            raise BackendContractError(f"inference output already exists: {target}")
+        target.parent.mkdir(parents=True, exist_ok=True)
+        staging = target.with_name(f".{target.name}.{uuid.uuid4().hex}.partial")
+        staging.mkdir()
+        return staging
+
+    def _seal(self, staging: Path, target: Path, manifests: Sequence[dict], weights_id: str) -> str:
+        ordered = b"".join(canonical_json(m) for m in manifests)
+        digest = hashlib.blake2s(ordered).hexdigest()
+        _create(staging / "ordered-manifest.jsonl", ordered)
+        _create(staging / "COMPLETE.json", canonical_json({
+            "schema": COMPLETE_SCHEMA, "family": self.adapter.family, "weights_id": weights_id,
+            "cases": len(manifests), "ordered_manifest_digest": digest}))
+        publish_directory_no_replace(staging, target)
+        return digest
+
+    def run(self, cases: Sequence[InferenceCase], *, weights_id: str, output_dir,
+            collective_error: Optional[Callable[[Optional[str], str], None]] = None,
+            collective_case_waves: Optional[int] = None) -> InferenceSummary:
+        """Generate ``cases`` in order and publish them as one directory.  With ``collective_error`` every rank takes
+        part in ``collective_case_waves`` exchanges (ranks with fewer cases idle through the extra waves)."""
+        waves = self._check_plan(cases, weights_id, collective_case_waves)
+        together = _Together(collective_error)
         target = Path(output_dir).resolve()
-        staging, err = None, None
-        try:
-            if target.exists():
-                raise BackendContractError(f"inference output already exists: {target}")
-            target.parent.mkdir(parents=True, exist_ok=True)
-            staging = target.with_name(f".{target.name}.{uuid.uuid4().hex}.partial")
-            staging.mkdir()
-        except Exception as exc:  # noqa: BLE001
-            err = f"{type(exc).__name__}: {exc}"
-        exchange(err, "output setup")
-        if err is not None or staging is None:
-            raise BackendContractError(f"inference output setup failed: {err}")
+        staging = together.phase("output setup", lambda: self._open_staging(target))
         manifests = []
         for wave in range(waves):
-            err, manifest = None, None
-            if wave < len(cases):
-                try:
-                    manifest = self._emit_case(staging, cases[wave], weights_id)
-                except Exception as exc:  # noqa: BLE001
-                    err = f"{type(exc).__name__}: {exc}"
-            exchange(err, f"case wave {wave}")
-            if err is not None:
-                raise BackendContractError(f"inference case wave {wave} failed: {err}")
-            if wave < len(cases):
+            mine = wave < len(cases)
+            manifest = together.phase(f"case wave {wave}", lambda: self._emit_case(staging, cases[wave], weights_id),
+                                      active=mine)
+            if mine:
                 manifests.append(manifest)
-        err, digest = None, ""
-        try:
-            ordered = b"".join(canonical_json(m) for m in manifests)
-            digest = hashlib.blake2s(ordered).hexdigest()
-            _create(staging / "ordered-manifest.jsonl", ordered)
-            _create(staging / "COMPLETE.json", canonical_json({
-                "schema": COMPLETE_SCHEMA, "family": self.adapter.family, "weights_id": weights_id,
-                "cases": len(cases), "ordered_manifest_digest": digest}))
-            publish_directory_no_replace(staging, target)
-        except Exception as exc:  # noqa: BLE001
-            err = f"{type(exc).__name__}: {exc}"
-        exchange(err, "partition commit")
-        if err is not None:
-            raise BackendContractError(f"inference partition commit failed: {err}")
+        digest = together.phase("partition commit", lambda: self._seal(staging, target, manifests, weights_id))
         return InferenceSummary(target, weights_id, len(cases), digest)
 
 

@@ -142,10 +142,41 @@ def mean_losses(results: Sequence[MicrobatchResult]) -> dict:
     return {n: sum(float(r.losses[n]) for r in results) / len(results) for n in sorted(names)}
 
 
+@dataclass
+class StepRecord:
+    """What one optimizer step produced, filled in phase by phase; ``event`` is its JSONL form."""
+
+    step: int
+    grad_accum: int
+    microbatches: list
+    gradient_norm: float = float("nan")
+    phase_ms: Mapping[str, float] = None
+
+    def event(self) -> dict:
+        out = {"schema": STEP_SCHEMA, "event": "optimizer_step", "step": self.step, "grad_accum": self.grad_accum,
+               "gradient_norm": self.gradient_norm, "losses": mean_losses(self.microbatches),
+               "microbatches": [{"identity": asdict(r.identity), "losses": dict(r.losses)} for r in self.microbatches]}
+        if self.phase_ms is not None:
+            out["phase_ms"] = dict(self.phase_ms)
+        return out
+
+
 class TrainingEngine:
+    """Drives a ``TrainingRuntime`` through optimizer steps.  A step is four phases run in a fixed order --
+    ``_accumulate`` (microbatches + peer identity), ``_update`` (gradient preparation, finite check, optimizer),
+    ``_advance`` (schedule, step counter, EMA) and ``_boundaries`` (checkpoint / validation when the policy says so) --
+    and one JSONL record.  The ORDER of the runtime hooks inside the phases is the protocol every backend relies on;
+    a failure in ``_accumulate`` or a non-finite norm in ``_update`` clears the gradients and leaves optimizer, EMA,
+    counter and checkpoints as they were."""
+
     def __init__(self, runtime: TrainingRuntime, policy: StepPolicy, *, event_sink: Callable[[Mapping], None] = None):
         self.runtime, self.policy = runtime, policy
         self.event_sink = event_sink or (lambda event: None)
+        # (policy test, runtime hook, event builder) for everything that can follow a step
+        self._boundary_table = (
+            (policy.should_save, self._save, lambda step, ident: {"event": "checkpoint", "checkpoint_id": ident}),
+            (policy.should_validate, runtime.validate, lambda step, report: {"event": "validation", "report": dict(report)}),
+        )
 
     def run(self) -> int:
         with paused_cycle_collection():
@@ -154,56 +185,69 @@ class TrainingEngine:
         return self.runtime.global_step
 
     def step(self) -> None:
+        timer = None
         if os.environ.get("SOLAR_PHASE_TIMES", "0") == "1":
             from ..utils.trace import PhaseTimer
 
             timer = PhaseTimer()
-            with timer.installed():
-                self._step(timer)
+        record = StepRecord(self.runtime.global_step + 1, self.policy.grad_accum, [])
+        if timer is None:
+            self._train(record)
         else:
-            self._step(None)
+            with timer.installed():
+                self._train(record)
+            record.phase_ms = {k: v["total_ms"] for k, v in timer.summary().items() if not k.startswith("block.")}
+        self.event_sink(record.event())
+        self._boundaries(record.step)
 
-    def _step(self, timer) -> None:
-        rt, policy = self.runtime, self.policy
-        target = rt.global_step + 1
-        rt.zero_grad()
-        done = []
+    # -- phases ---------------------------------------------------------------------------------------------------
+    def _train(self, record: StepRecord) -> None:
+        self.runtime.zero_grad()
+        self._accumulate(record)
+        self._update(record)
+        self._advance(record)
+
+    def _accumulate(self, record: StepRecord) -> None:
+        rt = self.runtime
         try:
-            for micro in range(policy.grad_accum):
-                result = rt.train_microbatch(micro, policy.grad_accum)
-                rt.assert_sp_peer_identity(result.identity)
-                done.append(result)
-        except Exception:
+            for index in range(record.grad_accum):
+                outcome = rt.train_microbatch(index, record.grad_accum)
+                rt.assert_sp_peer_identity(outcome.identity)
+                record.microbatches.append(outcome)
+        except BaseException:
             rt.zero_grad()
             raise
+
+    def _update(self, record: StepRecord) -> None:
         from ..utils.trace import span
 
+        rt = self.runtime
         with span("optimizer"):
             status = rt.prepare_optimizer_step()
-            if not status.finite or not math.isfinite(status.norm):
+            record.gradient_norm = status.norm
+            if not (status.finite and math.isfinite(status.norm)):
                 rt.zero_grad()
-                raise BackendContractError(f"non-finite gradients before optimizer step {target}: {status.norm}")
+                raise BackendContractError(f"non-finite gradients before optimizer step {record.step}: {status.norm}")
             rt.optimizer_step()
+
+    def _advance(self, record: StepRecord) -> None:
+        rt = self.runtime
         rt.scheduler_step()
-        rt.set_global_step(target)
-        rt.ema_update(target)
+        rt.set_global_step(record.step)
+        rt.ema_update(record.step)
         rt.zero_grad()
-        self.event_sink({
-            "schema": STEP_SCHEMA, "event": "optimizer_step", "step": target, "grad_accum": policy.grad_accum,
-            "gradient_norm": status.norm, "losses": mean_losses(done),
-            **({} if timer is None else {"phase_ms": {k: v["total_ms"] for k, v in timer.summary().items()
-                                                      if not k.startswith("block.")}}),
-            "microbatches": [{"identity": asdict(r.identity), "losses": dict(r.losses)} for r in done]})
-        boundary = False
-        if policy.should_save(target):
-            ident = rt.save_checkpoint(target)
-            if not ident:
-                raise BackendContractError("checkpoint hook returned an empty identity")
-            self.event_sink({"schema": EVENT_SCHEMA, "event": "checkpoint", "step": target, "checkpoint_id": ident})
-            boundary = True
-        if policy.should_validate(target):
-            report = rt.validate(target)
-            self.event_sink({"schema": EVENT_SCHEMA, "event": "validation", "step": target, "report": dict(report)})
-            boundary = True
-        if boundary:
-            gc.collect()
+
+    def _save(self, step: int) -> str:
+        ident = self.runtime.save_checkpoint(step)
+        if not ident:
+            raise BackendContractError("checkpoint hook returned an empty identity")
+        return ident
+
+    def _boundaries(self, step: int) -> None:
+        crossed = False
+        for due, hook, describe in self._boundary_table:
+            if due(step):
+                self.event_sink({"schema": EVENT_SCHEMA, "step": step, **describe(step, hook(step))})
+                crossed = True
+        if crossed:
+            gc.collect()             # cycle collection is paused inside the loop; boundaries are where it runs
