@@ -63,6 +63,10 @@ def parse_args():
                     help="after the timed region, run one more step under the phase timer and add the forward / "
                          "backward / optimizer split (CUDA events) to the JSON line")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
+    ap.add_argument("--fsdp", default="params", choices=["params", "optimizer"],
+                    help="N > 1 with --zero fused: 'params' also shards every block's bf16 parameters and fp32 gradient "
+                         "buffers (just-in-time gathers over NVLink, reduce-scatter under backward); 'optimizer' shards "
+                         "the optimizer state only")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="capture the whole training step in one CUDA graph and replay it (auto: on with the fused "
                          "transports at N > 1, where the step contains no library collective)")
@@ -244,7 +248,8 @@ def run_ours(args):
                                    and args.zero == "fused")
     opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
                            keep_blocks=keep, lean_kept=lean, max_grad_norm=1.0, seed=0, zero=zero,
-                           zero_transport=args.zero, cuda_graph=graph)
+                           zero_transport=args.zero, cuda_graph=graph,
+                           shard_params=zero and args.zero == "fused" and args.fsdp == "params")
     model = heap = None
     if zero:
         from solarwm_b200.models.wan import WanDiT
@@ -253,7 +258,10 @@ def run_ours(args):
         if args.zero == "fused":
             from solarwm_b200.parallel.symm import SymmetricHeap
 
-            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()) + (1 << 16), None)
+            from solarwm_b200.parallel.zero import fused_heap_bytes
+
+            heap = SymmetricHeap(fused_heap_bytes(model.units(), world,
+                                                  [b.unit for b in model.blocks] if args.fsdp == "params" else ()), None)
     trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp, model=model, heap=heap)
     with torch.no_grad():  # a zero head would zero every upstream gradient; keep the step representative
         trainer.model.get_parameter("head.head.weight").normal_(0, 0.02)
@@ -315,6 +323,7 @@ def run_ours(args):
                        "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
                        "optimizer_sharding": (f"zero-{args.zero}" if zero else "none"),
                        "cuda_graph_step": bool(graph),
+                       "parameter_sharding": ("blocks sharded 1/N, gathered just in time" if opts.shard_params else "none"),
                        "latent": [1, cfg.in_dim, args.frames, args.height, args.width],
                        "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt, "keep_blocks": keep,
                        "lean_resident_blocks": lean,

@@ -29,10 +29,11 @@ def build_contract(config: Mapping[str, Any], route, sp_size: int) -> Checkpoint
 
 def save_checkpoint(root, step: int, *, model, scheduler, contract: CheckpointContract, config,
                     ema_state: Optional[Mapping[str, Any]], ema_num_updates: int, rank_states, is_main: bool,
-                    barrier=None, optimizer=None, optimizer_state=None) -> str:
+                    barrier=None, optimizer=None, optimizer_state=None, weights=None) -> str:
     """``optimizer_state``: the un-sharded ``optimizer.state_dict()`` gathered by the caller on every rank (a sharded
     optimizer's ``state_dict`` is a collective, so it cannot be called from the main rank alone); ``optimizer`` is
-    accepted for single-rank callers and read here."""
+    accepted for single-rank callers and read here.  ``weights``: the full name -> tensor mapping when the model's
+    parameters are sharded (``ShardedParameters.materialize``); default ``model.state_dict()``."""
     if optimizer_state is None and is_main:
         if optimizer is None:
             raise CheckpointError("save_checkpoint needs optimizer_state (or an unsharded optimizer)")
@@ -44,7 +45,7 @@ def save_checkpoint(root, step: int, *, model, scheduler, contract: CheckpointCo
     if is_main:
         with CheckpointTransaction(target) as tx:
             payload = {
-                "generator": {k: v.detach().cpu() for k, v in model.state_dict().items()},
+                "generator": {k: v.detach().cpu() for k, v in (weights if weights is not None else model.state_dict()).items()},
                 "generator_ema": None if ema_state is None else {k: v.detach().cpu() for k, v in ema_state.items()},
                 "optimizer": optimizer_state,
                 "scheduler": scheduler.state_dict(),
@@ -71,9 +72,16 @@ def load_checkpoint(path, *, model, optimizer=None, scheduler=None, mode: str = 
         assert_resume_compatible(expected, verified.contract)
     payload = torch.load(Path(path) / "model.pt", map_location=map_location, weights_only=True)
     weights = payload["generator_ema"] if (weight_source == "ema" and payload.get("generator_ema")) else payload["generator"]
-    missing = model.load_state_dict(weights, strict=True)
-    if missing.missing_keys or missing.unexpected_keys:
-        raise CheckpointError(f"checkpoint weights do not match the model: {missing}")
+    provider = getattr(model, "param_provider", None)
+    if provider is not None:
+        try:
+            provider.load_state(model, weights)               # sharded parameters: every rank keeps its own slice
+        except (KeyError, ValueError) as exc:
+            raise CheckpointError(str(exc)) from exc
+    else:
+        missing = model.load_state_dict(weights, strict=True)
+        if missing.missing_keys or missing.unexpected_keys:
+            raise CheckpointError(f"checkpoint weights do not match the model: {missing}")
     if mode == "full_resume":
         if optimizer is not None:
             optimizer.load_state_dict(payload["optimizer"])

@@ -357,6 +357,10 @@ class WanStage0p5Runtime:
             from ...engine.ema import FlatEMAView
 
             ema_state = FlatEMAView(self.trainer.model, self.trainer.optimizer, gathered=opt_state).state_dict()
+        weights = None
+        provider = getattr(self.trainer.model, "param_provider", None)
+        if provider is not None and topo.is_main:
+            weights = provider.materialize(self.trainer.model)       # sharded blocks are gathered one by one
         if not topo.is_main:
             opt_state = ema_state = None
 
@@ -365,7 +369,7 @@ class WanStage0p5Runtime:
                                                    label="checkpoint commit")
 
         ident = ckpt.save_checkpoint(output_root(self.config), step, model=self.trainer.model,
-                                     optimizer_state=opt_state, scheduler=self.scheduler,
+                                     optimizer_state=opt_state, weights=weights, scheduler=self.scheduler,
                                      contract=self.contract, config=self.config, ema_state=ema_state,
                                      ema_num_updates=self.trainer.optimizer.step_count, rank_states=states,
                                      is_main=topo.is_main, barrier=agree)

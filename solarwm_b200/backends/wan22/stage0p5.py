@@ -42,6 +42,8 @@ class Stage0p5Options:
     lean_kept: bool = False          # resident blocks rebuild their norm outputs / FFN hidden in backward
     zero: bool = False                 # shard optimizer state + gradient reduction over all ranks (own FSDP)
     zero_transport: str = "collective"  # or "fused" (NVLink peer reduce / push; needs a symmetric heap)
+    shard_params: bool = False         # fused sharded optimizer only: keep 1 / world of every block's parameters and
+                                       # gather each block just in time (parallel/shard_params.py)
     cuda_graph: bool = False           # capture the whole step (forward, backward, optimizer) once and replay it; needs
                                        # the fused transports (no library collective inside the step) and grad_accum 1
     graph_warmup_steps: int = 2        # eager steps before the capture (lazy initialisation happens there)
@@ -68,7 +70,18 @@ class WanStage0p5Trainer:
 
             # gradients are SUMMED over every rank (SP partial sums and DP replicas alike; the loss carries
             # the 1 / (accum * sp * dp) factor), so the shard group is the whole job
-            self.optimizer = ZeroAdamW(self.model.units(), None, transport=opts.zero_transport, heap=heap, **okw)
+            shards = None
+            if opts.shard_params:
+                if opts.zero_transport != "fused" or heap is None:
+                    raise ValueError("shard_params needs the fused sharded optimizer (zero_transport='fused' and a heap)")
+                if opts.grad_accum != 1:
+                    raise ValueError("shard_params reduces every block's gradients inside backward: grad_accum must be 1")
+                from ...parallel.shard_params import ShardedParameters
+
+                shards = ShardedParameters([b.unit for b in self.model.blocks], heap)
+                self.model.param_provider = shards
+            self.optimizer = ZeroAdamW(self.model.units(), None, transport=opts.zero_transport, heap=heap,
+                                       param_shards=shards, **okw)
         else:
             self.optimizer = FlatAdamW(self.model.units(), **okw)
         if hasattr(self.optimizer, "unit_ready") and opts.grad_accum == 1:
@@ -200,6 +213,8 @@ class WanStage0p5Trainer:
             for k in keys:
                 st["inputs"][k].copy_(batch[k], non_blocking=True)
             torch.cuda.synchronize(self.device)
+            if getattr(self.model, "param_provider", None) is not None:
+                self.model.param_provider.reset_events()
             graph = torch.cuda.CUDAGraph()
             graph.register_generator_state(self.gen)
             if fused_opt:

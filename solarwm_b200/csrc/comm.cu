@@ -100,6 +100,18 @@ __global__ void comm_allsum_kernel(const float* src, int n, PeerTable tables, in
   }
 }
 
+// All-gather by pulling: dst[r * n16 .. (r + 1) * n16) = shard of rank r (16-byte units), read straight from the
+// peers' memory over NVLink.  Used to land a block's sharded parameters in local memory ahead of its first GEMM.
+__global__ void __launch_bounds__(256) comm_gather_kernel(uint4* __restrict__ dst, PeerTable src, long long n16) {
+  const long long total = n16 * src.n;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / n16);
+    const long long k = i - r * n16;
+    dst[i] = static_cast<const uint4*>(src.base[r])[k];
+  }
+}
+
 __global__ void comm_signal_kernel(PeerFlags flags) {
   if (threadIdx.x == 0 && blockIdx.x == 0) signal_all_peers(flags);
 }
@@ -235,6 +247,23 @@ extern "C" int solar_comm_allsum(const float* src, int n, void* const* table_bas
   comm_allsum_kernel<<<1, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       src, n, t, rank, make_flags(flag_ptrs, n_ranks, nullptr), static_cast<const unsigned*>(flag_ptrs[rank]), epoch,
       out, status, ns);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// dst (local) <- concatenation over ranks of the `shard_bytes` at src_bases[r] (each rank's shard, as mapped here).
+extern "C" int solar_comm_gather(void* dst, void* const* src_bases, int n_ranks, long long shard_bytes, int max_ctas,
+                                 void* stream) {
+  if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("comm: peer count out of range%s");
+  if (shard_bytes <= 0 || shard_bytes % 16 != 0) return fail("comm gather: shard size must be a positive multiple of 16%s");
+  PeerTable t;
+  t.n = n_ranks;
+  for (int i = 0; i < kMaxPeers; ++i) t.base[i] = i < n_ranks ? src_bases[i] : nullptr;
+  const long long n16 = shard_bytes / 16;
+  long long grid = (n16 * n_ranks + 255) / 256;
+  const long long cap = max_ctas > 0 ? max_ctas : 4LL * sm_count();
+  if (grid > cap) grid = cap;
+  comm_gather_kernel<<<(unsigned)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(dst), t, n16);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }

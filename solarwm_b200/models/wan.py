@@ -147,6 +147,21 @@ class _UnitReady(torch.autograd.Function):
         return g, None, None
 
 
+class _BlockGate(torch.autograd.Function):
+    """Identity on a block's OUTPUT: its backward runs before any node of the block and asks the parameter provider
+    to make the block's (sharded) weights resident again and to clear its gradient slot for writing."""
+
+    @staticmethod
+    def forward(ctx, x, provider, index):
+        ctx.provider, ctx.index = provider, index
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.provider.acquire(ctx.index, backward=True)
+        return g, None, None
+
+
 class _NoSP:
     size = 1
     rank = 0
@@ -381,6 +396,7 @@ class WanDiT(nn.Module):
         self.lean_kept = False       # kept blocks drop their norm outputs and FFN hidden (rebuilt in backward)
         self._rope_cache: dict = {}
         self.grad_ready_hook = None  # callable(unit): a block's parameter gradients are final (set by the trainer)
+        self.param_provider = None   # parallel.shard_params.ShardedParameters when block weights are sharded
         if seed is not None:
             self.init_weights(seed)
 
@@ -503,8 +519,26 @@ class WanDiT(nn.Module):
             return self._run_block_inner(block, x, e0, rope, ctx, kw, index)
 
     def _run_block_inner(self, block, x, e0, rope, ctx, kw, index):
-        if self.grad_ready_hook is not None and torch.is_grad_enabled() and x.requires_grad:
-            x = _UnitReady.apply(x, self.grad_ready_hook, block.unit)
+        prov = self.param_provider
+        k = None if prov is None else prov.index_of(block.unit)
+        training = torch.is_grad_enabled() and x.requires_grad
+        if self.grad_ready_hook is not None and training:
+            x = _UnitReady.apply(x, self._block_done if k is not None else self.grad_ready_hook, block.unit)
+        if k is not None:
+            prov.acquire(k)                       # the block's weights are gathered (prefetched one block ahead)
+        out = self._run_block_compute(block, x, e0, rope, ctx, kw, index)
+        if k is not None:
+            prov.release(k)
+            if training:
+                out = _BlockGate.apply(out, prov, k)
+        return out
+
+    def _block_done(self, unit) -> None:
+        """Backward of a block with sharded weights is complete: reduce its gradients, then free its slots."""
+        self.grad_ready_hook(unit)
+        self.param_provider.release(self.param_provider.index_of(unit))
+
+    def _run_block_compute(self, block, x, e0, rope, ctx, kw, index):
         exempt = index >= len(self.blocks) - int(self.keep_blocks)
         if self.checkpointing in ("full", "selective") and torch.is_grad_enabled() and not exempt:
             from torch.utils.checkpoint import checkpoint

@@ -43,13 +43,30 @@ from ..ops.functional import status_word
 from ..utils.trace import span
 
 
+def fused_heap_bytes(units, world: int, sharded=(), slots: int = 2) -> int:
+    """Bytes of symmetric heap the fused transport needs for ``units``: replicated units hold their bf16 parameters
+    and fp32 gradients there; ``sharded`` units hold a ``1 / world`` parameter shard each and share ``slots`` fp32
+    gradient buffers of the largest unit's size."""
+    sharded_ids = {id(u) for u in sharded}
+    total = 1 << 16
+    for u in units:
+        total += u.numel_v * 8 + 2048
+        total += (u.numel_m * 2 // world + 512) if id(u) in sharded_ids else u.numel_m * 6
+    if sharded_ids:
+        total += slots * (max(u.numel_m for u in sharded) * 4 + 512)
+    return total
+
+
 class ZeroAdamW(FlatAdamW):
     def __init__(self, units: Iterable, group=None, *, transport: str = "collective", heap=None, replica_group=None,
-                 reduce_ctas: int = 32, **kw):
+                 reduce_ctas: int = 32, param_shards=None, **kw):
         """``group``: the ranks one copy of the optimizer state is sharded over.  ``replica_group`` (hybrid
         sharding): the ranks that hold the SAME shard in other shard groups (e.g. one per node); the reduced
         gradient shard is summed over it before the update, so every replica applies the identical step.
-        ``reduce_ctas``: CTAs of one overlapped reduce launch (a small grid leaves the SMs to backward)."""
+        ``reduce_ctas``: CTAs of one overlapped reduce launch (a small grid leaves the SMs to backward).
+        ``param_shards``: a ``parallel.shard_params.ShardedParameters`` over some of the units (fused transport):
+        those units keep only this rank's parameter shard and share gathered / gradient slots; their update writes
+        the rank's own shard instead of pushing to every peer."""
         self.group = group
         self.replica_group = replica_group
         world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -62,17 +79,35 @@ class ZeroAdamW(FlatAdamW):
         self.heap = heap
         self.reduce_ctas = int(reduce_ctas)
         self._heap_off = {}
+        self.param_shards = param_shards if (transport == "fused" and world > 1) else None
+        self._sharded_units = {}
         if transport == "fused":
             if heap is None:
                 raise ValueError("the fused transport needs a SymmetricHeap")
             for i, u in enumerate(units):
                 u.ensure_grads()
-                flat, off_p = heap.alloc((u.numel_m,), u.flat.dtype)
+                k = None if self.param_shards is None else self.param_shards.index_of(u)
                 flat_v, off_pv = heap.alloc((u.numel_v,), u.flat_v.dtype)
-                grad, off_g = heap.alloc((u.numel_m,), torch.float32)
                 grad_v, off_gv = heap.alloc((u.numel_v,), torch.float32)
-                u.move_(flat, flat_v)
-                u.move_grads_(grad, grad_v)
+                if k is None:
+                    flat, off_p = heap.alloc((u.numel_m,), u.flat.dtype)
+                    grad, off_g = heap.alloc((u.numel_m,), torch.float32)
+                    u.move_(flat, flat_v)
+                    u.move_grads_(grad, grad_v)
+                else:
+                    # sharded unit: the matrices stay where they are until ``attach`` (the master weights are copied
+                    # out of them below); only the small fp32 vectors move into the heap now
+                    self._sharded_units[i] = k
+                    flat_v.copy_(u.flat_v)
+                    u.flat_v = flat_v
+                    for name, prm in u.params.items():
+                        if u.slots[name].is_vector:
+                            prm.data = u.view(name)
+                    grad_v.zero_()
+                    u.grad_v = grad_v
+                    u.ensure_grads()
+                    off_p = self.param_shards.shard_off[k]
+                    off_g = self.param_shards.gbuf_off[self.param_shards.slot_of(k)]
                 self._heap_off[i] = {"m": (off_p, off_g), "v": (off_pv, off_gv)}
             self._flag_unit = [heap.new_flag() for _ in units]
             self._flag_params = heap.new_flag()
@@ -90,6 +125,8 @@ class ZeroAdamW(FlatAdamW):
             self._norm_in = torch.zeros(2, dtype=torch.float32, device=dev)
             self._norm_out = torch.zeros(2, dtype=torch.float32, device=dev)
             self._host_prepared = False
+            if self.param_shards is not None:
+                self.param_shards.attach()
             self._build_table()
 
     # ------------------------------------------------------------------------------------
@@ -99,32 +136,41 @@ class ZeroAdamW(FlatAdamW):
                 yield i, key, buf, g, st[key]
 
     def _build_table(self) -> None:
-        """Device table of every shard (one entry per flat buffer) for the single-launch AdamW + push."""
+        """Device tables of every shard (one entry per flat buffer) for the single-launch AdamW: ``_tables`` is a list
+        of (table, segments, chunks, ranks to write to); replicated buffers are pushed to every rank, sharded matrix
+        buffers are written into this rank's own parameter shard only."""
         lib = self._lib
         lib.solar_zero_chunk_elems.restype = ctypes.c_longlong
         seg_bytes, chunk = int(lib.solar_zero_segment_bytes()), int(lib.solar_zero_chunk_elems())
-        entries = list(self._buffers())
-        host = (ctypes.c_ubyte * (seg_bytes * len(entries)))()
-        chunks = 0
-        for idx, (i, key, buf, g, s) in enumerate(entries):
-            a, b = s["range"]
-            is_bf16 = buf.dtype == torch.bfloat16
-            master = s["master"]
-            if master is None:
-                if is_bf16:
-                    raise ValueError("bf16 buffers need an fp32 master copy")
-                # fp32 vector units: the live shard is its own master; the kernel updates a copy and pushes it
-                master = self.__dict__.setdefault("_vec_master", {}).setdefault((i, key), buf[a:b].clone())
-            check(lib.solar_zero_segment_fill(host, ctypes.c_int(idx), ctypes.c_longlong(self._heap_off[i][key][0]),
-                                              ctypes.c_longlong(a), ctypes.c_longlong(b - a), ctypes.c_longlong(chunks),
-                                              ptr(master), ptr(s["exp_avg"]), ptr(s["exp_avg_sq"]),
-                                              ptr(self._reduced(i, key, b - a, buf.device)),
-                                              ptr(s["ema"]) if s["ema"] is not None else None,
-                                              ctypes.c_int(1 if is_bf16 else 0)), "solar_zero_segment_fill")
-            chunks += (b - a + chunk - 1) // chunk
-        raw = torch.frombuffer(bytearray(host), dtype=torch.uint8).clone()
-        self._table = raw.to(self.units[0].device)
-        self._n_seg, self._n_chunks = len(entries), chunks
+        pushed, own = [], []
+        for entry in self._buffers():
+            i, key = entry[0], entry[1]
+            (own if (key == "m" and i in self._sharded_units) else pushed).append(entry)
+        self._tables = []
+        for entries, to_all in ((pushed, True), (own, False)):
+            if not entries:
+                continue
+            host = (ctypes.c_ubyte * (seg_bytes * len(entries)))()
+            chunks = 0
+            for idx, (i, key, buf, g, s) in enumerate(entries):
+                a, b = s["range"]
+                is_bf16 = buf.dtype == torch.bfloat16
+                master = s["master"]
+                if master is None:
+                    if is_bf16:
+                        raise ValueError("bf16 buffers need an fp32 master copy")
+                    # fp32 vector units: the live shard is its own master; the kernel updates a copy and pushes it
+                    master = self.__dict__.setdefault("_vec_master", {}).setdefault((i, key), buf[a:b].clone())
+                # an own-shard segment addresses the shard buffer from its first element
+                check(lib.solar_zero_segment_fill(host, ctypes.c_int(idx), ctypes.c_longlong(self._heap_off[i][key][0]),
+                                                  ctypes.c_longlong(a if to_all else 0), ctypes.c_longlong(b - a),
+                                                  ctypes.c_longlong(chunks), ptr(master), ptr(s["exp_avg"]),
+                                                  ptr(s["exp_avg_sq"]), ptr(self._reduced(i, key, b - a, buf.device)),
+                                                  ptr(s["ema"]) if s["ema"] is not None else None,
+                                                  ctypes.c_int(1 if is_bf16 else 0)), "solar_zero_segment_fill")
+                chunks += (b - a + chunk - 1) // chunk
+            table = torch.frombuffer(bytearray(host), dtype=torch.uint8).clone().to(self.units[0].device)
+            self._tables.append((table, len(entries), chunks, to_all))
 
     # reduce-scatter ------------------------------------------------------------------------
     def unit_ready(self, unit_or_index) -> None:
@@ -156,6 +202,8 @@ class ZeroAdamW(FlatAdamW):
                                                   ptr(self._norm_sq), ctypes.c_int(self.reduce_ctas), stream_handle()),
                       "solar_zero_reduce")
                 _lib.count("zero_reduce")
+            if i in self._sharded_units:
+                self.param_shards.gradients_read(self._sharded_units[i])     # the shared gradient slot may be reused
 
     def reduce_scatter_grads(self) -> torch.Tensor:
         """Leaves the group-summed gradient in this rank's shard of every ``main_grad`` buffer and
@@ -255,14 +303,20 @@ class ZeroAdamW(FlatAdamW):
         self._dyn.copy_(self._dyn_host, non_blocking=True)
         b1, b2 = self.betas
         h = self.heap
-        heaps = (ctypes.c_void_p * self.world)(*h.ptrs)
-        check(self._lib.solar_zero_adamw_push_multi(
-            ptr(self._table), ctypes.c_int(self._n_seg), ctypes.c_longlong(self._n_chunks), heaps,
-            ctypes.c_int(self.world), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(self.eps),
-            ctypes.c_float(self.weight_decay), ctypes.c_float(0.0 if self.ema_decay is None else self.ema_decay),
-            ptr(self._dyn), ptr(self._scale), ptr(self._skip), ctypes.c_int(0), stream_handle()),
-            "solar_zero_adamw_push_multi")
-        _lib.count("zero_adamw_push")
+        if self.param_shards is not None:
+            self.param_shards.settle()
+        for table, n_seg, n_chunks, to_all in self._tables:
+            targets = list(h.ptrs) if to_all else [h.local_ptr]
+            heaps = (ctypes.c_void_p * len(targets))(*targets)
+            check(self._lib.solar_zero_adamw_push_multi(
+                ptr(table), ctypes.c_int(n_seg), ctypes.c_longlong(n_chunks), heaps,
+                ctypes.c_int(len(targets)), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(self.eps),
+                ctypes.c_float(self.weight_decay), ctypes.c_float(0.0 if self.ema_decay is None else self.ema_decay),
+                ptr(self._dyn), ptr(self._scale), ptr(self._skip), ctypes.c_int(0), stream_handle()),
+                "solar_zero_adamw_push_multi")
+            _lib.count("zero_adamw_push")
+        if self.param_shards is not None:
+            self.param_shards.invalidate()
         h.signal(self._flag_params)                    # every rank's pushes have landed here
         h.wait(self._flag_params)
 
