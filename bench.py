@@ -63,7 +63,7 @@ def parse_args():
                     help="after the timed region, run one more step under the phase timer and add the forward / "
                          "backward / optimizer split (CUDA events) to the JSON line")
     ap.add_argument("--attention", default=None, choices=[None, "native", "library"])
-    ap.add_argument("--fsdp", default="params", choices=["params", "optimizer"],
+    ap.add_argument("--fsdp", default="optimizer", choices=["params", "optimizer"],
                     help="N > 1 with --zero fused: 'params' also shards every block's bf16 parameters and fp32 gradient "
                          "buffers (just-in-time gathers over NVLink, reduce-scatter under backward); 'optimizer' shards "
                          "the optimizer state only")

@@ -16,7 +16,13 @@ class Wan22Backend:
         self.family = family
 
     def validate_config(self, config: Mapping[str, Any]) -> None:
+        """Structural validation always; ``metadata.contract: release`` additionally holds the config to the pinned
+        release recipe of the family (geometry, optimizer, EMA, sharding, initialisation)."""
         validate_wan_config(config, self.family)
+        if str((config.get("metadata") or {}).get("contract", "structural")).lower() == "release":
+            from .contracts import validate_release_recipe
+
+            validate_release_recipe(config, self.family)
 
     def train(self, config: Mapping[str, Any]) -> Mapping[str, Any]:
         route = validate_route(config)
