@@ -5,6 +5,10 @@ sides) and roofline fractions against the measured peaks of the box.
     python -m solarwm_b200.utils.kernel_bench attention --seq 27280 --heads 24 --head-dim 128 [--backward]
     python -m solarwm_b200.utils.kernel_bench rowops --rows 27280 --dim 3072
     python -m solarwm_b200.utils.kernel_bench suite            # the Wan-5B block shapes
+    python -m solarwm_b200.utils.kernel_bench probe --family rows|pointwise|headops|zero|attention|attention_bwd|conv|gemm
+                                                               # one launch of every kernel of a family on a case
+                                                               # larger than L2 and a few hundred MB at most: the
+                                                               # program a counter capture (ncu -k ... -c N) runs
 
 Each line of output is one JSON object: the op, its shape, milliseconds (median of the timed
 iterations), achieved TFLOP/s or GB/s, the fraction of the measured peak, and the same numbers
@@ -174,6 +178,130 @@ def bench_conv(T, H, W, cin, cout, kernel=(3, 3, 3), iters=5):
             "cudnn_ms": round(ms_lib, 4), "speedup_vs_cudnn": round(ms_lib / ms, 3)}
 
 
+def probe(family: str, rows: int = 27280, dim: int = 3072) -> dict:
+    """Launch every kernel of ``family`` once (after one warm-up launch of each) on inputs that exceed the L2 but stay
+    within a few hundred MB, and return {kernel: algorithmic bytes or FLOPs per launch}: the denominators for the
+    HBM-bytes-vs-algorithmic-bytes line of a counter summary."""
+    import math
+
+    from ..ops import functional as F_
+
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=g)          # noqa: E731
+    R, D = rows, dim
+    plan = {}
+
+    def run(name, fn, algorithmic):
+        fn()                                   # warm-up (first-use attributes, allocator)
+        torch.cuda.synchronize()
+        flush_l2()
+        fn()
+        torch.cuda.synchronize()
+        plan[name] = algorithmic
+
+    if family == "rows":
+        x, y = rnd(R, D).bfloat16(), rnd(R, D).bfloat16()
+        G = max(R // 880, 1)
+        rpg = (R + G - 1) // G
+        mod = rnd(G + 1, 6, D)
+        w = torch.ones(D, device=dev)
+        rope = torch.stack([torch.cos(rnd(R, 64)), torch.sin(rnd(R, 64))], -1).contiguous()
+        xr = x.clone().requires_grad_(True)
+        sh, sc, gt = (mod[:, i].clone().requires_grad_(True) for i in range(3))
+        with torch.no_grad():
+            run("norm_modulate_fwd", lambda: ops.norm_modulate(x, mod[:, 0], mod[:, 1], rows_per_group=rpg), {"bytes": 4 * R * D})
+            run("gated_residual", lambda: ops.gated_residual(x, y, mod[:, 2], rows_per_group=rpg), {"bytes": 6 * R * D})
+            run("rmsnorm_rope_fwd", lambda: ops.rmsnorm_rope(x, w, rope), {"bytes": 4 * R * D + 8 * R * 64})
+        out = ops.norm_modulate(xr, sh, sc, rows_per_group=rpg)
+        run("norm_modulate_bwd+colreduce", lambda: torch.autograd.grad(out, (xr, sh, sc), y, retain_graph=True),
+            {"bytes": 6 * R * D + 4 * R * D})
+        out2 = ops.gated_residual(xr, y, gt, rows_per_group=rpg)
+        run("gated_residual_bwd+colreduce", lambda: torch.autograd.grad(out2, (xr, gt), y, retain_graph=True), {"bytes": 8 * R * D})
+        wr = w.clone().requires_grad_(True)
+        out3 = ops.rmsnorm_rope(xr, wr, rope)
+        run("rmsnorm_rope_bwd+dw", lambda: torch.autograd.grad(out3, (xr, wr), y, retain_graph=True), {"bytes": 10 * R * D})
+    elif family == "pointwise":
+        n = R * D
+        x, y = rnd(R, D).bfloat16(), rnd(R, D).bfloat16()
+        xr = x.clone().requires_grad_(True)
+        with torch.no_grad():
+            run("gelu_fwd", lambda: ops.gelu(x), {"bytes": 4 * n})
+        o = ops.gelu(xr)
+        run("gelu_bwd", lambda: torch.autograd.grad(o, xr, y, retain_graph=True), {"bytes": 6 * n})
+        F = 31
+        lat, noise = rnd(F, 48, 44, 80).bfloat16(), rnd(F, 48, 44, 80).bfloat16()
+        sig = torch.rand(F, device=dev)
+        run("flow(add_noise)", lambda: ops.add_noise(lat, noise, sig), {"bytes": 8 * lat.numel()})
+        run("mse_fwd", lambda: ops.weighted_masked_mse(lat, noise, torch.ones(F, device=dev), torch.ones(F, device=dev)),
+            {"bytes": 4 * lat.numel()})
+        m = 64 * 1024 * 1024
+        master, m1, m2, gr = (torch.zeros(m, device=dev) for _ in range(4))
+        live = torch.zeros(m, device=dev, dtype=torch.bfloat16)
+        scale, skip = torch.ones(1, device=dev), torch.zeros(1, device=dev, dtype=torch.int32)
+        run("adamw", lambda: ops.adamw_(master, m1, m2, gr, live=live, lr=1e-4, beta1=0.9, beta2=0.99, eps=1e-8, wd=0.01,
+                                        step=1, grad_scale=scale, skip=skip), {"bytes": m * (4 * 4 + 3 * 4 + 2)})
+        run("sumsq", lambda: ops.sumsq(gr), {"bytes": 4 * m})
+        frame = rnd(3, 768, 1344).bfloat16()
+        run("rgb8", lambda: ops.rgb8(frame), {"bytes": frame.numel() * 3})
+    elif family == "headops":
+        H = D // 128
+        x = rnd(R, D).bfloat16()
+        w = torch.ones(128, device=dev)
+        cos, sin = torch.cos(rnd(R, 96)).contiguous(), torch.sin(rnd(R, 96)).contiguous()
+        mats = torch.eye(4, device=dev).repeat(R, 1, 1).contiguous()
+        with torch.no_grad():
+            run("headop_fwd", lambda: ops.head_norm_rope_prope(x, w, cos, sin, mats, heads=H), {"bytes": 4 * R * D + R * (96 * 8 + 64)})
+    elif family == "zero":
+        import ctypes
+
+        from ..ops._lib import load, ptr, stream_handle
+
+        lib = load()
+        n = 64 * 1024 * 1024
+        grads = torch.randn(n, device=dev)
+        out, ssq = torch.empty(n, device=dev), torch.zeros(1, device=dev)
+        one = (ctypes.c_void_p * 1)(grads.data_ptr())
+        run("zero_reduce(1 rank)", lambda: lib.solar_zero_reduce(one, ctypes.c_int(1), ctypes.c_longlong(0), ctypes.c_longlong(n),
+                                                                ptr(out), ptr(ssq), ctypes.c_int(0), stream_handle()),
+            {"bytes": 8 * n})
+        params = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        master, m1, m2 = (torch.zeros(n, device=dev) for _ in range(3))
+        scale, skip = torch.ones(1, device=dev), torch.zeros(1, device=dev, dtype=torch.int32)
+        pp = (ctypes.c_void_p * 1)(params.data_ptr())
+        run("zero_adamw_push(1 rank)", lambda: lib.solar_zero_adamw_push(
+            pp, ctypes.c_int(1), ctypes.c_int(1), ctypes.c_longlong(0), ctypes.c_longlong(n), ptr(master), ptr(m1), ptr(m2),
+            ptr(out), None, ctypes.c_float(1e-4), ctypes.c_float(0.9), ctypes.c_float(0.99), ctypes.c_float(1e-8),
+            ctypes.c_float(0.01), ctypes.c_int(1), ctypes.c_float(0.0), ptr(scale), ptr(skip), ctypes.c_int(0),
+            stream_handle()), {"bytes": n * (4 * 4 + 3 * 4 + 2)})
+    elif family in ("attention", "attention_bwd"):
+        from ..ops.attention_bwd_native import attn_bwd_native
+        from ..ops.attention_native import attn_fwd
+
+        S, H, Dh = 16384, 12, 128
+        q, k, v = (rnd(1, S, H, Dh).bfloat16() for _ in range(3))
+        scale = 1.0 / math.sqrt(Dh)
+        fl = 4.0 * S * S * H * Dh
+        if family == "attention":
+            run("attn_fwd", lambda: attn_fwd(q, k, v, scale), {"flops": fl, "bytes": 8 * S * H * Dh})
+        else:
+            o, lse = attn_fwd(q, k, v, scale)
+            do = rnd(1, S, H, Dh).bfloat16()
+            run("attn_bwd", lambda: attn_bwd_native(q, k, v, o, lse, do, scale), {"flops": 2.5 * fl, "bytes": 16 * S * H * Dh})
+    elif family == "conv":
+        x = rnd(4, 176, 320, 256).bfloat16()
+        w = (rnd(256, 256, 3, 3, 3) / (256 * 27) ** 0.5).bfloat16()
+        pw, pb = F_.pack_conv_weight(w, torch.zeros(256, device=dev).bfloat16())
+        run("conv3d", lambda: F_.conv3d_channels_last(x, pw, pb, (3, 3, 3)),
+            {"flops": 2.0 * 4 * 176 * 320 * 256 * 256 * 27, "bytes": 2 * x.numel() * 2 + pw.numel() * 2})
+    elif family == "gemm":
+        a, b = rnd(8192, 4096).bfloat16(), rnd(8192, 4096).bfloat16()
+        run("gemm_nt", lambda: ops.gemm(a, b, ops.NT), {"flops": 2.0 * 8192 * 8192 * 4096, "bytes": 2 * (2 * 8192 * 4096 + 8192 * 8192)})
+    else:
+        raise SystemExit(f"unknown kernel family {family!r}")
+    return plan
+
+
 def wan5b_suite(seq=27280):
     d, f = 3072, 14336
     rows = []
@@ -213,7 +341,15 @@ def main():
     c.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("suite")
     s.add_argument("--seq", type=int, default=27280)
+    pr = sub.add_parser("probe")
+    pr.add_argument("--family", required=True)
+    pr.add_argument("--rows", type=int, default=27280)
+    pr.add_argument("--dim", type=int, default=3072)
     args = ap.parse_args()
+    if args.cmd == "probe":
+        print(json.dumps({"family": args.family, "per_launch": probe(args.family, args.rows, args.dim)}))
+        ops.check_status()
+        return
     if args.cmd == "gemm":
         print(json.dumps(bench_gemm(args.m, args.n, args.k, args.layout, args.f32, args.iters)))
     elif args.cmd == "attention":
