@@ -101,11 +101,12 @@ class ShardedParameters:
     def _issue_gather(self, i: int) -> None:
         s = self.slot_of(i)
         side = self.stream
+        main = torch.cuda.current_stream()                   # the compute stream (read before switching streams)
         with torch.cuda.stream(side):
             if self._slot_free[s] is not None:
                 side.wait_event(self._slot_free[s])          # the slot's previous block is done with it
             else:
-                side.wait_stream(torch.cuda.current_stream())
+                side.wait_stream(main)
             u = self.units[i]
             per_bytes = (u.numel_m // self.world) * u.flat.element_size()
             check(self.lib.solar_comm_gather(ptr(self.gathered[s]), self.heap.peer_ptr_array(self.shard_off[i]),
