@@ -263,6 +263,8 @@ def run_ours(args):
             heap = SymmetricHeap(fused_heap_bytes(model.units(), world,
                                                   [b.unit for b in model.blocks] if args.fsdp == "params" else ()), None)
     trainer = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp, model=model, heap=heap)
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()            # construction transients (the un-sharded model) are not the step
     with torch.no_grad():  # a zero head would zero every upstream gradient; keep the step representative
         trainer.model.get_parameter("head.head.weight").normal_(0, 0.02)
     batch = make_batch(cfg, args)
@@ -301,6 +303,11 @@ def run_ours(args):
         phases = {k: v["total_ms"] for k, v in timer.summary().items() if not k.startswith("block.")}
     ops.check_status(f"cuda:{local}")
     peak_gib = torch.cuda.max_memory_allocated() / 2 ** 30
+    # the symmetric heap (parameters, gradients, exchange buffers of the fused transports) is allocated outside the
+    # caching allocator: report it, and the device's own view of used memory, next to the allocator's peak
+    free_b, total_b = torch.cuda.mem_get_info()
+    heap_gib = sum(h.nbytes for h in (heap, getattr(sp, "heap", None)) if h is not None) / 2 ** 30
+    used_gib = (total_b - free_b) / 2 ** 30
     utilization = {}
     try:        # model FLOPs (no recompute counted) against the measured sustained cuBLAS rate of this pool
         from solarwm_b200.utils.roofline import step_utilization
@@ -329,7 +336,8 @@ def run_ours(args):
                        "lean_resident_blocks": lean,
                        "attention_backend": ops.get_backend(), "optimizer": "AdamW fp32 master (in timed region)",
                        "l2": "no flush: per-step working set (>=10 GB of weights) exceeds the 126 MB L2",
-                       "peak_allocated_gib": round(peak_gib, 2)},
+                       "peak_allocated_gib": round(peak_gib, 2), "symmetric_heap_gib": round(heap_gib, 2),
+                       "device_memory_in_use_gib": round(used_gib, 2)},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
