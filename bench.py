@@ -37,19 +37,32 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="ti2v_5b", choices=["ti2v_5b", "ltx_2b", "small"],
-                    help="ltx_2b: LTX-Video-2B shape (pass --frames 16 --height 16 --width 24 for its 6,144-token clip)")
-    ap.add_argument("--mode", default="train", choices=["train", "realtime"],
-                    help="train: the headline training step; realtime: H3-shaped block-causal streaming (FPS)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"],
+                    help="reference: the unmodified reference package (Wan 5B shape only); baseline: THIS model code on "
+                         "library kernels -- cuBLAS GEMMs, cuDNN SDPA attention, NCCL all-to-all / reduce-scatter / "
+                         "all-gather, eager -- the NCCL+library arm for shapes the reference cannot run offline")
+    ap.add_argument("--model", default="ti2v_5b", choices=["ti2v_5b", "ltx_2b", "small", "i2v_a14b", "i2v_small"],
+                    help="ltx_2b: LTX-Video-2B shape (its 6,144-token clip [128,16,16,24] is the default geometry); "
+                         "i2v_a14b: Wan2.2 A14B-shaped TWO-expert training (high- / low-noise experts switched at sigma "
+                         "0.875, 75,600-token clip [16,21,90,160] + I2V conditioning; needs 8 GPUs); i2v_small: the same "
+                         "program on a small architecture")
+    ap.add_argument("--mode", default="train", choices=["train", "realtime", "infer"],
+                    help="train: the headline training step; realtime: H3-shaped block-causal streaming (FPS); infer: "
+                         "8-step flow-matching sampling of one clip (seconds per sample; BASELINE config 4 with "
+                         "--model ltx_2b)")
+    ap.add_argument("--sample-steps", type=int, default=8, help="infer mode: solver steps per sample")
     ap.add_argument("--h3", default="h3_33b", choices=["h3_33b", "tiny"], help="realtime mode: model preset")
     ap.add_argument("--prompt-tokens", type=int, default=512)
+    ap.add_argument("--geometry", default="baseline", choices=["baseline", "reference"],
+                    help="realtime mode: 'baseline' = chunks of 3 latent frames against a KV cache of 60 latent frames "
+                         "(20 chunks: 19 committed + the current one); 'reference' = the reference deployment's 5-latent "
+                         "chunks with 5 committed chunks of history.  Both run 4 denoise + 1 commit evaluation per chunk")
     ap.add_argument("--decode", default="vit", choices=["vit", "none"],
                     help="realtime mode: decode every generated latent to RGB8 frames with the streaming ViT decoder "
                          "(tiles dealt to the ranks) inside the timed region")
-    ap.add_argument("--frames", type=int, default=31)
-    ap.add_argument("--height", type=int, default=44)
-    ap.add_argument("--width", type=int, default=80)
+    ap.add_argument("--frames", type=int, default=None, help="latent frames (default: the model's benchmark clip)")
+    ap.add_argument("--height", type=int, default=None)
+    ap.add_argument("--width", type=int, default=None)
     ap.add_argument("--checkpointing", default="auto", choices=["auto", "none", "full", "selective"])
     ap.add_argument("--zero", default="fused", choices=["off", "collective", "fused"],
                     help="N > 1: shard optimizer state and gradient reduction over the ranks (own FSDP); "
@@ -72,7 +85,12 @@ def parse_args():
                          "transports at N > 1, where the step contains no library collective)")
     ap.add_argument("--sp-transport", default="fused", choices=["fused", "nccl"],
                     help="Ulysses exchange: fused into the kernels over NVLink peer memory, or NCCL all-to-all")
-    return ap.parse_args()
+    args = ap.parse_args()
+    f, h, w = GEOMETRY[args.model]
+    args.frames = f if args.frames is None else args.frames
+    args.height = h if args.height is None else args.height
+    args.width = w if args.width is None else args.width
+    return args
 
 
 class ClockSampler:
@@ -126,9 +144,18 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+GEOMETRY = {"ti2v_5b": (31, 44, 80), "small": (31, 44, 80), "ltx_2b": (16, 16, 24), "i2v_a14b": (21, 90, 160),
+            "i2v_small": (6, 16, 24)}
+
+
 def model_config(args):
     from solarwm_b200.models.wan import WanConfig, wan_preset
 
+    if args.model == "i2v_a14b":
+        return wan_preset("i2v_a14b")
+    if args.model == "i2v_small":
+        return WanConfig(model_type="i2v", in_dim=36, out_dim=16, dim=1024, ffn_dim=2048, num_heads=8, num_layers=3,
+                         text_dim=4096, text_len=512)
     if args.model == "small":
         return WanConfig(model_type="ti2v", in_dim=48, out_dim=48, dim=512, ffn_dim=2048, num_heads=8,
                          num_layers=4, text_dim=4096, text_len=512)
@@ -144,11 +171,18 @@ def make_batch(cfg, args, pinned=True):
     import torch
 
     g = torch.Generator().manual_seed(1234)
-    lat = torch.randn(1, args.frames, cfg.in_dim, args.height, args.width, generator=g).to(torch.bfloat16)
+    lat = torch.randn(1, args.frames, cfg.out_dim if cfg.model_type == "i2v" else cfg.in_dim, args.height, args.width,
+                      generator=g).to(torch.bfloat16)
     txt = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(torch.bfloat16)
+    batch = {"latents": lat, "text": txt}
+    if cfg.model_type == "i2v":          # I2V conditioning: 4-channel first-frame mask + the first frame's latent
+        y = torch.zeros(1, args.frames, cfg.in_dim - cfg.out_dim, args.height, args.width, dtype=torch.bfloat16)
+        y[:, 0, :4] = 1.0
+        y[:, 0, 4:] = lat[:, 0]
+        batch["y"] = y
     if pinned:
-        lat, txt = lat.pin_memory(), txt.pin_memory()
-    return {"latents": lat, "text": txt}
+        batch = {k: v.pin_memory() for k, v in batch.items()}
+    return batch
 
 
 def timed_region(steps, fn, dist, torch):
@@ -325,8 +359,9 @@ def run_ours(args):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None if BASELINE_TOKENS_PER_S is None else value / BASELINE_TOKENS_PER_S,
             "dtype": "bf16", "data": "synthetic latents/text of the named shapes, random-init weights",
-            "impl": "ours",
+            "impl": args.impl,
             "config": {"model": {"ti2v_5b": "wan22_ti2v_5b-shaped", "ltx_2b": "ltx_video_2b-shaped"}.get(args.model, "small-debug"),
+                       "gemm_backend": "library (cuBLAS)" if args.impl == "baseline" else "native",
                        "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
                        "optimizer_sharding": (f"zero-{args.zero}" if zero else "none"),
                        "cuda_graph_step": bool(graph),
@@ -351,6 +386,185 @@ def run_ours(args):
         if hasattr(sp, "close"):
             sp.close()
         dist.destroy_process_group()
+
+
+def run_infer(args):
+    """Seconds per ``--sample-steps``-step flow-matching sample of one clip (BASELINE config 4: LTX-Video-2B shape,
+    8 steps), through the LTX backend's public sampler, at SP = N.  A timed sample includes the host -> device copy of
+    the text embedding from pinned memory and the device -> host read of the finished latent."""
+    import torch
+
+    rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("LOCAL_RANK", 0), ("WORLD_SIZE", 1)))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dist = sp = None
+    cfg = model_config(args)
+    tokens = n_tokens(cfg, args)
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+        if args.sp_transport == "fused":
+            from solarwm_b200.parallel.fused_ulysses import FusedUlysses
+
+            sp = FusedUlysses(None, max_tokens=tokens, dim=cfg.dim, num_heads=cfg.num_heads,
+                              max_frame_tokens=max(tokens // args.frames, 64))
+        else:
+            from solarwm_b200.parallel.ulysses import UlyssesCollective
+
+            sp = UlyssesCollective(None)
+    from solarwm_b200 import ops
+    from solarwm_b200.backends.ltx25.backend import sample
+    from solarwm_b200.models.wan import WanDiT
+
+    if args.attention:
+        ops.set_backend(args.attention)
+    model = WanDiT(cfg, device=f"cuda:{local}", dtype=torch.bfloat16, seed=0)
+    with torch.no_grad():
+        model.get_parameter("head.head.weight").normal_(0, 0.02)
+    if sp is not None:
+        model.sp = sp
+    text_host = torch.randn(1, cfg.text_len, cfg.text_dim, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty(1, cfg.out_dim, args.frames, args.height, args.width, dtype=torch.bfloat16).pin_memory()
+
+    def one_sample():
+        text = text_host.to(f"cuda:{local}", non_blocking=True)
+        with torch.no_grad():
+            x = sample(model, text, frames=args.frames, height=args.height, width=args.width, steps=args.sample_steps, seed=3)
+        out_host.copy_(x, non_blocking=True)
+
+    for _ in range(max(args.warmup, 3)):
+        one_sample()
+    torch.cuda.synchronize()
+    ops.check_status(f"cuda:{local}")
+    sampler = ClockSampler(local)
+    sampler.start()
+    ops.reset_counters()
+    ms = timed_region(args.steps, one_sample, dist, torch)
+    launches = ops.total_launches()
+    clocks = sampler.stop()
+    ops.check_status(f"cuda:{local}")
+    if rank == 0:
+        per_sample = ms / args.steps / 1e3
+        print(json.dumps({
+            "metric": f"seconds per {args.sample_steps}-step flow-matching sample ({args.model}-shaped DiT)", "value": per_sample,
+            "unit": "s/sample", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic text embedding and seed noise of the named shapes, random-init weights",
+            "impl": args.impl,
+            "config": {"model": args.model, "solver": f"Euler, {args.sample_steps} steps, linear sigma grid", "seq_len": tokens,
+                       "latent": [1, cfg.out_dim, args.frames, args.height, args.width], "text": [1, cfg.text_len, cfg.text_dim],
+                       "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
+                       "attention_backend": ops.get_backend(),
+                       "gemm_backend": "library (cuBLAS)" if args.impl == "baseline" else "native",
+                       "l2": "no flush: 2 B parameters (4 GB) are re-read every solver step"},
+            "clocks": clocks,
+            "e2e": {"value": per_sample, "unit": "s/sample", "h2d_bytes_per_step": int(text_host.numel() * 2),
+                    "d2h_bytes_per_step": int(out_host.numel() * 2)},
+            "gpu_launches": launches, "tokens_per_s": tokens * args.sample_steps * args.steps / (ms / 1e3)}))
+    if dist is not None:
+        if hasattr(sp, "close"):
+            sp.close()
+        dist.destroy_process_group()
+
+
+def run_two_expert(args):
+    """BASELINE config 3: A14B-shaped two-expert training.  Both experts (40 blocks, dim 5120, 40 heads each) live
+    on the N GPUs with their parameters, gradient reductions and optimizer state sharded 1 / N (fused transports);
+    every step draws sigma, picks the expert by the 0.875 boundary and trains it on the 75,600-token clip."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus or world < 2:
+        raise SystemExit("the two-expert benchmark needs N >= 2 GPUs launched with torch.distributed.run "
+                         "(two 14 B experts with AdamW state do not fit one device)")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from solarwm_b200 import ops
+    from solarwm_b200.backends.wan22.experts import TwoExpertTrainer
+    from solarwm_b200.backends.wan22.stage0p5 import Stage0p5Options, WanStage0p5Trainer
+    from solarwm_b200.models.wan import WanDiT
+    from solarwm_b200.parallel.fused_ulysses import FusedUlysses
+    from solarwm_b200.parallel.symm import SymmetricHeap
+    from solarwm_b200.parallel.zero import fused_heap_bytes
+
+    cfg = model_config(args)
+    tokens = n_tokens(cfg, args)
+    frame_tokens = tokens // args.frames
+    sp = FusedUlysses(None, max_tokens=tokens, dim=cfg.dim, num_heads=cfg.num_heads, max_frame_tokens=frame_tokens)
+    ckpt = "none" if args.checkpointing == "auto" else args.checkpointing
+    graph = args.graph != "off"
+    trainers, need = {}, 1 << 20
+    models = {}
+    for i, name in enumerate(("high_noise", "low_noise")):
+        models[name] = WanDiT(cfg, device=f"cuda:{local}", dtype=torch.bfloat16, seed=i, shard_pad=2 * world)
+        with torch.no_grad():
+            models[name].get_parameter("head.head.weight").normal_(0, 0.02)
+        need += fused_heap_bytes(models[name].units(), world, [b.unit for b in models[name].blocks])
+    heap = SymmetricHeap(need, None)
+    for name in ("high_noise", "low_noise"):
+        opts = Stage0p5Options(lr=1e-4, timestep_shift=5.0, sigma_sampling="logit_normal", checkpointing=ckpt,
+                               max_grad_norm=1.0, seed=0, zero=True, zero_transport="fused", cuda_graph=graph,
+                               shard_params=True, ti2v_first_frame_clean=False)
+        trainers[name] = WanStage0p5Trainer(cfg, f"cuda:{local}", opts, sp=sp, model=models[name], heap=heap)
+        torch.cuda.empty_cache()
+    pair = TwoExpertTrainer(trainers["high_noise"], trainers["low_noise"], boundary=0.875, shift=5.0, seed=0)
+    batch = make_batch(cfg, args)
+    dev_batch = {k: v.to(f"cuda:{local}") for k, v in batch.items()}
+    h2d = sum(v.numel() * v.element_size() for v in batch.values())
+    losses = []
+    # warm-up must take BOTH experts past their eager steps and their graph capture
+    warm_sigmas = [0.95, 0.5] * max(args.warmup, 4)
+    for s_ in warm_sigmas:
+        losses.append(float(pair.train_step(batch, sigma=torch.tensor([s_])).item()))
+    ops.check_status(f"cuda:{local}")
+    torch.cuda.reset_peak_memory_stats()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ops.reset_counters()
+    pair.steps = {"high_noise": 0, "low_noise": 0}
+    ms = timed_region(args.steps, lambda: pair.train_step(dev_batch), dist, torch)
+    launches, counters = ops.total_launches(), dict(ops.COUNTERS)
+    per_expert = dict(pair.steps)
+
+    def step_e2e():
+        losses.append(float(pair.train_step(batch).item()))
+
+    ms_e2e = timed_region(args.steps, step_e2e, dist, torch)
+    clocks = sampler.stop()
+    ops.check_status(f"cuda:{local}")
+    free_b, total_b = torch.cuda.mem_get_info()
+    if rank == 0:
+        value = tokens * args.steps / (ms / 1e3)
+        print(json.dumps({
+            "metric": "DiT train tokens/s/box (Wan2.2 A14B-shaped two-expert flow-matching step)", "value": value,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": len(warm_sigmas),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic latents / I2V conditioning / text of the named shapes, random-init weights",
+            "impl": "ours",
+            "config": {"model": f"{args.model}: two experts x {cfg.num_layers} blocks, dim {cfg.dim}, {cfg.num_heads} heads, "
+                                f"ffn {cfg.ffn_dim}", "expert_boundary_sigma": 0.875, "steps_per_expert": per_expert,
+                       "global_batch": 1, "seq_len": tokens, "parallelism": f"sp{world}", "sp_transport": "fused",
+                       "optimizer_sharding": "zero-fused", "parameter_sharding": "blocks sharded 1/N, gathered just in time",
+                       "cuda_graph_step": graph, "latent": [1, cfg.out_dim, args.frames, args.height, args.width],
+                       "i2v_condition": [1, cfg.in_dim - cfg.out_dim, args.frames, args.height, args.width],
+                       "text": [1, cfg.text_len, cfg.text_dim], "activation_checkpointing": ckpt,
+                       "optimizer": "AdamW fp32 master per expert (in timed region)",
+                       "l2": "no flush: per-step working set exceeds the 126 MB L2",
+                       "peak_allocated_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2),
+                       "symmetric_heap_gib": round((heap.nbytes + sp.heap.nbytes) / 2 ** 30, 2),
+                       "device_memory_in_use_gib": round((total_b - free_b) / 2 ** 30, 2)},
+            "clocks": clocks,
+            "e2e": {"value": tokens * args.steps / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": h2d + 4, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "launch_counters": counters, "final_loss": losses[-1]}))
+    sp.close()
+    dist.destroy_process_group()
 
 
 def run_realtime(args):
@@ -456,8 +670,13 @@ def run_realtime(args):
                       + (", DiT + streaming ViT decode to RGB8)" if dec is not None else ", DiT only)"), "value": fps,
             "unit": "frames/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic prompt/anchor/cameras, random-init weights", "impl": "ours",
-            "config": {"model": args.h3, "chunk_latents": scfg.chunk_latents, "window_chunks": scfg.window_chunks,
+            "dtype": "bf16", "data": "synthetic prompt/anchor/cameras, random-init weights", "impl": args.impl,
+            "config": {"model": args.h3, "geometry": args.geometry, "chunk_latents": scfg.chunk_latents,
+                       "window_chunks": scfg.window_chunks,
+                       "kv_cache_latents": (scfg.window_chunks + 1) * scfg.chunk_latents,
+                       "sp_exchange": scfg.sp_exchange if world > 1 else "none",
+                       "gemm_backend": "library (cuBLAS)" if args.impl == "baseline" else "native",
+                       "attention_backend": ops.get_backend(),
                        "denoise_steps": scfg.denoise_steps, "rows_per_latent": gen.rows_per_latent,
                        "frames_per_chunk": frames,
                        "prompt_tokens": args.prompt_tokens, "parallelism": f"sp{world}",
@@ -474,8 +693,27 @@ def run_realtime(args):
 
 def main():
     args = parse_args()
-    if args.mode == "realtime" and args.impl == "ours":
+    if args.impl == "baseline":
+        # same model, library kernels and collectives: the baseline arm
+        args.attention, args.sp_transport, args.graph, args.fsdp = "library", "nccl", "off", "optimizer"
+        args.zero = "collective" if args.zero == "fused" else args.zero
+        from solarwm_b200 import ops as _ops
+
+        _ops.set_gemm_backend("library")
+    if args.mode == "realtime" and args.impl in ("ours", "baseline"):
         run_realtime(args)
+        return 0
+    if args.mode == "infer":
+        run_infer(args)
+        return 0
+    if args.model in ("i2v_a14b", "i2v_small"):
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "the reference trains one A14B expert and shards nothing over the SP group (its FSDP group is "
+                              "the logical-DP group, size 1 at SP=8): 14 B parameters with fp32 gradients and AdamW state do "
+                              "not fit one 180 GB device, and it has no two-expert training step"}))
+            return 0
+        run_two_expert(args)
         return 0
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT / "baseline"))

@@ -32,8 +32,15 @@ from .layout import TAG_TEXT, TAG_VIDEO, patchify_latents, spatial_axis, tempora
 
 
 def w6_attention(q, k, v, *, n_cond: int, chunk_rows: int, n_chunks: int, window_chunks: int):
-    """q / k / v [1, S, H, D] with S = n_cond + 2 * n_chunks * chunk_rows.  Returns [1, S, H, D]."""
+    """q / k / v [1, S, H, D] with S = n_cond + 2 * n_chunks * chunk_rows.  Returns [1, S, H, D].  On the device one
+    masked flash-attention call evaluates the whole rule (prefix rows, clean windows, noisy chunks); the per-chunk loop
+    below is its CPU form."""
     L = n_chunks * chunk_rows
+    if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and ops.get_backend() == "native":
+        from ...models.wan_tf import _cached_mask
+        from ...ops.attention_mask import masked_attention
+
+        return masked_attention(q, k, v, _cached_mask("tf", L, chunk_rows, window_chunks, 0, n_cond))
     c0, n0 = n_cond, n_cond + L                     # first clean row, first noisy row
     outs = [ops.attention(q[:, :n_cond], k[:, :n_cond], v[:, :n_cond])]
     clean, noisy = [], []

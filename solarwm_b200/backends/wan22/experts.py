@@ -75,3 +75,45 @@ class ExpertPair:
         if not (hi or lo):
             raise ValueError("timesteps of one call straddle the expert boundary")
         return self.model_for(float(side.flatten()[0]))(x, t, context, **kw)
+
+
+class TwoExpertTrainer:
+    """Flow-matching training of BOTH experts of an A14B-style pair in one run.
+
+    Every step draws the per-video sigma first -- on the host, from a generator that sequence-parallel peers seed
+    alike, so that choosing the expert costs no device read -- and then runs the whole step (forward, backward,
+    sharded update) on the expert that owns that side of ``boundary``: the high-noise expert for
+    ``sigma >= boundary``, the low-noise expert below it.  Each expert is a complete ``WanStage0p5Trainer`` with its
+    own sharded optimizer; the two share the sequence-parallel context and the symmetric heap.  With parameter
+    sharding only ``1 / world`` of either expert's weights, gradients' reductions and optimizer state is resident.
+
+    The reference trains the high-noise expert alone (its A14B recipe); the boundary switch follows the upstream
+    Wan2.2 two-expert inference rule."""
+
+    def __init__(self, high_noise, low_noise, *, boundary: float = BOUNDARY_I2V, shift: float = 5.0, seed: int = 0):
+        self.trainers = {"high_noise": high_noise, "low_noise": low_noise}
+        self.boundary, self.shift = float(boundary), float(shift)
+        self.host_gen = torch.Generator().manual_seed(int(seed) * 100003 + 17)
+        self.steps = {"high_noise": 0, "low_noise": 0}
+        self.last_expert = None
+
+    def draw_sigma(self, n: int = 1) -> torch.Tensor:
+        """Logit-normal sigmas with the timestep shift, on the host."""
+        u = torch.sigmoid(torch.randn(n, generator=self.host_gen))
+        return self.shift * u / (1.0 + (self.shift - 1.0) * u)
+
+    def train_step(self, batch: dict, sigma: Optional[torch.Tensor] = None) -> torch.Tensor:
+        sigma = self.draw_sigma(batch["latents"].shape[0]) if sigma is None else sigma
+        sides = {expert_for_sigma(float(s), self.boundary) for s in sigma}
+        if len(sides) != 1:
+            raise ValueError("the sigmas of one micro-batch straddle the expert boundary (use micro-batch 1)")
+        name = sides.pop()
+        trainer = self.trainers[name]
+        t_video = (sigma * trainer.scheduler.num_train_timesteps).to(torch.float32)
+        if batch["latents"].is_cuda:
+            t_video = t_video.to(batch["latents"].device)
+        elif trainer.device.type == "cuda":
+            t_video = t_video.pin_memory()
+        self.steps[name] += 1
+        self.last_expert = name
+        return trainer.train_step({**batch, "t_video": t_video})

@@ -63,7 +63,10 @@ class WanStage0p5Trainer:
         self.model.checkpointing = opts.checkpointing
         self.model.keep_blocks = opts.keep_blocks
         self.model.lean_kept = bool(opts.lean_kept)
-        self.model.ensure_grads()
+        if opts.shard_params:
+            self.model.stem.ensure_grads()       # block gradients live in the shared slots of the parameter shards
+        else:
+            self.model.ensure_grads()
         okw = dict(lr=opts.lr, betas=opts.betas, eps=opts.eps, weight_decay=opts.weight_decay, ema_decay=opts.ema_decay)
         if opts.zero and self.sp_size * self.dp_size > 1:
             from ...parallel.zero import ZeroAdamW
@@ -101,11 +104,14 @@ class WanStage0p5Trainer:
         s = logit_normal_sigmas(B, self.opts.timestep_shift, generator=self.gen, device=self.device)
         return s * self.scheduler.num_train_timesteps
 
-    def microbatch(self, latents: torch.Tensor, text: torch.Tensor, y: Optional[torch.Tensor] = None):
-        """latents [B, F, C, H, W] (frame-major, as stored by the data plane); text [B, T, text_dim]."""
+    def microbatch(self, latents: torch.Tensor, text: torch.Tensor, y: Optional[torch.Tensor] = None,
+                   t_video: Optional[torch.Tensor] = None):
+        """latents [B, F, C, H, W] (frame-major, as stored by the data plane); text [B, T, text_dim];
+        ``t_video`` [B]: the per-video timesteps when the caller draws them (two-expert training picks the expert
+        from them before the step), default: drawn here."""
         o = self.opts
         B, F = latents.shape[:2]
-        t_video = self.sample_timesteps(B)
+        t_video = self.sample_timesteps(B) if t_video is None else t_video.to(self.device, torch.float32)
         noise = torch.randn(latents.shape, generator=self.gen, device=self.device, dtype=torch.float32).to(latents.dtype)
         dropped = torch.rand(B, generator=self.gen, device=self.device) < o.image_dropout
         if self.sp is not None and self.sp.size > 1 and not getattr(self.sp, "fused", False):
@@ -171,7 +177,7 @@ class WanStage0p5Trainer:
         txt = batch["text"].to(dev, non_blocking=True)
         y = batch.get("y")
         y = None if y is None else y.to(dev, non_blocking=True)
-        loss = self.microbatch(lat, txt, y)
+        loss = self.microbatch(lat, txt, y, batch.get("t_video"))
         self.optimizer_step()
         return loss
 
@@ -198,12 +204,13 @@ class WanStage0p5Trainer:
         if why is not None:
             raise RuntimeError(f"cuda_graph is not available with {why}")
         st = self.__dict__.setdefault("_graph_state", {"eager": 0, "graph": None})
-        keys = [k for k in ("latents", "text", "y") if batch.get(k) is not None]
+        keys = [k for k in ("latents", "text", "y", "t_video") if batch.get(k) is not None]
         if st["graph"] is None and st["eager"] < int(self.opts.graph_warmup_steps):
             st["eager"] += 1
             dev = self.device
             loss = self.microbatch(batch["latents"].to(dev, non_blocking=True), batch["text"].to(dev, non_blocking=True),
-                                   None if batch.get("y") is None else batch["y"].to(dev, non_blocking=True))
+                                   None if batch.get("y") is None else batch["y"].to(dev, non_blocking=True),
+                                   batch.get("t_video"))
             self.optimizer_step()
             return loss
         opt = self.optimizer
@@ -223,7 +230,8 @@ class WanStage0p5Trainer:
             step_before = self.global_step
             counted = dict(ops.COUNTERS)
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                loss = self.microbatch(st["inputs"]["latents"], st["inputs"]["text"], st["inputs"].get("y"))
+                loss = self.microbatch(st["inputs"]["latents"], st["inputs"]["text"], st["inputs"].get("y"),
+                                       st["inputs"].get("t_video"))
                 norm = self.optimizer_step()
             self.global_step = step_before
             # the launch counters advanced while capturing although nothing ran: take that back, and add the same

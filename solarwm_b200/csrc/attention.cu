@@ -22,6 +22,7 @@
 //
 // Replaces flash_attn_varlen_func / SDPA on the reference's attention path
 // (solar/backends/wan22/runtime/modeling/attention.py:34-188).
+#include "attn_mask.cuh"
 #include "comm.cuh"
 #include "host_util.h"
 #include "sm100.cuh"
@@ -39,6 +40,7 @@ struct AttnParams {
   float scale;
   float* lse;         // [B, H, Sq] natural-log sum-exp of the scaled scores (may be null)
   int* status;
+  AttnMask mask;      // used by the MASKED instantiation only
 };
 
 template <int HD>
@@ -53,7 +55,7 @@ struct AttnSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-template <int HD>
+template <int HD, bool MASKED>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -79,7 +81,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int q0 = blockIdx.x * (2 * QT);
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
-  const int n_kv = (p.Sk + KT - 1) / KT;
+  const int n_kv = MASKED ? p.mask.tile_count[blockIdx.x] : (p.Sk + KT - 1) / KT;
+  const int* kv_list = MASKED ? p.mask.tile_list + static_cast<long long>(blockIdx.x) * p.mask.stride : nullptr;
+  // KV tile visited by iteration j (all tiles in order, or the CTA's list under a structured mask)
+  auto kv_tile = [&](int j) -> int { return MASKED ? (kv_list[j] & (kMaskPartialBit - 1)) : j; };
   // the second Q tile may be entirely past the end of the sequence
   const bool tile1_live = (q0 + QT) < p.Sq;
 
@@ -133,13 +138,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < L::CHUNKS; ++c)
           tma_load_4d(smem + L::K_OFF + s * L::TILE_BYTES + c * L::CHUNK_BYTES, &tmK, &k_full[s], c * 64, head,
-                      j * KT, batch);
+                      kv_tile(j) * KT, batch);
         if (!mbar_wait(&v_empty[s], ph ^ 1, abort_word, ST_TIMEOUT_EMPTY)) break;
         mbar_expect_tx(&v_full[s], L::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < L::CHUNKS; ++c)
           tma_load_4d(smem + L::V_OFF + s * L::TILE_BYTES + c * L::CHUNK_BYTES, &tmV, &v_full[s], c * 64, head,
-                      j * KT, batch);
+                      kv_tile(j) * KT, batch);
       }
     }
   } else if (warp == 1) {
@@ -227,10 +232,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m_used = -INFINITY, l = 0.f;
     const float c = p.scale_log2;
     bool ok = live;
+    // this row's key ranges (structured mask); rows past the end see nothing and are never stored
+    int rg[6] = {0, 0, 0, 0, 0, 0};
+    if (MASKED) {
+      const int qrow = q0 + t * QT + row;
+      if (qrow < p.Sq) {
+#pragma unroll
+        for (int i = 0; i < 6; ++i) rg[i] = __ldg(p.mask.row_ranges + static_cast<long long>(qrow) * 6 + i);
+      }
+    }
     for (int j = 0; j < n_kv && ok; ++j) {
       if (!mbar_wait(&s_ready[t], j & 1, abort_word, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int kv_valid = p.Sk - j * KT;       // >= 128 except on the last tile
+      const int k0 = kv_tile(j) * KT;
+      const int kv_valid = p.Sk - k0;           // >= 128 except on the last tile
       // the whole 128-score row of this thread in registers: four loads in flight, one wait
       uint32_t s[128];
 #pragma unroll
@@ -240,6 +255,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int e = 0; e < 128; ++e)
           if (e >= kv_valid) s[e] = __float_as_uint(-INFINITY);
+      }
+      if (MASKED && (kv_list[j] & kMaskPartialBit)) {
+        // some row of the CTA sees this tile only in part: rows that one of their ranges covers whole skip the work
+        const int k1 = min(k0 + KT, p.Sk);
+        const bool whole = (rg[0] <= k0 && k1 <= rg[1]) || (rg[2] <= k0 && k1 <= rg[3]) || (rg[4] <= k0 && k1 <= rg[5]);
+        if (!whole) {
+#pragma unroll
+          for (int e = 0; e < 128; ++e) {
+            if (!mask_sees(rg, k0 + e)) s[e] = __float_as_uint(-INFINITY);
+          }
+        }
       }
       float mx = fmaxf(__uint_as_float(s[0]), __uint_as_float(s[1]));
 #pragma unroll
@@ -270,7 +296,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // P = exp2(s * c - m * c) with packed fp32x2 arithmetic, bf16 pairs over the first 64 columns of S_t
       const float2 c2 = make_float2(c, c);
-      const float2 n2 = make_float2(-m_used * c, -m_used * c);
+      // a row that has seen no key yet keeps m = -inf; its scores are all -inf and must give P = 0, not NaN
+      const float m_exp = (MASKED && m_used == -INFINITY) ? 0.f : m_used;
+      const float2 n2 = make_float2(-m_exp * c, -m_exp * c);
       float2 l2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int e = 0; e < 64; ++e) {
@@ -291,7 +319,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok) ok = mbar_wait(&o_done[t], (n_kv - 1) & 1, abort_word, ST_TIMEOUT_OTHER);
     if (ok) {
       tc_fence_after();
-      const float inv_l = 1.0f / l;
+      const float inv_l = (MASKED && !(l > 0.f)) ? 0.f : 1.0f / l;
       uint8_t* obuf = smem + L::Q_OFF + t * L::TILE_BYTES;
 #pragma unroll
       for (int cc = 0; cc < HD / 32; ++cc) {
@@ -343,10 +371,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (rs.active()) cta_done_signal_peers(rs.flags);
 }
 
-template <int HD>
+template <int HD, bool MASKED>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const CUtensorMap& to, const AttnParams& p, cudaStream_t st, const RowScatter& rs) {
-  auto kern = attn_fwd_kernel<HD>;
+  auto kern = attn_fwd_kernel<HD, MASKED>;
   static PerDeviceOnce configured;   // the attribute is per device
   if (configured.first()) {
     SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<HD>::TOTAL));
@@ -375,7 +403,7 @@ using namespace solar;
 static int attn_fwd_entry(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
                           int H, int D, long long q_ss, long long q_sb, long long k_ss, long long k_sb,
                           long long v_ss, long long v_sb, long long o_ss, long long o_sb, float scale, int* status,
-                          void* stream, const RowScatter& rs) {
+                          void* stream, const RowScatter& rs, const AttnMask* mask = nullptr) {
   if (D != 64 && D != 128) return fail("attention: head_dim must be 64 or 128%s");
   if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0) return fail("attention: empty problem%s");
   CUtensorMap tq, tk, tv, to;
@@ -390,9 +418,15 @@ static int attn_fwd_entry(const void* q, const void* k, const void* v, void* o, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = lse;
   p.status = status;
+  memset(&p.mask, 0, sizeof(p.mask));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 128) return launch_attn_fwd<128>(tq, tk, tv, to, p, st, rs);
-  return launch_attn_fwd<64>(tq, tk, tv, to, p, st, rs);
+  if (mask != nullptr) {
+    p.mask = *mask;
+    if (D == 128) return launch_attn_fwd<128, true>(tq, tk, tv, to, p, st, rs);
+    return launch_attn_fwd<64, true>(tq, tk, tv, to, p, st, rs);
+  }
+  if (D == 128) return launch_attn_fwd<128, false>(tq, tk, tv, to, p, st, rs);
+  return launch_attn_fwd<64, false>(tq, tk, tv, to, p, st, rs);
 }
 
 extern "C" int solar_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B,
@@ -403,6 +437,24 @@ extern "C" int solar_attn_fwd(const void* q, const void* k, const void* v, void*
   memset(&none, 0, sizeof(none));
   return attn_fwd_entry(q, k, v, o, lse, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss, v_sb, o_ss, o_sb, scale,
                         status, stream, none);
+}
+
+// Attention under a structured mask: query row i attends the union of the key ranges row_ranges[i] (three [lo, hi)
+// pairs).  tile_list / tile_count: for every block of 256 query rows, the 128-key tiles that some row of the block
+// sees (bit 30 of an entry: some row sees the tile only in part), built by the caller (ops/attention_mask.py).
+// All three tables are int32 in device memory; every block of rows must list at least one tile.
+extern "C" int solar_attn_fwd_masked(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq,
+                                     int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
+                                     long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
+                                     float scale, int* status, void* stream, const int* row_ranges,
+                                     const int* tile_list, const int* tile_count, int list_stride) {
+  if (row_ranges == nullptr || tile_list == nullptr || tile_count == nullptr || list_stride < 1)
+    return fail("masked attention: the mask tables are required%s");
+  RowScatter none;
+  memset(&none, 0, sizeof(none));
+  AttnMask m{row_ranges, tile_list, tile_count, list_stride};
+  return attn_fwd_entry(q, k, v, o, lse, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss, v_sb, o_ss, o_sb, scale,
+                        status, stream, none, &m);
 }
 
 // Attention over this rank's heads and the whole sequence whose output rows are, in addition to

@@ -37,6 +37,7 @@
 //
 // Replaces the flash_attn / cuDNN SDPA backward used by the reference
 // (solar/backends/wan22/runtime/modeling/attention.py:98-135, solar/backends/minimax_h3/fast_attention.py:103).
+#include "attn_mask.cuh"
 #include "comm.cuh"
 #include "host_util.h"
 #include "sm100.cuh"
@@ -59,6 +60,7 @@ struct AttnBwdParams {
   const __nv_bfloat16* stat1; long long stat1_ss, stat1_sb;
   long long* trace;      // optional cycle counters of CTA (0,0,0): see solar_attn_bwd_trace
   int scat_col[2];       // peer scatter: destination column of head 0 for output 0 (dV / dQ) and output 1 (dK)
+  AttnMask mask;         // MASKED instantiations: row_ranges are per QUERY; the tile list is over the streamed operand
 };
 
 // trace slots (per mode, 8 each): 0 score-warp loop cycles, 1 score-warp wait strm_full, 2 score-warp
@@ -77,7 +79,8 @@ struct BwdSmem {
   static constexpr int STRM_OFF = 2 * STAT_TILE;            // BW_STAGES x (stream0 | stream1)
   static constexpr int BAR_OFF = STRM_OFF + BW_STAGES * 2 * STRM_TILE;
   static constexpr int VEC_OFF = BAR_OFF + 256;             // per compute warp: 32 L2 + 32 delta floats
-  static constexpr int TOTAL = VEC_OFF + 8 * 64 * 4 + 1024;
+  static constexpr int MASK_OFF = VEC_OFF + 8 * 64 * 4;     // per compute warp: key ranges of its 32 streamed queries
+  static constexpr int TOTAL = MASK_OFF + 8 * 32 * 6 * 4 + 1024;
 };
 
 __device__ __forceinline__ void bw_tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2,
@@ -147,8 +150,8 @@ __device__ __forceinline__ float ld_f1_early(const float* ptr) {
   return v;
 }
 
-// MODE 0 = dK/dV, MODE 1 = dQ.
-template <int HD, int MODE>
+// MODE 0 = dK/dV, MODE 1 = dQ.  MASKED: structured key ranges per query (attn_mask.cuh).
+template <int HD, int MODE, bool MASKED>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
                 const __grid_constant__ CUtensorMap tmStrm0, const __grid_constant__ CUtensorMap tmStrm1,
@@ -178,7 +181,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
   const int row0 = blockIdx.x * ST_ROWS;
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
-  const int n_tiles = (p.S_stream + SR_ROWS - 1) / SR_ROWS;
+  const int n_tiles = MASKED ? p.mask.tile_count[blockIdx.x] : (p.S_stream + SR_ROWS - 1) / SR_ROWS;
+  const int* tile_list = MASKED ? p.mask.tile_list + static_cast<long long>(blockIdx.x) * p.mask.stride : nullptr;
+  // streamed tile visited by iteration j (every tile in order, or this CTA's list under a structured mask)
+  auto tile_of = [&](int j) -> int { return MASKED ? (tile_list[j] & (kMaskPartialBit - 1)) : j; };
   const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   if (threadIdx.x == 0) {
@@ -242,9 +248,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
         uint8_t* base = smem + L::STRM_OFF + s * 2 * L::STRM_TILE;
 #pragma unroll
         for (int c = 0; c < L::CHUNKS; ++c) {
-          tma_load_4d(base + c * L::STRM_CHUNK, &tmStrm0, &strm_full[s], c * 64, head, j * SR_ROWS, batch);
+          tma_load_4d(base + c * L::STRM_CHUNK, &tmStrm0, &strm_full[s], c * 64, head, tile_of(j) * SR_ROWS, batch);
           tma_load_4d(base + L::STRM_TILE + c * L::STRM_CHUNK, &tmStrm1, &strm_full[s], c * 64, head,
-                      j * SR_ROWS, batch);
+                      tile_of(j) * SR_ROWS, batch);
         }
       }
       if (tracing) p.trace[MODE * 8 + 5] = w_empty;
@@ -431,8 +437,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
     float* vec_smem = reinterpret_cast<float*>(smem + L::VEC_OFF) + (warp - 4) * 64;
     float nxtL = 0.f, nxtD = 0.f;
     if (MODE == 0) {
-      nxtL = __ldg(p.L2 + vec_base + wg * 32 + lane);
-      nxtD = __ldg(p.delta + vec_base + wg * 32 + lane);
+      nxtL = __ldg(p.L2 + vec_base + tile_of(0) * SR_ROWS + wg * 32 + lane);
+      nxtD = __ldg(p.delta + vec_base + tile_of(0) * SR_ROWS + wg * 32 + lane);
+    }
+    // structured mask: in dQ mode the thread's row is a query with its own key ranges; in dK/dV mode the thread's row
+    // is a key and the ranges of the tile's 32 queries of this warpgroup are parked per warp in shared memory
+    int rg[6] = {0, 0, 0, 0, 0, 0};
+    int* mask_smem = reinterpret_cast<int*>(smem + L::MASK_OFF) + (warp - 4) * 32 * 6;
+    if (MASKED && MODE == 1 && row0 + row < p.S_stat) {
+#pragma unroll
+      for (int i = 0; i < 6; ++i) rg[i] = __ldg(p.mask.row_ranges + static_cast<long long>(row0 + row) * 6 + i);
     }
     // Both warpgroups work on every streamed tile: warpgroup g owns columns [32g, 32g+32) of the
     // 64-column S / dP tile and writes its packed bf16 results over columns [32g, 32g+16).
@@ -449,8 +463,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
         vec_smem[32 + lane] = -nxtD;
         __syncwarp();
         if (j + 1 < n_tiles) {
-          nxtL = ld_f1_early(p.L2 + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
-          nxtD = ld_f1_early(p.delta + vec_base + (j + 1) * SR_ROWS + wg * 32 + lane);
+          nxtL = ld_f1_early(p.L2 + vec_base + tile_of(j + 1) * SR_ROWS + wg * 32 + lane);
+          nxtD = ld_f1_early(p.delta + vec_base + tile_of(j + 1) * SR_ROWS + wg * 32 + lane);
         }
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -469,6 +483,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
       tmem_ld_wait();
       if (tracing) { const long long q1 = clock64(); seg[0] += q1 - q0; q0 = q1; }
       if (tracing) { const long long q1 = clock64(); seg[6] += q1 - q0; q0 = q1; }
+      if (MASKED && (tile_list[j] & kMaskPartialBit)) {
+        // masked (query, key) pairs get a score of -inf, hence P = 0 and dS = 0
+        const int t0 = tile_of(j) * SR_ROWS + wg * 32;          // first streamed index of this warpgroup's columns
+        if (MODE == 1) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (!mask_sees(rg, t0 + e)) s[e] = __float_as_uint(-INFINITY);
+        } else {
+          __syncwarp();
+          const int qi = t0 + lane;
+#pragma unroll
+          for (int i = 0; i < 6; ++i)
+            mask_smem[lane * 6 + i] = qi < p.S_stream ? __ldg(p.mask.row_ranges + static_cast<long long>(qi) * 6 + i) : 0;
+          __syncwarp();
+          const int key = row0 + row;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            int qr[6];
+#pragma unroll
+            for (int i = 0; i < 6; ++i) qr[i] = mask_smem[e * 6 + i];
+            if (!mask_sees(qr, key)) s[e] = __float_as_uint(-INFINITY);
+          }
+        }
+      }
       uint32_t pk[16], dk[16];
       // P = exp2(S * c - L2); kept as fp32 in s[] for the dS product
 #pragma unroll
@@ -640,9 +678,9 @@ static int bshd_map(CUtensorMap* m, const void* ptr, int B, int S, int H, int D,
   return make_tmap_4d(m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dims, strides, box);
 }
 
-template <int HD, int MODE>
+template <int HD, int MODE, bool MASKED = false>
 static int launch_bwd(const CUtensorMap* maps, const AttnBwdParams& p, cudaStream_t st, const RowScatter& rs) {
-  auto kern = attn_bwd_kernel<HD, MODE>;
+  auto kern = attn_bwd_kernel<HD, MODE, MASKED>;
   static PerDeviceOnce configured;   // the attribute is per device
   if (configured.first()) {
     SOLAR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<HD>::TOTAL));
@@ -709,7 +747,8 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
                          const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq, int Sk, int H,
                          int D, long long q_ss, long long q_sb, long long k_ss, long long k_sb, long long v_ss,
                          long long v_sb, long long o_ss, long long o_sb, long long do_ss, long long do_sb, float scale,
-                         int* status, void* stream, int allow_overlap, const BwdScatter* scat) {
+                         int* status, void* stream, int allow_overlap, const BwdScatter* scat,
+                         const AttnMask* mask_dkv = nullptr, const AttnMask* mask_dq = nullptr) {
   if (D != 64 && D != 128) return fail("attention backward: head_dim must be 64 or 128%s");
   if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0) return fail("attention backward: empty problem%s");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -731,6 +770,8 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
   p.L2 = L2; p.delta = delta; p.status = status;
   p.trace = nullptr;
   p.scat_col[0] = p.scat_col[1] = 0;
+  memset(&p.mask, 0, sizeof(p.mask));
+  const bool masked = mask_dkv != nullptr && mask_dq != nullptr;
   RowScatter rs;
   memset(&rs, 0, sizeof(rs));
   if (scat != nullptr) {
@@ -772,7 +813,12 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
       p.scat_col[0] = scat->col_dv;
       p.scat_col[1] = scat->col_dk;
     }
-    rc = D == 128 ? launch_bwd<128, 0>(m, p, st, rs) : launch_bwd<64, 0>(m, p, st, rs);
+    if (masked) {
+      p.mask = *mask_dkv;
+      rc = D == 128 ? launch_bwd<128, 0, true>(m, p, st, rs) : launch_bwd<64, 0, true>(m, p, st, rs);
+    } else {
+      rc = D == 128 ? launch_bwd<128, 0>(m, p, st, rs) : launch_bwd<64, 0>(m, p, st, rs);
+    }
     if (rc) return rc;
   }
   {
@@ -791,7 +837,12 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
       p.scat_col[0] = scat->col_dq;
       p.scat_col[1] = scat->col_dq;
     }
-    rc = D == 128 ? launch_bwd<128, 1>(m, p, st_dq, rs) : launch_bwd<64, 1>(m, p, st_dq, rs);
+    if (masked) {
+      p.mask = *mask_dq;
+      rc = D == 128 ? launch_bwd<128, 1, true>(m, p, st_dq, rs) : launch_bwd<64, 1, true>(m, p, st_dq, rs);
+    } else {
+      rc = D == 128 ? launch_bwd<128, 1>(m, p, st_dq, rs) : launch_bwd<64, 1>(m, p, st_dq, rs);
+    }
     if (st_dq != st) {                                               // join even when the launch failed
       cudaEventRecord(g_join_ev[dev], st_dq);
       cudaStreamWaitEvent(st, g_join_ev[dev], 0);
@@ -812,6 +863,23 @@ extern "C" int solar_attn_bwd(const void* q, const void* k, const void* v, const
                               long long do_ss, long long do_sb, float scale, int* status, void* stream) {
   return attn_bwd_impl(q, k, v, o, dout, lse, dq, dk, dv, scratch, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss,
                        v_sb, o_ss, o_sb, do_ss, do_sb, scale, status, stream, g_bwd_overlap, nullptr);
+}
+
+// Backward under a structured mask (see solar_attn_fwd_masked): row_ranges [Sq][6] are per query; dkv_* lists, for
+// every block of 128 keys, the 64-query tiles that see any of them; dq_* lists, for every block of 128 queries, the
+// 64-key tiles they see.  Bit 30 of a list entry marks a tile that contains a masked (query, key) pair.
+extern "C" int solar_attn_bwd_masked(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                     const float* lse, void* dq, void* dk, void* dv, float* scratch, int B, int Sq,
+                                     int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
+                                     long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
+                                     long long do_ss, long long do_sb, float scale, int* status, void* stream,
+                                     const int* row_ranges, const int* dkv_list, const int* dkv_count, int dkv_stride,
+                                     const int* dq_list, const int* dq_count, int dq_stride) {
+  if (!row_ranges || !dkv_list || !dkv_count || !dq_list || !dq_count || dkv_stride < 1 || dq_stride < 1)
+    return fail("masked attention backward: the mask tables are required%s");
+  AttnMask mkv{row_ranges, dkv_list, dkv_count, dkv_stride}, mq{row_ranges, dq_list, dq_count, dq_stride};
+  return attn_bwd_impl(q, k, v, o, dout, lse, dq, dk, dv, scratch, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss,
+                       v_sb, o_ss, o_sb, do_ss, do_sb, scale, status, stream, g_bwd_overlap, nullptr, &mkv, &mq);
 }
 
 // The same computation with all three kernels on the caller's stream whatever the tail-overlap switch says: no

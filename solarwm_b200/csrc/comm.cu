@@ -112,6 +112,39 @@ __global__ void __launch_bounds__(256) comm_gather_kernel(uint4* __restrict__ ds
   }
 }
 
+// Head exchange of up to three [rows, P * width] matrices (q, k, v after their per-head transforms) as peer stores:
+// column block d of every local row goes to rank d, at row `dst_row[t] + r` of that rank's destination t.  The
+// destinations may be different buffers with different leading dimensions -- k and v typically land straight in the
+// peers' KV caches (an in-place cache append over NVLink), q in an exchange buffer.  The last CTA signals every peer.
+struct ScatterColsSeg {
+  const uint4* src; long long src_ld16;      // source row stride in 16-byte units
+  PeerTable dst; long long dst_ld16; long long dst_row; long long dst_col16;
+};
+struct ScatterColsParams {
+  ScatterColsSeg seg[3];
+  int n_seg, n_ranks;
+  long long rows;
+  int width16;                               // 16-byte units per destination column block
+  PeerFlags flags;
+};
+__global__ void __launch_bounds__(256) comm_scatter_cols_kernel(const __grid_constant__ ScatterColsParams p) {
+  const long long per_seg = p.rows * p.n_ranks * p.width16;
+  const long long total = per_seg * p.n_seg;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / per_seg);
+    long long k = i - t * per_seg;
+    const int c = static_cast<int>(k % p.width16);
+    k /= p.width16;
+    const int d = static_cast<int>(k % p.n_ranks);
+    const long long r = k / p.n_ranks;
+    const ScatterColsSeg& sg = p.seg[t];
+    const uint4 v = sg.src[r * sg.src_ld16 + static_cast<long long>(d) * p.width16 + c];
+    static_cast<uint4*>(sg.dst.base[d])[(sg.dst_row + r) * sg.dst_ld16 + sg.dst_col16 + c] = v;
+  }
+  cta_done_signal_peers(p.flags);
+}
+
 __global__ void comm_signal_kernel(PeerFlags flags) {
   if (threadIdx.x == 0 && blockIdx.x == 0) signal_all_peers(flags);
 }
@@ -264,6 +297,40 @@ extern "C" int solar_comm_gather(void* dst, void* const* src_bases, int n_ranks,
   const long long cap = max_ctas > 0 ? max_ctas : 4LL * sm_count();
   if (grid > cap) grid = cap;
   comm_gather_kernel<<<(unsigned)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(dst), t, n16);
+  SOLAR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// n_seg (1..3) matrices src[t] [rows, n_ranks * width] bf16 (row stride src_ld[t] elements): column block d of every
+// row is stored at dst_bases[t * n_ranks + d] + ((dst_row[t] + r) * dst_ld[t] + dst_col[t]) elements.  All sizes in
+// elements of 2 bytes; width, strides and column offsets must be multiples of 8.  One signal per rank and call.
+extern "C" int solar_comm_scatter_cols(int n_seg, const void* const* src, const long long* src_ld, long long rows,
+                                       int width, void* const* dst_bases, const long long* dst_ld,
+                                       const long long* dst_row, const long long* dst_col, int n_ranks,
+                                       void* const* flag_ptrs, unsigned* counter, int max_ctas, void* stream) {
+  if (n_seg < 1 || n_seg > 3) return fail("comm scatter: 1..3 matrices%s");
+  if (n_ranks < 1 || n_ranks > kMaxPeers) return fail("comm: peer count out of range%s");
+  if (rows <= 0 || width <= 0 || width % 8) return fail("comm scatter: width must be a positive multiple of 8%s");
+  ScatterColsParams p;
+  memset(&p, 0, sizeof(p));
+  p.n_seg = n_seg; p.n_ranks = n_ranks; p.rows = rows; p.width16 = width / 8;
+  for (int t = 0; t < n_seg; ++t) {
+    if (src_ld[t] % 8 || dst_ld[t] % 8 || dst_col[t] % 8 || (reinterpret_cast<uintptr_t>(src[t]) & 15))
+      return fail("comm scatter: strides, offsets and pointers must be 16-byte aligned%s");
+    p.seg[t].src = static_cast<const uint4*>(src[t]);
+    p.seg[t].src_ld16 = src_ld[t] / 8;
+    p.seg[t].dst.n = n_ranks;
+    for (int d = 0; d < n_ranks; ++d) p.seg[t].dst.base[d] = dst_bases[t * n_ranks + d];
+    p.seg[t].dst_ld16 = dst_ld[t] / 8;
+    p.seg[t].dst_row = dst_row[t];
+    p.seg[t].dst_col16 = dst_col[t] / 8;
+  }
+  p.flags = make_flags(flag_ptrs, n_ranks, counter);
+  const long long total = rows * n_ranks * p.width16 * n_seg;
+  long long grid = (total + 255) / 256;
+  const long long cap = max_ctas > 0 ? max_ctas : 2LL * sm_count();
+  if (grid > cap) grid = cap;
+  comm_scatter_cols_kernel<<<(unsigned)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   SOLAR_CUDA_OK(cudaGetLastError());
   return 0;
 }

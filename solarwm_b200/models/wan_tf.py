@@ -26,10 +26,32 @@ from .wan import WanDiT, rope_table
 from .wan_causal import teacher_forcing_attention
 
 
+_MASKS: dict = {}
+
+
+def _cached_mask(kind: str, *key):
+    """Structured masks are pure functions of their geometry: build each once (tables are cached per device inside)."""
+    from ..ops import attention_mask as am
+
+    if (kind, key) not in _MASKS:
+        _MASKS[(kind, key)] = am.block_causal_mask(*key) if kind == "causal" else am.teacher_forcing_segment_mask(*key)
+    return _MASKS[(kind, key)]
+
+
+def _masked_kernel_ok(q) -> bool:
+    return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and ops.get_backend() == "native"
+
+
 def block_causal_attention(q, k, v, *, frame_tokens: int, chunk_frames: int, window_chunks: int,
                            sink_frames: int = 0):
-    """Chunk i attends sink + chunks max(0, i-W) .. i of the same sequence; tensors [1, L, H, D]."""
+    """Chunk i attends sink + chunks max(0, i-W) .. i of the same sequence; tensors [1, L, H, D].  On the device this
+    is ONE masked flash-attention call (per-row key ranges, tiles outside the window skipped); the chunk loop below is
+    the CPU form of the same rule."""
     ct = chunk_frames * frame_tokens
+    if _masked_kernel_ok(q):
+        from ..ops.attention_mask import masked_attention
+
+        return masked_attention(q, k, v, _cached_mask("causal", q.shape[1], ct, window_chunks, sink_frames * frame_tokens))
     n = (q.shape[1] + ct - 1) // ct
     sink = sink_frames * frame_tokens
     outs = []
@@ -110,6 +132,11 @@ def forward_teacher_forcing(model: WanDiT, clean, noisy, t, context, *, r: Optio
         L = f * ft
         if capture is not None and len(capture) < len(model.blocks):      # a checkpoint recompute must not append again
             capture.append((k[:, :L].detach(), v[:, :L].detach()))
+        if _masked_kernel_ok(q):
+            # one masked kernel over the whole [clean | noisy] sequence: no per-chunk launches, no key concatenation
+            from ..ops.attention_mask import masked_attention
+
+            return masked_attention(q, k, v, _cached_mask("tf", L, chunk_frames * ft, window_chunks, sink_frames * ft, 0))
         oc, on = teacher_forcing_attention(q[:, :L], k[:, :L], v[:, :L], q[:, L:], k[:, L:], v[:, L:],
                                            frame_tokens=ft, chunk_frames=chunk_frames,
                                            window_chunks=window_chunks, sink_frames=sink_frames)

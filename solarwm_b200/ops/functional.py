@@ -65,12 +65,43 @@ def _rowmajor(t: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------
 # GEMM
 # --------------------------------------------------------------------------------------
+_GEMM_BACKEND = "native"
+
+
+def set_gemm_backend(name: str) -> str:
+    """``native``: this library's tcgen05 kernels (default).  ``library``: ``torch.matmul`` (cuBLAS) with the bias /
+    activation / accumulate steps as separate torch ops -- only for A/B baselines (``bench.py --impl baseline``); the
+    fused-exchange entry points always run the native kernels.  Returns the previous setting."""
+    global _GEMM_BACKEND
+    if name not in ("native", "library"):
+        raise ValueError("gemm backend must be 'native' or 'library'")
+    previous, _GEMM_BACKEND = _GEMM_BACKEND, name
+    return previous
+
+
 def gemm(a, b, layout=NT, *, bias=None, act=None, out=None, out_dtype=None, accumulate=False,
          max_ctas=0):
     """C = op(A) op(B) with bf16 operands and fp32 accumulation.
 
     layout NT: a [M,K], b [N,K];  NN: a [M,K], b [K,N];  TN: a [K,M], b [K,N].
     """
+    if a.is_cuda and _GEMM_BACKEND == "library":
+        c = a @ b.t() if layout == NT else (a @ b if layout == NN else a.t() @ b)
+        count("library_gemm")
+        if bias is not None:
+            c = c + bias
+        if act == "gelu":
+            c = torch.nn.functional.gelu(c, approximate="tanh")
+        elif act == "swiglu":
+            g, u = c.view(c.shape[0], -1, 2, 64).unbind(2)
+            c = (torch.nn.functional.silu(g.float()) * u.float()).reshape(c.shape[0], -1).to(c.dtype)
+        if out is not None:
+            if accumulate:
+                out.add_(c.to(out.dtype))
+            else:
+                out.copy_(c)
+            return out
+        return c.to(out_dtype) if out_dtype is not None else c
     if not a.is_cuda:
         af, bf = a.float(), b.float()
         c = af @ bf.t() if layout == NT else (af @ bf if layout == NN else af.t() @ bf)

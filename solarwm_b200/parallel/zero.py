@@ -85,8 +85,9 @@ class ZeroAdamW(FlatAdamW):
             if heap is None:
                 raise ValueError("the fused transport needs a SymmetricHeap")
             for i, u in enumerate(units):
-                u.ensure_grads()
                 k = None if self.param_shards is None else self.param_shards.index_of(u)
+                if k is None:
+                    u.ensure_grads()
                 flat_v, off_pv = heap.alloc((u.numel_v,), u.flat_v.dtype)
                 grad_v, off_gv = heap.alloc((u.numel_v,), torch.float32)
                 if k is None:
@@ -104,8 +105,7 @@ class ZeroAdamW(FlatAdamW):
                         if u.slots[name].is_vector:
                             prm.data = u.view(name)
                     grad_v.zero_()
-                    u.grad_v = grad_v
-                    u.ensure_grads()
+                    u.grad_v = grad_v            # the matrix gradients come from the shared slots at ``attach``
                     off_p = self.param_shards.shard_off[k]
                     off_g = self.param_shards.gbuf_off[self.param_shards.slot_of(k)]
                 self._heap_off[i] = {"m": (off_p, off_g), "v": (off_pv, off_gv)}

@@ -51,6 +51,10 @@ class H3StreamConfig:
     memory_latents: int = 0            # capacity of the retrieved-memory segment (0 = no memory rows)
     memory_adapter: Optional[str] = None   # adapter bank active while memory rows are installed (fill and query
                                        # evaluations); without memory rows the primary adapter serves
+    sp_exchange: str = "fused"         # SP > 1 on CUDA: "fused" = this library's NVLink kernels (k / v rows are stored
+                                       # straight into the peers' KV caches, the evaluation is graph-capturable);
+                                       # "collective" = NCCL all-to-alls (the baseline arm; runs eagerly)
+    max_text_tokens: int = 1536        # sizes the exchange buffers of the fused transport
     seed: int = 0
 
 
@@ -82,6 +86,7 @@ class H3StreamingGenerator:
         self.times = rollout_times(cfg.denoise_steps, cfg.shift)[:cfg.denoise_steps]
         self.timings: List[ChunkTiming] = []
         self._graphs = None
+        self.fx = None                     # parallel.fused_stream.FusedHeadExchange when the fused transport is on
 
     # ------------------------------------------------------------------------------------ scene
     @torch.no_grad()
@@ -133,8 +138,26 @@ class H3StreamingGenerator:
         self.mem_rows = 0
         cap = self.o_cond + self.n_cond + (cfg.window_chunks + 1) * self.chunk_rows
         a_local = self.heads_local * mc.attention_head_dim
-        self.kv = [_LayerKV(torch.zeros(cap, a_local, dtype=dt, device=dev), torch.zeros(cap, a_local, dtype=dt, device=dev))
-                   for _ in m.blocks]
+        if self.P > 1 and cfg.sp_exchange == "fused" and dev.type == "cuda":
+            if self.n_text > cfg.max_text_tokens:
+                raise ValueError(f"{self.n_text} text rows exceed max_text_tokens={cfg.max_text_tokens}")
+            if self.fx is None:
+                from ..parallel.fused_stream import FusedHeadExchange
+
+                cap_max = self.o_cond + cfg.max_text_tokens + rows + (cfg.window_chunks + 1) * self.chunk_rows
+                self.fx = FusedHeadExchange(self.sp.group, heads=mc.num_attention_heads, head_dim=mc.attention_head_dim,
+                                            layers=len(m.blocks), cache_rows=cap_max,
+                                            max_rows=max(self.chunk_rows, cfg.max_text_tokens + rows, self.o_cond),
+                                            out_width=mc.latent_row_dim, dtype=dt)
+            # the KV caches are the exchange's symmetric buffers: peers append their rows in place
+            self.kv = [_LayerKV(k[:cap], v[:cap]) for k, v in zip(self.fx.k_cache, self.fx.v_cache)]
+            for kv in self.kv:
+                kv.k.zero_()
+                kv.v.zero_()
+            self.fx.barrier()
+        else:
+            self.kv = [_LayerKV(torch.zeros(cap, a_local, dtype=dt, device=dev), torch.zeros(cap, a_local, dtype=dt, device=dev))
+                       for _ in m.blocks]
         self.hist_chunks = 0
         self.chunk_index = 0
         self._graphs = None
@@ -188,17 +211,26 @@ class H3StreamingGenerator:
             q = ops.head_norm_rope_prope(blk.to_q(xm), blk.norm_q, cos, sin, cam_q, heads=H, **kw)
             k = ops.head_norm_rope_prope(blk.to_k(xm), blk.norm_k, cos, sin, cam_kv, heads=H, **kw)
             v = ops.head_norm_rope_prope(blk.to_v(xm), None, None, None, cam_kv, heads=H, **kw)
-            q, k, v = (t.view(1, S, H, hd) for t in (q, k, v))
-            if self.P > 1:
-                self.sp.set_layout_rows(1, balanced_lengths(n_rows, self.P))
-                q, k, v = self.sp.scatter_heads(q, k, v, contiguous=False)      # strided views of the exchange buffer
-            kv.k[key_base:key_base + n_rows].view(1, n_rows, hl, hd).copy_(k)     # one strided copy each
-            kv.v[key_base:key_base + n_rows].view(1, n_rows, hl, hd).copy_(v)
-            n_keys = key_hi - key_lo
-            o = ops.attention(q.reshape(1, n_rows, hl, hd), kv.k[key_lo:key_hi].view(1, n_keys, hl, hd),
-                              kv.v[key_lo:key_hi].view(1, n_keys, hl, hd))
-            if self.P > 1:
-                o = self.sp.gather_heads(o)
+            if self.fx is not None:
+                # fused transport: one launch stores q into the exchange buffer and k / v straight into every peer's
+                # cache rows; the attention epilogue returns the output rows to their owners
+                fx = self.fx
+                fx.set_rows(n_rows)
+                par = fx.next_parity()
+                qh = fx.exchange_qkv(q, k, v, bi, key_base, par)
+                o = fx.attention(qh, bi, key_lo, key_hi, 1.0 / (hd ** 0.5), par)
+            else:
+                q, k, v = (t.view(1, S, H, hd) for t in (q, k, v))
+                if self.P > 1:
+                    self.sp.set_layout_rows(1, balanced_lengths(n_rows, self.P))
+                    q, k, v = self.sp.scatter_heads(q, k, v, contiguous=False)      # strided views of the exchange buffer
+                kv.k[key_base:key_base + n_rows].view(1, n_rows, hl, hd).copy_(k)     # one strided copy each
+                kv.v[key_base:key_base + n_rows].view(1, n_rows, hl, hd).copy_(v)
+                n_keys = key_hi - key_lo
+                o = ops.attention(q.reshape(1, n_rows, hl, hd), kv.k[key_lo:key_hi].view(1, n_keys, hl, hd),
+                                  kv.v[key_lo:key_hi].view(1, n_keys, hl, hd))
+                if self.P > 1:
+                    o = self.sp.gather_heads(o)
             o = ops.head_norm_rope_prope(o.reshape(S, H * hd), None, None, None, cam_o, heads=H, **kw)
             x = F_.gated_residual(x, blk.to_out(o), table[:, 2], table=idx)
             xm = F_.norm_modulate(x, table[:, 3], table[:, 4], mode=1, w=blk.norm2, eps=mc.eps, table=idx)
@@ -243,7 +275,10 @@ class H3StreamingGenerator:
         x = F_.linear(self._x_in, self.model.proj_in)
         out = self._evaluate(x, self._t_in, self._pos_cache[first], self._video_tags, self._view_in, key_base=base,
                              n_rows=self.chunk_rows, tables=self._step_tables())
-        if self.P > 1:
+        if self.fx is not None:
+            self.fx.set_rows(self.chunk_rows)
+            out = self.fx.gather_rows(out)
+        elif self.P > 1:
             self.sp.set_layout_rows(1, balanced_lengths(self.chunk_rows, self.P))
             out = self.sp.gather_sequence(out, 1)
         self._out.copy_(out)
@@ -267,6 +302,8 @@ class H3StreamingGenerator:
         cfg, mc = self.cfg, self.model.cfg
         if self.hist_chunks < cfg.window_chunks:
             self.hist_chunks += 1
+            if self.fx is not None:
+                self.fx.barrier()
             return
         a, n = self.o_cond + self.n_cond, cfg.window_chunks * self.chunk_rows
         for kv in self.kv:
@@ -275,6 +312,8 @@ class H3StreamingGenerator:
             kv.k[a:a + n] = ops.head_norm_rope_prope(kv.k[a:a + n], None, self._delta_cos, self._delta_sin, None,
                                                      heads=self.heads_local, rot_dims=mc.rot_dims,
                                                      sections=mc.rope_sections, eps=mc.eps)
+        if self.fx is not None:
+            self.fx.barrier()          # peers append the next chunk's rows into this cache: not before the slide is done
 
     # ------------------------------------------------------------------------------------ memory
     @torch.no_grad()
@@ -378,6 +417,8 @@ class H3StreamingGenerator:
             self._chunk_eval()                       # warm-up on the side stream (allocator, lazy init)
         torch.cuda.current_stream(self.device).wait_stream(s)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        # with several ranks other threads of the process (the collective library's watchdog) make CUDA calls of
+        # their own: only this thread's calls belong to the capture
+        with torch.cuda.graph(g, capture_error_mode="thread_local" if self.P > 1 else "global"):
             self._chunk_eval()
         self._graphs = g

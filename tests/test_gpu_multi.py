@@ -313,3 +313,61 @@ def test_fused_exchanges_uneven_frames_and_graph_replay(tmp_path, world):
         # fetches the third again; the two whole-model reads of the check above gather every block once each
         assert r["gathers"]["eager"] == 0 and r["gathers"]["sharded"] == 5 * 4 + 2 * 3, r
         assert r["sharded_roundtrip"] and r["sharded_graph_roundtrip"], r
+
+
+def _stream_worker(rank, world, port, out_path):
+    """Block-causal streaming at SP = world: the fused head exchange (k / v appended straight into the peers' KV
+    caches, graph replay once the window is full) against the NCCL all-to-all form of the same generator."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=timedelta(seconds=180),
+                            device_id=torch.device("cuda", rank))
+    from solarwm_b200 import ops
+    from solarwm_b200.models.h3 import H3Config, H3DiT
+    from solarwm_b200.parallel.ulysses import UlyssesCollective
+    from solarwm_b200.serve.h3_stream import H3StreamConfig, H3StreamingGenerator
+
+    cfg = H3Config(num_attention_heads=2 * world, attention_head_dim=128, hidden_size=256, num_layers=2, num_refiner_layers=1,
+                   ffn_dim=512, text_dim=64, time_embed_hidden_dim=64, time_embed_dim=128)
+    model = H3DiT(cfg, device="cuda", dtype=torch.bfloat16, seed=0)
+    g = torch.Generator().manual_seed(0)
+    text, anchor = torch.randn(40, cfg.text_dim, generator=g), torch.randn(24, 1, 8, 12, generator=g)
+    result, outs = {}, {}
+    for mode in ("collective", "fused"):
+        scfg = H3StreamConfig(grid_hw=(4, 6), chunk_latents=2, window_chunks=2, denoise_steps=2, sp_exchange=mode,
+                              max_text_tokens=64, use_cuda_graph=mode == "fused", seed=5)
+        gen = H3StreamingGenerator(model, scfg, sp=UlyssesCollective(None))
+        gen.start(text, anchor, torch.eye(4))
+        ops.reset_counters()
+        chunks = []
+        for i in range(5):
+            cams = torch.eye(4).repeat(2, 1, 1)
+            cams[:, 0, 3] = 0.02 * i
+            chunks.append(gen.next_chunk(cams).float().cpu())
+        torch.cuda.synchronize()
+        ops.check_status()
+        outs[mode] = chunks
+        result[f"{mode}_graph"] = [t.graph for t in gen.timings]
+        result[f"{mode}_scatter"] = ops.COUNTERS.get("scatter_cols", 0)
+        dist.barrier()
+        if gen.fx is not None:
+            gen.fx.close()
+    result["max_rel"] = max(((a - b).norm() / b.norm()).item() for a, b in zip(outs["fused"], outs["collective"]))
+    result["finite"] = bool(all(torch.isfinite(c).all() for c in outs["fused"]))
+    torch.save(result, f"{out_path}.{rank}")
+    dist.destroy_process_group()
+
+
+def test_fused_stream_exchange_matches_collective_and_replays_as_a_graph(tmp_path):
+    _need_two()
+    import torch.multiprocessing as mp
+
+    out = str(tmp_path / "stream")
+    mp.spawn(_stream_worker, args=(2, 29577, out), nprocs=2, join=True)
+    for rank in range(2):
+        r = torch.load(f"{out}.{rank}", weights_only=True)
+        assert r["finite"] and r["max_rel"] < 2e-2, r
+        assert r["fused_graph"] == [False, False, True, True, True] and not any(r["collective_graph"]), r
+        assert r["fused_scatter"] > 0 and r["collective_scatter"] == 0, r
