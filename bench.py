@@ -429,10 +429,14 @@ def run_infer(args):
     text_host = torch.randn(1, cfg.text_len, cfg.text_dim, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
     out_host = torch.empty(1, cfg.out_dim, args.frames, args.height, args.width, dtype=torch.bfloat16).pin_memory()
 
+    # the network evaluation is replayed from a CUDA graph unless a library collective sits inside it
+    graph_state = {} if (args.graph != "off" and (world == 1 or args.sp_transport == "fused")) else None
+
     def one_sample():
         text = text_host.to(f"cuda:{local}", non_blocking=True)
         with torch.no_grad():
-            x = sample(model, text, frames=args.frames, height=args.height, width=args.width, steps=args.sample_steps, seed=3)
+            x = sample(model, text, frames=args.frames, height=args.height, width=args.width, steps=args.sample_steps,
+                       seed=3, graph=graph_state)
         out_host.copy_(x, non_blocking=True)
 
     for _ in range(max(args.warmup, 3)):
@@ -457,7 +461,7 @@ def run_infer(args):
             "config": {"model": args.model, "solver": f"Euler, {args.sample_steps} steps, linear sigma grid", "seq_len": tokens,
                        "latent": [1, cfg.out_dim, args.frames, args.height, args.width], "text": [1, cfg.text_len, cfg.text_dim],
                        "parallelism": f"sp{world}", "sp_transport": args.sp_transport if world > 1 else "none",
-                       "attention_backend": ops.get_backend(),
+                       "attention_backend": ops.get_backend(), "cuda_graph_forward": graph_state is not None,
                        "gemm_backend": "library (cuBLAS)" if args.impl == "baseline" else "native",
                        "l2": "no flush: 2 B parameters (4 GB) are re-read every solver step"},
             "clocks": clocks,

@@ -62,19 +62,58 @@ class LTXTrainer:
         return loss.detach()
 
 
+class GraphedForward:
+    """``model(x, t, text)`` as one replayed CUDA graph for a fixed clip geometry: the solver's evaluations all have
+    the same shapes, so the network is captured once (after an eager warm-up evaluation on a side stream) and every
+    later evaluation is a copy into the static inputs plus a replay -- no per-kernel launch cost on the host, which
+    is what bounds a 2 B-parameter network on a few thousand tokens.  Works at SP > 1 when the model's exchanges are
+    the fused ones (no library collective inside the forward); the caller keeps one instance per geometry."""
+
+    def __init__(self, model, x, t, text):
+        self.model = model
+        self.x, self.t, self.text = x.clone(), t.clone(), text.clone()
+        side = torch.cuda.Stream(device=x.device)
+        side.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(side), torch.no_grad():
+            model(self.x, self.t, self.text)
+        torch.cuda.current_stream(x.device).wait_stream(side)
+        torch.cuda.synchronize(x.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"), torch.no_grad():
+            self.out = model(self.x, self.t, self.text)
+
+    def matches(self, x, t, text) -> bool:
+        return x.shape == self.x.shape and t.shape == self.t.shape and text.shape == self.text.shape
+
+    def __call__(self, x, t, text):
+        self.x.copy_(x)
+        self.t.copy_(t)
+        if text.data_ptr() != self.text.data_ptr():
+            self.text.copy_(text)
+        self.graph.replay()
+        return self.out
+
+
 @torch.no_grad()
-def sample(model, text, *, frames, height, width, steps=8, seed=0, first_frame=None):
-    """Euler sampler on the linear sigma grid 1 -> 0 (one-stage LTX sampler)."""
+def sample(model, text, *, frames, height, width, steps=8, seed=0, first_frame=None, graph=None):
+    """Euler sampler on the linear sigma grid 1 -> 0 (one-stage LTX sampler).  ``graph``: a dict the caller keeps
+    between calls; when given (CUDA only) the network evaluation is captured once per geometry and replayed."""
     dev = next(model.parameters()).device
     g = torch.Generator(device=dev).manual_seed(int(seed))
     x = torch.randn(1, model.cfg.out_dim, frames, height, width, generator=g, device=dev).to(model.dtype)
     sig = torch.linspace(1.0, 0.0, steps + 1, device=dev)
+    evaluate = model
     for i in range(steps):
         t = sig[i].expand(1, frames).clone()
         if first_frame is not None:
             x[:, :, 0] = first_frame
             t[:, 0] = 0.0
-        v = model(x, t * 1000.0, text)
+        if graph is not None and dev.type == "cuda" and not torch.is_grad_enabled():
+            runner = graph.get("runner")
+            if runner is None or not runner.matches(x, t, text):
+                runner = graph["runner"] = GraphedForward(model, x, t * 1000.0, text)
+            evaluate = runner
+        v = evaluate(x, t * 1000.0, text)
         x = (x.float() + (sig[i + 1] - sig[i]) * v.float()).to(x.dtype)
     if first_frame is not None:
         x[:, :, 0] = first_frame
