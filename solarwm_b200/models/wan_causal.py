@@ -1,11 +1,18 @@
 """Block-causal (chunk-wise autoregressive) execution of the Wan DiT with a rolling KV cache.
 
-Per transformer block the cache holds, for every cached token, the *normalised but un-rotated*
-key and the value: ``[sink frames | local window | current chunk]``.  RoPE is applied when the
-cache is read, with window-relative frame positions (sink first, then the window, then the chunk),
-so a rollout longer than the training length keeps seeing positions it was trained on -- the
-reference's block-relative re-basing (solar/backends/wan22/runtime/modeling/causal_model.py:
-657-876, 1028-1235, 1948-2088).
+Per transformer block the cache holds, for every cached token, the normalised AND ROTATED key and
+the value: ``[sink frames | local window | current chunk]``.  Keys are written once with the RoPE of
+the position they have at that moment; a denoising evaluation therefore reads the window as it is
+(no pass over the cached keys per layer and step).  Positions follow the reference's re-basing rule
+(solar/backends/wan22/runtime/modeling/causal_model.py:88-220, 657-876, 1028-1235, 1948-2088): sink
+frames keep positions ``0 ..``; the newest frame sits at ``min(absolute index, position_cap - 1)`` and
+the window counts down from there, so a rollout longer than the training length keeps seeing positions
+it was trained on.  ``position_cap`` is the cache capacity by default (window-relative positions), the
+training length for block-relative RoPE, or a finite ``pmax`` for EchoRoPE.  When the rule moves the
+history (the window slides, or the cap is reached) the cached window keys are re-based by ONE delta
+rotation per chunk -- RoPE rotations compose and only the temporal pairs move -- fused with the
+window shift.  ``rope_at_read=True`` keeps the original form (un-rotated keys, RoPE at every read) as
+the oracle the tests compare against.
 
 Differences from the reference, on purpose:
   * a forward with ``commit=False`` (the denoising steps of a chunk) writes the chunk's K/V into the
@@ -52,6 +59,13 @@ class KVCache:
     total_frames: int = 0              # frames generated so far (absolute)
     grid_hw: tuple = (0, 0)
     cam_inv: Optional[torch.Tensor] = None   # [capacity_frames, 4, 4] P^-1 of every cached frame (camera runs)
+    position_cap: int = 0              # the newest frame's RoPE position never exceeds position_cap - 1
+    newest_pos: int = -1               # position the newest committed non-sink frame was rotated to
+
+    @property
+    def positions_saturated(self) -> bool:
+        """The newest position has reached the cap: from here on every chunk moves the history by its own length."""
+        return self.total_frames >= self.position_cap - self.chunk_frames
 
     @property
     def capacity_frames(self) -> int:
@@ -59,7 +73,10 @@ class KVCache:
 
 
 def allocate_kv_cache(model: WanDiT, *, grid_hw, chunk_frames: int, window_frames: Optional[int] = None,
-                      sink_frames: Optional[int] = None, heads_local: Optional[int] = None, device=None) -> KVCache:
+                      sink_frames: Optional[int] = None, heads_local: Optional[int] = None, device=None,
+                      position_cap: Optional[int] = None) -> KVCache:
+    """``position_cap``: RoPE positions of the newest frame are clamped to ``position_cap - 1`` (default: the cache
+    capacity in frames = window-relative positions; pass the training length for block-relative RoPE)."""
     cfg = model.cfg
     h, w = grid_hw
     ft = h * w
@@ -72,16 +89,56 @@ def allocate_kv_cache(model: WanDiT, *, grid_hw, chunk_frames: int, window_frame
     cap = (sink + window + chunk_frames) * ft
     layers = [LayerCache(torch.zeros(cap, dim_local, dtype=model.dtype, device=dev),
                          torch.zeros(cap, dim_local, dtype=model.dtype, device=dev)) for _ in model.blocks]
-    return KVCache(layers, ft, sink, window, chunk_frames, grid_hw=(h, w))
+    cap_frames = sink + window + chunk_frames
+    if position_cap is not None and position_cap < cap_frames:
+        raise ValueError(f"position_cap {position_cap} is below the cache capacity of {cap_frames} frames")
+    return KVCache(layers, ft, sink, window, chunk_frames, grid_hw=(h, w),
+                   position_cap=cap_frames if position_cap is None else int(position_cap))
 
 
 class CausalWanRunner:
     """Chunk-by-chunk forward of a ``WanDiT`` against a ``KVCache`` (inference; no autograd)."""
 
-    def __init__(self, model: WanDiT, sp=None):
+    def __init__(self, model: WanDiT, sp=None, rope_at_read: bool = False):
         self.model = model
         self.sp = sp
+        self.rope_at_read = bool(rope_at_read)
         self._rope_cache = {}
+
+    # -- positions ------------------------------------------------------------------------------------------------
+    @staticmethod
+    def chunk_first_position(cache: KVCache, f: int) -> int:
+        """RoPE position of the first frame of the chunk that comes next (absolute until the cap, then clamped)."""
+        a0 = cache.total_frames
+        if a0 + f <= cache.sink_frames:
+            return a0
+        return min(a0 + f - 1, cache.position_cap - 1) - f + 1
+
+    def _delta_table(self, n_tokens: int, delta_frames: int, device):
+        """(cos, sin) per token that rotates the temporal RoPE pairs by ``delta_frames`` positions and leaves the
+        spatial pairs alone."""
+        key = ("delta", n_tokens, delta_frames, str(device))
+        if key not in self._rope_cache:
+            from .wan import rope_axis_dims
+
+            hd = self.model.cfg.head_dim
+            cf, ch, cw = rope_axis_dims(hd)
+            inv = 1.0 / torch.pow(10000.0, torch.arange(0, 2 * cf, 2, dtype=torch.float64) / (2 * cf))
+            ang = torch.cat([float(delta_frames) * inv, torch.zeros(ch + cw, dtype=torch.float64)])
+            tab = torch.stack([torch.cos(ang), torch.sin(ang)], -1).to(torch.float32)
+            self._rope_cache[key] = tab.unsqueeze(0).expand(n_tokens, -1, -1).contiguous().to(device)
+        return self._rope_cache[key]
+
+    def _rebase_window(self, cache: KVCache, delta_frames: int) -> None:
+        """Move the cached (non-sink) window keys by ``delta_frames`` positions: one rotation pass per layer."""
+        ft = cache.frame_tokens
+        a = cache.sink_frames * ft
+        b = cache.committed_frames * ft
+        if b > a and delta_frames != 0:
+            tab = self._delta_table(b - a, delta_frames, cache.layers[0].k.device)
+            for lc in cache.layers:
+                lc.k[a:b] = F_.rmsnorm_rope(lc.k[a:b], None, tab, no_norm=True)
+        cache.newest_pos += delta_frames
 
     def _rope(self, frames, hw, device, first=0):
         key = (frames, hw, first, str(device))
@@ -122,8 +179,17 @@ class CausalWanRunner:
         D, H, hd = cfg.dim, cfg.num_heads, cfg.head_dim
         ctx_frames = cache.committed_frames
         n_ctx, n_new = ctx_frames * ft, f * ft
-        rope_all = self._rope(ctx_frames + f, (h, w), xs.device)
-        rope_q = rope_all[n_ctx:]
+        if self.rope_at_read:
+            rope_all = self._rope(ctx_frames + f, (h, w), xs.device)
+            rope_q = rope_all[n_ctx:]
+        else:
+            # keys are cached rotated: bring the history to where this chunk expects it (a no-op in the steady state,
+            # where the commit of the previous chunk already did it), then rotate only the new rows
+            first = self.chunk_first_position(cache, f)
+            if ctx_frames > cache.sink_frames and cache.newest_pos != first - 1:
+                self._rebase_window(cache, first - 1 - cache.newest_pos)
+            rope_all = None
+            rope_q = self._rope(f, (h, w), xs.device, first=first)
         sp = self.sp
         P = 1 if sp is None else sp.size
         hl = H // P
@@ -147,7 +213,8 @@ class CausalWanRunner:
             xm = F_.norm_modulate(xs, mod[:, 0], mod[:, 1], mode=0, eps=cfg.eps, **gk)
             qkv = blk._fused_linear(xm, "self_attn.q", "self_attn.v", 3 * D)
             q = F_.rmsnorm_rope(qkv[:, :D], blk._p("self_attn.norm_q.weight").float(), rope_q, eps=cfg.eps)
-            k_raw = F_.rmsnorm_rope(qkv[:, D:2 * D], blk._p("self_attn.norm_k.weight").float(), None, eps=cfg.eps)
+            k_raw = F_.rmsnorm_rope(qkv[:, D:2 * D], blk._p("self_attn.norm_k.weight").float(),
+                                    None if self.rope_at_read else rope_q, eps=cfg.eps)
             cs = slice(h0 * hd, (h0 + hl) * hd)
             v_new = qkv[:, 2 * D:][:, cs]
             q_loc = q[:, cs]
@@ -156,7 +223,8 @@ class CausalWanRunner:
                 v_new = camera_prope.apply(v_new.contiguous(), cam[1], hl)       # values are cached transformed
             lc.k[n_ctx:n_ctx + n_new] = k_raw[:, cs]
             lc.v[n_ctx:n_ctx + n_new] = v_new
-            k_all = F_.rmsnorm_rope(lc.k[:n_ctx + n_new], None, _head_slice(rope_all, None), no_norm=True)
+            k_all = F_.rmsnorm_rope(lc.k[:n_ctx + n_new], None, rope_all, no_norm=True) if self.rope_at_read \
+                else lc.k[:n_ctx + n_new]
             if cam is not None:
                 k_all = camera_prope.apply(k_all, cam[3], hl)                    # after RoPE, each key with its own camera
             o = ops.attention(q_loc.reshape(1, n_new, hl, hd), k_all.view(1, n_ctx + n_new, hl, hd),
@@ -183,6 +251,8 @@ class CausalWanRunner:
         xh = F_.norm_modulate(xs, hm[:, 0], hm[:, 1], mode=0, eps=cfg.eps, rows_per_group=ft)
         out = m.unpatchify(F_.linear(xh, P_["head.head.weight"], P_["head.head.bias"]), 1, (f, h, w))
         if commit:
+            if not self.rope_at_read and cache.total_frames + f > cache.sink_frames:
+                cache.newest_pos = self.chunk_first_position(cache, f) + f - 1
             self._commit(cache, f)
         return out
 
@@ -203,10 +273,12 @@ class CausalWanRunner:
                 fs, fk = cache.sink_frames, keep // ft
                 cache.cam_inv[fs:fs + fk] = cache.cam_inv[fs + extra:fs + extra + fk].clone()
             cache.committed_frames = limit
-
-
-def _head_slice(rope, _):
-    return rope
+        if not self.rope_at_read and cache.committed_frames > cache.sink_frames:
+            # re-base now for the chunk that comes next (assumed to have this chunk's length), so that a captured
+            # commit contains the rotation and the next evaluations read the window as it is
+            nxt = self.chunk_first_position(cache, f)
+            if cache.newest_pos != nxt - 1:
+                self._rebase_window(cache, nxt - 1 - cache.newest_pos)
 
 
 def teacher_forcing_attention(q_clean, k_clean, v_clean, q_noisy, k_noisy, v_noisy, *, frame_tokens: int,

@@ -106,12 +106,12 @@ class StreamingGenerator:
         g["denoise"] = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g["denoise"]):
             g["v"] = self.runner.forward_chunk(self.cache, g["x"], g["t"], commit=False)
-        frames_before = (self.cache.committed_frames, self.cache.total_frames)
+        frames_before = (self.cache.committed_frames, self.cache.total_frames, self.cache.newest_pos)
         g["commit"] = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g["commit"]):
             self.runner.forward_chunk(self.cache, g["x"], g["t"], commit=True)
         # capture ran the host-side bookkeeping once without running the kernels: undo it
-        self.cache.committed_frames, self.cache.total_frames = frames_before
+        self.cache.committed_frames, self.cache.total_frames, self.cache.newest_pos = frames_before
         return g
 
     def _chunk_graph(self, f):
@@ -136,7 +136,9 @@ class StreamingGenerator:
         """Generate the next chunk of clean latents [1, C, f, H, W]."""
         c, cache = self.cfg, self.cache
         f = c.chunk_frames
-        full = cache.committed_frames == cache.sink_frames + cache.window_frames
+        # graphs are captured once the window is full AND the position rule has reached its cap: only then does
+        # every chunk run the same program (same shapes, same re-basing rotation at commit)
+        full = cache.committed_frames == cache.sink_frames + cache.window_frames and cache.positions_saturated
         use_graph = c.use_cuda_graphs and self.device.type == "cuda" and full
         if use_graph and self._graphs is None:
             self._graphs = self._capture(f)

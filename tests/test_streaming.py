@@ -182,3 +182,49 @@ def test_wan_codec_adapters_btchw_contract_and_streaming_chunks():
     x0 = flow_to_x0(x_t, v, torch.tensor([0.25, 0.5]))
     assert x0.dtype == torch.bfloat16
     assert torch.allclose(x0.float(), (x_t.double() - torch.tensor([0.25, 0.5]).view(2, 1, 1).double() * v.double()).float(), atol=2e-2)
+
+
+def test_rotated_key_cache_equals_rope_at_read_over_a_long_rollout():
+    """Keys cached after RoPE and re-based by one delta rotation per chunk give the same predictions as the original
+    form (un-rotated keys, RoPE over the whole window at every read), through the fill phase, the sliding window with a
+    sink, and -- with a larger position cap (block-relative RoPE) -- through the stretch where positions are still
+    absolute and the point where they saturate."""
+    m = _model()
+    g = torch.Generator().manual_seed(3)
+    ctx = torch.randn(1, 32, 256, generator=g)
+    chunks = [torch.randn(1, 16, 2, 8, 8, generator=g) for _ in range(8)]
+    for cap in (None, 11):
+        outs = {}
+        for at_read in (True, False):
+            runner = CausalWanRunner(m, rope_at_read=at_read)
+            cache = allocate_kv_cache(m, grid_hw=(4, 4), chunk_frames=2, window_frames=6, sink_frames=2,
+                                      position_cap=None if at_read else cap)
+            runner.encode_text(cache, ctx)
+            got = []
+            for i, x in enumerate(chunks):
+                t = torch.full((1, 2), 300.0 + 50 * i)
+                got.append(runner.forward_chunk(cache, x, t, commit=False))      # a denoise step leaves the cache alone
+                runner.forward_chunk(cache, x, torch.zeros(1, 2), commit=True)
+            outs[at_read] = got
+            assert cache.committed_frames == 6 and cache.total_frames == 16
+        if cap is None:
+            for a, b in zip(outs[True], outs[False]):
+                assert torch.allclose(a, b, atol=2e-4, rtol=1e-4)
+        else:
+            # with the larger cap positions differ from the window-relative ones once the window slides, but stay equal
+            # while nothing has been evicted (first three chunks) ...
+            for a, b in zip(outs[True][:3], outs[False][:3]):
+                assert torch.allclose(a, b, atol=2e-4, rtol=1e-4)
+            # ... and the newest position ends clamped at cap - 1
+            assert cache.newest_pos == 11 - 1 - 2 and cache.positions_saturated
+
+
+def test_block_relative_positions_follow_the_rule():
+    m = _model()
+    cache = allocate_kv_cache(m, grid_hw=(4, 4), chunk_frames=3, window_frames=9, sink_frames=3, position_cap=21)
+    first = []
+    for _ in range(9):
+        first.append(CausalWanRunner.chunk_first_position(cache, 3))
+        cache.total_frames += 3
+    # absolute positions until the newest frame would pass cap - 1 = 20, then clamped (top-aligned)
+    assert first == [0, 3, 6, 9, 12, 15, 18, 18, 18]
