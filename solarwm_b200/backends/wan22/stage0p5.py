@@ -177,7 +177,8 @@ class WanStage0p5Trainer:
         txt = batch["text"].to(dev, non_blocking=True)
         y = batch.get("y")
         y = None if y is None else y.to(dev, non_blocking=True)
-        loss = self.microbatch(lat, txt, y, batch.get("t_video"))
+        extra = {} if batch.get("t_video") is None else {"t_video": batch["t_video"]}
+        loss = self.microbatch(lat, txt, y, **extra)        # (stage trainers that draw their own times take no t_video)
         self.optimizer_step()
         return loss
 
@@ -210,7 +211,7 @@ class WanStage0p5Trainer:
             dev = self.device
             loss = self.microbatch(batch["latents"].to(dev, non_blocking=True), batch["text"].to(dev, non_blocking=True),
                                    None if batch.get("y") is None else batch["y"].to(dev, non_blocking=True),
-                                   batch.get("t_video"))
+                                   **({} if batch.get("t_video") is None else {"t_video": batch["t_video"]}))
             self.optimizer_step()
             return loss
         opt = self.optimizer
@@ -231,7 +232,7 @@ class WanStage0p5Trainer:
             counted = dict(ops.COUNTERS)
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 loss = self.microbatch(st["inputs"]["latents"], st["inputs"]["text"], st["inputs"].get("y"),
-                                       st["inputs"].get("t_video"))
+                                       **({} if "t_video" not in st["inputs"] else {"t_video": st["inputs"]["t_video"]}))
                 norm = self.optimizer_step()
             self.global_step = step_before
             # the launch counters advanced while capturing although nothing ran: take that back, and add the same
