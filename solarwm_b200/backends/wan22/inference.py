@@ -18,27 +18,116 @@ from ...runtime.output_layout import output_root, public_validation_dir
 from ...runtime.randomness import stable_validation_seed
 
 
+def _velocity(model, x, timestep: float, text, anchor):
+    """One network evaluation at a uniform noise level; with an anchor, frame 0 is clean (timestep 0, the given
+    latent) and its velocity is dropped."""
+    frames = x.shape[1]
+    t = torch.full((1, frames), float(timestep), device=x.device, dtype=torch.float32)
+    if anchor is not None:
+        x[:, 0] = anchor
+        t[:, 0] = 0.0
+    v = model(x.permute(0, 2, 1, 3, 4), t, text).permute(0, 2, 1, 3, 4).contiguous()
+    if anchor is not None:
+        v[:, 0] = 0
+    return v
+
+
 @torch.no_grad()
-def sample_bidirectional(model, text, *, frames, height, width, steps=8, shift=5.0, seed=0, first_frame=None):
+def sample_bidirectional(model, text, *, frames, height, width, steps=50, shift=5.0, seed=0, first_frame=None,
+                         solver="unipc"):
+    """Denoise ``[1, frames, C, height, width]`` latents from seeded noise.  ``solver`` is ``"unipc"`` (the second-order
+    multistep predictor-corrector on the pinned shifted grid, the validation default at 50 steps) or ``"euler"``
+    (first-order flow steps through the fused update kernel).  ``first_frame`` anchors latent frame 0 (text+image
+    conditioning of the 5B family): it enters every evaluation clean and is restored after every step (reference:
+    CudaWanGenerationAdapter._bidirectional, solar/backends/wan22/runtime/inference.py:1647-1712)."""
     dev = next(model.parameters()).device
     cfg = model.cfg
-    sched = FlowMatchScheduler(shift=shift)
-    sched.set_timesteps(steps)
-    sig = torch.cat([sched.sigmas, torch.zeros(1)]).to(dev)
     g = torch.Generator(device=dev).manual_seed(int(seed))
     x = torch.randn(1, frames, cfg.out_dim, height, width, generator=g, device=dev).to(model.dtype)
-    for i in range(steps):
-        s = sig[i].expand(frames).clone()
-        s_next = sig[i + 1].expand(frames).clone()
-        t = (s * 1000.0).view(1, frames).clone()
-        if first_frame is not None:
-            x[:, 0] = first_frame
-            t[:, 0] = 0.0
-        v = model(x.permute(0, 2, 1, 3, 4), t, text).permute(0, 2, 1, 3, 4).contiguous()
-        x = ops.euler_step(x.reshape(frames, -1), v.reshape(frames, -1), s.float(), s_next.float()).view_as(x)
-    if first_frame is not None:
-        x[:, 0] = first_frame
-    return x, [float(v) for v in sig.tolist()]
+    anchor = None if first_frame is None else first_frame.to(dev, model.dtype)
+    if solver == "unipc":
+        from ...engine.unipc import FlowUniPC
+
+        unipc = FlowUniPC(int(steps), float(shift))
+        for i in range(int(steps)):
+            v = _velocity(model, x, float(unipc.timesteps[i]), text, anchor)
+            x = unipc.step(v.float(), x.float()).to(model.dtype)
+        sigmas = [float(s) for s in unipc.sigmas.tolist()]
+    elif solver == "euler":
+        sched = FlowMatchScheduler(shift=shift)
+        sched.set_timesteps(steps)
+        sig = torch.cat([sched.sigmas, torch.zeros(1)]).to(dev)
+        for i in range(steps):
+            v = _velocity(model, x, float(sig[i]) * 1000.0, text, anchor)
+            s, s_next = sig[i].expand(frames).clone(), sig[i + 1].expand(frames).clone()
+            x = ops.euler_step(x.reshape(frames, -1), v.reshape(frames, -1), s.float(), s_next.float()).view_as(x)
+        sigmas = [float(s) for s in sig.tolist()]
+    else:
+        raise BackendContractError(f"inference.solver must be unipc or euler, not {solver!r}")
+    if anchor is not None:
+        x[:, 0] = anchor
+    return x, sigmas
+
+
+def partition_cases(cases, dp_rank: int, dp_world: int):
+    """The cases of one data-parallel replica: ordinal ``i`` goes to replica ``i % dp_world``, so replicas differ by
+    at most one case and sequence-parallel peers of a replica hold the same list (reference:
+    _partition_generation_cases, solar/backends/wan22/runtime/inference.py:2259-2272)."""
+    if dp_world < 1 or not 0 <= dp_rank < dp_world:
+        raise BackendContractError(f"data-parallel identity {dp_rank}/{dp_world} is invalid")
+    if len({int(c.slot) for c in cases}) != len(cases):
+        raise BackendContractError("generation cases contain duplicate slots")
+    return tuple(c for i, c in enumerate(cases) if i % dp_world == dp_rank)
+
+
+def merge_partitions(parts, target, *, family: str, weights_id: str, expected_cases: int):
+    """Join the sealed per-replica publications ``parts`` into ``target`` (create-only): slot folders move over, the
+    ordered manifest is rebuilt in slot order and sealed with one COMPLETE record.  Every slot must appear exactly
+    once (reference: _merge_generation_partitions, solar/backends/wan22/runtime/inference.py:2298-2370)."""
+    import hashlib
+    import os
+    import uuid
+    from pathlib import Path
+
+    from ...engine.inference_engine import COMPLETE_SCHEMA, _create
+    from ...config.loader import canonical_json
+    from ...runtime.create_only import publish_directory_no_replace
+
+    target = Path(target)
+    if target.exists():
+        raise BackendContractError(f"inference output already exists: {target}")
+    staging = target.with_name(f".{target.name}.{uuid.uuid4().hex}.merge")
+    staging.mkdir(parents=True)
+    by_slot = {}
+    for part in map(Path, parts):
+        seal = json.loads((part / "COMPLETE.json").read_text())
+        if seal.get("weights_id") != weights_id or seal.get("family") != family:
+            raise BackendContractError(f"partition {part} was generated by other weights or another family")
+        lines = [ln for ln in (part / "ordered-manifest.jsonl").read_bytes().split(b"\n") if ln.strip()]
+        if len(lines) != int(seal["cases"]):
+            raise BackendContractError(f"partition {part} lists {len(lines)} cases, its seal says {seal['cases']}")
+        for ln in lines:
+            m = json.loads(ln)
+            slot = int(m["case"]["slot"])
+            if slot in by_slot:
+                raise BackendContractError(f"slot {slot} was generated by two replicas")
+            by_slot[slot] = (part, m)
+    if len(by_slot) != int(expected_cases):
+        raise BackendContractError(f"merged publication has {len(by_slot)} cases, the plan has {expected_cases}")
+    ordered = []
+    for slot in sorted(by_slot):
+        part, m = by_slot[slot]
+        name = f"slot-{slot:06d}"
+        os.replace(part / name, staging / name)
+        ordered.append(m)
+    blob = b"".join(canonical_json(m) for m in ordered)
+    digest = hashlib.blake2s(blob).hexdigest()
+    _create(staging / "ordered-manifest.jsonl", blob)
+    _create(staging / "COMPLETE.json", canonical_json({
+        "schema": COMPLETE_SCHEMA, "family": family, "weights_id": weights_id, "cases": len(ordered),
+        "ordered_manifest_digest": digest}))
+    publish_directory_no_replace(staging, target)
+    return digest
 
 
 class WanLatentAdapter:
@@ -112,15 +201,34 @@ class WanLatentAdapter:
         g = torch.Generator().manual_seed(stable_validation_seed("prompt", case.prompt, case.sample_id) % (2 ** 31))
         return torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(dev, self.model.dtype)
 
+    def _first_frame(self, case: InferenceCase, shape, dev):
+        """The anchor latent of text+image generation: ``inference.first_frame`` names a ``.pt`` file holding
+        ``[C, H, W]`` (one for every case) or ``[cases, C, H, W]`` (indexed by slot); ``"seeded"`` draws one from the
+        case's seed (synthetic runs).  Absent: no anchor."""
+        spec = (self.config.get("inference", {}) or {}).get("first_frame")
+        if not spec:
+            return None
+        if spec == "seeded":
+            g = torch.Generator().manual_seed(stable_validation_seed("first-frame", case.sample_id) % (2 ** 31))
+            return torch.randn(*shape, generator=g).to(dev, self.model.dtype)
+        value = torch.load(str(spec), map_location="cpu", weights_only=True)
+        if value.dim() == len(shape) + 1:
+            value = value[case.slot]
+        if tuple(value.shape) != tuple(shape):
+            raise BackendContractError(f"inference.first_frame holds {tuple(value.shape)}, the model takes {tuple(shape)}")
+        return value.to(dev, self.model.dtype)
+
     def generate(self, case: InferenceCase, *, weights_id: str) -> GeneratedSample:
         inf = self.config.get("inference", {}) or {}
         cfg = self.model.cfg
         dev = next(self.model.parameters()).device
         text = self._embed(case, dev)
+        solver = str(inf.get("solver", "unipc"))
+        frames, h, w = int(inf.get("latent_frames", 5)), int(inf.get("latent_height", 16)), int(inf.get("latent_width", 16))
         lat, sigmas = sample_bidirectional(
-            self.model, text, frames=int(inf.get("latent_frames", 5)), height=int(inf.get("latent_height", 16)),
-            width=int(inf.get("latent_width", 16)), steps=int(inf.get("steps", 8)),
-            shift=float(self.config["model"].get("timestep_shift", 5.0)), seed=case.noise_seed)
+            self.model, text, frames=frames, height=h, width=w, steps=int(inf.get("steps", 50)),
+            shift=float(self.config["model"].get("timestep_shift", 5.0)), seed=case.noise_seed, solver=solver,
+            first_frame=self._first_frame(case, (cfg.out_dim, h, w), dev))
         buf = io.BytesIO()
         torch.save(lat.float().cpu(), buf)
         artifacts = {"latents.pt": buf.getvalue(), "schedule.json": json.dumps({"sigmas": sigmas}).encode()}
@@ -130,7 +238,8 @@ class WanLatentAdapter:
         return GeneratedSample(artifacts,
                                tuple(lat.shape), str(lat.dtype).replace("torch.", ""),
                                metrics={"latent_abs_mean": float(lat.float().abs().mean())},
-                               provenance={"sampler": "euler-flow", "steps": len(sigmas) - 1})
+                               provenance={"sampler": "unipc-flow" if solver == "unipc" else "euler-flow",
+                                           "steps": len(sigmas) - 1, "anchored_first_frame": bool(inf.get("first_frame"))})
 
 
 def _cases(config, count):
@@ -147,6 +256,68 @@ def _cases(config, count):
             for i in range(count)]
 
 
+def _fail_together(error, label):
+    """Every rank learns whether any rank failed the phase ``label`` (an object all-gather of the error texts)."""
+    import torch.distributed as dist
+
+    texts = [None] * dist.get_world_size()
+    dist.all_gather_object(texts, error)
+    failed = [(r, t) for r, t in enumerate(texts) if t is not None]
+    if failed and error is None:
+        raise BackendContractError(f"inference {label} failed on rank {failed[0][0]}: {failed[0][1]}")
+
+
+def _run_partitioned(adapter, cases, target, weights_id, topo):
+    """Data-parallel generation: every replica generates its share of the cases into a private partition next to the
+    target, all ranks walk the same number of case waves (a replica short of a case idles through the last one) and
+    report failures to each other after each, then the main rank joins the partitions into the public directory."""
+    import shutil
+    import torch.distributed as dist
+
+    mine = partition_cases(cases, topo.dp_rank, topo.dp_size)
+    waves = (len(cases) + topo.dp_size - 1) // topo.dp_size
+    parts_root = target.with_name(f".{target.name}.parts")
+    part = parts_root / f"replica-{topo.dp_rank:04d}"
+    writer = topo.sp_rank == 0                              # sequence-parallel peers compute, one of them writes
+    engine = InferenceEngine(adapter)
+    if writer:
+        engine.run(mine, weights_id=weights_id, output_dir=part, collective_error=_fail_together,
+                   collective_case_waves=waves)
+    else:
+        _PeerOnly(adapter).run(mine, weights_id, waves)
+    dist.barrier()
+    digest = None
+    if topo.is_main:
+        digest = merge_partitions([parts_root / f"replica-{d:04d}" for d in range(topo.dp_size)], target,
+                                  family=adapter.family, weights_id=weights_id, expected_cases=len(cases))
+        shutil.rmtree(parts_root, ignore_errors=True)
+    box = [digest]
+    dist.broadcast_object_list(box, src=0)
+    return box[0], len(cases)
+
+
+class _PeerOnly:
+    """A sequence-parallel peer of a writing rank: it takes part in every network evaluation and every failure
+    exchange of the writer's phases, and publishes nothing."""
+
+    def __init__(self, adapter):
+        self.adapter = adapter
+
+    def run(self, cases, weights_id, waves):
+        _fail_together(None, "output setup")
+        for wave in range(waves):
+            error = None
+            if wave < len(cases):
+                try:
+                    self.adapter.generate(cases[wave], weights_id=weights_id)
+                except Exception as exc:  # noqa: BLE001 - only the text crosses ranks
+                    error = f"{type(exc).__name__}: {exc}"
+            _fail_together(error, f"case wave {wave}")
+            if error is not None:
+                raise BackendContractError(f"inference case wave {wave} failed: {error}")
+        _fail_together(None, "partition commit")
+
+
 def run_inference(config: Mapping[str, Any], family: str) -> Mapping[str, Any]:
     from ...models.wan import WanDiT
     from ...parallel import dist_init
@@ -154,11 +325,19 @@ def run_inference(config: Mapping[str, Any], family: str) -> Mapping[str, Any]:
     from .checkpoint import load_checkpoint
     from .contracts import architecture
 
-    ctx = dist_init.initialize(1, device=str(config.get("runtime", {}).get("device", "auto")))
+    sp_size = int((config.get("inference", {}) or {}).get("sequence_parallel_size", 1))
+    ctx = dist_init.initialize(sp_size, device=str(config.get("runtime", {}).get("device", "auto")))
     try:
         dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
         model = WanDiT(architecture(config), device=ctx.device, dtype=dtype,
                        seed=model_init_seed(family, int(config["data"].get("seed", 0))))
+        if bool(config["model"].get("nonzero_head_init", False)):      # synthetic runs: a head that predicts something
+            g = torch.Generator().manual_seed(model_init_seed(family, int(config["data"].get("seed", 0))) + 1)
+            w = model.get_parameter("head.head.weight")
+            with torch.no_grad():
+                w.copy_(torch.randn(w.shape, generator=g).mul_(0.02))
+        if ctx.sp is not None:
+            model.sp = ctx.sp
         weights_id = "init:random"
         c = config.get("checkpoint", {}) or {}
         if c.get("resume_from"):
@@ -176,10 +355,14 @@ def run_inference(config: Mapping[str, Any], family: str) -> Mapping[str, Any]:
         inf = config.get("inference", {}) or {}
         cases = _cases(config, int(inf.get("cases", 1)))
         target = output_root(config) / str(inf.get("output_name", "generate"))
-        summary = InferenceEngine(WanLatentAdapter(family, model, config)).run(cases, weights_id=weights_id,
-                                                                             output_dir=target)
-        return {"output_dir": str(summary.output_dir), "cases": summary.cases,
-                "ordered_manifest_digest": summary.ordered_manifest_digest, "weights_id": weights_id}
+        adapter = WanLatentAdapter(family, model, config)
+        topo = ctx.topology
+        if topo.raw_world_size == 1:
+            summary = InferenceEngine(adapter).run(cases, weights_id=weights_id, output_dir=target)
+            digest, count = summary.ordered_manifest_digest, summary.cases
+        else:
+            digest, count = _run_partitioned(adapter, cases, target, weights_id, topo)
+        return {"output_dir": str(target), "cases": count, "ordered_manifest_digest": digest, "weights_id": weights_id}
     finally:
         dist_init.shutdown(ctx)
 
