@@ -1,8 +1,8 @@
-"""H3 backend boundary and the Stage0.5 LoRA flow-matching runtime
-(reference: MiniMaxH3Backend solar/backends/minimax_h3/backend.py:15-44, H3TrainingRuntime
-runtime.py:491-1316, H3Stage0p5Core stage0p5.py:37-300).  The frozen bf16 base is never saved; the
-checkpoint holds ``adapter.pt`` (schema solarwm.minimax-h3-lora.v1), ``optimizer.pt``,
-``scheduler.pt``, ``rank-state.pt`` and ``runtime.pt``."""
+"""H3 backend boundary (reference: MiniMaxH3Backend solar/backends/minimax_h3/backend.py:15-44, H3Stage0p5Core
+stage0p5.py:37-300).  Stage0.5 adapter training runs through ``runtime.H3TrainingRuntime`` (any SP x DP layout); the
+frozen bf16 base is never saved, the checkpoint holds ``adapter.pt`` (schema solarwm.minimax-h3-lora.v1),
+``optimizer.pt``, ``scheduler.pt``, ``ema.pt``, ``rank-state.pt`` and ``runtime.pt``.  ``H3Stage0p5Trainer`` is the
+single-process step the benchmarks and unit tests drive directly."""
 from __future__ import annotations
 
 import time
@@ -95,53 +95,9 @@ class MiniMaxH3Backend:
         route = validate_route(config)
         if route.stage in ("stage1", "stage2"):
             return self._train_causal(config, route)
-        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
-        from ...data.synthetic import h3_sample
+        from .runtime import run_training
 
-        data = config["data"]
-        tr = H3Stage0p5Trainer(self._cfg(config), dev, lr=float(config["train"].get("optimizer", {}).get("lr", 1e-4)),
-                               seed=int(data.get("seed", 0)))
-        self._load_released(tr.model, config)
-        from ..wan22.runtime import activation_and_sharding_options
-
-        tr.model.checkpointing = activation_and_sharding_options(config["train"], 1)["checkpointing"]
-        losses, t0 = [], time.time()
-        corpus = None
-        if str(data.get("source", "synthetic")) == "index":         # a pre-encoded corpus: first latent = anchor frame
-            from ..wan22.runtime import iter_encoded_samples
-
-            corpus = iter_encoded_samples(data)
-        for step in range(int(config["train"]["max_steps"])):
-            if corpus is not None:
-                row, enc = next(corpus)
-                lat = enc["latents"]                                 # [F, C, h, w]
-                if lat.shape[0] < 2 or tuple(enc["text"].shape[1:]) != (tr.model.cfg.text_dim,):
-                    raise BackendContractError(f"{row.sample_id}: needs >= 2 latent frames and text of width {tr.model.cfg.text_dim}")
-                s = {"target_latents": lat[1:].permute(1, 0, 2, 3).contiguous(), "anchor_latents": lat[:1].permute(1, 0, 2, 3).contiguous(),
-                     "prompt_embeds": enc["text"]}
-            else:
-                s = h3_sample(latent_frames=int(data.get("latent_frames", 3)), height=int(data.get("latent_height", 8)),
-                              width=int(data.get("latent_width", 8)), prompt_len=int(data.get("prompt_len", 8)),
-                              text_dim=tr.model.cfg.text_dim, seed=step)
-            s["camera_w2c"] = torch.eye(4).repeat(s["target_latents"].shape[1] + 1, 1, 1)
-            losses.append(float(tr.train_step(s).item()))
-            print(f"[h3-stage0p5] step={step + 1} loss={losses[-1]:.5f} lr={tr.opt.lr:g} compute_time_s={time.time() - t0:.2f}")
-        root = output_root(config)
-        target = checkpoint_model_dir(root, len(losses))
-        with CheckpointTransaction(target) as tx:
-            adapter = {n: p.detach().cpu() for n, p in tr.model.named_parameters() if p.requires_grad}
-            torch.save({"schema": "solarwm.minimax-h3-lora.v1", "state": adapter, "rank": tr.model.cfg.lora_rank}, tx.path / "adapter.pt")
-            torch.save(tr.opt.state_dict(), tx.path / "optimizer.pt")
-            torch.save({"last_step": len(losses)}, tx.path / "scheduler.pt")
-            torch.save({"torch_cpu": torch.get_rng_state()}, tx.path / "rank-state.pt")
-            torch.save({"global_step": len(losses)}, tx.path / "runtime.pt")
-            tx.commit(step=len(losses), contract=CheckpointContract(
-                family="minimax_h3", stage="stage0p5", causal_mode="bidirectional", objective="flow_matching",
-                objective_variant="", camera_translation_transform="logd4", parameterization="lora", sp_size=1,
-                data_generation="synthetic"), required_components=["adapter.pt", "optimizer.pt", "scheduler.pt",
-                                                                    "rank-state.pt", "runtime.pt"], metadata={})
-        return {"final_step": len(losses), "last_loss": losses[-1], "checkpoint": str(target),
-                "native_launches": ops.total_launches()}
+        return run_training(config, model_config=self._cfg(config), load_released=self._load_released)
 
     def _train_causal(self, config, route):
         """Stage1 (teacher forcing: flow matching or AnyFlow under the W6 rule) and Stage2 (SGF) on the

@@ -237,6 +237,12 @@ class H3DiT(nn.Module):
         self.norm_out = nn.Parameter(torch.ones(h, device=device), requires_grad=False)
         self.proj_out, self.audio_proj_out = lin(h, cfg.latent_row_dim, 0.02), lin(h, cfg.audio_row_dim, 0.02)
         self.sp = None
+        # training under sequence parallelism: ``forward`` keeps this rank's balanced share of the packed rows through
+        # the blocks (attention exchanges heads for rows) and returns the predictions of ITS rows only;
+        # ``local_video_rows`` / ``local_audio_rows`` then give their ranges in video / audio row coordinates.  The
+        # streaming generator shards its rows itself and leaves this off.
+        self.shard_rows = False
+        self.local_video_rows = self.local_audio_rows = None
         # inference-only caches installed by renderer.service (None = off)
         # activation checkpointing of the main blocks: "none" | "full" (recompute the block in backward) |
         # "selective" (recompute everything but the attention call, whose output is carried across the recompute;
@@ -318,6 +324,17 @@ class H3DiT(nn.Module):
         cam_q = cam_kv = cam_o = None
         if viewmats is not None:
             cam_q, cam_kv, cam_o = prope_row_matrices(viewmats.to(x.device), fx, fy)
+        lo, hi = 0, S
+        if self.shard_rows and self.sp is not None and self.sp.size > 1:
+            from ..parallel.ulysses import balanced_bounds, balanced_lengths
+
+            if tables is not None:
+                raise ValueError("fixed modulation tables are an inference cache; row-sharded training builds its own")
+            self.sp.set_layout_rows(1, balanced_lengths(S, self.sp.size))
+            lo, hi = balanced_bounds(S, self.sp.size, self.sp.rank)
+            x, idx, cos, sin = x[lo:hi], idx[lo:hi].contiguous(), cos[lo:hi].contiguous(), sin[lo:hi].contiguous()
+            if cam_q is not None:
+                cam_q, cam_kv, cam_o = (m[lo:hi].contiguous() for m in (cam_q, cam_kv, cam_o))
         ckpt = self.checkpointing if torch.is_grad_enabled() else "none"
         for bi, blk in enumerate(self.blocks):
             if ckpt in ("full", "selective"):
@@ -330,8 +347,15 @@ class H3DiT(nn.Module):
             x = blk(x, tables[bi] if tables is not None else blk.tables(temb), idx, cos, sin, cam_q, cam_kv, cam_o,
                     sp=self.sp, attn_fn=attn_fn)
         xn = F_.norm_modulate(x, mode=1, w=self.norm_out, eps=cfg.eps)
-        vid = F_.linear(xn[S - n_video:], self.proj_out)
+
+        def part(first, last):                       # packed rows [first, last) that this rank holds
+            a, b = min(max(first, lo), hi), min(max(last, lo), hi)
+            return a - lo, b - lo, (a - first, b - first)
+
+        va, vb, self.local_video_rows = part(S - n_video, S)
+        vid = F_.linear(xn[va:vb], self.proj_out)
         aud = None
         if n_audio:
-            aud = F_.linear(xn[S - n_video - n_audio:S - n_video], self.audio_proj_out)
+            aa, ab, self.local_audio_rows = part(S - n_video - n_audio, S - n_video)
+            aud = F_.linear(xn[aa:ab], self.audio_proj_out)
         return vid, aud

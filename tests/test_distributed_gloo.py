@@ -1,6 +1,7 @@
 """Real two-process gloo runs on CPU: fail-together error propagation, the data-readiness side
 channel with a failing and a slow reader, and the tiny Wan-style DiT (2 blocks, dim 128, SP=2 on gloo) trained
 with Ulysses SP=2 matches the single-process oracle in loss and in every parameter gradient."""
+import json
 import os
 import time
 from datetime import timedelta
@@ -352,3 +353,71 @@ def test_sharded_optimizer_and_ema_checkpoint_resumes_exactly(tmp_path):
     for s in (3, 4):
         for r in range(2):
             assert rb[r]["steps"][s] == ra[r]["steps"][s], (s, r, rb[r]["steps"][s], ra[r]["steps"][s])
+
+
+def _h3_config(root, world, sp, resume_from=None, max_steps=4, save_every=2):
+    return {"schema": "solarwm.run.v1", "action": "train", "name": "h3-multi",
+            "model": {"family": "minimax_h3", "architecture": "tiny", "adapter": {"rank": 4},
+                      "camera_translation_transform": "logd4"},
+            "data": {"source": "synthetic", "seed": 0, "pixel_frames": 158, "latent_frames": 3, "latent_height": 8,
+                     "latent_width": 8, "prompt_len": 7},
+            "distributed": {"world_size": world, "sequence_parallel_size": sp},
+            "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "max_steps": max_steps,
+                      "grad_accum": 1, "optimizer": {"lr": 1e-3, "warmup_steps": 1}, "ema": {"enabled": True, "decay": 0.9}},
+            "checkpoint": ({"mode": "full_resume", "resume_from": resume_from} if resume_from else {"mode": "none"}),
+            "runtime": {"output_dir": root, "device": "cpu", "save_every": 0 if resume_from else save_every,
+                        "save_final": not resume_from}}
+
+
+def _h3_train_worker(rank, world, path, out, root, sp, resume_from):
+    import json
+    import os
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world))
+    _init(rank, world, path)
+    from solarwm_b200.registry import load_backend
+
+    load_backend("minimax_h3").train(_h3_config(root, world, sp, resume_from))
+    events = [json.loads(l) for l in open(os.path.join(root, "events", f"rank-{rank:05d}.jsonl"))]
+    steps = {e["step"]: (e["losses"], e["gradient_norm"]) for e in events if e["event"] == "optimizer_step"}
+    torch.save({"steps": steps}, f"{out}.{rank}")
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def test_h3_adapter_training_on_two_ranks(tmp_path):
+    """SP = 2 (both ranks hold half the packed rows of one sample) reproduces the single-process losses and gradient
+    norms; a checkpoint written by both ranks holds ``ema.pt`` and every rank's random streams, and a resumed run
+    repeats steps 3 and 4."""
+    from solarwm_b200.registry import load_backend
+
+    one = load_backend("minimax_h3").train(_h3_config(str(tmp_path / "one"), 1, 1))
+    single = {e["step"]: (e["losses"]["loss"], e["gradient_norm"])
+              for e in map(json.loads, open(tmp_path / "one" / "events" / "rank-00000.jsonl")) if e["event"] == "optimizer_step"}
+    assert one["final_step"] == 4 and sorted(single) == [1, 2, 3, 4]
+    a, b = str(tmp_path / "a"), str(tmp_path / "b")
+    mp.spawn(_h3_train_worker, args=(2, str(tmp_path / "rdv-a"), a, str(tmp_path / "ra"), 2, None), nprocs=2, join=True)
+    got = [torch.load(f"{a}.{r}", weights_only=False)["steps"] for r in range(2)]
+    assert got[0] == got[1]
+    for s in range(1, 5):
+        assert abs(got[0][s][0]["loss"] - single[s][0]) < 1e-4 * max(1.0, single[s][0]), (s, got[0][s], single[s])
+        assert abs(got[0][s][1] - single[s][1]) < 1e-3 * max(1.0, single[s][1]), (s, got[0][s], single[s])
+    ckpt = tmp_path / "ra" / "checkpoint_model_000002"
+    assert {"adapter.pt", "optimizer.pt", "scheduler.pt", "ema.pt", "rank-state.pt", "runtime.pt"} <= {p.name for p in ckpt.iterdir()}
+    ranks = torch.load(ckpt / "rank-state.pt", weights_only=True)
+    assert ranks["world_size"] == 2 and len(ranks["ranks"]) == 2
+    ema = torch.load(ckpt / "ema.pt", weights_only=True)
+    adapter = torch.load(ckpt / "adapter.pt", weights_only=True)["state"]
+    assert ema["num_updates"] == 2 and set(ema["state"]) == set(adapter)
+    assert any(not torch.allclose(ema["state"][k], adapter[k].float()) for k in adapter)      # an average, not a copy
+    mp.spawn(_h3_train_worker, args=(2, str(tmp_path / "rdv-b"), b, str(tmp_path / "rb"), 2, str(ckpt)), nprocs=2, join=True)
+    again = torch.load(f"{b}.0", weights_only=False)["steps"]
+    assert sorted(again) == [3, 4] and all(again[s] == got[0][s] for s in (3, 4))
+
+
+def test_h3_data_parallel_ranks_average_their_gradients(tmp_path):
+    """DP = 2: the replicas read different samples, report different losses and apply ONE averaged gradient."""
+    out = str(tmp_path / "dp")
+    mp.spawn(_h3_train_worker, args=(2, str(tmp_path / "rdv"), out, str(tmp_path / "r"), 1, None), nprocs=2, join=True)
+    got = [torch.load(f"{out}.{r}", weights_only=False)["steps"] for r in range(2)]
+    assert all(got[0][s][0] != got[1][s][0] for s in got[0]) and all(got[0][s][1] == got[1][s][1] for s in got[0])
