@@ -56,6 +56,11 @@ def architecture(config: Mapping[str, Any]) -> WanConfig:
         raise ConfigurationError("model.architecture must be a preset name or a mapping")
     if str(_map(config, "train", required=False).get("objective", "")) == "anyflow_forward_map":
         base.flow_objective = "anyflow_forward_map"
+    mode = model.get("camera_attention_mode")
+    if mode is not None:                       # the reference spells the parallel branch's default by name
+        if mode not in ("none", "fused_prope", "parallel"):
+            raise ConfigurationError(f"model.camera_attention_mode must be none, fused_prope or parallel, not {mode!r}")
+        base.camera_attention_mode = str(mode)
     return base
 
 

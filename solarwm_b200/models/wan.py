@@ -54,7 +54,10 @@ class WanConfig:
     num_frame_per_block: int = 3
     flow_objective: str = "flow_matching"   # or "anyflow_forward_map"
     anyflow_gate: float = 0.25
-    camera_attention_mode: str = "none"     # "none" | "fused_prope"
+    # "none" / "fused_prope": cameras (when given) transform the heads of the block's own self-attention;
+    # "parallel": every block owns a second, zero-initialised self-attention that sees positions only through the
+    # cameras (reference: CausalPropeSelfAttention, runtime/modeling/causal_model.py:1238-1525)
+    camera_attention_mode: str = "none"
     norm_type: str = "layer"                # "layer": LayerNorm without affine (Wan); "rms": RMSNorm (LTX)
 
     @property
@@ -206,7 +209,17 @@ def _block_specs(cfg: WanConfig):
               ("modulation", (1, 6, d), True)]
     if cfg.cross_attn_norm:
         specs += [("norm3.weight", (d,), True), ("norm3.bias", (d,), True)]
+    if cfg.camera_attention_mode == "parallel":
+        pre = "cam_self_attn"
+        specs += [(f"{pre}.{n}_proj.weight", (d, d), False) for n in ("q", "k", "v")]
+        specs += [(f"{pre}.{n}_proj.bias", (d,), False) for n in ("q", "k", "v")]
+        specs += [(f"{pre}.out_proj.weight", (d, d), False), (f"{pre}.out_proj.bias", (d,), False),
+                  (f"{pre}.norm_q.weight", (d,), True), (f"{pre}.norm_k.weight", (d,), True)]
     return specs
+
+
+# adjacent projection slots that one GEMM serves, by the name of the first
+_SPAN_NAMES = {"q": ("q", "k", "v"), "k": ("k", "v"), "q_proj": ("q_proj", "k_proj", "v_proj")}
 
 
 class WanBlock(nn.Module):
@@ -245,7 +258,7 @@ class WanBlock(nn.Module):
         if torch.is_grad_enabled() and self.unit.grad is not None:
             w.main_grad = self.unit.grad_span(first + ".weight", last + ".weight", (n_out, d_in))
             b.main_grad = self.unit.grad_span(first + ".bias", last + ".bias", (n_out,))
-            names = {"q": ("q", "k", "v"), "k": ("k", "v")}[first.rsplit(".", 1)[1]]
+            names = _SPAN_NAMES[first.rsplit(".", 1)[1]]
             pre = first.rsplit(".", 1)[0]
             w._anchors = tuple(self._p(f"{pre}.{n}.weight") for n in names)
             b._anchors = tuple(self._p(f"{pre}.{n}.bias") for n in names)
@@ -256,7 +269,7 @@ class WanBlock(nn.Module):
     def _fused_linear(self, x, first, last, n_out):
         """One GEMM over adjacent weight slots ``first..last`` (e.g. q|k|v)."""
         if not x.is_cuda or (torch.is_grad_enabled() and self.unit.grad is None):
-            names = {"q": ("q", "k", "v"), "k": ("k", "v")}[first.rsplit(".", 1)[1]]
+            names = _SPAN_NAMES[first.rsplit(".", 1)[1]]
             pre = first.rsplit(".", 1)[0]
             w = torch.cat([self._p(f"{pre}.{n}.weight") for n in names], 0)
             b = torch.cat([self._p(f"{pre}.{n}.bias") for n in names], 0)
@@ -281,6 +294,8 @@ class WanBlock(nn.Module):
         # block's residual stream (two row passes and one GEMM) -- 8 of the block's 22 row-widths of activations
         lean = bool(getattr(self, "lean", False)) and torch.is_grad_enabled()
         Ll = x.shape[0] // B
+        branch = camera is not None and cfg.camera_attention_mode == "parallel"
+        cam_branch, camera = (camera, None) if branch else (None, camera)
         fused_sp = attn_fn is None and camera is None and bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
             (not torch.is_grad_enabled() or self.unit.grad is not None)
         xm = None if (lean and not fused_sp) else F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
@@ -321,6 +336,10 @@ class WanBlock(nn.Module):
             if camera is not None:
                 o = camera_prope.apply(o, camera[2], H)
             y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
+        if cam_branch is not None:
+            if xm is None:
+                xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
+            y = y + self.camera_attention(xm, cam_branch, B=B, sp=sp, attn_fn=attn_fn)
         x = F_.gated_residual(x, y, mod[:, 2], **gk)
 
         # ---- cross attention (text keys/values are replicated on every SP rank)
@@ -357,6 +376,31 @@ class WanBlock(nn.Module):
             y = F_.recompute_segment(ffn, self._p("ffn.2.weight"), x, mod[:, 3], mod[:, 4]) if lean else ffn(x, mod[:, 3], mod[:, 4])
         x = F_.gated_residual(x, y, mod[:, 5], **gk)
         return x
+
+
+def _camera_attention(self, xm, camera, *, B, sp, attn_fn=None):
+    """The parallel camera branch on the block's modulated input: its own q | k | v projection (one GEMM), RMS-normed
+    q and k WITHOUT rotary positions, the camera transforms on whole heads (q <- P^T, k / v <- P^-1, output <- P), the
+    same attention pattern as the main branch, and a zero-initialised output projection."""
+    from . import camera_prope
+
+    cfg = self.cfg
+    D, H, hd = cfg.dim, cfg.num_heads, cfg.head_dim
+    Ll = xm.shape[0] // B
+    qkv = self._fused_linear(xm, "cam_self_attn.q_proj", "cam_self_attn.v_proj", 3 * D)
+    q, k, v = F_.split_columns(qkv, (D, D, D))
+    q = F_.rmsnorm_rope(q, self._p("cam_self_attn.norm_q.weight").float(), None, eps=cfg.eps)
+    k = F_.rmsnorm_rope(k, self._p("cam_self_attn.norm_k.weight").float(), None, eps=cfg.eps)
+    q = camera_prope.apply(q, camera[0], H)
+    k = camera_prope.apply(k, camera[1], H)
+    v = camera_prope.apply(v.contiguous(), camera[1], H)
+    q, k, v = sp.scatter_heads(*(t.reshape(B, Ll, H, hd) for t in (q, k, v)))
+    o = attn_fn(q, k, v) if attn_fn is not None else ops.attention(q, k, v)
+    o = camera_prope.apply(sp.gather_heads(o).reshape(B * Ll, D), camera[2], H)
+    return self._linear(o, "cam_self_attn.out_proj.weight", "cam_self_attn.out_proj.bias")
+
+
+WanBlock.camera_attention = _camera_attention
 
 
 def _stem_specs(cfg: WanConfig):
@@ -450,7 +494,7 @@ class WanDiT(nn.Module):
                 fill(p, "zeros")
             elif name.startswith(("text_embedding", "time_embedding", "delta_embedding")):
                 fill(p, "normal", 0.02)
-            elif name.startswith("head.head"):
+            elif name.startswith("head.head") or ".cam_self_attn.out_proj." in name:
                 fill(p, "zeros")
             else:
                 fill(p, "xavier")

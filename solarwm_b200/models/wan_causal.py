@@ -46,6 +46,8 @@ class LayerCache:
     v: torch.Tensor          # [capacity_tokens, dim_local]
     text_k: Optional[torch.Tensor] = None   # [T, dim] projected + normalised text keys
     text_v: Optional[torch.Tensor] = None
+    cam_k: Optional[torch.Tensor] = None    # the parallel camera branch's own cache: keys / values stored AFTER the
+    cam_v: Optional[torch.Tensor] = None    # P^-1 of their own frame (no rotary positions, so a slide is a plain move)
 
 
 @dataclass
@@ -87,8 +89,11 @@ def allocate_kv_cache(model: WanDiT, *, grid_hw, chunk_frames: int, window_frame
     dim_local = hl * cfg.head_dim
     dev = device or next(model.parameters()).device
     cap = (sink + window + chunk_frames) * ft
-    layers = [LayerCache(torch.zeros(cap, dim_local, dtype=model.dtype, device=dev),
-                         torch.zeros(cap, dim_local, dtype=model.dtype, device=dev)) for _ in model.blocks]
+    buf = lambda: torch.zeros(cap, dim_local, dtype=model.dtype, device=dev)   # noqa: E731
+    layers = [LayerCache(buf(), buf()) for _ in model.blocks]
+    if cfg.camera_attention_mode == "parallel":
+        for lc in layers:
+            lc.cam_k, lc.cam_v = buf(), buf()
     cap_frames = sink + window + chunk_frames
     if position_cap is not None and position_cap < cap_frames:
         raise ValueError(f"position_cap {position_cap} is below the cache capacity of {cap_frames} frames")
@@ -196,6 +201,7 @@ class CausalWanRunner:
         h0 = 0 if sp is None else sp.rank * hl
         gk = dict(rows_per_group=ft)
         cam = None
+        parallel = cfg.camera_attention_mode == "parallel"
         if y_camera is not None:
             from . import camera_prope
 
@@ -218,23 +224,39 @@ class CausalWanRunner:
             cs = slice(h0 * hd, (h0 + hl) * hd)
             v_new = qkv[:, 2 * D:][:, cs]
             q_loc = q[:, cs]
-            if cam is not None:
+            own = cam is not None and not parallel          # cameras on the block's own attention
+            if own:
                 q_loc = camera_prope.apply(q_loc.contiguous(), cam[0], hl)
                 v_new = camera_prope.apply(v_new.contiguous(), cam[1], hl)       # values are cached transformed
             lc.k[n_ctx:n_ctx + n_new] = k_raw[:, cs]
             lc.v[n_ctx:n_ctx + n_new] = v_new
             k_all = F_.rmsnorm_rope(lc.k[:n_ctx + n_new], None, rope_all, no_norm=True) if self.rope_at_read \
                 else lc.k[:n_ctx + n_new]
-            if cam is not None:
+            if own:
                 k_all = camera_prope.apply(k_all, cam[3], hl)                    # after RoPE, each key with its own camera
             o = ops.attention(q_loc.reshape(1, n_new, hl, hd), k_all.view(1, n_ctx + n_new, hl, hd),
                               lc.v[:n_ctx + n_new].view(1, n_ctx + n_new, hl, hd))
             o = o.reshape(n_new, hl * hd)
-            if cam is not None:
+            if own:
                 o = camera_prope.apply(o, cam[2], hl)
             if P > 1:
                 o = sp.all_gather_heads(o)
             yb = blk._linear(o, "self_attn.o.weight", "self_attn.o.bias")
+            if cam is not None and parallel:
+                # the camera branch: no rotary positions, keys and values enter ITS cache already in their own
+                # frame's camera coordinates, so the history is read as it is
+                cqkv = blk._fused_linear(xm, "cam_self_attn.q_proj", "cam_self_attn.v_proj", 3 * D)
+                cq = F_.rmsnorm_rope(cqkv[:, :D], blk._p("cam_self_attn.norm_q.weight").float(), None, eps=cfg.eps)
+                ck = F_.rmsnorm_rope(cqkv[:, D:2 * D], blk._p("cam_self_attn.norm_k.weight").float(), None, eps=cfg.eps)
+                cq = camera_prope.apply(cq[:, cs].contiguous(), cam[0], hl)
+                lc.cam_k[n_ctx:n_ctx + n_new] = camera_prope.apply(ck[:, cs].contiguous(), cam[1], hl)
+                lc.cam_v[n_ctx:n_ctx + n_new] = camera_prope.apply(cqkv[:, 2 * D:][:, cs].contiguous(), cam[1], hl)
+                oc_ = ops.attention(cq.reshape(1, n_new, hl, hd), lc.cam_k[:n_ctx + n_new].view(1, n_ctx + n_new, hl, hd),
+                                    lc.cam_v[:n_ctx + n_new].view(1, n_ctx + n_new, hl, hd)).reshape(n_new, hl * hd)
+                oc_ = camera_prope.apply(oc_, cam[2], hl)
+                if P > 1:
+                    oc_ = sp.all_gather_heads(oc_)
+                yb = yb + blk._linear(oc_, "cam_self_attn.out_proj.weight", "cam_self_attn.out_proj.bias")
             xs = F_.gated_residual(xs, yb, mod[:, 2], **gk)
             xn = F_.norm_modulate(xs, mode=2, w=blk._p("norm3.weight").float(), b=blk._p("norm3.bias").float(),
                                   eps=cfg.eps) if cfg.cross_attn_norm else xs
@@ -267,8 +289,9 @@ class CausalWanRunner:
             s0 = cache.sink_frames * ft
             keep = (cache.committed_frames - cache.sink_frames - extra) * ft
             for lc in cache.layers:
-                for buf in (lc.k, lc.v):
-                    buf[s0:s0 + keep] = buf[s0 + extra * ft:s0 + extra * ft + keep].clone()
+                for buf in (lc.k, lc.v, lc.cam_k, lc.cam_v):
+                    if buf is not None:
+                        buf[s0:s0 + keep] = buf[s0 + extra * ft:s0 + extra * ft + keep].clone()
             if cache.cam_inv is not None:
                 fs, fk = cache.sink_frames, keep // ft
                 cache.cam_inv[fs:fs + fk] = cache.cam_inv[fs + extra:fs + extra + fk].clone()

@@ -67,8 +67,10 @@ def block_causal_attention(q, k, v, *, frame_tokens: int, chunk_frames: int, win
     return torch.cat(outs, 1)
 
 
-def _run(model: WanDiT, tok, t_frames, r_frames, context, frame_positions, grid_hw, attn_fn, out_frames):
-    """Shared body: tok [F_all*ft, dim] (B = 1), per-frame times, explicit frame positions."""
+def _run(model: WanDiT, tok, t_frames, r_frames, context, frame_positions, grid_hw, attn_fn, out_frames, y_camera=None):
+    """Shared body: tok [F_all*ft, dim] (B = 1), per-frame times, explicit frame positions; ``y_camera`` =
+    ``{"viewmats": [1, F_all, 4, 4], "Ks": [1, F_all, 3, 3] or None, "transform": str}`` (one camera per packed
+    frame) conditions the self-attention as in the bidirectional forward."""
     cfg = model.cfg
     P = model.stem.params
     h, w = grid_hw
@@ -86,6 +88,14 @@ def _run(model: WanDiT, tok, t_frames, r_frames, context, frame_positions, grid_
         sp.set_layout(1, f_all, ft)
     rope = rope_table((fl, h, w), cfg.head_dim, tok.device, frame_positions=frame_positions[f0:f0 + fl])
     kw = dict(B=1, L=f_all * ft, frame_tokens=ft, group_offset=f0 if sp.size > 1 else 0, sp=sp, attn_fn=attn_fn)
+    if y_camera is not None:
+        from . import camera_prope
+
+        Ks = y_camera.get("Ks")
+        mats = camera_prope.prope_matrices(y_camera["viewmats"][0, f0:f0 + fl].to(tok.device),
+                                           None if Ks is None else Ks[0, f0:f0 + fl].to(tok.device),
+                                           transform=y_camera.get("transform", "linear"))
+        kw["camera"] = tuple(camera_prope.per_row(m_, ft) for m_ in mats)
     xs = tok
     for bi, block in enumerate(model.blocks):
         if model.checkpointing != "none" and torch.is_grad_enabled():
@@ -112,13 +122,18 @@ def _embed(model: WanDiT, x):
 
 def forward_teacher_forcing(model: WanDiT, clean, noisy, t, context, *, r: Optional[torch.Tensor] = None,
                             chunk_frames: int = 3, window_chunks: int = 6, sink_frames: int = 0,
-                            capture: Optional[list] = None):
+                            capture: Optional[list] = None, y_camera=None):
     """clean / noisy [1, C, F, H, W]; t (and r) [1, F] on the 1000-step grid; returns the prediction
     for the noisy half [1, C_out, F, H, W].  With ``capture`` (an empty list) every block appends the detached
     keys / values of the clean half (this rank's heads): clean rows never see a noisy row, so they are the same in
     every evaluation of a step and ``forward_noisy_suffix`` can reuse them."""
     if clean.shape[0] != 1:
         raise ValueError("teacher forcing packs one video per call")
+    if y_camera is not None:
+        if capture is not None and model.cfg.camera_attention_mode == "parallel":
+            raise ValueError("key / value capture follows one attention per block; the parallel camera branch adds a second")
+        twice = lambda v: None if v is None else torch.cat([v, v], dim=1)      # noqa: E731  clean | noisy share cameras
+        y_camera = dict(y_camera, viewmats=twice(y_camera["viewmats"]), Ks=twice(y_camera.get("Ks")))
     tok_c, grid = _embed(model, clean)
     tok_n, _ = _embed(model, noisy)
     f, h, w = grid
@@ -142,7 +157,7 @@ def forward_teacher_forcing(model: WanDiT, clean, noisy, t, context, *, r: Optio
                                            window_chunks=window_chunks, sink_frames=sink_frames)
         return torch.cat([oc, on], 1)
 
-    return _run(model, torch.cat([tok_c, tok_n], 0), t_all, r_all, context, pos, (h, w), attn, (f, 2 * f))
+    return _run(model, torch.cat([tok_c, tok_n], 0), t_all, r_all, context, pos, (h, w), attn, (f, 2 * f), y_camera)
 
 
 @torch.no_grad()
@@ -180,7 +195,7 @@ def forward_noisy_suffix(model: WanDiT, noisy, t, context, captured, *, r: Optio
 
 
 def forward_window(model: WanDiT, frames, t, context, *, first_frame: int, current_frames: int,
-                   chunk_frames: int = 3, window_chunks: int = 6, r: Optional[torch.Tensor] = None):
+                   chunk_frames: int = 3, window_chunks: int = 6, r: Optional[torch.Tensor] = None, y_camera=None):
     """frames [1, C, Fw, H, W] = clean history followed by the current noisy chunk; t [1, Fw] (0 on the
     history); ``first_frame`` = absolute index of the window's first frame.  Returns the prediction for
     the last ``current_frames`` frames."""
@@ -192,4 +207,4 @@ def forward_window(model: WanDiT, frames, t, context, *, first_frame: int, curre
         return block_causal_attention(q, k, v, frame_tokens=h * w, chunk_frames=chunk_frames,
                                       window_chunks=window_chunks)
 
-    return _run(model, tok, t, r, context, pos, (h, w), attn, (f - current_frames, f))
+    return _run(model, tok, t, r, context, pos, (h, w), attn, (f - current_frames, f), y_camera)

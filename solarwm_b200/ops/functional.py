@@ -7,6 +7,7 @@ fallback on CUDA: if the native library cannot be loaded the call raises.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -292,13 +293,43 @@ class _LinearMainGradFn(torch.autograd.Function):
         (x,) = ctx.saved_tensors
         w, b = ctx.w, ctx.b
         dy = _rowmajor(dy)
-        dx = gemm(dy, w, NN) if ctx.needs_input_grad[0] else None
-        if w.requires_grad:
-            gemm(dy, x, TN, out=w.main_grad, accumulate=_grad_is_live(w))
-            _mark_grad_live(w)
+        dgrad = (lambda: gemm(dy, w, NN)) if ctx.needs_input_grad[0] else (lambda: None)
+        dx = wgrad_beside(dy, x, w, dgrad) if w.requires_grad else dgrad()
         if b is not None and b.requires_grad:
             accumulate_main_grad(b, colsum(dy))
         return dx, None, None
+
+
+# The weight-gradient GEMM of a linear has no consumer until its block's gradients are reduced, and it is independent
+# of the input-gradient GEMM.  Both are persistent kernels that fill the GPU, so run back to back each pays its own
+# partial last wave -- at 8-way sequence parallelism a [3410 x 3072] product is 168 CTA-pair tiles over 74 pairs: 2.27
+# waves that take 3.  Launched on two streams, the CTAs of the second kernel start on SMs as the first one's CTAs run
+# out of tiles, so the pair pays one tail instead of two.  The main stream joins the side stream before anything else
+# is enqueued, so every later kernel (and the allocator's reuse of ``dy``) is ordered after both.
+_WGRAD_SIDE: dict = {}
+_WGRAD_OVERLAP = os.environ.get("SOLAR_WGRAD_OVERLAP", "1") != "0"
+
+
+def wgrad_beside(dy, x, w, dgrad):
+    """``w.main_grad (+)= dy^T x`` on a side stream while ``dgrad()`` (the input-gradient work) is enqueued on the
+    current one; returns what ``dgrad`` returns."""
+    def wgrad():
+        gemm(dy, x, TN, out=w.main_grad, accumulate=_grad_is_live(w))
+        _mark_grad_live(w)
+
+    if not (_WGRAD_OVERLAP and dy.is_cuda):
+        wgrad()
+        return dgrad()
+    main = torch.cuda.current_stream()
+    side = _WGRAD_SIDE.get(dy.device.index)
+    if side is None:
+        side = _WGRAD_SIDE[dy.device.index] = torch.cuda.Stream(device=dy.device)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        wgrad()
+    out = dgrad()
+    main.wait_stream(side)
+    return out
 
 
 def _grad_is_live(p) -> bool:
@@ -597,19 +628,23 @@ class _GeluLinearMainGradFn(torch.autograd.Function):
         (h,) = ctx.saved_tensors
         w, b = ctx.w, ctx.b
         dy = _rowmajor(dy)
-        if w.requires_grad:
-            a = torch.empty_like(h)
-            _gelu_launch(h, None, a, 0)
-            gemm(dy, a, TN, out=w.main_grad, accumulate=_grad_is_live(w))
-            _mark_grad_live(w)
-            del a
-        if b is not None and b.requires_grad:
-            accumulate_main_grad(b, colsum(dy))
-        dh = None
-        if ctx.needs_input_grad[0]:
+        def dgrad():
+            if not ctx.needs_input_grad[0]:
+                return None
             da = gemm(dy, w, NN)
             dh = torch.empty_like(h)
             _gelu_launch(h, da, dh, 1)
+            return dh
+
+        if w.requires_grad:
+            a = torch.empty_like(h)
+            _gelu_launch(h, None, a, 0)
+            dh = wgrad_beside(dy, a, w, dgrad)
+            del a
+        else:
+            dh = dgrad()
+        if b is not None and b.requires_grad:
+            accumulate_main_grad(b, colsum(dy))
         return dh, None, None
 
 

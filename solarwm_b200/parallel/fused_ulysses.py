@@ -300,9 +300,7 @@ class FusedSelfAttention(torch.autograd.Function):
         dy = F_._rowmajor(dy)
         # 4': dO leaves through the dgrad GEMM's epilogue; the weight / bias gradients run while it lands
         with span("sa.bwd.dgrad_exchange"):
-            slot_do = sp.dgrad_exchange(dy, w_o, parity)
-            F_.gemm(dy, tokens, F_.TN, out=w_o.main_grad, accumulate=F_._grad_is_live(w_o))
-            F_._mark_grad_live(w_o)
+            slot_do = F_.wgrad_beside(dy, tokens, w_o, lambda: sp.dgrad_exchange(dy, w_o, parity))
             if b_o is not None:
                 F_.accumulate_main_grad(b_o, F_.colsum(dy))
             sp.heap.wait(slot_do, sp.size)
@@ -323,8 +321,6 @@ class FusedSelfAttention(torch.autograd.Function):
             check(rc, "solar_rmsnorm_rope_bwd")
             count("rmsnorm_rope_bwd")
             dws.append(part.sum(0))
-        dxm = F_.gemm(g, w, F_.NN)
-        F_.gemm(g, xm, F_.TN, out=w.main_grad, accumulate=F_._grad_is_live(w))
-        F_._mark_grad_live(w)
+        dxm = F_.wgrad_beside(g, xm, w, lambda: F_.gemm(g, w, F_.NN))
         F_.accumulate_main_grad(b, F_.colsum(g))
         return dxm, None, None, dws[0], dws[1], None, None, None, None, None, None, None, None

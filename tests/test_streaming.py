@@ -228,3 +228,90 @@ def test_block_relative_positions_follow_the_rule():
         cache.total_frames += 3
     # absolute positions until the newest frame would pass cap - 1 = 20, then clamped (top-aligned)
     assert first == [0, 3, 6, 9, 12, 15, 18, 18, 18]
+
+
+def _camera_pair(g, frames):
+    import torch
+
+    q, _ = torch.linalg.qr(torch.randn(frames, 3, 3, generator=g))
+    view = torch.eye(4).repeat(1, frames, 1, 1)
+    view[0, :, :3, :3] = q
+    view[0, :, :3, 3] = torch.randn(frames, 3, generator=g) * 0.3
+    Ks = torch.eye(3).repeat(1, frames, 1, 1)
+    Ks[0, :, 0, 0], Ks[0, :, 1, 1] = 0.7, 1.1
+    return {"viewmats": view, "Ks": Ks}
+
+
+def test_parallel_camera_branch_is_zero_at_init_matches_its_oracle_and_streams():
+    """``camera_attention_mode = "parallel"``: a second self-attention per block that knows positions only through the
+    cameras.  At initialisation it changes nothing; with a trained output projection its contribution is the plain
+    formula (own projections, q/k RMS norm, P^T / P^-1 / P on every 4-vector, softmax attention); the cache runner,
+    which keeps the branch's keys and values in a cache of their own, reproduces the full forward chunk by chunk."""
+    import torch
+
+    from solarwm_b200.models import camera_prope
+    from solarwm_b200.models.wan import WanConfig, WanDiT
+    from solarwm_b200.models.wan_causal import CausalWanRunner, allocate_kv_cache
+
+    cfg = WanConfig(model_type="t2v", in_dim=4, out_dim=4, dim=32, ffn_dim=64, num_heads=2, num_layers=2, text_dim=32,
+                    text_len=8, freq_dim=32, camera_attention_mode="parallel")
+    m = WanDiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    names = {n for n, _ in m.named_parameters()}
+    assert {"blocks.0.cam_self_attn.q_proj.weight", "blocks.1.cam_self_attn.out_proj.bias",
+            "blocks.0.cam_self_attn.norm_k.weight"} <= names
+    with torch.no_grad():
+        m.get_parameter("head.head.weight").normal_(0, 0.05)
+    g = torch.Generator().manual_seed(0)
+    x, ctx = torch.randn(1, 4, 2, 4, 4, generator=g), torch.randn(1, 8, 32, generator=g)
+    t = torch.tensor([[400.0, 400.0]])
+    cam = _camera_pair(g, 2)
+    assert float(m.get_parameter("blocks.0.cam_self_attn.out_proj.weight").detach().abs().max()) == 0.0
+    assert torch.equal(m(x, t, ctx, y_camera=cam), m(x, t, ctx))                       # zero-initialised branch
+    with torch.no_grad():
+        for b in m.blocks:
+            b._p("cam_self_attn.out_proj.weight").normal_(0, 0.2, generator=g)
+            b._p("cam_self_attn.out_proj.bias").normal_(0, 0.1, generator=g)
+    with_cam = m(x, t, ctx, y_camera=cam)
+    assert not torch.allclose(with_cam, m(x, t, ctx), atol=1e-4)
+
+    # the branch of one block against the formula
+    blk, D, H = m.blocks[0], 32, 2
+    xm = torch.randn(8, D, generator=g)                                    # 2 frames x 4 tokens
+    mats = camera_prope.prope_matrices(cam["viewmats"][0], cam["Ks"][0], transform="linear")
+    rows = tuple(camera_prope.per_row(mm, 4) for mm in mats)
+    got = blk.camera_attention(xm, rows, B=1, sp=__import__("solarwm_b200.models.wan", fromlist=["_NoSP"])._NoSP())
+
+    def lin(v, n):
+        return v @ blk._p(f"cam_self_attn.{n}.weight").T + blk._p(f"cam_self_attn.{n}.bias")
+
+    def rms(v, n):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * blk._p(f"cam_self_attn.{n}.weight")
+
+    def lift(v, mm):                                                        # every 4-vector of a row times its matrix
+        return torch.einsum("rij,rnj->rni", mm, v.view(v.shape[0], -1, 4)).reshape(v.shape)
+
+    q, k, v = lift(rms(lin(xm, "q_proj"), "norm_q"), rows[0]), lift(rms(lin(xm, "k_proj"), "norm_k"), rows[1]), \
+        lift(lin(xm, "v_proj"), rows[1])
+    hd = D // H
+    att = torch.softmax(torch.einsum("qhd,khd->hqk", q.view(8, H, hd), k.view(8, H, hd)) / hd ** 0.5, -1)
+    o = torch.einsum("hqk,khd->qhd", att, v.view(8, H, hd)).reshape(8, D)
+    assert torch.allclose(got, lin(lift(o, rows[2]), "out_proj"), atol=1e-5)
+
+    # chunked generation with the branch's own cache == the full forward (one chunk), and a second chunk attends the
+    # first through cached camera-space keys
+    runner = CausalWanRunner(m)
+    cache = allocate_kv_cache(m, grid_hw=(2, 2), chunk_frames=2, window_frames=4, sink_frames=0)
+    assert cache.layers[0].cam_k is not None and cache.layers[0].cam_k.shape == cache.layers[0].k.shape
+    runner.encode_text(cache, ctx)
+    assert torch.allclose(runner.forward_chunk(cache, x, t, commit=True, y_camera=cam), with_cam, atol=1e-4)
+    x2, cam2 = torch.randn(1, 4, 2, 4, 4, generator=g), _camera_pair(g, 2)
+    both = {"viewmats": torch.cat([cam["viewmats"], cam2["viewmats"]], 1), "Ks": torch.cat([cam["Ks"], cam2["Ks"]], 1)}
+    second = runner.forward_chunk(cache, x2, t, commit=False, y_camera=cam2)
+    # oracle: the 4-frame causal forward, second chunk's rows (chunk 1 attends chunk 0 and itself)
+    from solarwm_b200.models.wan_tf import forward_window
+
+    with torch.no_grad():
+        want = forward_window(m, torch.cat([x, x2], 2), torch.cat([t, t], 1), ctx, first_frame=0, current_frames=2,
+                              chunk_frames=2, window_chunks=4, y_camera=both)
+    assert torch.allclose(second, want, atol=1e-4)
+    assert torch.isfinite(second).all() and not torch.allclose(second, runner.forward_chunk(cache, x2, t, commit=False), atol=1e-4)
