@@ -25,7 +25,9 @@ def _arch(config):
 class LTXTrainer:
     """One rectified-flow step: sigma sampling, clean first frame, DiT, masked loss, fused AdamW."""
 
-    def __init__(self, cfg, device, lr=1e-4, seed=0, sp=None, checkpointing="none"):
+    def __init__(self, cfg, device, lr=1e-4, seed=0, sp=None, checkpointing="none", lora_rank=0, lora_alpha=None):
+        """``lora_rank > 0``: the base is frozen and low-rank adapters on the q / k / v / out projections of both
+        attentions and on both FFN linears train instead (``models/lora.py``), under an fp32-master AdamW."""
         dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
         self.model = LTXDiT(cfg, device=device, dtype=dtype, seed=seed)
         with torch.no_grad():
@@ -34,8 +36,17 @@ class LTXTrainer:
             self.model.sp = sp
         self.sp = sp
         self.model.checkpointing = checkpointing
-        self.model.ensure_grads()
-        self.opt = FlatAdamW(self.model.units(), lr=lr)
+        self.lora = None
+        if lora_rank:
+            from ...engine.master_adamw import FP32MasterAdamW
+            from ...models.lora import inject_lora
+
+            self.lora = inject_lora(self.model, rank=int(lora_rank), alpha=lora_alpha, seed=seed + 1)
+            self.lora.broadcast()
+            self.opt = FP32MasterAdamW(self.lora.parameters, lr=lr, betas=(0.9, 0.95), weight_decay=0.0)
+        else:
+            self.model.ensure_grads()
+            self.opt = FlatAdamW(self.model.units(), lr=lr)
         self.device = torch.device(device)
         self.gen = torch.Generator(device=self.device).manual_seed(seed * 100003)
 
@@ -52,6 +63,14 @@ class LTXTrainer:
         pred = self.model(x_t, per_frame * 1000.0, txt)
         loss = masked_flow_loss(pred, target)
         (loss / (1 if self.sp is None else self.sp.size)).backward()
+        if self.lora is not None:
+            flat = self.opt.gather_grads()
+            if self.sp is not None and self.sp.size > 1:
+                self.sp.sum_gradients_([flat])           # adapters are replicated: one fp32 all-reduce of the flat buffer
+            self.opt.clip_(1.0)
+            self.opt.step()
+            self.opt.zero_grad()
+            return loss.detach()
         self.model.finalize_grads()
         if self.sp is not None and self.sp.size > 1:
             self.sp.sum_gradients_([g for u in self.model.units() for g in (u.grad, u.grad_v)])
@@ -252,8 +271,10 @@ class LTX25Backend:
         validate_route(config)
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
         cfg = _arch(config)
+        adapter = (config["model"].get("adapter") or {})
         tr = LTXTrainer(cfg, dev, lr=float(config["train"].get("optimizer", {}).get("lr", 1e-4)),
-                        seed=int(config["data"].get("seed", 0)))
+                        seed=int(config["data"].get("seed", 0)), lora_rank=int(adapter.get("rank", 0)),
+                        lora_alpha=adapter.get("alpha"))
         data = config["data"]
         g = torch.Generator().manual_seed(int(data.get("seed", 0)))
         shape = (1, cfg.in_dim, int(data.get("latent_frames", 4)), int(data.get("latent_height", 8)), int(data.get("latent_width", 8)))
@@ -272,7 +293,31 @@ class LTX25Backend:
             else:
                 lat, txt = torch.randn(shape, generator=g), torch.randn(1, cfg.text_len, cfg.text_dim, generator=g)
             losses.append(float(tr.train_step(lat, txt).item()))
-        return {"final_step": len(losses), "last_loss": losses[-1], "native_launches": ops.total_launches()}
+        out = {"final_step": len(losses), "last_loss": losses[-1], "native_launches": ops.total_launches()}
+        if tr.lora is not None:
+            out["checkpoint"] = str(self._save_adapter(config, tr, len(losses)))
+        return out
+
+    @staticmethod
+    def _save_adapter(config, tr, step: int):
+        """``adapter.pt`` (state under the released key inventory + its metadata record), ``optimizer.pt`` and
+        ``runtime.pt`` through the transactional store; the frozen base is never written."""
+        from ...checkpoint.store import CheckpointContract, CheckpointTransaction
+        from ...runtime.output_layout import checkpoint_model_dir
+
+        route = validate_route(config)
+        target = checkpoint_model_dir(output_root(config), step)
+        with CheckpointTransaction(target) as tx:
+            torch.save({"metadata": tr.lora.metadata(), "state": {k: v.cpu() for k, v in tr.lora.state_dict().items()}},
+                       tx.path / "adapter.pt")
+            torch.save(tr.opt.state_dict(), tx.path / "optimizer.pt")
+            torch.save({"global_step": int(step)}, tx.path / "runtime.pt")
+            tx.commit(step=int(step), contract=CheckpointContract(
+                family="ltx25_video", stage=route.stage, causal_mode=route.causal_mode, objective=route.objective,
+                objective_variant=route.variant, camera_translation_transform=str(config["model"].get("camera_translation_transform", "linear")),
+                parameterization="lora", sp_size=1, data_generation=str(config["data"].get("source", "synthetic"))),
+                required_components=["adapter.pt", "optimizer.pt", "runtime.pt"], metadata={})
+        return target
 
     def infer(self, config):
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"

@@ -59,6 +59,11 @@ class WanConfig:
     # cameras (reference: CausalPropeSelfAttention, runtime/modeling/causal_model.py:1238-1525)
     camera_attention_mode: str = "none"
     norm_type: str = "layer"                # "layer": LayerNorm without affine (Wan); "rms": RMSNorm (LTX)
+    # per-head output gate of the self-attention: o_h <- o_h * 2 sigmoid(x_mod W_g^T + b_g)_h with W_g, b_g zero at
+    # initialisation (gate 1), applied after the camera output transform and before the output projection
+    # (reference: to_gate_logits / gated_attention_function, solar/backends/ltx25/torch_model.py:259-261, order
+    # "native_head_gate_and_output_projection" in solar/backends/ltx25/adapter.py:14-20)
+    gated_attention: bool = False
 
     @property
     def head_dim(self) -> int:
@@ -80,6 +85,12 @@ def wan_preset(name: str) -> WanConfig:
         # LTX-Video-2B-shaped: 28 blocks, dim 2048, 32 heads x 64, 128-channel latents, patch 1, RMSNorm
         return WanConfig(model_type="t2v", patch_size=(1, 1, 1), in_dim=128, out_dim=128, dim=2048, ffn_dim=8192,
                          num_heads=32, num_layers=28, text_dim=4096, text_len=128, norm_type="rms", cross_attn_norm=False)
+    if name in ("ltx25_video_13b", "ltx25_13b"):
+        # the released LTX-2.5 video core: 48 blocks, 32 heads x 128, 128-channel latents, 1024 caption tokens of
+        # width 4096, per-head attention gates (reference layout check: solar/backends/ltx25/checkpoint.py:308-322)
+        return WanConfig(model_type="t2v", patch_size=(1, 1, 1), in_dim=128, out_dim=128, dim=4096, ffn_dim=16384,
+                         num_heads=32, num_layers=48, text_dim=4096, text_len=1024, norm_type="rms", cross_attn_norm=False,
+                         gated_attention=True)
     if name == "tiny":
         return WanConfig(model_type="t2v", in_dim=16, out_dim=16, dim=128, ffn_dim=512, num_heads=4,
                          num_layers=2, text_dim=256, text_len=32, freq_dim=64)
@@ -209,6 +220,9 @@ def _block_specs(cfg: WanConfig):
               ("modulation", (1, 6, d), True)]
     if cfg.cross_attn_norm:
         specs += [("norm3.weight", (d,), True), ("norm3.bias", (d,), True)]
+    if cfg.gated_attention:
+        specs += [("self_attn.to_gate_logits.weight", (cfg.num_heads, d), False),
+                  ("self_attn.to_gate_logits.bias", (cfg.num_heads,), False)]
     if cfg.camera_attention_mode == "parallel":
         pre = "cam_self_attn"
         specs += [(f"{pre}.{n}_proj.weight", (d, d), False) for n in ("q", "k", "v")]
@@ -229,6 +243,13 @@ class WanBlock(nn.Module):
         self.unit = FlatUnit(_block_specs(cfg), device, dtype, pad_to=shard_pad)
         for name in self.unit.slots:
             _register(self, name, self.unit.parameter(name))
+        self.lora = None            # ModuleDict of low-rank adapters once ``models.lora.inject_lora`` ran
+
+    def _adapter(self, wname: str):
+        if not self.lora:
+            return None
+        key = wname[:-len(".weight")].replace(".", "__")
+        return self.lora[key] if key in self.lora else None
 
     # parameters through the unit (fused views where slots are adjacent) ------------------
     def _p(self, name):
@@ -247,6 +268,9 @@ class WanBlock(nn.Module):
         return {"mode": 1, "w": ones}
 
     def _linear(self, x, wname, bname):
+        ad = self._adapter(wname)
+        if ad is not None:
+            return F_.lora_linear(x, self._p(wname), self._p(bname), ad.lora_A, ad.lora_B, ad.scale)
         return F_.linear(x, self._p(wname), self._p(bname))
 
     def _fused_params(self, first, last, n_out):
@@ -268,6 +292,10 @@ class WanBlock(nn.Module):
 
     def _fused_linear(self, x, first, last, n_out):
         """One GEMM over adjacent weight slots ``first..last`` (e.g. q|k|v)."""
+        if self.lora:               # adapters are per projection: issue the parts one by one
+            pre = first.rsplit(".", 1)[0]
+            return torch.cat([self._linear(x, f"{pre}.{n}.weight", f"{pre}.{n}.bias")
+                              for n in _SPAN_NAMES[first.rsplit(".", 1)[1]]], dim=1)
         if not x.is_cuda or (torch.is_grad_enabled() and self.unit.grad is None):
             names = _SPAN_NAMES[first.rsplit(".", 1)[1]]
             pre = first.rsplit(".", 1)[0]
@@ -296,7 +324,8 @@ class WanBlock(nn.Module):
         Ll = x.shape[0] // B
         branch = camera is not None and cfg.camera_attention_mode == "parallel"
         cam_branch, camera = (camera, None) if branch else (None, camera)
-        fused_sp = attn_fn is None and camera is None and bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
+        fused_sp = attn_fn is None and camera is None and not self.lora and not cfg.gated_attention and \
+            bool(getattr(sp, "fused", False)) and x.is_cuda and B == 1 and sp.size > 1 and \
             (not torch.is_grad_enabled() or self.unit.grad is not None)
         xm = None if (lean and not fused_sp) else F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
         if fused_sp:
@@ -335,6 +364,12 @@ class WanBlock(nn.Module):
             o = sp.gather_heads(o).reshape(B * Ll, D)
             if camera is not None:
                 o = camera_prope.apply(o, camera[2], H)
+            if cfg.gated_attention:
+                if xm is None:
+                    xm = F_.norm_modulate(x, mod[:, 0], mod[:, 1], eps=cfg.eps, **nk, **gk)
+                gate = 2.0 * torch.sigmoid(F_.linear(xm, self._p("self_attn.to_gate_logits.weight"),
+                                                     self._p("self_attn.to_gate_logits.bias")).float())
+                o = (o.view(B * Ll, H, hd) * gate.to(o.dtype).unsqueeze(-1)).reshape(B * Ll, D)
             y = self._linear(o, "self_attn.o.weight", "self_attn.o.bias")
         if cam_branch is not None:
             if xm is None:
@@ -370,6 +405,8 @@ class WanBlock(nn.Module):
         # ---- feed forward
         def ffn(a, s3, s4):
             hm = F_.norm_modulate(a, s3, s4, eps=cfg.eps, **nk, **gk)
+            if self._adapter("ffn.2.weight") is not None:      # the adapter reads the activation, so it is kept
+                return self._linear(F_.gelu(self._linear(hm, "ffn.0.weight", "ffn.0.bias")), "ffn.2.weight", "ffn.2.bias")
             return F_.gelu_linear(self._linear(hm, "ffn.0.weight", "ffn.0.bias"), self._p("ffn.2.weight"), self._p("ffn.2.bias"))
 
         with span("ffn.fwd"):
@@ -494,7 +531,7 @@ class WanDiT(nn.Module):
                 fill(p, "zeros")
             elif name.startswith(("text_embedding", "time_embedding", "delta_embedding")):
                 fill(p, "normal", 0.02)
-            elif name.startswith("head.head") or ".cam_self_attn.out_proj." in name:
+            elif name.startswith("head.head") or ".cam_self_attn.out_proj." in name or ".to_gate_logits." in name:
                 fill(p, "zeros")
             else:
                 fill(p, "xavier")

@@ -241,6 +241,10 @@ class CausalWanRunner:
                 o = camera_prope.apply(o, cam[2], hl)
             if P > 1:
                 o = sp.all_gather_heads(o)
+            if cfg.gated_attention:
+                gate = 2.0 * torch.sigmoid(F_.linear(xm, blk._p("self_attn.to_gate_logits.weight"),
+                                                     blk._p("self_attn.to_gate_logits.bias")).float())
+                o = (o.view(n_new, H, hd) * gate.to(o.dtype).unsqueeze(-1)).reshape(n_new, D)
             yb = blk._linear(o, "self_attn.o.weight", "self_attn.o.bias")
             if cam is not None and parallel:
                 # the camera branch: no rotary positions, keys and values enter ITS cache already in their own

@@ -206,6 +206,46 @@ def linear(x, w, b=None, act=None):
     return _LinearFn.apply(x, w, b)
 
 
+class _LoRALinearFn(torch.autograd.Function):
+    """y = x W^T + b + s (x A^T) B^T with W and b frozen: the adapter product lands in the base GEMM's output through
+    the reduce-add epilogue, and backward is four GEMMs (dt = s dy B; dx = dy W + dt A; dA = dt^T x; dB = s dy^T t)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, a, bb, scale):
+        y = gemm(x, w, NT, bias=b)
+        t = gemm(x, a, NT)
+        bs = bb if scale == 1.0 else (bb * scale).to(bb.dtype)
+        gemm(t, bs, NT, out=y, accumulate=True)
+        ctx.save_for_backward(x, w, a, bs, t)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, a, bs, t = ctx.saved_tensors
+        dy = _rowmajor(dy)
+        dt = gemm(dy, bs, NN)                           # [M, r], the scale is folded into bs
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, w, NN)
+            gemm(dt, a, NN, out=dx, accumulate=True)
+        da = gemm(dt, x, TN, out_dtype=a.dtype)
+        db = gemm(dy, t, TN, out_dtype=bs.dtype)
+        if ctx.scale != 1.0:
+            db = (db * ctx.scale).to(db.dtype)
+        return dx, None, None, da, db, None
+
+
+def lora_linear(x, w, b, lora_a, lora_b, scale: float = 1.0):
+    """A frozen linear with a trainable low-rank update: ``lora_a`` [r, in], ``lora_b`` [out, r]."""
+    if not x.is_cuda:
+        y = x.float() @ w.float().t() + scale * ((x.float() @ lora_a.float().t()) @ lora_b.float().t())
+        if b is not None:
+            y = y + b.float()
+        return y.to(x.dtype)
+    return _LoRALinearFn.apply(x, w, b, lora_a, lora_b, float(scale))
+
+
 # Weights (by address) whose forward product is not needed right now: the last GEMM of a segment that is being
 # re-run in backward only to rebuild what that GEMM's own backward keeps (its input), not its output.
 _SKIP_FORWARD: set = set()
@@ -307,7 +347,7 @@ class _LinearMainGradFn(torch.autograd.Function):
 # out of tiles, so the pair pays one tail instead of two.  The main stream joins the side stream before anything else
 # is enqueued, so every later kernel (and the allocator's reuse of ``dy``) is ordered after both.
 _WGRAD_SIDE: dict = {}
-_WGRAD_OVERLAP = os.environ.get("SOLAR_WGRAD_OVERLAP", "1") != "0"
+_WGRAD_OVERLAP = os.environ.get("SOLAR_WGRAD_OVERLAP", "0") == "1"
 
 
 def wgrad_beside(dy, x, w, dgrad):
