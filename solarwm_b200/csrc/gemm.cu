@@ -652,12 +652,48 @@ using namespace solar;
 // dimensions in elements of the row-major arrays as they sit in memory.
 // out_f32: C is fp32 instead of bf16.  accumulate: C += (atomic-free TMA reduce-add).
 // status: optional device int that receives a non-zero code if a bounded wait gave up.
-// -1: choose per problem; 0: single-CTA kernel only; 1: CTA-pair kernel whenever legal.
+// -1: choose per problem; 0: single-CTA kernel with 256-column tiles only; 1: CTA-pair kernel whenever legal;
+// 2: single-CTA kernel with 192-column tiles (for measurements).
 static int g_pair_mode = -1;
 extern "C" int solar_gemm_pair_mode(int mode) {
   const int old = g_pair_mode;
-  if (mode >= -1 && mode <= 1) g_pair_mode = mode;
+  if (mode >= -1 && mode <= 2) g_pair_mode = mode;
   return old;
+}
+
+// Tile shape per problem.  Both kernels are persistent with one tile (or CTA-pair tile) in flight per SM, so a
+// problem costs ceil(tiles / slots) waves of its tile time.  The CTA-pair kernel (256 x 256 over two SMs) is the
+// fastest per FLOP, but with few tiles its last wave is mostly empty: a [3410 x 3072] product -- the out-projection
+// and FFN-down shapes of 8-way sequence parallelism -- is 168 pair tiles over 74 pairs, 2.27 waves that cost 3.  The
+// single-CTA kernel with 192-column tiles cuts the same problem into 432 tiles of 0.75 tile times over 148 SMs:
+// 2.92 waves that cost 3 x 0.75 = 2.25.  The per-FLOP handicaps of the narrower shapes (kSingle256, kSingle192) are
+// measured figures; a narrower shape is taken only when its estimate beats the pair kernel's by a clear margin.
+static int g_tile_search = 0;   // narrower tiles against partial last waves: off until switched on by the caller
+extern "C" int solar_gemm_tile_search(int on) {
+  const int old = g_tile_search;
+  g_tile_search = on != 0;
+  return old;
+}
+struct TileChoice {
+  bool pair;
+  int ntile;
+};
+static constexpr double kSingle256 = 1.07, kSingle192 = 1.12, kMargin = 0.93;
+static TileChoice choose_tiles(int M, int N, int act) {
+  const int sms = sm_count();
+  auto cdiv = [](long long a, long long b) { return (a + b - 1) / b; };
+  const long long pair_tiles = cdiv(M, 2 * BM) * cdiv(N, BN);
+  if (g_pair_mode == 1) return {true, BN};
+  if (g_pair_mode == 0) return {false, BN};
+  if (g_pair_mode == 2) return {false, act == 2 ? BN : 192};
+  if (pair_tiles < sms / 2) return {false, BN};   // too small to fill the machine with pairs
+  if (!g_tile_search) return {true, BN};
+  const double c_pair = static_cast<double>(cdiv(pair_tiles, sms / 2));
+  const double c_256 = static_cast<double>(cdiv(cdiv(M, BM) * cdiv(N, BN), sms)) * kSingle256;
+  const double c_192 = act == 2 ? 1e30 : static_cast<double>(cdiv(cdiv(M, BM) * cdiv(N, 192), sms)) * 0.75 * kSingle192;
+  if (c_192 < c_pair * kMargin && c_192 <= c_256) return {false, 192};
+  if (c_256 < c_pair * kMargin) return {false, BN};
+  return {true, BN};
 }
 
 static int gemm_entry(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
@@ -679,10 +715,10 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   if (rc) return rc;
   // CTA pairs pay off once there are enough 256-row tiles to fill the machine; small problems stay on the
   // single-CTA kernel.  (The scatter epilogue and its last-CTA signalling are per CTA and work in both.)
-  const bool use_pair = g_pair_mode == 1 || (g_pair_mode < 0 &&
-                        static_cast<long long>((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) >= sm_count() / 2);
+  const TileChoice choice = choose_tiles(M, N, act);
+  const bool use_pair = choice.pair;
   if (layout == 0) {  // B stored [N, K]
-    rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, use_pair ? P_BN_HALF : BN, BK);
+    rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, use_pair ? P_BN_HALF : choice.ntile, BK);
   } else {            // B stored [K, N]
     rc = make_tmap_2d(&tB, B, bf, 2, K, N, ldb, BK, 64);
   }
@@ -695,10 +731,10 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   if (rc) return rc;
   GemmParams p;
   memset(&p.conv, 0, sizeof(p.conv));
-  p.ntile = BN;
+  p.ntile = choice.ntile;
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = use_pair ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
-  p.tiles_n = (N + BN - 1) / BN;
+  p.tiles_n = (N + choice.ntile - 1) / choice.ntile;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.act = act;
   p.accumulate = accumulate;

@@ -312,6 +312,44 @@ def wan5b_suite(seq=27280):
     return rows
 
 
+def tile_modes(seq=3410, iters=10):
+    """Every GEMM of a Wan-5B block at ``seq`` rows per rank under each forced tile shape (CTA pair 256 x 256, one CTA
+    128 x 256, one CTA 128 x 192) and under the launcher's own choice; each forced result is checked against the fp32
+    product of the same operands."""
+    from ..ops import _lib
+
+    lib = _lib.load()
+    d, f = 3072, 14336
+    rows = []
+    for (M, N, K, lay) in [(seq, 3 * d, d, "nt"), (seq, d, d, "nt"), (seq, f, d, "nt"), (seq, d, f, "nt"),
+                           (seq, d, 3 * d, "nn"), (seq, d, f, "nn"), (seq, f, d, "nn"),
+                           (3 * d, d, seq, "tn"), (f, d, seq, "tn"), (d, f, seq, "tn")]:
+        layc = {"nt": ops.NT, "nn": ops.NN, "tn": ops.TN}[lay]
+        g = torch.Generator(device="cuda").manual_seed(1)
+        sa, sb = {"nt": ((M, K), (N, K)), "nn": ((M, K), (K, N)), "tn": ((K, M), (K, N))}[lay]
+        a = torch.randn(sa, device="cuda", generator=g).bfloat16()
+        b = torch.randn(sb, device="cuda", generator=g).bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.float32 if lay == "tn" else torch.bfloat16)
+        af, bf = a[:256].float() if lay != "tn" else a[:, :256].float(), b.float()
+        want = {"nt": lambda: af @ bf.t(), "nn": lambda: af @ bf, "tn": lambda: af.t() @ bf}[lay]()
+        row = {"layout": lay, "M": M, "N": N, "K": K}
+        for name, mode in (("pair256", 1), ("single256", 0), ("single192", 2), ("auto", -1)):
+            old = lib.solar_gemm_pair_mode(mode)
+            search = lib.solar_gemm_tile_search(1)
+            try:
+                ms = time_fn(lambda: ops.gemm(a, b, layc, out=out), iters)
+                err = float((out[:256].float() - want).abs().max() / want.abs().max())
+            finally:
+                lib.solar_gemm_pair_mode(old)
+                lib.solar_gemm_tile_search(search)
+            row[name + "_ms"] = round(ms, 4)
+            row[name + "_rel_err"] = round(err, 5)
+        row["tflops_auto"] = round(2.0 * M * N * K / row["auto_ms"] / 1e9, 1)
+        rows.append(row)
+    ops.check_status()
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -341,6 +379,9 @@ def main():
     c.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("suite")
     s.add_argument("--seq", type=int, default=27280)
+    tl = sub.add_parser("tiles")
+    tl.add_argument("--seq", type=int, default=3410)
+    tl.add_argument("--iters", type=int, default=10)
     pr = sub.add_parser("probe")
     pr.add_argument("--family", required=True)
     pr.add_argument("--rows", type=int, default=27280)
@@ -349,6 +390,10 @@ def main():
     if args.cmd == "probe":
         print(json.dumps({"family": args.family, "per_launch": probe(args.family, args.rows, args.dim)}))
         ops.check_status()
+        return
+    if args.cmd == "tiles":
+        for row in tile_modes(args.seq, args.iters):
+            print(json.dumps(row))
         return
     if args.cmd == "gemm":
         print(json.dumps(bench_gemm(args.m, args.n, args.k, args.layout, args.f32, args.iters)))
