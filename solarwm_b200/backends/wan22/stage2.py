@@ -109,6 +109,22 @@ class WanStage2Trainer:
         return torch.randn(shape, generator=self.gen, device=self.device, dtype=torch.float32).to(dtype)
 
     # ------------------------------------------------------------------------------------
+    def rollout_cache(self, grid_hw):
+        """The student's rolling KV cache (sink + window + one chunk, per block) for a token grid, allocated ONCE per
+        geometry and reset between rollouts, so no step of the training loop allocates cache memory (reference:
+        allocate_kv_cache / allocate_crossattn_cache, solar/backends/wan22/runtime/stage2.py:1758-1854; the projected
+        text keys / values, its cross-attention cache, are rebuilt per sample by ``encode_text``)."""
+        caches = self.__dict__.setdefault("_rollout_caches", {})
+        key = tuple(int(v) for v in grid_hw)
+        cache = caches.get(key)
+        if cache is None:
+            o = self.opts
+            cache = caches[key] = allocate_kv_cache(self.student, grid_hw=key, chunk_frames=o.chunk_frames,
+                                                    window_frames=o.window_chunks * o.chunk_frames + o.sink_frames,
+                                                    sink_frames=o.sink_frames, device=self.device)
+        cache.reset()
+        return cache
+
     @torch.no_grad()
     def rollout(self, text, shape, dtype, exit_index: Optional[int] = None):
         """Chunked no-grad rollout.  Returns (generated x0 [1,F,C,H,W], exit timestep, exit_index)."""
@@ -122,9 +138,7 @@ class WanStage2Trainer:
             exit_index = int(idx.item())
         runner = CausalWanRunner(self.student, sp=None)
         ph, pw = self.cfg.patch_size[1], self.cfg.patch_size[2]
-        cache = allocate_kv_cache(self.student, grid_hw=(H // ph, W // pw), chunk_frames=o.chunk_frames,
-                                  window_frames=o.window_chunks * o.chunk_frames + o.sink_frames,
-                                  sink_frames=o.sink_frames, device=self.device)
+        cache = self.rollout_cache((H // ph, W // pw))
         runner.encode_text(cache, text)
         outs = []
         for f0 in range(0, F, o.chunk_frames):

@@ -64,6 +64,16 @@ class KVCache:
     position_cap: int = 0              # the newest frame's RoPE position never exceeds position_cap - 1
     newest_pos: int = -1               # position the newest committed non-sink frame was rotated to
 
+    def reset(self) -> None:
+        """Start a new stream in the same buffers (nothing is cleared: rows beyond ``committed_frames`` are never read);
+        the projected text of the previous stream is dropped."""
+        self.committed_frames = self.total_frames = 0
+        self.newest_pos = -1
+        if self.cam_inv is not None:
+            self.cam_inv.copy_(torch.eye(4, device=self.cam_inv.device).expand_as(self.cam_inv))
+        for lc in self.layers:
+            lc.text_k = lc.text_v = None
+
     @property
     def positions_saturated(self) -> bool:
         """The newest position has reached the cap: from here on every chunk moves the history by its own length."""

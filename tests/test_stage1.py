@@ -189,3 +189,28 @@ def test_stage1_anyflow_step_with_and_without_prefix_reuse_agree():
         grads.append(tr.model.get_parameter("blocks.0.ffn.0.weight").grad.clone())
     assert abs(losses[0] - losses[1]) < 1e-5 * max(1.0, abs(losses[0]))
     assert torch.allclose(grads[0], grads[1], atol=1e-6, rtol=1e-4)
+
+
+def test_stage2_rollouts_share_one_preallocated_cache():
+    """The rollout cache is allocated once per token grid and reset between rollouts; a rollout that follows another
+    one (and therefore runs in used buffers) equals the same rollout in a fresh trainer."""
+    from solarwm_b200.backends.wan22.stage2 import Stage2Options, WanStage2Trainer
+
+    cfg, _ = tiny()
+    opts = Stage2Options(chunk_frames=2, window_chunks=1, critic_updates_per_student=1, denoising_steps=(1000.0, 500.0))
+
+    def make():
+        tr = WanStage2Trainer(cfg, "cpu", opts, dtype=torch.float32)
+        with torch.no_grad():
+            tr.student.get_parameter("head.head.weight").normal_(0, 0.05, generator=torch.Generator().manual_seed(3))
+        return tr
+
+    text = torch.randn(1, 8, 32, generator=torch.Generator().manual_seed(4))
+    a, b = make(), make()
+    a.rollout(text, (1, 6, 4, 4, 4), torch.float32, exit_index=0)           # leaves the buffers used (window slid)
+    cache = a.rollout_cache((2, 2))
+    assert a.rollout_cache((2, 2)) is cache and cache.committed_frames == 0 and cache.layers[0].text_k is None
+    b.gen.set_state(a.gen.get_state())
+    got, _, _ = a.rollout(text, (1, 6, 4, 4, 4), torch.float32, exit_index=1)
+    want, _, _ = b.rollout(text, (1, 6, 4, 4, 4), torch.float32, exit_index=1)
+    assert torch.equal(got, want)
