@@ -350,6 +350,27 @@ def tile_modes(seq=3410, iters=10):
     return rows
 
 
+def bwd_trace(seq=8192, heads=12, head_dim=128):
+    """Cycle counters the attention-backward kernels keep for CTA (0, 0, 0) of each launch (``clock64`` deltas of
+    its roles), read back after one backward pass."""
+    import ctypes
+
+    from ..ops import _lib
+    from ..ops.attention_native import attn_bwd, attn_fwd
+
+    lib = _lib.load()
+    lib.solar_attn_bwd_trace.argtypes = [ctypes.c_int, ctypes.c_void_p]
+    q, k, v = (torch.randn(1, seq, heads, head_dim, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    o, lse = attn_fwd(q, k, v, head_dim ** -0.5)
+    do = torch.randn_like(o)
+    lib.solar_attn_bwd_trace(1, None)
+    attn_bwd(q, k, v, o, lse, do, head_dim ** -0.5)
+    torch.cuda.synchronize()
+    out = (ctypes.c_longlong * 32)()
+    lib.solar_attn_bwd_trace(0, out)
+    return {"seq": seq, "heads": heads, "head_dim": head_dim, "counters": list(out)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -379,6 +400,9 @@ def main():
     c.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("suite")
     s.add_argument("--seq", type=int, default=27280)
+    bt = sub.add_parser("bwd-trace")
+    bt.add_argument("--seq", type=int, default=8192)
+    bt.add_argument("--heads", type=int, default=12)
     tl = sub.add_parser("tiles")
     tl.add_argument("--seq", type=int, default=3410)
     tl.add_argument("--iters", type=int, default=10)
@@ -390,6 +414,9 @@ def main():
     if args.cmd == "probe":
         print(json.dumps({"family": args.family, "per_launch": probe(args.family, args.rows, args.dim)}))
         ops.check_status()
+        return
+    if args.cmd == "bwd-trace":
+        print(json.dumps(bwd_trace(args.seq, args.heads)))
         return
     if args.cmd == "tiles":
         for row in tile_modes(args.seq, args.iters):
