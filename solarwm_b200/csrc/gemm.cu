@@ -484,7 +484,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM;
-        const int nb0 = tn * BN + static_cast<int>(rank) * P_BN_HALF;      // this CTA's half of the B tile
+        const int half = p.ntile >> 1;                                     // B columns staged per CTA
+        const int nb0 = tn * p.ntile + static_cast<int>(rank) * half;      // this CTA's half of the B tile
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -493,7 +494,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           uint8_t* sa = smem + stage * P_STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           const uint32_t full_leader = mapa_u32(smem_u32(&full_bar[stage]), 0);
-          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);   // both CTAs' bytes
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * (A_BYTES + half * BK * 2));   // both CTAs' bytes
           const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
@@ -503,7 +504,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < P_BN_HALF / 64; ++c)
+            for (int c = 0; c < half / 64; ++c)
               tma_load_2d_pair(sb + c * (64 * BK * 2), &tmB, full_leader, nb0 + c * 64, k0);
           } else {
             tma_load_2d_pair(sb, &tmB, full_leader, k0, nb0);
@@ -534,7 +535,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           umma_commit_pair(bar_peer + off);
         }
       };
-      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      const uint32_t idesc = umma_idesc_bf16(2 * BM, p.ntile, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -580,13 +581,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int tile = pair; tile < num_tiles; tile += n_pairs, ++local) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-      const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM, n0 = tn * BN;
+      const int m0 = tm * 2 * BM + static_cast<int>(rank) * BM, n0 = tn * p.ntile;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane);
+      epilogue_tile<OUT_F32>(tmC, p, sc, t_row, m0 + q * 32, n0, my_buf, buf, lane, 0, 0, 0, p.ntile);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + acc * 8);
     }
@@ -653,47 +654,35 @@ using namespace solar;
 // out_f32: C is fp32 instead of bf16.  accumulate: C += (atomic-free TMA reduce-add).
 // status: optional device int that receives a non-zero code if a bounded wait gave up.
 // -1: choose per problem; 0: single-CTA kernel with 256-column tiles only; 1: CTA-pair kernel whenever legal;
-// 2: single-CTA kernel with 192-column tiles (for measurements).
+// 2: single-CTA kernel with 192-column tiles, 3: CTA-pair kernel with 128-column tiles (for measurements).
 static int g_pair_mode = -1;
 extern "C" int solar_gemm_pair_mode(int mode) {
   const int old = g_pair_mode;
-  if (mode >= -1 && mode <= 2) g_pair_mode = mode;
+  if (mode >= -1 && mode <= 3) g_pair_mode = mode;
   return old;
 }
 
 // Tile shape per problem.  Both kernels are persistent with one tile (or CTA-pair tile) in flight per SM, so a
-// problem costs ceil(tiles / slots) waves of its tile time.  The CTA-pair kernel (256 x 256 over two SMs) is the
-// fastest per FLOP, but with few tiles its last wave is mostly empty: a [3410 x 3072] product -- the out-projection
-// and FFN-down shapes of 8-way sequence parallelism -- is 168 pair tiles over 74 pairs, 2.27 waves that cost 3.  The
-// single-CTA kernel with 192-column tiles cuts the same problem into 432 tiles of 0.75 tile times over 148 SMs:
-// 2.92 waves that cost 3 x 0.75 = 2.25.  The per-FLOP handicaps of the narrower shapes (kSingle256, kSingle192) are
-// measured figures; a narrower shape is taken only when its estimate beats the pair kernel's by a clear margin.
-static int g_tile_search = 0;   // narrower tiles against partial last waves: off until switched on by the caller
-extern "C" int solar_gemm_tile_search(int on) {
-  const int old = g_tile_search;
-  g_tile_search = on != 0;
-  return old;
-}
+// problem costs ceil(tiles / slots) waves of its tile time.  With few tiles the last wave is mostly empty: a
+// [3410 x 3072] product -- the out-projection and FFN-down shapes of 8-way sequence parallelism -- is 168 pair tiles
+// over 74 pairs, 2.27 waves that cost 3 (measured: 1,232 TFLOP/s where the same kernel reaches 1,570 on full waves).
+// Narrower tiles do NOT recover that; measured on the ten GEMMs of a Wan-5B block at 3,410 / 6,820 / 13,640 rows
+// (sum of the ten, ms): pair 256 x 256 1.90 / 3.49 / 6.74; pair 256 x 128 (modes 3) 2.59 / 4.92 / 10.25; one CTA
+// 128 x 256 and 128 x 192 (modes 0, 2) 15-25 % behind the pair kernel on every shape.  So the choice is only between
+// the pair kernel and, for problems too small to fill the machine with pairs, the single-CTA kernel; the other
+// shapes stay selectable for measurements (`kernel_bench tiles`).
 struct TileChoice {
   bool pair;
   int ntile;
 };
-static constexpr double kSingle256 = 1.07, kSingle192 = 1.12, kMargin = 0.93;
 static TileChoice choose_tiles(int M, int N, int act) {
   const int sms = sm_count();
   auto cdiv = [](long long a, long long b) { return (a + b - 1) / b; };
-  const long long pair_tiles = cdiv(M, 2 * BM) * cdiv(N, BN);
   if (g_pair_mode == 1) return {true, BN};
   if (g_pair_mode == 0) return {false, BN};
   if (g_pair_mode == 2) return {false, act == 2 ? BN : 192};
-  if (pair_tiles < sms / 2) return {false, BN};   // too small to fill the machine with pairs
-  if (!g_tile_search) return {true, BN};
-  const double c_pair = static_cast<double>(cdiv(pair_tiles, sms / 2));
-  const double c_256 = static_cast<double>(cdiv(cdiv(M, BM) * cdiv(N, BN), sms)) * kSingle256;
-  const double c_192 = act == 2 ? 1e30 : static_cast<double>(cdiv(cdiv(M, BM) * cdiv(N, 192), sms)) * 0.75 * kSingle192;
-  if (c_192 < c_pair * kMargin && c_192 <= c_256) return {false, 192};
-  if (c_256 < c_pair * kMargin) return {false, BN};
-  return {true, BN};
+  if (g_pair_mode == 3) return {true, 128};
+  return {cdiv(M, 2 * BM) * cdiv(N, BN) >= sms / 2, BN};
 }
 
 static int gemm_entry(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
@@ -718,7 +707,7 @@ static int gemm_entry(const void* A, const void* B, void* C, const void* bias, i
   const TileChoice choice = choose_tiles(M, N, act);
   const bool use_pair = choice.pair;
   if (layout == 0) {  // B stored [N, K]
-    rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, use_pair ? P_BN_HALF : choice.ntile, BK);
+    rc = make_tmap_2d(&tB, B, bf, 2, N, K, ldb, use_pair ? choice.ntile / 2 : choice.ntile, BK);
   } else {            // B stored [K, N]
     rc = make_tmap_2d(&tB, B, bf, 2, K, N, ldb, BK, 64);
   }

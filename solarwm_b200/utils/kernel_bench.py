@@ -333,15 +333,13 @@ def tile_modes(seq=3410, iters=10):
         af, bf = a[:256].float() if lay != "tn" else a[:, :256].float(), b.float()
         want = {"nt": lambda: af @ bf.t(), "nn": lambda: af @ bf, "tn": lambda: af.t() @ bf}[lay]()
         row = {"layout": lay, "M": M, "N": N, "K": K}
-        for name, mode in (("pair256", 1), ("single256", 0), ("single192", 2), ("auto", -1)):
+        for name, mode in (("pair256", 1), ("pair128", 3), ("single256", 0), ("single192", 2), ("auto", -1)):
             old = lib.solar_gemm_pair_mode(mode)
-            search = lib.solar_gemm_tile_search(1)
             try:
                 ms = time_fn(lambda: ops.gemm(a, b, layc, out=out), iters)
                 err = float((out[:256].float() - want).abs().max() / want.abs().max())
             finally:
                 lib.solar_gemm_pair_mode(old)
-                lib.solar_gemm_tile_search(search)
             row[name + "_ms"] = round(ms, 4)
             row[name + "_rel_err"] = round(err, 5)
         row["tflops_auto"] = round(2.0 * M * N * K / row["auto_ms"] / 1e9, 1)
