@@ -593,9 +593,13 @@ def run_realtime(args):
     cfg = h3_preset(args.h3)
     model = H3DiT(cfg, device=f"cuda:{local}", dtype=torch.bfloat16, seed=0)
     scfg = H3StreamConfig() if args.h3 == "h3_33b" else H3StreamConfig(grid_hw=(8, 16))
-    # the chunk evaluation is graph-captured on one GPU; with SP > 1 it contains NCCL exchanges and runs eagerly
-    # (a captured run with NCCL all-to-alls did not finish on this pool; not retried)
-    scfg.use_cuda_graph = world == 1
+    # the chunk evaluation is graph-captured on one GPU and, with the fused head exchange (no library collective inside
+    # the evaluation), at SP > 1 too; the NCCL form runs eagerly (a captured run with NCCL all-to-alls did not finish
+    # on this pool: collectives enqueued from a capture need every rank's capture to reach them in step, which the
+    # eager warm-up chunks of the generator do not guarantee; not retried)
+    if args.sp_transport != "fused":
+        scfg.sp_exchange = "collective"
+    scfg.use_cuda_graph = args.graph != "off" and (world == 1 or scfg.sp_exchange == "fused")
     gen = H3StreamingGenerator(model, scfg, sp=sp)
     g = torch.Generator().manual_seed(0)
     text = torch.randn(args.prompt_tokens, cfg.text_dim, generator=g).pin_memory()
