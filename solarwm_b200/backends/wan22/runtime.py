@@ -117,7 +117,10 @@ def activation_and_sharding_options(train: Mapping[str, Any], world_size: int) -
     ``activation_memory.keep_blocks`` / ``.lean``: how many of the last blocks stay resident, and whether resident
     blocks rebuild their norm outputs and FFN hidden tensor in backward;
     optimizer sharding is on with ``zero.enabled`` or ``fsdp.enabled`` (more than one rank), its transport is
-    ``zero.transport``: "collective" (NCCL) or "fused" (peer loads / stores over NVLink)."""
+    ``zero.transport``: "collective" (NCCL) or "fused" (peer loads / stores over NVLink);
+    ``fsdp.shard_parameters`` (fused transport only) also shards every block's parameters and gradient buffers with
+    just-in-time gathers; ``cuda_graph`` captures the whole optimizer step once and replays it (fused transports or
+    one rank, no gradient accumulation)."""
     fsdp = train.get("fsdp", {}) or {}
     ac = fsdp.get("activation_checkpointing", False)
     if isinstance(ac, str):
@@ -133,8 +136,12 @@ def activation_and_sharding_options(train: Mapping[str, Any], world_size: int) -
     transport = str(zero_cfg.get("transport", "collective"))
     if transport not in ("collective", "fused"):
         raise ConfigurationError("train.zero.transport must be collective or fused")
+    zero = bool(zero_cfg.get("enabled", fsdp.get("enabled", False))) and world_size > 1
+    shard = bool(fsdp.get("shard_parameters", False)) and zero
+    if shard and transport != "fused":
+        raise ConfigurationError("train.fsdp.shard_parameters needs train.zero.transport: fused")
     return dict(checkpointing=mode, keep_blocks=int(mem.get("keep_blocks", 0)), lean_kept=bool(mem.get("lean", False)),
-                zero=bool(zero_cfg.get("enabled", fsdp.get("enabled", False))) and world_size > 1, zero_transport=transport)
+                zero=zero, zero_transport=transport, shard_params=shard, cuda_graph=bool(train.get("cuda_graph", False)))
 
 
 class WanStage0p5Runtime:
@@ -178,6 +185,7 @@ class WanStage0p5Runtime:
             self.trainer = trainer_cls(self.arch, self.ctx.device, opts, sp=sp_ctx, model=model,
                                        dp_group=self.ctx.dp_group, dp_size=topo.dp_size, heap=heap)
         self.trainer.gen.manual_seed(objective_seed(seed, topo.dp_rank))
+        self._graphed = bool(getattr(opts, "cuda_graph", False)) and self.ctx.device.type == "cuda"
         self.scheduler = WarmupCosine(self.trainer.optimizer, warmup_steps=int(train.get("warmup_steps", 0)),
                                       total_steps=int(train["max_steps"]),
                                       min_lr_ratio=float(opt.get("min_lr_ratio", 0.1)))
@@ -256,7 +264,10 @@ class WanStage0p5Runtime:
         if want_zero:
             from ...parallel.symm import SymmetricHeap
 
-            heap = SymmetricHeap(sum(u.numel_m * 6 + u.numel_v * 8 + 2048 for u in model.units()) + (1 << 16), None)
+            from ...parallel.zero import fused_heap_bytes
+
+            sharded = [b.unit for b in model.blocks] if getattr(opts, "shard_params", False) else ()
+            heap = SymmetricHeap(fused_heap_bytes(model.units(), topo.raw_world_size, sharded) + (1 << 16), None)
         return sp_ctx, heap
 
     def zero_grad(self) -> None:
@@ -267,9 +278,15 @@ class WanStage0p5Runtime:
         self.batches_consumed += 1
         dev = self.ctx.device
         seed_digest = hashlib.blake2s(self.trainer.gen.get_state().cpu().numpy().tobytes()).hexdigest()
-        loss = self.trainer.microbatch(batch["latents"].to(dev, non_blocking=True),
-                                       batch["text"].to(dev, non_blocking=True),
-                                       None if "y" not in batch else batch["y"].to(dev, non_blocking=True))
+        if self._graphed:
+            # ``train.cuda_graph``: the WHOLE optimizer step (this microbatch, the reduce-scatter, clipping and the
+            # sharded AdamW with its device-side skip on a non-finite norm) is one replayed graph; the two optimizer
+            # hooks that follow only report what it computed
+            loss = self.trainer.train_step({k: batch[k] for k in ("latents", "text", "y") if k in batch})
+        else:
+            loss = self.trainer.microbatch(batch["latents"].to(dev, non_blocking=True),
+                                           batch["text"].to(dev, non_blocking=True),
+                                           None if "y" not in batch else batch["y"].to(dev, non_blocking=True))
         value = float(loss.item())
         if value != value or value in (float("inf"), float("-inf")):
             raise BackendContractError(f"non-finite Wan Stage0.5 loss: {value}")
@@ -287,6 +304,10 @@ class WanStage0p5Runtime:
 
     def prepare_optimizer_step(self) -> GradientStatus:
         tr = self.trainer
+        if self._graphed:
+            value = float(tr.last_grad_norm.item())
+            self._check_device_waits(value)
+            return GradientStatus(finite=value == value and value not in (float("inf"), float("-inf")), norm=value)
         tr.model.finalize_grads()
         if hasattr(tr.optimizer, "sharded_step"):
             norm = tr.optimizer.global_grad_norm(tr.optimizer.reduce_scatter_grads())
@@ -325,7 +346,8 @@ class WanStage0p5Runtime:
                                           dist=dist if self.ctx.topology.raw_world_size > 1 else None)
 
     def optimizer_step(self) -> None:
-        self.trainer.optimizer.step()
+        if not self._graphed:
+            self.trainer.optimizer.step()
 
     def scheduler_step(self) -> None:
         self.scheduler.step()
