@@ -397,6 +397,17 @@ class H3StreamingGenerator:
         self._slide()
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
+            if self.fx is not None:
+                # the fused exchange's device-side waits are bounded: one that gave up set the status word and let the
+                # consumers run on what had arrived.  The chunk is complete here (the synchronize above), so reading
+                # the word costs nothing; a non-zero word means a peer fell behind or left, and the chunk is discarded
+                # (the peers' own waits run out the same way, so every rank raises)
+                from ..ops.functional import read_status
+
+                code = read_status(self.device, clear=True)
+                if code:
+                    raise RuntimeError(f"streaming chunk {self.chunk_index}: a device-side exchange wait gave up "
+                                       f"(code {code}); a sequence-parallel peer did not deliver its rows in time")
         self.timings.append(ChunkTiming(self.chunk_index, (time.perf_counter() - t0) * 1e3, use_graph))
         self.chunk_index += 1
         h, w = cfg.grid_hw
