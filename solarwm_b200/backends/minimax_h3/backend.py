@@ -93,7 +93,7 @@ class MiniMaxH3Backend:
 
     def train(self, config):
         route = validate_route(config)
-        if route.stage in ("stage1", "stage2"):
+        if route.stage == "stage2":
             return self._train_causal(config, route)
         from .runtime import run_training
 

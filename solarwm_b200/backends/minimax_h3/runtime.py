@@ -183,6 +183,21 @@ class H3TrainingRuntime:
         self.ema = AdapterEMA(self.optimizer, float(e.get("decay", 0.999))) if e.get("enabled", True) else None
         self.ema_start, self.ema_every = int(e.get("start_step", 0)), int(e.get("update_every_steps", 1))
         self.gen = torch.Generator(device=dev).manual_seed(objective_seed(self.seed, topo.dp_rank))
+        self.core = None
+        if self.route.stage == "stage1":
+            # teacher forcing under the block-causal mask: one packed sample per replica, so data parallelism only
+            if topo.sp_size > 1:
+                raise BackendContractError("H3 Stage1 packs clean and noisy halves of one video per rank: "
+                                           "sequence_parallel_size must be 1 (use data parallelism)")
+            from .stage1 import H3Stage1Trainer
+
+            causal = config["model"].get("causal", {}) or {}
+            self.core = H3Stage1Trainer(model_config, dev, model=self.model, optimizer=self.optimizer, generator=self.gen,
+                                        objective="anyflow" if self.route.objective.startswith("anyflow") else "tf_fm",
+                                        chunk_latents=int(causal.get("chunk_latents", 5)),
+                                        window_chunks=int(causal.get("window_chunks", 5)))
+        elif self.route.stage != "stage0p5":
+            raise BackendContractError(f"no multi-rank H3 runtime for {self.route.stage}")
         self._global_step, self.batches_consumed = 0, 0
         self.checkpoint_id = "init:random"
         self.plan_fingerprint = f"h3-{self.route.stage}-seed{self.seed}-dp{topo.dp_size}"
@@ -222,7 +237,8 @@ class H3TrainingRuntime:
         else:
             from ...data.synthetic import h3_sample
 
-            s = h3_sample(latent_frames=int(data.get("latent_frames", 3)), height=int(data.get("latent_height", 8)),
+            default_frames = 3 if self.core is None else 2 * self.core.chunk_latents
+            s = h3_sample(latent_frames=int(data.get("latent_frames", default_frames)), height=int(data.get("latent_height", 8)),
                           width=int(data.get("latent_width", 8)), prompt_len=int(data.get("prompt_len", 8)),
                           text_dim=cfg.text_dim, seed=self.seed * 100003 + ordinal)
             ident = f"synthetic-{ordinal:08d}"
@@ -231,6 +247,15 @@ class H3TrainingRuntime:
 
     def train_microbatch(self, micro_index: int, grad_accum: int) -> MicrobatchResult:
         ident, ordinal, sample = self._next_sample()
+        if self.core is not None:
+            objective = self.core.compute_loss(sample)
+            (objective / grad_accum).backward()
+            loss = float(objective.detach())
+            if not math.isfinite(loss):
+                raise BackendContractError(f"non-finite loss on {ident}")
+            identity = BatchIdentity((ident,), (0,), (objective_seed(self.seed, self.topology.dp_rank) + ordinal,),
+                                     self.checkpoint_id, self.plan_fingerprint)
+            return MicrobatchResult(identity, {"loss": loss})
         dev, dt = self.device, self.model.dtype
         lat, anchor = sample["target_latents"].to(dev), sample["anchor_latents"].to(dev)
         prompt = sample["prompt_embeds"].to(dev)

@@ -184,13 +184,16 @@ def suffix_forward(model: H3DiT, *, captured, noisy_rows, t_chunks: torch.Tensor
 class H3Stage1Trainer:
     def __init__(self, cfg, device, *, objective: str = "tf_fm", chunk_latents: int = 5, window_chunks: int = 5,
                  lr: float = 1e-4, seed: int = 0, diffusion_ratio: float = 0.5, consistency_ratio: float = 0.25,
-                 epsilon: float = 0.005, reuse_prefix: bool = True):
+                 epsilon: float = 0.005, reuse_prefix: bool = True, model=None, optimizer=None, generator=None):
+        """``model`` / ``optimizer`` / ``generator``: objects a training runtime already owns (it then drives
+        ``compute_loss`` itself and this class builds nothing)."""
         self.reuse_prefix = bool(reuse_prefix)     # AnyFlow probes reuse the trainable evaluation's prefix K / V
         dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
-        self.model = H3DiT(cfg, device=device, dtype=dtype, seed=seed)
-        self.opt = FP32MasterAdamW(self.model.trainable_parameters(), lr=lr)
+        self.model = model if model is not None else H3DiT(cfg, device=device, dtype=dtype, seed=seed)
+        self.opt = optimizer if optimizer is not None else FP32MasterAdamW(self.model.trainable_parameters(), lr=lr)
         self.device = torch.device(device)
-        self.gen = torch.Generator(device=self.device).manual_seed(seed * 100003 + 1)
+        self.gen = generator if generator is not None else \
+            torch.Generator(device=self.device).manual_seed(seed * 100003 + 1)
         self.objective, self.chunk_latents, self.window_chunks = objective, chunk_latents, window_chunks
         self.ratios, self.epsilon = (diffusion_ratio, consistency_ratio), float(epsilon)
 
@@ -215,6 +218,16 @@ class H3Stage1Trainer:
                                        cameras=sample.get("camera_w2c"))
 
     def train_step(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        loss = self.compute_loss(sample)
+        loss.backward()
+        self.opt.gather_grads()
+        self.opt.clip_(1.0)
+        self.opt.step()
+        self.opt.zero_grad()
+        return loss.detach()
+
+    def compute_loss(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        """The objective of one packed sample (teacher-forcing flow matching or AnyFlow), with its graph."""
         dev = self.device
         lat = sample["target_latents"].to(dev)
         C, F, H, W = lat.shape
@@ -251,9 +264,4 @@ class H3Stage1Trainer:
             chunk_loss = per_chunk(resid.pow(2).mean(dim=1))
             chunk_loss = af.adaptive_rescale(chunk_loss, pairs.is_diffusion)
             loss = chunk_loss.mean()
-        loss.backward()
-        self.opt.gather_grads()
-        self.opt.clip_(1.0)
-        self.opt.step()
-        self.opt.zero_grad()
-        return loss.detach()
+        return loss

@@ -355,21 +355,24 @@ def test_sharded_optimizer_and_ema_checkpoint_resumes_exactly(tmp_path):
             assert rb[r]["steps"][s] == ra[r]["steps"][s], (s, r, rb[r]["steps"][s], ra[r]["steps"][s])
 
 
-def _h3_config(root, world, sp, resume_from=None, max_steps=4, save_every=2):
+def _h3_config(root, world, sp, resume_from=None, max_steps=4, save_every=2, stage="stage0p5"):
+    route = {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching"} if stage == "stage0p5" else \
+        {"stage": "stage1", "causal_mode": "teacher_forcing", "objective": "anyflow_forward_map", "objective_variant": "v1_5"}
+    frames = {"latent_frames": 3, "latent_height": 8, "latent_width": 8} if stage == "stage0p5" else \
+        {"latent_frames": 4, "latent_height": 4, "latent_width": 4}
     return {"schema": "solarwm.run.v1", "action": "train", "name": "h3-multi",
             "model": {"family": "minimax_h3", "architecture": "tiny", "adapter": {"rank": 4},
-                      "camera_translation_transform": "logd4"},
-            "data": {"source": "synthetic", "seed": 0, "pixel_frames": 158, "latent_frames": 3, "latent_height": 8,
-                     "latent_width": 8, "prompt_len": 7},
+                      "camera_translation_transform": "logd4", "causal": {"chunk_latents": 2, "window_chunks": 1}},
+            "data": {"source": "synthetic", "seed": 0, "pixel_frames": 158, "prompt_len": 7, **frames},
             "distributed": {"world_size": world, "sequence_parallel_size": sp},
-            "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "max_steps": max_steps,
+            "train": {**route, "max_steps": max_steps,
                       "grad_accum": 1, "optimizer": {"lr": 1e-3, "warmup_steps": 1}, "ema": {"enabled": True, "decay": 0.9}},
             "checkpoint": ({"mode": "full_resume", "resume_from": resume_from} if resume_from else {"mode": "none"}),
             "runtime": {"output_dir": root, "device": "cpu", "save_every": 0 if resume_from else save_every,
                         "save_final": not resume_from}}
 
 
-def _h3_train_worker(rank, world, path, out, root, sp, resume_from):
+def _h3_train_worker(rank, world, path, out, root, sp, resume_from, stage="stage0p5"):
     import json
     import os
 
@@ -377,7 +380,7 @@ def _h3_train_worker(rank, world, path, out, root, sp, resume_from):
     _init(rank, world, path)
     from solarwm_b200.registry import load_backend
 
-    load_backend("minimax_h3").train(_h3_config(root, world, sp, resume_from))
+    load_backend("minimax_h3").train(_h3_config(root, world, sp, resume_from, stage=stage))
     events = [json.loads(l) for l in open(os.path.join(root, "events", f"rank-{rank:05d}.jsonl"))]
     steps = {e["step"]: (e["losses"], e["gradient_norm"]) for e in events if e["event"] == "optimizer_step"}
     torch.save({"steps": steps}, f"{out}.{rank}")
@@ -421,3 +424,14 @@ def test_h3_data_parallel_ranks_average_their_gradients(tmp_path):
     mp.spawn(_h3_train_worker, args=(2, str(tmp_path / "rdv"), out, str(tmp_path / "r"), 1, None), nprocs=2, join=True)
     got = [torch.load(f"{out}.{r}", weights_only=False)["steps"] for r in range(2)]
     assert all(got[0][s][0] != got[1][s][0] for s in got[0]) and all(got[0][s][1] == got[1][s][1] for s in got[0])
+
+
+def test_h3_stage1_anyflow_runs_data_parallel_and_refuses_sequence_parallel(tmp_path):
+    """Stage1 (teacher forcing, AnyFlow objective) behind the same runtime: two replicas on different samples apply one
+    averaged adapter gradient; SP > 1 is refused up front (one packed video per rank)."""
+    out = str(tmp_path / "s1")
+    mp.spawn(_h3_train_worker, args=(2, str(tmp_path / "rdv"), out, str(tmp_path / "r"), 1, None, "stage1"), nprocs=2, join=True)
+    got = [torch.load(f"{out}.{r}", weights_only=False)["steps"] for r in range(2)]
+    assert sorted(got[0]) == [1, 2, 3, 4]
+    assert all(got[0][s][0] != got[1][s][0] for s in got[0]) and all(got[0][s][1] == got[1][s][1] for s in got[0])
+    assert (tmp_path / "r" / "checkpoint_model_000004" / "ema.pt").is_file()
