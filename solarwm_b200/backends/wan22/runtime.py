@@ -208,7 +208,7 @@ class WanStage0p5Runtime:
         verified, payload = ckpt.load_checkpoint(
             c["resume_from"], model=self.trainer.model, optimizer=self.trainer.optimizer, scheduler=self.scheduler,
             mode=mode, expected=self.contract, weight_source=str(c.get("weight_source", "live")),
-            map_location=self.ctx.device)
+            map_location=self.ctx.device, ema_source=c.get("ema_source"))
         self.checkpoint_id = verified.manifest_digest
         if mode == "full_resume":
             self._step = int(payload["global_step"])

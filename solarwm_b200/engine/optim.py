@@ -12,7 +12,7 @@ with ~8 element-wise kernels each, ``ShardedEMA.update`` (solar/training/ema.py:
 """
 from __future__ import annotations
 
-from typing import Iterable, Optional
+from typing import Iterable, Mapping, Optional
 
 import torch
 
@@ -145,6 +145,73 @@ class FlatAdamW:
                     if theirs.numel() != total:
                         raise ValueError("optimizer state tensor does not cover the whole flat buffer")
                     mine.copy_(theirs[a:b])
+
+    # weights that arrive from outside the optimizer ----------------------------------------------------------------
+    def _live_shard(self, index: int, key: str) -> torch.Tensor:
+        """This rank's range of the live parameters of unit ``index`` (``key``: "m" matrices, "v" vectors)."""
+        u = self.units[index]
+        a, b = self.state[index][key]["range"]
+        return (u.flat if key == "m" else u.flat_v)[a:b]
+
+    @torch.no_grad()
+    def adopt_live_weights(self, reset_ema: bool = True) -> None:
+        """The live parameters were overwritten from outside (a weights-only checkpoint load): take them as the fp32
+        master weights -- otherwise the first step would write the OLD master back over them -- and, with
+        ``reset_ema``, restart the EMA shadow from them.  Moments and the step counter are left alone."""
+        for i, st in enumerate(self.state):
+            for key in ("m", "v"):
+                live = self._live_shard(i, key).float()
+                if st[key]["master"] is not None:
+                    st[key]["master"].copy_(live)
+                if reset_ema and st[key]["ema"] is not None:
+                    st[key]["ema"].copy_(live)
+
+    @torch.no_grad()
+    def load_named_ema(self, model, named: Mapping[str, torch.Tensor]) -> None:
+        """EMA shadow from a parameter-name -> tensor mapping (e.g. a checkpoint's averaged weights next to its live
+        ones); every rank copies the part of each parameter that falls into its own range.  Strict about names and
+        shapes."""
+        if self.ema_decay is None:
+            raise ValueError("the optimizer was built without an EMA shadow")
+        index = {id(u): i for i, u in enumerate(self.units)}
+        params = dict(model.named_parameters())
+        if set(params) != set(named):
+            odd = sorted(set(params) ^ set(named))
+            raise ValueError(f"averaged weights do not match the model (e.g. {odd[:4]})")
+        for name, p in params.items():
+            slot = p.flat_unit.slots[p.flat_name]
+            src = named[name]
+            if tuple(src.shape) != tuple(slot.shape):
+                raise ValueError(f"{name}: averaged weight has shape {tuple(src.shape)}, the model {tuple(slot.shape)}")
+            st = self.state[index[id(p.flat_unit)]]["v" if slot.is_vector else "m"]
+            a, b = st["range"]
+            lo, hi = max(a, slot.offset), min(b, slot.offset + slot.numel)
+            if lo < hi:
+                st["ema"][lo - a:hi - a].copy_(src.reshape(-1)[lo - slot.offset:hi - slot.offset].to(st["ema"].device, torch.float32))
+
+    @torch.no_grad()
+    def load_named_moments(self, model, named: Mapping[str, Mapping[str, torch.Tensor]], step: int) -> None:
+        """Adam moments from a per-parameter mapping ``{name: {"exp_avg", "exp_avg_sq"}}`` -- the form a
+        ``torch.optim.AdamW`` full state takes once its entries are keyed by parameter name (the reference's
+        checkpoints) -- packed into the flat buffers; parameters the mapping does not name keep zero moments only if
+        ``named`` is empty for them everywhere, otherwise the mismatch is an error."""
+        index = {id(u): i for i, u in enumerate(self.units)}
+        params = dict(model.named_parameters())
+        if set(params) != set(named):
+            odd = sorted(set(params) ^ set(named))
+            raise ValueError(f"optimizer entries do not match the model's parameters (e.g. {odd[:4]})")
+        for name, p in params.items():
+            slot = p.flat_unit.slots[p.flat_name]
+            st = self.state[index[id(p.flat_unit)]]["v" if slot.is_vector else "m"]
+            a, b = st["range"]
+            lo, hi = max(a, slot.offset), min(b, slot.offset + slot.numel)
+            for field in ("exp_avg", "exp_avg_sq"):
+                src = named[name][field]
+                if src.numel() != slot.numel:
+                    raise ValueError(f"{name}: {field} has {src.numel()} elements, the parameter {slot.numel}")
+                if lo < hi:
+                    st[field][lo - a:hi - a].copy_(src.reshape(-1)[lo - slot.offset:hi - slot.offset].to(st[field].device, torch.float32))
+        self.step_count = int(step)
 
     def ema_state_dict(self, model, gathered=None) -> dict:
         """The EMA shadow under the model's parameter names (un-sharded).  ``gathered``: a ``state_dict()`` result to

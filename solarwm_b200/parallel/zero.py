@@ -320,6 +320,18 @@ class ZeroAdamW(FlatAdamW):
         h.signal(self._flag_params)                    # every rank's pushes have landed here
         h.wait(self._flag_params)
 
+    def _live_shard(self, index: int, key: str) -> torch.Tensor:
+        k = getattr(self, "_sharded_units", {}).get(index)
+        if key == "m" and k is not None:
+            return self.param_shards.shard[k]            # a sharded block's matrices live only as this rank's shard
+        return super()._live_shard(index, key)
+
+    def adopt_live_weights(self, reset_ema: bool = True) -> None:
+        super().adopt_live_weights(reset_ema)
+        self.__dict__.pop("_vec_master", None)           # fp32 vector shards are re-cloned at the next step
+        if self.param_shards is not None:
+            self.param_shards.invalidate()
+
     def _gather_shard(self, shard: torch.Tensor, total: int) -> torch.Tensor:
         """All ranks' shards of one state tensor, concatenated in rank order (a collective over the shard group)."""
         if self.world == 1:
