@@ -244,11 +244,18 @@ def test_train_section_maps_to_activation_and_sharding_options():
     from solarwm_b200.backends.wan22.runtime import activation_and_sharding_options as opts
     from solarwm_b200.errors import ConfigurationError
 
-    assert opts({}, 1) == dict(checkpointing="none", keep_blocks=0, lean_kept=False, zero=False, zero_transport="collective")
+    assert opts({}, 1) == dict(checkpointing="none", keep_blocks=0, lean_kept=False, zero=False, zero_transport="collective",
+                               shard_params=False, cuda_graph=False)
     assert opts({"fsdp": {"activation_checkpointing": True}}, 8)["checkpointing"] == "full"
     assert opts({"fsdp": {"activation_checkpointing": True, "saved_attention_blocks": 30}}, 8)["checkpointing"] == "selective"
     assert opts({"fsdp": {"activation_checkpointing": "selective"}, "activation_memory": {"keep_blocks": 19, "lean": True}}, 1) == \
-        dict(checkpointing="selective", keep_blocks=19, lean_kept=True, zero=False, zero_transport="collective")
+        dict(checkpointing="selective", keep_blocks=19, lean_kept=True, zero=False, zero_transport="collective",
+             shard_params=False, cuda_graph=False)
+    sharded = opts({"zero": {"enabled": True, "transport": "fused"}, "fsdp": {"shard_parameters": True}, "cuda_graph": True}, 8)
+    assert sharded["shard_params"] is True and sharded["cuda_graph"] is True
+    assert opts({"zero": {"enabled": True, "transport": "fused"}, "fsdp": {"shard_parameters": True}}, 1)["shard_params"] is False
+    with pytest.raises(ConfigurationError):                                  # parameter sharding rides the fused transport
+        opts({"zero": {"enabled": True}, "fsdp": {"shard_parameters": True}}, 8)
     assert opts({"zero": {"enabled": True, "transport": "fused"}}, 8)["zero"] is True
     assert opts({"zero": {"enabled": True}}, 1)["zero"] is False             # one rank: nothing to shard over
     assert opts({"fsdp": {"enabled": True}}, 2)["zero"] is True
