@@ -135,17 +135,12 @@ class WanLatentAdapter:
         self.family, self.model, self.config = family, model, config
         self._text_encoder = None
 
-    def _decode(self, latents):
-        """``inference.vae`` (``{z_dim, base, temporal_ups, checkpoint?, fps?, chunk_latent_frames?}``) turns the sampled latents
-        [1, F, C, H, W] into an MP4 (streaming chunk decode through the codec adapter, OpenCV's encoder)."""
+    def _pixels(self, latents):
+        """``inference.vae`` (``{z_dim, base, temporal_ups, checkpoint?, fps?, chunk_latent_frames?}``): the sampled latents
+        [1, F, C, H, W] decoded chunk by chunk through the codec adapter, as pieces ``[T, 3, H, W]`` in [-1, 1]."""
         spec = (self.config.get("inference", {}) or {}).get("vae")
         if not spec:
             return None
-        import os
-        import tempfile
-
-        import cv2
-
         from ...models.vae import VAEConfig, VideoVAE
         from .codec import WanVideoCodec
 
@@ -159,12 +154,21 @@ class WanLatentAdapter:
             if ckpt:
                 vae.load_state_dict(torch.load(ckpt, map_location=latents.device, weights_only=True))
             self._codec = WanVideoCodec(vae)
+        return (piece[0] for piece in self._codec.decode_streaming_chunks(latents, chunk_latent_frames=self._chunk))
+
+    def _encode_mp4(self, pieces) -> bytes:
+        """Pieces ``[T, 3, H, W]`` in [-1, 1] -> MP4 bytes (OpenCV's encoder through a temporary file)."""
+        import os
+        import tempfile
+
+        import cv2
+
         fd, path = tempfile.mkstemp(suffix=".mp4")
         os.close(fd)
         writer = None
         try:
-            for piece in self._codec.decode_streaming_chunks(latents, chunk_latent_frames=self._chunk):
-                rgb = ((piece[0].permute(0, 2, 3, 1) * 0.5 + 0.5).clamp(0, 1) * 255).round().to(torch.uint8).numpy()   # [T, H, W, 3]
+            for piece in pieces:
+                rgb = ((piece.float().permute(0, 2, 3, 1) * 0.5 + 0.5).clamp(0, 1) * 255).round().to(torch.uint8).cpu().numpy()
                 if writer is None:
                     writer = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"mp4v"), self._fps, (rgb.shape[2], rgb.shape[1]))
                     if not writer.isOpened():
@@ -177,6 +181,39 @@ class WanLatentAdapter:
                 return fh.read()
         finally:
             os.unlink(path)
+
+    def _decode(self, latents):
+        pieces = self._pixels(latents)
+        return None if pieces is None else self._encode_mp4(pieces)
+
+    def _source_latents(self, case: InferenceCase, like):
+        """The clip a generated sample is compared with: ``inference.compare_source`` names a ``.pt`` file holding
+        ``[F, C, H, W]`` or ``[cases, F, C, H, W]`` latents, or ``"seeded"`` (a seeded stand-in, synthetic runs)."""
+        spec = (self.config.get("inference", {}) or {}).get("compare_source")
+        if not spec:
+            return None
+        if spec == "seeded":
+            g = torch.Generator().manual_seed(stable_validation_seed("source", case.sample_id) % (2 ** 31))
+            return torch.randn(like.shape, generator=g).to(like.device, like.dtype)
+        value = torch.load(str(spec), map_location="cpu", weights_only=True)
+        if value.dim() == like.dim():
+            value = value[case.slot]
+        if tuple(value.shape) != tuple(like.shape[1:]):
+            raise BackendContractError(f"inference.compare_source holds {tuple(value.shape)}, the sample is {tuple(like.shape[1:])}")
+        return value.unsqueeze(0).to(like.device, like.dtype)
+
+    def _compare(self, case: InferenceCase, latents):
+        """``compare.mp4``: the generated clip beside its source, both through the same decoder."""
+        source = self._source_latents(case, latents)
+        if source is None:
+            return None
+        gen, src = self._pixels(latents), self._pixels(source)
+        if gen is None:
+            raise BackendContractError("inference.compare_source needs inference.vae (both clips are decoded)")
+        from ...engine.comparison import side_by_side
+
+        view = side_by_side(torch.cat(list(gen), 0), torch.cat(list(src), 0))
+        return self._encode_mp4([view])
 
     def _embed(self, case: InferenceCase, dev):
         """The prompt's embedding: through the configured text encoder (``inference.text_encoder``: a ``T5Config``
@@ -235,6 +272,9 @@ class WanLatentAdapter:
         video = self._decode(lat)
         if video is not None:
             artifacts["video.mp4"] = video
+        compare = self._compare(case, lat)
+        if compare is not None:
+            artifacts["compare.mp4"] = compare
         return GeneratedSample(artifacts,
                                tuple(lat.shape), str(lat.dtype).replace("torch.", ""),
                                metrics={"latent_abs_mean": float(lat.float().abs().mean())},
@@ -376,4 +416,15 @@ def run_inline_validation(runtime, step: int) -> Mapping[str, Any]:
         return {"skipped": True}
     adapter = WanLatentAdapter(runtime.route.family, runtime.trainer.model, cfg)
     summary = InferenceEngine(adapter).run(_cases(cfg, count), weights_id=runtime.checkpoint_id, output_dir=target)
-    return {"output_dir": str(summary.output_dir), "cases": summary.cases}
+    report = {"output_dir": str(summary.output_dir), "cases": summary.cases}
+    if (cfg.get("inference", {}) or {}).get("compare_source"):
+        # the browsable comparison view of this pass, next to the publication it links into
+        from ...engine.comparison import publish_comparison_view, seal_comparison_view
+
+        name = str(val.get("pass_name", "live"))
+        view = target.with_name(f"{target.name}_compare")
+        publish_comparison_view(target, view, step=step, pass_name=name, cases=summary.cases, dp_world_size=1,
+                                sp_size=runtime.ctx.topology.sp_size, run_root=output_root(cfg))
+        seal_comparison_view(view, step=step, pass_name=name, cases=summary.cases)
+        report["comparison_view"] = str(view)
+    return report

@@ -126,3 +126,24 @@ def test_infer_decodes_to_a_video_when_a_vae_is_configured(tmp_path, monkeypatch
     blob = (tmp_path / "generate" / "slot-000000" / "video.mp4").read_bytes()
     info = raw_video.probe(blob)
     assert info["frames"] == 5 and (info["height"], info["width"]) == (16, 24)        # 1 + 2 * 2 frames, 4 x spatial
+
+
+def test_validation_publishes_a_comparison_view(tmp_path, monkeypatch):
+    """Training with inline validation, a decoder and a comparison source: every validation pass publishes its slots
+    (latents, video, the generated clip beside its source) and the flat comparison view that links into them."""
+    pytest.importorskip("cv2")
+    from solarwm_b200.data import raw_video
+
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path))
+    assert main(["train", "--config", CONFIG, "--set", "runtime.device=cpu", "--set", "train.max_steps=2", "--set", "runtime.save_every=0",
+                 "--set", "runtime.validate_every=2", "--set", "validation={sample_count: 2, pass_name: live}",
+                 "--set", "inference={steps: 1, latent_frames: 3, latent_height: 4, latent_width: 6, compare_source: seeded, "
+                          "vae: {z_dim: 16, base: 8, temporal_ups: [true, false], fps: 8}}"]) == 0
+    views = sorted(p for p in (tmp_path / "validation").rglob("COMPLETE.json") if p.parent.name.endswith("_compare"))
+    assert len(views) == 1
+    view = views[0].parent
+    videos = sorted((view / "compare").iterdir())
+    assert len(videos) == 2 and videos[0].name.startswith("rank000_round00_dp000_case-0000_start000000")
+    info = raw_video.probe(videos[1].read_bytes())
+    assert info["frames"] == 5 and info["width"] == 2 * 24 + 8                      # generated | band | source
+    assert json.loads((view / "manifests" / "rank_001.json").read_text())["step"] == 2
