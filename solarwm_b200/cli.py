@@ -158,8 +158,8 @@ def data_command(args) -> int:
         from .data.prefetch import warm_cache
         from .data.transport import resolver_from_config
 
-        n = warm_cache(resolver_from_config(data), rows)
-        print(json.dumps({"shards": n}))
+        done = warm_cache(resolver_from_config(data), rows)
+        print(json.dumps({"shards": done.shards, "bytes": done.bytes, "seconds": round(done.seconds, 3)}))
         return 0
     from .data.sampling import CanonicalSampler, ReaderIdentity, SamplingConfig, plan_fingerprint
 

@@ -2,8 +2,11 @@
 ``CachedRemoteResolver`` stages remote objects (``gs://`` through an injected downloader) into a
 local cache with per-object flock, size receipts and LRU eviction, so concurrent readers on a node
 download each shard once.  ``resolver_from_config`` picks one from ``data.transport``
-(reference: solar/data/transport.py:47-623; the network downloader itself is injected because
-this package makes no outbound connections on its own)."""
+(reference: solar/data/transport.py:47-623).  ``GCSRestDownloader`` is the stdlib downloader for ``gs://`` objects
+(JSON API ``alt=media``, bearer token from ``TokenProvider``: a token file, ``GOOGLE_OAUTH_ACCESS_TOKEN`` or the
+metadata server): bounded by a deadline, retries transient failures with capped exponential back-off, gives
+authorisation failures a longer budget (tokens rotate) and never retries other 4xx answers.  Its URL opener, clock
+and sleep are injectable, which is how it is tested without a network."""
 from __future__ import annotations
 
 import fcntl
@@ -15,6 +18,129 @@ from typing import Callable, Mapping, Optional
 
 from ..errors import DataContractError
 from .index import validate_relative_key
+
+
+class DownloadTimeout(DataContractError):
+    """A transfer did not finish inside its time budget (transient: the caller may try again later)."""
+
+
+def parse_gs_uri(uri: str):
+    if not uri.startswith("gs://"):
+        raise DataContractError(f"not a gs:// uri: {uri!r}")
+    bucket, _, name = uri[5:].partition("/")
+    if not bucket or not name:
+        raise DataContractError(f"gs:// uri needs a bucket and an object name: {uri!r}")
+    return bucket, name
+
+
+def is_transient(exc: Optional[BaseException]) -> bool:
+    """Worth retrying: time-outs, connection failures, short reads, 408 / 429 / 5xx; never other 4xx answers."""
+    import http.client
+    import urllib.error
+
+    while exc is not None:
+        if isinstance(exc, urllib.error.HTTPError):
+            return exc.code in (408, 429) or exc.code >= 500
+        if isinstance(exc, (TimeoutError, ConnectionError, http.client.IncompleteRead, urllib.error.URLError, OSError)):
+            return True
+        exc = exc.__cause__
+    return False
+
+
+class TokenProvider:
+    """Bearer token for bucket reads: ``token_file`` if it holds one, else ``GOOGLE_OAUTH_ACCESS_TOKEN``, else the
+    instance metadata server (reference: GoogleTokenProvider, solar/data/transport.py:134-163)."""
+
+    METADATA_URL = "http://metadata.google.internal/computeMetadata/v1/instance/service-accounts/default/token"
+
+    def __init__(self, token_file=None, opener=None, environ=None):
+        self.token_file = None if token_file is None else Path(token_file)
+        self.opener, self.environ = opener, os.environ if environ is None else environ
+
+    def __call__(self) -> str:
+        import urllib.request
+
+        if self.token_file is not None and self.token_file.is_file():
+            text = self.token_file.read_text().strip()
+            if text:
+                return text
+        text = str(self.environ.get("GOOGLE_OAUTH_ACCESS_TOKEN", "")).strip()
+        if text:
+            return text
+        request = urllib.request.Request(self.METADATA_URL, headers={"Metadata-Flavor": "Google"})
+        try:
+            with (self.opener or urllib.request.urlopen)(request, timeout=10) as response:
+                token = str(json.load(response).get("access_token") or "")
+        except (OSError, ValueError) as exc:
+            raise DataContractError("no access token: give a token file, GOOGLE_OAUTH_ACCESS_TOKEN or run where the "
+                                    "metadata server answers") from exc
+        if not token:
+            raise DataContractError("the metadata server returned an empty access token")
+        return token
+
+
+class GCSRestDownloader:
+    """``downloader(uri, path)`` for ``CachedRemoteResolver`` (reference: GCSRestDownloader,
+    solar/data/transport.py:166-265)."""
+
+    def __init__(self, token: Optional[Callable[[], str]] = None, *, socket_timeout_s: float = 120.0,
+                 time_budget_s: float = 300.0, attempts: int = 12, auth_attempts: int = 72,
+                 chunk_bytes: int = 16 << 20, opener=None, sleep=time.sleep, clock=time.monotonic):
+        if min(socket_timeout_s, time_budget_s) <= 0 or min(attempts, auth_attempts, chunk_bytes) < 1:
+            raise DataContractError("downloader limits must be positive")
+        self.token = token or TokenProvider()
+        self.socket_timeout_s, self.time_budget_s = float(socket_timeout_s), float(time_budget_s)
+        self.attempts, self.auth_attempts, self.chunk_bytes = int(attempts), int(auth_attempts), int(chunk_bytes)
+        self.opener, self.sleep, self.clock = opener, sleep, clock
+
+    @staticmethod
+    def media_url(uri: str) -> str:
+        import urllib.parse
+
+        bucket, name = parse_gs_uri(uri)
+        return (f"https://storage.googleapis.com/download/storage/v1/b/{urllib.parse.quote(bucket, safe='')}/o/"
+                f"{urllib.parse.quote(name, safe='')}?alt=media")
+
+    def __call__(self, uri: str, path, deadline: Optional[float] = None) -> int:
+        import urllib.error
+        import urllib.request
+
+        url, start = self.media_url(uri), self.clock()
+        deadline = start + self.time_budget_s if deadline is None else min(float(deadline), start + self.time_budget_s)
+        opener = self.opener or urllib.request.urlopen
+        last, auth_seen = None, False
+        for attempt in range(max(self.attempts, self.auth_attempts)):
+            left = deadline - self.clock()
+            if left <= 0:
+                raise DownloadTimeout(f"{uri}: time budget used up after {attempt} attempt(s)") from last
+            try:
+                request = urllib.request.Request(url, headers={"Authorization": f"Bearer {self.token()}"})
+                size = 0
+                with opener(request, timeout=max(1e-3, min(self.socket_timeout_s, left))) as response, open(path, "wb") as out:
+                    read = getattr(response, "read1", response.read)
+                    while True:
+                        if self.clock() >= deadline:
+                            raise DownloadTimeout(f"{uri}: time budget used up after {size} bytes")
+                        chunk = read(self.chunk_bytes)
+                        if not chunk:
+                            break
+                        out.write(chunk)
+                        size += len(chunk)
+                return size
+            except DownloadTimeout:
+                raise
+            except Exception as exc:  # noqa: BLE001 - urllib raises environment-specific types; classified below
+                last = exc
+                auth = isinstance(exc, urllib.error.HTTPError) and exc.code in (401, 403)
+                auth_seen = auth_seen or auth
+                if not auth and not is_transient(exc):
+                    break                                             # a permanent answer (404, 400 ...)
+                if attempt + 1 >= (self.auth_attempts if auth_seen else self.attempts):
+                    break
+                self.sleep(max(0.0, min(10.0, 0.5 * 2 ** min(attempt, 5), deadline - self.clock())))
+        if is_transient(last):
+            raise DownloadTimeout(f"{uri}: retries used up: {last}") from last
+        raise DataContractError(f"download of {uri} failed: {last}") from last
 
 
 class LocalResolver:
@@ -105,7 +231,8 @@ def resolver_from_config(data_config: Mapping, downloader: Optional[Callable[[st
         return LocalResolver(root)
     if root.startswith("gs://") or kind in ("gcs", "bucket"):
         if downloader is None:
-            raise DataContractError("bucket transport needs a downloader (no network access from this package)")
+            downloader = GCSRestDownloader(TokenProvider(transport.get("token_file")),
+                                           time_budget_s=float(transport.get("download_seconds", 300.0)))
         cache = data_config.get("cache_dir")
         if not cache:
             raise DataContractError("bucket transport requires data.cache_dir")

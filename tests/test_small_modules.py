@@ -28,7 +28,8 @@ def test_prefetcher_keeps_lookahead_shards_in_flight_and_preserves_order():
     assert sorted(set(calls)) == [f"s{i}" for i in range(5)] and len(calls) == 5     # every shard resolved once
     rows = [SimpleNamespace(shard=f"s{i % 3}", values={"shard_size": 10 + i % 3}) for i in range(9)]
     calls.clear()
-    assert warm_cache(Resolver(), rows) == 3 and sorted(calls) == ["s0", "s1", "s2"]
+    done = warm_cache(Resolver(), rows)
+    assert (done.shards, done.bytes) == (3, 10 + 11 + 12) and sorted(calls) == ["s0", "s1", "s2"]
 
 
 def test_fp32_master_adamw_matches_torch_adamw_and_refuses_casting_loads():
