@@ -501,7 +501,8 @@ def run_two_expert(args):
     tokens = n_tokens(cfg, args)
     frame_tokens = tokens // args.frames
     sp = FusedUlysses(None, max_tokens=tokens, dim=cfg.dim, num_heads=cfg.num_heads, max_frame_tokens=frame_tokens)
-    ckpt = "none" if args.checkpointing == "auto" else args.checkpointing
+    # two 14B experts: selective recompute keeps one expert's activations near 20 GiB per rank at 8 ranks
+    ckpt = ("selective" if args.model == "i2v_a14b" else "none") if args.checkpointing == "auto" else args.checkpointing
     graph = args.graph != "off"
     trainers, need = {}, 1 << 20
     models = {}

@@ -92,6 +92,9 @@ class TwoExpertTrainer:
 
     def __init__(self, high_noise, low_noise, *, boundary: float = BOUNDARY_I2V, shift: float = 5.0, seed: int = 0):
         self.trainers = {"high_noise": high_noise, "low_noise": low_noise}
+        # one expert trains per step, so their captured steps can share one pool of activation memory: whichever
+        # captures second borrows the first one's pool (two private pools of a 14B step do not fit beside each other)
+        high_noise.graph_pool_donor, low_noise.graph_pool_donor = low_noise, high_noise
         self.boundary, self.shift = float(boundary), float(shift)
         self.host_gen = torch.Generator().manual_seed(int(seed) * 100003 + 17)
         self.steps = {"high_noise": 0, "low_noise": 0}

@@ -230,7 +230,11 @@ class WanStage0p5Trainer:
                 opt._host_prepared = True
             step_before = self.global_step
             counted = dict(ops.COUNTERS)
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            # a trainer that never runs at the same time as this one (the other expert of a two-expert model) lends
+            # its graph's memory pool: the two captured steps then reuse ONE set of activation buffers
+            donor = getattr(self, "graph_pool_donor", None)
+            lent = None if donor is None else (donor.__dict__.get("_graph_state") or {}).get("graph")
+            with torch.cuda.graph(graph, pool=None if lent is None else lent.pool(), capture_error_mode="thread_local"):
                 loss = self.microbatch(st["inputs"]["latents"], st["inputs"]["text"], st["inputs"].get("y"),
                                        **({} if "t_video" not in st["inputs"] else {"t_video": st["inputs"]["t_video"]}))
                 norm = self.optimizer_step()

@@ -235,11 +235,14 @@ def _wide_worker(rank, world, port, out_path):
         outs[name] = (out.detach().float().cpu(), {n: p.main_grad.float().cpu() for n, p in model.named_parameters()})
     result["forward_identical"] = bool(torch.equal(outs["nccl"][0], outs["fused"][0]))
     worst, worst_name = 0.0, ""
+    # gradients that are zero in exact arithmetic (a key bias shifts every score of a row alike, so softmax cancels it)
+    # hold only summation noise, whose ORDER differs between the transports once more than two ranks contribute:
+    # measure every difference against at least a thousandth of the largest gradient
+    floor = 1e-3 * max(float(r.norm()) for r in outs["nccl"][1].values())
     for n, r in outs["nccl"][1].items():
-        if r.norm() > 1e-6:
-            rel = ((outs["fused"][1][n] - r).norm() / r.norm()).item()
-            if rel > worst:
-                worst, worst_name = rel, n
+        rel = ((outs["fused"][1][n] - r).norm() / max(float(r.norm()), floor)).item()
+        if rel > worst:
+            worst, worst_name = rel, n
     result["worst_grad_rel"], result["worst_grad_name"] = worst, worst_name
     fused.close()
     del model, outs
