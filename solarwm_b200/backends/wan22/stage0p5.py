@@ -100,7 +100,7 @@ class WanStage0p5Trainer:
         """One timestep per video on the 1000-step grid (values in [0, 1000])."""
         if self.opts.sigma_sampling == "uniform_index":
             idx = torch.randint(0, self.scheduler.num_train_timesteps, (B,), generator=self.gen, device=self.device)
-            return self.scheduler.timesteps.to(self.device)[idx]
+            return self.scheduler._on("timesteps", self.device)[idx]      # the cached device copy (no host copy in a captured step)
         s = logit_normal_sigmas(B, self.opts.timestep_shift, generator=self.gen, device=self.device)
         return s * self.scheduler.num_train_timesteps
 
