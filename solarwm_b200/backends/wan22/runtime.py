@@ -373,9 +373,9 @@ class WanStage0p5Runtime:
             dist.all_gather_object(states, state)
         # the optimizer state is gathered into the un-sharded layout on every rank (a collective when the optimizer is
         # sharded); the EMA weights are named out of the same gathered tensors
-        opt_state = self.trainer.optimizer.state_dict()
+        opt_state = self.trainer.optimizer.state_dict(keep=topo.is_main)
         ema_state = None
-        if self.trainer.optimizer.ema_decay is not None:
+        if self.trainer.optimizer.ema_decay is not None and topo.is_main:
             from ...engine.ema import FlatEMAView
 
             ema_state = FlatEMAView(self.trainer.model, self.trainer.optimizer, gathered=opt_state).state_dict()

@@ -102,11 +102,12 @@ class FlatAdamW:
         subclasses make this a collective over their shard group."""
         return shard
 
-    def state_dict(self):
+    def state_dict(self, keep: bool = True):
         """State in the UN-SHARDED layout: every tensor covers the whole flat buffer, whatever the number of ranks the
         optimizer is sharded over, so that a checkpoint can be resumed at another shard count.  With a sharded
-        optimizer this is a collective: every rank of the shard group must call it; all ranks receive the full
-        tensors (on the host) and the caller decides which rank writes them."""
+        optimizer this is a collective: every rank of the shard group must call it.  ``keep`` = False on the ranks
+        that will not write the checkpoint: they take part in every gather and drop the result instead of copying
+        tens of gigabytes to their host memory (their tensors are ``None``)."""
         out = {"step": self.step_count, "lr": self.lr, "betas": self.betas, "eps": self.eps,
                "weight_decay": self.weight_decay, "layout": "full", "units": []}
         for u, st in zip(self.units, self.state):
@@ -116,7 +117,12 @@ class FlatAdamW:
                 entry[key] = {"numel": int(buf.numel())}
                 for name in self._STATE_TENSORS:
                     t = s[name]
-                    entry[key][name] = None if t is None else self._gather_shard(t.detach(), buf.numel()).cpu()
+                    if t is None:
+                        entry[key][name] = None
+                        continue
+                    full = self._gather_shard(t.detach(), buf.numel())
+                    entry[key][name] = full.cpu() if keep else None
+                    del full
             out["units"].append(entry)
         return out
 
