@@ -5,7 +5,7 @@ sides) and roofline fractions against the measured peaks of the box.
     python -m solarwm_b200.utils.kernel_bench attention --seq 27280 --heads 24 --head-dim 128 [--backward]
     python -m solarwm_b200.utils.kernel_bench rowops --rows 27280 --dim 3072
     python -m solarwm_b200.utils.kernel_bench suite            # the Wan-5B block shapes
-    python -m solarwm_b200.utils.kernel_bench probe --family rows|pointwise|headops|zero|attention|attention_bwd|conv|gemm
+    python -m solarwm_b200.utils.kernel_bench probe --family rows|pointwise|headops|zero|attention|attention_bwd|masked_attention|scatter|conv|gemm
                                                                # one launch of every kernel of a family on a case
                                                                # larger than L2 and a few hundred MB at most: the
                                                                # program a counter capture (ncu -k ... -c N) runs
@@ -294,6 +294,51 @@ def probe(family: str, rows: int = 27280, dim: int = 3072) -> dict:
         pw, pb = F_.pack_conv_weight(w, torch.zeros(256, device=dev).bfloat16())
         run("conv3d", lambda: F_.conv3d_channels_last(x, pw, pb, (3, 3, 3)),
             {"flops": 2.0 * 4 * 176 * 320 * 256 * 256 * 27, "bytes": 2 * x.numel() * 2 + pw.numel() * 2})
+    elif family == "masked_attention":
+        # teacher forcing over [clean | noisy] halves: 2 x 10 frames of 880 tokens, 3-frame chunks, 6-chunk window
+        from ..ops.attention_mask import masked_attention, teacher_forcing_segment_mask
+
+        L, H, Dh = 10 * 880, 12, 128
+        mask = teacher_forcing_segment_mask(L, 3 * 880, 6, 0, 0)
+        q, k, v = (rnd(1, 2 * L, H, Dh).bfloat16() for _ in range(3))
+        live = 4.0 * (2 * L) ** 2 * H * Dh * mask.density
+        with torch.no_grad():
+            run("attn_fwd_masked", lambda: masked_attention(q, k, v, mask), {"flops": live, "bytes": 8 * 2 * L * H * Dh})
+        qr = q.clone().requires_grad_(True)
+        o = masked_attention(qr, k, v, mask)
+        do = rnd(1, 2 * L, H, Dh).bfloat16()
+        run("attn_bwd_masked", lambda: torch.autograd.grad(o, qr, do, retain_graph=True), {"flops": 2.5 * live, "bytes": 16 * 2 * L * H * Dh})
+    elif family == "scatter":
+        # the peer-scatter epilogues in their single-rank form (every "peer" is this GPU, nothing waits): what the
+        # epilogue costs beside the plain kernel, without NVLink in the picture
+        import ctypes
+
+        from ..ops._lib import c_float, c_int, c_ll, load, ptr, stream_handle
+        from ..ops.functional import status_word
+
+        lib = load()
+        M, D = 6820, 3072
+        x, w = rnd(M, D).bfloat16(), (rnd(3 * D, D) / D ** 0.5).bfloat16()
+        bias = torch.zeros(3 * D, device=dev, dtype=torch.bfloat16)
+        qkv, recv = torch.empty(M, 3 * D, device=dev, dtype=torch.bfloat16), torch.empty(M, 3 * D, device=dev, dtype=torch.bfloat16)
+        flag, counter = torch.zeros(4, device=dev, dtype=torch.int32), torch.zeros(1, device=dev, dtype=torch.int32)
+        one = lambda t: (ctypes.c_void_p * 1)(t.data_ptr())       # noqa: E731
+        dst, flags = one(recv), one(flag)
+        run("gemm_scatter(1 rank)", lambda: lib.solar_gemm_bf16_scatter(
+            ptr(x), ptr(w), ptr(qkv), ptr(bias), c_int(M), c_int(3 * D), c_int(D), c_ll(D), c_ll(D), c_ll(3 * D), c_int(0),
+            c_int(0), ptr(status_word(dev)), c_int(0), stream_handle(), dst, flags, ptr(counter), c_int(1), c_ll(3 * D),
+            c_int(D), c_int(D), c_int(0), c_int(2 * D), c_int(0)),
+            {"flops": 2.0 * M * 3 * D * D, "bytes": 2 * (M * D + 3 * D * D + M * 3 * D)})
+        S, H, Dh = 16384, 6, 128
+        q, k, v = (rnd(S, H * Dh).bfloat16() for _ in range(3))
+        o, obuf = torch.empty(S, H * Dh, device=dev, dtype=torch.bfloat16), torch.empty(S, H * Dh, device=dev, dtype=torch.bfloat16)
+        lse = torch.empty(1, H, S, device=dev)
+        starts = (ctypes.c_int * 2)(0, S)
+        run("attn_fwd_scatter(1 rank)", lambda: lib.solar_attn_fwd_scatter(
+            ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), c_int(S), c_int(S), c_int(H), c_int(Dh), c_ll(H * Dh), c_ll(H * Dh),
+            c_ll(H * Dh), c_ll(H * Dh), c_float(1.0 / math.sqrt(Dh)), ptr(status_word(dev)), stream_handle(), one(obuf), flags,
+            ptr(counter), c_int(1), c_ll(H * Dh), c_ll(S), starts, c_int(0)),
+            {"flops": 4.0 * S * S * H * Dh, "bytes": 8 * S * H * Dh})
     elif family == "gemm":
         a, b = rnd(8192, 4096).bfloat16(), rnd(8192, 4096).bfloat16()
         run("gemm_nt", lambda: ops.gemm(a, b, ops.NT), {"flops": 2.0 * 8192 * 8192 * 4096, "bytes": 2 * (2 * 8192 * 4096 + 8192 * 8192)})
