@@ -301,7 +301,7 @@ def probe(family: str, rows: int = 27280, dim: int = 3072) -> dict:
         L, H, Dh = 10 * 880, 12, 128
         mask = teacher_forcing_segment_mask(L, 3 * 880, 6, 0, 0)
         q, k, v = (rnd(1, 2 * L, H, Dh).bfloat16() for _ in range(3))
-        live = 4.0 * (2 * L) ** 2 * H * Dh * mask.density
+        live = 4.0 * (2 * L) ** 2 * H * Dh * mask.density()
         with torch.no_grad():
             run("attn_fwd_masked", lambda: masked_attention(q, k, v, mask), {"flops": live, "bytes": 8 * 2 * L * H * Dh})
         qr = q.clone().requires_grad_(True)
