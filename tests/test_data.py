@@ -184,3 +184,41 @@ def test_raw_video_decode_matches_written_frames(tmp_path):
         raw_video.decode_frames(blob, [200])
     with pytest.raises(DataContractError):
         raw_video.decode_frames(b"not a video", [0])
+
+
+def test_plan_multiplexer_interleaves_workers_and_resumes_anywhere():
+    """Two loader workers of one rank: batches alternate between them, each worker follows its own canonical plan
+    stream across epochs, and a state saved at ANY point continues with exactly the plans an uninterrupted run sees."""
+    from solarwm_b200.data.plan_mux import PlanMultiplexer
+    from solarwm_b200.runtime.topology import Topology
+
+    rows, cfg, topo = _rows(10, 2), SamplingConfig(seed=3, pixel_frames=81, shuffle_buffer=4), Topology(2, 1, 2, 1, 1)
+    full = PlanMultiplexer(rows, cfg, topo, num_workers=2)
+    stream = [full.next_batch(2) for _ in range(12)]                      # three epochs' worth for this rank
+    workers = [p.worker_id for batch in stream for p in batch]
+    assert workers[:8] == [0, 0, 1, 1, 0, 0, 1, 1] and {p.reader_rank for b in stream for p in b} == {1}
+    # each worker's sub-stream is the canonical sampler's, epoch after epoch
+    for w in range(2):
+        ref = CanonicalSampler(rows, cfg, ReaderIdentity.from_topology(topo, worker_id=w, num_workers=2))
+        want = [p for e in range(4) for p in ref.iter_epoch(e)]
+        got = [p for batch in stream for p in batch if p.worker_id == w]
+        assert got == want[:len(got)] and max(p.epoch for p in got) >= 1
+    for cut in (0, 1, 5, 8):                                              # including a cut at an epoch boundary
+        a = PlanMultiplexer(rows, cfg, topo, num_workers=2)
+        for _ in range(cut):
+            a.next_batch(2)
+        state = a.state_dict()
+        assert state["schema"] == "solarwm.plan-multiplexer.v1"
+        import json
+        b = PlanMultiplexer(rows, cfg, topo, num_workers=2)
+        b.load_state_dict(json.loads(json.dumps(state)))                  # the state is plain JSON
+        assert [b.next_batch(2) for _ in range(12 - cut)] == stream[cut:]
+    m = PlanMultiplexer(rows, cfg, topo, num_workers=2)
+    with pytest.raises(DataContractError):
+        m.finish_batch(1)                                                 # worker 0's batch comes first
+    with pytest.raises(DataContractError):
+        PlanMultiplexer(rows, cfg, topo, num_workers=3).load_state_dict(m.state_dict())
+    with pytest.raises(DataContractError):
+        PlanMultiplexer(_rows(14, 2), cfg, topo, num_workers=2).load_state_dict(m.state_dict())   # another index
+    with pytest.raises(DataContractError):
+        m.load_state_dict({"schema": "other"})
