@@ -33,7 +33,10 @@ setInterval(async()=>{const r=await fetch('/state');state.textContent=JSON.strin
 </script></body></html>"""
 
 
-def make_server(state, navigation, fragments=None, host: str = "127.0.0.1", port: int = 8900) -> ThreadingHTTPServer:
+def make_server(state, navigation, fragments=None, host: str = "127.0.0.1", port: int = 8900,
+                media=None) -> ThreadingHTTPServer:
+    """``media``: a ``serve.fragments.MediaStore``; ``GET /media?scene=&sequence=&cursor=&limit=`` then serves whole
+    fMP4 fragments of a live (or finished) preview to clients that resume by cursor."""
     class Handler(BaseHTTPRequestHandler):
         def log_message(self, *a):
             return
@@ -61,6 +64,18 @@ def make_server(state, navigation, fragments=None, host: str = "127.0.0.1", port
             if url.path == "/fragments" and fragments is not None:
                 since = int(parse_qs(url.query).get("since", ["0"])[0])
                 return self._send(200, [{"index": i, "data": base64.b64encode(b).decode()} for i, b in fragments.since(since)])
+            if url.path == "/media" and media is not None:
+                q = parse_qs(url.query)
+                try:
+                    got = media.fragments(q.get("scene", [""])[0], int(q.get("sequence", ["0"])[0]),
+                                          int(q.get("cursor", ["0"])[0]), int(q.get("limit", ["16"])[0]))
+                except FileNotFoundError:
+                    return self._send(404, {"error": "no such preview"})
+                except ValueError as exc:
+                    return self._send(400, {"error": str(exc)})
+                enc = lambda b: None if b is None else base64.b64encode(b).decode()    # noqa: E731
+                return self._send(200, {"rows": got["rows"], "data": [enc(b) for b in got["data"]], "init": enc(got["init"]),
+                                        "produced": got["produced"], "done": got["done"], "next_cursor": got["next_cursor"]})
             self._send(404, {"error": "not found"})
 
         def do_POST(self):
