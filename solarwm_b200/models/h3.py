@@ -254,6 +254,26 @@ class H3DiT(nn.Module):
     def trainable_parameters(self):
         return [p for p in self.parameters() if p.requires_grad]
 
+    @torch.no_grad()
+    def fuse_qkv_(self) -> int:
+        """Inference: make the q, k and v projection weights of every adapter-free block views of ONE ``[3 A, hidden]``
+        buffer (``block.qkv_weight``), so that a caller can run the three projections as one GEMM.  At a few hundred
+        rows per rank one projection is 84 CTA-pair tiles on 74 pairs -- two waves for 1.13 -- and the fused one is
+        252 tiles in four waves instead of six.  No memory is added (the parameters move into the buffer); the
+        per-projection modules keep working.  Returns the number of blocks fused."""
+        done = 0
+        for blk in list(self.refiner) + list(self.blocks):
+            mods = (blk.to_q, blk.to_k, blk.to_v)
+            if getattr(blk, "qkv_weight", None) is not None or any(m.rank > 0 or m._bank is not None for m in mods):
+                continue
+            a = mods[0].weight.shape[0]
+            fused = torch.cat([m.weight.data for m in mods], dim=0)
+            for i, m in enumerate(mods):
+                m.weight.data = fused[i * a:(i + 1) * a]
+            blk.qkv_weight = fused
+            done += 1
+        return done
+
     # named adapter banks: independent LoRA sets over the same frozen base, one active at a time ----------
     def add_adapter(self, name: str, rank: int, seed: int = 0) -> None:
         gen = torch.Generator(device="cpu").manual_seed(seed)

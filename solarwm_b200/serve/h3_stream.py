@@ -55,6 +55,7 @@ class H3StreamConfig:
                                        # straight into the peers' KV caches, the evaluation is graph-capturable);
                                        # "collective" = NCCL all-to-alls (the baseline arm; runs eagerly)
     max_text_tokens: int = 1536        # sizes the exchange buffers of the fused transport
+    fuse_qkv: bool = True              # run q | k | v of adapter-free blocks as one GEMM (``H3DiT.fuse_qkv_``)
     seed: int = 0
 
 
@@ -82,6 +83,8 @@ class H3StreamingGenerator:
         self.chunk_rows = cfg.chunk_latents * self.rows_per_latent
         assert self.chunk_rows >= self.P, "every SP rank needs at least one row of a chunk"
         self.device = model.proj_in.device
+        if cfg.fuse_qkv:
+            model.fuse_qkv_()
         self.gen = torch.Generator(device=self.device).manual_seed(cfg.seed)
         self.times = rollout_times(cfg.denoise_steps, cfg.shift)[:cfg.denoise_steps]
         self.timings: List[ChunkTiming] = []
@@ -208,9 +211,16 @@ class H3StreamingGenerator:
         for bi, (blk, kv) in enumerate(zip(m.blocks, self.kv)):
             table = tables[bi] if tables is not None else blk.tables(temb)
             xm = F_.norm_modulate(x, table[:, 0], table[:, 1], mode=1, w=blk.norm1, eps=mc.eps, table=idx)
-            q = ops.head_norm_rope_prope(blk.to_q(xm), blk.norm_q, cos, sin, cam_q, heads=H, **kw)
-            k = ops.head_norm_rope_prope(blk.to_k(xm), blk.norm_k, cos, sin, cam_kv, heads=H, **kw)
-            v = ops.head_norm_rope_prope(blk.to_v(xm), None, None, None, cam_kv, heads=H, **kw)
+            fused_w = getattr(blk, "qkv_weight", None) if blk.to_q._bank is None else None
+            if fused_w is not None:                                      # one GEMM for the three projections
+                qkv = F_.linear(xm, fused_w)
+                a_ = H * hd
+                q_in, k_in, v_in = qkv[:, :a_], qkv[:, a_:2 * a_], qkv[:, 2 * a_:]
+            else:
+                q_in, k_in, v_in = blk.to_q(xm), blk.to_k(xm), blk.to_v(xm)
+            q = ops.head_norm_rope_prope(q_in, blk.norm_q, cos, sin, cam_q, heads=H, **kw)
+            k = ops.head_norm_rope_prope(k_in, blk.norm_k, cos, sin, cam_kv, heads=H, **kw)
+            v = ops.head_norm_rope_prope(v_in, None, None, None, cam_kv, heads=H, **kw)
             if self.fx is not None:
                 # fused transport: one launch stores q into the exchange buffer and k / v straight into every peer's
                 # cache rows; the attention epilogue returns the output rows to their owners

@@ -159,3 +159,30 @@ def test_memory_adapter_bank_is_active_only_while_memory_rows_are_installed():
     assert not torch.allclose(a[1], b[1])                                 # memory rows served by the Memory adapter
     with pytest.raises(KeyError):
         model.set_adapter("nope")
+
+
+def test_fused_qkv_projection_changes_nothing_and_yields_to_adapter_banks():
+    """``fuse_qkv``: the three projection weights of a block become views of one buffer and the generator issues one
+    GEMM; the stream is the same as with three GEMMs, the per-projection modules still work, and a block whose adapter
+    bank is switched on goes back to them."""
+    cfg = h3_preset("tiny")
+    outs = {}
+    for fuse in (False, True):
+        model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+        scfg = H3StreamConfig(grid_hw=(2, 3), chunk_latents=2, window_chunks=2, denoise_steps=2, use_cuda_graph=False, fuse_qkv=fuse)
+        g = H3StreamingGenerator(model, scfg)
+        torch.manual_seed(0)
+        g.start(torch.randn(6, cfg.text_dim), torch.randn(24, 1, 4, 6), torch.eye(4))
+        outs[fuse] = torch.stack([g.next_chunk(None) for _ in range(3)])
+        blk = model.blocks[0]
+        if fuse:
+            a = blk.to_q.weight.shape[0]
+            assert blk.qkv_weight.shape[0] == 3 * a and blk.to_k.weight.data_ptr() == blk.qkv_weight[a:].data_ptr()
+            x = torch.randn(5, cfg.hidden_size)
+            assert torch.allclose(blk.to_v(x), x @ blk.qkv_weight[2 * a:].t(), atol=1e-5)
+            assert model.fuse_qkv_() == 0                                  # nothing left to fuse
+        else:
+            assert getattr(blk, "qkv_weight", None) is None
+    assert torch.allclose(outs[True], outs[False], atol=1e-5)
+    lora = H3DiT(h3_preset("tiny").__class__(**{**h3_preset("tiny").__dict__, "lora_rank": 2}), device="cpu", dtype=torch.float32, seed=0)
+    assert lora.fuse_qkv_() == 0                                           # trainable adapters: left alone
