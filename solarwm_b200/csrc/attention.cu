@@ -78,11 +78,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * (2 * QT);
+  const int q_tile = MASKED ? mask_tile_of_cta(p.mask, blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int q0 = q_tile * (2 * QT);
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
-  const int n_kv = MASKED ? p.mask.tile_count[blockIdx.x] : (p.Sk + KT - 1) / KT;
-  const int* kv_list = MASKED ? p.mask.tile_list + static_cast<long long>(blockIdx.x) * p.mask.stride : nullptr;
+  const int n_kv = MASKED ? p.mask.tile_count[q_tile] : (p.Sk + KT - 1) / KT;
+  const int* kv_list = MASKED ? p.mask.tile_list + static_cast<long long>(q_tile) * p.mask.stride : nullptr;
   // KV tile visited by iteration j (all tiles in order, or the CTA's list under a structured mask)
   auto kv_tile = [&](int j) -> int { return MASKED ? (kv_list[j] & (kMaskPartialBit - 1)) : j; };
   // the second Q tile may be entirely past the end of the sequence
@@ -447,12 +448,12 @@ extern "C" int solar_attn_fwd_masked(const void* q, const void* k, const void* v
                                      int Sk, int H, int D, long long q_ss, long long q_sb, long long k_ss,
                                      long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
                                      float scale, int* status, void* stream, const int* row_ranges,
-                                     const int* tile_list, const int* tile_count, int list_stride) {
+                                     const int* tile_list, const int* tile_count, int list_stride, const int* order) {
   if (row_ranges == nullptr || tile_list == nullptr || tile_count == nullptr || list_stride < 1)
     return fail("masked attention: the mask tables are required%s");
   RowScatter none;
   memset(&none, 0, sizeof(none));
-  AttnMask m{row_ranges, tile_list, tile_count, list_stride};
+  AttnMask m{row_ranges, tile_list, tile_count, list_stride, order};
   return attn_fwd_entry(q, k, v, o, lse, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss, v_sb, o_ss, o_sb, scale,
                         status, stream, none, &m);
 }

@@ -178,11 +178,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmStat1,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * ST_ROWS;
+  const int st_tile = MASKED ? mask_tile_of_cta(p.mask, blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int row0 = st_tile * ST_ROWS;
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
-  const int n_tiles = MASKED ? p.mask.tile_count[blockIdx.x] : (p.S_stream + SR_ROWS - 1) / SR_ROWS;
-  const int* tile_list = MASKED ? p.mask.tile_list + static_cast<long long>(blockIdx.x) * p.mask.stride : nullptr;
+  const int n_tiles = MASKED ? p.mask.tile_count[st_tile] : (p.S_stream + SR_ROWS - 1) / SR_ROWS;
+  const int* tile_list = MASKED ? p.mask.tile_list + static_cast<long long>(st_tile) * p.mask.stride : nullptr;
   // streamed tile visited by iteration j (every tile in order, or this CTA's list under a structured mask)
   auto tile_of = [&](int j) -> int { return MASKED ? (tile_list[j] & (kMaskPartialBit - 1)) : j; };
   const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
@@ -874,10 +875,11 @@ extern "C" int solar_attn_bwd_masked(const void* q, const void* k, const void* v
                                      long long k_sb, long long v_ss, long long v_sb, long long o_ss, long long o_sb,
                                      long long do_ss, long long do_sb, float scale, int* status, void* stream,
                                      const int* row_ranges, const int* dkv_list, const int* dkv_count, int dkv_stride,
-                                     const int* dq_list, const int* dq_count, int dq_stride) {
+                                     const int* dq_list, const int* dq_count, int dq_stride, const int* dkv_order,
+                                     const int* dq_order) {
   if (!row_ranges || !dkv_list || !dkv_count || !dq_list || !dq_count || dkv_stride < 1 || dq_stride < 1)
     return fail("masked attention backward: the mask tables are required%s");
-  AttnMask mkv{row_ranges, dkv_list, dkv_count, dkv_stride}, mq{row_ranges, dq_list, dq_count, dq_stride};
+  AttnMask mkv{row_ranges, dkv_list, dkv_count, dkv_stride, dkv_order}, mq{row_ranges, dq_list, dq_count, dq_stride, dq_order};
   return attn_bwd_impl(q, k, v, o, dout, lse, dq, dk, dv, scratch, B, Sq, Sk, H, D, q_ss, q_sb, k_ss, k_sb, v_ss,
                        v_sb, o_ss, o_sb, do_ss, do_sb, scale, status, stream, g_bwd_overlap, nullptr, &mkv, &mq);
 }

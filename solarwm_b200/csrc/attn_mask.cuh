@@ -14,7 +14,12 @@ struct AttnMask {
   const int* tile_list;    // [gridDim.x][stride] tile indices of the streamed operand
   const int* tile_count;   // [gridDim.x], >= 1
   int stride;
+  const int* order;        // [gridDim.x] or null: the stationary tile that CTA x works on.  CTAs are dispatched in
+                           // index order and own very different numbers of live tiles (a query tile of the first
+                           // chunk sees one chunk of keys, one of the last sees the whole window); listing the
+                           // heaviest tiles first keeps the end of the launch for the light ones
 };
+__device__ __forceinline__ int mask_tile_of_cta(const AttnMask& m, int cta) { return m.order ? m.order[cta] : cta; }
 constexpr int kMaskPartialBit = 1 << 30;
 
 __device__ __forceinline__ bool mask_sees(const int (&rg)[6], int key) {

@@ -147,10 +147,14 @@ class SegmentMask:
             dq = self._pack(self._tiles_over_keys(128, 64), "query")
             dkv = self._pack(self._tiles_over_queries(128, 64), "key")
             to = lambda a: torch.from_numpy(a).to(device)          # noqa: E731
+            # launch order of the CTAs: heaviest stationary tile first (CTAs are dispatched in index order, so the
+            # launch then ends with its lightest tiles instead of its longest ones)
+            order = lambda counts: to(np.argsort(-counts.astype(np.int64), kind="stable").astype(np.int32))   # noqa: E731
             self._device[key] = {
                 "row_ranges": to(self.row_ranges()),
                 "fwd": (to(fwd[0]), to(fwd[1]), fwd[2]), "dq": (to(dq[0]), to(dq[1]), dq[2]),
                 "dkv": (to(dkv[0]), to(dkv[1]), dkv[2]),
+                "fwd_order": order(fwd[1]), "dq_order": order(dq[1]), "dkv_order": order(dkv[1]),
                 "tiles_visited": int(fwd[1].sum()), "tiles_dense": len(fwd[1]) * (-(-self.Sk // 128)),
             }
         return self._device[key]
@@ -215,7 +219,7 @@ class _MaskedAttentionFn(torch.autograd.Function):
             ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), c_int(B), c_int(Sq), c_int(Sk), c_int(H), c_int(D),
             c_ll(q.stride(1)), c_ll(q.stride(0)), c_ll(k.stride(1)), c_ll(k.stride(0)), c_ll(v.stride(1)), c_ll(v.stride(0)),
             c_ll(o.stride(1)), c_ll(o.stride(0)), c_float(scale), ptr(status_word(q.device)), stream_handle(),
-            ptr(t["row_ranges"]), ptr(lst), ptr(cnt), c_int(stride))
+            ptr(t["row_ranges"]), ptr(lst), ptr(cnt), c_int(stride), ptr(t["fwd_order"]))
         check(rc, "solar_attn_fwd_masked")
         count("attn_fwd_masked")
         ctx.save_for_backward(q, k, v, o, lse)
@@ -246,7 +250,7 @@ class _MaskedAttentionFn(torch.autograd.Function):
             c_int(Sk), c_int(H), c_int(D), c_ll(q.stride(1)), c_ll(q.stride(0)), c_ll(k.stride(1)), c_ll(k.stride(0)),
             c_ll(v.stride(1)), c_ll(v.stride(0)), c_ll(o.stride(1)), c_ll(o.stride(0)), c_ll(do.stride(1)), c_ll(do.stride(0)),
             c_float(ctx.scale), ptr(status_word(q.device)), stream_handle(), ptr(t["row_ranges"]), ptr(kl), ptr(kc),
-            c_int(ks), ptr(ql), ptr(qc), c_int(qs))
+            c_int(ks), ptr(ql), ptr(qc), c_int(qs), ptr(t["dkv_order"]), ptr(t["dq_order"]))
         check(rc, "solar_attn_bwd_masked")
         count("attn_bwd_masked", 3)
         return dq, dk, dv, None, None
