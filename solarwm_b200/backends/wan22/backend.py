@@ -24,8 +24,18 @@ class Wan22Backend:
 
             validate_release_recipe(config, self.family)
 
+    def readiness(self, config: Mapping[str, Any], *, require_cuda: bool = False):
+        """Dependencies, assets, architecture, weights, indexes, inference controls and the device in one report."""
+        self.validate_config(config)
+        from .readiness import probe_runtime
+
+        return probe_runtime(config, family=self.family, require_cuda=require_cuda)
+
     def train(self, config: Mapping[str, Any]) -> Mapping[str, Any]:
         route = validate_route(config)
+        from .readiness import require_training_runtime
+
+        require_training_runtime(config, family=self.family)
         if route.stage == "stage0p5":
             from .runtime import run_training
 

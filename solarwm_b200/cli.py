@@ -69,6 +69,9 @@ def build_parser() -> argparse.ArgumentParser:
         mw.add_argument(flag, required=True, type=Path)
     env = sub.add_parser("environment").add_subparsers(dest="environment_command", required=True)
     env.add_parser("probe")
+    rd = env.add_parser("readiness", help="dependencies, assets, weights, indexes and device a configuration needs")
+    _add_config_args(rd)
+    rd.add_argument("--require-cuda", action="store_true")
     pub = sub.add_parser("publish-validation")
     pub.add_argument("--source", required=True)
     pub.add_argument("--destination", required=True)
@@ -179,6 +182,17 @@ def data_command(args) -> int:
 
 
 def environment_command(args) -> int:
+    if args.environment_command == "readiness":
+        from .registry import load_backend
+
+        resolved = load_config(args.config, args.overrides)
+        backend = load_backend(str(resolved.values["model"]["family"]))
+        if not hasattr(backend, "readiness"):
+            raise ConfigurationError(f"the {resolved.values['model']['family']} backend has no readiness report")
+        report = backend.readiness(resolved.values, require_cuda=bool(args.require_cuda))
+        report = report.as_dict() if hasattr(report, "as_dict") else dict(report)
+        print(json.dumps(report, sort_keys=True, indent=1))
+        return 0 if report.get("ready") else 3
     from .runtime.env_probe import probe_python_runtime
 
     print(json.dumps(probe_python_runtime(), sort_keys=True, indent=1))
