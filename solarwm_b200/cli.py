@@ -9,7 +9,7 @@
     solar data warm-cache --config FILE
     solar data materialize-wan153f --train-index F --test-index F --train-window-index F --test-window-index F --output F
     solar environment probe
-    solar publish-validation --source DIR --destination URI
+    solar publish-validation (--source DIR | --run-dir DIR [--node-rank I --num-nodes N]) --destination URI
 
 ``train/infer/preencode`` resolve the config, reject inline secrets, check that the config's action
 matches the command, validate the route, load the backend lazily, let it validate its own section
@@ -73,8 +73,11 @@ def build_parser() -> argparse.ArgumentParser:
     _add_config_args(rd)
     rd.add_argument("--require-cuda", action="store_true")
     pub = sub.add_parser("publish-validation")
-    pub.add_argument("--source", required=True)
+    pub.add_argument("--source", help="one pass directory (or a folder of them) to upload as it is")
+    pub.add_argument("--run-dir", help="a run directory: publish the comparison views under <run-dir>/validation through the store protocol")
     pub.add_argument("--destination", required=True)
+    pub.add_argument("--node-rank", type=int, default=int(os.environ.get("NODE_RANK", "0")))
+    pub.add_argument("--num-nodes", type=int, default=int(os.environ.get("NUM_NODES", "1")))
     return ap
 
 
@@ -200,9 +203,17 @@ def environment_command(args) -> int:
 
 
 def publish_validation_command(args) -> int:
-    from .runtime.validation_publish import publish_validation
+    from .runtime.validation_publish import ValidationPublisher, publish_validation
 
-    print(json.dumps(publish_validation(args.source, args.destination), sort_keys=True))
+    if args.run_dir:
+        from .runtime.object_store import store_for
+
+        report = ValidationPublisher(args.run_dir, store_for(args.destination), node=args.node_rank, nodes=args.num_nodes).scan()
+        print(json.dumps(report, sort_keys=True))
+        return 3 if report["errors"] else 0
+    if not args.source:
+        raise ValueError("publish-validation needs --source or --run-dir")
+    print(json.dumps(publish_validation(args.source, args.destination, node=args.node_rank, nodes=args.num_nodes), sort_keys=True))
     return 0
 
 
