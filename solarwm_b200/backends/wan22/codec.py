@@ -9,8 +9,9 @@
   continuous feature cache across pieces (so the pieces concatenate to exactly the one-shot decode), each checked
   for non-finite pixels before it leaves the device; the cache is cleared at the start and in ``finally``.
 
-``Wan5BVAE`` (48 channels, 4 x 16 x 16 compression) takes its statistics from the checkpoint;
-``WanA14BVAE`` (16 channels, 4 x 8 x 8) carries the published Wan2.1 statistics.  ``flow_to_x0`` does the
+``Wan5BVAE`` (48 channels, 4 x 16 x 16 compression) and ``WanA14BVAE`` (16 channels, 4 x 8 x 8) carry the published
+latent statistics; ``from_checkpoint`` builds the published topology (``models.wan_vae_released``) and fills it
+strictly from the published weight file, ``build`` gives this package's own lighter topology for random-init runs.  ``flow_to_x0`` does the
 flow -> clean-sample conversion in fp64 as the reference's scheduler wrapper does.
 
 Reference behaviour: solar/backends/wan22/runtime/components.py:66-330 (``Wan5BVAE``, ``WanA14BVAE``),
@@ -76,8 +77,23 @@ class WanVideoCodec:
 
 
 class Wan5BVAE(WanVideoCodec):
-    """48-channel Wan2.2 VAE (TI2V-5B); statistics come with the checkpoint."""
+    """48-channel Wan2.2 VAE (TI2V-5B) with its published latent statistics."""
     latent_channels = 48
+    mean = (-0.2289, -0.0052, -0.1323, -0.2339, -0.2799, 0.0174, 0.1838, 0.1557, -0.1382, 0.0542, 0.2813, 0.0891,
+            0.1570, -0.0098, 0.0375, -0.1825, -0.2246, -0.1207, -0.0698, 0.5109, 0.2665, -0.2108, -0.2158, 0.2502,
+            -0.2055, -0.0322, 0.1109, 0.1567, -0.0729, 0.0899, -0.2799, -0.1230, -0.0313, -0.1649, 0.0117, 0.0723,
+            -0.2839, -0.2083, -0.0520, 0.3748, 0.0152, 0.1957, 0.1433, -0.2944, 0.3573, -0.0548, -0.1681, -0.0667)
+    std = (0.4765, 1.0364, 0.4514, 1.1677, 0.5313, 0.4990, 0.4818, 0.5013, 0.8158, 1.0344, 0.5894, 1.0901,
+            0.6885, 0.6165, 0.8454, 0.4978, 0.5759, 0.3523, 0.7135, 0.6804, 0.5833, 1.4146, 0.8986, 0.5659,
+            0.7069, 0.5338, 0.4889, 0.4917, 0.4069, 0.4999, 0.6866, 0.4093, 0.5709, 0.6065, 0.6415, 0.4944,
+            0.5726, 1.2042, 0.5458, 1.6887, 0.3971, 1.0600, 0.3943, 0.5537, 0.5444, 0.4089, 0.7468, 0.7744)
+
+    @classmethod
+    def from_checkpoint(cls, path, *, device="cpu", dtype=torch.float32):
+        """The published ``Wan2.2_VAE.pth`` in the published topology (160-wide encoder, 256-wide decoder)."""
+        from ...models.wan_vae_released import ReleasedVAEConfig, load_released
+
+        return cls(load_released(path, ReleasedVAEConfig.wan22(), cls.mean, cls.std, device=device, dtype=dtype))
 
     @classmethod
     def build(cls, mean: Sequence[float], std: Sequence[float], base: int = 64):
@@ -97,6 +113,13 @@ class WanA14BVAE(WanVideoCodec):
     @classmethod
     def build(cls, base: int = 96):
         return cls(VideoVAE(VAEConfig(z_dim=16, base=base, temporal_ups=(True, True, False)), list(cls.mean), list(cls.std)))
+
+    @classmethod
+    def from_checkpoint(cls, path, *, device="cpu", dtype=torch.float32):
+        """The published ``Wan2.1_VAE.pth`` (original or diffusers tensor names) in the published topology."""
+        from ...models.wan_vae_released import ReleasedVAEConfig, load_released
+
+        return cls(load_released(path, ReleasedVAEConfig.wan21(), cls.mean, cls.std, device=device, dtype=dtype))
 
 
 def flow_to_x0(x_t: torch.Tensor, flow: torch.Tensor, sigma: torch.Tensor) -> torch.Tensor:

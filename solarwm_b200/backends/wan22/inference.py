@@ -136,7 +136,7 @@ class WanLatentAdapter:
         self._text_encoder = None
 
     def _pixels(self, latents):
-        """``inference.vae`` (``{z_dim, base, temporal_ups, checkpoint?, fps?, chunk_latent_frames?}``): the sampled latents
+        """``inference.vae`` (``{z_dim, base, temporal_ups, checkpoint?, released?, fps?, chunk_latent_frames?}``): the sampled latents
         [1, F, C, H, W] decoded chunk by chunk through the codec adapter, as pieces ``[T, 3, H, W]`` in [-1, 1]."""
         spec = (self.config.get("inference", {}) or {}).get("vae")
         if not spec:
@@ -148,6 +148,15 @@ class WanLatentAdapter:
             spec = dict(spec)
             ckpt, self._fps = spec.pop("checkpoint", None), float(spec.pop("fps", 16.0))
             self._chunk = int(spec.pop("chunk_latent_frames", 8))
+            released = spec.pop("released", None)       # "wan2.2" / "wan2.1": the published topology + weight file
+            if released:
+                from .codec import Wan5BVAE, WanA14BVAE
+
+                kind = {"wan2.2": Wan5BVAE, "wan2.1": WanA14BVAE}.get(str(released))
+                if kind is None or not ckpt:
+                    raise BackendContractError("inference.vae.released is 'wan2.2' or 'wan2.1' and needs a checkpoint")
+                self._codec = kind.from_checkpoint(ckpt, device=latents.device, dtype=latents.dtype)
+                return (piece[0] for piece in self._codec.decode_streaming_chunks(latents, chunk_latent_frames=self._chunk))
             if "temporal_ups" in spec:
                 spec["temporal_ups"] = tuple(bool(u) for u in spec["temporal_ups"])
             vae = VideoVAE(VAEConfig(**spec)).to(latents.device, latents.dtype)
@@ -225,10 +234,13 @@ class WanLatentAdapter:
                 from ...models.t5 import T5Config, WanTextEncoder
 
                 spec = dict(spec)
-                ckpt = spec.pop("checkpoint", None)
-                enc = WanTextEncoder(T5Config(**spec), device=dev, dtype=torch.float32)
-                if ckpt:
-                    enc.model.load_state_dict(torch.load(ckpt, map_location=dev, weights_only=True))
+                ckpt, tokenizer = spec.pop("checkpoint", None), spec.pop("tokenizer", None)
+                if ckpt and tokenizer:                  # the published encoder file + tokenizer directory
+                    enc = WanTextEncoder.from_released(ckpt, tokenizer, cfg=T5Config(**spec), device=dev)
+                else:
+                    enc = WanTextEncoder(T5Config(**spec), device=dev, dtype=torch.float32)
+                    if ckpt:
+                        enc.model.load_state_dict(torch.load(ckpt, map_location=dev, weights_only=True))
                 self._text_encoder = enc
             text = self._text_encoder([case.prompt])
             if tuple(text.shape[1:]) != (cfg.text_len, cfg.text_dim):

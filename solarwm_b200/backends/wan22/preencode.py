@@ -80,14 +80,28 @@ def run_preencode(config: Mapping[str, Any], family: str, *, latent_channels: in
     vcfg = VAEConfig(z_dim=int(codecs.get("z_dim", latent_channels or prof.latent_channels)),
                      base=int(codecs.get("vae_base", 16)), temporal_ups=ups)
     tcfg = T5Config(**codecs["t5"]) if "t5" in codecs else T5Config.tiny()
-    vae = VideoVAE(vcfg).to(device=device, dtype=torch.float32).eval()
-    text = WanTextEncoder(tcfg, device=device, dtype=torch.float32)
-    if codecs.get("vae_checkpoint"):
-        vae.load_state_dict(torch.load(codecs["vae_checkpoint"], map_location=device, weights_only=True))
-    if codecs.get("t5_checkpoint"):
-        text.model.load_state_dict(torch.load(codecs["t5_checkpoint"], map_location=device, weights_only=True))
-    t_stride = 2 ** sum(vcfg.temporal_ups)
-    s_stride = 2 ** len(vcfg.temporal_ups)
+    released = codecs.get("released_vae")           # "wan2.2" / "wan2.1": the published topology + ``vae_checkpoint``
+    if released:
+        from .codec import Wan5BVAE, WanA14BVAE
+
+        kind = {"wan2.2": Wan5BVAE, "wan2.1": WanA14BVAE}.get(str(released))
+        if kind is None or not codecs.get("vae_checkpoint"):
+            raise BackendContractError("preencode.codecs.released_vae is 'wan2.2' or 'wan2.1' and needs vae_checkpoint")
+        vae = kind.from_checkpoint(codecs["vae_checkpoint"], device=device).vae
+        t_stride, s_stride = 4, 8 * vae.cfg.patch
+        vcfg = vae.cfg
+    else:
+        vae = VideoVAE(vcfg).to(device=device, dtype=torch.float32).eval()
+        if codecs.get("vae_checkpoint"):
+            vae.load_state_dict(torch.load(codecs["vae_checkpoint"], map_location=device, weights_only=True))
+        t_stride = 2 ** sum(vcfg.temporal_ups)
+        s_stride = 2 ** len(vcfg.temporal_ups)
+    if codecs.get("t5_checkpoint") and codecs.get("tokenizer"):     # the published encoder file + tokenizer directory
+        text = WanTextEncoder.from_released(codecs["t5_checkpoint"], codecs["tokenizer"], cfg=tcfg, device=device, dtype=torch.float32)
+    else:
+        text = WanTextEncoder(tcfg, device=device, dtype=torch.float32)
+        if codecs.get("t5_checkpoint"):
+            text.model.load_state_dict(torch.load(codecs["t5_checkpoint"], map_location=device, weights_only=True))
     contract = wan_contract(family, pixel_frames=int(data["pixel_frames"]), height=int(data["pixel_height"]),
                             width=int(data["pixel_width"]), z_dim=vcfg.z_dim, text_len=tcfg.text_len,
                             text_dim=tcfg.dim, temporal_stride=t_stride, spatial_stride=s_stride,

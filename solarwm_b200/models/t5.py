@@ -129,6 +129,50 @@ class HashTokenizer:
         return ids, mask
 
 
+def clean_prompt(text: str) -> str:
+    """HTML entities resolved (twice, as scraped captions need), whitespace runs collapsed, ends stripped."""
+    import html
+    import re
+
+    return re.sub(r"\s+", " ", html.unescape(html.unescape(text))).strip()
+
+
+class PromptTokenizer:
+    """The published tokenizer directory behind the ``(ids, mask)`` contract: ``tokenizer.json`` through the
+    ``tokenizers`` library when present, else ``spiece.model`` through sentencepiece.  Prompts are cleaned, cut to
+    ``text_len - 1`` pieces, closed with the end-of-sequence id and padded with the pad id (reference:
+    solar/backends/wan22/runtime/modeling/tokenizers.py:20-82, ``padding="max_length", truncation=True``)."""
+
+    def __init__(self, directory, text_len: int, *, pad_id: int = 0, eos_id: int = 1):
+        from pathlib import Path
+
+        root = Path(directory)
+        self.text_len, self.pad_id, self.eos_id = int(text_len), pad_id, eos_id
+        if (root / "tokenizer.json").is_file():
+            from tokenizers import Tokenizer
+
+            tk = Tokenizer.from_file(str(root / "tokenizer.json"))
+            tk.no_padding()
+            tk.no_truncation()
+            self._pieces = lambda text: tk.encode(text, add_special_tokens=False).ids
+        elif (root / "spiece.model").is_file():
+            import sentencepiece
+
+            sp = sentencepiece.SentencePieceProcessor(model_file=str(root / "spiece.model"))
+            self._pieces = lambda text: list(sp.encode(text))
+        else:
+            raise FileNotFoundError(f"{root} holds neither tokenizer.json nor spiece.model")
+
+    def __call__(self, texts: Sequence[str]):
+        ids = torch.full((len(texts), self.text_len), self.pad_id, dtype=torch.long)
+        mask = torch.zeros(len(texts), self.text_len, dtype=torch.bool)
+        for i, t in enumerate(texts):
+            toks = [x for x in self._pieces(clean_prompt(t)) if x != self.eos_id][: self.text_len - 1] + [self.eos_id]
+            ids[i, :len(toks)] = torch.tensor(toks)
+            mask[i, :len(toks)] = True
+        return ids, mask
+
+
 class WanTextEncoder:
     """prompts -> [B, text_len, dim] with the positions past each prompt zeroed (what the DiT's text
     embedding consumes)."""
@@ -143,6 +187,23 @@ class WanTextEncoder:
         self.model = self.model.to(device=device, dtype=dtype).eval().requires_grad_(False)
         self.tok = tokenizer or HashTokenizer(cfg.vocab, cfg.text_len)
         self.device = torch.device(device)
+
+    @classmethod
+    def from_released(cls, weights, tokenizer_dir, *, cfg: T5Config = T5Config(), device="cpu", dtype=torch.bfloat16):
+        """The published encoder file (``models_t5_umt5-xxl-enc-bf16.pth``: a plain state dict under the names of this
+        module) loaded strictly, with the published tokenizer directory (reference: WanTextEncoder,
+        solar/backends/wan22/runtime/components.py:21-64)."""
+        self = cls.__new__(cls)
+        with torch.device("meta"):
+            model = T5Encoder(cfg)
+        state = torch.load(str(weights), map_location="cpu", weights_only=True, mmap=True)
+        result = model.load_state_dict(state, strict=True, assign=True)
+        if result.missing_keys or result.unexpected_keys or any(p.is_meta for p in model.parameters()):
+            raise ValueError(f"text-encoder checkpoint {weights} does not match the architecture")
+        self.model = model.to(device=device, dtype=dtype).eval().requires_grad_(False)
+        self.tok = PromptTokenizer(tokenizer_dir, cfg.text_len)
+        self.device = torch.device(device)
+        return self
 
     @torch.no_grad()
     def __call__(self, prompts: Sequence[str]):

@@ -71,6 +71,30 @@ def test_vae_decoder_on_native_convolutions_matches_library_path_and_streams():
     assert isinstance(vae.decoder.conv_in, CausalConv3d)
 
 
+def test_published_topology_decoder_on_native_convolutions_matches_fp32_and_streams():
+    from solarwm_b200.models.vae import StreamingDecoder
+    from solarwm_b200.models.wan_vae_released import ReleasedVAE, ReleasedVAEConfig
+    from solarwm_b200.ops import _lib
+
+    for cfg in (ReleasedVAEConfig.wan22(enc_dim=16, dec_dim=16, z_dim=16), ReleasedVAEConfig.wan21(dim=16, z_dim=16)):
+        torch.manual_seed(0)
+        vae = ReleasedVAE(cfg).cuda().bfloat16().eval()
+        z = torch.randn(1, 16, 3, 6, 10).cuda().bfloat16()
+        before = _lib.COUNTERS.get("conv3d", 0)
+        with torch.no_grad():
+            native = vae.decode(z).float()
+        assert _lib.COUNTERS.get("conv3d", 0) > before
+        ref_vae = ReleasedVAE(cfg).cuda().float().eval()
+        ref_vae.load_state_dict({k: v.float() for k, v in vae.state_dict().items()})
+        with torch.no_grad():
+            want = ref_vae.decode(z.float())
+        assert native.shape == want.shape == (1, 3, 9, 48 * cfg.patch, 80 * cfg.patch)
+        assert (native - want).abs().max() / want.abs().max() < 6e-2
+        dec = StreamingDecoder(vae)
+        streamed = torch.cat([dec.push(z[:, :, :1]), dec.push(z[:, :, 1:])], 2).float()
+        assert (streamed - native).abs().max() / native.abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("C", [16, 64, 160, 1024])
 def test_rms_silu_channels_last_matches_unfused_composition(C):
     from solarwm_b200.models.vae import RMSNormC
