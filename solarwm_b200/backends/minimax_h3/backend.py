@@ -1,5 +1,6 @@
 """H3 backend boundary (reference: MiniMaxH3Backend solar/backends/minimax_h3/backend.py:15-44, H3Stage0p5Core
-stage0p5.py:37-300).  Stage0.5 adapter training runs through ``runtime.H3TrainingRuntime`` (any SP x DP layout); the
+stage0p5.py:37-300).  Stage0.5 and Stage1 adapter training run through ``runtime.H3TrainingRuntime`` (any SP x DP layout for Stage0.5),
+Stage2 through ``stage2_runtime.H3SGFRuntime`` (three roles over one base, data parallel); the
 frozen bf16 base is never saved, the checkpoint holds ``adapter.pt`` (schema solarwm.minimax-h3-lora.v1),
 ``optimizer.pt``, ``scheduler.pt``, ``ema.pt``, ``rank-state.pt`` and ``runtime.pt``.  ``H3Stage0p5Trainer`` is the
 single-process step the benchmarks and unit tests drive directly."""
@@ -11,12 +12,11 @@ from typing import Any, Mapping
 import torch
 
 from ... import ops
-from ...checkpoint.store import CheckpointContract, CheckpointTransaction
 from ...config.routes import validate_route
 from ...engine.master_adamw import FP32MasterAdamW
 from ...errors import BackendContractError, ConfigurationError
 from ...models.h3 import H3DiT, h3_preset
-from ...runtime.output_layout import checkpoint_model_dir, output_root
+from ...runtime.output_layout import output_root
 from . import flow
 from .layout import build_layout, expand_cameras, patchify_latents
 
@@ -94,60 +94,12 @@ class MiniMaxH3Backend:
     def train(self, config):
         route = validate_route(config)
         if route.stage == "stage2":
-            return self._train_causal(config, route)
+            from .stage2_runtime import run_sgf_training
+
+            return run_sgf_training(config, model_config=self._cfg(config), load_released=self._load_released)
         from .runtime import run_training
 
         return run_training(config, model_config=self._cfg(config), load_released=self._load_released)
-
-    def _train_causal(self, config, route):
-        """Stage1 (teacher forcing: flow matching or AnyFlow under the W6 rule) and Stage2 (SGF) on the
-        configured synthetic source; adapters and optimizer state go through the transactional store."""
-        from ...data.synthetic import h3_sample
-        from .stage1 import H3Stage1Trainer
-        from .stage2 import H3Stage2Trainer
-
-        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
-        data, train = config["data"], config["train"]
-        causal = config["model"].get("causal", {}) or {}
-        k, w = int(causal.get("chunk_latents", 5)), int(causal.get("window_chunks", 5))
-        cfg = self._cfg(config)
-        lr = float(train.get("optimizer", {}).get("lr", 1e-4))
-        seed = int(data.get("seed", 0))
-        frames = int(data.get("latent_frames", 2 * k))
-        size = (int(data.get("latent_height", 8)), int(data.get("latent_width", 8)))
-        if route.stage == "stage1":
-            objective = "anyflow" if route.objective.startswith("anyflow") else "tf_fm"
-            tr = H3Stage1Trainer(cfg, dev, objective=objective, chunk_latents=k, window_chunks=w, lr=lr, seed=seed)
-            step = lambda s: {"loss": float(tr.train_step(s))}      # noqa: E731
-            adapters = lambda: {"student": tr.model}                  # noqa: E731
-        else:
-            tr = H3Stage2Trainer(cfg, dev, chunk_latents=k, window_chunks=w, grid_hw=(size[0] // 2, size[1] // 2),
-                                 denoise_steps=int(train.get("denoise_steps", 4)), lr_student=lr,
-                                 lr_critic=float(train.get("critic_optimizer", {}).get("lr", lr * 0.2)),
-                                 critic_updates_per_student=int(train.get("critic_updates_per_student", 5)), seed=seed)
-            step = lambda s: dict(tr.train_outer_step(s, n_chunks=frames // k))     # noqa: E731
-            adapters = lambda: {"student": tr.student, "critic": tr.critic}           # noqa: E731
-        last, t0 = {}, time.time()
-        n = int(train["max_steps"])
-        for i in range(n):
-            s = h3_sample(latent_frames=frames, height=size[0], width=size[1], prompt_len=int(data.get("prompt_len", 8)),
-                          text_dim=cfg.text_dim, seed=seed * 1000 + i)
-            s["camera_w2c"] = torch.eye(4).repeat(frames + 1, 1, 1)
-            last = step(s)
-            print(f"[h3-{route.stage}] step={i + 1} " + " ".join(f"{a}={b:.5f}" for a, b in last.items())
-                  + f" compute_time_s={time.time() - t0:.2f}")
-        target = checkpoint_model_dir(output_root(config), n)
-        with CheckpointTransaction(target) as tx:
-            for role, model in adapters().items():
-                torch.save({"schema": "solarwm.minimax-h3-lora.v1", "rank": cfg.lora_rank,
-                            "state": {k_: p.detach().cpu() for k_, p in model.named_parameters() if p.requires_grad}},
-                           tx.path / ("adapter.pt" if role == "student" else f"{role}.pt"))
-            torch.save({"global_step": n}, tx.path / "runtime.pt")
-            tx.commit(step=n, contract=CheckpointContract(
-                family="minimax_h3", stage=route.stage, causal_mode=route.causal_mode, objective=route.objective,
-                objective_variant=route.variant, camera_translation_transform="logd4", parameterization="lora",
-                sp_size=1, data_generation="synthetic"), required_components=["adapter.pt", "runtime.pt"], metadata={})
-        return {"final_step": n, "last": last, "checkpoint": str(target), "native_launches": ops.total_launches()}
 
     def infer(self, config):
         """Camera-length generation: chunk-by-chunk streaming over the camera path with the latent memory bank

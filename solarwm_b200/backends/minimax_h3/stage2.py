@@ -55,7 +55,22 @@ class H3Stage2Trainer:
                                          denoise_steps=denoise_steps, use_cuda_graph=False, seed=seed)
         self.ratio, self.scale = critic_updates_per_student, guidance_scale
         self.gen = torch.Generator(device=self.device).manual_seed(seed * 100003 + 11)
-        self.global_step = 0
+        self.global_step = self.student_step = 0
+        self.teacher = None                    # ``set_teacher``: a third role with its own frozen adapters
+        self.sync = None                       # ``sync(params, flat_fp32_grad)``: the runtime's reduction over ranks
+
+    def set_teacher(self, adapter_state: Mapping[str, torch.Tensor], seed: int = 0) -> None:
+        """Build the teacher role: the shared frozen base with the given adapter weights, never trained."""
+        t = H3DiT(self.student.cfg, device=self.device, dtype=self.student.dtype, seed=seed)
+        share_base(t, self.student)
+        own = dict(t.named_parameters())
+        wanted = {n for n, p in own.items() if p.requires_grad}
+        if set(adapter_state) != wanted:
+            raise ValueError("the teacher's adapter file does not hold exactly this architecture's adapter tensors")
+        with torch.no_grad():
+            for n in wanted:
+                own[n].copy_(adapter_state[n].to(own[n]))
+        self.teacher = t.eval().requires_grad_(False)
 
     # ------------------------------------------------------------------------------------
     def _adapters_off(self, model):
@@ -93,60 +108,114 @@ class H3Stage2Trainer:
         exit_index = int(torch.randint(0, len(gen.times), (1,), generator=self.gen, device=self.device).item())
         return torch.cat(chunks, dim=1), float(gen.times[exit_index])
 
-    def train_outer_step(self, sample: Mapping[str, torch.Tensor], n_chunks: int = 2) -> Mapping[str, float]:
+    def _replay(self, sample, n_chunks: int, *, grad: bool):
+        """Roll the student out (no gradient), then evaluate it once under teacher forcing at the exit time; returns
+        the student's clean-sample rows (with a graph when ``grad``) and the latent geometry."""
         dev = self.device
         cams = sample.get("camera_w2c")
         generated, t_exit = self.rollout(sample, n_chunks, cams)                     # [C, F, H, W]
         C, F, H, W = generated.shape
         dt = self.student.dtype
-        update_student = should_update_student(self.global_step, self.ratio)
         noise = torch.randn(generated.shape, generator=self.gen, device=dev, dtype=torch.float32)
         clean_rows = patchify_latents(generated).to(dt)
         noisy_rows = (t_exit * clean_rows.float() + (1 - t_exit) * patchify_latents(noise)).to(dt)
         anchor_rows = patchify_latents(sample["anchor_latents"].to(dev)).to(dt)
-        with torch.set_grad_enabled(update_student):
+        with torch.set_grad_enabled(grad):
             v = teacher_forcing_forward(self.student, prompt=sample["prompt_embeds"].to(dev, dt), anchor_rows=anchor_rows,
                                         clean_rows=clean_rows, noisy_rows=noisy_rows,
                                         t_chunks=torch.full((n_chunks,), t_exit, device=dev), grid_hw=(H // 2, W // 2),
                                         chunk_latents=self.stream_cfg.chunk_latents,
                                         window_chunks=self.stream_cfg.window_chunks, cameras=cams)
             out_rows = noisy_rows.float() + (1 - t_exit) * v.float()                 # student x0 (rows)
+        return out_rows, (C, F, H, W)
+
+    def _finish(self, opt, label: str) -> float:
+        """Pack the gradients, let the runtime reduce them over the ranks, refuse non-finite norms, clip, step."""
+        flat = opt.gather_grads()
+        if self.sync is not None:
+            self.sync(opt.params, flat)
+        norm = float(opt.clip_(10.0))
+        if not (norm == norm and norm != float("inf")):
+            opt.zero_grad()
+            raise FloatingPointError(f"non-finite H3 SGF {label} gradient norm")
+        opt.step()
+        opt.zero_grad()
+        return norm
+
+    def _real_x0(self, x_t, t_s, sample, cams):
+        """The guided "real" score: the teacher role when one was built, else the student with its adapters off."""
+        import contextlib
+
+        model = self.teacher if self.teacher is not None else self.student
+        scope = contextlib.nullcontext() if self.teacher is not None else self._adapters_off(self.student)
+        with scope:
+            real, _ = self._bidirectional_x0(model, x_t, t_s, sample, cams)
+            if self.scale != 1.0:
+                null = dict(sample, prompt_embeds=torch.zeros_like(sample["prompt_embeds"]))
+                real_u, _ = self._bidirectional_x0(model, x_t, t_s, null, cams)
+                real = real_u + self.scale * (real - real_u)
+        return real
+
+    def student_phase(self, sample: Mapping[str, torch.Tensor], n_chunks: int = 2) -> Mapping[str, float]:
         from .layout import unpatchify_rows
 
+        dev, dt, cams = self.device, self.student.dtype, sample.get("camera_w2c")
+        out_rows, (C, F, H, W) = self._replay(sample, n_chunks, grad=True)
         out_lat = unpatchify_rows(out_rows.detach().to(dt), C, F, H, W)
-        result = {}
-        if update_student:
-            t_s = float(0.02 + 0.96 * torch.rand(1, generator=self.gen, device=dev))
-            n2 = torch.randn(generated.shape, generator=self.gen, device=dev, dtype=torch.float32).to(dt)
-            x_t = flow.interpolate(out_lat, n2, t_s)
-            with torch.no_grad():
-                fake, _ = self._bidirectional_x0(self.critic, x_t, t_s, sample, cams)
-                with self._adapters_off(self.student):
-                    real, _ = self._bidirectional_x0(self.student, x_t, t_s, sample, cams)
-                    if self.scale != 1.0:
-                        null = dict(sample, prompt_embeds=torch.zeros_like(sample["prompt_embeds"]))
-                        real_u, _ = self._bidirectional_x0(self.student, x_t, t_s, null, cams)
-                        real = real_u + self.scale * (real - real_u)
-            g = sgf_kl_gradient(fake_x0=fake.unsqueeze(0), real_x0=real.unsqueeze(0), student_output=out_rows.detach().unsqueeze(0))
-            loss_s = sgf_student_loss(out_rows.unsqueeze(0), g)
-            loss_s.backward()
-            self.opt_s.gather_grads()
-            self.opt_s.clip_(10.0)
-            self.opt_s.step()
-            self.opt_s.zero_grad()
-            result["student"] = float(loss_s.detach())
-        # critic: flow matching on the student's sample
+        t_s = float(0.02 + 0.96 * torch.rand(1, generator=self.gen, device=dev))
+        n2 = torch.randn((C, F, H, W), generator=self.gen, device=dev, dtype=torch.float32).to(dt)
+        x_t = flow.interpolate(out_lat, n2, t_s)
+        with torch.no_grad():
+            fake, _ = self._bidirectional_x0(self.critic, x_t, t_s, sample, cams)
+            real = self._real_x0(x_t, t_s, sample, cams)
+            if not bool(torch.isfinite(fake).all() and torch.isfinite(real).all()):
+                raise FloatingPointError("non-finite H3 SGF score output")
+        g = sgf_kl_gradient(fake_x0=fake.unsqueeze(0), real_x0=real.unsqueeze(0), student_output=out_rows.detach().unsqueeze(0))
+        loss_s = sgf_student_loss(out_rows.unsqueeze(0), g)
+        loss_s.backward()
+        norm = self._finish(self.opt_s, "student")
+        self.student_step += 1
+        return {"student": float(loss_s.detach()), "student_grad_norm": norm}
+
+    def critic_phase(self, sample: Mapping[str, torch.Tensor], n_chunks: int = 2, replayed=None) -> Mapping[str, float]:
+        """Flow matching of the critic on the student's sample (``replayed``: rows and geometry of a replay that was
+        just made on the same sample, so the single-sample form of the outer step does not roll out twice)."""
+        from .layout import unpatchify_rows
+
+        dev, dt, cams = self.device, self.student.dtype, sample.get("camera_w2c")
+        out_rows, (C, F, H, W) = replayed if replayed is not None else self._replay(sample, n_chunks, grad=False)
+        out_lat = unpatchify_rows(out_rows.detach().to(dt), C, F, H, W)
         t_c = float(0.02 + 0.96 * torch.rand(1, generator=self.gen, device=dev))
-        n3 = torch.randn(generated.shape, generator=self.gen, device=dev, dtype=torch.float32).to(dt)
+        n3 = torch.randn((C, F, H, W), generator=self.gen, device=dev, dtype=torch.float32).to(dt)
         x_tc = flow.interpolate(out_lat, n3, t_c)
         _, vel = self._bidirectional_x0(self.critic, x_tc, t_c, sample, cams)
         target = patchify_latents(out_lat.float() - n3.float())
         loss_c = (vel.float() - target).pow(2).mean()
+        if not bool(torch.isfinite(loss_c)):
+            raise FloatingPointError("non-finite H3 SGF critic loss")
         loss_c.backward()
-        self.opt_c.gather_grads()
-        self.opt_c.clip_(10.0)
-        self.opt_c.step()
-        self.opt_c.zero_grad()
-        result["critic"] = float(loss_c.detach())
+        norm = self._finish(self.opt_c, "critic")
+        return {"critic": float(loss_c.detach()), "critic_grad_norm": norm}
+
+    def train_outer_step(self, sample: Mapping[str, torch.Tensor], n_chunks: int = 2, critic_sample=None) -> Mapping[str, float]:
+        """One outer step: the student phase on every ``critic_updates_per_student``-th step, the critic phase always.
+        With ``critic_sample`` the two phases see different samples (two rollouts, as the training runtime does);
+        without it the critic learns from the replay the student phase just made."""
+        result = {}
+        update_student = should_update_student(self.global_step, self.ratio)
+        if critic_sample is None:
+            out_rows, geometry = self._replay(sample, n_chunks, grad=update_student)
+            if update_student:
+                held = self._replay
+                self._replay = lambda *a, **k: (out_rows, geometry)          # the phase consumes the replay made above
+                try:
+                    result.update(self.student_phase(sample, n_chunks))
+                finally:
+                    self._replay = held
+            result.update(self.critic_phase(sample, n_chunks, replayed=(out_rows.detach(), geometry)))
+        else:
+            if update_student:
+                result.update(self.student_phase(sample, n_chunks))
+            result.update(self.critic_phase(critic_sample, n_chunks))
         self.global_step += 1
         return result
