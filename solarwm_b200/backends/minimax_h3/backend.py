@@ -110,6 +110,8 @@ class MiniMaxH3Backend:
         from ...serve.h3_stream import H3StreamConfig
 
         inf = config.get("inference", {}) or {}
+        if inf.get("length_policy") == "source":
+            return self._infer_source_length(config)
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
         cfg = self._cfg(config)
         cfg.lora_rank = 0 if inf.get("merged_weights", True) else cfg.lora_rank
@@ -185,6 +187,78 @@ class MiniMaxH3Backend:
         return {"output_dir": str(out_dir), "chunks": manifest.get("chunks"), "frames": manifest.get("frames"),
                 "video": manifest.get("video"),
                 "native_launches": ops.total_launches()}
+
+    def _infer_source_length(self, config):
+        """``inference.length_policy: source``: every row of ``inference.plan`` is prepared once (cameras at the clip's
+        latent cadence, prompt and anchor from ``<inference.sources>/<key>.pt`` holding ``text``, ``anchor_latent``,
+        ``c2w`` [F, 4, 4], ``intrinsics`` [F, 3, 3]) and generated at the clip's own length; ranks split the plan, finished
+        cases are verified and skipped (``serve/h3_source_length.py``)."""
+        import os
+        from pathlib import Path
+
+        from ...serve.h3_source_length import load_plan, prepare_case, run_plan
+        from ...serve.h3_stream import H3StreamConfig
+
+        inf = config["inference"]
+        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
+        cfg = self._cfg(config)
+        cfg.lora_rank = 0 if inf.get("merged_weights", True) else cfg.lora_rank
+        model = H3DiT(cfg, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, seed=int(inf.get("seed", 0)))
+        self._load_released(model, config)
+        gh, gw = (int(v) for v in inf.get("grid_hw", (24, 42)))
+        use_memory = bool(inf.get("memory", False))
+        top_k = int(inf.get("top_k", 5))
+        scfg = H3StreamConfig(grid_hw=(gh, gw), chunk_latents=5, window_chunks=int(inf.get("window_chunks", 5)),
+                              denoise_steps=int(inf.get("denoise_steps", 4)), use_cuda_graph=dev == "cuda",
+                              memory_latents=top_k if use_memory else 0)
+        fps_policy = str(inf.get("fps_policy", "source"))
+        rows = load_plan(inf["plan"], stream_decode=bool(inf.get("stream_decode", False)), fps_policy=fps_policy)
+        rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+        work = Path(str(inf.get("work_dir") or (output_root(config) / "work")))
+        sources = Path(str(inf["sources"]))
+        prep_identity = {"sources": str(sources), "grid_hw": [gh, gw], "text_dim": cfg.text_dim}
+        for row in rows[rank::world]:
+            src = torch.load(sources / f"{row['key']}.pt", map_location="cpu", weights_only=True)
+            prepare_case(work, row, c2w=src["c2w"], intrinsics=src["intrinsics"], encode_prompt=lambda _t, s=src: s["text"],
+                         encode_anchor=lambda s=src: s["anchor_latent"], identity=prep_identity)
+        decoder_factory = writer_factory = None
+        if inf.get("decoder"):
+            from ...models.vit_decoder import StreamingViTDecoder, ViTDecoderConfig, ViTVideoDecoder
+            from ...serve.media import SIGNED_UNIT, FrameSink
+
+            spec = dict(inf["decoder"])
+            ckpt = spec.pop("checkpoint", None)
+            vcfg = ViTDecoderConfig(latent_channels=scfg.latent_channels, **spec)
+            vit = ViTVideoDecoder(vcfg, device=dev, dtype=model.dtype, seed=0)
+            if ckpt:
+                vit.load_state_dict(torch.load(ckpt, map_location=dev, weights_only=True))
+            decoder_factory = lambda: StreamingViTDecoder(vit, (2 * gh, 2 * gw))      # noqa: E731
+
+            class _Writer:
+                def __init__(self, path, fps):
+                    self.path = Path(path)
+                    self.sink = FrameSink(self.path.with_suffix(""), 2 * gw * vcfg.patch, 2 * gh * vcfg.patch, fps=fps,
+                                          use_ffmpeg=inf.get("use_ffmpeg"), normalization=SIGNED_UNIT)
+
+                def push(self, frames):
+                    for f in range(frames.shape[1]):
+                        self.sink.push(frames[:, f])
+
+                def close(self):
+                    info = self.sink.close()
+                    self.path.write_text(json.dumps(dict(info), sort_keys=True, default=str))
+
+            import json
+
+            writer_factory = _Writer
+        summary = run_plan(model, rows, work_dir=work, out_dir=output_root(config) / "generate", stream_cfg=scfg,
+                           identity={"weights": str(config.get("model", {}).get("base_path", "init:random")),
+                                     "checkpoint": str((config.get("checkpoint", {}) or {}).get("resume_from", "")),
+                                     "denoise_steps": scfg.denoise_steps, "window_chunks": scfg.window_chunks},
+                           rank=rank, world=world, noise_seed=int(inf.get("seed", 0)), decoder_factory=decoder_factory,
+                           writer_factory=writer_factory, use_memory=use_memory, top_k=top_k, fps_policy=fps_policy,
+                           save_latents=bool(inf.get("save_latents", False)))
+        return {"output_dir": str(output_root(config) / "generate"), **summary, "native_launches": ops.total_launches()}
 
     def preencode(self, config):
         """Raw clips + captions -> 24-channel latent / text shards (4 x 16 x 16 codec geometry; random-init codecs

@@ -33,10 +33,16 @@ def _w2c(c2w: torch.Tensor) -> torch.Tensor:
 def generate_full_length(model, *, text: torch.Tensor, anchor_latent: torch.Tensor, c2w: torch.Tensor,
                          intrinsics: torch.Tensor, stream_cfg: H3StreamConfig = H3StreamConfig(), sp=None,
                          decoder=None, frame_sink: Optional[Callable[[torch.Tensor], None]] = None,
-                         use_memory: bool = False, top_k: int = 5, out_dir=None) -> Mapping[str, object]:
+                         use_memory: bool = False, top_k: int = 5, out_dir=None, decode_latents: Optional[int] = None,
+                         max_frames: Optional[int] = None, progress: Optional[Callable[[int, int], None]] = None,
+                         keep_latents: bool = False) -> Mapping[str, object]:
     """c2w [1 + n_latents, 4, 4] (anchor first), intrinsics [1 + n_latents, 3, 3] normalised.  ``decoder`` is a
     ``StreamingViTDecoder``-like object with ``push(latent [C, h, w]) -> frames or None``; ``frame_sink`` receives
-    every emitted frame block [3, F, H, W].  Returns the manifest (also written to ``out_dir``)."""
+    every emitted frame block [3, F, H, W].  ``decode_latents`` stops decoding after that many generated latents (a
+    rollout is whole chunks, the clip may end inside the last one) and ``max_frames`` caps the frames handed to the
+    sink; ``progress(chunk, chunks)`` is called after every chunk; ``keep_latents`` returns the generated latents on
+    the host under ``"latents"`` (not written to the manifest file).  Returns the manifest (also written to
+    ``out_dir``)."""
     cfg = stream_cfg
     k = cfg.chunk_latents
     n_lat = c2w.shape[0] - 1
@@ -53,7 +59,7 @@ def generate_full_length(model, *, text: torch.Tensor, anchor_latent: torch.Tens
     dev = gen.device
     if dev.type == "cuda":
         torch.cuda.reset_peak_memory_stats(dev)
-    chunk_s, decode_s, frames_out, retrieved = [], 0.0, 0, []
+    chunk_s, decode_s, frames_out, retrieved, decoded, kept = [], 0.0, 0, [], 0, []
     for ci in range(n_chunks):
         t0 = time.perf_counter()
         sl = slice(1 + ci * k, 1 + (ci + 1) * k)
@@ -75,14 +81,24 @@ def generate_full_length(model, *, text: torch.Tensor, anchor_latent: torch.Tens
         if decoder is not None:
             t1 = time.perf_counter()
             for li in range(k):
+                if decode_latents is not None and decoded >= decode_latents:
+                    break
                 frames = decoder.push(chunk[:, li].float() if dev.type == "cpu" else chunk[:, li])
+                decoded += 1
                 if frames is not None:
-                    frames_out += frames.shape[1]
-                    if frame_sink is not None:
-                        frame_sink(frames)
+                    if max_frames is not None:
+                        frames = frames[:, :max(0, max_frames - frames_out)]
+                    if frames.shape[1]:
+                        frames_out += frames.shape[1]
+                        if frame_sink is not None:
+                            frame_sink(frames)
             if dev.type == "cuda":
                 torch.cuda.synchronize(dev)
             decode_s += time.perf_counter() - t1
+        if keep_latents:
+            kept.append(chunk.detach().to("cpu"))
+        if progress is not None:
+            progress(ci + 1, n_chunks)
     total = sum(chunk_s) + decode_s
     manifest = {"schema": "solarwm.h3-full-inference.v1", "chunks": n_chunks, "latents": n_chunks * k,
                 "chunk_seconds": [round(s, 4) for s in chunk_s], "generation_seconds": round(sum(chunk_s), 4),
@@ -93,4 +109,6 @@ def generate_full_length(model, *, text: torch.Tensor, anchor_latent: torch.Tens
     if out_dir is not None:
         Path(out_dir).mkdir(parents=True, exist_ok=True)
         (Path(out_dir) / "manifest.json").write_text(json.dumps(manifest, sort_keys=True, indent=1))
+    if keep_latents:
+        manifest = dict(manifest, latents_tensor=torch.cat(kept, dim=1))
     return manifest
