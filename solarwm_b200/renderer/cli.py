@@ -1,6 +1,8 @@
 """``solar-renderer``: train / distill / render on the configured (or synthetic) data.
 
-    python -m solarwm_b200.renderer.cli train   --steps N [--arch tiny] [--patterns shared=1,known_frames=1]
+    python -m solarwm_b200.renderer.cli train   --config FILE [--set KEY=VALUE ...] [--resolve]     (corpus-driven)
+    python -m solarwm_b200.renderer.cli export  --checkpoint DIR --out FILE [--weight-source live|ema]
+    python -m solarwm_b200.renderer.cli train   --steps N [--arch tiny] [--patterns shared=1,known_frames=1]     (synthetic)
     python -m solarwm_b200.renderer.cli distill --steps N
     python -m solarwm_b200.renderer.cli render  --out DIR [--steps 8]
 
@@ -28,9 +30,38 @@ def _sample(cfg, seed, frames=4, size=8):
     return s
 
 
+def _train_from_config(args) -> int:
+    import os
+
+    from ..config.loader import load_config
+    from ..runtime.provenance import reject_inline_secrets
+    from .runtime import run_control_training, validate_config
+
+    resolved = load_config(args.config, args.set, route_validator=validate_config)
+    reject_inline_secrets(resolved.values)
+    config = resolved.mutable_copy()
+    config["runtime"]["output_dir"] = str(Path(config["runtime"]["output_dir"]).expanduser().resolve())
+    if args.resolve:
+        print(json.dumps(config, indent=2, sort_keys=True))
+        return 0
+    out = Path(config["runtime"]["output_dir"])
+    if int(os.environ.get("RANK", "0")) == 0:
+        out.mkdir(parents=True, exist_ok=True)
+        (out / "runtime-config.json").write_text(json.dumps(config, indent=2, sort_keys=True) + "\n")
+    if config["train"].get("objective", "flow_matching") == "dmd":
+        raise SystemExit("renderer distillation runs through the 'distill' command")
+    print(json.dumps(run_control_training(config), sort_keys=True, default=str))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="solar-renderer")
-    ap.add_argument("command", choices=["train", "distill", "render"])
+    ap.add_argument("command", choices=["train", "distill", "render", "export"])
+    ap.add_argument("--config", default=None, help="a renderer training config (YAML); trains on its omni corpus")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE")
+    ap.add_argument("--resolve", action="store_true", help="validate and print the configuration")
+    ap.add_argument("--checkpoint", default=None)
+    ap.add_argument("--weight-source", default="live")
     ap.add_argument("--arch", default="tiny")
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--lora-rank", type=int, default=4)
@@ -38,6 +69,13 @@ def main(argv=None) -> int:
     ap.add_argument("--out", default=None)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     args = ap.parse_args(argv)
+    if args.command == "export":
+        from .runtime import export_adapter
+
+        print(json.dumps(export_adapter(args.checkpoint, args.out, weight_source=args.weight_source), sort_keys=True))
+        return 0
+    if args.command == "train" and args.config:
+        return _train_from_config(args)
     cfg = h3_preset(args.arch)
     cfg.lora_rank = args.lora_rank
     if args.command == "train":

@@ -75,17 +75,18 @@ def packed_forward(model: H3DiT, *, prompt, anchor_rows, structure_rows, target_
 
 class OmniFlowTrainer:
     def __init__(self, cfg, device, profile: ObservationProfile = ObservationProfile(), lr: float = 1e-4, seed: int = 0,
-                 model: Optional[H3DiT] = None):
+                 model: Optional[H3DiT] = None, optimizer: Optional[FP32MasterAdamW] = None):
         dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
         self.device = torch.device(device)
         self.model = model or H3DiT(cfg, device=device, dtype=dtype, seed=seed)
-        self.opt = FP32MasterAdamW(self.model.trainable_parameters(), lr=lr)
+        self.opt = optimizer or FP32MasterAdamW(self.model.trainable_parameters(), lr=lr)
         self.profile = profile
         self.rng = np.random.default_rng(seed)
         self.gen = torch.Generator(device=self.device).manual_seed(seed * 100003 + 29)
         self.last_plan: Optional[ObservationPlan] = None
 
-    def train_step(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
+    def compute_loss(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        """The plan-weighted flow-matching loss of one sample, with its graph (the caller runs backward)."""
         dev, dt = self.device, self.model.dtype
         lat = sample["target_latents"].to(dev)
         C, F, H, W = lat.shape
@@ -107,7 +108,10 @@ class OmniFlowTrainer:
                               cameras=sample.get("camera_w2c") if plan.use_camera else None)
         keep = torch.from_numpy(plan.loss_rows).to(dev)
         err = (pred.float() - (x0_rows - n_rows)).pow(2).mean(dim=1)
-        loss = (err * keep).sum() / keep.sum().clamp_min(1)
+        return (err * keep).sum() / keep.sum().clamp_min(1)
+
+    def train_step(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        loss = self.compute_loss(sample)
         loss.backward()
         self.opt.gather_grads()
         self.opt.clip_(1.0)
