@@ -1,6 +1,8 @@
 """``solar-renderer``: train / distill / render on the configured (or synthetic) data.
 
     python -m solarwm_b200.renderer.cli train   --config FILE [--set KEY=VALUE ...] [--resolve]     (corpus-driven)
+    python -m solarwm_b200.renderer.cli preencode --input rows.jsonl --out DIR --media-root DIR --codecs pkg.mod:factory
+                                                  [--shard I --shards N] | --out DIR --merge
     python -m solarwm_b200.renderer.cli export  --checkpoint DIR --out FILE [--weight-source live|ema]
     python -m solarwm_b200.renderer.cli train   --steps N [--arch tiny] [--patterns shared=1,known_frames=1]     (synthetic)
     python -m solarwm_b200.renderer.cli distill --steps N
@@ -56,7 +58,14 @@ def _train_from_config(args) -> int:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="solar-renderer")
-    ap.add_argument("command", choices=["train", "distill", "render", "export"])
+    ap.add_argument("command", choices=["train", "distill", "render", "export", "preencode"])
+    ap.add_argument("--input", default=None, help="preencode: JSON lines of media rows")
+    ap.add_argument("--media-root", default=".")
+    ap.add_argument("--codecs", default=None, help="preencode: 'package.module:factory' returning renderer.preencode.Codecs "
+                                                   "(the released H3 front end is external to this package)")
+    ap.add_argument("--shard", type=int, default=0)
+    ap.add_argument("--shards", type=int, default=1)
+    ap.add_argument("--merge", action="store_true", help="preencode: only merge the shard indexes into index.jsonl")
     ap.add_argument("--config", default=None, help="a renderer training config (YAML); trains on its omni corpus")
     ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE")
     ap.add_argument("--resolve", action="store_true", help="validate and print the configuration")
@@ -76,6 +85,22 @@ def main(argv=None) -> int:
         return 0
     if args.command == "train" and args.config:
         return _train_from_config(args)
+    if args.command == "preencode":
+        import importlib
+
+        from .preencode import merge_indexes, run_shard
+
+        if args.merge:
+            print(json.dumps({"samples": merge_indexes(args.out)}))
+            return 0
+        if not (args.input and args.out and args.codecs and ":" in args.codecs):
+            raise SystemExit("preencode needs --input, --out and --codecs package.module:factory")
+        module, _, factory = args.codecs.partition(":")
+        codecs = getattr(importlib.import_module(module), factory)()
+        rows = [json.loads(line) for line in Path(args.input).read_text().splitlines() if line.strip()]
+        report = run_shard(rows, out=args.out, media_root=args.media_root, codecs=codecs, shard=args.shard, shards=args.shards)
+        print(json.dumps(report, sort_keys=True))
+        return 0 if not report["pending"] else 4
     cfg = h3_preset(args.arch)
     cfg.lora_rank = args.lora_rank
     if args.command == "train":
