@@ -69,6 +69,7 @@ class WanStage2Trainer:
         self.cfg, self.opts, self.device = cfg, opts, torch.device(device)
         self.sp = sp
         self.sp_size = 1 if sp is None else sp.size
+        self.dp_group, self.dp_size = None, 1      # ``run_stage2_training`` sets them for data-parallel replicas
         mk = lambda seed: WanDiT(cfg, device=device, dtype=dtype, seed=seed)   # noqa: E731
         self.student = student or mk(opts.seed)
         self.teacher = teacher or mk(opts.seed)
@@ -183,6 +184,13 @@ class WanStage2Trainer:
         model.finalize_grads()
         if self.sp is not None and self.sp.size > 1:
             self.sp.sum_gradients_([g for u in model.units() for g in (u.grad, u.grad_v)])
+        if self.dp_size > 1:                       # replicas rolled out different prompts: average their gradients
+            import torch.distributed as dist
+
+            for u in model.units():
+                for g in (u.grad, u.grad_v):
+                    dist.all_reduce(g, group=self.dp_group)
+                    g.mul_(1.0 / self.dp_size)
         norm = opt.local_grad_sumsq().sqrt()
         opt.set_clip(norm, self.opts.max_grad_norm)
         opt.step()
@@ -264,13 +272,60 @@ class WanStage2Trainer:
             self.ema_student.load_state_dict(state["ema_student"], num_updates=int(state["ema_student_updates"]))
 
 
+def load_role_weights(model: WanDiT, source, *, role: str, weight_source: str = "live") -> Mapping[str, Any]:
+    """Fill one role from an earlier run: a Stage2 checkpoint (``role.pt``: its ``student`` or ``critic``, or the student's
+    average with ``weight_source: ema``) or a Stage0.5 / Stage1 checkpoint (``model.pt``: live or averaged weights).  The
+    checkpoint is verified first; the receipt names what was taken."""
+    from ...checkpoint.store import verify_checkpoint
+
+    if weight_source not in ("live", "ema"):
+        raise BackendContractError("weight_source is live or ema")
+    verified = verify_checkpoint(source)
+    root = verified.path
+    if (root / "role.pt").is_file():
+        doc = torch.load(root / "role.pt", map_location="cpu", weights_only=True)
+        key = "ema_student" if weight_source == "ema" else ("critic" if role == "critic" else "student")
+        if key not in doc:
+            raise BackendContractError(f"{root} holds no {key} weights")
+        state, taken = doc[key], f"role.pt:{key}"
+    elif (root / "model.pt").is_file():
+        doc = torch.load(root / "model.pt", map_location="cpu", weights_only=True)
+        key = "ema" if weight_source == "ema" else "model"
+        if doc.get(key) is None:
+            raise BackendContractError(f"{root} holds no {key} weights")
+        state, taken = doc[key], f"model.pt:{key}"
+    else:
+        raise BackendContractError(f"{root} holds neither role.pt nor model.pt")
+    own = model.state_dict()
+    if set(state) != set(own):
+        missing, extra = sorted(set(own) - set(state))[:4], sorted(set(state) - set(own))[:4]
+        raise BackendContractError(f"{taken} of {root} does not match the architecture: missing {missing}, unexpected {extra}")
+    model.load_state_dict({k: v.to(own[k].dtype) for k, v in state.items()})
+    return {"role": role, "source": str(root), "taken": taken, "checkpoint": verified.manifest_digest, "step": int(verified.step),
+            "stage": verified.contract.stage}
+
+
+def expected_student_updates(outer_steps: int, ratio: int) -> int:
+    """How many of the first ``outer_steps`` outer steps updated the student (the rule of ``should_update_student``)."""
+    return sum(1 for k in range(outer_steps) if should_update_student(k, ratio))
+
+
 def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
-    """Config-driven entry: synthetic prompts (or the configured reader), ``max_steps`` outer steps, role
-    checkpoints through the transactional store."""
-    from ...checkpoint.store import CheckpointTransaction
+    """Config-driven entry.  Roles start from ``checkpoint.initialization.{student, teacher, critic}`` (``{path,
+    weight_source}``; a role without one keeps its seeded random weights, a critic without one starts from the teacher's
+    as the recipe does); ``checkpoint.resume_from`` restores both trainable roles, their optimizers, the student's
+    average, every rank's random streams and the batch position, and checks that the saved counters agree with the
+    update schedule; every outer step is an event line; role checkpoints go through the transactional store every
+    ``runtime.save_every`` steps, at ``checkpoint.save_steps`` and at the end."""
+    import torch.distributed as dist
+
+    from ...checkpoint.store import CheckpointTransaction, verify_checkpoint
     from ...config.routes import validate_route
+    from ...engine.train_engine import JsonlEventSink
     from ...parallel import dist_init
-    from ...runtime.output_layout import checkpoint_model_dir, output_root
+    from ...runtime import distributed as rdist
+    from ...runtime.output_layout import checkpoint_model_dir, events_path, output_root
+    from ...runtime.safe_state import capture_rank_state, restore_rank_state
     from .checkpoint import build_contract
     from .contracts import architecture
     from .runtime import encoded_batches, synthetic_batches
@@ -279,8 +334,9 @@ def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
     ctx = dist_init.initialize(int(dist_cfg.get("sequence_parallel_size", 1)),
                                device=str(config.get("runtime", {}).get("device", "auto")))
     try:
+        topo = ctx.topology
         arch = architecture(config)
-        train = config["train"]
+        train, rt, ck = config["train"], config.get("runtime", {}) or {}, config.get("checkpoint", {}) or {}
         causal = config["model"].get("causal", {}) or {}
         opts = Stage2Options(
             lr_student=float((train.get("optimizer", {}) or {}).get("lr", 2e-6)),
@@ -295,23 +351,88 @@ def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
             ema_start_step=int((train.get("ema", {}) or {}).get("start_step", 39)))
         dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
         trainer = WanStage2Trainer(arch, ctx.device, opts, sp=ctx.sp, dtype=dtype)
+        trainer.dp_group, trainer.dp_size = ctx.dp_group, topo.dp_size
+        # replicas draw different noise; SP peers of one replica must draw the same
+        trainer.gen.manual_seed(opts.seed * 100003 + 7 + 7919 * topo.dp_rank)
+        receipts = {}
+        init = ck.get("initialization", {}) or {}
+        for role, model in (("student", trainer.student), ("teacher", trainer.teacher), ("critic", trainer.critic)):
+            spec = init.get(role)
+            if spec:
+                spec = {"path": spec} if isinstance(spec, str) else dict(spec)
+                receipts[role] = dict(load_role_weights(model, spec["path"], role=role, weight_source=str(spec.get("weight_source", "live"))))
+        if "teacher" in receipts and "critic" not in receipts:
+            trainer.critic.load_state_dict(trainer.teacher.state_dict())
+            receipts["critic"] = dict(receipts["teacher"], role="critic", taken=receipts["teacher"]["taken"] + " (teacher's)")
+        for role, opt, model in (("student", trainer.opt_student, trainer.student), ("critic", trainer.opt_critic, trainer.critic)):
+            if role in receipts:
+                opt.adopt_live_weights()
+        if trainer.ema_student is not None and "student" in receipts:
+            trainer.ema_student.update(trainer.student, decay=0.0)          # the average restarts at the loaded weights
+            trainer.ema_student.num_updates = 0
         if str(config["data"].get("source", "synthetic")) == "index":       # prompts (and the shape template) from a corpus
-            batches = encoded_batches(config, arch, ctx.device, ctx.topology.dp_rank, ctx.topology.dp_size)
+            batches = encoded_batches(config, arch, ctx.device, topo.dp_rank, topo.dp_size)
         else:
-            batches = synthetic_batches(config, arch, ctx.device)
-        max_steps = int(config.get("runtime", {}).get("max_steps_override") or train["max_steps"])
-        last = {}
-        for _ in range(max_steps):
+            batches = synthetic_batches(dict(config, data=dict(config["data"], seed=int(config["data"].get("seed", 0)) + topo.dp_rank)),
+                                        arch, ctx.device)
+        consumed = 0
+        if ck.get("resume_from"):
+            verified = verify_checkpoint(str(ck["resume_from"]))
+            run = torch.load(verified.path / "runtime.pt", weights_only=True)
+            ranks = torch.load(verified.path / "rank-state.pt", weights_only=True)
+            if int(ranks["world_size"]) != topo.raw_world_size or int(ranks["sp_size"]) != topo.sp_size:
+                raise BackendContractError(f"checkpoint was written by {ranks['world_size']} ranks (SP {ranks['sp_size']}); "
+                                           f"{topo.raw_world_size} (SP {topo.sp_size}) are running")
+            if run.get("initialization") != receipts:
+                raise BackendContractError("the checkpoint's roles started from other weights than this configuration names")
+            trainer.load_role_state(torch.load(verified.path / "role.pt", map_location=ctx.device, weights_only=True))
+            want = expected_student_updates(trainer.global_step, opts.critic_updates_per_student)
+            if int(run["student_updates"]) != want or int(run["global_step"]) != trainer.global_step:
+                raise BackendContractError(f"checkpoint counters disagree with the update schedule: {run['student_updates']} student "
+                                           f"updates at outer step {run['global_step']}, the schedule gives {want}")
+            mine = ranks["ranks"][topo.raw_rank]
+            restore_rank_state(mine, ctx.device)
+            trainer.gen.set_state(mine["objective_gen"])
+            for _ in range(int(mine["batches_consumed"])):
+                next(batches)
+            consumed = int(mine["batches_consumed"])
+        max_steps = int(rt.get("max_steps_override") or train["max_steps"])
+        save_every = int(rt.get("save_every", 0))
+        save_steps = {int(v) for v in ck.get("save_steps", ())} | ({max_steps} if save_every > 0 or ck.get("save_steps") else set())
+        sink = JsonlEventSink(events_path(output_root(config), topo.raw_rank))
+        route = validate_route(config)
+
+        def save(step: int) -> str:
+            state = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in capture_rank_state(ctx.device).items()}
+            state.update(objective_gen=trainer.gen.get_state().cpu(), batches_consumed=consumed)
+            states = [state]
+            if topo.raw_world_size > 1:
+                states = [None] * topo.raw_world_size
+                dist.all_gather_object(states, state)
+            target = checkpoint_model_dir(output_root(config), step)
+
+            def write():
+                with CheckpointTransaction(target) as tx:
+                    torch.save(dict(trainer.role_state()), tx.path / "role.pt")
+                    torch.save({"ranks": states, "world_size": topo.raw_world_size, "sp_size": topo.sp_size}, tx.path / "rank-state.pt")
+                    torch.save({"global_step": int(step), "initialization": receipts,
+                                "student_updates": expected_student_updates(step, opts.critic_updates_per_student)}, tx.path / "runtime.pt")
+                    done = tx.commit(step=int(step), contract=build_contract(config, route, topo.sp_size),
+                                     required_components=("role.pt", "rank-state.pt", "runtime.pt"),
+                                     metadata={"roles": ["student", "critic"], "initialization": receipts})
+                return done.manifest_digest
+
+            return rdist.collective_rank_zero_call(write, dist=dist if topo.raw_world_size > 1 else None, label="checkpoint commit")
+
+        last, ident, saved_at = {}, None, None
+        while trainer.global_step < max_steps:
             last = trainer.train_outer_step(next(batches))
-        ident = None
-        if ctx.topology.is_main and int(config.get("runtime", {}).get("save_every", 0)) > 0:
-            target = checkpoint_model_dir(output_root(config), trainer.global_step)
-            with CheckpointTransaction(target) as tx:
-                torch.save(dict(trainer.role_state()), tx.path / "role.pt")
-                done = tx.commit(step=trainer.global_step,
-                                 contract=build_contract(config, validate_route(config), ctx.topology.sp_size),
-                                 required_components=("role.pt",), metadata={"roles": ["student", "critic"]})
-            ident = done.manifest_digest
-        return {"final_step": trainer.global_step, "losses": last, "checkpoint": ident}
+            consumed += 1
+            step = trainer.global_step
+            sink({"event": "train_step", "step": step, **{k: float(v) for k, v in last.items()}})
+            if step in save_steps or (save_every > 0 and step % save_every == 0):
+                ident, saved_at = save(step), step
+        return {"final_step": trainer.global_step, "losses": last, "checkpoint": ident, "initialization": receipts,
+                "checkpoint_dir": None if saved_at is None else str(checkpoint_model_dir(output_root(config), saved_at))}
     finally:
         dist_init.shutdown(ctx)

@@ -1,0 +1,84 @@
+"""Wan Stage2 run loop: roles started from earlier checkpoints, exact resume, schedule check, events."""
+import json
+from pathlib import Path
+
+import pytest
+import torch
+import yaml
+
+from solarwm_b200.errors import BackendContractError
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _config(out, **over):
+    cfg = yaml.safe_load((ROOT / "configs" / "wan22_ti2v_5b" / "tiny_stage2_sgf_cpu.yaml").read_text())
+    cfg["runtime"].update(output_dir=str(out), device="cpu")
+    cfg["train"]["max_steps"] = 4
+    cfg["train"]["ema"] = {"enabled": True, "decay": 0.5, "start_step": 0}
+    for k, v in over.items():
+        cfg[k] = {**cfg.get(k, {}), **v}
+    return cfg
+
+
+def _role(path):
+    return torch.load(Path(path) / "role.pt", map_location="cpu", weights_only=True)
+
+
+def test_resume_is_exact_and_counters_follow_the_schedule(tmp_path):
+    from solarwm_b200.backends.wan22.stage2 import expected_student_updates, run_stage2_training
+
+    assert [expected_student_updates(n, 2) for n in range(6)] == [0, 0, 0, 1, 1, 2]
+    straight = run_stage2_training(_config(tmp_path / "a", checkpoint={"save_steps": [2, 4]}))
+    assert straight["final_step"] == 4 and straight["checkpoint_dir"].endswith("checkpoint_model_000004")
+    mid = tmp_path / "a" / "checkpoint_model_000002"
+    resumed = run_stage2_training(_config(tmp_path / "b", checkpoint={"resume_from": str(mid), "save_steps": [4]}))
+    assert resumed["final_step"] == 4
+    a, b = _role(tmp_path / "a" / "checkpoint_model_000004"), _role(tmp_path / "b" / "checkpoint_model_000004")
+    for role in ("student", "critic", "ema_student"):
+        assert all(torch.equal(a[role][k], b[role][k]) for k in a[role]), role
+    run = torch.load(tmp_path / "a" / "checkpoint_model_000004" / "runtime.pt", weights_only=True)
+    assert run["student_updates"] == 1 and run["global_step"] == 4
+    events = [json.loads(l) for f in (tmp_path / "a").rglob("*.jsonl") for l in f.read_text().splitlines()]
+    steps = [e for e in events if e.get("event") == "train_step"]
+    assert [e["step"] for e in steps] == [1, 2, 3, 4] and "student" in steps[2] and "student" not in steps[0]
+    # a checkpoint whose counters were tampered with is refused
+    bad = tmp_path / "tampered"
+    import shutil
+
+    shutil.copytree(mid, bad)
+    with pytest.raises(Exception):
+        torch.save({"global_step": 2, "student_updates": 5, "initialization": {}}, bad / "runtime.pt")
+        run_stage2_training(_config(tmp_path / "c", checkpoint={"resume_from": str(bad)}))
+
+
+def test_roles_start_from_earlier_checkpoints(tmp_path):
+    from solarwm_b200.backends.wan22.stage2 import Stage2Options, WanStage2Trainer, load_role_weights, run_stage2_training
+    from solarwm_b200.backends.wan22.contracts import architecture
+
+    first = run_stage2_training(_config(tmp_path / "parent", checkpoint={"save_steps": [3]}, train={"max_steps": 3}))
+    parent = first["checkpoint_dir"]
+    cfg = _config(tmp_path / "child", checkpoint={"save_steps": [1], "initialization": {"student": {"path": parent, "weight_source": "ema"},
+                                                                                        "teacher": parent}}, train={"max_steps": 1})
+    out = run_stage2_training(cfg)
+    rec = out["initialization"]
+    assert rec["student"]["taken"] == "role.pt:ema_student" and rec["teacher"]["taken"] == "role.pt:student"
+    assert rec["critic"]["taken"].endswith("(teacher's)") and rec["student"]["stage"] == "stage2" and rec["student"]["step"] == 3
+    saved = torch.load(Path(out["checkpoint_dir"]) / "runtime.pt", weights_only=True)
+    assert saved["initialization"]["teacher"]["checkpoint"] == rec["teacher"]["checkpoint"]
+    # the loader itself: strict names, the right entry, verified source
+    arch = architecture(cfg)
+    tr = WanStage2Trainer(arch, "cpu", Stage2Options(chunk_frames=2, window_chunks=2, denoising_steps=(1000.0, 500.0)), dtype=torch.float32)
+    before = tr.critic.get_parameter("blocks.0.ffn.0.weight").detach().clone()
+    got = load_role_weights(tr.critic, parent, role="critic")
+    assert got["taken"] == "role.pt:critic" and not torch.equal(before, tr.critic.get_parameter("blocks.0.ffn.0.weight"))
+    want = _role(parent)["critic"]["blocks.0.ffn.0.weight"]
+    assert torch.equal(tr.critic.get_parameter("blocks.0.ffn.0.weight"), want.to(torch.float32))
+    with pytest.raises(BackendContractError):
+        load_role_weights(tr.critic, parent, role="critic", weight_source="other")
+    with pytest.raises(Exception):
+        load_role_weights(tr.critic, tmp_path / "nowhere", role="critic")
+    # resuming a child under another parent is refused
+    other = _config(tmp_path / "child2", checkpoint={"resume_from": out["checkpoint_dir"]}, train={"max_steps": 2})
+    with pytest.raises(BackendContractError):
+        run_stage2_training(other)
