@@ -114,6 +114,165 @@ class SolarRendererPrompt:
         return (f"{lead} {text}",)
 
 
+def snap_frames(available: int, wanted: int) -> int:
+    """The longest ``17 n + 5`` frames within both the request and the structure video (at least 22)."""
+    frames = min(int(wanted), int(available))
+    if frames < 22:
+        raise ValueError(f"the renderer needs at least 22 frames of structure video, got {frames}")
+    return 17 * ((frames - 5) // 17) + 5
+
+
+def fit_images(images: torch.Tensor, width: int, height: int) -> torch.Tensor:
+    """Host images ``[T, H, W, 3]`` in [0, 1] -> cover-resized and centre-cropped to ``height x width``."""
+    import torch.nn.functional as F
+
+    T, h, w, _ = images.shape
+    scale = max(height / h, width / w)
+    nh, nw = max(height, round(h * scale)), max(width, round(w * scale))
+    x = F.interpolate(images.permute(0, 3, 1, 2).float(), size=(nh, nw), mode="bilinear", align_corners=False, antialias=scale < 1)
+    top, left = (nh - height) // 2, (nw - width) // 2
+    return x[:, :, top:top + height, left:left + width].permute(0, 2, 3, 1).clamp(0, 1)
+
+
+class SolarRendererConditioning:
+    """Structure video + prompt (+ the look's first frame) -> what the sampler consumes.  ``TEXT_ENCODER`` is a callable
+    ``prompt -> [L, D]``; ``VAE`` an object whose ``encode(images [T, H, W, 3] in [0, 1])`` returns latents
+    ``[C, F, h, w]`` (both are the host's own loaders; the renderer does not bundle the official codecs)."""
+
+    @classmethod
+    def INPUT_TYPES(cls):
+        return {"required": {"text_encoder": ("TEXT_ENCODER",), "vae": ("VAE",),
+                             "structure": ("IMAGE", {"tooltip": "the structure video at 24 fps; the render follows it frame for frame"}),
+                             "prompt": ("STRING", {"multiline": True}),
+                             "width": ("INT", {"default": 1344, "min": 64, "max": 2048, "step": 32}),
+                             "height": ("INT", {"default": 768, "min": 64, "max": 2048, "step": 32}),
+                             "length": ("INT", {"default": 158, "min": 22, "max": 3609,
+                                                "tooltip": "frames to render, snapped down to 17 n + 5 and to the structure video"})},
+                "optional": {"first_frame": ("IMAGE", {"tooltip": "the look of the shot: its first frame, already in that look"}),
+                             "structure_vae": ("VAE", {"tooltip": "a faster codec for the structure video; the first frame keeps vae"})}}
+
+    RETURN_TYPES = ("CONDITIONING", "LATENT")
+    RETURN_NAMES = ("positive", "latent")
+    FUNCTION = "encode"
+    CATEGORY = CATEGORY
+
+    def encode(self, text_encoder, vae, structure, prompt, width=1344, height=768, length=158, first_frame=None, structure_vae=None):
+        frames = snap_frames(structure.shape[0], length)
+        video = fit_images(structure[:frames], int(width), int(height))
+        structure_latents = (structure_vae or vae).encode(video)
+        if structure_latents.ndim != 4 or structure_latents.shape[1] != 5 * ((frames - 5) // 17) + 2:
+            raise ValueError(f"the codec returned {tuple(structure_latents.shape)} for {frames} frames")
+        C, F, H, W = structure_latents.shape
+        if first_frame is not None:
+            anchor = vae.encode(fit_images(first_frame[:1], int(width), int(height)))[:, :1]
+            if tuple(anchor.shape) != (C, 1, H, W):
+                raise ValueError("the first frame's latent does not sit on the structure video's grid")
+        else:
+            anchor = torch.zeros(C, 1, H, W, dtype=structure_latents.dtype, device=structure_latents.device)
+        text = text_encoder(str(prompt))
+        if text.ndim != 2:
+            raise ValueError("the text encoder returns [tokens, width]")
+        cond = {"prompt_embeds": text, "anchor_latents": anchor, "structure_latents": structure_latents, "shape": (C, F, H, W),
+                "pixel_frames": frames, "has_first_frame": first_frame is not None}
+        return (cond, {"samples": torch.zeros(1, C, F, H, W)})
+
+
+class SolarRendererLoraLoader:
+    """Fill the model's adapters from an exported adapter file (``renderer.runtime.export_adapter``) and re-prepare it."""
+
+    @classmethod
+    def INPUT_TYPES(cls):
+        return {"required": {"model": ("MODEL",), "adapter_path": ("STRING", {"default": ""}),
+                             "strength": ("FLOAT", {"default": 1.0, "min": 0.0, "max": 2.0, "step": 0.05})}}
+
+    RETURN_TYPES = ("MODEL",)
+    FUNCTION = "load"
+    CATEGORY = CATEGORY
+
+    def load(self, model, adapter_path, strength=1.0):
+        from .runtime import read_adapter
+
+        state = read_adapter(adapter_path)
+        own = {n: p for n, p in model.model.named_parameters() if "lora_" in n}
+        if set(own) != set(state):
+            raise ValueError("the adapter file does not fit this model's adapters")
+        with torch.no_grad():
+            for n, p in own.items():
+                # the product B A scales linearly in either factor: the strength goes on the up-projection
+                p.copy_((state[n] * (float(strength) if "lora_B" in n else 1.0)).to(p))
+        model.prepare()
+        return (model,)
+
+
+def capture_plan(script: str) -> list:
+    """A key / mouse script as time-ordered ``(seconds, action, argument)`` events.  Items are separated by commas or new
+    lines: ``t:Key[:hold]`` (a key press), ``t:down:Key`` / ``t:up:Key``, ``t:mouse:dx:dy[:over]`` (a move spread over
+    ``over`` seconds in 1/30 s steps), ``t:click[:hold]``."""
+    plan = []
+    for item in (x.strip() for x in script.replace("\n", ",").split(",")):
+        if not item:
+            continue
+        parts = item.split(":")
+        if len(parts) < 2:
+            raise ValueError(f"capture script item {item!r} is not seconds:action")
+        t, kind = float(parts[0]), parts[1]
+        if t < 0:
+            raise ValueError("capture script times are non-negative")
+        if kind in ("down", "up"):
+            plan.append((t, kind, parts[2]))
+        elif kind == "mouse":
+            dx, dy = float(parts[2]), float(parts[3])
+            over = float(parts[4]) if len(parts) > 4 else 0.4
+            steps = max(1, int(over * 30))
+            plan += [(t + over * i / steps, "move", (dx / steps, dy / steps)) for i in range(steps)]
+        elif kind == "click":
+            hold = float(parts[2]) if len(parts) > 2 else 0.15
+            plan += [(t, "mdown", None), (t + hold, "mup", None)]
+        else:
+            hold = float(parts[2]) if len(parts) > 2 else 0.12
+            plan += [(t, "down", kind), (t + hold, "up", kind)]
+    return sorted(plan, key=lambda e: e[0])
+
+
+class SolarRendererWebCapture:
+    """A recorded web page (a game, a 3-D scene) as a structure video.  The recording itself is done by a separate
+    process -- ``command`` with ``{url} {out} {frames} {script}`` filled in -- so a browser that hangs never takes the
+    host with it; that process needs a headless browser with a GPU canvas, which this package does not bundle.  The node
+    checks the script, runs the command when one is given, and loads ``<out>.npy`` (RGB8 ``[T, H, W, 3]``)."""
+
+    @classmethod
+    def INPUT_TYPES(cls):
+        return {"required": {"url": ("STRING", {"default": ""}), "frames": ("INT", {"default": 158, "min": 22, "max": 3609}),
+                             "out": ("STRING", {"default": "capture"})},
+                "optional": {"script": ("STRING", {"multiline": True, "default": ""}), "command": ("STRING", {"default": ""}),
+                             "timeout_seconds": ("INT", {"default": 600, "min": 10, "max": 7200})}}
+
+    RETURN_TYPES = ("IMAGE",)
+    FUNCTION = "capture"
+    CATEGORY = CATEGORY
+
+    def capture(self, url, frames=158, out="capture", script="", command="", timeout_seconds=600):
+        import shlex
+        import subprocess
+        from pathlib import Path
+
+        import numpy as np
+
+        capture_plan(script)                                            # refuse a malformed script before anything runs
+        target = Path(f"{out}.npy")
+        if command:
+            argv = [a.format(url=url, out=out, frames=int(frames), script=script) for a in shlex.split(command)]
+            done = subprocess.run(argv, capture_output=True, text=True, timeout=int(timeout_seconds))
+            if done.returncode != 0:
+                raise RuntimeError(f"the capture process failed ({done.returncode}): {done.stderr[-400:]}")
+        if not target.is_file():
+            raise FileNotFoundError(f"{target} was not recorded")
+        data = np.load(target, allow_pickle=False)
+        if data.ndim != 4 or data.shape[-1] != 3 or data.dtype != np.uint8 or len(data) < 22:
+            raise ValueError("a capture is RGB8 [T >= 22, H, W, 3]")
+        return (torch.from_numpy(data[:int(frames)].astype(np.float32) / 255.0),)
+
+
 class SolarRendererSampler:
     @classmethod
     def INPUT_TYPES(cls):
@@ -137,6 +296,9 @@ NODE_CLASS_MAPPINGS = {
     "SolarRendererSigmas": SolarRendererSigmas,
     "SolarRendererAttention": SolarRendererAttention,
     "SolarRendererPrompt": SolarRendererPrompt,
+    "SolarRendererConditioning": SolarRendererConditioning,
+    "SolarRendererLoraLoader": SolarRendererLoraLoader,
+    "SolarRendererWebCapture": SolarRendererWebCapture,
     "SolarRendererSampler": SolarRendererSampler,
 }
 NODE_DISPLAY_NAME_MAPPINGS = {
@@ -144,5 +306,8 @@ NODE_DISPLAY_NAME_MAPPINGS = {
     "SolarRendererSigmas": "SolarRenderer sigmas",
     "SolarRendererAttention": "SolarRenderer attention backend",
     "SolarRendererPrompt": "SolarRenderer prompt",
+    "SolarRendererConditioning": "SolarRenderer conditioning",
+    "SolarRendererLoraLoader": "SolarRenderer LoRA loader",
+    "SolarRendererWebCapture": "SolarRenderer web capture",
     "SolarRendererSampler": "SolarRenderer sampler",
 }

@@ -150,3 +150,86 @@ def test_node_graph_front_end_follows_the_node_protocol_and_renders():
             cn.SolarRendererSampler().sample(svc, s, seed=1, sigmas=sig[:2])
     finally:
         ops.set_backend(before)
+
+
+def test_conditioning_lora_and_capture_nodes(tmp_path):
+    import numpy as np
+
+    from solarwm_b200.models.h3 import h3_preset
+    from solarwm_b200.renderer import comfy_nodes as cn
+
+    assert [cn.snap_frames(200, n) for n in (22, 38, 39, 158, 500)] == [22, 22, 39, 158, 192]
+    with pytest.raises(ValueError):
+        cn.snap_frames(21, 158)
+    wide = torch.zeros(2, 20, 60, 3)
+    wide[:, :, 25:35] = 1.0
+    fitted = cn.fit_images(wide, 16, 16)
+    assert fitted.shape == (2, 16, 16, 3) and float(fitted[0, 8, 8, 0]) > 0.9 and float(fitted[0, 8, 0, 0]) < 0.1
+
+    class Codec:                                                     # the host's VAE protocol, at the codec's cadence
+        def encode(self, images):
+            T = images.shape[0]
+            F = 1 if T < 22 else 5 * ((T - 5) // 17) + 2
+            return images[:1].mean(dim=(0, 3))[None, None, ::4, ::4].repeat(24, F, 1, 1)
+
+    cfg = h3_preset("tiny")
+    node = cn.SolarRendererConditioning()
+    structure = torch.rand(30, 20, 30, 3)
+    cond, latent = node.encode(lambda p: torch.full((5, cfg.text_dim), float(len(p))), Codec(), structure, "a harbour", width=32, height=16,
+                               length=158, first_frame=torch.rand(1, 20, 30, 3))
+    assert cond["shape"] == (24, 7, 4, 8) and cond["pixel_frames"] == 22 and cond["has_first_frame"]
+    assert latent["samples"].shape == (1, 24, 7, 4, 8) and cond["anchor_latents"].shape == (24, 1, 4, 8)
+    no_first, _ = node.encode(lambda p: torch.zeros(5, cfg.text_dim), Codec(), structure, "x", width=32, height=16, length=22)
+    assert float(no_first["anchor_latents"].abs().sum()) == 0.0
+    with pytest.raises(ValueError):
+        node.encode(lambda p: torch.zeros(5, cfg.text_dim), Codec(), structure[:10], "x", width=32, height=16)
+    # the conditioning renders through the sampler node
+    (svc,) = cn.SolarRendererModelLoader().load(architecture="tiny", steps=2, device="cpu")
+    (lat,) = cn.SolarRendererSampler().sample(svc, cond, seed=0)
+    assert lat["samples"].shape == (1, 24, 7, 4, 8) and torch.isfinite(lat["samples"]).all()
+    # key / mouse scripts
+    plan = cn.capture_plan("0.5:KeyW:1.0, 1.0:mouse:30:0:0.1\n2:click, 0.2:down:ShiftLeft, 3:up:ShiftLeft")
+    assert plan[0] == (0.2, "down", "ShiftLeft") and (0.5, "down", "KeyW") in plan and (1.5, "up", "KeyW") in plan
+    moves = [e for e in plan if e[1] == "move"]
+    assert len(moves) == 3 and sum(m[2][0] for m in moves) == pytest.approx(30.0) and plan[-1] == (3.0, "up", "ShiftLeft")
+    assert [e[1] for e in plan if e[1].startswith("m") and e[1] != "move"] == ["mdown", "mup"]
+    for bad in ("oops", "-1:KeyW"):
+        with pytest.raises(ValueError):
+            cn.capture_plan(bad)
+    # a capture made by an external process is loaded as host images; the command is run with its fields filled in
+    out = tmp_path / "cap"
+    import sys
+
+    maker = tmp_path / "fake_capture.py"
+    maker.write_text("import sys, numpy as np\nnp.save(sys.argv[2] + '.npy', np.full((int(sys.argv[3]), 6, 8, 3), 128, np.uint8))\n")
+    (images,) = cn.SolarRendererWebCapture().capture("http://127.0.0.1/x", frames=24, out=str(out), script="0:KeyW",
+                                                     command=f"{sys.executable} {maker} {{url}} {{out}} {{frames}}")
+    assert images.shape == (24, 6, 8, 3) and float(images.mean()) == pytest.approx(128 / 255, abs=1e-6)
+    with pytest.raises(FileNotFoundError):
+        cn.SolarRendererWebCapture().capture("u", out=str(tmp_path / "absent"))
+    with pytest.raises(RuntimeError):
+        cn.SolarRendererWebCapture().capture("u", out=str(out), command=f"{sys.executable} -c 'raise SystemExit(3)'")
+
+
+def test_lora_loader_node_fills_adapters_and_scales_the_up_projection(tmp_path):
+    from solarwm_b200.backends.minimax_h3.runtime import ADAPTER_SCHEMA
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.renderer import comfy_nodes as cn
+    from solarwm_b200.renderer.service import RenderService
+
+    cfg = h3_preset("tiny")
+    cfg.lora_rank = 4
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    svc = RenderService(model, steps=2)
+    svc.prepare()
+    g = torch.Generator().manual_seed(1)
+    state = {n: torch.randn(p.shape, generator=g) for n, p in model.named_parameters() if "lora_" in n}
+    torch.save({"schema": ADAPTER_SCHEMA, "state": state, "rank": 4}, tmp_path / "adapter.pt")
+    (svc,) = cn.SolarRendererLoraLoader().load(svc, str(tmp_path / "adapter.pt"), strength=0.5)
+    got = dict(model.named_parameters())
+    a = next(n for n in state if "lora_A" in n)
+    b = next(n for n in state if "lora_B" in n)
+    assert torch.equal(got[a], state[a]) and torch.allclose(got[b], 0.5 * state[b])
+    torch.save({"schema": ADAPTER_SCHEMA, "state": {"other": torch.zeros(1)}, "rank": 4}, tmp_path / "bad.pt")
+    with pytest.raises(ValueError):
+        cn.SolarRendererLoraLoader().load(svc, str(tmp_path / "bad.pt"))
