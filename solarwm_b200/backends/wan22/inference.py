@@ -267,6 +267,60 @@ class WanLatentAdapter:
             raise BackendContractError(f"inference.first_frame holds {tuple(value.shape)}, the model takes {tuple(shape)}")
         return value.to(dev, self.model.dtype)
 
+    @property
+    def autoregressive(self) -> bool:
+        """Causal checkpoints (teacher forcing, self-gradient forcing) are sampled chunk by chunk with the rolling KV
+        cache and the few-step schedule they were trained for; ``inference.mode`` overrides the route's choice."""
+        mode = (self.config.get("inference", {}) or {}).get("mode")
+        if mode is not None:
+            if mode not in ("bidirectional", "autoregressive"):
+                raise BackendContractError("inference.mode is bidirectional or autoregressive")
+            return mode == "autoregressive"
+        return str((self.config.get("train", {}) or {}).get("causal_mode", "bidirectional")) in ("teacher_forcing", "self_gradient_forcing")
+
+    def _rollout(self, case: InferenceCase, text, frames: int, h: int, w: int, first, dev):
+        """Chunked rollout of ``frames`` latent frames.  With ``inference.cameras`` (a ``.pt`` holding ``viewmats``
+        ``[cases?, F, 4, 4]`` first-frame-relative world-to-camera and optional ``Ks``) every chunk carries its cameras and
+        the clip is as long as the camera path; otherwise the generator runs ``frames / chunk_frames`` chunks."""
+        from ...serve.streaming import StreamingConfig, StreamingGenerator, camera_rollout
+
+        inf, model_cfg = self.config.get("inference", {}) or {}, self.config["model"]
+        causal = model_cfg.get("causal", {}) or {}
+        k = int(causal.get("chunk_frames", 3))
+        window = int(causal.get("window_chunks", 6)) * k
+        steps = tuple(float(t) for t in inf.get("denoising_steps", (self.config.get("train", {}) or {}).get("denoising_steps", (1000.0, 750.0, 500.0, 250.0))))
+        scfg = StreamingConfig(chunk_frames=k, denoise_timesteps=steps, timestep_shift=float(model_cfg.get("timestep_shift", 5.0)),
+                               window_frames=window, sink_frames=int(causal.get("sink_frames", 0)),
+                               use_cuda_graphs=bool(inf.get("cuda_graphs", dev.type == "cuda")), seed=int(case.noise_seed))
+        ph, pw = self.model.cfg.patch_size[1], self.model.cfg.patch_size[2]
+        grid = (h // ph, w // pw)
+        anchor = None if first is None else first.unsqueeze(0).unsqueeze(2)           # [1, C, 1, H, W]
+        cams = inf.get("cameras")
+        if cams:
+            doc = torch.load(str(cams), map_location="cpu", weights_only=True)
+            views = doc["viewmats"]
+            views = views[case.slot] if views.dim() == 4 else views
+            Ks = doc.get("Ks")
+            Ks = None if Ks is None else (Ks[case.slot] if Ks.dim() == 4 else Ks)
+            if views.shape[0] < 1 or tuple(views.shape[1:]) != (4, 4):
+                raise BackendContractError("inference.cameras holds viewmats [F, 4, 4] (or one set per case)")
+            lat = camera_rollout(self.model, text, grid, views.unsqueeze(0).to(dev), None if Ks is None else Ks.unsqueeze(0).to(dev),
+                                 cfg=scfg, first_frame=anchor, transform=str(model_cfg.get("camera_translation_transform", "linear")),
+                                 sp=getattr(self.model, "sp", None))
+            extra = {"mode": "autoregressive", "camera_frames": int(views.shape[0]), "chunk_frames": k}
+        else:
+            body = frames - (0 if anchor is None else 1)
+            if body < 1 or body % k:
+                raise BackendContractError(f"inference.latent_frames leaves {body} frames to generate; chunks hold {k}")
+            gen = StreamingGenerator(self.model, scfg, sp=getattr(self.model, "sp", None))
+            gen.start(text, grid, first_frame=anchor)
+            parts = ([] if anchor is None else [anchor.to(dev, self.model.dtype)]) + [gen.next_chunk() for _ in range(body // k)]
+            lat = torch.cat(parts, dim=2)
+            extra = {"mode": "autoregressive", "chunks": body // k, "chunk_frames": k,
+                     "graph_chunks": sum(1 for st in gen.stats if st.graph)}
+        sigmas = [float(t) / 1000.0 for t in steps] + [0.0]
+        return lat.permute(0, 2, 1, 3, 4).contiguous(), sigmas, extra        # [1, F, C, H, W] like the bidirectional sampler
+
     def generate(self, case: InferenceCase, *, weights_id: str) -> GeneratedSample:
         inf = self.config.get("inference", {}) or {}
         cfg = self.model.cfg
@@ -274,10 +328,16 @@ class WanLatentAdapter:
         text = self._embed(case, dev)
         solver = str(inf.get("solver", "unipc"))
         frames, h, w = int(inf.get("latent_frames", 5)), int(inf.get("latent_height", 16)), int(inf.get("latent_width", 16))
-        lat, sigmas = sample_bidirectional(
-            self.model, text, frames=frames, height=h, width=w, steps=int(inf.get("steps", 50)),
-            shift=float(self.config["model"].get("timestep_shift", 5.0)), seed=case.noise_seed, solver=solver,
-            first_frame=self._first_frame(case, (cfg.out_dim, h, w), dev))
+        first = self._first_frame(case, (cfg.out_dim, h, w), dev)
+        if self.autoregressive:
+            lat, sigmas, extra = self._rollout(case, text, frames, h, w, first, dev)
+            solver = "few-step-rollout"
+        else:
+            lat, sigmas = sample_bidirectional(
+                self.model, text, frames=frames, height=h, width=w, steps=int(inf.get("steps", 50)),
+                shift=float(self.config["model"].get("timestep_shift", 5.0)), seed=case.noise_seed, solver=solver,
+                first_frame=first)
+            extra = {}
         buf = io.BytesIO()
         torch.save(lat.float().cpu(), buf)
         artifacts = {"latents.pt": buf.getvalue(), "schedule.json": json.dumps({"sigmas": sigmas}).encode()}
@@ -290,8 +350,8 @@ class WanLatentAdapter:
         return GeneratedSample(artifacts,
                                tuple(lat.shape), str(lat.dtype).replace("torch.", ""),
                                metrics={"latent_abs_mean": float(lat.float().abs().mean())},
-                               provenance={"sampler": "unipc-flow" if solver == "unipc" else "euler-flow",
-                                           "steps": len(sigmas) - 1, "anchored_first_frame": bool(inf.get("first_frame"))})
+                               provenance={"sampler": {"unipc": "unipc-flow", "euler": "euler-flow"}.get(solver, solver),
+                                           "steps": len(sigmas) - 1, "anchored_first_frame": bool(inf.get("first_frame")), **extra})
 
 
 def _cases(config, count):

@@ -135,3 +135,34 @@ def test_two_ranks_publish_what_one_rank_does(tmp_path, sp):
         x = torch.load(one / f"slot-{slot:06d}" / "latents.pt")
         y = torch.load(two / f"slot-{slot:06d}" / "latents.pt")
         torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-5)
+
+
+def test_causal_routes_are_sampled_by_chunked_rollout_with_optional_cameras(tmp_path):
+    from solarwm_b200.backends.wan22.inference import WanLatentAdapter
+
+    model, cfg = _tiny()
+    base = {"model": {"family": "wan22_ti2v_5b", "timestep_shift": 3.0, "causal": {"chunk_frames": 2, "window_chunks": 2}},
+            "train": {"stage": "stage2", "causal_mode": "self_gradient_forcing", "denoising_steps": [1000.0, 500.0]},
+            "inference": {"latent_frames": 5, "latent_height": 4, "latent_width": 4, "first_frame": "seeded"}}
+    ad = WanLatentAdapter("wan22_ti2v_5b", model, base)
+    assert ad.autoregressive
+    out = ad.generate(_case(0), weights_id="w")
+    assert out.shape == (1, 5, cfg.out_dim, 4, 4) and out.provenance["sampler"] == "few-step-rollout"
+    assert out.provenance["mode"] == "autoregressive" and out.provenance["chunks"] == 2 and out.provenance["steps"] == 2
+    again = ad.generate(_case(0), weights_id="w")
+    assert out.artifacts["latents.pt"] == again.artifacts["latents.pt"]                  # seeded by the case
+    assert ad.generate(_case(1), weights_id="w").artifacts["latents.pt"] != out.artifacts["latents.pt"]
+    # the bidirectional route of the same weights is another sampler; inference.mode overrides the route
+    bi = WanLatentAdapter("wan22_ti2v_5b", model, {**base, "inference": {**base["inference"], "mode": "bidirectional", "steps": 2}})
+    assert not bi.autoregressive and bi.generate(_case(0), weights_id="w").provenance["sampler"] == "unipc-flow"
+    with pytest.raises(BackendContractError):
+        WanLatentAdapter("wan22_ti2v_5b", model, {**base, "inference": {"mode": "other"}}).autoregressive
+    with pytest.raises(BackendContractError):                                            # 4 + anchor does not split into chunks of 2... 3 does not
+        WanLatentAdapter("wan22_ti2v_5b", model, {**base, "inference": {**base["inference"], "latent_frames": 4}}).generate(_case(0), weights_id="w")
+    # camera-length rollout: as many frames as the path has
+    views = torch.eye(4).repeat(7, 1, 1)
+    views[:, 2, 3] = -torch.arange(7) * 0.1
+    torch.save({"viewmats": views}, tmp_path / "cams.pt")
+    cam = WanLatentAdapter("wan22_ti2v_5b", model, {**base, "inference": {**base["inference"], "cameras": str(tmp_path / "cams.pt")}})
+    got = cam.generate(_case(0), weights_id="w")
+    assert got.shape[1] == 7 and got.provenance["camera_frames"] == 7
