@@ -199,12 +199,22 @@ class RuntimeProvider:
             report["native_library"] = True
         except Exception as exc:  # noqa: BLE001 - reported, not raised
             report["problems"].append(f"native library: {exc}")
+        import os
+
         assets = (self.config.get("model", {}) or {}).get("assets", {}) or {}
         for name, path in assets.items():
-            import os
-
             if not os.path.exists(str(path)):
                 report["problems"].append(f"asset {name} missing: {path}")
+        base = assets.get("base_checkpoint")
+        if base and os.path.isfile(str(base)) and str(base).endswith(".safetensors"):
+            # header-only: tensor families, counts, dtype policy and layout digest, before any weight byte is read
+            from ...errors import BackendContractError
+            from .checkpoint import inspect_base_checkpoint
+
+            try:
+                report["base_checkpoint"] = inspect_base_checkpoint(base).as_dict()
+            except BackendContractError as exc:
+                report["problems"].append(f"base checkpoint: {exc}")
         report["ready"] = not report["problems"]
         return report
 
