@@ -109,6 +109,68 @@ def encoded_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) ->
         yield batch
 
 
+def build_online_codecs(config: Mapping[str, Any], device):
+    """The text encoder and the video VAE of ``data.encoding: online`` training.  With ``model.base_path`` the published
+    files are loaded strictly (``WanTextEncoder.from_released``; ``Wan5BVAE`` / ``WanA14BVAE.from_checkpoint``); without
+    one, ``data.online_codecs`` (``{t5: T5Config fields, vae: {z_dim, base, temporal_ups}}``) builds seeded stand-ins so the
+    path runs without any weight file (reference: build_online_codec_components,
+    solar/backends/wan22/runtime/components.py:662-673)."""
+    from ...models.t5 import T5Config, WanTextEncoder
+    from ...models.vae import VAEConfig, VideoVAE
+    from .codec import Wan5BVAE, WanA14BVAE, WanVideoCodec
+    from .readiness import AssetLayout
+
+    family = str(config["model"]["family"])
+    layout = AssetLayout.from_config(config)
+    if layout.base is not None:
+        kind = {"wan22_ti2v_5b": Wan5BVAE, "wan22_i2v_a14b": WanA14BVAE}.get(family)
+        if kind is None:
+            raise BackendContractError(f"no online codec for family {family!r}")
+        text = WanTextEncoder.from_released(layout.text_encoder, layout.tokenizer, device=device)
+        return text, kind.from_checkpoint(layout.vae, device=device, dtype=torch.bfloat16 if device.type == "cuda" else torch.float32)
+    spec = config["data"].get("online_codecs") or {}
+    tcfg = T5Config(**spec["t5"]) if "t5" in spec else T5Config.tiny()
+    v = dict(spec.get("vae", {}))
+    if "temporal_ups" in v:
+        v["temporal_ups"] = tuple(bool(u) for u in v["temporal_ups"])
+    vae = VideoVAE(VAEConfig(**v)).to(device=device, dtype=torch.float32).eval()
+    return WanTextEncoder(tcfg, device=device, dtype=torch.float32), WanVideoCodec(vae)
+
+
+def online_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) -> Iterator[dict]:
+    """Training batches encoded on the fly (``data.encoding: online``): raw clips and captions of this rank (the same
+    reader the pre-encoder uses: synthetic clips, or tar shards of ``.npy`` / compressed video) go through the frozen VAE
+    and text encoder right before the step, so no latent corpus has to exist.  The epoch repeats when the source ends."""
+    from ...errors import DataContractError
+    from .preencode import _clips
+
+    text_encoder, codec = build_online_codecs(config, device)
+    data = config["data"]
+    micro = int(config["train"].get("micro_batch_size", 1))
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    source = dict(config, preencode={"source": str(data.get("raw_source", data.get("source", "synthetic"))).replace("raw", "index"),
+                                      "raw_root": data.get("raw_root"), "raw_index": data.get("raw_index"),
+                                      "num_samples": int(data.get("num_samples", 8))})
+    while True:
+        group = []
+        for sample_id, clip, caption in _clips(source, dp_rank, dp_size):
+            with torch.no_grad():
+                z = codec.encode(clip.permute(1, 0, 2, 3).unsqueeze(0).to(device))[0]                 # [F, z, h, w]
+                e = text_encoder([caption])[0]
+            if z.shape[1] != arch.out_dim or tuple(e.shape) != (arch.text_len, arch.text_dim):
+                raise DataContractError(f"{sample_id}: online codecs give latents {tuple(z.shape)} / text {tuple(e.shape)}; the model "
+                                        f"takes {arch.out_dim} channels and text ({arch.text_len}, {arch.text_dim})")
+            if not bool(torch.isfinite(z.float()).all()):
+                raise DataContractError(f"{sample_id}: the VAE produced non-finite latents")
+            group.append((sample_id, z, e))
+            if len(group) == micro:
+                yield {"latents": torch.stack([g[1] for g in group]).to(dtype), "text": torch.stack([g[2] for g in group]).to(dtype),
+                       "sample_ids": [g[0] for g in group], "start_frames": [0] * micro}
+                group = []
+        if not group and micro > int(data.get("num_samples", 8)) and source["preencode"]["source"] == "synthetic":
+            raise DataContractError("the online source holds fewer clips than one micro batch")
+
+
 def activation_and_sharding_options(train: Mapping[str, Any], world_size: int) -> Mapping[str, Any]:
     """Trainer options out of the ``train`` section.
 
@@ -189,7 +251,9 @@ class WanStage0p5Runtime:
         self.scheduler = WarmupCosine(self.trainer.optimizer, warmup_steps=int(train.get("warmup_steps", 0)),
                                       total_steps=int(train["max_steps"]),
                                       min_lr_ratio=float(opt.get("min_lr_ratio", 0.1)))
-        if str(config["data"].get("source", "synthetic")) == "index":
+        if str(config["data"].get("encoding", "preencoded")) == "online":
+            self.batches = online_batches(config, self.arch, self.ctx.device, topo.dp_rank, topo.dp_size)
+        elif str(config["data"].get("source", "synthetic")) == "index":
             self.batches = encoded_batches(config, self.arch, self.ctx.device, topo.dp_rank, topo.dp_size)
         else:
             self.batches = synthetic_batches(config, self.arch, self.ctx.device)
