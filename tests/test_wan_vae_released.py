@@ -224,3 +224,27 @@ def test_codec_adapters_take_the_published_files(tmp_path):
     assert px.shape == (1, 5, 3, 16, 16) and float(px.abs().max()) <= 1.0
     pieces = list(codec.decode_streaming_chunks(z, chunk_latent_frames=1))
     assert torch.allclose(torch.cat(pieces, dim=1), px, atol=1e-4)
+
+
+def test_online_encoding_batches_come_from_raw_clips_through_the_codecs():
+    from solarwm_b200.backends.wan22.runtime import build_online_codecs, online_batches
+    from solarwm_b200.models.wan import wan_preset
+
+    arch = wan_preset("tiny")
+    config = {"model": {"family": "wan22_ti2v_5b"}, "train": {"micro_batch_size": 2},
+              "data": {"source": "synthetic", "encoding": "online", "num_samples": 3, "seed": 1, "pixel_frames": 9, "pixel_height": 32,
+                       "pixel_width": 32,
+                       "online_codecs": {"t5": {"vocab": 512, "dim": 256, "dim_attn": 64, "dim_ffn": 128, "num_heads": 2, "num_layers": 1, "text_len": 32},
+                                         "vae": {"z_dim": 16, "base": 8, "temporal_ups": [True, True, False]}}}}
+    stream = online_batches(config, arch, torch.device("cpu"))
+    a, b = next(stream), next(stream)
+    assert a["latents"].shape == (2, 3, 16, 4, 4) and a["text"].shape == (2, 32, 256) and a["sample_ids"] == ["synthetic-000000", "synthetic-000001"]
+    # 3 clips, micro batch 2: the third clip is dropped at the epoch's end and the epoch repeats with the same encodings
+    assert b["sample_ids"] == a["sample_ids"] and torch.equal(a["latents"], b["latents"])
+    text, codec = build_online_codecs(config, torch.device("cpu"))
+    assert codec.vae.cfg.z_dim == 16 and text(["a caption"]).shape == (1, 32, 256)
+    bad = {**config, "data": {**config["data"], "online_codecs": {**config["data"]["online_codecs"], "vae": {"z_dim": 8, "base": 8}}}}
+    from solarwm_b200.errors import DataContractError
+
+    with pytest.raises(DataContractError):
+        next(online_batches(bad, arch, torch.device("cpu")))
