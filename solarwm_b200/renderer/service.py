@@ -80,12 +80,54 @@ class RenderService:
 
 
 # ------------------------------------------------------------------------------------------ HTTP transport
+CLIENT_PAGE = """<!doctype html>
+<html lang="en"><head><meta charset="utf-8"><title>SolarRenderer</title>
+<style>
+ body{font:14px/1.4 system-ui,sans-serif;margin:2rem;max-width:60rem;color:#ddd;background:#181818}
+ h1{font-size:1.2rem} select,input,button{font:inherit;padding:.3rem .5rem;margin-right:.5rem}
+ table{border-collapse:collapse;margin-top:1rem;width:100%} td,th{border-bottom:1px solid #333;padding:.3rem .6rem;text-align:left}
+ #status{margin:.6rem 0;color:#9c9} .err{color:#e88}
+</style></head><body>
+<h1>SolarRenderer service</h1>
+<div id="status">connecting...</div>
+<div><select id="sample"></select><input id="seed" type="number" min="0" value="0" size="6">
+<button id="go">Render</button></div>
+<table><thead><tr><th>sample</th><th>seed</th><th>latents</th><th>seconds</th><th>file</th></tr></thead><tbody id="jobs"></tbody></table>
+<script>
+const $ = id => document.getElementById(id);
+const get = path => fetch(path).then(r => r.json());
+function row(j){ const tr=document.createElement('tr');
+  for (const v of [j.sample,j.seed,(j.shape||[]).join(' x '),j.seconds,j.file]){ const td=document.createElement('td'); td.textContent=v; tr.appendChild(td);} return tr; }
+async function refresh(){
+  const h = await get('/health');
+  $('status').textContent = h.prepared ? `ready: ${h.steps} steps, ${h.time_sets.length} prepared time sets` : 'not prepared';
+  const jobs = await get('/jobs'); $('jobs').replaceChildren(...jobs.slice().reverse().map(row));
+}
+async function start(){
+  for (const s of await get('/samples')){ const o=document.createElement('option'); o.value=o.textContent=s; $('sample').appendChild(o); }
+  await refresh();
+}
+$('go').onclick = async () => {
+  $('go').disabled = true; $('status').className=''; $('status').textContent = 'rendering...';
+  try {
+    const r = await fetch('/render',{method:'POST',headers:{'Content-Type':'application/json'},
+                                     body:JSON.stringify({sample:$('sample').value,seed:Number($('seed').value)})});
+    const j = await r.json();
+    if (!r.ok) { $('status').className='err'; $('status').textContent = j.error; } else await refresh();
+  } finally { $('go').disabled = false; }
+};
+start().catch(e => { $('status').className='err'; $('status').textContent = String(e); });
+</script></body></html>
+"""
+
+
 def make_server(service: "RenderService", samples: Mapping[str, Mapping[str, torch.Tensor]], out_dir, *,
                 host: str = "127.0.0.1", port: int = 0):
     """Stdlib HTTP front of the service: ``GET /health`` (the prepare report), ``GET /samples`` (ids),
     ``POST /render {"sample": id, "seed": n}`` -> renders on the serving thread under a lock (one request on the
     device at a time), saves the latents under ``out_dir`` and answers with the file name and the latency,
-    ``GET /jobs`` (history).  Unknown samples and malformed bodies are refused with 4xx, never forwarded."""
+    ``GET /jobs`` (history), ``GET /`` (a dependency-free browser client of these four calls).  Unknown samples and
+    malformed bodies are refused with 4xx, never forwarded."""
     import json
     import threading
     import time
@@ -109,6 +151,13 @@ def make_server(service: "RenderService", samples: Mapping[str, Mapping[str, tor
             self.wfile.write(body)
 
         def do_GET(self):
+            if self.path in ("/", "/index.html"):
+                page = CLIENT_PAGE.encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/html; charset=utf-8")
+                self.send_header("Content-Length", str(len(page)))
+                self.end_headers()
+                return self.wfile.write(page)
             if self.path == "/health":
                 rep = service.report
                 return self._send(200, {"prepared": rep is not None, "steps": service.steps,

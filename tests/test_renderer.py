@@ -115,6 +115,12 @@ def test_render_service_http_transport(tmp_path):
         assert torch.equal(torch.load(tmp_path / "out" / job["file"]), svc.render(_sample(cfg, 0), seed=3).cpu())
         assert call("POST", "/render", {"sample": "nope"})[0] == 404 and call("POST", "/render", {"seed": 1})[0] == 400
         assert call("GET", "/jobs")[1] == [job] and call("GET", "/x")[0] == 404
+        c = http.client.HTTPConnection("127.0.0.1", server.server_address[1], timeout=60)
+        c.request("GET", "/")
+        page = c.getresponse()
+        html = page.read().decode()
+        assert page.status == 200 and page.getheader("Content-Type").startswith("text/html")
+        assert all(path in html for path in ("'/health'", "'/samples'", "'/render'", "'/jobs'")) and "<script src" not in html
     finally:
         server.shutdown()
 
