@@ -256,24 +256,8 @@ class H3TrainingRuntime:
             identity = BatchIdentity((ident,), (0,), (objective_seed(self.seed, self.topology.dp_rank) + ordinal,),
                                      self.checkpoint_id, self.plan_fingerprint)
             return MicrobatchResult(identity, {"loss": loss})
-        dev, dt = self.device, self.model.dtype
-        lat, anchor = sample["target_latents"].to(dev), sample["anchor_latents"].to(dev)
-        prompt = sample["prompt_embeds"].to(dev)
-        C, F, H, W = lat.shape
-        u = torch.rand(1, generator=self.gen, device=dev)
-        t_video = float(1.0 - flow.shifted_sigma(u, flow.VIDEO_SHIFT))
-        layout = build_layout(n_text=prompt.shape[0], latent_frames=F, grid_hw=(H // 2, W // 2), t_video=t_video)
-        noise = torch.randn(lat.shape, generator=self.gen, device=dev, dtype=torch.float32).to(lat.dtype)
-        a_noise = torch.randn(anchor.shape, generator=self.gen, device=dev, dtype=torch.float32).to(lat.dtype)
-        x_t, anchor_t = flow.interpolate(lat, noise, t_video), flow.interpolate(anchor, a_noise, 0.999)
-        vid, _ = self.model(video_rows=patchify_latents(x_t).to(dt), text_rows=prompt.to(dt),
-                            anchor_rows=patchify_latents(anchor_t).to(dt), timesteps=layout.timesteps,
-                            t_index=layout.t_index.to(dev), tags=layout.tags.to(dev), position_ids=layout.position_ids,
-                            viewmats=expand_cameras(layout, sample["camera_w2c"]))
-        tgt = patchify_latents(flow.target(lat, noise).to(lat.dtype)).float()
-        a, b = self.model.local_video_rows                      # this rank's share of the video rows
-        # the sample's mean square error, of which this rank holds the terms of its rows
-        share = (vid.float() - tgt[a:b]).pow(2).sum() / tgt.numel()
+        u = torch.rand(1, generator=self.gen, device=self.device)
+        share, tgt_numel = self._stage0p5_share(sample, float(1.0 - flow.shifted_sigma(u, flow.VIDEO_SHIFT)), self.gen)
         (share / grad_accum).backward()
         total = share.detach().clone()
         if self.topology.sp_size > 1:
@@ -286,6 +270,25 @@ class H3TrainingRuntime:
         identity = BatchIdentity((ident,), (0,), (objective_seed(self.seed, self.topology.dp_rank) + ordinal,),
                                  self.checkpoint_id, self.plan_fingerprint)
         return MicrobatchResult(identity, {"loss": loss})
+
+    def _stage0p5_share(self, sample, t_video: float, gen: torch.Generator):
+        """This rank's share of the sample's mean-square flow-matching error at time ``t_video`` (all noise from ``gen``);
+        summed over the SP group it is the sample's loss."""
+        dev, dt = self.device, self.model.dtype
+        lat, anchor = sample["target_latents"].to(dev), sample["anchor_latents"].to(dev)
+        prompt = sample["prompt_embeds"].to(dev)
+        C, F, H, W = lat.shape
+        layout = build_layout(n_text=prompt.shape[0], latent_frames=F, grid_hw=(H // 2, W // 2), t_video=t_video)
+        noise = torch.randn(lat.shape, generator=gen, device=dev, dtype=torch.float32).to(lat.dtype)
+        a_noise = torch.randn(anchor.shape, generator=gen, device=dev, dtype=torch.float32).to(lat.dtype)
+        x_t, anchor_t = flow.interpolate(lat, noise, t_video), flow.interpolate(anchor, a_noise, 0.999)
+        vid, _ = self.model(video_rows=patchify_latents(x_t).to(dt), text_rows=prompt.to(dt),
+                            anchor_rows=patchify_latents(anchor_t).to(dt), timesteps=layout.timesteps,
+                            t_index=layout.t_index.to(dev), tags=layout.tags.to(dev), position_ids=layout.position_ids,
+                            viewmats=expand_cameras(layout, sample["camera_w2c"]))
+        tgt = patchify_latents(flow.target(lat, noise).to(lat.dtype)).float()
+        a, b = self.model.local_video_rows                      # this rank's share of the video rows
+        return (vid.float() - tgt[a:b]).pow(2).sum() / tgt.numel(), tgt.numel()
 
     def assert_sp_peer_identity(self, identity: BatchIdentity) -> None:
         if self.topology.sp_size == 1:
@@ -388,11 +391,56 @@ class H3TrainingRuntime:
         self.checkpoint_id = verified.manifest_digest
 
     def validate(self, step: int) -> Mapping[str, Any]:
-        """The adapters' state at a validation boundary: norms of the live and the averaged weights."""
+        """The adapters' state at a validation boundary (norms of the live and the averaged weights) and, for Stage0.5
+        with ``validation.index``, the loss on the run's fixed, source-balanced validation clips (``validation.py``)."""
         report = {"step": int(step), "adapter_norm": float(self.optimizer.master.norm())}
         if self.ema is not None:
             report["ema_norm"] = float(self.ema.shadow.norm())
+        val = self.config.get("validation", {}) or {}
+        if val.get("index") and self.core is None:
+            report["validation"] = self._validation_loss(val)
         return report
+
+    def _validation_loss(self, val: Mapping[str, Any]) -> Mapping[str, Any]:
+        import torch.distributed as dist
+        from pathlib import Path
+
+        from ...data.index import read_index
+        from ...preencode.shards import read_encoded_sample
+        from .validation import IndexedValidation, score
+
+        topo = self.topology
+        if getattr(self, "_validation", None) is None:
+            index = Path(str(val["index"]))
+            root = Path(str(val.get("root") or index.parent))
+
+            def read(row):
+                enc = read_encoded_sample(root, row.values)
+                lat = enc["latents"]
+                if lat.shape[0] < 2:
+                    raise BackendContractError(f"{row.sample_id}: needs at least two latent frames")
+                return {"target_latents": lat[1:].permute(1, 0, 2, 3).contiguous(), "anchor_latents": lat[:1].permute(1, 0, 2, 3).contiguous(),
+                        "prompt_embeds": enc["text"], "camera_w2c": torch.eye(4).repeat(lat.shape[0], 1, 1)}
+
+            self._validation = IndexedValidation(read_index(index), read, sample_count=int(val.get("sample_count", 8)),
+                                                 seed=int(val.get("seed", 42)), dp_rank=topo.dp_rank, dp_size=topo.dp_size,
+                                                 balance=bool(val.get("balance_sources", True)),
+                                                 freeze_path=output_root(self.config) / "validation-selection.json")
+            self._validation.prepare(dist if topo.raw_world_size > 1 else None)
+
+        def loss_at(sample, t, gen):
+            share, _ = self._stage0p5_share(sample, t, gen)
+            if topo.sp_size > 1:
+                share = share.clone()
+                dist.all_reduce(share, group=self.ctx.sp_group)
+            return share
+
+        was_training = self.model.training
+        self.model.eval()
+        try:
+            return dict(score(self._validation, loss_at, device=self.device, dist=dist if topo.dp_size > 1 else None, group=self.ctx.dp_group))
+        finally:
+            self.model.train(was_training)
 
     def close(self) -> None:
         dist_init.shutdown(self.ctx)
