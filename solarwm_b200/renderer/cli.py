@@ -6,7 +6,7 @@
     python -m solarwm_b200.renderer.cli export  --checkpoint DIR --out FILE [--weight-source live|ema]
     python -m solarwm_b200.renderer.cli train   --steps N [--arch tiny] [--patterns shared=1,known_frames=1]     (synthetic)
     python -m solarwm_b200.renderer.cli distill --steps N
-    python -m solarwm_b200.renderer.cli render  --out DIR [--steps 8]
+    python -m solarwm_b200.renderer.cli render  --out DIR [--steps 8] [--causal --frames F --chunk 5 --window 6]
 
 (reference: solar/renderer/__main__.py, render.py)."""
 from __future__ import annotations
@@ -76,6 +76,10 @@ def main(argv=None) -> int:
     ap.add_argument("--lora-rank", type=int, default=4)
     ap.add_argument("--patterns", default="shared=1,known_frames=1,known_region=1,confidence_map=1,ramp=1")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--causal", action="store_true", help="render: chunk by chunk with a key / value window (clips of any length)")
+    ap.add_argument("--frames", type=int, default=4, help="render: latent frames of the synthetic sample")
+    ap.add_argument("--chunk", type=int, default=5)
+    ap.add_argument("--window", type=int, default=6)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     args = ap.parse_args(argv)
     if args.command == "export":
@@ -118,7 +122,12 @@ def main(argv=None) -> int:
         from ..models.h3 import H3DiT
 
         model = H3DiT(cfg, device=args.device, dtype=torch.bfloat16 if args.device == "cuda" else torch.float32)
-        lat = render(model, _sample(cfg, 0), steps=max(args.steps, 2))
+        if args.causal:
+            from .causal import CausalRenderer
+
+            lat = CausalRenderer(model, chunk=args.chunk, window=args.window, steps=max(args.steps, 2)).render(_sample(cfg, 0, frames=args.frames))
+        else:
+            lat = render(model, _sample(cfg, 0, frames=args.frames), steps=max(args.steps, 2))
         if args.out:
             Path(args.out).mkdir(parents=True, exist_ok=True)
             torch.save(lat.cpu(), Path(args.out) / "latents.pt")

@@ -291,6 +291,32 @@ class SolarRendererSampler:
         return ({"samples": latents.unsqueeze(0)},)
 
 
+class SolarRendererCausalSampler:
+    """Chunk-by-chunk sampling with a key / value window: clips longer than the training length."""
+
+    @classmethod
+    def INPUT_TYPES(cls):
+        return {"required": {"model": ("MODEL",), "conditioning": ("CONDITIONING",),
+                             "seed": ("INT", {"default": 0, "min": 0, "max": 2 ** 31 - 1}),
+                             "chunk": ("INT", {"default": 5, "min": 1, "max": 16}), "window": ("INT", {"default": 6, "min": 1, "max": 32}),
+                             "steps": ("INT", {"default": 8, "min": 2, "max": 50})}}
+
+    RETURN_TYPES = ("LATENT",)
+    FUNCTION = "sample"
+    CATEGORY = CATEGORY
+
+    def sample(self, model, conditioning, seed=0, chunk=5, window=6, steps=8):
+        from .causal import CausalRenderer
+
+        held = model.model.fixed_tables                  # the prepared tables cover the fixed schedule only
+        model.model.fixed_tables = None
+        try:
+            latents = CausalRenderer(model.model, chunk=int(chunk), window=int(window), steps=int(steps)).render(conditioning, seed=int(seed))
+        finally:
+            model.model.fixed_tables = held
+        return ({"samples": latents.unsqueeze(0)},)
+
+
 NODE_CLASS_MAPPINGS = {
     "SolarRendererModelLoader": SolarRendererModelLoader,
     "SolarRendererSigmas": SolarRendererSigmas,
@@ -300,6 +326,7 @@ NODE_CLASS_MAPPINGS = {
     "SolarRendererLoraLoader": SolarRendererLoraLoader,
     "SolarRendererWebCapture": SolarRendererWebCapture,
     "SolarRendererSampler": SolarRendererSampler,
+    "SolarRendererCausalSampler": SolarRendererCausalSampler,
 }
 NODE_DISPLAY_NAME_MAPPINGS = {
     "SolarRendererModelLoader": "SolarRenderer model",
@@ -310,4 +337,5 @@ NODE_DISPLAY_NAME_MAPPINGS = {
     "SolarRendererLoraLoader": "SolarRenderer LoRA loader",
     "SolarRendererWebCapture": "SolarRenderer web capture",
     "SolarRendererSampler": "SolarRenderer sampler",
+    "SolarRendererCausalSampler": "SolarRenderer causal sampler",
 }

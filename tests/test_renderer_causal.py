@@ -1,0 +1,116 @@
+"""Block-causal renderer: the visibility plan against its dense oracle, segment attention against masked attention, and
+the stream's chunk evaluations against the training document's predictions."""
+import pytest
+import torch
+
+from solarwm_b200.backends.minimax_h3.layout import patchify_latents
+from solarwm_b200.models.h3 import H3DiT, h3_preset
+from solarwm_b200.renderer.causal import (CLEAN_LEVEL, CausalRenderer, ChunkKVCache, chunk_spans, document_rows, plan_mask,
+                                          segment_attention, teacher_forcing_prediction, training_plan)
+from solarwm_b200.renderer.cli import _sample
+
+
+def test_plan_follows_the_visibility_rule():
+    assert chunk_spans(12, 5) == [(0, 5), (5, 10), (10, 12)]
+    with pytest.raises(ValueError):
+        chunk_spans(0, 5)
+    rows = document_rows(3, [2, 2, 2], structure=True, clean_copy=True)
+    assert rows.static == (0, 3) and rows.structure[1] == (5, 7) and rows.clean[0] == (9, 11) and rows.noisy[2] == (19, 21) and rows.total == 21
+    m = plan_mask(training_plan(rows, window=2), rows.total)
+    static, s, c, n = slice(0, 3), rows.structure, rows.clean, rows.noisy
+    sl = lambda span: slice(*span)                                    # noqa: E731
+    assert m[static, static].all() and not m[static, 3:].any()
+    assert m[sl(s[1]), static].all() and m[sl(s[1]), sl(s[1])].all() and not m[sl(s[1]), sl(s[0])].any() and not m[sl(s[1]), 9:].any()
+    # noisy chunk 2 with a window of two: structure 1-2, clean 1, itself; not structure 0, clean 0, clean 2, other noisy chunks
+    q = sl(n[2])
+    assert m[q, static].all() and m[q, sl(s[1])].all() and m[q, sl(s[2])].all() and m[q, sl(c[1])].all() and m[q, q].all()
+    assert not m[q, sl(s[0])].any() and not m[q, sl(c[0])].any() and not m[q, sl(c[2])].any() and not m[q, sl(n[1])].any()
+    # clean chunk 2 sees the same with its own rows in place of the noisy ones
+    qc = sl(c[2])
+    assert m[qc, sl(c[1])].all() and m[qc, qc].all() and not m[qc, sl(n[2])].any() and not m[qc, sl(c[0])].any()
+    # nothing sees a later chunk
+    for j in range(3):
+        for later in range(j + 1, 3):
+            for kind in (s, c, n):
+                assert not m[sl(n[j]), sl(kind[later])].any() and not m[sl(c[j]), sl(kind[later])].any()
+    # diffusion forcing (no clean copy): the history is the noisy chunks themselves
+    df = document_rows(3, [2, 2, 2], structure=False, clean_copy=False)
+    md = plan_mask(training_plan(df, window=2), df.total)
+    assert md[sl(df.noisy[2]), sl(df.noisy[1])].all() and not md[sl(df.noisy[2]), sl(df.noisy[0])].any()
+
+
+def test_segment_attention_equals_masked_attention():
+    torch.manual_seed(0)
+    rows = document_rows(3, [2, 4, 2], structure=True, clean_copy=True)
+    plan = training_plan(rows, window=2)
+    S = rows.total
+    q, k, v = (torch.randn(1, S, 2, 16) for _ in range(3))
+    got = segment_attention(q, k, v, plan)
+    mask = plan_mask(plan, S)
+    want = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask).transpose(1, 2)
+    assert torch.allclose(got, want, atol=1e-5)
+
+
+def _model_and_sample(frames=6):
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    s = _sample(cfg, 3, frames=frames, size=4)
+    g = torch.Generator().manual_seed(9)
+    cams = torch.eye(4).repeat(frames + 1, 1, 1)
+    cams[:, 0, 3] = torch.arange(frames + 1) * 0.05
+    s["camera_w2c"] = cams
+    return model, s, g
+
+
+def test_the_stream_computes_what_the_training_document_predicts():
+    model, s, g = _model_and_sample()
+    C, F, H, W = s["shape"]
+    per = (H // 2) * (W // 2)
+    noisy = torch.randn(F * per, C * 4, generator=g)
+    t_chunks = torch.tensor([0.3, 0.5, 0.7])
+    with torch.no_grad():
+        want = teacher_forcing_prediction(model, s, noisy, t_chunks, chunk=2, window=2)
+        r = CausalRenderer(model, chunk=2, window=2, steps=2)
+        cache = ChunkKVCache(2)
+        prompt = s["prompt_embeds"].float()
+        anchor_rows = patchify_latents(s["anchor_latents"]).float()
+        s_rows, clean = patchify_latents(s["structure_latents"]).float(), patchify_latents(s["target_latents"]).float()
+        for j, (a, b) in enumerate(chunk_spans(F, 2)):
+            kw = dict(prompt=prompt, anchor_rows=anchor_rows, structure_rows=s_rows[a * per:b * per], frames=(a, b), total_frames=F,
+                      grid_hw=(H // 2, W // 2), cameras=s["camera_w2c"])
+            got = r._evaluate(cache, target_rows=noisy[a * per:b * per], t=float(t_chunks[j]), commit=False, **kw)
+            assert torch.allclose(got, want[a * per:b * per], atol=2e-4, rtol=1e-4), (j, (got - want[a * per:b * per]).abs().max())
+            assert cache.chunks == min(j, 1)                           # a window of two keeps one committed chunk
+            r._evaluate(cache, target_rows=clean[a * per:b * per], t=CLEAN_LEVEL, commit=True, **kw)
+    # a wider window changes what chunk 2 sees
+    with torch.no_grad():
+        wide = teacher_forcing_prediction(model, s, noisy, t_chunks, chunk=2, window=3)
+    assert torch.allclose(wide[:2 * 2 * per], want[:2 * 2 * per], atol=1e-5) and not torch.allclose(wide[4 * per:], want[4 * per:], atol=1e-4)
+
+
+def test_rendering_is_chunked_seeded_and_bounded():
+    model, s, _ = _model_and_sample(frames=7)
+    record = []
+    r = CausalRenderer(model, chunk=3, window=2, steps=2)
+    a = r.render(s, seed=5, record=record)
+    assert a.shape == tuple(s["shape"]) and torch.isfinite(a).all()
+    assert [x["frames"] for x in record] == [[0, 3], [3, 6], [6, 7]] and max(x["cached_chunks"] for x in record) == 1
+    assert torch.equal(a, r.render(s, seed=5)) and not torch.equal(a, r.render(s, seed=6))
+    plain = dict(s)
+    plain.pop("structure_latents")
+    b = r.render(plain, seed=5)                                       # no structure stream: still a valid document
+    assert b.shape == a.shape and not torch.equal(a, b)
+
+
+def test_causal_sampler_node_and_cli(tmp_path, capsys):
+    import json
+
+    from solarwm_b200.renderer import comfy_nodes as cn
+    from solarwm_b200.renderer.cli import main
+
+    (svc,) = cn.SolarRendererModelLoader().load(architecture="tiny", steps=2, device="cpu")
+    s = _sample(h3_preset("tiny"), 2, frames=6, size=4)
+    (lat,) = cn.SolarRendererCausalSampler().sample(svc, s, seed=1, chunk=2, window=2, steps=2)
+    assert lat["samples"].shape == (1, *s["shape"]) and svc.model.fixed_tables is not None
+    assert main(["render", "--causal", "--frames", "6", "--chunk", "2", "--window", "2", "--device", "cpu", "--out", str(tmp_path)]) == 0
+    assert json.loads(capsys.readouterr().out)["finite"] is True and (tmp_path / "latents.pt").is_file()
