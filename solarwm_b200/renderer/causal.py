@@ -284,3 +284,32 @@ class CausalRenderer:
                 record.append({"frames": [a, b], "cached_chunks": cache.chunks})
             done.append(x)
         return unpatchify_rows(torch.cat(done).to(dt), C, F, H, W)
+
+
+class CausalOmniTrainer:
+    """Teacher-forcing training of the block-causal renderer: every chunk draws its own shifted time, the noisy chunks are
+    predicted in ONE pass over the training document, the loss is the flow-matching error over all target rows.  Shares
+    the ``compute_loss`` / ``last_plan`` surface of ``renderer.core.OmniFlowTrainer`` so the training runtime drives either."""
+
+    def __init__(self, model: H3DiT, optimizer, *, chunk: int = 5, window: int = 6, seed: int = 0):
+        from types import SimpleNamespace
+
+        self.model, self.opt, self.chunk, self.window = model, optimizer, int(chunk), int(window)
+        self.device = model.proj_in.device
+        self.rng = np.random.default_rng(seed)
+        self.gen = torch.Generator(device=self.device).manual_seed(int(seed) * 100003 + 31)
+        self.last_plan = SimpleNamespace(pattern="block_causal", generated_fraction=1.0)
+
+    def compute_loss(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
+        dev = self.device
+        lat = sample["target_latents"].to(dev)
+        C, F, H, W = lat.shape
+        per = (H // 2) * (W // 2)
+        spans = chunk_spans(F, self.chunk)
+        t_chunks = torch.tensor([float(1.0 - flow.shifted_sigma(torch.tensor(self.rng.random()), flow.VIDEO_SHIFT)) for _ in spans])
+        noise = torch.randn(lat.shape, generator=self.gen, device=dev, dtype=torch.float32)
+        x0, n = patchify_latents(lat).float(), patchify_latents(noise)
+        t_rows = torch.cat([torch.full(((b - a) * per,), float(t_chunks[i])) for i, (a, b) in enumerate(spans)]).to(dev).view(-1, 1)
+        noisy = t_rows * x0 + (1.0 - t_rows) * n
+        pred = teacher_forcing_prediction(self.model, sample, noisy, t_chunks, chunk=self.chunk, window=self.window)
+        return (pred.float() - (x0 - n)).pow(2).mean()

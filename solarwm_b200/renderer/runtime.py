@@ -57,6 +57,10 @@ def validate_config(config: Mapping[str, Any]) -> None:
             raise ConfigurationError(f"data.{key} is required")
     if int((config.get("distributed", {}) or {}).get("sequence_parallel_size", 1)) != 1:
         raise ConfigurationError("renderer training is data parallel: distributed.sequence_parallel_size must be 1")
+    causal = train.get("causal_omni")
+    if causal is not None:
+        if not isinstance(causal, Mapping) or int(causal.get("chunk", 5)) < 1 or int(causal.get("window", 6)) < 1:
+            raise ConfigurationError("train.causal_omni is a mapping with positive chunk and window")
     if not config["runtime"].get("output_dir"):
         raise ConfigurationError("runtime.output_dir is required")
 
@@ -106,8 +110,15 @@ class RendererTrainingRuntime:
         self.ema = AdapterEMA(self.optimizer, float(e.get("decay", 0.999))) if e.get("enabled", True) else None
         self.ema_start, self.ema_every = int(e.get("start_step", 0)), int(e.get("update_every_steps", 1))
         self.profile = ObservationProfile.from_config(train) or ObservationProfile()
-        self.core = OmniFlowTrainer(cfg, dev, self.profile, model=self.model, optimizer=self.optimizer,
-                                    seed=objective_seed(self.seed, topo.dp_rank) % (2 ** 31))
+        causal = train.get("causal_omni")
+        if causal:
+            from .causal import CausalOmniTrainer
+
+            self.core = CausalOmniTrainer(self.model, self.optimizer, chunk=int(causal.get("chunk", 5)), window=int(causal.get("window", 6)),
+                                          seed=objective_seed(self.seed, topo.dp_rank) % (2 ** 31))
+        else:
+            self.core = OmniFlowTrainer(cfg, dev, self.profile, model=self.model, optimizer=self.optimizer,
+                                        seed=objective_seed(self.seed, topo.dp_rank) % (2 ** 31))
         c = data.get("member_contract", {}) or {}
         contract = MemberContract(latent_channels=int(c.get("latent_channels", 24)), text_dim=int(c.get("text_dim", cfg.text_dim)),
                                   grids=tuple(tuple(int(v) for v in g) for g in c.get("grids", ((48, 84), (84, 48)))),
@@ -201,13 +212,15 @@ class RendererTrainingRuntime:
     # -- checkpoints --------------------------------------------------------------------------------------------------------
     def _contract(self) -> CheckpointContract:
         train = self.config["train"]
-        return CheckpointContract(family="minimax_h3_renderer", stage="control", causal_mode="bidirectional",
+        return CheckpointContract(family="minimax_h3_renderer", stage="control",
+                                  causal_mode="block_causal" if train.get("causal_omni") else "bidirectional",
                                   objective=str(train.get("objective", "flow_matching")), objective_variant="data_ward_velocity",
                                   camera_translation_transform="logd4", parameterization=f"lora-r{self.model.cfg.lora_rank}",
                                   sp_size=1, data_generation="solarrenderer.omni.v1")
 
     def _metadata(self) -> dict:
-        return {"observations": dict(self.profile.fingerprint()), "data_plan": self.plan_fingerprint, "parents": dict(self.parents)}
+        return {"observations": dict(self.profile.fingerprint()), "data_plan": self.plan_fingerprint, "parents": dict(self.parents),
+                "causal_omni": dict(self.config["train"].get("causal_omni") or {})}
 
     def _rank_state(self) -> dict:
         state = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in capture_rank_state(self.device).items()}
@@ -249,7 +262,8 @@ class RendererTrainingRuntime:
         root, topo = verified.path, self.topology
         run = torch.load(root / "runtime.pt", weights_only=True)
         mine = self._metadata()
-        for key, what in (("data_plan", "data plan"), ("observations", "observation profile"), ("parents", "parent adapters")):
+        for key, what in (("data_plan", "data plan"), ("observations", "observation profile"), ("parents", "parent adapters"),
+                          ("causal_omni", "causal chunking")):
             if run.get(key) != mine[key]:
                 raise BackendContractError(f"the checkpoint was trained under another {what}")
         ranks = torch.load(root / "rank-state.pt", weights_only=True)

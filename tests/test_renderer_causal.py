@@ -114,3 +114,36 @@ def test_causal_sampler_node_and_cli(tmp_path, capsys):
     assert lat["samples"].shape == (1, *s["shape"]) and svc.model.fixed_tables is not None
     assert main(["render", "--causal", "--frames", "6", "--chunk", "2", "--window", "2", "--device", "cpu", "--out", str(tmp_path)]) == 0
     assert json.loads(capsys.readouterr().out)["finite"] is True and (tmp_path / "latents.pt").is_file()
+
+
+def test_causal_training_runs_behind_the_renderer_runtime(tmp_path):
+    from solarwm_b200.checkpoint.store import verify_checkpoint
+    from solarwm_b200.errors import BackendContractError, ConfigurationError
+    from solarwm_b200.renderer.runtime import RendererTrainingRuntime, run_control_training, validate_config
+    from tests.test_renderer_runtime import _config, _corpus
+
+    _corpus(tmp_path / "corpus", n=4, frames=lambda i: 4)
+    cfg = _config(tmp_path / "corpus", tmp_path / "run", train={"causal_omni": {"chunk": 2, "window": 2}, "max_steps": 2,
+                                                                "gradient_accumulation_steps": 1})
+    out = run_control_training(cfg)
+    assert out["final_step"] == 2 and out["last_loss"] == out["last_loss"]
+    ck = verify_checkpoint(out["checkpoint"])
+    assert ck.contract.causal_mode == "block_causal"
+    # the causal chunking is part of the resume identity
+    other = _config(tmp_path / "corpus", tmp_path / "run2", train={"causal_omni": {"chunk": 4, "window": 2}, "max_steps": 3,
+                                                                   "gradient_accumulation_steps": 1}, checkpoint={"resume_from": out["checkpoint"]})
+    with pytest.raises(BackendContractError):
+        RendererTrainingRuntime(other)
+    with pytest.raises(ConfigurationError):
+        validate_config(_config(tmp_path / "corpus", tmp_path / "x", train={"causal_omni": {"chunk": 0}}))
+    # gradients reach the adapters through the segment-attention document
+    rt = RendererTrainingRuntime(_config(tmp_path / "corpus", tmp_path / "run3", train={"causal_omni": {"chunk": 2, "window": 2}}))
+    try:
+        with torch.no_grad():
+            rt.optimizer.master.add_(0.02)
+            rt.optimizer.live.copy_(rt.optimizer.master.to(rt.optimizer.live.dtype))
+        rt.train_microbatch(0, 1)
+        grads = [p.grad for p in rt.optimizer.params if p.grad is not None]
+        assert grads and any(float(g.abs().sum()) > 0 for g in grads)
+    finally:
+        rt.close()
