@@ -51,7 +51,10 @@ def _train_from_config(args) -> int:
         out.mkdir(parents=True, exist_ok=True)
         (out / "runtime-config.json").write_text(json.dumps(config, indent=2, sort_keys=True) + "\n")
     if config["train"].get("objective", "flow_matching") == "dmd":
-        raise SystemExit("renderer distillation runs through the 'distill' command")
+        from .dmd_runtime import run_dmd_training
+
+        print(json.dumps(run_dmd_training(config), sort_keys=True, default=str))
+        return 0
     print(json.dumps(run_control_training(config), sort_keys=True, default=str))
     return 0
 

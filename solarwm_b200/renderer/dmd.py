@@ -38,7 +38,34 @@ class RendererDMDTrainer:
         self.opt_c = FP32MasterAdamW(self.critic.trainable_parameters(), lr=lr_critic, betas=(0.0, 0.999))
         self.steps, self.guidance, self.ratio = student_steps, guidance, critic_updates_per_student
         self.gen = torch.Generator(device=self.device).manual_seed(seed * 100003 + 31)
-        self.global_step = 0
+        self.global_step = self.student_step = 0
+        self.teacher = None                 # ``set_teacher``: the control-trained renderer as a frozen third role
+        self.sync = None                    # ``sync(params, flat_fp32_grad)``: the runtime's reduction over the replicas
+
+    def set_teacher(self, adapter_state: Mapping[str, torch.Tensor]) -> None:
+        """The teacher of a renderer distillation is the control-trained renderer: the shared base with ITS adapters,
+        frozen.  Without one the base alone (the student with its adapters off) stands in."""
+        t = H3DiT(self.student.cfg, device=self.device, dtype=self.student.dtype, seed=0)
+        share_base(t, self.student)
+        own = {n: p for n, p in t.named_parameters() if p.requires_grad}
+        if set(own) != set(adapter_state):
+            raise ValueError("the teacher's adapter file does not hold exactly this architecture's adapter tensors")
+        with torch.no_grad():
+            for n, p in own.items():
+                p.copy_(adapter_state[n].to(p))
+        self.teacher = t.eval().requires_grad_(False)
+
+    def _finish(self, opt, label: str) -> float:
+        flat = opt.gather_grads()
+        if self.sync is not None:
+            self.sync(opt.params, flat)
+        norm = float(opt.clip_(10.0))
+        if not (norm == norm and norm != float("inf")):
+            opt.zero_grad()
+            raise FloatingPointError(f"non-finite renderer distillation {label} gradient norm")
+        opt.step()
+        opt.zero_grad()
+        return norm
 
     def _teacher(self):
         student = self.student
@@ -85,28 +112,31 @@ class RendererDMDTrainer:
             x_t = t_s * out.detach() + (1 - t_s) * n2
             with torch.no_grad():
                 fake, _ = self._x0(self.critic, sample, x_t, t_s, True)
-                with self._teacher():
-                    real, _ = self._x0(self.student, sample, x_t, t_s, True)
-                    free, _ = self._x0(self.student, sample, x_t, t_s, False)
+                if self.teacher is not None:
+                    real, _ = self._x0(self.teacher, sample, x_t, t_s, True)
+                    free, _ = self._x0(self.teacher, sample, x_t, t_s, False)
+                else:
+                    with self._teacher():
+                        real, _ = self._x0(self.student, sample, x_t, t_s, True)
+                        free, _ = self._x0(self.student, sample, x_t, t_s, False)
                 real = structure_guided(real, free, self.guidance)
+                if not bool(torch.isfinite(fake).all() and torch.isfinite(real).all()):
+                    raise FloatingPointError("non-finite renderer distillation score")
             g = sgf_kl_gradient(fake_x0=fake.unsqueeze(0), real_x0=real.unsqueeze(0), student_output=out.detach().unsqueeze(0))
             loss_s = sgf_student_loss(out.unsqueeze(0), g)
             loss_s.backward()
-            self.opt_s.gather_grads()
-            self.opt_s.clip_(10.0)
-            self.opt_s.step()
-            self.opt_s.zero_grad()
+            result["student_grad_norm"] = self._finish(self.opt_s, "student")
             result["student"] = float(loss_s.detach())
+            self.student_step += 1
         t_c = float(0.02 + 0.96 * torch.rand(1, generator=self.gen, device=dev))
         n3 = torch.randn(x_rows.shape, generator=self.gen, device=dev)
         x0 = out.detach()
         _, vel = self._x0(self.critic, sample, t_c * x0 + (1 - t_c) * n3, t_c, True)
         loss_c = (vel.float() - (x0 - n3)).pow(2).mean()
+        if not bool(torch.isfinite(loss_c)):
+            raise FloatingPointError("non-finite renderer distillation critic loss")
         loss_c.backward()
-        self.opt_c.gather_grads()
-        self.opt_c.clip_(10.0)
-        self.opt_c.step()
-        self.opt_c.zero_grad()
+        result["critic_grad_norm"] = self._finish(self.opt_c, "critic")
         result["critic"] = float(loss_c.detach())
         self.global_step += 1
         return result
