@@ -30,8 +30,9 @@ class LTXTrainer:
         attentions and on both FFN linears train instead (``models/lora.py``), under an fp32-master AdamW."""
         dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
         self.model = LTXDiT(cfg, device=device, dtype=dtype, seed=seed)
-        with torch.no_grad():
-            self.model.get_parameter("head.head.weight").normal_(0, 0.02)
+        with torch.no_grad():                  # seeded by the run, not by the process-wide stream: a resumed run rebuilds the same base
+            head = self.model.get_parameter("head.head.weight")
+            head.copy_(torch.randn(head.shape, generator=torch.Generator().manual_seed(int(seed) * 7919 + 5)).mul_(0.02).to(head))
         if sp is not None:
             self.model.sp = sp
         self.sp = sp
@@ -279,6 +280,11 @@ class LTX25Backend:
 
     def train(self, config):
         validate_route(config)
+        if int((config["model"].get("adapter") or {}).get("rank", 0)) > 0:
+            # adapter training: any SP x DP layout behind the shared engine, with schedule, average and exact resume
+            from .runtime import run_training
+
+            return run_training(config)
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
         cfg = _arch(config)
         adapter = (config["model"].get("adapter") or {})
