@@ -337,10 +337,26 @@ class LTX25Backend:
 
     def infer(self, config):
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
-        model = LTXDiT(_arch(config), device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32)
+        trainer_seed = int((config.get("data", {}) or {}).get("seed", 0))
+        ck = config.get("checkpoint", {}) or {}
+        weights_id = "init:random"
+        if ck.get("resume_from"):
+            # the base the adapters were trained on is rebuilt from the run's seed; the adapters (live or averaged) are
+            # installed under the released key inventory and folded into the base weights for sampling
+            from ...models.lora import inject_lora
+            from .runtime import adapter_weights
+
+            meta, state, verified = adapter_weights(ck["resume_from"], str(ck.get("weight_source", "ema")))
+            model = LTXTrainer(_arch(config), dev, seed=trainer_seed).model
+            lora = inject_lora(model, rank=int(meta["rank"]), alpha=float(meta["alpha"]))
+            lora.load_state_dict({k: v.to(dev) for k, v in state.items()}, broadcast=False)
+            lora.merge_()
+            weights_id = verified.manifest_digest
+        else:
+            model = LTXDiT(_arch(config), device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32)
         cases = [InferenceCase(i, f"case-{i}", "synthetic", 0, 1000 + i, "none") for i in range(int(config.get("inference", {}).get("cases", 1)))]
-        s = InferenceEngine(_Adapter(model, config)).run(cases, weights_id="init:random", output_dir=output_root(config) / "generate")
-        return {"output_dir": str(s.output_dir), "cases": s.cases}
+        s = InferenceEngine(_Adapter(model, config)).run(cases, weights_id=weights_id, output_dir=output_root(config) / "generate")
+        return {"output_dir": str(s.output_dir), "cases": s.cases, "weights_id": weights_id}
 
     def preencode(self, config):
         """Raw clips + captions -> 128-channel latent / text shards (8 x 32 x 32 codec geometry; random-init codecs

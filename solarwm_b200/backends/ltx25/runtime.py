@@ -243,6 +243,30 @@ class LTXTrainingRuntime:
         dist_init.shutdown(self.ctx)
 
 
+def adapter_weights(checkpoint, weight_source: str = "live"):
+    """``(metadata, {released key: tensor})`` of a verified adapter checkpoint: the live adapters, or the averaged ones
+    unpacked from the flat fp32 buffer (the optimizer's layout: parameters in key order, each padded to 64 elements)."""
+    if weight_source not in ("live", "ema"):
+        raise BackendContractError("weight_source is live or ema")
+    verified = verify_checkpoint(checkpoint)
+    doc = torch.load(verified.path / "adapter.pt", map_location="cpu", weights_only=True)
+    meta, state = doc["metadata"], doc["state"]
+    if weight_source == "ema":
+        ema = torch.load(verified.path / "ema.pt", map_location="cpu", weights_only=True)
+        flat = ema.get("flat")
+        if flat is None:
+            raise BackendContractError("the checkpoint holds no averaged adapters")
+        out, at = {}, 0
+        for key in meta["state_keys"]:
+            n = state[key].numel()
+            out[key] = flat[at:at + n].view(state[key].shape).to(state[key].dtype)
+            at += (n + 63) // 64 * 64
+        if at != flat.numel():
+            raise BackendContractError("the averaged buffer does not match the adapter inventory")
+        state = out
+    return meta, state, verified
+
+
 def run_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
     runtime = LTXTrainingRuntime(config)
     try:

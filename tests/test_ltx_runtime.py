@@ -94,3 +94,27 @@ def test_sequence_parallel_equals_one_process_and_data_parallel_keeps_replicas_i
     assert sp2[0]["losses"] == pytest.approx(one["losses"], rel=2e-4) and sp2[0]["abs"] == pytest.approx(one["abs"], rel=1e-4)
     dp2 = _spawn(tmp_path, 2, 1)
     assert dp2[0]["master"] == dp2[1]["master"] and dp2[0]["losses"] != dp2[1]["losses"]     # different samples, one set of adapters
+
+
+def test_inference_samples_with_trained_adapters_live_or_averaged(tmp_path):
+    from solarwm_b200.backends.ltx25.runtime import adapter_weights, run_training
+    from solarwm_b200.registry import load_backend
+
+    out = run_training(_config(tmp_path / "train"))
+    meta, live, _ = adapter_weights(out["checkpoint"], "live")
+    _, ema, _ = adapter_weights(out["checkpoint"], "ema")
+    assert set(live) == set(ema) == set(meta["state_keys"]) and all(live[k].shape == ema[k].shape for k in live)
+    moved = [k for k in live if "lora_B" in k and float((live[k] - ema[k]).abs().max()) > 0]
+    assert moved                                                    # the average trails the live weights
+    be = load_backend("ltx25_video")
+    base = {"schema": "solarwm.run.v1", "action": "infer", "model": {"family": "ltx25_video", "architecture": "tiny"},
+            "data": {"seed": 2}, "inference": {"cases": 1, "latent_frames": 2, "latent_height": 4, "latent_width": 4, "steps": 2}}
+    got = {}
+    for name, ck in (("random", {}), ("live", {"resume_from": out["checkpoint"], "weight_source": "live"}),
+                     ("ema", {"resume_from": out["checkpoint"], "weight_source": "ema"})):
+        r = be.infer({**base, "checkpoint": ck, "runtime": {"output_dir": str(tmp_path / name), "device": "cpu"}})
+        got[name] = torch.load(next((tmp_path / name / "generate").rglob("latents.pt")), weights_only=True)
+        assert (r["weights_id"] == "init:random") == (name == "random")
+    assert not torch.equal(got["live"], got["ema"]) and got["live"].shape == got["ema"].shape
+    with pytest.raises(BackendContractError):
+        adapter_weights(out["checkpoint"], "other")
