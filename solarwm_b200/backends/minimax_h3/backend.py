@@ -91,6 +91,56 @@ class MiniMaxH3Backend:
         rules = config["model"].get("weight_rules")
         strict_load_mapped(model, directory, DEFAULT_RULES if not rules else [tuple(r) for r in rules])
 
+    def _inference_model(self, config, dev):
+        """The model an ``infer`` run samples with.  With ``checkpoint.resume_from`` the adapters of that (verified)
+        training checkpoint -- ``checkpoint.weight_source``: ``ema`` (default when the checkpoint holds an average) or
+        ``live`` -- are installed and folded into the base weights, so sampling runs adapter-free GEMMs; the manifest
+        digest becomes the run's weights identity.  Without one the released / seeded base alone is used."""
+        inf = config.get("inference", {}) or {}
+        ck = config.get("checkpoint", {}) or {}
+        cfg = self._cfg(config)
+        dtype = torch.bfloat16 if dev == "cuda" else torch.float32
+        if not ck.get("resume_from"):
+            cfg.lora_rank = 0 if inf.get("merged_weights", True) else cfg.lora_rank
+            model = H3DiT(cfg, device=dev, dtype=dtype, seed=int(inf.get("seed", 0)))
+            self._load_released(model, config)
+            return model, "init:random" if not config["model"].get("weights_dir") else "released"
+        from ...checkpoint.store import verify_checkpoint
+        from ...runtime.randomness import model_init_seed
+        from .runtime import ADAPTER_SCHEMA
+
+        verified = verify_checkpoint(ck["resume_from"])
+        doc = torch.load(verified.path / "adapter.pt", map_location="cpu", weights_only=True)
+        if doc.get("schema") != ADAPTER_SCHEMA:
+            raise BackendContractError(f"{verified.path / 'adapter.pt'} is not an H3 adapter file")
+        state, source = doc["state"], str(ck.get("weight_source", "") or "")
+        ema = torch.load(verified.path / "ema.pt", map_location="cpu", weights_only=True) if (verified.path / "ema.pt").is_file() else {}
+        if source not in ("", "live", "ema"):
+            raise BackendContractError("checkpoint.weight_source is live or ema")
+        if source == "ema" or (source == "" and ema.get("state") is not None):
+            if ema.get("state") is None:
+                raise BackendContractError("the checkpoint holds no averaged adapters")
+            state, source = ema["state"], "ema"
+        cfg.lora_rank = int(doc.get("rank") or cfg.lora_rank)
+        # the base the adapters were trained on: the released weights, or the seeded stand-in of the training run
+        seed = model_init_seed("minimax_h3", int((config.get("data", {}) or {}).get("seed", 0))) % (2 ** 31)
+        model = H3DiT(cfg, device=dev, dtype=dtype, seed=seed)
+        self._load_released(model, config)
+        own = {n: p for n, p in model.named_parameters() if p.requires_grad}
+        if set(own) != set(state):
+            raise BackendContractError("the checkpoint's adapters do not fit this architecture")
+        from ...models.h3 import LoRALinear
+
+        with torch.no_grad():
+            for n, p in own.items():
+                p.copy_(state[n].to(p))
+            for mod in model.modules():
+                if isinstance(mod, LoRALinear):
+                    mod.merge_()
+                    mod.rank = 0
+        model.requires_grad_(False)
+        return model, f"{verified.manifest_digest}:{source or 'live'}"
+
     def train(self, config):
         route = validate_route(config)
         if route.stage == "stage2":
@@ -113,10 +163,8 @@ class MiniMaxH3Backend:
         if inf.get("length_policy") == "source":
             return self._infer_source_length(config)
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
-        cfg = self._cfg(config)
-        cfg.lora_rank = 0 if inf.get("merged_weights", True) else cfg.lora_rank
-        model = H3DiT(cfg, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, seed=int(inf.get("seed", 0)))
-        self._load_released(model, config)
+        model, weights_id = self._inference_model(config, dev)
+        cfg = model.cfg
         gh, gw = (int(v) for v in inf.get("grid_hw", (4, 6)))
         k, chunks = int(inf.get("chunk_latents", 2)), int(inf.get("chunks", 2))
         use_memory = bool(inf.get("memory", False))
@@ -185,7 +233,7 @@ class MiniMaxH3Backend:
         if decoder is not None:
             manifest = dict(manifest, video=frame_sink.close())
         return {"output_dir": str(out_dir), "chunks": manifest.get("chunks"), "frames": manifest.get("frames"),
-                "video": manifest.get("video"),
+                "video": manifest.get("video"), "weights_id": weights_id,
                 "native_launches": ops.total_launches()}
 
     def _infer_source_length(self, config):
@@ -201,10 +249,8 @@ class MiniMaxH3Backend:
 
         inf = config["inference"]
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
-        cfg = self._cfg(config)
-        cfg.lora_rank = 0 if inf.get("merged_weights", True) else cfg.lora_rank
-        model = H3DiT(cfg, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, seed=int(inf.get("seed", 0)))
-        self._load_released(model, config)
+        model, weights_id = self._inference_model(config, dev)
+        cfg = model.cfg
         gh, gw = (int(v) for v in inf.get("grid_hw", (24, 42)))
         use_memory = bool(inf.get("memory", False))
         top_k = int(inf.get("top_k", 5))
@@ -252,8 +298,7 @@ class MiniMaxH3Backend:
 
             writer_factory = _Writer
         summary = run_plan(model, rows, work_dir=work, out_dir=output_root(config) / "generate", stream_cfg=scfg,
-                           identity={"weights": str(config.get("model", {}).get("base_path", "init:random")),
-                                     "checkpoint": str((config.get("checkpoint", {}) or {}).get("resume_from", "")),
+                           identity={"weights": weights_id,
                                      "denoise_steps": scfg.denoise_steps, "window_chunks": scfg.window_chunks},
                            rank=rank, world=world, noise_seed=int(inf.get("seed", 0)), decoder_factory=decoder_factory,
                            writer_factory=writer_factory, use_memory=use_memory, top_k=top_k, fps_policy=fps_policy,

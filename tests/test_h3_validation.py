@@ -117,3 +117,32 @@ def test_runtime_validates_on_its_frozen_clips(tmp_path):
         assert moved["selected"] == first["selected"] and moved["loss"] != first["loss"]
     finally:
         rt.close()
+
+
+def test_inference_uses_the_trained_adapters_of_a_checkpoint(tmp_path):
+    from solarwm_b200.registry import load_backend
+
+    be = load_backend("minimax_h3")
+    train = {"schema": "solarwm.run.v1", "action": "train",
+             "model": {"family": "minimax_h3", "architecture": "tiny", "adapter": {"rank": 4}, "camera_translation_transform": "logd4"},
+             "data": {"source": "synthetic", "seed": 3, "pixel_frames": 158, "latent_frames": 3, "latent_height": 8, "latent_width": 8},
+             "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "max_steps": 6,
+                       "optimizer": {"lr": 2e-2}, "ema": {"decay": 0.5}},
+             "runtime": {"device": "cpu", "output_dir": str(tmp_path / "train")}}
+    out = be.train(train)
+    infer = {"schema": "solarwm.run.v1", "action": "infer", "model": train["model"], "data": {"seed": 3},
+             "inference": {"source": "synthetic", "grid_hw": [2, 2], "chunk_latents": 2, "chunks": 1, "denoise_steps": 1, "seed": 1}}
+    runs = {}
+    for name, ck in (("base", {}), ("live", {"resume_from": out["checkpoint"], "weight_source": "live"}),
+                     ("ema", {"resume_from": out["checkpoint"]})):
+        model, weights_id = be._inference_model({**infer, "checkpoint": ck}, "cpu")
+        runs[name] = (weights_id, {n: p.detach().clone() for n, p in model.named_parameters() if n.endswith("q.weight") or ".q." in n})
+        assert not any(p.requires_grad for p in model.parameters()) or name == "base"
+        r = be.infer({**infer, "checkpoint": ck, "runtime": {"device": "cpu", "output_dir": str(tmp_path / name)}})
+        assert r["chunks"] == 1 and r["weights_id"] == weights_id
+    assert runs["base"][0] == "init:random" and runs["live"][0].endswith(":live") and runs["ema"][0].endswith(":ema")
+    import pytest as _pytest
+    from solarwm_b200.errors import BackendContractError
+
+    with _pytest.raises(BackendContractError):
+        be._inference_model({**infer, "checkpoint": {"resume_from": out["checkpoint"], "weight_source": "other"}}, "cpu")
