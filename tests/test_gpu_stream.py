@@ -134,3 +134,66 @@ def test_wan_teacher_forcing_matches_cpu_fp32():
     got = wan_tf.forward_teacher_forcing(gpu, clean.cuda(), noisy.cuda(), t.cuda(), ctx.cuda(), chunk_frames=2,
                                          window_chunks=1).float().cpu()
     assert ((got - want).norm() / want.norm()) < 3e-2
+
+
+def test_causal_renderer_stream_equals_training_document_on_the_device():
+    """The chunk stream and the one-pass training document agree on a GPU too (bf16, this package's attention kernels
+    over concatenated key spans of uneven lengths), and both stay close to the CPU fp32 model."""
+    from solarwm_b200 import ops
+    from solarwm_b200.backends.minimax_h3.layout import patchify_latents
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.renderer.causal import CLEAN_LEVEL, CausalRenderer, ChunkKVCache, chunk_spans, teacher_forcing_prediction
+    from solarwm_b200.renderer.cli import _sample
+
+    cfg = h3_preset("tiny")
+    gpu = H3DiT(cfg, device="cuda", dtype=torch.bfloat16, seed=0)
+    cpu = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    gpu.load_state_dict({k: v for k, v in cpu.state_dict().items()})       # the seeded initialisation depends on the device
+    s = _sample(cfg, 3, frames=6, size=8)
+    C, F, H, W = s["shape"]
+    per = (H // 2) * (W // 2)
+    g = torch.Generator().manual_seed(9)
+    noisy = torch.randn(F * per, C * 4, generator=g)
+    t_chunks = torch.tensor([0.3, 0.5, 0.7])
+    before = ops.total_launches()
+    with torch.no_grad():
+        doc = teacher_forcing_prediction(gpu, s, noisy.cuda(), t_chunks, chunk=2, window=2).float().cpu()
+        ref = teacher_forcing_prediction(cpu, s, noisy, t_chunks, chunk=2, window=2)
+        r, cache = CausalRenderer(gpu, chunk=2, window=2, steps=2), ChunkKVCache(2)
+        prompt, anchor_rows = s["prompt_embeds"].cuda().bfloat16(), patchify_latents(s["anchor_latents"]).cuda().bfloat16()
+        s_rows, clean = patchify_latents(s["structure_latents"]).cuda().bfloat16(), patchify_latents(s["target_latents"]).cuda().bfloat16()
+        parts = []
+        for j, (a, b) in enumerate(chunk_spans(F, 2)):
+            kw = dict(prompt=prompt, anchor_rows=anchor_rows, structure_rows=s_rows[a * per:b * per], frames=(a, b), total_frames=F,
+                      grid_hw=(H // 2, W // 2), cameras=s["camera_w2c"])
+            parts.append(r._evaluate(cache, target_rows=noisy[a * per:b * per].cuda().bfloat16(), t=float(t_chunks[j]), commit=False, **kw).float().cpu())
+            r._evaluate(cache, target_rows=clean[a * per:b * per], t=CLEAN_LEVEL, commit=True, **kw)
+        stream = torch.cat(parts)
+        out = r.render(s, seed=1)
+    ops.check_status()
+    assert ops.total_launches() > before                              # the native kernels ran
+    scale = float(ref.abs().max())
+    assert float((stream - doc).abs().max()) < 4e-2 * scale           # same function, bf16 rounding apart
+    assert float((doc - ref).abs().max()) < 8e-2 * scale
+    assert out.shape == (C, F, H, W) and bool(torch.isfinite(out.float()).all())
+
+
+def test_memory_session_engine_on_the_device(tmp_path):
+    from solarwm_b200 import ops
+    from solarwm_b200.models.h3 import H3DiT, h3_preset
+    from solarwm_b200.serve.h3_stream import H3StreamConfig
+    from solarwm_b200.serve.memory_engine import MemorySessionEngine
+
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cuda", dtype=torch.bfloat16, seed=0)
+    scfg = H3StreamConfig(grid_hw=(4, 8), chunk_latents=5, window_chunks=2, denoise_steps=2, use_cuda_graph=False, memory_latents=2)
+    eng = MemorySessionEngine(model, scfg, run_dir=tmp_path, top_k=2)
+    eng.set_condition(text=torch.randn(16, cfg.text_dim), anchor_latent=torch.randn(24, 1, 8, 16), scene_id="gpu-scene")
+    eng.start(seed=3)
+    for j in range(5):
+        eng.advance_camera([["w"] if j < 3 else ["s"]] * (4 if j == 0 else 5))
+        chunk, ms = eng.generate()
+        assert chunk.is_cuda and chunk.shape == (24, 5, 8, 16) and bool(torch.isfinite(chunk.float()).all())
+    assert [len(r["memory_latent_indices"]) for r in eng.records] == [0, 0, 0, 2, 2]
+    assert eng.stop()["chunks"] == 5
+    ops.check_status()
