@@ -126,6 +126,7 @@ class LoRALinear(nn.Module):
             return F_.linear(x, self.weight)
         if not x.is_cuda:
             return (x.float() @ self.weight.float().t() + (x.float() @ a.float().t()) @ b.float().t()).to(x.dtype)
+        a, b = F_.pad_adapter_rank(a, b)
         return _LoRAFn.apply(x, self.weight, a, b)
 
     @torch.no_grad()

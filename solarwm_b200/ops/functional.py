@@ -236,6 +236,17 @@ class _LoRALinearFn(torch.autograd.Function):
         return dx, None, None, da, db, None
 
 
+def pad_adapter_rank(lora_a, lora_b):
+    """The GEMM kernels take inner and outer extents in multiples of 8.  The released rank (384) is one; a rank that is not
+    (small test models) is zero-padded for the call: zero rows of A times zero columns of B add nothing, the padding is a
+    differentiable view-and-copy, and its gradient slices fall away."""
+    r = lora_a.shape[0]
+    if r % 8 == 0:
+        return lora_a, lora_b
+    extra = 8 - r % 8
+    return torch.nn.functional.pad(lora_a, (0, 0, 0, extra)), torch.nn.functional.pad(lora_b, (0, extra))
+
+
 def lora_linear(x, w, b, lora_a, lora_b, scale: float = 1.0):
     """A frozen linear with a trainable low-rank update: ``lora_a`` [r, in], ``lora_b`` [out, r]."""
     if not x.is_cuda:
@@ -243,6 +254,7 @@ def lora_linear(x, w, b, lora_a, lora_b, scale: float = 1.0):
         if b is not None:
             y = y + b.float()
         return y.to(x.dtype)
+    lora_a, lora_b = pad_adapter_rank(lora_a, lora_b)
     return _LoRALinearFn.apply(x, w, b, lora_a, lora_b, float(scale))
 
 
