@@ -162,6 +162,8 @@ class MiniMaxH3Backend:
         inf = config.get("inference", {}) or {}
         if inf.get("length_policy") == "source":
             return self._infer_source_length(config)
+        if inf.get("cases") is not None or inf.get("case_conditions"):
+            return self._infer_cases(config)
         dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
         model, weights_id = self._inference_model(config, dev)
         cfg = model.cfg
@@ -235,6 +237,41 @@ class MiniMaxH3Backend:
         return {"output_dir": str(out_dir), "chunks": manifest.get("chunks"), "frames": manifest.get("frames"),
                 "video": manifest.get("video"), "weights_id": weights_id,
                 "native_launches": ops.total_launches()}
+
+    def _infer_cases(self, config):
+        """``inference.cases: N`` (seeded conditions) or ``inference.case_conditions`` (a ``.pt`` list of condition
+        mappings): N published cases through the shared inference engine, sampled the way the route's stage asks
+        (``inference.py``: bidirectional Euler for Stage0.5 weights, the few-step rollout for block-causal ones)."""
+        from ...engine.inference_engine import InferenceEngine
+        from ...serve.h3_stream import H3StreamConfig
+        from .inference import H3InferenceAdapter, build_cases
+
+        inf = config["inference"]
+        dev = "cuda" if torch.cuda.is_available() and config.get("runtime", {}).get("device") != "cpu" else "cpu"
+        model, weights_id = self._inference_model(config, dev)
+        cfg = model.cfg
+        gh, gw = (int(v) for v in inf.get("grid_hw", (4, 6)))
+        k = int(inf.get("chunk_latents", 5))
+        frames = int(inf.get("latent_frames", 2 * k))
+        if inf.get("case_conditions"):
+            conditions = torch.load(str(inf["case_conditions"]), map_location="cpu", weights_only=True)
+        else:
+            conditions = []
+            for i in range(int(inf["cases"])):
+                g = torch.Generator().manual_seed(int(inf.get("seed", 0)) * 1009 + i)
+                views = torch.eye(4).repeat(frames + 1, 1, 1)
+                views[:, 2, 3] = -torch.arange(frames + 1) * 0.05
+                conditions.append({"sample_id": f"synthetic-{i:04d}", "prompt_embeds": torch.randn(int(inf.get("prompt_len", 8)), cfg.text_dim, generator=g),
+                                   "anchor_latents": torch.randn(cfg.latent_row_dim // 4, 1, 2 * gh, 2 * gw, generator=g), "camera_w2c": views})
+        stage = str((config.get("train", {}) or {}).get("stage", "stage0p5"))
+        scfg = H3StreamConfig(grid_hw=(gh, gw), latent_channels=cfg.latent_row_dim // 4, chunk_latents=k,
+                              window_chunks=int(inf.get("window_chunks", 5)), denoise_steps=int(inf.get("denoise_steps", 4)),
+                              use_cuda_graph=dev == "cuda")
+        adapter = H3InferenceAdapter(model, conditions, stage=stage, steps=int(inf.get("steps", 8)), stream_cfg=scfg)
+        summary = InferenceEngine(adapter).run(build_cases(conditions, noise_seed=int(inf.get("seed", 0))), weights_id=weights_id,
+                                               output_dir=output_root(config) / str(inf.get("output_name", "generate")))
+        return {"output_dir": str(summary.output_dir), "cases": summary.cases, "ordered_manifest_digest": summary.ordered_manifest_digest,
+                "weights_id": weights_id, "native_launches": ops.total_launches()}
 
     def _infer_source_length(self, config):
         """``inference.length_policy: source``: every row of ``inference.plan`` is prepared once (cameras at the clip's
