@@ -123,3 +123,39 @@ def test_benchmark_pass_is_resumable_and_summary_ranks_methods(tmp_path, capsys)
     assert json.loads(capsys.readouterr().out)["ranking"][0]["method"] == "good"
     with pytest.raises(ValueError):
         compute(root, tmp_path / "renders" / "good", "good", out, metrics=("nonsense",))
+
+
+def test_render_pass_is_resumable_and_survives_a_failing_case(tmp_path):
+    import cv2
+
+    from solarwm_b200.eval.render_benchmark import render_cases, write_video
+    from solarwm_b200.eval.run_metrics import read_video
+
+    root = tmp_path / "bench"
+    rows = []
+    for i in range(3):
+        clip = _scene(seed=i)
+        _write(root / "media" / f"c{i}.mp4", clip)
+        cv2.imwrite(str(root / "media" / f"f{i}.png"), clip[0])
+        rows.append({"clip_id": f"clip{i}", "prompt": "p", "files": {"condition.mp4": f"media/c{i}.mp4", "first_frame.png": f"media/f{i}.png"},
+                     "ground_truth": f"media/c{i}.mp4", "condition": "edges"})
+    (root / "benchmark" / "heldout").mkdir(parents=True)
+    (root / "benchmark" / "heldout" / "cases.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    calls = []
+
+    def method(case):
+        calls.append(case.id)
+        if case.id == "clip1":
+            raise RuntimeError("out of memory")
+        return read_video(case.condition)[:, ::-1].copy()           # a "render": the structure video upside down
+
+    first = render_cases(root, tmp_path / "renders", method, split="heldout")
+    assert first["rendered"] == ["heldout/clip0", "heldout/clip2"] and first["failed"][0]["case"] == "heldout/clip1"
+    again = render_cases(root, tmp_path / "renders", method, split="heldout")
+    assert again["skipped"] == ["heldout/clip0", "heldout/clip2"] and calls.count("clip0") == 1 and calls.count("clip1") == 2
+    assert read_video(tmp_path / "renders" / "heldout" / "clip0.mp4").shape == (12, 64, 96, 3)
+    log = [json.loads(l) for l in (tmp_path / "renders" / "render-log-0000.jsonl").read_text().splitlines()]
+    assert sum("error" in e for e in log) == 2 and sum("seconds" in e for e in log) == 2
+    assert not list((tmp_path / "renders").rglob("*.tmp.mp4"))
+    with pytest.raises(ValueError):
+        write_video(tmp_path / "x.mp4", np.zeros((2, 4, 4), np.uint8))
