@@ -234,6 +234,11 @@ class H3TrainingRuntime:
             s = {"target_latents": lat[1:].permute(1, 0, 2, 3).contiguous(),
                  "anchor_latents": lat[:1].permute(1, 0, 2, 3).contiguous(), "prompt_embeds": enc["text"]}
             ident = str(row.sample_id)
+            if "camera_c2w" in enc:                 # absolute poses of the corpus -> world-to-camera relative to the anchor's camera
+                from ...renderer.data import views_from_c2w
+
+                s["camera_w2c"] = views_from_c2w(enc["camera_c2w"].float())
+                return ident, ordinal, s
         else:
             from ...data.synthetic import h3_sample
 

@@ -27,6 +27,15 @@ from ...preencode.shards import EncodedShardWriter
 from .contracts import PROFILES
 
 
+def _camera_of(blob: bytes, frame_indices, source_hw, target_hw):
+    """Absolute poses and normalised intrinsics of the latent frames out of a clip's camera archive."""
+    from ..minimax_h3.geometry import ResizeCrop, decode_camera
+
+    how = ResizeCrop(source_hw[1], source_hw[0], target_hw[1], target_hw[0], target_hw[1], target_hw[0])     # plain resize
+    c2w, K = decode_camera(blob, [int(i) for i in frame_indices], how, focal_guard=False)
+    return torch.from_numpy(c2w), torch.from_numpy(K)
+
+
 def _clips(config: Mapping[str, Any], rank: int, world: int) -> Iterator[Tuple[str, torch.Tensor, str]]:
     pre = config["preencode"]
     data = config["data"]
@@ -35,7 +44,14 @@ def _clips(config: Mapping[str, Any], rank: int, world: int) -> Iterator[Tuple[s
         n = int(pre.get("num_samples", 4))
         for i in range(rank, n, world):
             g = torch.Generator().manual_seed(int(data.get("seed", 0)) * 7919 + i)
-            yield f"synthetic-{i:06d}", torch.rand(3, T, H, W, generator=g) * 2 - 1, f"synthetic clip {i}"
+            clip = torch.rand(3, T, H, W, generator=g) * 2 - 1
+            if pre.get("cameras"):                  # a seeded dolly so that camera-conditioned paths have something to read
+                c2w = torch.eye(4).repeat(T, 1, 1)
+                c2w[:, 2, 3] = torch.arange(T) * 0.01 * (1 + i)
+                K = torch.tensor([[0.505, 0.0, 0.5], [0.0, 0.898, 0.5], [0.0, 0.0, 1.0]]).repeat(T, 1, 1)
+                yield f"synthetic-{i:06d}", clip, f"synthetic clip {i}", (c2w, K)
+            else:
+                yield f"synthetic-{i:06d}", clip, f"synthetic clip {i}"
         return
     from ...data.archive import TarShardReader
 
@@ -54,7 +70,14 @@ def _clips(config: Mapping[str, Any], rank: int, world: int) -> Iterator[Tuple[s
             if clip.shape[2:] != (H, W):
                 clip = torch.nn.functional.interpolate(clip.permute(1, 0, 2, 3), size=(H, W), mode="bilinear",
                                                        align_corners=False).permute(1, 0, 2, 3)
-            yield row.sample_id, clip, got[members["caption"]].decode("utf-8").strip()
+            caption = got[members["caption"]].decode("utf-8").strip()
+            if pre.get("cameras"):
+                if "camera" not in members:
+                    raise BackendContractError(f"{row.sample_id}: preencode.cameras is on and the sample has no camera member")
+                blob = reader.read_members(root / row.shard, [members["camera"]])[members["camera"]]
+                yield row.sample_id, clip, caption, _camera_of(blob, range(T), vid.shape[1:3], (H, W))
+            else:
+                yield row.sample_id, clip, caption
     finally:
         reader.close()
 
@@ -106,17 +129,21 @@ def run_preencode(config: Mapping[str, Any], family: str, *, latent_channels: in
                             width=int(data["pixel_width"]), z_dim=vcfg.z_dim, text_len=tcfg.text_len,
                             text_dim=tcfg.dim, temporal_stride=t_stride, spatial_stride=s_stride,
                             video_codec=str(codecs.get("video_codec", "causal-vae-random-init")),
-                            text_codec=str(codecs.get("text_codec", "t5-random-init")))
+                            text_codec=str(codecs.get("text_codec", "t5-random-init")), cameras=bool(pre.get("cameras")))
     out = Path(pre["output_root"])
     writer = EncodedShardWriter(out, contract, samples_per_shard=int(pre.get("samples_per_shard", 64)),
                                 prefix=f"encoded-r{rank:03d}")
     error = None
     try:
-        for sample_id, clip, caption in _clips(config, rank, world):
+        for sample_id, clip, caption, *camera in _clips(config, rank, world):
             with torch.no_grad():
                 z = vae.encode(clip.unsqueeze(0).to(device))[0].permute(1, 0, 2, 3)      # [F, z, h, w]
                 e = text([caption])[0]
-            writer.add(sample_id, {"latents": z.to(dtype).cpu(), "text": e.to(dtype).cpu()}, {"caption": caption})
+            tensors = {"latents": z.to(dtype).cpu(), "text": e.to(dtype).cpu()}
+            if camera:                              # per pixel frame -> the frame each latent starts at
+                at = torch.arange(z.shape[0]) * t_stride
+                tensors["camera_c2w"], tensors["camera_K"] = camera[0][0][at].float(), camera[0][1][at].float()
+            writer.add(sample_id, tensors, {"caption": caption})
         index = writer.finish(index_name=f"index-r{rank:03d}.jsonl") if writer.rows or writer._pending else None
     except Exception as exc:  # noqa: BLE001 - exchanged so that every rank fails together
         error, index = exc, None

@@ -153,7 +153,7 @@ def online_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) -> 
                                       "num_samples": int(data.get("num_samples", 8))})
     while True:
         group = []
-        for sample_id, clip, caption in _clips(source, dp_rank, dp_size):
+        for sample_id, clip, caption, *_ in _clips(source, dp_rank, dp_size):
             with torch.no_grad():
                 z = codec.encode(clip.permute(1, 0, 2, 3).unsqueeze(0).to(device))[0]                 # [F, z, h, w]
                 e = text_encoder([caption])[0]

@@ -122,9 +122,13 @@ def validate_encoded_tensors(contract: EncoderContract, tensors: Mapping[str, An
 def wan_contract(family: str, *, pixel_frames: int, height: int, width: int, z_dim: int, text_len: int,
                  text_dim: int, temporal_stride: int = 4, spatial_stride: int = 16,
                  video_codec: str = "wan2.2-vae", text_codec: str = "umt5-xxl",
-                 dtype: str = "bfloat16", extras: Optional[Mapping[str, Any]] = None) -> EncoderContract:
+                 dtype: str = "bfloat16", extras: Optional[Mapping[str, Any]] = None, cameras: bool = False) -> EncoderContract:
+    """``cameras``: every sample also carries the absolute camera-to-world pose and the normalised intrinsics of each
+    latent frame (``camera_c2w`` [F, 4, 4], ``camera_K`` [F, 3, 3], fp32)."""
     f = (pixel_frames - 1) // temporal_stride + 1
-    return EncoderContract(family, video_codec, text_codec, pixel_frames, height, width, temporal_stride,
-                           spatial_stride,
-                           (TensorSpec("latents", dtype, (f, z_dim, height // spatial_stride, width // spatial_stride)),
-                            TensorSpec("text", dtype, (text_len, text_dim))), dict(extras or {}))
+    tensors = (TensorSpec("latents", dtype, (f, z_dim, height // spatial_stride, width // spatial_stride)),
+               TensorSpec("text", dtype, (text_len, text_dim)))
+    if cameras:
+        tensors += (TensorSpec("camera_c2w", "float32", (f, 4, 4)), TensorSpec("camera_K", "float32", (f, 3, 3)))
+    return EncoderContract(family, video_codec, text_codec, pixel_frames, height, width, temporal_stride, spatial_stride, tensors,
+                           dict(extras or {}))

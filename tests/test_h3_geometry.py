@@ -91,3 +91,35 @@ def test_camera_archives_in_their_several_forms():
                 _archive(c2w=np.full_like(c2w, np.nan)), _archive(c2w=c2w[:, :3])):
         with pytest.raises(DataContractError):
             decode_camera(bad, [0, 3], how)
+
+
+def test_cameras_travel_from_the_preencoder_to_the_training_sample(tmp_path):
+    import torch
+
+    from solarwm_b200.backends.minimax_h3.runtime import H3TrainingRuntime
+    from solarwm_b200.registry import load_backend
+
+    be = load_backend("minimax_h3")
+    pre = {"data": {"pixel_frames": 9, "pixel_height": 64, "pixel_width": 64, "seed": 1}, "runtime": {"device": "cpu"},
+           "preencode": {"source": "synthetic", "num_samples": 2, "cameras": True, "output_root": str(tmp_path / "enc"),
+                         "codecs": {"vae_base": 4, "t5": {"vocab": 512, "dim": 64, "dim_attn": 32, "dim_ffn": 64, "num_heads": 2,
+                                                         "num_layers": 1, "text_len": 8}}}}
+    assert be.preencode(pre)["samples"] == 2
+    import json
+
+    contract = json.loads((tmp_path / "enc" / "encoder-contract.json").read_text())
+    assert {t["name"] for t in contract["tensors"]} == {"latents", "text", "camera_c2w", "camera_K"}
+    config = {"schema": "solarwm.run.v1", "action": "train",
+              "model": {"family": "minimax_h3", "architecture": "tiny", "adapter": {"rank": 4}, "camera_translation_transform": "logd4"},
+              "data": {"source": "index", "index": str(tmp_path / "enc" / "index.jsonl"), "seed": 0, "pixel_frames": 158},
+              "train": {"stage": "stage0p5", "causal_mode": "bidirectional", "objective": "flow_matching", "max_steps": 1, "optimizer": {"lr": 1e-3}},
+              "runtime": {"device": "cpu", "output_dir": str(tmp_path / "run")}}
+    rt = H3TrainingRuntime(config, model_config=be._cfg(config))
+    try:
+        _, _, sample = rt._next_sample()
+        views = sample["camera_w2c"]
+        assert views.shape == (3, 4, 4) and torch.equal(views[0], torch.eye(4))
+        assert float(views[1:, 2, 3].abs().min()) > 0                  # the dolly of the corpus, relative to the anchor's camera
+        rt.train_microbatch(0, 1)
+    finally:
+        rt.close()
