@@ -39,6 +39,11 @@ def synthetic_batches(config, arch, device) -> Iterator[dict]:
         txt = torch.randn(micro, arch.text_len, arch.text_dim, generator=g).to(dtype)
         batch = {"latents": lat, "text": txt, "sample_ids": [f"synthetic-{step}-{i}" for i in range(micro)],
                  "start_frames": [0] * micro}
+        if data.get("cameras"):                     # a seeded dolly per clip for the camera-conditioned routes
+            c2w = torch.eye(4).repeat(micro, frames, 1, 1)
+            c2w[:, :, 2, 3] = torch.arange(frames) * 0.05 * (1.0 + torch.rand(micro, 1, generator=g))
+            batch["camera_c2w"] = c2w
+            batch["camera_K"] = torch.tensor([[0.505, 0.0, 0.5], [0.0, 0.898, 0.5], [0.0, 0.0, 1.0]]).repeat(micro, frames, 1, 1)
         if arch.in_dim > ch:
             batch["y"] = torch.randn(micro, frames, arch.in_dim - ch, h, w, generator=g).to(dtype)
         if device.type == "cuda":
@@ -104,9 +109,28 @@ def encoded_batches(config, arch, device, dp_rank: int = 0, dp_size: int = 1) ->
         batch = {"latents": torch.stack([smp["latents"][:frames] for _, smp in group]).to(dtype),
                  "text": torch.stack([smp["text"] for _, smp in group]).to(dtype),
                  "sample_ids": [r.sample_id for r, _ in group], "start_frames": [0] * micro}
+        if all("camera_c2w" in smp for _, smp in group):
+            batch["camera_c2w"] = torch.stack([smp["camera_c2w"][:frames].float() for _, smp in group])
+            batch["camera_K"] = torch.stack([smp["camera_K"][:frames].float() for _, smp in group])
         if device.type == "cuda":
             batch = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in batch.items()}
         yield batch
+
+
+def camera_condition(batch: Mapping[str, Any], arch, transform: str, device):
+    """The ``y_camera`` argument of the camera-conditioned models out of a batch's absolute poses: world-to-camera
+    matrices relative to each clip's first camera, the normalised intrinsics, the translation compression.  ``None`` when
+    the architecture has no camera path or the batch carries no cameras."""
+    if getattr(arch, "camera_attention_mode", "none") == "none" or "camera_c2w" not in batch:
+        return None
+    c2w = batch["camera_c2w"].to(device=device, dtype=torch.float64)
+    if c2w.dim() != 4 or tuple(c2w.shape[-2:]) != (4, 4) or not bool(torch.isfinite(c2w).all()):
+        raise BackendContractError("camera_c2w must be finite [B, F, 4, 4]")
+    rel = torch.linalg.inv(c2w[:, :1]) @ c2w
+    rel[:, 0] = torch.eye(4, dtype=torch.float64, device=device)
+    Ks = batch.get("camera_K")
+    return {"viewmats": torch.linalg.inv(rel).float(), "Ks": None if Ks is None else Ks.to(device=device, dtype=torch.float32),
+            "transform": str(transform)}
 
 
 def build_online_codecs(config: Mapping[str, Any], device):
@@ -342,6 +366,9 @@ class WanStage0p5Runtime:
         self.batches_consumed += 1
         dev = self.ctx.device
         seed_digest = hashlib.blake2s(self.trainer.gen.get_state().cpu().numpy().tobytes()).hexdigest()
+        self.trainer.y_camera = camera_condition(batch, self.arch, str(self.config["model"].get("camera_translation_transform", "linear")), dev)
+        if self._graphed and self.trainer.y_camera is not None:
+            raise BackendContractError("camera-conditioned steps are not captured as a graph: set train.cuda_graph: false")
         if self._graphed:
             # ``train.cuda_graph``: the WHOLE optimizer step (this microbatch, the reduce-scatter, clipping and the
             # sharded AdamW with its device-side skip on a non-finite norm) is one replayed graph; the two optimizer

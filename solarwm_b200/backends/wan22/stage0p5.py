@@ -133,7 +133,7 @@ class WanStage0p5Trainer:
         x_in = x_t.view(B, F, *latents.shape[2:]).permute(0, 2, 1, 3, 4)
         y_in = None if y is None else y.permute(0, 2, 1, 3, 4)
         with span("forward"):
-            pred = self.model(x_in, t, text, y=y_in)                       # [B, C, F, H, W]
+            pred = self.model(x_in, t, text, y=y_in, y_camera=getattr(self, "y_camera", None))      # [B, C, F, H, W]
             pred = pred.permute(0, 2, 1, 3, 4).reshape(B * F, *pred.shape[1:2], *pred.shape[3:]).contiguous()
             weight = self.scheduler.training_weight(t_video).view(B, 1).expand(B, F).reshape(B * F)
             loss = ops.weighted_masked_mse(pred, target[:, :pred.shape[1]], weight.float(),

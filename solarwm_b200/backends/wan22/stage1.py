@@ -62,7 +62,7 @@ class WanStage1Trainer(WanStage0p5Trainer):
             pred = forward_noisy_suffix(self.model, x_t.permute(0, 2, 1, 3, 4), t, text, captured, **kw)
         else:
             pred = forward_teacher_forcing(self.model, clean.permute(0, 2, 1, 3, 4), x_t.permute(0, 2, 1, 3, 4), t, text,
-                                           capture=capture, **kw)
+                                           capture=capture, y_camera=getattr(self, "y_camera", None), **kw)
         return pred.permute(0, 2, 1, 3, 4)                      # [1, F, C, H, W]
 
     def microbatch(self, latents: torch.Tensor, text: torch.Tensor, y: Optional[torch.Tensor] = None):
@@ -111,7 +111,8 @@ class WanStage1Trainer(WanStage0p5Trainer):
             self.sp.broadcast_(flag)
             probes = bool(flag.item())
         # the clean half is the same in the trainable evaluation and in both probes: its keys / values are kept
-        prefix = [] if (probes and o.reuse_prefix) else None
+        # (the suffix evaluation carries no cameras, so camera-conditioned steps evaluate the probes in full)
+        prefix = [] if (probes and o.reuse_prefix and getattr(self, "y_camera", None) is None) else None
         u = self._predict(latents, x_t, t, text, r=r, capture=prefix)
         # central difference along the interpolation path x(t') = (1 - s') x0 + s' n, s' = t' / N
         tp_c, tm_c = af.difference_window(t_c, r_c, epsilon=o.difference_epsilon, num_train_timesteps=N)

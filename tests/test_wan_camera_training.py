@@ -1,0 +1,63 @@
+"""Cameras reach the Wan trainers: batch poses -> relative world-to-camera condition -> the camera path of the model."""
+from pathlib import Path
+
+import pytest
+import torch
+import yaml
+
+from solarwm_b200.backends.wan22.runtime import camera_condition, synthetic_batches
+from solarwm_b200.errors import BackendContractError
+from solarwm_b200.models.wan import wan_preset
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_camera_condition_is_relative_to_the_first_camera():
+    arch = wan_preset("tiny")
+    c2w = torch.eye(4).repeat(2, 3, 1, 1)
+    c2w[0, :, 0, 3] = torch.tensor([5.0, 6.0, 8.0])
+    c2w[1, :, 2, 3] = torch.tensor([1.0, 1.5, 2.5])
+    batch = {"camera_c2w": c2w, "camera_K": torch.eye(3).repeat(2, 3, 1, 1)}
+    assert camera_condition(batch, arch, "linear", torch.device("cpu")) is None          # no camera path in this architecture
+    arch.camera_attention_mode = "fused_prope"
+    y = camera_condition(batch, arch, "logd4", torch.device("cpu"))
+    assert y["transform"] == "logd4" and y["viewmats"].shape == (2, 3, 4, 4) and y["Ks"].shape == (2, 3, 3, 3)
+    assert torch.equal(y["viewmats"][:, 0], torch.eye(4).repeat(2, 1, 1))
+    assert torch.allclose(y["viewmats"][0, :, 0, 3], torch.tensor([0.0, -1.0, -3.0])) and torch.allclose(y["viewmats"][1, 2, 2, 3], torch.tensor(-1.5))
+    assert camera_condition({"latents": c2w}, arch, "linear", torch.device("cpu")) is None
+    with pytest.raises(BackendContractError):
+        camera_condition({"camera_c2w": c2w[0]}, arch, "linear", torch.device("cpu"))
+
+
+@pytest.mark.parametrize("name", ["tiny_stage0p5_cpu.yaml", "tiny_stage1_anyflow_cpu.yaml"])
+def test_camera_conditioned_training_steps(tmp_path, name):
+    from solarwm_b200.registry import load_backend
+
+    cfg = yaml.safe_load((ROOT / "configs" / "wan22_ti2v_5b" / name).read_text())
+    cfg["runtime"].update(output_dir=str(tmp_path / "run"), device="cpu", save_every=0)
+    cfg["train"]["max_steps"] = 2
+    cfg["model"]["camera_attention_mode"] = "parallel"
+    cfg["data"]["cameras"] = True
+    from solarwm_b200.backends.wan22.contracts import architecture
+
+    batch = next(synthetic_batches(cfg, architecture(cfg), torch.device("cpu")))
+    assert batch["camera_c2w"].shape[:2] == batch["latents"].shape[:2] and float(batch["camera_c2w"][0, -1, 2, 3]) > 0
+    out = load_backend("wan22_ti2v_5b").train(cfg)
+    assert out["final_step"] == 2
+    if name != "tiny_stage0p5_cpu.yaml":
+        return
+    # the condition really reaches the model: the trainer holds it after the step, and the architecture has the camera branch
+    from solarwm_b200.backends.wan22.runtime import WanStage0p5Runtime
+
+    rt = WanStage0p5Runtime(dict(cfg, runtime=dict(cfg["runtime"], output_dir=str(tmp_path / "probe"))))
+    try:
+        assert [n for n, _ in rt.trainer.model.named_parameters() if "cam" in n], "the parallel camera branch has parameters"
+        rt.train_microbatch(0, 1)
+        assert rt.trainer.y_camera is not None and rt.trainer.y_camera["viewmats"].shape[1] == batch["latents"].shape[1]
+        seen = {}
+        held = rt.trainer.model.forward
+        rt.trainer.model.forward = lambda *a, **k: (seen.update(k), held(*a, **k))[1]
+        rt.train_microbatch(1, 1)
+        assert seen.get("y_camera") is rt.trainer.y_camera
+    finally:
+        rt.close()
