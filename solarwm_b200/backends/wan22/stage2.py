@@ -142,17 +142,25 @@ class WanStage2Trainer:
         cache = self.rollout_cache((H // ph, W // pw))
         runner.encode_text(cache, text)
         outs = []
+        cam_all = getattr(self, "y_camera", None)      # set per batch by ``train_outer_step``: every chunk carries its cameras
+
+        def cams(a, b):
+            if cam_all is None:
+                return {}
+            return {"y_camera": {"viewmats": cam_all["viewmats"][:, a:b], "Ks": None if cam_all["Ks"] is None else cam_all["Ks"][:, a:b],
+                                 "transform": cam_all["transform"]}}
+
         for f0 in range(0, F, o.chunk_frames):
             f = min(o.chunk_frames, F - f0)
             x = self._randn((1, f, C, H, W), dtype)
             x0 = x
             for si, t in enumerate(steps):
                 tt = torch.full((1, f), float(t), device=self.device)
-                v = runner.forward_chunk(cache, _to_bcfhw(x), tt, commit=False)
+                v = runner.forward_chunk(cache, _to_bcfhw(x), tt, commit=False, **cams(f0, f0 + f))
                 x0 = self._x0(x, _to_bcfhw(v), tt[0])
                 if si + 1 < len(steps):
                     x = self._add_noise(x0, self._randn(x0.shape, dtype), torch.full((f,), float(steps[si + 1])))
-            runner.forward_chunk(cache, _to_bcfhw(x0), torch.zeros((1, f), device=self.device), commit=True)
+            runner.forward_chunk(cache, _to_bcfhw(x0), torch.zeros((1, f), device=self.device), commit=True, **cams(f0, f0 + f))
             outs.append(x0)
         return torch.cat(outs, dim=1), float(steps[exit_index]), exit_index
 
@@ -165,7 +173,7 @@ class WanStage2Trainer:
         noisy = self._add_noise(generated, self._randn(generated.shape, generated.dtype), t)
         v = forward_teacher_forcing(self.student, _to_bcfhw(generated), _to_bcfhw(noisy), t.view(1, F), text,
                                     chunk_frames=o.chunk_frames, window_chunks=o.window_chunks,
-                                    sink_frames=o.sink_frames)
+                                    sink_frames=o.sink_frames, y_camera=getattr(self, "y_camera", None))
         v = _to_bcfhw(v)
         sig = self._sigma(t).view(1, F, 1, 1, 1)
         return (noisy.float() - sig * v.float())
@@ -173,9 +181,10 @@ class WanStage2Trainer:
     def _score_x0(self, model, x_t, t_frames, text, null_text=None, scale: float = 1.0):
         F = x_t.shape[1]
         tt = t_frames.view(1, F)
-        v = model(_to_bcfhw(x_t), tt, text)
+        cam = getattr(self, "y_camera", None)          # the scores see the same trajectory the student rolled out along
+        v = model(_to_bcfhw(x_t), tt, text, y_camera=cam)
         if null_text is not None and scale != 1.0:
-            vu = model(_to_bcfhw(x_t), tt, null_text)
+            vu = model(_to_bcfhw(x_t), tt, null_text, y_camera=cam)
             v = vu + scale * (v - vu)
         sig = self._sigma(t_frames).view(1, F, 1, 1, 1)
         return x_t.float() - sig * _to_bcfhw(v).float()
@@ -204,6 +213,9 @@ class WanStage2Trainer:
         dev = self.device
         lat = batch["latents"].to(dev, non_blocking=True)
         text = batch["text"].to(dev, non_blocking=True)
+        from .runtime import camera_condition
+
+        self.y_camera = camera_condition(batch, self.cfg, getattr(self, "camera_transform", "linear"), dev)
         null = batch.get("null_text")
         null = torch.zeros_like(text) if null is None else null.to(dev, non_blocking=True)
         F = lat.shape[1]
@@ -352,6 +364,7 @@ def run_stage2_training(config: Mapping[str, Any]) -> Mapping[str, Any]:
         dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
         trainer = WanStage2Trainer(arch, ctx.device, opts, sp=ctx.sp, dtype=dtype)
         trainer.dp_group, trainer.dp_size = ctx.dp_group, topo.dp_size
+        trainer.camera_transform = str(config["model"].get("camera_translation_transform", "linear"))
         # replicas draw different noise; SP peers of one replica must draw the same
         trainer.gen.manual_seed(opts.seed * 100003 + 7 + 7919 * topo.dp_rank)
         receipts = {}

@@ -61,3 +61,17 @@ def test_camera_conditioned_training_steps(tmp_path, name):
         assert seen.get("y_camera") is rt.trainer.y_camera
     finally:
         rt.close()
+
+
+def test_stage2_rolls_out_replays_and_scores_along_the_batch_cameras(tmp_path):
+    from solarwm_b200.backends.wan22.stage2 import run_stage2_training
+
+    cfg = yaml.safe_load((ROOT / "configs" / "wan22_ti2v_5b" / "tiny_stage2_sgf_cpu.yaml").read_text())
+    cfg["runtime"].update(output_dir=str(tmp_path / "plain"), device="cpu")
+    cfg["train"]["max_steps"] = 3
+    plain = run_stage2_training(cfg)
+    cam = {**cfg, "model": {**cfg["model"], "camera_attention_mode": "parallel"}, "data": {**cfg["data"], "cameras": True},
+           "runtime": {**cfg["runtime"], "output_dir": str(tmp_path / "cam")}}
+    with_cam = run_stage2_training(cam)
+    assert with_cam["final_step"] == 3 and all(v == v for v in with_cam["losses"].values())
+    assert set(with_cam["losses"]) == set(plain["losses"])
