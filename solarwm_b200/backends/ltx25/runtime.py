@@ -111,10 +111,29 @@ class LTXTrainingRuntime:
             row, enc = next(self._corpus)
             if enc["latents"].shape[1] != self.arch.in_dim or tuple(enc["text"].shape) != (self.arch.text_len, self.arch.text_dim):
                 raise BackendContractError(f"{row.sample_id}: latents / text do not match the architecture")
+            self._cameras = enc["camera_c2w"].float().unsqueeze(0) if "camera_c2w" in enc else None
             return str(row.sample_id), ordinal, enc["latents"].permute(1, 0, 2, 3).unsqueeze(0).float(), enc["text"].unsqueeze(0).float()
         g = torch.Generator().manual_seed(self.seed * 100003 + ordinal)
-        return (f"synthetic-{ordinal:08d}", ordinal, torch.randn(self._shape, generator=g),
-                torch.randn(1, self.arch.text_len, self.arch.text_dim, generator=g))
+        lat, txt = torch.randn(self._shape, generator=g), torch.randn(1, self.arch.text_len, self.arch.text_dim, generator=g)
+        self._cameras = None
+        if self.config["data"].get("cameras"):      # a seeded dolly for the camera-conditioned recipe
+            frames = self._shape[2]
+            c2w = torch.eye(4).repeat(1, frames, 1, 1)
+            c2w[0, :, 2, 3] = torch.arange(frames) * 0.05 * (1.0 + float(torch.rand(1, generator=g)))
+            self._cameras = c2w
+        return f"synthetic-{ordinal:08d}", ordinal, lat, txt
+
+    def _camera_condition(self):
+        """Parameter-free PRoPE with the family's fixed intrinsics over world-to-camera matrices relative to the clip's
+        first camera; ``None`` when the sample carries no cameras."""
+        if getattr(self, "_cameras", None) is None:
+            return None
+        from ...models.ltx import ltx_camera_condition
+
+        c2w = self._cameras.to(self.device, torch.float64)
+        rel = torch.linalg.inv(c2w[:, :1]) @ c2w
+        rel[:, 0] = torch.eye(4, dtype=torch.float64, device=self.device)
+        return ltx_camera_condition(torch.linalg.inv(rel).float(), str(self.config["model"].get("camera_translation_transform", "linear")))
 
     def train_microbatch(self, micro_index: int, grad_accum: int) -> MicrobatchResult:
         ident, ordinal, latents, text = self._next_sample()
@@ -126,7 +145,7 @@ class LTXTrainingRuntime:
         if sp is not None and sp.size > 1:
             sp.broadcast_(sigma, noise)
         x_t, target, per_frame = noisy_input_and_target(lat, noise, sigma)
-        loss = masked_flow_loss(core.model(x_t, per_frame * 1000.0, text.to(self.device)), target)
+        loss = masked_flow_loss(core.model(x_t, per_frame * 1000.0, text.to(self.device), y_camera=self._camera_condition()), target)
         (loss / (grad_accum * (1 if sp is None else sp.size))).backward()
         value = float(loss.detach())
         if not math.isfinite(value):

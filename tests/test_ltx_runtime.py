@@ -118,3 +118,20 @@ def test_inference_samples_with_trained_adapters_live_or_averaged(tmp_path):
     assert not torch.equal(got["live"], got["ema"]) and got["live"].shape == got["ema"].shape
     with pytest.raises(BackendContractError):
         adapter_weights(out["checkpoint"], "other")
+
+
+def test_cameras_condition_the_adapter_training_step(tmp_path):
+    from solarwm_b200.backends.ltx25.runtime import LTXTrainingRuntime
+
+    losses = {}
+    for name, data in (("plain", {}), ("cameras", {"cameras": True})):
+        rt = LTXTrainingRuntime(_config(tmp_path / name, data=data))
+        try:
+            losses[name] = rt.train_microbatch(0, 1).losses["loss"]
+            cond = rt._camera_condition()
+            assert (cond is None) == (name == "plain")
+            if cond is not None:
+                assert cond["viewmats"].shape == (1, 2, 4, 4) and torch.equal(cond["viewmats"][0, 0], torch.eye(4)) and cond["Ks"].shape == (1, 2, 3, 3)
+        finally:
+            rt.close()
+    assert losses["plain"] != losses["cameras"]                       # same sample and noise, another attention geometry
