@@ -18,7 +18,7 @@ from ...runtime.output_layout import output_root, public_validation_dir
 from ...runtime.randomness import stable_validation_seed
 
 
-def _velocity(model, x, timestep: float, text, anchor):
+def _velocity(model, x, timestep: float, text, anchor, y_camera=None):
     """One network evaluation at a uniform noise level; with an anchor, frame 0 is clean (timestep 0, the given
     latent) and its velocity is dropped."""
     frames = x.shape[1]
@@ -26,7 +26,7 @@ def _velocity(model, x, timestep: float, text, anchor):
     if anchor is not None:
         x[:, 0] = anchor
         t[:, 0] = 0.0
-    v = model(x.permute(0, 2, 1, 3, 4), t, text).permute(0, 2, 1, 3, 4).contiguous()
+    v = model(x.permute(0, 2, 1, 3, 4), t, text, y_camera=y_camera).permute(0, 2, 1, 3, 4).contiguous()
     if anchor is not None:
         v[:, 0] = 0
     return v
@@ -34,10 +34,11 @@ def _velocity(model, x, timestep: float, text, anchor):
 
 @torch.no_grad()
 def sample_bidirectional(model, text, *, frames, height, width, steps=50, shift=5.0, seed=0, first_frame=None,
-                         solver="unipc"):
+                         solver="unipc", y_camera=None):
     """Denoise ``[1, frames, C, height, width]`` latents from seeded noise.  ``solver`` is ``"unipc"`` (the second-order
     multistep predictor-corrector on the pinned shifted grid, the validation default at 50 steps) or ``"euler"``
-    (first-order flow steps through the fused update kernel).  ``first_frame`` anchors latent frame 0 (text+image
+    (first-order flow steps through the fused update kernel).  ``y_camera`` conditions every evaluation on a camera path.
+    ``first_frame`` anchors latent frame 0 (text+image
     conditioning of the 5B family): it enters every evaluation clean and is restored after every step (reference:
     CudaWanGenerationAdapter._bidirectional, solar/backends/wan22/runtime/inference.py:1647-1712)."""
     dev = next(model.parameters()).device
@@ -50,7 +51,7 @@ def sample_bidirectional(model, text, *, frames, height, width, steps=50, shift=
 
         unipc = FlowUniPC(int(steps), float(shift))
         for i in range(int(steps)):
-            v = _velocity(model, x, float(unipc.timesteps[i]), text, anchor)
+            v = _velocity(model, x, float(unipc.timesteps[i]), text, anchor, y_camera)
             x = unipc.step(v.float(), x.float()).to(model.dtype)
         sigmas = [float(s) for s in unipc.sigmas.tolist()]
     elif solver == "euler":
@@ -58,7 +59,7 @@ def sample_bidirectional(model, text, *, frames, height, width, steps=50, shift=
         sched.set_timesteps(steps)
         sig = torch.cat([sched.sigmas, torch.zeros(1)]).to(dev)
         for i in range(steps):
-            v = _velocity(model, x, float(sig[i]) * 1000.0, text, anchor)
+            v = _velocity(model, x, float(sig[i]) * 1000.0, text, anchor, y_camera)
             s, s_next = sig[i].expand(frames).clone(), sig[i + 1].expand(frames).clone()
             x = ops.euler_step(x.reshape(frames, -1), v.reshape(frames, -1), s.float(), s_next.float()).view_as(x)
         sigmas = [float(s) for s in sig.tolist()]
@@ -333,11 +334,22 @@ class WanLatentAdapter:
             lat, sigmas, extra = self._rollout(case, text, frames, h, w, first, dev)
             solver = "few-step-rollout"
         else:
+            y_camera, extra = None, {}
+            if inf.get("cameras"):
+                doc = torch.load(str(inf["cameras"]), map_location="cpu", weights_only=True)
+                views = doc["viewmats"]
+                views = views[case.slot] if views.dim() == 4 else views
+                if tuple(views.shape) != (frames, 4, 4):
+                    raise BackendContractError(f"inference.cameras holds {tuple(views.shape)} for {frames} latent frames")
+                Ks = doc.get("Ks")
+                Ks = None if Ks is None else (Ks[case.slot] if Ks.dim() == 4 else Ks)
+                y_camera = {"viewmats": views.unsqueeze(0).to(dev), "Ks": None if Ks is None else Ks.unsqueeze(0).to(dev),
+                            "transform": str(self.config["model"].get("camera_translation_transform", "linear"))}
+                extra = {"camera_frames": int(frames)}
             lat, sigmas = sample_bidirectional(
                 self.model, text, frames=frames, height=h, width=w, steps=int(inf.get("steps", 50)),
                 shift=float(self.config["model"].get("timestep_shift", 5.0)), seed=case.noise_seed, solver=solver,
-                first_frame=first)
-            extra = {}
+                first_frame=first, y_camera=y_camera)
         buf = io.BytesIO()
         torch.save(lat.float().cpu(), buf)
         artifacts = {"latents.pt": buf.getvalue(), "schedule.json": json.dumps({"sigmas": sigmas}).encode()}

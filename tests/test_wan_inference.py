@@ -166,3 +166,21 @@ def test_causal_routes_are_sampled_by_chunked_rollout_with_optional_cameras(tmp_
     cam = WanLatentAdapter("wan22_ti2v_5b", model, {**base, "inference": {**base["inference"], "cameras": str(tmp_path / "cams.pt")}})
     got = cam.generate(_case(0), weights_id="w")
     assert got.shape[1] == 7 and got.provenance["camera_frames"] == 7
+
+
+def test_bidirectional_sampling_follows_a_camera_path(tmp_path):
+    from solarwm_b200.backends.wan22.inference import WanLatentAdapter
+
+    model, cfg = _tiny()
+    base = {"model": {"family": "wan22_ti2v_5b", "timestep_shift": 3.0}, "train": {"stage": "stage0p5", "causal_mode": "bidirectional"},
+            "inference": {"latent_frames": 3, "latent_height": 4, "latent_width": 4, "steps": 2}}
+    plain = WanLatentAdapter("wan22_ti2v_5b", model, base).generate(_case(0), weights_id="w")
+    views = torch.eye(4).repeat(3, 1, 1)
+    views[:, 0, 3] = -torch.arange(3) * 0.3
+    torch.save({"viewmats": views}, tmp_path / "cams.pt")
+    cam_cfg = {**base, "inference": {**base["inference"], "cameras": str(tmp_path / "cams.pt")}}
+    moved = WanLatentAdapter("wan22_ti2v_5b", model, cam_cfg).generate(_case(0), weights_id="w")
+    assert moved.provenance["camera_frames"] == 3 and moved.artifacts["latents.pt"] != plain.artifacts["latents.pt"]
+    torch.save({"viewmats": views[:2]}, tmp_path / "short.pt")
+    with pytest.raises(BackendContractError):
+        WanLatentAdapter("wan22_ti2v_5b", model, {**base, "inference": {**base["inference"], "cameras": str(tmp_path / "short.pt")}}).generate(_case(0), weights_id="w")
