@@ -111,3 +111,54 @@ class RetrievalCameras:
 
     def select(self, chunk_index: int, **kw):
         return select_memory(np.stack(self.c2w), np.stack(self.K), chunk_index, **kw)
+
+
+def adapter_digest(state) -> str:
+    """sha256 over names and bytes of an adapter state, in name order."""
+    import hashlib
+
+    import torch
+
+    h = hashlib.sha256()
+    for key in sorted(state):
+        h.update(key.encode())
+        h.update(state[key].detach().cpu().contiguous().view(torch.uint8).numpy().tobytes())
+    return h.hexdigest()
+
+
+def attach_memory_adapter(model, *, rank: int, memory_state=None, frozen_identity: str = "", seed: int = 0):
+    """Install the Memory adapter as a named bank beside the generation adapters and return its identity record.
+
+    The generation (Stage2) adapters must already be part of the base -- merged, as ``infer`` does -- or frozen: the
+    Memory bank is evaluated INSTEAD of the primary adapter while memory rows are installed, so only a merged base gives
+    the composition "Stage2 + Memory".  A fresh bank must contribute exactly zero (its up-projections are zero); a given
+    ``memory_state`` (``{parameter name ending in __memory: tensor}``) is loaded strictly.  Afterwards nothing in the model
+    trains.  (reference: attach_memory_adapter, solar/backends/minimax_h3/memory_adapter.py:11-61)"""
+    import torch
+
+    from ..models.h3 import LoRALinear
+
+    mods = [m for m in model.modules() if isinstance(m, LoRALinear)]
+    if any(m.rank > 0 and any(p.requires_grad for p in (m.lora_A, m.lora_B)) for m in mods):
+        raise ValueError("the generation adapters must be merged into the base or frozen before the Memory bank is attached")
+    if any(hasattr(m, "lora_A__memory") for m in mods):
+        raise ValueError("a Memory bank is already attached")
+    model.add_adapter("memory", rank=int(rank), seed=int(seed))
+    own = {k: v for k, v in model.named_parameters() if k.endswith("__memory")}
+    if memory_state is None:
+        if any(int(torch.count_nonzero(p)) for k, p in own.items() if "lora_B__" in k):
+            raise ValueError("a new Memory bank must initially contribute zero")
+        digest = "fresh-zero"
+    else:
+        if set(memory_state) != set(own):
+            odd = sorted(set(memory_state) ^ set(own))[:4]
+            raise ValueError(f"the Memory adapter's tensors do not match the bank (e.g. {odd})")
+        with torch.no_grad():
+            for k, p in own.items():
+                if tuple(memory_state[k].shape) != tuple(p.shape):
+                    raise ValueError(f"{k}: shape {tuple(memory_state[k].shape)} does not fit {tuple(p.shape)}")
+                p.copy_(memory_state[k].to(p))
+        digest = adapter_digest(memory_state)
+    model.requires_grad_(False)
+    return {"frozen_adapter": str(frozen_identity), "memory_adapter": digest, "rank": int(rank),
+            "parameter_count": int(sum(p.numel() for p in own.values())), "tensors": len(own), "active_with_memory_rows": ["merged-base", "memory"]}

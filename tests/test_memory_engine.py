@@ -96,3 +96,44 @@ def test_failure_is_sticky(tmp_path):
         eng.start()
     with pytest.raises(ValueError):
         MemorySessionEngine(eng.model, H3StreamConfig(grid_hw=(2, 3), memory_latents=1), run_dir=tmp_path, top_k=5)
+
+
+def test_memory_bank_attaches_beside_merged_generation_adapters(tmp_path):
+    from solarwm_b200.serve.memory import adapter_digest, attach_memory_adapter
+
+    cfg = h3_preset("tiny")
+    cfg.lora_rank = 4
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    with pytest.raises(ValueError):
+        attach_memory_adapter(model, rank=4)                        # trainable generation adapters: not a frozen parent
+    from solarwm_b200.models.h3 import LoRALinear
+
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, LoRALinear):
+                m.lora_B.normal_(0, 0.02)
+                m.merge_()
+                m.rank = 0
+    ident = attach_memory_adapter(model, rank=4, frozen_identity="stage2:ema:step=12")
+    assert ident["memory_adapter"] == "fresh-zero" and ident["parameter_count"] > 0 and ident["frozen_adapter"].startswith("stage2")
+    assert not any(p.requires_grad for p in model.parameters())
+    with pytest.raises(ValueError):
+        attach_memory_adapter(model, rank=4)                        # already attached
+    # a trained bank loads strictly and is identified by its digest
+    state = {k: torch.randn_like(v) * 0.01 for k, v in model.named_parameters() if k.endswith("__memory")}
+    fresh = H3DiT(h3_preset("tiny"), device="cpu", dtype=torch.float32, seed=0)
+    got = attach_memory_adapter(fresh, rank=4, memory_state=state)
+    assert got["memory_adapter"] == adapter_digest(state) and got["tensors"] == len(state)
+    other = H3DiT(h3_preset("tiny"), device="cpu", dtype=torch.float32, seed=0)
+    with pytest.raises(ValueError):
+        attach_memory_adapter(other, rank=4, memory_state={k: v for k, v in list(state.items())[:-1]})
+    # the engine runs with the bank switched on while memory rows are installed
+    scfg = H3StreamConfig(grid_hw=(2, 3), chunk_latents=5, window_chunks=2, denoise_steps=1, use_cuda_graph=False, memory_latents=2,
+                          memory_adapter="memory")
+    eng = MemorySessionEngine(fresh, scfg, run_dir=tmp_path, top_k=2, identity=got)
+    eng.set_condition(text=torch.randn(6, fresh.cfg.text_dim), anchor_latent=torch.randn(24, 1, 4, 6), scene_id="s")
+    eng.start()
+    for j in range(4):
+        eng.advance_camera([["w"]] * (4 if j == 0 else 5))
+        eng.generate()
+    assert eng.stop()["memory"]["memory_adapter"] == got["memory_adapter"]
