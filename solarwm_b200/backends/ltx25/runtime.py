@@ -253,10 +253,47 @@ class LTXTrainingRuntime:
         self.checkpoint_id = verified.manifest_digest
 
     def validate(self, step: int) -> Mapping[str, Any]:
+        """Adapter norms and, with ``validation.index``, the flow loss at fixed noise levels (seeded per clip and level) on
+        the run's frozen, source-balanced validation clips (the selection machinery of ``minimax_h3.validation``)."""
         report = {"step": int(step), "adapter_norm": float(self.optimizer.master.norm())}
         if self.ema is not None:
             report["ema_norm"] = float(self.ema.norm())
+        val = self.config.get("validation", {}) or {}
+        if val.get("index"):
+            report["validation"] = self._validation_loss(val)
         return report
+
+    def _validation_loss(self, val: Mapping[str, Any]) -> Mapping[str, Any]:
+        import torch.distributed as dist
+        from pathlib import Path
+
+        from ...data.index import read_index
+        from ...preencode.shards import read_encoded_sample
+        from ..minimax_h3.validation import IndexedValidation, score
+
+        topo, core = self.topology, self.core
+        if getattr(self, "_validation", None) is None:
+            index = Path(str(val["index"]))
+            root = Path(str(val.get("root") or index.parent))
+
+            def read(row):
+                enc = read_encoded_sample(root, row.values)
+                if enc["latents"].shape[1] != self.arch.in_dim or tuple(enc["text"].shape) != (self.arch.text_len, self.arch.text_dim):
+                    raise BackendContractError(f"{row.sample_id}: latents / text do not match the architecture")
+                return {"latents": enc["latents"].permute(1, 0, 2, 3).unsqueeze(0).float(), "text": enc["text"].unsqueeze(0).float()}
+
+            self._validation = IndexedValidation(read_index(index), read, sample_count=int(val.get("sample_count", 8)), seed=int(val.get("seed", 42)),
+                                                 dp_rank=topo.dp_rank, dp_size=topo.dp_size, balance=bool(val.get("balance_sources", True)),
+                                                 freeze_path=output_root(self.config) / "validation-selection.json")
+            self._validation.prepare(dist if topo.raw_world_size > 1 else None)
+
+        def loss_at(sample, sigma, gen):
+            lat = sample["latents"].to(self.device).to(core.model.dtype)
+            noise = torch.randn(lat.shape, generator=gen, device=self.device, dtype=torch.float32).to(lat.dtype)
+            x_t, target, per_frame = noisy_input_and_target(lat, noise, torch.full((1,), float(sigma), device=self.device))
+            return masked_flow_loss(core.model(x_t, per_frame * 1000.0, sample["text"].to(self.device)), target)
+
+        return dict(score(self._validation, loss_at, device=self.device, dist=dist if topo.dp_size > 1 else None, group=self.ctx.dp_group))
 
     def close(self) -> None:
         dist_init.shutdown(self.ctx)

@@ -135,3 +135,27 @@ def test_cameras_condition_the_adapter_training_step(tmp_path):
         finally:
             rt.close()
     assert losses["plain"] != losses["cameras"]                       # same sample and noise, another attention geometry
+
+
+def test_validation_loss_on_frozen_clips(tmp_path):
+    from solarwm_b200.backends.ltx25.runtime import LTXTrainingRuntime
+    from solarwm_b200.registry import load_backend
+
+    be = load_backend("ltx25_video")
+    pre = {"schema": "solarwm.run.v1", "action": "preencode", "model": {"family": "ltx25_video", "architecture": "tiny"},
+           "data": {"pixel_frames": 9, "pixel_height": 64, "pixel_width": 64, "seed": 1}, "runtime": {"device": "cpu", "output_dir": str(tmp_path / "pre")},
+           "preencode": {"source": "synthetic", "num_samples": 3, "output_root": str(tmp_path / "enc"),
+                         "codecs": {"z_dim": 16, "vae_base": 4, "t5": {"vocab": 512, "dim": 64, "dim_attn": 32, "dim_ffn": 64, "num_heads": 2,
+                                                                      "num_layers": 1, "text_len": 16}}}}
+    assert be.preencode(pre)["samples"] == 3
+    cfg = _config(tmp_path / "run", validation={"index": str(tmp_path / "enc" / "index.jsonl"), "sample_count": 2, "balance_sources": False})
+    rt = LTXTrainingRuntime(cfg)
+    try:
+        first = rt.validate(0)["validation"]
+        assert first["clips"] == 2 and first["loss"] > 0 and rt.validate(0)["validation"] == first
+        with torch.no_grad():
+            rt.optimizer.master.add_(0.05)
+            rt.optimizer.live.copy_(rt.optimizer.master.to(rt.optimizer.live.dtype))
+        assert rt.validate(1)["validation"]["loss"] != first["loss"]
+    finally:
+        rt.close()
