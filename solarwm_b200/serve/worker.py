@@ -116,6 +116,8 @@ def run(args) -> int:
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if torch.cuda.is_available() else torch.device("cpu")
     state, nav = SessionState(), NavigationState()
     try:
+        if args.family == "memory":
+            return _run_memory(args, rank, out_dir, dev, state, nav)
         if args.family == "h3":
             return _run_h3(args, rank, out_dir, dev, state, nav)
         cfg = wan_preset(args.model) if args.model != "small" else WanConfig(
@@ -279,9 +281,69 @@ def _run_h3(args, rank, out_dir, dev, state, nav) -> int:
     return 0
 
 
+def _run_memory(args, rank, out_dir, dev, state, nav) -> int:
+    """The Memory backend's worker (``--family memory``): interactive sessions whose chunks retrieve old latents by camera
+    overlap (``serve/memory_engine.py``).  One key packet per chunk comes from the navigation state; a session report is
+    written when the session stops."""
+    from ..models.h3 import H3DiT, h3_preset
+    from .h3_stream import H3StreamConfig
+    from .memory import attach_memory_adapter
+    from .memory_engine import MemorySessionEngine
+
+    cfg = h3_preset("tiny" if args.model in ("small", "tiny") else args.model)
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    model = H3DiT(cfg, device=dev, dtype=dtype, seed=0)
+    identity = attach_memory_adapter(model, rank=8 if cfg.hidden_size <= 512 else 384, frozen_identity="init:random")
+    top_k = 5
+    scfg = H3StreamConfig(grid_hw=(args.height // 2, args.width // 2), chunk_latents=5, window_chunks=max(1, args.window_frames // 5),
+                          use_cuda_graph=False, memory_latents=top_k, memory_adapter="memory")
+    engine = MemorySessionEngine(model, scfg, run_dir=out_dir, rank=rank, top_k=top_k, identity=identity)
+    g = torch.Generator().manual_seed(0)
+    engine.set_condition(text=torch.randn(16, cfg.text_dim, generator=g),
+                         anchor_latent=torch.randn(scfg.latent_channels, 1, args.height, args.width, generator=g), scene_id="synthetic")
+    state.set_phase("preparing")
+    engine.start(seed=42)
+    state.set_phase("running")
+    nav.set_key("w", True)
+
+    def one():
+        keys = nav.next_actions(4 if engine.index == 0 else 5)
+        if engine.index >= max(2, args.chunks // 2):               # walk back over the same ground so retrieval has something to find
+            keys = [["s"] for _ in keys]
+        engine.advance_camera(keys)
+        _, ms = engine.generate()
+        state.generated(engine.index - 1, ms, 0.0)
+
+    if args.smoke:
+        for _ in range(args.chunks):
+            one()
+        report = engine.stop()
+        if rank == 0:
+            steady = report["dit_ms"][1:] or report["dit_ms"]
+            print(json.dumps({"family": "memory", "chunks": report["chunks"], "median_chunk_ms": sorted(steady)[len(steady) // 2],
+                              "retrieved": [len(r["memory_latent_indices"]) for r in report["retrieval"]]}))
+    else:
+        while True:
+            cmd = state.next_command()
+            if cmd["op"] == "shutdown":
+                break
+            if cmd["op"] == "stop" and engine.active:
+                engine.stop()
+                state.set_phase("stopped")
+            elif cmd["op"] == "start" and not engine.active:
+                engine.start(seed=42)
+                state.set_phase("running")
+            elif cmd["op"] == "chunk" and state.phase == "running":
+                one()
+        if engine.active:
+            engine.stop()
+    _receipt(out_dir, f"exit-rank{rank}.json", {"rank": rank, "status": "ok", "chunks": len(state.chunks), "time": time.time()})
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--family", default="wan", choices=["wan", "h3"])
+    ap.add_argument("--family", default="wan", choices=["wan", "h3", "memory"])
     ap.add_argument("--model", default="small")
     ap.add_argument("--height", type=int, default=16)
     ap.add_argument("--width", type=int, default=16)

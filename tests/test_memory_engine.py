@@ -137,3 +137,15 @@ def test_memory_bank_attaches_beside_merged_generation_adapters(tmp_path):
         eng.advance_camera([["w"]] * (4 if j == 0 else 5))
         eng.generate()
     assert eng.stop()["memory"]["memory_adapter"] == got["memory_adapter"]
+
+
+def test_worker_runs_the_memory_family(tmp_path, capsys):
+    import json
+
+    from solarwm_b200.serve.worker import main
+
+    assert main(["--smoke", "--family", "memory", "--height", "4", "--width", "6", "--chunks", "7", "--window-frames", "10",
+                 "--output", str(tmp_path)]) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["family"] == "memory" and line["retrieved"] == [0, 0, 0, 5, 5, 5, 5]
+    assert (tmp_path / "memory-session-1-rank0.json").is_file() and (tmp_path / "exit-rank0.json").is_file()
