@@ -32,6 +32,63 @@ def _sample(cfg, seed, frames=4, size=8):
     return s
 
 
+def _render_media(args, model) -> int:
+    """``render --structure VIDEO --prompt TEXT --codecs pkg.mod:factory``: the structure video (and the optional first
+    frame) are fitted onto the canvas and encoded by the factory's codecs (``renderer.preencode.Codecs``: ``video`` takes
+    RGB8 frames, ``text`` a prompt), the clip is rendered in one pass or, with ``--causal``, chunk by chunk, and the latents
+    are saved with a record of what produced them (reference: solar/renderer/render.py)."""
+    import importlib
+
+    import numpy as np
+
+    from .comfy_nodes import snap_frames
+    from .preencode import fit, on_grid, read_media, usable_frames
+
+    if not (args.codecs and ":" in args.codecs and args.prompt.strip() and args.out):
+        raise SystemExit("render --structure needs --prompt, --out and --codecs package.module:factory")
+    module, _, factory = args.codecs.partition(":")
+    codecs = getattr(importlib.import_module(module), factory)()
+    H, W = (int(v) for v in args.canvas.lower().split("x"))
+    frames, fps = read_media(args.structure)
+    frames = on_grid(frames, fps) if len(frames) > 1 else np.repeat(frames, 22, axis=0)
+    keep = snap_frames(len(frames), args.length)
+    structure = codecs.video(fit(frames[:keep], (H, W)))
+    C, F, h2, w2 = structure.shape
+    if args.first_frame:
+        still, _ = read_media(args.first_frame)
+        anchor = codecs.video(np.repeat(fit(still[:1], (H, W)), usable_frames(22), axis=0))[:, :1]
+    else:
+        anchor = torch.zeros(C, 1, h2, w2)
+    text, _tags = codecs.text(args.prompt)
+    dev, dt = model.proj_in.device, model.dtype
+    if args.adapter:
+        from .runtime import read_adapter
+
+        state = read_adapter(args.adapter)
+        own = {n: p for n, p in model.named_parameters() if "lora_" in n}
+        if set(own) != set(state):
+            raise SystemExit("the adapter file does not fit this model's adapters")
+        with torch.no_grad():
+            for n, p in own.items():
+                p.copy_(state[n].to(p))
+    sample = {"prompt_embeds": text.to(dev, dt), "anchor_latents": anchor.to(dev, dt), "structure_latents": structure.to(dev, dt), "shape": (C, F, h2, w2)}
+    if args.causal:
+        from .causal import CausalRenderer
+
+        lat = CausalRenderer(model, chunk=args.chunk, window=args.window, steps=max(args.steps, 2)).render(sample, seed=args.seed)
+    else:
+        lat = render(model, sample, steps=max(args.steps, 2), seed=args.seed)
+    out = Path(args.out)
+    out.mkdir(parents=True, exist_ok=True)
+    torch.save(lat.float().cpu(), out / "latents.pt")
+    record = {"structure": str(args.structure), "first_frame": args.first_frame, "prompt": args.prompt, "pixel_frames": int(keep), "latents": list(lat.shape),
+              "canvas": [H, W], "mode": "causal" if args.causal else "bidirectional", "steps": max(args.steps, 2), "seed": args.seed,
+              "adapter": args.adapter, "finite": bool(torch.isfinite(lat.float()).all())}
+    (out / "render.json").write_text(json.dumps(record, indent=1, sort_keys=True))
+    print(json.dumps(record, sort_keys=True))
+    return 0 if record["finite"] else 5
+
+
 def _train_from_config(args) -> int:
     import os
 
@@ -79,6 +136,13 @@ def main(argv=None) -> int:
     ap.add_argument("--lora-rank", type=int, default=4)
     ap.add_argument("--patterns", default="shared=1,known_frames=1,known_region=1,confidence_map=1,ramp=1")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--structure", default=None, help="render: a structure video (mp4 / image); needs --prompt and --codecs")
+    ap.add_argument("--prompt", default="")
+    ap.add_argument("--first-frame", default=None, help="render: an image in the look of the shot")
+    ap.add_argument("--canvas", default="768x1344", help="render: HEIGHTxWIDTH of the render")
+    ap.add_argument("--length", type=int, default=158, help="render: frames, snapped down to 17 n + 5 and to the structure video")
+    ap.add_argument("--adapter", default=None, help="render: an exported adapter file to load into the model")
+    ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--causal", action="store_true", help="render: chunk by chunk with a key / value window (clips of any length)")
     ap.add_argument("--frames", type=int, default=4, help="render: latent frames of the synthetic sample")
     ap.add_argument("--chunk", type=int, default=5)
@@ -125,6 +189,8 @@ def main(argv=None) -> int:
         from ..models.h3 import H3DiT
 
         model = H3DiT(cfg, device=args.device, dtype=torch.bfloat16 if args.device == "cuda" else torch.float32)
+        if args.structure:
+            return _render_media(args, model)
         if args.causal:
             from .causal import CausalRenderer
 

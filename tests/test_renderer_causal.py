@@ -147,3 +147,30 @@ def test_causal_training_runs_behind_the_renderer_runtime(tmp_path):
         assert grads and any(float(g.abs().sum()) > 0 for g in grads)
     finally:
         rt.close()
+
+
+def test_render_command_from_media(tmp_path, capsys):
+    import json
+
+    import cv2
+    import numpy as np
+
+    from solarwm_b200.renderer.cli import main
+
+    rng = np.random.default_rng(0)
+    frames = rng.integers(0, 255, (30, 40, 60, 3), dtype=np.uint8)
+    wr = cv2.VideoWriter(str(tmp_path / "structure.mp4"), cv2.VideoWriter_fourcc(*"mp4v"), 24.0, (60, 40))
+    for f in frames:
+        wr.write(f)
+    wr.release()
+    cv2.imwrite(str(tmp_path / "first.png"), frames[0])
+    base = ["render", "--structure", str(tmp_path / "structure.mp4"), "--prompt", "a harbour at dusk", "--codecs", "tests.helpers.stub_codecs:factory",
+            "--canvas", "32x48", "--device", "cpu", "--steps", "2"]
+    assert main(base + ["--out", str(tmp_path / "a"), "--first-frame", str(tmp_path / "first.png")]) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["pixel_frames"] == 22 and rec["latents"] == [24, 7, 4, 6] and rec["mode"] == "bidirectional" and rec["finite"]
+    assert main(base + ["--out", str(tmp_path / "b"), "--causal", "--chunk", "3", "--window", "2"]) == 0
+    assert json.loads((tmp_path / "b" / "render.json").read_text())["mode"] == "causal"
+    assert torch.load(tmp_path / "b" / "latents.pt", weights_only=True).shape == (24, 7, 4, 6)
+    with pytest.raises(SystemExit):
+        main(["render", "--structure", str(tmp_path / "structure.mp4"), "--out", str(tmp_path / "c"), "--device", "cpu"])
