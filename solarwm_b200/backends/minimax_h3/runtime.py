@@ -183,6 +183,11 @@ class H3TrainingRuntime:
         self.ema = AdapterEMA(self.optimizer, float(e.get("decay", 0.999))) if e.get("enabled", True) else None
         self.ema_start, self.ema_every = int(e.get("start_step", 0)), int(e.get("update_every_steps", 1))
         self.gen = torch.Generator(device=dev).manual_seed(objective_seed(self.seed, topo.dp_rank))
+        self.silence = None
+        if data.get("silence_latents_path"):
+            from .silence import load_silence_latents, silence_rows
+
+            self.silence = silence_rows(load_silence_latents(data["silence_latents_path"], pixel_frames=int(data.get("pixel_frames", 158))))
         self.core = None
         if self.route.stage == "stage1":
             # teacher forcing under the block-causal mask: one packed sample per replica, so data parallelism only
@@ -283,11 +288,18 @@ class H3TrainingRuntime:
         lat, anchor = sample["target_latents"].to(dev), sample["anchor_latents"].to(dev)
         prompt = sample["prompt_embeds"].to(dev)
         C, F, H, W = lat.shape
-        layout = build_layout(n_text=prompt.shape[0], latent_frames=F, grid_hw=(H // 2, W // 2), t_video=t_video)
+        audio, t_audio = None, 0.5
+        if self.silence is not None:                # the silent soundtrack: input rows at their own time, prediction ignored
+            from .silence import noised_silence
+
+            audio, t_audio = noised_silence(self.silence, gen, dev)
+        layout = build_layout(n_text=prompt.shape[0], latent_frames=F, grid_hw=(H // 2, W // 2), t_video=t_video,
+                              n_audio=0 if audio is None else audio.shape[0], t_audio=t_audio)
         noise = torch.randn(lat.shape, generator=gen, device=dev, dtype=torch.float32).to(lat.dtype)
         a_noise = torch.randn(anchor.shape, generator=gen, device=dev, dtype=torch.float32).to(lat.dtype)
         x_t, anchor_t = flow.interpolate(lat, noise, t_video), flow.interpolate(anchor, a_noise, 0.999)
         vid, _ = self.model(video_rows=patchify_latents(x_t).to(dt), text_rows=prompt.to(dt),
+                            audio_rows=None if audio is None else audio.to(dt),
                             anchor_rows=patchify_latents(anchor_t).to(dt), timesteps=layout.timesteps,
                             t_index=layout.t_index.to(dev), tags=layout.tags.to(dev), position_ids=layout.position_ids,
                             viewmats=expand_cameras(layout, sample["camera_w2c"]))
