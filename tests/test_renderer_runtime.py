@@ -170,3 +170,47 @@ def test_runtime_trains_resumes_exactly_and_exports(tmp_path, capsys):
     assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["final_step"] == 2
     assert main(["export", "--checkpoint", str(tmp_path / "e" / "checkpoint_model_000002"), "--out", str(tmp_path / "e.pt")]) == 0
     assert (tmp_path / "e.pt").is_file()
+
+
+WORKER = """
+import json, os, sys, torch
+sys.path.insert(0, os.environ["REPO"])
+from pathlib import Path
+from tests.test_renderer_runtime import _config
+from solarwm_b200.renderer.runtime import RendererTrainingRuntime
+from solarwm_b200.engine.train_engine import StepPolicy, TrainingEngine
+root = Path(os.environ["CORPUS"])
+cfg = _config(root, os.environ["OUT"], train={"max_steps": 2, "gradient_accumulation_steps": 1}, data={"omni_length_buckets": True})
+rt = RendererTrainingRuntime(cfg)
+ids = []
+TrainingEngine(rt, StepPolicy(max_steps=2, grad_accum=1, save_steps=(2,)),
+               event_sink=lambda e: ids.extend(e.get("sample_ids", [])) if e.get("event") == "optimizer_step" else None).run()
+print("RESULT " + json.dumps({"rank": rt.topology.raw_rank, "master": float(rt.optimizer.master.double().sum()), "cursor": rt.reader.cursor}), flush=True)
+rt.close()
+"""
+
+
+def test_two_data_parallel_ranks_share_one_set_of_adapters(tmp_path):
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    _corpus(tmp_path / "corpus", n=6)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, REPO=repo, CORPUS=str(tmp_path / "corpus"), OUT=str(tmp_path / "run"), RANK=str(rank), LOCAL_RANK=str(rank),
+                   WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    rows = [json.loads(l.split("RESULT ", 1)[1]) for o in outs for l in o.splitlines() if l.startswith("RESULT ")]
+    assert len(rows) == 2 and rows[0]["master"] == rows[1]["master"] and rows[0]["cursor"] == rows[1]["cursor"] == 2
+    saved = torch.load(tmp_path / "run" / "checkpoint_model_000002" / "rank-state.pt", weights_only=True)
+    assert saved["world_size"] == 2 and [r["reader"]["cursor"] for r in saved["ranks"]] == [2, 2]
