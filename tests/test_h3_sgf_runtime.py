@@ -170,7 +170,7 @@ def test_two_data_parallel_ranks_keep_their_adapters_identical(tmp_path):
     procs = []
     for rank in range(2):
         env = dict(os.environ, REPO=repo, OUT=str(tmp_path / "run"), RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2",
-                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="")
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=600)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs

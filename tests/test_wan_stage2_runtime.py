@@ -84,3 +84,43 @@ def test_roles_start_from_earlier_checkpoints(tmp_path):
     other = _config(tmp_path / "child2", checkpoint={"resume_from": out["checkpoint_dir"]}, train={"max_steps": 2})
     with pytest.raises(BackendContractError):
         run_stage2_training(other)
+
+
+WORKER = """
+import json, os, sys, torch
+sys.path.insert(0, os.environ["REPO"])
+from tests.test_wan_stage2_runtime import _config, _role
+from solarwm_b200.backends.wan22.stage2 import run_stage2_training
+cfg = _config(os.environ["OUT"], checkpoint={"save_steps": [3]}, distributed={"world_size": 2, "sequence_parallel_size": 1})
+cfg["train"]["max_steps"] = 3
+out = run_stage2_training(cfg)
+rank = int(os.environ["RANK"])
+print("RESULT " + json.dumps({"rank": rank, "losses": out["losses"], "final": out["final_step"]}), flush=True)
+"""
+
+
+def test_two_data_parallel_ranks_average_their_gradients(tmp_path):
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, REPO=repo, OUT=str(tmp_path / "run"), RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2",
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    rows = [json.loads(l.split("RESULT ", 1)[1]) for o in outs for l in o.splitlines() if l.startswith("RESULT ")]
+    assert len(rows) == 2 and all(r["final"] == 3 for r in rows)
+    assert rows[0]["losses"]["critic"] != rows[1]["losses"]["critic"]           # the replicas rolled out different prompts and noise
+    saved = _role(tmp_path / "run" / "checkpoint_model_000003")
+    ranks = torch.load(tmp_path / "run" / "checkpoint_model_000003" / "rank-state.pt", weights_only=True)
+    assert ranks["world_size"] == 2 and len(ranks["ranks"]) == 2 and "student" in saved
