@@ -56,6 +56,9 @@ def test_cli_errors_exit_2_and_helpers(tmp_path, monkeypatch, capsys):
     ("wan22_ti2v_5b/tiny_preencode_cpu.yaml", "preencode"),
     ("wan22_ti2v_5b/tiny_stage0p5_online_cpu.yaml", "train"),
     ("ltx25_video/tiny_stage0p5_cpu.yaml", "train"),
+    ("ltx25_video/tiny_lora_cameras_cpu.yaml", "train"),
+    ("minimax_h3/tiny_stage2_sgf_cpu.yaml", "train"),
+    ("minimax_h3/tiny_infer_cases_cpu.yaml", "infer"),
     ("minimax_h3/tiny_stage0p5_cpu.yaml", "train"),
     ("minimax_h3/tiny_infer_cpu.yaml", "infer"),
 ])
