@@ -214,3 +214,16 @@ def test_two_data_parallel_ranks_share_one_set_of_adapters(tmp_path):
     assert len(rows) == 2 and rows[0]["master"] == rows[1]["master"] and rows[0]["cursor"] == rows[1]["cursor"] == 2
     saved = torch.load(tmp_path / "run" / "checkpoint_model_000002" / "rank-state.pt", weights_only=True)
     assert saved["world_size"] == 2 and [r["reader"]["cursor"] for r in saved["ranks"]] == [2, 2]
+
+
+def test_example_config_trains_on_a_corpus(tmp_path, monkeypatch, capsys):
+    from pathlib import Path
+
+    from solarwm_b200.renderer.cli import main
+
+    _corpus(tmp_path / "corpus", n=4)
+    monkeypatch.setenv("SOLAR_OMNI_ROOT", str(tmp_path / "corpus"))
+    monkeypatch.setenv("SOLAR_OUTPUT_DIR", str(tmp_path / "out"))
+    config = str(Path(__file__).resolve().parent.parent / "configs" / "renderer" / "control_tiny_cpu.yaml")
+    assert main(["train", "--config", config, "--set", "train.max_steps=2"]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["final_step"] == 2
