@@ -131,3 +131,64 @@ def test_recorded_answers_resume_and_follow_the_files(tmp_path):
     log.write_text("\n".join(lines) + "\n")
     with pytest.raises(ValueError):
         RecordedJudge(live, log)
+
+
+def test_command_line_against_a_local_endpoint(tmp_path, capsys):
+    """The whole pass over real files and a real HTTP round trip to a server on the loopback interface."""
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    from PIL import Image
+
+    from solarwm_b200.eval.judge_client import main
+    from solarwm_b200.eval.render_benchmark import write_video
+
+    root = tmp_path / "bench"
+    (root / "benchmark" / "hard").mkdir(parents=True)
+    (root / "benchmark" / "heldout").mkdir(parents=True)
+    rows = []
+    for cid in ("s1__day", "s1__night", "s2__day"):
+        base = root / "cases" / cid
+        base.mkdir(parents=True)
+        (base / "prompt.txt").write_text("a street")
+        write_video(base / "condition.mp4", _clip(5, frames=9, h=32, w=48))
+        Image.fromarray(_clip(5, h=32, w=48)[0]).save(base / "first_frame.png")
+        rows.append({"case_id": cid, "files": {k: f"cases/{cid}/{k}" for k in ("prompt.txt", "condition.mp4", "first_frame.png")}})
+        write_video(tmp_path / "ours" / "hard" / f"{cid}.mp4", _clip(220, frames=9, h=32, w=48))
+        write_video(tmp_path / "base" / "hard" / f"{cid}.mp4", _clip(30, frames=9, h=32, w=48))
+    (root / "benchmark" / "hard" / "cases.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    (root / "benchmark" / "heldout" / "cases.jsonl").write_text("")
+
+    brain, seen = FakeEndpoint(), []
+
+    class Handler(BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = self.rfile.read(int(self.headers["Content-Length"]))
+            seen.append((self.path, self.headers.get("Authorization")))
+            status, reply = brain(self.path, dict(self.headers), body)
+            self.send_response(status)
+            self.send_header("Content-Length", str(len(reply)))
+            self.end_headers()
+            self.wfile.write(reply)
+
+        def log_message(self, *a):
+            pass
+
+    server = HTTPServer(("127.0.0.1", 0), Handler)
+    thread = threading.Thread(target=server.serve_forever, daemon=True)
+    thread.start()
+    try:
+        argv = ["--root", str(root), "--a", f"ours={tmp_path / 'ours'}", "--b", f"base={tmp_path / 'base'}", "--endpoint",
+                f"http://127.0.0.1:{server.server_port}/v1", "--model", "vlm", "--out", str(tmp_path / "out"), "--split", "hard",
+                "--questions", "q1_visual_quality,q4_overall", "--cells", "4"]
+        assert main(argv) == 0
+        first = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert first == {"cases": 3, "asked": 6, "reused": 0, "q1_visual_quality": 1.0, "q4_overall": 1.0}
+        assert main(argv) == 0
+        assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["reused"] == 6 and len(seen) == 6
+    finally:
+        server.shutdown()
+        server.server_close()
+    assert all(path == "/v1/chat/completions" and auth is None for path, auth in seen)
+    report = json.loads((tmp_path / "out" / "verdicts-ours-vs-base.json").read_text())
+    assert report["net"]["q4_overall"]["wins"] == 3 and [r["case"] for r in report["rows"]] == [f"hard/{r['case_id']}" for r in rows]
