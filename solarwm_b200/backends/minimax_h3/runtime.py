@@ -201,6 +201,7 @@ class H3TrainingRuntime:
                                         objective="anyflow" if self.route.objective.startswith("anyflow") else "tf_fm",
                                         chunk_latents=int(causal.get("chunk_latents", 5)),
                                         window_chunks=int(causal.get("window_chunks", 5)))
+            self.core.silence = self.silence
         elif self.route.stage != "stage0p5":
             raise BackendContractError(f"no multi-rank H3 runtime for {self.route.stage}")
         self._global_step, self.batches_consumed = 0, 0

@@ -28,21 +28,30 @@ from ...engine import anyflow as af
 from ...engine.master_adamw import FP32MasterAdamW
 from ...models.h3 import H3DiT
 from . import flow
-from .layout import TAG_TEXT, TAG_VIDEO, patchify_latents, spatial_axis, temporal_positions
+from .layout import TAG_AUDIO, TAG_TEXT, TAG_VIDEO, patchify_latents, spatial_axis, temporal_positions
 
 
-def w6_attention(q, k, v, *, n_cond: int, chunk_rows: int, n_chunks: int, window_chunks: int):
-    """q / k / v [1, S, H, D] with S = n_cond + 2 * n_chunks * chunk_rows.  Returns [1, S, H, D].  On the device one
-    masked flash-attention call evaluates the whole rule (prefix rows, clean windows, noisy chunks); the per-chunk loop
-    below is its CPU form."""
+def w6_attention(q, k, v, *, n_cond: int, chunk_rows: int, n_chunks: int, window_chunks: int, n_audio: int = 0):
+    """q / k / v [1, S, H, D] with S = n_cond + n_audio + 2 * n_chunks * chunk_rows, rows in the order
+    [condition | audio | clean | noisy].  Returns [1, S, H, D].  Condition rows see condition rows, audio rows see
+    condition and audio rows, every video row sees both on top of its own window.  On the device one masked
+    flash-attention call evaluates the whole rule (prefix rows, clean windows, noisy chunks) with the audio rows counted
+    into the prefix, and the condition rows -- the only ones that rule shows too much -- are evaluated again on their
+    own; the per-chunk loop below is the CPU form."""
     L = n_chunks * chunk_rows
+    cond_rows, n_cond = n_cond, n_cond + n_audio    # from here on ``n_cond`` is the whole common prefix
     if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and ops.get_backend() == "native":
         from ...models.wan_tf import _cached_mask
         from ...ops.attention_mask import masked_attention
 
-        return masked_attention(q, k, v, _cached_mask("tf", L, chunk_rows, window_chunks, 0, n_cond))
+        out = masked_attention(q, k, v, _cached_mask("tf", L, chunk_rows, window_chunks, 0, n_cond))
+        if n_audio:
+            out = torch.cat([ops.attention(q[:, :cond_rows], k[:, :cond_rows], v[:, :cond_rows]), out[:, cond_rows:]], 1)
+        return out
     c0, n0 = n_cond, n_cond + L                     # first clean row, first noisy row
-    outs = [ops.attention(q[:, :n_cond], k[:, :n_cond], v[:, :n_cond])]
+    outs = [ops.attention(q[:, :cond_rows], k[:, :cond_rows], v[:, :cond_rows])]
+    if n_audio:
+        outs.append(ops.attention(q[:, cond_rows:n_cond], k[:, :n_cond], v[:, :n_cond]))
     clean, noisy = [], []
     for i in range(n_chunks):
         lo = c0 + max(0, i - window_chunks) * chunk_rows
@@ -57,13 +66,15 @@ def w6_attention(q, k, v, *, n_cond: int, chunk_rows: int, n_chunks: int, window
     return torch.cat(outs + clean + noisy, 1)
 
 
-def w6_mask(n_cond: int, chunk_rows: int, n_chunks: int, window_chunks: int) -> torch.Tensor:
+def w6_mask(n_cond: int, chunk_rows: int, n_chunks: int, window_chunks: int, n_audio: int = 0) -> torch.Tensor:
     """Dense boolean oracle of ``w6_attention`` (True = visible)."""
     L = n_chunks * chunk_rows
+    cond_rows, n_cond = n_cond, n_cond + n_audio
     S = n_cond + 2 * L
     m = torch.zeros(S, S, dtype=torch.bool)
     m[:, :n_cond] = True
     m[:n_cond, n_cond:] = False
+    m[:cond_rows, cond_rows:] = False
     ch = torch.arange(L) // chunk_rows
     qc, kc = ch.view(-1, 1), ch.view(1, -1)
     m[n_cond:n_cond + L, n_cond:n_cond + L] = (kc <= qc) & (kc >= qc - window_chunks)
@@ -74,11 +85,13 @@ def w6_mask(n_cond: int, chunk_rows: int, n_chunks: int, window_chunks: int) -> 
 
 def teacher_forcing_forward(model: H3DiT, *, prompt, anchor_rows, clean_rows, noisy_rows, t_chunks: torch.Tensor,
                             grid_hw, chunk_latents: int, window_chunks: int, cameras: Optional[torch.Tensor] = None,
-                            capture: Optional[list] = None):
+                            capture: Optional[list] = None, audio_rows: Optional[torch.Tensor] = None, t_audio: float = 0.5):
     """Rows are already patchified ([n, 96]); ``t_chunks`` [n_chunks] in [0, 1] (1 = clean).  Returns the
-    prediction for the noisy rows [L, 96].  With ``capture`` (an empty list) every main block appends the detached
-    keys / values of the prefix rows ``[text | anchor | clean]``: under W6 those rows never see a noisy row, so
-    they are the same in every evaluation of the step and ``suffix_forward`` can reuse them."""
+    prediction for the noisy rows [L, 96].  ``audio_rows`` [Na, 32] (the silent soundtrack already noised to
+    ``t_audio``) sit between the anchor and the video; their prediction is dropped.  With ``capture`` (an empty list)
+    every main block appends the detached keys / values of the prefix rows ``[text | anchor | audio | clean]``: under
+    W6 those rows never see a noisy row, so they are the same in every evaluation of the step and ``suffix_forward``
+    can reuse them."""
     h, w = grid_hw
     rows = h * w
     L = clean_rows.shape[0]
@@ -86,14 +99,17 @@ def teacher_forcing_forward(model: H3DiT, *, prompt, anchor_rows, clean_rows, no
     n_chunks = F // chunk_latents
     n_text = prompt.shape[0]
     n_cond = n_text + anchor_rows.shape[0]
+    n_audio = 0 if audio_rows is None else audio_rows.shape[0]
     dev = clean_rows.device
-    # ---- per-row timestep groups: text / clean -> 1.0 ; anchor -> 0.999 ; noisy chunk i -> t_chunks[i]
-    values = torch.cat([torch.tensor([1.0, 0.999]), t_chunks.detach().float().cpu()])
+    # ---- per-row timestep groups: text / clean -> 1.0 ; anchor -> 0.999 ; audio -> t_audio ; noisy chunk i -> t_chunks[i]
+    values = torch.cat([torch.tensor([1.0, 0.999, float(t_audio)]), t_chunks.detach().float().cpu()])
     uniq, inverse = torch.unique(values, return_inverse=True)
     chunk_rows = chunk_latents * rows
     t_index = torch.cat([torch.full((n_text,), int(inverse[0])), torch.full((anchor_rows.shape[0],), int(inverse[1])),
-                         torch.full((L,), int(inverse[0])), inverse[2:].repeat_interleave(chunk_rows)]).to(torch.int32)
-    tags = torch.cat([torch.full((n_text,), TAG_TEXT), torch.full((anchor_rows.shape[0] + 2 * L,), TAG_VIDEO)]).to(torch.int32)
+                         torch.full((n_audio,), int(inverse[2])),
+                         torch.full((L,), int(inverse[0])), inverse[3:].repeat_interleave(chunk_rows)]).to(torch.int32)
+    tags = torch.cat([torch.full((n_text,), TAG_TEXT), torch.full((anchor_rows.shape[0],), TAG_VIDEO),
+                      torch.full((n_audio,), TAG_AUDIO), torch.full((2 * L,), TAG_VIDEO)]).to(torch.int32)
     # ---- positions: both video copies share the native grid positions
     pos_text = torch.zeros(n_text, 3, dtype=torch.float64)
     pos_text[:, 0] = torch.arange(n_text)
@@ -108,18 +124,23 @@ def teacher_forcing_forward(model: H3DiT, *, prompt, anchor_rows, clean_rows, no
         return p
 
     vid_pos = frames(tpos[1:].tolist())
-    pos = torch.cat([pos_text, frames([float(tpos[0])])[:anchor_rows.shape[0]], vid_pos, vid_pos])
+    pos_audio = torch.zeros(n_audio, 3, dtype=torch.float64)          # (origin + j, 0, first | last column), as in the
+    pos_audio[:, 0] = n_text + torch.arange(n_audio)                   # bidirectional document
+    pos_audio[:, 2] = torch.from_numpy(np.where(np.arange(n_audio) < n_audio // 2, float(xs[0]), float(xs[-1])))
+    pos = torch.cat([pos_text, frames([float(tpos[0])])[:anchor_rows.shape[0]], pos_audio, vid_pos, vid_pos])
     view = None
     if cameras is not None:                 # [1 + F, 4, 4]: anchor then frames
         per = cameras[1:].float().repeat_interleave(rows, dim=0)
-        view = torch.cat([torch.eye(4).repeat(n_text, 1, 1), cameras[:1].float().repeat(anchor_rows.shape[0], 1, 1), per, per])
+        view = torch.cat([torch.eye(4).repeat(n_text, 1, 1), cameras[:1].float().repeat(anchor_rows.shape[0], 1, 1),
+                          torch.eye(4).repeat(n_audio, 1, 1), per, per])
 
     def attn(q, k, v):
         if capture is not None:
-            capture.append((k[:, :n_cond + L].detach(), v[:, :n_cond + L].detach()))
-        return w6_attention(q, k, v, n_cond=n_cond, chunk_rows=chunk_rows, n_chunks=n_chunks, window_chunks=window_chunks)
+            capture.append((k[:, :n_cond + n_audio + L].detach(), v[:, :n_cond + n_audio + L].detach()))
+        return w6_attention(q, k, v, n_cond=n_cond, chunk_rows=chunk_rows, n_chunks=n_chunks, window_chunks=window_chunks,
+                            n_audio=n_audio)
 
-    vid, _ = model(video_rows=torch.cat([clean_rows, noisy_rows]), text_rows=prompt, anchor_rows=anchor_rows,
+    vid, _ = model(video_rows=torch.cat([clean_rows, noisy_rows]), text_rows=prompt, anchor_rows=anchor_rows, audio_rows=audio_rows,
                    timesteps=uniq, t_index=t_index.to(dev), tags=tags.to(dev), position_ids=pos, viewmats=view,
                    attn_fn=attn)
     return vid[L:]
@@ -127,7 +148,7 @@ def teacher_forcing_forward(model: H3DiT, *, prompt, anchor_rows, clean_rows, no
 
 @torch.no_grad()
 def suffix_forward(model: H3DiT, *, captured, noisy_rows, t_chunks: torch.Tensor, n_text: int, n_anchor: int, grid_hw,
-                   chunk_latents: int, window_chunks: int, cameras: Optional[torch.Tensor] = None):
+                   chunk_latents: int, window_chunks: int, cameras: Optional[torch.Tensor] = None, n_audio: int = 0):
     """The noisy half alone against captured prefix keys / values (one ``(k, v)`` pair per main block from
     ``teacher_forcing_forward(capture=...)``): the same prediction as a full evaluation for these noisy rows, at
     about half its cost -- the text, anchor and clean rows are not recomputed.  No-grad evaluations only (the
@@ -143,7 +164,7 @@ def suffix_forward(model: H3DiT, *, captured, noisy_rows, t_chunks: torch.Tensor
     F = L // rows
     n_chunks = F // chunk_latents
     chunk_rows = chunk_latents * rows
-    n_cond = n_text + n_anchor
+    n_cond = n_text + n_anchor + n_audio            # the common prefix every video row sees
     dev = noisy_rows.device
     if len(captured) != len(model.blocks):
         raise ValueError("one captured (k, v) pair per main block is required")
@@ -196,6 +217,8 @@ class H3Stage1Trainer:
             torch.Generator(device=self.device).manual_seed(seed * 100003 + 1)
         self.objective, self.chunk_latents, self.window_chunks = objective, chunk_latents, window_chunks
         self.ratios, self.epsilon = (diffusion_ratio, consistency_ratio), float(epsilon)
+        self.silence: Optional[torch.Tensor] = None     # packed rows of encoded silence [Na, 32]; None = no audio rows
+        self._audio = None                              # this step's (noised rows, audio time), shared by its evaluations
 
     def _predict(self, sample, lat, noise, t_chunks, capture=None, captured=None):
         dev, dt = self.device, self.model.dtype
@@ -205,17 +228,20 @@ class H3Stage1Trainer:
         clean = patchify_latents(lat).to(dt)
         noisy = (t_rows * clean.float() + (1.0 - t_rows) * patchify_latents(noise).float()).to(dt)
         anchor = sample["anchor_latents"].to(dev)
+        audio, t_audio = self._audio if self._audio is not None else (None, 0.5)
         if captured is not None:                   # probe: the noisy half against the captured prefix
             return suffix_forward(self.model, captured=captured, noisy_rows=noisy, t_chunks=t_chunks,
                                   n_text=sample["prompt_embeds"].shape[0], n_anchor=patchify_latents(anchor).shape[0],
                                   grid_hw=(H // 2, W // 2), chunk_latents=self.chunk_latents,
-                                  window_chunks=self.window_chunks, cameras=sample.get("camera_w2c"))
+                                  window_chunks=self.window_chunks, cameras=sample.get("camera_w2c"),
+                                  n_audio=0 if audio is None else audio.shape[0])
         a_noise = torch.randn(anchor.shape, generator=self.gen, device=dev, dtype=torch.float32).to(anchor.dtype)
         return teacher_forcing_forward(self.model, capture=capture, prompt=sample["prompt_embeds"].to(dev, dt),
                                        anchor_rows=patchify_latents(flow.interpolate(anchor, a_noise, 0.999)).to(dt),
                                        clean_rows=clean, noisy_rows=noisy, t_chunks=t_chunks, grid_hw=(H // 2, W // 2),
                                        chunk_latents=self.chunk_latents, window_chunks=self.window_chunks,
-                                       cameras=sample.get("camera_w2c"))
+                                       cameras=sample.get("camera_w2c"), audio_rows=None if audio is None else audio.to(dt),
+                                       t_audio=t_audio)
 
     def train_step(self, sample: Mapping[str, torch.Tensor]) -> torch.Tensor:
         loss = self.compute_loss(sample)
@@ -234,6 +260,11 @@ class H3Stage1Trainer:
         n_chunks = F // self.chunk_latents
         rows = (H // 2) * (W // 2)
         noise = torch.randn(lat.shape, generator=self.gen, device=dev, dtype=torch.float32).to(lat.dtype)
+        self._audio = None
+        if self.silence is not None:     # one audio time and one audio noise per step: every evaluation of the step sees them
+            from .silence import noised_silence
+
+            self._audio = noised_silence(self.silence, self.gen, dev)
         target = patchify_latents((lat.float() - noise.float())).float()                 # x0 - n
         per_chunk = lambda e: e.view(n_chunks, -1).mean(dim=1)   # noqa: E731
         if self.objective == "tf_fm":

@@ -58,6 +58,7 @@ class H3Stage2Trainer:
         self.global_step = self.student_step = 0
         self.teacher = None                    # ``set_teacher``: a third role with its own frozen adapters
         self.sync = None                       # ``sync(params, flat_fp32_grad)``: the runtime's reduction over ranks
+        self.silence = None                    # packed rows of encoded silence [Na, 32]: the replay's and the scores' audio
 
     def set_teacher(self, adapter_state: Mapping[str, torch.Tensor], seed: int = 0) -> None:
         """Build the teacher role: the shared frozen base with the given adapter weights, never trained."""
@@ -84,14 +85,25 @@ class H3Stage2Trainer:
                     m.rank = r
         return _Off()
 
-    def _bidirectional_x0(self, model, x_t, t: float, sample, cameras):
-        """x0 prediction of a bidirectional evaluation on the packed document; x_t [C, F, H, W]."""
+    def _audio(self):
+        """The silent soundtrack at a freshly drawn audio time, ``(rows, t_audio)``, or None when no silence is set."""
+        if self.silence is None:
+            return None
+        from .silence import noised_silence
+
+        return noised_silence(self.silence, self.gen, self.device)
+
+    def _bidirectional_x0(self, model, x_t, t: float, sample, cameras, audio=None):
+        """x0 prediction of a bidirectional evaluation on the packed document; x_t [C, F, H, W]; ``audio`` as ``_audio``
+        returns it (evaluations that are compared with one another get the same one)."""
         dev, dt = self.device, model.dtype
         C, F, H, W = x_t.shape
         prompt = sample["prompt_embeds"].to(dev, dt)
-        layout = build_layout(n_text=prompt.shape[0], latent_frames=F, grid_hw=(H // 2, W // 2), t_video=float(t))
+        layout = build_layout(n_text=prompt.shape[0], latent_frames=F, grid_hw=(H // 2, W // 2), t_video=float(t),
+                              n_audio=0 if audio is None else audio[0].shape[0], t_audio=0.5 if audio is None else audio[1])
         view = None if cameras is None else expand_cameras(layout, cameras)
         vid, _ = model(video_rows=patchify_latents(x_t).to(dt), text_rows=prompt,
+                       audio_rows=None if audio is None else audio[0].to(dt),
                        anchor_rows=patchify_latents(sample["anchor_latents"].to(dev)).to(dt), timesteps=layout.timesteps,
                        t_index=layout.t_index.to(dev), tags=layout.tags.to(dev), position_ids=layout.position_ids,
                        viewmats=view)
@@ -120,8 +132,10 @@ class H3Stage2Trainer:
         clean_rows = patchify_latents(generated).to(dt)
         noisy_rows = (t_exit * clean_rows.float() + (1 - t_exit) * patchify_latents(noise)).to(dt)
         anchor_rows = patchify_latents(sample["anchor_latents"].to(dev)).to(dt)
+        audio = self._audio()
+        extra = {} if audio is None else {"audio_rows": audio[0].to(dt), "t_audio": audio[1]}
         with torch.set_grad_enabled(grad):
-            v = teacher_forcing_forward(self.student, prompt=sample["prompt_embeds"].to(dev, dt), anchor_rows=anchor_rows,
+            v = teacher_forcing_forward(self.student, prompt=sample["prompt_embeds"].to(dev, dt), anchor_rows=anchor_rows, **extra,
                                         clean_rows=clean_rows, noisy_rows=noisy_rows,
                                         t_chunks=torch.full((n_chunks,), t_exit, device=dev), grid_hw=(H // 2, W // 2),
                                         chunk_latents=self.stream_cfg.chunk_latents,
@@ -142,17 +156,17 @@ class H3Stage2Trainer:
         opt.zero_grad()
         return norm
 
-    def _real_x0(self, x_t, t_s, sample, cams):
+    def _real_x0(self, x_t, t_s, sample, cams, audio=None):
         """The guided "real" score: the teacher role when one was built, else the student with its adapters off."""
         import contextlib
 
         model = self.teacher if self.teacher is not None else self.student
         scope = contextlib.nullcontext() if self.teacher is not None else self._adapters_off(self.student)
         with scope:
-            real, _ = self._bidirectional_x0(model, x_t, t_s, sample, cams)
+            real, _ = self._bidirectional_x0(model, x_t, t_s, sample, cams, audio)
             if self.scale != 1.0:
                 null = dict(sample, prompt_embeds=torch.zeros_like(sample["prompt_embeds"]))
-                real_u, _ = self._bidirectional_x0(model, x_t, t_s, null, cams)
+                real_u, _ = self._bidirectional_x0(model, x_t, t_s, null, cams, audio)
                 real = real_u + self.scale * (real - real_u)
         return real
 
@@ -165,9 +179,10 @@ class H3Stage2Trainer:
         t_s = float(0.02 + 0.96 * torch.rand(1, generator=self.gen, device=dev))
         n2 = torch.randn((C, F, H, W), generator=self.gen, device=dev, dtype=torch.float32).to(dt)
         x_t = flow.interpolate(out_lat, n2, t_s)
+        audio = self._audio()                       # one silent soundtrack for the scores that are subtracted
         with torch.no_grad():
-            fake, _ = self._bidirectional_x0(self.critic, x_t, t_s, sample, cams)
-            real = self._real_x0(x_t, t_s, sample, cams)
+            fake, _ = self._bidirectional_x0(self.critic, x_t, t_s, sample, cams, audio)
+            real = self._real_x0(x_t, t_s, sample, cams, audio)
             if not bool(torch.isfinite(fake).all() and torch.isfinite(real).all()):
                 raise FloatingPointError("non-finite H3 SGF score output")
         g = sgf_kl_gradient(fake_x0=fake.unsqueeze(0), real_x0=real.unsqueeze(0), student_output=out_rows.detach().unsqueeze(0))
@@ -188,7 +203,7 @@ class H3Stage2Trainer:
         t_c = float(0.02 + 0.96 * torch.rand(1, generator=self.gen, device=dev))
         n3 = torch.randn((C, F, H, W), generator=self.gen, device=dev, dtype=torch.float32).to(dt)
         x_tc = flow.interpolate(out_lat, n3, t_c)
-        _, vel = self._bidirectional_x0(self.critic, x_tc, t_c, sample, cams)
+        _, vel = self._bidirectional_x0(self.critic, x_tc, t_c, sample, cams, self._audio())
         target = patchify_latents(out_lat.float() - n3.float())
         loss_c = (vel.float() - target).pow(2).mean()
         if not bool(torch.isfinite(loss_c)):

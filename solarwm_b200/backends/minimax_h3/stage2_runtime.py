@@ -96,6 +96,10 @@ class H3SGFRuntime:
         if load_released is not None:
             load_released(tr.student, config)              # the critic and the teacher alias the same base tensors
         tr.gen = torch.Generator(device=dev).manual_seed(objective_seed(self.seed, topo.dp_rank))
+        if data.get("silence_latents_path"):
+            from .silence import load_silence_latents, silence_rows
+
+            tr.silence = silence_rows(load_silence_latents(data["silence_latents_path"], pixel_frames=int(data.get("pixel_frames", 158))))
         if topo.dp_size > 1:
             tr.sync = lambda params, flat: sync_adapter_gradients(params, flat, sp_group=None, sp_size=1,
                                                                   dp_group=self.ctx.dp_group,

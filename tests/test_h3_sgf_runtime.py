@@ -179,3 +179,41 @@ def test_two_data_parallel_ranks_keep_their_adapters_identical(tmp_path):
     assert all(r["consumed"] == 4 for r in rows)                   # one critic sample per step, one more for the student on step 3
     saved = torch.load(tmp_path / "run" / "checkpoint_model_000003" / "rank-state.pt", weights_only=True)
     assert saved["world_size"] == 2 and len(saved["ranks"]) == 2
+
+
+def test_the_silent_soundtrack_enters_the_replay_and_every_score(tmp_path):
+    """With ``data.silence_latents_path`` the teacher-forced replay and the critic / real score evaluations carry the
+    audio rows (the score evaluations of one student phase share one draw); a run with them repeats itself exactly."""
+    from safetensors.torch import save_file
+
+    from solarwm_b200.backends.minimax_h3.silence import LENGTHS
+    from solarwm_b200.backends.minimax_h3.stage2_runtime import H3SGFRuntime
+
+    path = tmp_path / "s.safetensors"
+    save_file({"silence_158f": (torch.randn(2, 32, LENGTHS[158], generator=torch.Generator().manual_seed(0)) * 0.1).to(torch.bfloat16)}, str(path))
+    mc = _model_config()
+
+    def run(name, silent):
+        cfg = _config(tmp_path / name, data={"silence_latents_path": str(path)} if silent else {})
+        rt = H3SGFRuntime(cfg, model_config=mc(cfg))
+        _kick(rt)
+        seen = []
+        for role, model in (("student", rt.trainer.student), ("critic", rt.trainer.critic)):
+            held = model.forward
+            model.forward = (lambda held, role: lambda **k: (seen.append(
+                (role, None if k.get("audio_rows") is None else (tuple(k["audio_rows"].shape), float(k["audio_rows"].float().sum())))), held(**k))[1])(held, role)
+        stats = [rt.train_outer_step() for _ in range(3)]
+        return seen, stats, [p.detach().clone() for p in rt.trainer.student.trainable_parameters()]
+
+    plain_seen, plain_stats, _ = run("plain", False)
+    assert plain_seen and all(a is None for _, a in plain_seen)
+    seen, stats, weights = run("silent", True)
+    # the streaming rollout itself carries no audio rows; every teacher-forced and bidirectional evaluation does
+    with_audio = [(r, a) for r, a in seen if a is not None]
+    assert with_audio and all(a[0] == (2 * LENGTHS[158], 32) for _, a in with_audio)
+    assert {r for r, _ in with_audio} == {"student", "critic"}
+    third = stats[2]
+    assert third["student_updated"] == 1.0 and third["loss"] == third["loss"]
+    assert stats[0]["loss_critic"] != plain_stats[0]["loss_critic"]
+    again_seen, again_stats, again_weights = run("silent-again", True)
+    assert again_seen == seen and all(torch.equal(a, b) for a, b in zip(weights, again_weights))

@@ -248,3 +248,62 @@ def test_h3_backend_infer_decodes_frames_when_a_decoder_is_configured(tmp_path):
     out = load_backend("minimax_h3").infer(config)
     assert out["frames"] > 0 and out["video"]["frames"] == out["frames"]
     assert (tmp_path / "run" / "generate" / "frames" / "video.rgb").stat().st_size == out["frames"] * (4 * 2) * (6 * 2) * 3
+
+
+def test_w6_with_audio_rows_matches_its_dense_mask():
+    """Condition rows see the condition, audio rows the condition and the audio, video rows both plus their window."""
+    torch.manual_seed(1)
+    n_cond, n_audio, chunk_rows, n_chunks, W = 5, 3, 4, 3, 1
+    S = n_cond + n_audio + 2 * n_chunks * chunk_rows
+    q, k, v = (torch.randn(1, S, 2, 16) for _ in range(3))
+    mask = w6_mask(n_cond, chunk_rows, n_chunks, W, n_audio=n_audio)
+    assert not mask[:n_cond, n_cond:].any() and mask[n_cond:n_cond + n_audio, :n_cond + n_audio].all()
+    assert not mask[n_cond:n_cond + n_audio, n_cond + n_audio:].any() and mask[n_cond + n_audio:, :n_cond + n_audio].all()
+    got = w6_attention(q, k, v, n_cond=n_cond, chunk_rows=chunk_rows, n_chunks=n_chunks, window_chunks=W, n_audio=n_audio)
+    assert torch.allclose(got, R.attention(q, k, v, mask=mask.view(1, 1, S, S)), atol=1e-5)
+
+
+def test_silent_soundtrack_in_teacher_forcing():
+    """Audio rows enter the document (the video prediction depends on them), the prefix capture holds them, the suffix
+    evaluation on that prefix equals the full one, and a trainer with silence installed steps on both objectives."""
+    from solarwm_b200.backends.minimax_h3.layout import patchify_latents
+    from solarwm_b200.backends.minimax_h3.stage1 import suffix_forward, teacher_forcing_forward
+    from solarwm_b200.models.h3 import H3DiT
+
+    cfg = h3_preset("tiny")
+    model = H3DiT(cfg, device="cpu", dtype=torch.float32, seed=0)
+    s = h3_sample(latent_frames=4, height=4, width=4, prompt_len=6, text_dim=cfg.text_dim, seed=1)
+    clean = patchify_latents(s["target_latents"]).float()
+    anchor = patchify_latents(s["anchor_latents"]).float()
+    audio = torch.randn(6, cfg.audio_row_dim, generator=torch.Generator().manual_seed(5))
+    noisy = clean * 0.5 + torch.randn(clean.shape, generator=torch.Generator().manual_seed(2))
+    kw = dict(grid_hw=(2, 2), chunk_latents=2, window_chunks=1, cameras=torch.eye(4).repeat(5, 1, 1))
+    t0, t1 = torch.tensor([0.3, 0.7]), torch.tensor([0.4, 0.6])
+    common = dict(prompt=s["prompt_embeds"].float(), anchor_rows=anchor, clean_rows=clean, noisy_rows=noisy)
+    with torch.no_grad():
+        prefix = []
+        with_audio = teacher_forcing_forward(model, t_chunks=t0, audio_rows=audio, t_audio=0.4, capture=prefix, **common, **kw)
+        without = teacher_forcing_forward(model, t_chunks=t0, **common, **kw)
+        other_time = teacher_forcing_forward(model, t_chunks=t0, audio_rows=audio, t_audio=0.8, **common, **kw)
+        assert with_audio.shape == without.shape == clean.shape
+        assert not torch.allclose(with_audio, without, atol=1e-4) and not torch.allclose(with_audio, other_time, atol=1e-5)
+        assert prefix[0][0].shape[1] == 6 + anchor.shape[0] + 6 + clean.shape[0]
+        want = teacher_forcing_forward(model, t_chunks=t1, audio_rows=audio, t_audio=0.4, **common, **kw)
+        got = suffix_forward(model, captured=prefix, noisy_rows=noisy, t_chunks=t1, n_text=6, n_anchor=anchor.shape[0], n_audio=6, **kw)
+    assert torch.allclose(got, want, atol=2e-5, rtol=1e-4)
+
+    cfg.lora_rank = 4
+    for objective in ("tf_fm", "anyflow"):
+        losses = {}
+        for silent in (False, True):
+            tr = H3Stage1Trainer(cfg, "cpu", objective=objective, chunk_latents=2, window_chunks=1, lr=1e-3, seed=3,
+                                 diffusion_ratio=0.0, consistency_ratio=0.5)
+            for p in tr.model.trainable_parameters():
+                torch.nn.init.normal_(p, std=0.02, generator=torch.Generator().manual_seed(p.numel()))
+            if silent:
+                tr.silence = audio
+            before = [p.detach().clone() for p in tr.model.trainable_parameters()]
+            losses[silent] = float(tr.train_step(dict(s, camera_w2c=kw["cameras"])))
+            assert losses[silent] == losses[silent]
+            assert any(not torch.equal(a, b) for a, b in zip(before, tr.model.trainable_parameters()))
+        assert losses[False] != losses[True]
