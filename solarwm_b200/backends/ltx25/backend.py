@@ -22,17 +22,31 @@ def _arch(config):
     return ltx_preset(arch) if isinstance(arch, str) else ltx_preset("tiny")
 
 
+def load_base_weights(model, spec):
+    """``spec``: None, a path, or ``{path, allow_unplaced: [...], allow_missing: [...]}``.  Returns the load report."""
+    if not spec:
+        return None
+    from .loader import load_video_core
+
+    spec = {"path": spec} if isinstance(spec, (str, bytes)) or hasattr(spec, "__fspath__") else dict(spec)
+    return load_video_core(model, spec["path"], allow_unplaced=tuple(spec.get("allow_unplaced", ())),
+                           allow_missing=tuple(spec.get("allow_missing", ())))
+
+
 class LTXTrainer:
     """One rectified-flow step: sigma sampling, clean first frame, DiT, masked loss, fused AdamW."""
 
-    def __init__(self, cfg, device, lr=1e-4, seed=0, sp=None, checkpointing="none", lora_rank=0, lora_alpha=None):
+    def __init__(self, cfg, device, lr=1e-4, seed=0, sp=None, checkpointing="none", lora_rank=0, lora_alpha=None, base_weights=None):
         """``lora_rank > 0``: the base is frozen and low-rank adapters on the q / k / v / out projections of both
-        attentions and on both FFN linears train instead (``models/lora.py``), under an fp32-master AdamW."""
+        attentions and on both FFN linears train instead (``models/lora.py``), under an fp32-master AdamW.
+        ``base_weights``: ``model.base_weights`` of the run configuration (a released-layout checkpoint that replaces
+        the seeded base before any adapter is attached)."""
         dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
         self.model = LTXDiT(cfg, device=device, dtype=dtype, seed=seed)
         with torch.no_grad():                  # seeded by the run, not by the process-wide stream: a resumed run rebuilds the same base
             head = self.model.get_parameter("head.head.weight")
             head.copy_(torch.randn(head.shape, generator=torch.Generator().manual_seed(int(seed) * 7919 + 5)).mul_(0.02).to(head))
+        self.base_report = load_base_weights(self.model, base_weights)
         if sp is not None:
             self.model.sp = sp
         self.sp = sp
@@ -347,13 +361,16 @@ class LTX25Backend:
             from .runtime import adapter_weights
 
             meta, state, verified = adapter_weights(ck["resume_from"], str(ck.get("weight_source", "ema")))
-            model = LTXTrainer(_arch(config), dev, seed=trainer_seed).model
+            model = LTXTrainer(_arch(config), dev, seed=trainer_seed, base_weights=config["model"].get("base_weights")).model
             lora = inject_lora(model, rank=int(meta["rank"]), alpha=float(meta["alpha"]))
             lora.load_state_dict({k: v.to(dev) for k, v in state.items()}, broadcast=False)
             lora.merge_()
             weights_id = verified.manifest_digest
         else:
             model = LTXDiT(_arch(config), device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32)
+            report = load_base_weights(model, config["model"].get("base_weights"))
+            if report is not None:
+                weights_id = "released:" + report.header_digest
         cases = [InferenceCase(i, f"case-{i}", "synthetic", 0, 1000 + i, "none") for i in range(int(config.get("inference", {}).get("cases", 1)))]
         s = InferenceEngine(_Adapter(model, config)).run(cases, weights_id=weights_id, output_dir=output_root(config) / "generate")
         return {"output_dir": str(s.output_dir), "cases": s.cases, "weights_id": weights_id}

@@ -62,7 +62,8 @@ class LTXTrainingRuntime:
         fsdp = train.get("fsdp", {}) or {}
         ac = fsdp.get("activation_checkpointing", False)
         self.core = LTXTrainer(self.arch, self.device, lr=float(o.get("lr", 1e-4)), seed=self.seed, sp=self.ctx.sp,
-                               checkpointing=("full" if ac is True else (ac or "none")), lora_rank=int(adapter["rank"]), lora_alpha=adapter.get("alpha"))
+                               checkpointing=("full" if ac is True else (ac or "none")), lora_rank=int(adapter["rank"]), lora_alpha=adapter.get("alpha"),
+                               base_weights=config["model"].get("base_weights"))
         self.core.gen.manual_seed(objective_seed(self.seed, topo.dp_rank))
         self.optimizer, self.lora = self.core.opt, self.core.lora
         self.clip = float(o.get("grad_clip", 1.0))
